@@ -1,0 +1,290 @@
+"""CPU oracle for the attention + Gated-DeltaNet path (TEST INFRASTRUCTURE ONLY).
+
+ctypes/numpy front end of ``oracle/tt_oracle.c`` (own restatement) and, when
+it has been built, of ``oracle/_ref/libtinytitan_ref.so`` (the reference's two
+delta-rule C kernels compiled unmodified from their sources). Only the test
+suite, the smoke check and the bench's CPU-baseline leg may import this
+package; the product library never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_f32p = C.POINTER(C.c_float)
+_u8p = C.POINTER(C.c_uint8)
+
+
+def build(quiet: bool = True) -> None:
+    """Compile liboracle.so (and _ref when the reference tree is present)."""
+    subprocess.run(["make", "-C", _HERE], check=True,
+                   stdout=subprocess.DEVNULL if quiet else None)
+
+
+def _load(path: str):
+    return C.CDLL(path) if os.path.exists(path) else None
+
+
+_lib = None
+_ref = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        so = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(so):
+            build()
+        _lib = C.CDLL(so)
+        _lib.tt_oracle_max_threads.restype = C.c_int
+        _lib.tt_oracle_delta_rule_chunk.restype = C.c_int
+        _lib.tt_oracle_gdn_scan_heads.restype = C.c_int
+        _lib.tt_oracle_cpu_engine_attention_batch.restype = C.c_int
+        _lib.tt_oracle_cpu_engine_attention_head.restype = C.c_int
+    return _lib
+
+
+def ref():
+    """The compiled reference kernels, or None when oracle/_ref was not built."""
+    global _ref
+    if _ref is None:
+        _ref = _load(os.path.join(_HERE, "_ref", "libtinytitan_ref.so"))
+        if _ref is not None:
+            _ref.tinytitan_delta_rule_chunk.restype = C.c_int
+    return _ref
+
+
+def max_threads() -> int:
+    return int(lib().tt_oracle_max_threads())
+
+
+def _f(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(_f32p)
+
+
+# --------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------
+def attn_decode(q, k, v, n_kv_heads: int, scale: float, window: int = -1) -> np.ndarray:
+    """q [Hq,hd], k/v [S,Hkv,hd] -> [Hq,hd] (materialised-softmax reference)."""
+    q, k, v = _f(q), _f(k), _f(v)
+    hq, hd = q.shape
+    s = k.shape[0]
+    out = np.empty((hq, hd), np.float32)
+    lib().tt_oracle_attn_decode(_p(q), _p(k), _p(v), hd, hq, n_kv_heads, s, window,
+                                C.c_float(scale), _p(out))
+    return out
+
+
+def attn_decode_split(q, k, v, n_kv_heads: int, scale: float, seq_len: int, kv_start: int = 0,
+                      keep=None, ring_capacity: int = 0, n_chunks: int = 16,
+                      kv_stride: int | None = None) -> np.ndarray:
+    """Split-KV partial + combine form; k/v are [rows, kv_stride] fp32."""
+    q = _f(q)
+    hq, hd = q.shape
+    k = _f(k).reshape(k.shape[0], -1)
+    v = _f(v).reshape(v.shape[0], -1)
+    stride = kv_stride or k.shape[1]
+    out = np.empty((hq, hd), np.float32)
+    kp = None
+    if keep is not None:
+        keep = np.ascontiguousarray(keep, dtype=np.uint8)
+        kp = keep.ctypes.data_as(_u8p)
+    lib().tt_oracle_attn_decode_split(_p(q), _p(k), _p(v), hd, hq, n_kv_heads, C.c_size_t(stride),
+                                      seq_len, kv_start, C.c_float(scale), kp, ring_capacity,
+                                      n_chunks, _p(out))
+    return out
+
+
+def attn_partial(q_row, k, v, n_kv_heads: int, kv_head: int, p_start: int, p_end: int,
+                 scale: float, keep=None, ring_capacity: int = 0):
+    q_row = _f(q_row)
+    hd = q_row.shape[0]
+    k = _f(k).reshape(k.shape[0], -1)
+    v = _f(v).reshape(v.shape[0], -1)
+    m = C.c_float()
+    d = C.c_float()
+    o = np.empty(hd, np.float32)
+    kp = None
+    if keep is not None:
+        keep = np.ascontiguousarray(keep, dtype=np.uint8)
+        kp = keep.ctypes.data_as(_u8p)
+    lib().tt_oracle_attn_partial(_p(q_row), _p(k), _p(v), hd, n_kv_heads, kv_head,
+                                 C.c_size_t(k.shape[1]), p_start, p_end, C.c_float(scale), kp,
+                                 ring_capacity, C.byref(m), C.byref(d), _p(o))
+    return m.value, d.value, o
+
+
+def attn_combine(m, d, o) -> np.ndarray:
+    m, d, o = _f(m), _f(d), _f(o)
+    n, hd = o.shape
+    out = np.empty(hd, np.float32)
+    lib().tt_oracle_attn_combine(_p(m), _p(d), _p(o), n, hd, _p(out))
+    return out
+
+
+def attn_prefill(q, k, v, q_stride: int, kv_stride: int, head_dim: int, q_heads: int,
+                 kv_heads: int, start: int, chunk: int, kv_valid: int, window: int,
+                 scale: float, threads: int = 0) -> np.ndarray:
+    """Strided causal prefill reference; q/k/v are flat fp32 buffers; out [T,Hq,hd]."""
+    q, k, v = _f(q).ravel(), _f(k).ravel(), _f(v).ravel()
+    out = np.empty((chunk, q_heads, head_dim), np.float32)
+    lib().tt_oracle_attn_prefill(_p(q), _p(k), _p(v), C.c_size_t(q_stride), C.c_size_t(kv_stride),
+                                 head_dim, q_heads, kv_heads, start, chunk, kv_valid, window,
+                                 C.c_float(scale), threads or max_threads(), _p(out))
+    return out
+
+
+def cpu_engine_attention(query, keys, values, kv_heads: int, scale: float, threads: int = 1):
+    """The reference CPU engine's decode attention: query [H,dim], keys/values [S,Hkv*dim]."""
+    query, keys, values = _f(query), _f(keys), _f(values)
+    heads, dim = query.shape
+    cached = keys.shape[0]
+    out = np.empty((heads, dim), np.float32)
+    lib().tt_oracle_cpu_engine_attention(_p(query), _p(keys), _p(values), heads, kv_heads, dim,
+                                         cached, C.c_float(scale), threads, _p(out))
+    return out
+
+
+def cpu_engine_attention_sessions(query, keys, values, cached, row_base, kv_heads: int,
+                                  scale: float, threads: int):
+    """query [N,H,dim]; keys/values one shared fp32 store [rows, Hkv*dim]."""
+    query, keys, values = _f(query), _f(keys), _f(values)
+    n, heads, dim = query.shape
+    cached = np.ascontiguousarray(cached, dtype=np.int32)
+    row_base = np.ascontiguousarray(row_base, dtype=np.int64)
+    out = np.empty((n, heads, dim), np.float32)
+    lib().tt_oracle_cpu_engine_attention_sessions(
+        _p(query), _p(keys), _p(values), cached.ctypes.data_as(C.POINTER(C.c_int)),
+        row_base.ctypes.data_as(C.POINTER(C.c_longlong)), n, heads, kv_heads, dim,
+        C.c_float(scale), threads, _p(out))
+    return out
+
+
+def cpu_engine_attention_batch(query, keys, values, kv_heads: int, base_position: int,
+                               scale: float, threads: int = 0):
+    """Batched prefill attention of the CPU engine. query [T,H,dim]; keys/values [P,Hkv*dim]."""
+    query, keys, values = _f(query), _f(keys), _f(values)
+    t, heads, dim = query.shape
+    positions = keys.shape[0]
+    out = np.empty((t, heads, dim), np.float32)
+    rc = lib().tt_oracle_cpu_engine_attention_batch(
+        _p(query), t, heads, dim, _p(keys), _p(values), positions, kv_heads, base_position,
+        C.c_float(scale), threads or max_threads(), _p(out))
+    if rc:
+        raise RuntimeError(f"attention mask limit past the cache (rc={rc})")
+    return out
+
+
+# --------------------------------------------------------------------------
+# gated delta rule
+# --------------------------------------------------------------------------
+def _delta_rule_call(fn, query, key, value, a, b, decay_log, decay_bias, key_heads, inverse, state):
+    query, key, value = _f(query).ravel(), _f(key).ravel(), _f(value)
+    heads, dv = value.shape
+    dk = key.size // key_heads
+    a, b, decay_log, decay_bias = _f(a), _f(b), _f(decay_log), _f(decay_bias)
+    state = np.array(state, dtype=np.float32, copy=True).reshape(heads, dv, dk)
+    readout = np.empty((heads, dv), np.float32)
+    fn(_p(query), _p(key), _p(value), _p(a), _p(b), _p(decay_log), _p(decay_bias),
+       C.c_size_t(heads), C.c_size_t(key_heads), C.c_size_t(dk), C.c_size_t(dv),
+       C.c_float(inverse), _p(state), _p(readout))
+    return readout, state
+
+
+def delta_rule(query, key, value, a, b, decay_log, decay_bias, key_heads, inverse, state):
+    """Own restatement of the CPU one-token rule. Returns (readout [H,dv], new state)."""
+    return _delta_rule_call(lib().tt_oracle_delta_rule, query, key, value, a, b, decay_log,
+                            decay_bias, key_heads, inverse, state)
+
+
+def ref_delta_rule(query, key, value, a, b, decay_log, decay_bias, key_heads, inverse, state):
+    """The compiled reference kernel tinytitan_delta_rule."""
+    return _delta_rule_call(ref().tinytitan_delta_rule, query, key, value, a, b, decay_log,
+                            decay_bias, key_heads, inverse, state)
+
+
+def _chunk_call(fn, queries, keys, values, alphas, betas, state):
+    queries, keys, values = _f(queries), _f(keys), _f(values)
+    alphas, betas = _f(alphas), _f(betas)
+    t, dk = keys.shape
+    dv = values.shape[1]
+    state = np.array(state, dtype=np.float32, copy=True).reshape(dv, dk)
+    ro = np.empty((t, dv), np.float32)
+    rc = fn(_p(queries), C.c_size_t(dk), _p(keys), C.c_size_t(dk), _p(values), C.c_size_t(dv),
+            _p(alphas), C.c_size_t(1), _p(betas), C.c_size_t(1), C.c_size_t(t), C.c_size_t(dk),
+            C.c_size_t(dv), _p(state), _p(ro), C.c_size_t(dv))
+    if rc:
+        raise MemoryError("chunk kernel scratch allocation failed")
+    return ro, state
+
+
+def delta_rule_chunk(queries, keys, values, alphas, betas, state):
+    """Own restatement of the chunked rule, one head. Returns (readouts [T,dv], state)."""
+    return _chunk_call(lib().tt_oracle_delta_rule_chunk, queries, keys, values, alphas, betas, state)
+
+
+def ref_delta_rule_chunk(queries, keys, values, alphas, betas, state):
+    return _chunk_call(ref().tinytitan_delta_rule_chunk, queries, keys, values, alphas, betas, state)
+
+
+def gdn_step_rows(conv_out, a, b, a_log, dt_bias, hk, hv, dk, dv, state, a_preexp=False,
+                  v_tiled=False, readout_scale=1.0, want_checkpoint=False):
+    """GPU-kernel form of the rule over rows sequentially (all-fp32 arithmetic).
+
+    conv_out [rows, C] with C >= 2*hk*dk + hv*dv; a/b [rows, hv]. Returns
+    (y [rows, hv*dv], state', checkpoint or None)."""
+    conv_out = _f(conv_out)
+    rows, stride = conv_out.shape
+    a, b, a_log, dt_bias = _f(a).reshape(rows, hv), _f(b).reshape(rows, hv), _f(a_log), _f(dt_bias)
+    state = np.array(state, dtype=np.float32, copy=True).reshape(hv, dv, dk)
+    ck = np.empty_like(state) if want_checkpoint else None
+    y = np.empty((rows, hv * dv), np.float32)
+    lib().tt_oracle_gdn_step_rows(_p(conv_out), C.c_size_t(stride), _p(a), _p(b), _p(a_log),
+                                  _p(dt_bias), hk, hv, dk, dv, rows, int(a_preexp), int(v_tiled),
+                                  C.c_float(readout_scale), _p(state),
+                                  _p(ck) if ck is not None else None, _p(y))
+    return y, state, ck
+
+
+def gdn_scan_heads(q, k, v, alpha, beta, hk, hv, dk, dv, chunk, state, threads=0, use_ref=False):
+    """Chunked scan over all heads. q/k [T,hk*dk], v [T,hv*dv], alpha/beta [T,hv]."""
+    q, k, v, alpha, beta = _f(q), _f(k), _f(v), _f(alpha), _f(beta)
+    t = q.shape[0]
+    state = np.array(state, dtype=np.float32, copy=True).reshape(hv, dv, dk)
+    y = np.empty((t, hv * dv), np.float32)
+    fn = None
+    if use_ref:
+        fn = C.cast(ref().tinytitan_delta_rule_chunk, C.c_void_p)
+    rc = lib().tt_oracle_gdn_scan_heads(fn, _p(q), _p(k), _p(v), _p(alpha), _p(beta), t, hk, hv,
+                                        dk, dv, chunk, threads or max_threads(), _p(state), _p(y))
+    if rc:
+        raise MemoryError("chunk kernel scratch allocation failed")
+    return y, state
+
+
+def delta_rule_sessions(query, key, value, a, b, decay_log, decay_bias, key_heads, inverse, state,
+                        threads=0, use_ref=False):
+    """One-token CPU rule over N sessions. query/key [N,Hk*dk], value [N,H,dv], a/b [N,H]."""
+    query, key, value, a, b = _f(query), _f(key), _f(value), _f(a), _f(b)
+    decay_log, decay_bias = _f(decay_log), _f(decay_bias)
+    n, heads, dv = value.shape
+    dk = key.shape[1] // key_heads
+    state = np.array(state, dtype=np.float32, copy=True).reshape(n, heads, dv, dk)
+    ro = np.empty((n, heads, dv), np.float32)
+    fn = None
+    if use_ref:
+        fn = C.cast(ref().tinytitan_delta_rule_range, C.c_void_p)
+    lib().tt_oracle_delta_rule_sessions(fn, _p(query), _p(key), _p(value), _p(a), _p(b),
+                                        _p(decay_log), _p(decay_bias), n, heads, key_heads, dk, dv,
+                                        C.c_float(inverse), threads or max_threads(), _p(state),
+                                        _p(ro))
+    return ro, state
