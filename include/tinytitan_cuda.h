@@ -1,0 +1,372 @@
+/*
+ * tinytitan_cuda.h -- C ABI of the B200 (sm_100a) attention / Gated-DeltaNet
+ * library that stands behind TinyTitan's attention operator entry points.
+ *
+ * The header is strict C99 so that a SwiftPM C target can import it the way
+ * the reference imports its own C kernels (Package.swift:105-124). Every entry
+ * point names the reference interface it replaces (file:line inside the
+ * TinyTitan source tree).
+ *
+ * Conventions
+ *   - Device buffers are plain pointers; "MTLBuffer + byte offset" of the
+ *     reference becomes pointer arithmetic done by the caller.
+ *   - `tt_stream` is a cudaStream_t. Every op ENQUEUES on that stream and
+ *     returns (the reference's encode-into-a-command-buffer semantics);
+ *     ordering is stream order.
+ *   - Every function returns an int status (TT_OK == 0); creators return NULL
+ *     and set *out_err. Nothing traps, throws or writes to stdout/stderr.
+ *   - A context belongs to one device and is not re-entrant: two threads must
+ *     not enqueue through the same context at once (the reference's operators
+ *     are not re-entrant either, Attention.swift:173-192).
+ *   - There is no CPU fallback: without a usable CUDA device the ops fail with
+ *     TT_ERR_CUDA.
+ */
+#ifndef TINYTITAN_CUDA_H
+#define TINYTITAN_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tt_context tt_context;
+typedef struct tt_kv_cache tt_kv_cache;
+typedef struct tt_gdn_state tt_gdn_state;
+typedef void *tt_stream;
+
+enum tt_status {
+    TT_OK = 0,
+    TT_ERR_INVALID_ARG = 1,       /* the reference's precondition failures */
+    TT_ERR_UNSUPPORTED_SHAPE = 2, /* refused outright, never silently skipped */
+    TT_ERR_OOM = 3,               /* ModelError.residentBufferWrapFailed */
+    TT_ERR_CUDA = 4,
+    TT_ERR_TIMEOUT = 5,
+    TT_ERR_BUSY = 6
+};
+
+enum tt_dtype { TT_F16 = 0, TT_BF16 = 1 };
+
+/* ---------------------------------------------------------------- context */
+
+typedef struct tt_context_options {
+    size_t workspace_bytes; /* split-KV partials; 0 selects 192 MiB */
+    uint32_t max_sessions;  /* rows of one batched call; 0 selects 1024 */
+    uint32_t reserved;
+} tt_context_options;
+
+/* Replaces MetalContext + the per-operator scratch the Swift classes own
+ * (sources/TinyTitan/Kernels/Attention/Attention.swift:140-156): all device
+ * scratch is allocated here, never on the decode path. */
+tt_context *tt_context_create(int device, const tt_context_options *options, int *out_err);
+void tt_context_destroy(tt_context *ctx);
+/* Text of the last failure seen through this context (never NULL). */
+const char *tt_last_error_string(const tt_context *ctx);
+const char *tt_status_string(int status);
+/* Asynchronous device-side status word (bounded waits that ran out, unsupported
+ * work reached on the device). 0 when clean. Synchronises the stream. */
+int tt_ctx_poll_status(tt_context *ctx, tt_stream stream, uint32_t *out_flags);
+int tt_stream_synchronize(tt_context *ctx, tt_stream stream);
+/* Number of kernels this context has launched since creation (diagnostic). */
+uint64_t tt_ctx_launch_count(const tt_context *ctx);
+/* Per-kernel device timing, the counterpart of the reference's per-command-buffer
+ * GPU timestamps (EngineRunner.kernelGPUTimingSummary, EngineRunner.swift:58-66;
+ * TINYTITAN_KERNEL_SPLIT in RealForwardRunner+DecodeGEMV.swift:29-50). While
+ * enabled, every split-KV pass-1 launch is bracketed by a pair of events on its
+ * own stream (up to 256 launches are kept). tt_ctx_profile_collect waits for the
+ * recorded events, writes the durations in milliseconds, returns how many there
+ * were in *out_count and clears the record. */
+int tt_ctx_profile_enable(tt_context *ctx, int enabled);
+int tt_ctx_profile_collect(tt_context *ctx, float *out_ms, uint32_t capacity, uint32_t *out_count);
+
+/* ------------------------------------------------- decode attention (SDPA) */
+
+/* KVView's format fields (KVCacheManager.swift:20-43). Only bits == 16 (fp16 or
+ * bf16 rows) is implemented; 8 / 4 are refused with TT_ERR_UNSUPPORTED_SHAPE. */
+typedef struct tt_kv_format {
+    uint32_t bits;
+    uint32_t stride_bytes; /* bytes per token row; 0 means n_kv_heads*head_dim*2 */
+    uint32_t value_bytes;
+    uint32_t group_size;
+} tt_kv_format;
+
+/* One query row against one session's cache. Replaces Attention.encodeFull and
+ * Attention.encodeSWA -> encodeSplit (Attention.swift:233-470) and the kernels
+ * attention_decode_partial / attention_decode_combine
+ * (sources/TinyTitanCore/Metal/Attention/attention.metal:162-269, :395-437).
+ * q,out: [n_q_heads, head_dim] fp16. k,v: logical position 0 of the session's
+ * rows, row p at p*stride (or (p % ring_capacity)*stride). Keys attended are
+ * [kv_start, seq_len); keep_mask[p]==0 drops key p. An empty range writes
+ * zeros. SWA callers pass kv_start = seq_len > window ? seq_len - window : 0. */
+int tt_attn_decode(tt_context *ctx, tt_stream stream, const void *q, const void *k,
+                   const void *v, void *out, uint32_t head_dim, uint32_t n_q_heads,
+                   uint32_t n_kv_heads, uint32_t seq_len, uint32_t kv_start, float scale,
+                   const tt_kv_format *kv_format, const uint8_t *keep_mask,
+                   uint32_t ring_capacity);
+
+/* One session of a batched / few-token decode step. Row r of `q_rows` sits at
+ * base position seq_len - q_rows + r and attends keys
+ * [kv_start, seq_len - (q_rows - 1 - r)), which is the decode-order verify rule
+ * of RealForwardRunner+VerifyDecodeOrderAttention.swift:84-105. */
+typedef struct tt_attn_session {
+    const void *q;   /* [q_rows] rows, q_row_stride elements apart */
+    void *out;       /* [q_rows] rows, out_row_stride elements apart */
+    const void *k;   /* position 0 of this session's K rows */
+    const void *v;
+    uint32_t seq_len; /* keys visible to the LAST row (cursor + q_rows) */
+    uint32_t q_rows;  /* 1 for plain decode; up to 64/(Hq/Hkv) per kernel pass */
+    uint32_t kv_start;
+    uint32_t reserved;
+} tt_attn_session;
+
+typedef struct tt_attn_batch_params {
+    uint32_t head_dim, n_q_heads, n_kv_heads;
+    uint32_t kv_token_stride_elements; /* >= n_kv_heads*head_dim */
+    uint32_t q_row_stride_elements;    /* >= n_q_heads*head_dim */
+    uint32_t out_row_stride_elements;
+    float scale;
+    uint32_t io_dtype; /* tt_dtype of q, k, v, out */
+} tt_attn_batch_params;
+
+/* Replaces the per-row loop of RealForwardRunner+BatchAttention.swift:165-218
+ * (N serial encodeFull calls) with one launch pair over all sessions; work is
+ * split by KV bytes, not by session. `sessions` is host memory and may be
+ * reused as soon as the call returns. */
+int tt_attn_decode_batched(tt_context *ctx, tt_stream stream, const tt_attn_session *sessions,
+                           uint32_t n_sessions, const tt_attn_batch_params *params);
+
+/* Split-KV halves exposed for a KV range that lives on several GPUs: pass 1
+ * leaves ONE unnormalised (m, d, o) triple per q head for keys
+ * [kv_start, seq_len) of this device (the chunk-partial format of
+ * attention.metal:146-159), pass 2 merges n_parts such triples
+ * (attention.metal:395-437). m,d: [n_parts][n_q_heads] fp32; o:
+ * [n_parts][n_q_heads][head_dim] fp32. */
+int tt_attn_decode_partial(tt_context *ctx, tt_stream stream, const void *q, const void *k,
+                           const void *v, uint32_t head_dim, uint32_t n_q_heads,
+                           uint32_t n_kv_heads, uint32_t seq_len, uint32_t kv_start, float scale,
+                           uint32_t kv_token_stride_elements, uint32_t io_dtype, float *m_out,
+                           float *d_out, float *o_out);
+int tt_attn_combine(tt_context *ctx, tt_stream stream, const float *m, const float *d,
+                    const float *o, uint32_t n_parts, uint32_t n_q_heads, uint32_t head_dim,
+                    void *out, uint32_t io_dtype);
+
+/* Split geometry of the reference, kept for callers and tests that pin it
+ * (Attention.splitGeometry, Attention.swift:196-227). This library's own split
+ * is chosen per call from the byte count; any partition of the key range is
+ * legal because the result is defined by the merge. */
+typedef struct tt_split_geometry {
+    uint32_t effective_length, num_chunks, chunk_length, partial_threadgroups;
+    uint32_t use_swa_grouped_partial;
+} tt_split_geometry;
+void tt_attn_reference_split_geometry(uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t seq_len,
+                                      uint32_t kv_start, int prefer_gqa_swa,
+                                      tt_split_geometry *out);
+
+/* The split this library would use (host-only arithmetic, no device needed):
+ * keys per work item and number of work items for a batch with the given
+ * per-session key counts. */
+int tt_attn_plan_splits(const uint32_t *keys_per_session, const uint32_t *q_rows_per_session,
+                        uint32_t n_sessions, uint32_t head_dim, uint32_t n_q_heads,
+                        uint32_t n_kv_heads, uint32_t sm_count, size_t workspace_bytes,
+                        uint32_t *out_keys_per_item, uint32_t *out_n_items);
+
+/* ------------------------------------------------------- prefill attention */
+
+/* Field for field the reference's PrefillAttentionParams
+ * (sources/TinyTitan/Kernels/Attention/PrefillAttention.swift:5-21; MSL mirror
+ * sources/TinyTitanCore/Metal/Prefill/prefill.metal:754-770). */
+typedef struct tt_prefill_params {
+    uint32_t start_position;
+    uint32_t query_count;
+    uint32_t head_dim;
+    uint32_t n_q_heads;
+    uint32_t n_kv_heads;
+    uint32_t kv_valid_count;
+    uint32_t sliding_window; /* 0 = none */
+    uint32_t kv_token_stride_elements;
+    uint32_t q_token_stride_elements;
+    uint32_t o_token_stride_elements;
+    float scale;
+    uint32_t kv_bits; /* 16 only */
+    uint32_t kv_token_stride_bytes;
+    uint32_t kv_value_bytes;
+    uint32_t kv_group_size;
+} tt_prefill_params;
+
+/* Replaces PrefillAttention.encodeCausal (PrefillAttention.swift:165-258) and
+ * the kernels attention_prefill_causal_q8 / _tiled (prefill.metal:1056-1313).
+ * Query t is at absolute position start_position + t and sees keys
+ * [first, min(kv_valid_count, start_position + t + 1)). Shapes whose strides
+ * and base pointers are 16-byte aligned with head_dim 256 run on the
+ * tcgen05/TMA kernel; everything else runs on a generic CUDA kernel. */
+int tt_attn_prefill_causal(tt_context *ctx, tt_stream stream, const void *q, const void *k,
+                           const void *v, void *out, const tt_prefill_params *params,
+                           uint32_t kv_ring_capacity, uint32_t io_dtype);
+/* Which kernel the call above would take: 0 generic, 1 tcgen05. */
+int tt_attn_prefill_path(const void *q, const void *k, const void *v, const void *out,
+                         const tt_prefill_params *params, uint32_t kv_ring_capacity);
+
+/* ------------------------------------------------------ Gated DeltaNet ops */
+
+enum tt_gdn_flags {
+    TT_GDN_A_LOG_PREEXP = 1, /* `a_log` already holds -exp(A_log) (GGUF ssm_a) */
+    TT_GDN_V_TILED = 2,      /* key head = h % Hk instead of h / (Hv/Hk) */
+    TT_GDN_GATES_F32 = 4     /* a,b hold per-token alpha,beta as fp32 (the
+                                tinytitan_delta_rule_chunk calling form) */
+};
+
+/* LinearAttentionConfig's geometry
+ * (sources/TinyTitanCore/Format/ModelTypes+Configs.swift:147-188) and the two
+ * storage conventions of GDNStorageConvention.swift:7-25. */
+typedef struct tt_gdn_shape {
+    uint32_t n_k_heads, n_v_heads, key_dim, value_dim;
+    uint32_t flags;
+    float readout_scale; /* y = (S q) * readout_scale; 1.0 on the GPU path */
+} tt_gdn_shape;
+
+/* `rows` tokens applied one after another with the state carried; rows == 1 is
+ * GDN.encodeDeltaStepDecode -> gdn_delta_step_decode
+ * (sources/TinyTitan/Kernels/GDN/GDN.swift:318-347,
+ * sources/TinyTitanCore/Metal/GDN/gdn.metal:529-585); rows > 1 is
+ * GDN.encodeDeltaStepPrefill -> gdn_delta_step_prefill (GDN.swift:351-396,
+ * gdn.metal:590-669), exact sequential arithmetic.
+ * conv_out: fp16 [rows][row_stride] = [q: Hk*Dk | k: Hk*Dk | v: Hv*Dv | ...];
+ * a,b: fp16 [rows][Hv]; a_log, dt_bias: bf16 [Hv]; state: fp32 [Hv][Dv][Dk]
+ * updated in place; y: fp16 [rows][Hv*Dv]; checkpoint_state (nullable)
+ * receives the state after row 0. */
+int tt_gdn_step(tt_context *ctx, tt_stream stream, const void *conv_out, const void *a,
+                const void *b, const void *a_log, const void *dt_bias, float *state, void *y,
+                const tt_gdn_shape *shape, uint32_t rows, uint32_t row_stride,
+                float *checkpoint_state);
+
+typedef struct tt_gdn_session {
+    const void *conv_out;
+    const void *a;
+    const void *b;
+    float *state;
+    void *y;
+    float *checkpoint_state; /* nullable */
+} tt_gdn_session;
+
+/* The same step over many independent sessions in one launch (the per-row
+ * loops of RealForwardRunner+VerifyDecodeOrderAttention.swift:166-189 and
+ * RealForwardRunner+BatchAttention.swift). */
+int tt_gdn_step_batched(tt_context *ctx, tt_stream stream, const tt_gdn_session *sessions,
+                        uint32_t n_sessions, const void *a_log, const void *dt_bias,
+                        const tt_gdn_shape *shape, uint32_t rows, uint32_t row_stride);
+
+/* Chunk-parallel prefill scan: the same recurrence evaluated `chunk` tokens at
+ * a time (the algorithm of tinytitan_delta_rule_chunk,
+ * sources/TinyTitanKernelsC/gdn_chunk.c:72-195, on tensor cores). Same
+ * arguments as tt_gdn_step; agrees with it to rounding, not bit for bit.
+ * chunk must be 64. */
+int tt_gdn_scan_chunked(tt_context *ctx, tt_stream stream, const void *conv_out, const void *a,
+                        const void *b, const void *a_log, const void *dt_bias, float *state,
+                        void *y, const tt_gdn_shape *shape, uint32_t rows, uint32_t row_stride,
+                        uint32_t chunk);
+
+/* ------------------------------------------------------------- allocators */
+
+/* Where the managers get memory. NULL selects CUDA device memory on the
+ * current device; a host implementation lets the bookkeeping be tested without
+ * a GPU. copy/zero return 0 on success. */
+typedef struct tt_allocator {
+    void *user;
+    void *(*alloc)(void *user, size_t bytes);
+    void (*release)(void *user, void *ptr);
+    int (*copy)(void *user, void *dst, const void *src, size_t bytes);
+    int (*zero)(void *user, void *dst, size_t bytes);
+} tt_allocator;
+
+/* The part of ArchConfig the managers read. layer_kind[i]: 0 sliding-window,
+ * 1 full attention, 2 linear (ArchConfig.fullAttentionLayerMask). */
+typedef struct tt_arch {
+    uint32_t n_layers;
+    const uint8_t *layer_kind;
+    uint32_t n_kv_heads, head_dim;           /* sliding-window layers */
+    uint32_t n_full_kv_heads, full_head_dim; /* full-attention layers */
+    uint32_t sliding_window;
+    uint32_t gdn_k_heads, gdn_v_heads, gdn_key_dim, gdn_value_dim, gdn_conv_kernel;
+} tt_arch;
+
+typedef struct tt_kv_view {
+    void *buffer;              /* the layer's K (or V) allocation */
+    size_t offset;             /* byte offset of logical position 0 of the slot */
+    uint32_t stride;           /* bytes per token */
+    uint32_t valid_token_count;
+    uint32_t precision_bits;
+    uint32_t value_bytes;
+    uint32_t group_size;
+    uint32_t ring_capacity;    /* 0 unless a ring-backed sliding-window layer */
+} tt_kv_view;
+
+/* KVCacheManager.rowLayout (KVCacheManager+Validation.swift:30-41): bytes per
+ * token row and bytes of packed values for `elements` values at 16/8/4 bits. */
+void tt_kv_row_layout(uint32_t elements, uint32_t precision_bits, uint32_t *out_stride,
+                      uint32_t *out_value_bytes);
+
+/* KVCacheManager.init (sources/TinyTitan/Runtime/KVCache/KVCacheManager.swift:
+ * 161-333): per non-linear layer one K and one V allocation of
+ * slots*capacity*stride bytes; capacity starts at min(max_context, 8192). */
+tt_kv_cache *tt_kv_cache_create(const tt_arch *arch, uint32_t max_context, uint32_t slots,
+                                uint32_t precision_bits, int fp16_ring_enabled,
+                                uint32_t max_prefill_chunk_tokens, const tt_allocator *allocator,
+                                int *out_err);
+void tt_kv_cache_destroy(tt_kv_cache *cache);
+/* reserve(tokens:slot:) (KVCacheManager+Storage.swift:92-139): doubling growth
+ * that keeps min(capacity, position[s]) rows of every slot. Views and slot
+ * pointers fetched earlier are invalid afterwards. */
+int tt_kv_cache_reserve(tt_kv_cache *cache, uint32_t tokens, uint32_t slot);
+/* kSlot / vSlot (:161-211): where the projection writes position `position`. */
+int tt_kv_cache_k_slot(tt_kv_cache *cache, uint32_t layer, uint32_t position, uint32_t slot,
+                       void **out_ptr);
+int tt_kv_cache_v_slot(tt_kv_cache *cache, uint32_t layer, uint32_t position, uint32_t slot,
+                       void **out_ptr);
+/* keyView / valueView (KVCacheManager+Views.swift:11-72). */
+int tt_kv_cache_key_view(tt_kv_cache *cache, uint32_t layer, uint32_t slot,
+                         uint32_t valid_token_count, tt_kv_view *out_view);
+int tt_kv_cache_value_view(tt_kv_cache *cache, uint32_t layer, uint32_t slot,
+                           uint32_t valid_token_count, tt_kv_view *out_view);
+/* advance / rewind / reset / reset(slot:) (KVCacheManager+Storage.swift:272-337):
+ * cursors only; rows are never cleared. */
+int tt_kv_cache_advance(tt_kv_cache *cache, uint32_t slot, uint32_t count);
+int tt_kv_cache_rewind(tt_kv_cache *cache, uint32_t slot, uint32_t new_position);
+int tt_kv_cache_reset(tt_kv_cache *cache);
+int tt_kv_cache_reset_slot(tt_kv_cache *cache, uint32_t slot);
+uint32_t tt_kv_cache_position(const tt_kv_cache *cache, uint32_t slot);
+uint32_t tt_kv_cache_capacity(const tt_kv_cache *cache, uint32_t layer);
+uint32_t tt_kv_cache_stride(const tt_kv_cache *cache, uint32_t layer);
+uint32_t tt_kv_cache_layer_kind(const tt_kv_cache *cache, uint32_t layer);
+size_t tt_kv_cache_buffer_length(const tt_kv_cache *cache, uint32_t layer);
+/* worstCaseBytes: every non-linear layer at max_context, K and V, all slots. */
+size_t tt_kv_cache_worst_case_bytes(const tt_arch *arch, uint32_t max_context,
+                                    uint32_t precision_bits, uint32_t slots);
+
+/* GDNStateManager (sources/TinyTitan/Runtime/KVCache/GDNStateManager.swift:
+ * 18-354): per linear layer a zero-initialised fp32 state buffer of
+ * slots*Hv*Dv*Dk*4 bytes and an fp16 conv-tail buffer of
+ * slots*(K-1)*qkvDim*2 bytes, optional checkpoint twins. */
+tt_gdn_state *tt_gdn_state_create(const tt_arch *arch, uint32_t slots,
+                                  int enable_speculative_checkpoint,
+                                  const tt_allocator *allocator, int *out_err);
+void tt_gdn_state_destroy(tt_gdn_state *state);
+int tt_gdn_state_state_slot(tt_gdn_state *state, uint32_t layer, uint32_t slot, void **out_ptr);
+int tt_gdn_state_conv_tail_slot(tt_gdn_state *state, uint32_t layer, uint32_t slot,
+                                void **out_ptr);
+int tt_gdn_state_speculative_state_slot(tt_gdn_state *state, uint32_t layer, uint32_t slot,
+                                        void **out_ptr);
+int tt_gdn_state_reset(tt_gdn_state *state);
+int tt_gdn_state_reset_slot(tt_gdn_state *state, uint32_t slot);
+/* encodeSpeculativeRestore (:265-292): checkpoint twins -> live buffers. */
+int tt_gdn_state_speculative_restore(tt_gdn_state *state);
+size_t tt_gdn_state_bytes_per_layer(const tt_gdn_state *state);
+size_t tt_gdn_state_conv_tail_bytes_per_layer(const tt_gdn_state *state);
+int tt_gdn_state_is_linear(const tt_gdn_state *state, uint32_t layer);
+size_t tt_gdn_state_worst_case_bytes(const tt_arch *arch, uint32_t slots);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TINYTITAN_CUDA_H */

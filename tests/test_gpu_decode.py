@@ -1,0 +1,221 @@
+"""Decode SDPA through the C ABI against the CPU oracle (B200 only)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import tinytitan_b200 as tt
+from oracle.prng import seed_tree_key
+from gpu_util import TOL, context, dev, host, rounded, bf16_tol
+
+pytestmark = pytest.mark.gpu
+
+
+def _decode(q, k, v, hkv, scale=None, seq_len=None, **kw):
+    hq, hd = q.shape
+    s = k.shape[0] if seq_len is None else seq_len
+    qd, kd, vd = dev(q), dev(k), dev(v)
+    out = torch.full((hq, hd), float("nan"), device="cuda", dtype=torch.float16)
+    attn = tt.Attention(context())
+    window = kw.pop("window", None)
+    if window is not None:
+        attn.encode_swa(qd, kd, vd, out, hd, hq, hkv, s, window, scale=scale, **kw)
+    else:
+        attn.encode_full(qd, kd, vd, out, hd, hq, hkv, s, scale=scale, **kw)
+    torch.cuda.synchronize()
+    assert context().poll_status() == 0
+    return host(out)
+
+
+@pytest.mark.parametrize("root,label,hd,hq,hkv,s,aliased", [
+    (0x174, "attn-h8-kv1-d64-T128-kv=false", 64, 8, 1, 128, False),
+    (0x175, "attn-h16-kv2-d256-T128-kv=false", 256, 16, 2, 128, False),
+    (0x176, "attn-h8-kv1-d64-T128-kv=true", 64, 8, 1, 128, True),
+    (0x177, "attn-h16-kv2-d256-T128-kv=true", 256, 16, 2, 128, True),
+])
+def test_reference_seeded_cases(root, label, hd, hq, hkv, s, aliased):
+    # tests/TinyTitan/Kernels/Attention/AttentionTests.swift:399-425 (reference bar: rel < 1e-2)
+    g = seed_tree_key(root, label)
+    q = rounded(g.uniform_array(hq * hd, -0.5, 0.5).reshape(hq, hd))
+    k = rounded(g.uniform_array(s * hkv * hd, -0.5, 0.5).reshape(s, hkv, hd))
+    v = k if aliased else rounded(g.uniform_array(s * hkv * hd, -0.5, 0.5).reshape(s, hkv, hd))
+    want = oracle.attn_decode(q, k, v, hkv, 1.0 / np.sqrt(hd))
+    got = _decode(q, k, v, hkv)
+    assert np.abs(got - want).max() <= TOL
+    assert np.abs(got - want).max() / np.abs(want).max() < 1e-2
+
+
+def test_runtime_scale_is_honoured():
+    # AttentionTests.swift:59-123: scale 1.0 differs from the default-scale result
+    g = seed_tree_key(0x501, "attn-scale1-swa")
+    hd, hq, hkv, s = 64, 4, 2, 8
+    q = rounded(g.uniform_array(hq * hd, -0.5, 0.5).reshape(hq, hd))
+    k = rounded(g.uniform_array(s * hkv * hd, -0.5, 0.5).reshape(s, hkv, hd))
+    v = rounded(g.uniform_array(s * hkv * hd, -0.5, 0.5).reshape(s, hkv, hd))
+    got1 = _decode(q, k, v, hkv, scale=1.0, window=8)
+    want1 = oracle.attn_decode(q, k, v, hkv, 1.0, window=8)
+    assert np.abs(got1 - want1).max() <= TOL
+    got_default = _decode(q, k, v, hkv, window=8)
+    assert np.abs(got1 - got_default).max() > 1e-3
+
+
+@pytest.mark.parametrize("hd,hq,hkv,s", [(256, 8, 2, 4096), (256, 16, 2, 1), (256, 16, 2, 17), (128, 8, 8, 300),
+                                          (64, 4, 2, 1000), (256, 24, 2, 700), (256, 32, 2, 2049)])
+def test_shapes_normal_inputs(hd, hq, hkv, s):
+    r = np.random.default_rng(hd + hq + s)
+    q = rounded(r.normal(size=(hq, hd))); k = rounded(r.normal(size=(s, hkv, hd))); v = rounded(r.normal(size=(s, hkv, hd)))
+    scale = 1.0 / np.sqrt(hd)
+    want = oracle.attn_decode(q, k, v, hkv, scale)
+    got = _decode(q, k, v, hkv, scale=scale)
+    assert np.abs(got - want).max() <= TOL
+
+
+def test_sliding_window_ring_and_keep_mask():
+    r = np.random.default_rng(7)
+    hd, hq, hkv, s = 256, 16, 2, 900
+    q = rounded(r.normal(size=(hq, hd))); k = rounded(r.normal(size=(s, hkv, hd))); v = rounded(r.normal(size=(s, hkv, hd)))
+    scale = 0.0625
+    # window
+    want = oracle.attn_decode(q, k, v, hkv, scale, window=129)
+    assert np.abs(_decode(q, k, v, hkv, scale=scale, window=129) - want).max() <= TOL
+    # ring: logical p at row p % cap
+    cap = 160
+    rk = np.zeros((cap, hkv, hd), np.float32); rv = np.zeros((cap, hkv, hd), np.float32)
+    for p in range(s):
+        rk[p % cap] = k[p]; rv[p % cap] = v[p]
+    want = oracle.attn_decode(q, k, v, hkv, scale, window=128)
+    got = _decode(q, rk, rv, hkv, scale=scale, seq_len=s, window=128, ring_capacity=cap)
+    assert np.abs(got - want).max() <= TOL
+    # sparse keep mask (SimdPartialAttentionTests.swift:15-35: empty chunks must not NaN)
+    for frac in (0.55, 0.02):
+        keep = (r.uniform(size=s) < frac).astype(np.uint8); keep[-1] = 1
+        want = oracle.attn_decode_split(q, k, v, hkv, scale, s, keep=keep)
+        got = _decode(q, k, v, hkv, scale=scale, keep_mask=torch.as_tensor(keep).cuda())
+        assert np.isfinite(got).all() and np.abs(got - want).max() <= TOL
+    # everything masked -> zeros (attention.metal:418-424)
+    got = _decode(q, k, v, hkv, scale=scale, keep_mask=torch.zeros(s, dtype=torch.uint8, device="cuda"))
+    assert np.all(got == 0)
+
+
+def _batched_case(r, n, hq, hkv, hd, lens, q_rows, dtype=torch.float16, stride_pad=0):
+    """Sessions packed into one KV store of the reference layout: slot s at row s*capacity."""
+    cap = max(lens) + 8
+    stride = hkv * hd + stride_pad
+    kbuf = np.zeros((n * cap, stride), np.float32); vbuf = np.zeros((n * cap, stride), np.float32)
+    kbuf[:, :hkv * hd] = r.normal(size=(n * cap, hkv * hd)); vbuf[:, :hkv * hd] = r.normal(size=(n * cap, hkv * hd))
+    kbuf = rounded(kbuf, dtype); vbuf = rounded(vbuf, dtype)
+    q = rounded(r.normal(size=(n, q_rows, hq * hd)), dtype)
+    return cap, stride, kbuf, vbuf, q
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_batched_ragged_sessions(dtype):
+    r = np.random.default_rng(11)
+    n, hq, hkv, hd = 9, 16, 2, 256
+    lens = [int(x) for x in r.integers(1, 3000, size=n)]
+    lens[0], lens[1] = 1, 2999
+    cap, stride, kbuf, vbuf, q = _batched_case(r, n, hq, hkv, hd, lens, 1, dtype, stride_pad=8)
+    kd, vd, qd = dev(kbuf, dtype), dev(vbuf, dtype), dev(q, dtype)
+    out = torch.full((n, 1, hq * hd), float("nan"), device="cuda", dtype=dtype)
+    esz = 2
+    sessions = [tt.DecodeSession(qd, out, kd, vd, lens[i], 1, 0, q_offset=i * hq * hd * esz,
+                                 out_offset=i * hq * hd * esz, k_offset=i * cap * stride * esz,
+                                 v_offset=i * cap * stride * esz) for i in range(n)]
+    tt.Attention(context()).encode_batched(sessions, hd, hq, hkv, kv_token_stride_elements=stride, scale=0.0625)
+    torch.cuda.synchronize()
+    assert context().poll_status() == 0
+    got = host(out)
+    for i in range(n):
+        kk = kbuf[i * cap:i * cap + lens[i], :hkv * hd].reshape(lens[i], hkv, hd)
+        vv = vbuf[i * cap:i * cap + lens[i], :hkv * hd].reshape(lens[i], hkv, hd)
+        want = oracle.attn_decode(q[i, 0].reshape(hq, hd), kk, vv, hkv, 0.0625).reshape(-1)
+        tol = TOL if dtype == torch.float16 else bf16_tol(want)
+        assert np.all(np.abs(got[i, 0] - want) <= tol), (i, lens[i], np.abs(got[i, 0] - want).max())
+
+
+@pytest.mark.parametrize("hq,q_rows", [(16, 4), (32, 4), (8, 2), (24, 3)])
+def test_few_token_verify_rows(hq, q_rows):
+    # Row r of W at base position P attends keys [0, P + r]
+    # (RealForwardRunner+VerifyDecodeOrderAttention.swift:84-105): equal to W single-row decodes.
+    r = np.random.default_rng(hq * 10 + q_rows)
+    n, hkv, hd = 3, 2, 256
+    lens = [600 + q_rows, 64 + q_rows, q_rows]   # seq_len counts the draft rows themselves
+    cap, stride, kbuf, vbuf, q = _batched_case(r, n, hq, hkv, hd, lens, q_rows)
+    kd, vd, qd = dev(kbuf), dev(vbuf), dev(q)
+    out = torch.full((n, q_rows, hq * hd), float("nan"), device="cuda", dtype=torch.float16)
+    sessions = [tt.DecodeSession(qd, out, kd, vd, lens[i], q_rows, 0, q_offset=i * q_rows * hq * hd * 2,
+                                 out_offset=i * q_rows * hq * hd * 2, k_offset=i * cap * stride * 2,
+                                 v_offset=i * cap * stride * 2) for i in range(n)]
+    tt.Attention(context()).encode_batched(sessions, hd, hq, hkv, scale=0.0625)
+    torch.cuda.synchronize()
+    assert context().poll_status() == 0
+    got = host(out)
+    for i in range(n):
+        for w in range(q_rows):
+            vis = lens[i] - (q_rows - 1 - w)
+            kk = kbuf[i * cap:i * cap + vis].reshape(vis, hkv, hd); vv = vbuf[i * cap:i * cap + vis].reshape(vis, hkv, hd)
+            want = oracle.attn_decode(q[i, w].reshape(hq, hd), kk, vv, hkv, 0.0625).reshape(-1)
+            assert np.abs(got[i, w] - want).max() <= TOL, (i, w)
+
+
+def test_partial_and_combine_across_shards():
+    # A KV range split over G "devices": each produces one (m, d, o) triple per head, the merge
+    # equals attention over the whole range (config 4's exchange, done here on one GPU).
+    r = np.random.default_rng(3)
+    hq, hkv, hd, s, shards = 16, 2, 256, 5000, 4
+    q = rounded(r.normal(size=(hq, hd))); k = rounded(r.normal(size=(s, hkv, hd))); v = rounded(r.normal(size=(s, hkv, hd)))
+    qd, kd, vd = dev(q), dev(k), dev(v)
+    m = torch.zeros(shards, hq, device="cuda"); d = torch.zeros(shards, hq, device="cuda")
+    o = torch.zeros(shards, hq, hd, device="cuda")
+    attn = tt.Attention(context())
+    bounds = [0, 1300, 1300, 3700, s]   # shard 1 is empty on purpose
+    for g in range(shards):
+        lo, hi = bounds[g], bounds[g + 1]
+        attn.encode_partial(qd, kd, vd, hd, hq, hkv, hi, lo, m[g], d[g], o[g], scale=0.0625)
+    out = torch.empty(hq, hd, device="cuda", dtype=torch.float16)
+    attn.encode_combine(m, d, o, shards, hq, hd, out)
+    torch.cuda.synchronize()
+    want = oracle.attn_decode(q, k, v, hkv, 0.0625)
+    assert np.abs(host(out) - want).max() <= TOL
+    assert np.isinf(host(m[1])).all() and np.all(host(d[1]) == 0)   # empty shard: (-inf, 0, 0)
+    # the partial format is the reference's: m = max score, d = sum exp(s - m)
+    mo, do_, oo = oracle.attn_partial(q[3], k.reshape(s, -1), v.reshape(s, -1), hkv, 0, 0, 1300, 0.0625)
+    assert abs(host(m[0])[3] - mo) < 1e-3 and abs(host(d[0])[3] - do_) / do_ < 2e-3
+
+
+def test_rejects_bad_arguments():
+    attn = tt.Attention(context())
+    x = torch.zeros(16, 256, device="cuda", dtype=torch.float16)
+    kv = torch.zeros(8, 2, 256, device="cuda", dtype=torch.float16)
+    with pytest.raises(tt.InvalidArgument):
+        attn.encode_full(x, kv, kv, x, 256, 16, 3, 8)          # 16 % 3 != 0
+    with pytest.raises(tt.InvalidArgument):
+        attn.encode_full(x, kv, kv, x, 256, 16, 2, 0)          # needs one KV position
+    with pytest.raises(tt.UnsupportedShape):
+        attn.encode_full(x, kv, kv, x, 256, 16, 2, 8, kv_format=tt.KVFormat(bits=8, stride=544))
+    with pytest.raises(tt.UnsupportedShape):
+        attn.encode_full(x, kv, kv, x, 96, 16, 2, 8)           # head_dim without a kernel: refused, not skipped
+
+
+def test_large_batch_property_partition_invariance():
+    # At full config-2 size the oracle is too slow; the result must not depend on how the key
+    # range is partitioned: one batched call (library split) vs explicit shards merged by combine.
+    r = torch.Generator(device="cuda"); r.manual_seed(5)
+    hq, hkv, hd, s = 16, 2, 256, 32768
+    q = torch.randn(hq, hd, device="cuda", generator=r).half()
+    k = torch.randn(s, hkv, hd, device="cuda", generator=r).half()
+    v = torch.randn(s, hkv, hd, device="cuda", generator=r).half()
+    attn = tt.Attention(context())
+    out_a = torch.empty(hq, hd, device="cuda", dtype=torch.float16)
+    attn.encode_full(q, k, v, out_a, hd, hq, hkv, s, scale=0.0625)
+    m = torch.zeros(3, hq, device="cuda"); d = torch.zeros(3, hq, device="cuda"); o = torch.zeros(3, hq, hd, device="cuda")
+    for g, (lo, hi) in enumerate([(0, 10000), (10000, 10001), (10001, s)]):
+        attn.encode_partial(q, k, v, hd, hq, hkv, hi, lo, m[g], d[g], o[g], scale=0.0625)
+    out_b = torch.empty_like(out_a)
+    attn.encode_combine(m, d, o, 3, hq, hd, out_b)
+    torch.cuda.synchronize()
+    assert (out_a.float() - out_b.float()).abs().max().item() <= 1e-3
+    # and against a float64 statement of the same softmax on the device
+    sc = torch.einsum("hd,shd->hs", q.double(), k.double().repeat_interleave(hq // hkv, dim=1)) * 0.0625
+    ref = torch.einsum("hs,shd->hd", torch.softmax(sc, dim=1), v.double().repeat_interleave(hq // hkv, dim=1))
+    assert (out_a.double() - ref).abs().max().item() <= TOL

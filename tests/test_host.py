@@ -1,0 +1,215 @@
+"""Host-side logic and the C ABI surface, without a GPU."""
+import ctypes
+import os
+import re
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import tinytitan_b200 as tt
+from tinytitan_b200 import _lib as L
+from tinytitan_b200 import sharding
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "tinytitan_cuda.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(tt_[a-z0-9_]+)\s*\(", header))
+    assert len(declared) >= 45
+    handle = ctypes.CDLL(L.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(handle, name), f"{name} is declared but not exported"
+    assert declared == set(L.SIGNATURES), declared ^ set(L.SIGNATURES)
+
+
+def test_header_is_strict_c99():
+    # the reference's own flag set for its C target (Package.swift:108-118)
+    src = '#include "tinytitan_cuda.h"\nint main(void) { tt_prefill_params p; (void)p; return (int)TT_OK; }\n'
+    r = subprocess.run(["gcc", "-std=c99", "-pedantic-errors", "-Wall", "-Wextra", "-Werror", "-fsyntax-only",
+                        "-I", os.path.join(ROOT, "include"), "-x", "c", "-"], input=src.encode(), capture_output=True)
+    assert r.returncode == 0, r.stderr.decode()
+
+
+def test_reference_split_geometry_numbers():
+    # tests/TinyTitan/Kernels/Attention/AttentionTests.swift:27-51
+    g = tt.Attention.split_geometry(16, 2, 1536, 0, False)
+    assert (g.num_chunks, g.chunk_length, g.partial_threadgroups) == (16, 96, 256)
+    g = tt.Attention.split_geometry(16, 2, 5, 0, False)
+    assert (g.num_chunks, g.chunk_length) == (5, 1)
+    g = tt.Attention.split_geometry(4, 2, 1024, 0, True)       # q_per_kv 2 -> grouped SWA partial
+    assert g.use_swa_grouped_partial and g.num_chunks == 16 and g.partial_threadgroups == 2 * 16
+    g = tt.Attention.split_geometry(16, 2, 1024, 512, True)    # q_per_kv 8 -> per-q-head split
+    assert not g.use_swa_grouped_partial and g.effective_length == 512 and g.num_chunks == 16
+
+
+def _plan(keys, rows, hd=256, hq=16, hkv=2, sms=148, ws=192 << 20):
+    n = len(keys)
+    k = (ctypes.c_uint32 * n)(*keys); r = (ctypes.c_uint32 * n)(*rows)
+    per, items = ctypes.c_uint32(0), ctypes.c_uint32(0)
+    rc = L.lib().tt_attn_plan_splits(k, r, n, hd, hq, hkv, sms, ws, ctypes.byref(per), ctypes.byref(items))
+    return rc, per.value, items.value
+
+
+def test_split_planner():
+    rng = np.random.default_rng(0)
+    keys = [int(x) for x in rng.integers(1024, 32769, size=32)]
+    rc, per, items = _plan(keys, [1] * 32)
+    assert rc == 0 and per % 64 == 0 and 256 <= per <= 16384
+    assert items == sum(-(-k // per) for k in keys) * 2
+    assert 4 * 148 <= items <= 16 * 148            # enough items to balance, not so many that merges dominate
+    # a single short session is not split below the minimum item length
+    rc, per, items = _plan([4096], [1], hq=8)
+    assert rc == 0 and per == 256 and items == 16 * 2
+    # an empty range still yields one (empty) item per kv head
+    rc, per, items = _plan([0], [1])
+    assert rc == 0 and items == 2
+    # 64 packed rows (4 draft rows x group 16) -> 4 row tiles per kv head
+    rc, per, items = _plan([16384] * 64, [4] * 64, hq=32)
+    assert rc == 0 and items == 64 * 2 * 4 * (-(-16384 // per))
+    # workspace too small for even one part per session -> OOM status, never a silent truncation
+    rc, _, _ = _plan([100000] * 8, [1] * 8, ws=1024)
+    assert rc == L.TT_ERR_OOM
+
+
+def test_context_without_gpu_fails_loudly():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(tt.TinyTitanError):
+        tt.Context(0)
+
+
+def test_kv_row_layout_pins():
+    # tests/TinyTitan/Kernels/Attention/KVCacheQuantizedAttentionTests.swift:86-101 (2 heads x 256)
+    assert tt.KVCacheManager.row_layout(512, 16) == (1024, 1024)
+    assert tt.KVCacheManager.row_layout(512, 8) == (544, 512)
+    assert tt.KVCacheManager.row_layout(512, 4) == (288, 256)
+    assert tt.KVCacheManager.row_layout(65, 4) == (34 + 2 * 4, 34)
+
+
+def _read(ptr, n):
+    return bytes((ctypes.c_ubyte * n).from_address(ptr))
+
+
+def _write(ptr, data: bytes):
+    ctypes.memmove(ptr, data, len(data))
+
+
+def test_kv_cache_manager_bookkeeping_on_host_memory():
+    # KVCacheManagerTests / KVCacheGrowthTests (tests/TinyTitan/Runtime/KVCache): strides, disjoint
+    # linear slot regions, independent cursors, doubling growth that keeps every slot's rows,
+    # rewind moves only the cursor, per-slot reset.
+    cfg = tt.ArchConfig.qwen36_35b_a3b()
+    kv = tt.KVCacheManager(cfg, max_context=40000, slots=3, allocator="host")
+    full = [i for i, k in enumerate(cfg.layer_kinds) if k == tt.FULL]
+    assert len(full) == 10 and kv.layer_kind(0) == tt.LINEAR and kv.stride(0) == 0
+    layer = full[0]
+    assert kv.stride(layer) == 1024 and kv.capacity(layer) == 8192
+    assert kv.buffer_length(layer) == 3 * 8192 * 1024
+    base = kv.key_view(layer, 0).buffer
+    assert kv.k_slot(layer, 0, 1) - base == 8192 * 1024              # slot regions are linear in the slot
+    assert kv.k_slot(layer, 5, 2) - base == (2 * 8192 + 5) * 1024
+    assert kv.v_slot(layer, 0, 0) != kv.k_slot(layer, 0, 0)           # K and V never alias
+    with pytest.raises(tt.InvalidArgument):
+        kv.k_slot(0, 0, 0)                                            # linear layers have no KV slots
+    with pytest.raises(tt.InvalidArgument):
+        kv.k_slot(layer, 8192, 0)                                     # beyond capacity: reserve first
+    with pytest.raises(tt.InvalidArgument):
+        kv.k_slot(layer, 0, 3)
+    rows = {0: b"\x11" * 1024, 1: b"\x22" * 1024, 2: b"\x33" * 1024}
+    for slot, n in ((0, 3), (1, 8192), (2, 1)):
+        _write(kv.k_slot(layer, n - 1, slot), rows[slot]); _write(kv.v_slot(layer, n - 1, slot), rows[slot][::-1])
+        kv.advance(slot, n)
+    assert [kv.position(s) for s in range(3)] == [3, 8192, 1]
+    kv.reserve(8193, slot=1)
+    assert kv.capacity(layer) == 16384 and kv.capacity(full[-1]) == 16384
+    for slot, n in ((0, 3), (1, 8192), (2, 1)):
+        assert _read(kv.k_slot(layer, n - 1, slot), 1024) == rows[slot]
+        view = kv.key_view(layer, slot)
+        assert view.offset == slot * 16384 * 1024 and view.valid_token_count == n and view.stride == 1024
+    kv.reserve(10 ** 9, slot=0)                                       # clamped to maxContext
+    assert kv.capacity(layer) == 40000
+    kv.rewind(2, slot=0)
+    assert kv.position(0) == 2 and _read(kv.k_slot(layer, 2, 0), 1024) == rows[0]   # rows stay
+    with pytest.raises(tt.InvalidArgument):
+        kv.rewind(5, slot=0)
+    kv.reset(slot=1)
+    assert [kv.position(s) for s in range(3)] == [2, 0, 1]
+    kv.reset()
+    assert [kv.position(s) for s in range(3)] == [0, 0, 0]
+    with pytest.raises(tt.InvalidArgument):
+        kv.advance(0, 40001)
+    assert tt.KVCacheManager.worst_case_bytes(cfg, 32768, 16, 32) == 10 * 2 * 32 * 32768 * 1024
+    kv.close()
+    with pytest.raises(tt.InvalidArgument):
+        tt.KVCacheManager(cfg, 1024, slots=257, allocator="host")
+
+
+def test_kv_cache_ring_and_quantised_strides():
+    cfg = tt.ArchConfig([tt.SWA, tt.FULL], 8, 256, 2, 512, sliding_window=1024)
+    kv = tt.KVCacheManager(cfg, max_context=100000, fp16_ring_enabled=True, max_prefill_chunk_tokens=128,
+                           allocator="host")
+    assert kv.capacity(0) == 1024 + 128 and kv.capacity(1) == 8192
+    assert kv.key_view(0, 0, 10).ring_capacity == 1152 and kv.key_view(1, 0, 10).ring_capacity == 0
+    base = kv.key_view(0).buffer
+    assert kv.k_slot(0, 1152 + 7, 0) - base == 7 * kv.stride(0)       # physicalSlot = position % capacity
+    kv.reserve(20000)
+    assert kv.capacity(0) == 1152 and kv.capacity(1) == 32768         # rings never grow
+    kv.close()
+    kv8 = tt.KVCacheManager(cfg, 4096, precision=8, allocator="host")
+    assert kv8.stride(1) == tt.KVCacheManager.row_layout(2 * 512, 8)[0] == 1024 + 16 * 4
+    assert kv8.key_view(1, 0, 0).value_bytes == 1024
+    kv8.close()
+
+
+def test_gdn_state_manager_on_host_memory():
+    # GDNStateManagerTests (tests/TinyTitan/Runtime/KVCache/GDNStateManagerTests.swift:29-95)
+    cfg = tt.ArchConfig.qwen36_35b_a3b()
+    g = tt.GDNStateManager(cfg, slots=3, enable_speculative_checkpoint=True, allocator="host")
+    assert g.state_bytes_per_layer == 32 * 128 * 128 * 4 == 2 << 20
+    assert g.conv_tail_bytes_per_layer == 3 * 8192 * 2 == 49152
+    assert g.is_linear(0) and not g.is_linear(3)
+    with pytest.raises(tt.InvalidArgument):
+        g.state_slot(3, 0)
+    with pytest.raises(tt.InvalidArgument):
+        g.state_slot(0, 3)
+    s0, s2 = g.state_slot(0, 0), g.state_slot(0, 2)
+    assert s2 - s0 == 2 * g.state_bytes_per_layer
+    assert g.conv_tail_slot(0, 1) - g.conv_tail_slot(0, 0) == g.conv_tail_bytes_per_layer
+    assert _read(s0, 4096) == b"\0" * 4096                            # the empty state is all zeros
+    _write(s0, b"\x7f" * 64); _write(s2, b"\x55" * 64)
+    g.reset(slot=0)
+    assert _read(s0, 64) == b"\0" * 64 and _read(s2, 64) == b"\x55" * 64
+    _write(g.speculative_state_slot(0, 0), b"\x42" * 64)
+    g.speculative_restore()
+    assert _read(s0, 64) == b"\x42" * 64 and _read(s2, 64) == b"\x55" * 64
+    g.reset()
+    assert _read(s2, 64) == b"\0" * 64
+    assert tt.GDNStateManager.worst_case_bytes(cfg, 2) == 2 * 30 * ((2 << 20) + 49152)
+    g.close()
+    g2 = tt.GDNStateManager(cfg, slots=1, allocator="host")
+    with pytest.raises(tt.InvalidArgument):
+        g2.speculative_restore()                                      # no checkpoint twins: invalid layout
+    g2.close()
+
+
+def test_session_sharding_and_kv_ranges():
+    rng = np.random.default_rng(1)
+    lens = [int(x) for x in rng.integers(1024, 32769, size=32)]
+    for world in (1, 2, 4, 8):
+        shards = sharding.shard_sessions(lens, world)
+        assert sorted(i for s in shards for i in s) == list(range(32))
+        loads = [sum(lens[i] for i in s) for s in shards]
+        assert max(loads) - min(loads) <= max(lens)                   # greedy balance bound
+        rr = sharding.shard_sessions(lens, world, "round_robin")
+        assert all(i % world == r for r, s in enumerate(rr) for i in s)
+    for world in (1, 2, 4, 8, 3):
+        ranges = sharding.kv_split_ranges(262144, world)
+        assert ranges[0][0] == 0 and ranges[-1][1] == 262144
+        assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+    assert sharding.kv_split_ranges(3, 8)[4:] == [(3, 3)] * 4             # empty trailing ranks
+    assert sharding.kv_split_ranges(10, 2, kv_start=4) == [(4, 7), (7, 10)]

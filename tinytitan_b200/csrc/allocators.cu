@@ -1,0 +1,410 @@
+// KV-cache and Gated-DeltaNet state managers.
+//
+// Re-statement of the bookkeeping of KVCacheManager
+// (sources/TinyTitan/Runtime/KVCache/KVCacheManager.swift:62-333, +Storage.swift:18-339,
+// +Views.swift:11-72, +Validation.swift:12-81) and GDNStateManager
+// (sources/TinyTitan/Runtime/KVCache/GDNStateManager.swift:18-354) over plain device
+// allocations: the byte layouts (slot regions, strides, doubling growth, zero-initialised
+// state) are the reference's, so the kernels read exactly what the reference's would.
+// Memory comes through a tt_allocator so the same code runs on host memory in CPU-only tests.
+#include "tt_common.h"
+
+#include <new>
+#include <vector>
+
+namespace {
+
+void *cuda_alloc(void *, size_t bytes) {
+    void *p = nullptr;
+    if (cudaMalloc(&p, bytes ? bytes : 1) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return p;
+}
+void cuda_release(void *, void *p) { cudaFree(p); }
+int cuda_copy(void *, void *dst, const void *src, size_t bytes) {
+    return cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToDevice) == cudaSuccess ? 0 : 1;
+}
+int cuda_zero(void *, void *dst, size_t bytes) { return cudaMemset(dst, 0, bytes) == cudaSuccess ? 0 : 1; }
+
+const tt_allocator kCudaAllocator = {nullptr, cuda_alloc, cuda_release, cuda_copy, cuda_zero};
+
+constexpr uint32_t kMaximumSlots = 256;            // KVCacheManager.maximumSlots
+constexpr uint32_t kInitialCapacityTokens = 8192;  // KVCacheManager.initialCapacityTokens
+constexpr uint32_t kQuantGroup = 64;               // KVCacheManager.quantizationGroupSize
+
+bool allocator_ok(const tt_allocator *a) {
+    return a->alloc != nullptr && a->release != nullptr && a->copy != nullptr && a->zero != nullptr;
+}
+
+}  // namespace
+
+TT_API void tt_kv_row_layout(uint32_t elements, uint32_t precision_bits, uint32_t *out_stride,
+                             uint32_t *out_value_bytes) {
+    uint32_t stride, value_bytes;
+    if (precision_bits == 16) {
+        stride = value_bytes = elements * 2;
+    } else {
+        const uint32_t packed = (elements * precision_bits + 7) / 8;
+        const uint32_t aligned = (packed + 1) & ~1u;
+        const uint32_t groups = (elements + kQuantGroup - 1) / kQuantGroup;
+        stride = aligned + groups * 2 * 2;  // fp16 scale + fp16 bias per group, after the values
+        value_bytes = aligned;
+    }
+    if (out_stride) *out_stride = stride;
+    if (out_value_bytes) *out_value_bytes = value_bytes;
+}
+
+struct tt_kv_cache {
+    tt_allocator alloc;
+    uint32_t max_context = 0, slots = 0, precision_bits = 16;
+    bool ring = false;
+    std::vector<void *> k, v;
+    std::vector<uint32_t> stride, value_bytes, capacity;
+    std::vector<uint8_t> kind;  // 0 swa, 1 full, 2 linear
+    std::vector<uint32_t> position;
+};
+
+TT_API tt_kv_cache *tt_kv_cache_create(const tt_arch *arch, uint32_t max_context, uint32_t slots,
+                                       uint32_t precision_bits, int fp16_ring_enabled,
+                                       uint32_t max_prefill_chunk_tokens, const tt_allocator *allocator,
+                                       int *out_err) {
+    int err_local;
+    int *err = out_err ? out_err : &err_local;
+    *err = TT_OK;
+    if (arch == nullptr || arch->layer_kind == nullptr || arch->n_layers == 0 || max_context == 0 ||
+        max_prefill_chunk_tokens == 0 || slots == 0 || slots > kMaximumSlots ||
+        (precision_bits != 16 && precision_bits != 8 && precision_bits != 4) ||
+        (allocator != nullptr && !allocator_ok(allocator))) {
+        *err = TT_ERR_INVALID_ARG;
+        return nullptr;
+    }
+    tt_kv_cache *c = new (std::nothrow) tt_kv_cache();
+    if (c == nullptr) { *err = TT_ERR_OOM; return nullptr; }
+    c->alloc = allocator ? *allocator : kCudaAllocator;
+    c->max_context = max_context;
+    c->slots = slots;
+    c->precision_bits = precision_bits;
+    c->ring = fp16_ring_enabled != 0;
+    c->position.assign(slots, 0);
+    const uint32_t swa_elems = arch->n_kv_heads * arch->head_dim;
+    const uint32_t full_elems = arch->n_full_kv_heads * arch->full_head_dim;
+    uint32_t swa_capacity = arch->sliding_window + max_prefill_chunk_tokens;
+    if (swa_capacity < 1) swa_capacity = 1;
+    if (swa_capacity > max_context) swa_capacity = max_context;
+    for (uint32_t layer = 0; layer < arch->n_layers; ++layer) {
+        const uint8_t kind = arch->layer_kind[layer];
+        if (kind == 2) {  // linear layers keep no per-token rows
+            c->k.push_back(nullptr); c->v.push_back(nullptr);
+            c->stride.push_back(0); c->value_bytes.push_back(0); c->capacity.push_back(0);
+            c->kind.push_back(2);
+            continue;
+        }
+        const bool full = kind != 0;
+        uint32_t stride, vbytes;
+        tt_kv_row_layout(full ? full_elems : swa_elems, precision_bits, &stride, &vbytes);
+        uint32_t capacity = (c->ring && !full) ? swa_capacity
+                                               : (max_context < kInitialCapacityTokens ? max_context
+                                                                                       : kInitialCapacityTokens);
+        const size_t length = (size_t)slots * capacity * stride;
+        void *kb = c->alloc.alloc(c->alloc.user, length);
+        void *vb = kb ? c->alloc.alloc(c->alloc.user, length) : nullptr;
+        if (kb == nullptr || vb == nullptr) {
+            if (kb) c->alloc.release(c->alloc.user, kb);
+            tt_kv_cache_destroy(c);
+            *err = TT_ERR_OOM;
+            return nullptr;
+        }
+        c->k.push_back(kb); c->v.push_back(vb);
+        c->stride.push_back(stride); c->value_bytes.push_back(vbytes); c->capacity.push_back(capacity);
+        c->kind.push_back(full ? 1 : 0);
+    }
+    return c;
+}
+
+TT_API void tt_kv_cache_destroy(tt_kv_cache *c) {
+    if (c == nullptr) return;
+    for (size_t i = 0; i < c->k.size(); ++i) {
+        if (c->k[i]) c->alloc.release(c->alloc.user, c->k[i]);
+        if (c->v[i]) c->alloc.release(c->alloc.user, c->v[i]);
+    }
+    delete c;
+}
+
+TT_API int tt_kv_cache_reserve(tt_kv_cache *c, uint32_t tokens, uint32_t slot) {
+    if (c == nullptr || slot >= c->slots) return TT_ERR_INVALID_ARG;
+    uint32_t needed = tokens < 1 ? 1 : tokens;
+    if (needed > c->max_context) needed = c->max_context;
+    for (size_t layer = 0; layer < c->kind.size(); ++layer) {
+        if (c->kind[layer] == 2) continue;
+        if (c->ring && c->kind[layer] == 0) continue;  // a ring's capacity is its window
+        const uint32_t current = c->capacity[layer];
+        if (current >= needed) continue;
+        uint64_t target = current;
+        while (target < needed) target *= 2;
+        if (target > c->max_context) target = c->max_context;
+        const uint32_t stride = c->stride[layer];
+        const size_t length = (size_t)c->slots * target * stride;
+        void *nk = c->alloc.alloc(c->alloc.user, length);
+        void *nv = nk ? c->alloc.alloc(c->alloc.user, length) : nullptr;
+        if (nk == nullptr || nv == nullptr) {
+            if (nk) c->alloc.release(c->alloc.user, nk);
+            return TT_ERR_OOM;
+        }
+        for (uint32_t s = 0; s < c->slots; ++s) {
+            const uint32_t live = c->position[s] < current ? c->position[s] : current;
+            const size_t used = (size_t)live * stride;
+            if (used == 0) continue;
+            int bad = c->alloc.copy(c->alloc.user, (char *)nk + (size_t)s * target * stride,
+                                    (const char *)c->k[layer] + (size_t)s * current * stride, used);
+            bad |= c->alloc.copy(c->alloc.user, (char *)nv + (size_t)s * target * stride,
+                                 (const char *)c->v[layer] + (size_t)s * current * stride, used);
+            if (bad) {
+                c->alloc.release(c->alloc.user, nk);
+                c->alloc.release(c->alloc.user, nv);
+                return TT_ERR_CUDA;
+            }
+        }
+        c->alloc.release(c->alloc.user, c->k[layer]);
+        c->alloc.release(c->alloc.user, c->v[layer]);
+        c->k[layer] = nk; c->v[layer] = nv;
+        c->capacity[layer] = (uint32_t)target;
+    }
+    return TT_OK;
+}
+
+static int kv_slot(tt_kv_cache *c, bool value, uint32_t layer, uint32_t position, uint32_t slot, void **out) {
+    if (c == nullptr || out == nullptr || layer >= c->kind.size() || slot >= c->slots) return TT_ERR_INVALID_ARG;
+    if (c->kind[layer] == 2) return TT_ERR_INVALID_ARG;  // linear layers have no KV slots
+    if ((uint64_t)position + 1 > c->max_context) return TT_ERR_INVALID_ARG;
+    const uint32_t cap = c->capacity[layer];
+    const bool ring_layer = c->ring && c->kind[layer] == 0;
+    if (!ring_layer && position >= cap) return TT_ERR_INVALID_ARG;  // reserve() first
+    const size_t token = (size_t)slot * cap + position % cap;
+    *out = (char *)(value ? c->v[layer] : c->k[layer]) + token * c->stride[layer];
+    return TT_OK;
+}
+
+TT_API int tt_kv_cache_k_slot(tt_kv_cache *c, uint32_t layer, uint32_t position, uint32_t slot, void **out) {
+    return kv_slot(c, false, layer, position, slot, out);
+}
+TT_API int tt_kv_cache_v_slot(tt_kv_cache *c, uint32_t layer, uint32_t position, uint32_t slot, void **out) {
+    return kv_slot(c, true, layer, position, slot, out);
+}
+
+static int kv_view(tt_kv_cache *c, bool value, uint32_t layer, uint32_t slot, uint32_t valid, tt_kv_view *out) {
+    if (c == nullptr || out == nullptr || layer >= c->kind.size() || slot >= c->slots) return TT_ERR_INVALID_ARG;
+    if (valid > c->max_context) return TT_ERR_INVALID_ARG;
+    out->buffer = value ? c->v[layer] : c->k[layer];
+    out->offset = (size_t)slot * c->capacity[layer] * c->stride[layer];
+    out->stride = c->stride[layer];
+    out->valid_token_count = valid;
+    out->precision_bits = c->precision_bits;
+    out->value_bytes = c->value_bytes[layer];
+    out->group_size = kQuantGroup;
+    out->ring_capacity = (c->ring && c->kind[layer] == 0) ? c->capacity[layer] : 0;
+    return TT_OK;
+}
+
+TT_API int tt_kv_cache_key_view(tt_kv_cache *c, uint32_t layer, uint32_t slot, uint32_t valid, tt_kv_view *out) {
+    return kv_view(c, false, layer, slot, valid, out);
+}
+TT_API int tt_kv_cache_value_view(tt_kv_cache *c, uint32_t layer, uint32_t slot, uint32_t valid, tt_kv_view *out) {
+    return kv_view(c, true, layer, slot, valid, out);
+}
+
+TT_API int tt_kv_cache_advance(tt_kv_cache *c, uint32_t slot, uint32_t count) {
+    if (c == nullptr || slot >= c->slots) return TT_ERR_INVALID_ARG;
+    if ((uint64_t)c->position[slot] + count > c->max_context) return TT_ERR_INVALID_ARG;
+    c->position[slot] += count;
+    return TT_OK;
+}
+
+TT_API int tt_kv_cache_rewind(tt_kv_cache *c, uint32_t slot, uint32_t new_position) {
+    if (c == nullptr || slot >= c->slots) return TT_ERR_INVALID_ARG;
+    if (new_position > c->position[slot]) return TT_ERR_INVALID_ARG;
+    c->position[slot] = new_position;  // rows stay; a later pass overwrites them
+    return TT_OK;
+}
+
+TT_API int tt_kv_cache_reset(tt_kv_cache *c) {
+    if (c == nullptr) return TT_ERR_INVALID_ARG;
+    for (auto &p : c->position) p = 0;
+    return TT_OK;
+}
+
+TT_API int tt_kv_cache_reset_slot(tt_kv_cache *c, uint32_t slot) {
+    if (c == nullptr || slot >= c->slots) return TT_ERR_INVALID_ARG;
+    c->position[slot] = 0;
+    return TT_OK;
+}
+
+TT_API uint32_t tt_kv_cache_position(const tt_kv_cache *c, uint32_t slot) {
+    return (c && slot < c->slots) ? c->position[slot] : 0;
+}
+TT_API uint32_t tt_kv_cache_capacity(const tt_kv_cache *c, uint32_t layer) {
+    return (c && layer < c->capacity.size()) ? c->capacity[layer] : 0;
+}
+TT_API uint32_t tt_kv_cache_stride(const tt_kv_cache *c, uint32_t layer) {
+    return (c && layer < c->stride.size()) ? c->stride[layer] : 0;
+}
+TT_API uint32_t tt_kv_cache_layer_kind(const tt_kv_cache *c, uint32_t layer) {
+    return (c && layer < c->kind.size()) ? c->kind[layer] : 2;
+}
+TT_API size_t tt_kv_cache_buffer_length(const tt_kv_cache *c, uint32_t layer) {
+    return (c && layer < c->kind.size()) ? (size_t)c->slots * c->capacity[layer] * c->stride[layer] : 0;
+}
+
+TT_API size_t tt_kv_cache_worst_case_bytes(const tt_arch *arch, uint32_t max_context, uint32_t precision_bits,
+                                           uint32_t slots) {
+    if (arch == nullptr || arch->layer_kind == nullptr) return 0;
+    size_t total = 0;
+    for (uint32_t layer = 0; layer < arch->n_layers; ++layer) {
+        const uint8_t kind = arch->layer_kind[layer];
+        if (kind == 2) continue;
+        uint32_t stride, vb;
+        tt_kv_row_layout(kind ? arch->n_full_kv_heads * arch->full_head_dim : arch->n_kv_heads * arch->head_dim,
+                         precision_bits, &stride, &vb);
+        total += (size_t)slots * max_context * stride * 2;
+    }
+    return total;
+}
+
+// ------------------------------------------------------------------ GDN state
+
+struct tt_gdn_state {
+    tt_allocator alloc;
+    uint32_t slots = 0;
+    size_t state_bytes = 0, tail_bytes = 0;
+    std::vector<void *> state, tail, spec_state, spec_tail;  // null for non-linear layers
+};
+
+TT_API size_t tt_gdn_state_worst_case_bytes(const tt_arch *arch, uint32_t slots) {
+    if (arch == nullptr || arch->layer_kind == nullptr) return 0;
+    const size_t sb = (size_t)arch->gdn_v_heads * arch->gdn_value_dim * arch->gdn_key_dim * 4;
+    const uint32_t qkv = 2 * arch->gdn_k_heads * arch->gdn_key_dim + arch->gdn_v_heads * arch->gdn_value_dim;
+    const size_t tb = (size_t)(arch->gdn_conv_kernel > 0 ? arch->gdn_conv_kernel - 1 : 0) * qkv * 2;
+    size_t linear = 0;
+    for (uint32_t i = 0; i < arch->n_layers; ++i) linear += arch->layer_kind[i] == 2;
+    return (size_t)slots * linear * (sb + tb);
+}
+
+TT_API tt_gdn_state *tt_gdn_state_create(const tt_arch *arch, uint32_t slots, int enable_speculative_checkpoint,
+                                         const tt_allocator *allocator, int *out_err) {
+    int err_local;
+    int *err = out_err ? out_err : &err_local;
+    *err = TT_OK;
+    if (arch == nullptr || arch->layer_kind == nullptr || slots == 0 || slots > kMaximumSlots ||
+        (allocator != nullptr && !allocator_ok(allocator))) {
+        *err = TT_ERR_INVALID_ARG;
+        return nullptr;
+    }
+    tt_gdn_state *g = new (std::nothrow) tt_gdn_state();
+    if (g == nullptr) { *err = TT_ERR_OOM; return nullptr; }
+    g->alloc = allocator ? *allocator : kCudaAllocator;
+    g->slots = slots;
+    g->state_bytes = (size_t)arch->gdn_v_heads * arch->gdn_value_dim * arch->gdn_key_dim * 4;
+    const uint32_t qkv = 2 * arch->gdn_k_heads * arch->gdn_key_dim + arch->gdn_v_heads * arch->gdn_value_dim;
+    g->tail_bytes = (size_t)(arch->gdn_conv_kernel > 0 ? arch->gdn_conv_kernel - 1 : 0) * qkv * 2;
+    for (uint32_t layer = 0; layer < arch->n_layers; ++layer) {
+        void *s = nullptr, *t = nullptr, *ss = nullptr, *st = nullptr;
+        if (arch->layer_kind[layer] == 2) {
+            if (g->state_bytes == 0 || g->tail_bytes == 0) {  // linear layer with an empty config
+                tt_gdn_state_destroy(g);
+                *err = TT_ERR_INVALID_ARG;
+                return nullptr;
+            }
+            s = g->alloc.alloc(g->alloc.user, g->state_bytes * slots);
+            t = g->alloc.alloc(g->alloc.user, g->tail_bytes * slots);
+            if (enable_speculative_checkpoint) {
+                ss = g->alloc.alloc(g->alloc.user, g->state_bytes * slots);
+                st = g->alloc.alloc(g->alloc.user, g->tail_bytes * slots);
+            }
+            const bool ok = s && t && (!enable_speculative_checkpoint || (ss && st));
+            g->state.push_back(s); g->tail.push_back(t); g->spec_state.push_back(ss); g->spec_tail.push_back(st);
+            if (!ok) {
+                tt_gdn_state_destroy(g);
+                *err = TT_ERR_OOM;
+                return nullptr;
+            }
+        } else {
+            g->state.push_back(nullptr); g->tail.push_back(nullptr);
+            g->spec_state.push_back(nullptr); g->spec_tail.push_back(nullptr);
+        }
+    }
+    if (tt_gdn_state_reset(g) != TT_OK) {
+        tt_gdn_state_destroy(g);
+        *err = TT_ERR_CUDA;
+        return nullptr;
+    }
+    return g;
+}
+
+TT_API void tt_gdn_state_destroy(tt_gdn_state *g) {
+    if (g == nullptr) return;
+    for (size_t i = 0; i < g->state.size(); ++i) {
+        if (g->state[i]) g->alloc.release(g->alloc.user, g->state[i]);
+        if (g->tail[i]) g->alloc.release(g->alloc.user, g->tail[i]);
+        if (g->spec_state[i]) g->alloc.release(g->alloc.user, g->spec_state[i]);
+        if (g->spec_tail[i]) g->alloc.release(g->alloc.user, g->spec_tail[i]);
+    }
+    delete g;
+}
+
+static int gdn_slot(tt_gdn_state *g, const std::vector<void *> &bufs, size_t bytes, uint32_t layer, uint32_t slot,
+                    void **out) {
+    if (g == nullptr || out == nullptr || layer >= bufs.size() || slot >= g->slots) return TT_ERR_INVALID_ARG;
+    if (bufs[layer] == nullptr) return TT_ERR_INVALID_ARG;  // not a linear layer / no checkpoint twin
+    *out = (char *)bufs[layer] + (size_t)slot * bytes;
+    return TT_OK;
+}
+
+TT_API int tt_gdn_state_state_slot(tt_gdn_state *g, uint32_t layer, uint32_t slot, void **out) {
+    return g ? gdn_slot(g, g->state, g->state_bytes, layer, slot, out) : TT_ERR_INVALID_ARG;
+}
+TT_API int tt_gdn_state_conv_tail_slot(tt_gdn_state *g, uint32_t layer, uint32_t slot, void **out) {
+    return g ? gdn_slot(g, g->tail, g->tail_bytes, layer, slot, out) : TT_ERR_INVALID_ARG;
+}
+TT_API int tt_gdn_state_speculative_state_slot(tt_gdn_state *g, uint32_t layer, uint32_t slot, void **out) {
+    return g ? gdn_slot(g, g->spec_state, g->state_bytes, layer, slot, out) : TT_ERR_INVALID_ARG;
+}
+
+TT_API int tt_gdn_state_reset(tt_gdn_state *g) {
+    if (g == nullptr) return TT_ERR_INVALID_ARG;
+    int bad = 0;
+    for (size_t i = 0; i < g->state.size(); ++i) {
+        if (g->state[i]) bad |= g->alloc.zero(g->alloc.user, g->state[i], g->state_bytes * g->slots);
+        if (g->tail[i]) bad |= g->alloc.zero(g->alloc.user, g->tail[i], g->tail_bytes * g->slots);
+        if (g->spec_state[i]) bad |= g->alloc.zero(g->alloc.user, g->spec_state[i], g->state_bytes * g->slots);
+        if (g->spec_tail[i]) bad |= g->alloc.zero(g->alloc.user, g->spec_tail[i], g->tail_bytes * g->slots);
+    }
+    return bad ? TT_ERR_CUDA : TT_OK;
+}
+
+TT_API int tt_gdn_state_reset_slot(tt_gdn_state *g, uint32_t slot) {
+    if (g == nullptr || slot >= g->slots) return TT_ERR_INVALID_ARG;
+    int bad = 0;
+    for (size_t i = 0; i < g->state.size(); ++i) {
+        if (g->state[i]) bad |= g->alloc.zero(g->alloc.user, (char *)g->state[i] + slot * g->state_bytes, g->state_bytes);
+        if (g->tail[i]) bad |= g->alloc.zero(g->alloc.user, (char *)g->tail[i] + slot * g->tail_bytes, g->tail_bytes);
+    }
+    return bad ? TT_ERR_CUDA : TT_OK;
+}
+
+TT_API int tt_gdn_state_speculative_restore(tt_gdn_state *g) {
+    if (g == nullptr) return TT_ERR_INVALID_ARG;
+    for (size_t i = 0; i < g->state.size(); ++i)
+        if (g->state[i] && (!g->spec_state[i] || !g->spec_tail[i])) return TT_ERR_INVALID_ARG;  // invalidLayout
+    int bad = 0;
+    for (size_t i = 0; i < g->state.size(); ++i) {
+        if (!g->state[i]) continue;
+        // slot 0's segment, as the reference copies stateBytesPerLayer from offset 0
+        bad |= g->alloc.copy(g->alloc.user, g->state[i], g->spec_state[i], g->state_bytes);
+        bad |= g->alloc.copy(g->alloc.user, g->tail[i], g->spec_tail[i], g->tail_bytes);
+    }
+    return bad ? TT_ERR_CUDA : TT_OK;
+}
+
+TT_API size_t tt_gdn_state_bytes_per_layer(const tt_gdn_state *g) { return g ? g->state_bytes : 0; }
+TT_API size_t tt_gdn_state_conv_tail_bytes_per_layer(const tt_gdn_state *g) { return g ? g->tail_bytes : 0; }
+TT_API int tt_gdn_state_is_linear(const tt_gdn_state *g, uint32_t layer) {
+    return (g && layer < g->state.size() && g->state[layer] != nullptr) ? 1 : 0;
+}

@@ -1,0 +1,747 @@
+// Split-KV decode attention for sm_100a: batched over sessions, GQA-packed.
+//
+// Replaces attention_decode_partial / attention_decode_combine
+// (sources/TinyTitanCore/Metal/Attention/attention.metal:162-269, :395-437) and the host
+// dispatch Attention.encodeSplit (sources/TinyTitan/Kernels/Attention/Attention.swift:314-470).
+//
+// HBM-bound design. A work item is (session, kv head, 16-row tile of packed query rows, key
+// range). Every K/V row of the range is read from HBM once per KV head and serves all query
+// rows of the group (the reference re-reads it per q head). Each warp of a CTA streams its own
+// 16-key blocks through a private 3-stage shared-memory ring filled by bulk async copies
+// (cp.async.bulk + mbarrier complete_tx), so there is no CTA-wide barrier in the key loop;
+// Q.K^T and P.V run on mma.sync m16n8k16 with fp32 accumulation, the softmax is done on the
+// accumulator fragments with quad shuffles, and the warps' (m, l, O) states are merged once at
+// the end. Pass 2 merges the items of a session by log-sum-exp.
+#include "tt_common.h"
+
+namespace {
+
+constexpr int kKeysPerBlock = 16;   // keys per warp pipeline stage
+constexpr int kStages = 3;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr uint32_t kWaitLimit = 4000000u;  // mbarrier polls before a wait gives up
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+
+// Bounded wait: false when the poll limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < kWaitLimit; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void bulk_copy_g2s(void *dst, const void *src, uint32_t bytes,
+                                              uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+template <typename T>
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                          uint32_t b1);
+
+template <>
+__device__ __forceinline__ void mma_16816<__half>(float (&c)[4], const uint32_t (&a)[4],
+                                                  uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <>
+__device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4],
+                                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+template <int HD>
+struct DecodeSmem {
+    static constexpr int kPitch = HD + 8;                          // elements per staged row
+    static constexpr int kRowBytes = kPitch * 2;
+    static constexpr int kTileBytes = kKeysPerBlock * kRowBytes;   // one K (or V) block
+    static constexpr int kStageBytes = 2 * kTileBytes;             // K block + V block
+    static constexpr int kWarpBytes = kStages * kStageBytes;
+    static constexpr int kQBytes = 16 * kRowBytes;
+    static constexpr int total(int warps) { return kQBytes + warps * kWarpBytes + 64 * warps; }
+};
+
+// ---------------------------------------------------------------------------------------
+// Pass 1. grid = items, block = NW warps.
+// ---------------------------------------------------------------------------------------
+template <int HD, int NW, typename T>
+__global__ void __launch_bounds__(NW * 32, (HD >= 256 ? (NW <= 2 ? 2 : 1) : 2))
+attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
+                           const TTDecodeSession *__restrict__ sessions, float *__restrict__ part_o,
+                           float *__restrict__ part_m, float *__restrict__ part_l,
+                           uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t kv_stride_bytes,
+                           uint32_t q_row_stride, float scale_log2, uint32_t *__restrict__ status) {
+    using S = DecodeSmem<HD>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const TTDecodeItem item = items[blockIdx.x];
+    const TTDecodeSession ses = sessions[item.session];
+    const uint32_t group = n_q_heads / n_kv_heads;
+
+    unsigned char *q_smem = smem;
+    unsigned char *ring = smem + S::kQBytes + warp * S::kWarpBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::kQBytes + NW * S::kWarpBytes) + warp * kStages;
+
+    // ---- stage the 16-row Q tile (zero rows past row_count) ----
+    {
+        constexpr int kVecPerRow = HD / 8;  // 16-byte vectors per row
+        for (int idx = threadIdx.x; idx < 16 * kVecPerRow; idx += NW * 32) {
+            const int r = idx / kVecPerRow, c = idx % kVecPerRow;
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (r < (int)item.row_count) {
+                const uint32_t packed = item.row_begin + r;     // w * group + g
+                const uint32_t w = packed / group, g = packed % group;
+                const T *src = reinterpret_cast<const T *>(ses.q) + (size_t)w * q_row_stride +
+                               (size_t)(item.kv_head * group + g) * HD;
+                val = reinterpret_cast<const uint4 *>(src)[c];
+            }
+            *reinterpret_cast<uint4 *>(q_smem + r * S::kRowBytes + c * 16) = val;
+        }
+    }
+    if (lane == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
+
+    // ---- this warp's 16-key blocks: warp, warp+NW, ... ----
+    const uint32_t n_keys = item.key_end - item.key_begin;
+    const uint32_t n_blocks = (n_keys + kKeysPerBlock - 1) / kKeysPerBlock;
+    const uint32_t my_blocks = n_blocks > (uint32_t)warp ? (n_blocks - warp + NW - 1) / NW : 0u;
+
+    const unsigned char *kbase = reinterpret_cast<const unsigned char *>(ses.k) + (size_t)item.kv_head * HD * 2;
+    const unsigned char *vbase = reinterpret_cast<const unsigned char *>(ses.v) + (size_t)item.kv_head * HD * 2;
+
+    auto issue = [&](uint32_t i) {
+        // block i of this warp -> stage i % kStages; lanes 0-15 fetch K rows, 16-31 V rows.
+        const uint32_t blk = warp + i * NW;
+        const uint32_t key0 = item.key_begin + blk * kKeysPerBlock;
+        const uint32_t valid = min((uint32_t)kKeysPerBlock, item.key_end - key0);
+        unsigned char *stage = ring + (i % kStages) * S::kStageBytes;
+        uint64_t *bar = &bars[i % kStages];
+        if (lane == 0) mbar_expect_tx(bar, valid * 2u * (uint32_t)(HD * 2));
+        __syncwarp();
+        const uint32_t r = lane & 15;
+        const bool is_v = lane >= 16;
+        unsigned char *dst = stage + (is_v ? S::kTileBytes : 0) + r * S::kRowBytes;
+        if (r < valid) {
+            uint32_t p = key0 + r;
+            if (ses.ring_capacity) p %= ses.ring_capacity;
+            const unsigned char *src = (is_v ? vbase : kbase) + (size_t)p * kv_stride_bytes;
+            bulk_copy_g2s(dst, src, HD * 2, bar);
+        } else if (is_v) {
+            // a V row that is never fetched must still be finite: it meets p == 0 in P.V
+            uint4 z = make_uint4(0u, 0u, 0u, 0u);
+            for (int c = 0; c < HD / 8; ++c) reinterpret_cast<uint4 *>(dst)[c] = z;
+        }
+    };
+
+    // per-thread softmax state for rows (lane/4) and (lane/4 + 8)
+    float m_run[2] = {-INFINITY, -INFINITY};
+    float l_run[2] = {0.f, 0.f};
+    float acc[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
+
+    // visible-key limit of the two rows this thread owns
+    uint32_t limit[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t r = (lane >> 2) + 8 * h;
+        if (r < item.row_count) {
+            const uint32_t w = (item.row_begin + r) / group;
+            limit[h] = ses.seq_len - (ses.q_rows - 1 - w);
+        } else {
+            limit[h] = 0;
+        }
+    }
+
+    bool timed_out = false;
+    const uint32_t prologue = min(my_blocks, (uint32_t)(kStages - 1));
+    for (uint32_t i = 0; i < prologue; ++i) issue(i);
+
+    const uint32_t q_addr = smem_u32(q_smem) + (lane & 15) * S::kRowBytes + (lane >> 4) * 16;
+
+    for (uint32_t i = 0; i < my_blocks; ++i) {
+        if (i + kStages - 1 < my_blocks) issue(i + kStages - 1);
+        if (!mbar_wait(&bars[i % kStages], (i / kStages) & 1)) { timed_out = true; break; }
+
+        const unsigned char *stage = ring + (i % kStages) * S::kStageBytes;
+        const uint32_t k_addr = smem_u32(stage) + ((lane & 7) + ((lane >> 4) << 3)) * S::kRowBytes +
+                                ((lane >> 3) & 1) * 16;
+        const uint32_t v_addr = smem_u32(stage) + S::kTileBytes +
+                                ((lane & 7) + ((lane >> 3) & 1) * 8) * S::kRowBytes + (lane >> 4) * 16;
+
+        // ---- S = Q K^T for 16 rows x 16 keys ----
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            uint32_t a[4], b[4];
+            ldmatrix_x4(a, q_addr + ks * 32);
+            ldmatrix_x4(b, k_addr + ks * 32);
+            mma_16816<T>(s0, a, b[0], b[1]);
+            mma_16816<T>(s1, a, b[2], b[3]);
+        }
+
+        // ---- mask, online softmax ----
+        const uint32_t blk = warp + i * NW;
+        const uint32_t key0 = item.key_begin + blk * kKeysPerBlock + (lane & 3) * 2;
+        float sv[2][4];  // [row half][key: n0c0 n0c1 n1c0 n1c1]
+        sv[0][0] = s0[0]; sv[0][1] = s0[1]; sv[0][2] = s1[0]; sv[0][3] = s1[1];
+        sv[1][0] = s0[2]; sv[1][1] = s0[3]; sv[1][2] = s1[2]; sv[1][3] = s1[3];
+        uint32_t pa[4];
+        float alpha[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t key = key0 + (j >> 1) * 8 + (j & 1);
+                bool ok = key < limit[h] && key < item.key_end;
+                if (ok && ses.keep != nullptr) ok = ses.keep[key] != 0;
+                sv[h][j] = ok ? sv[h][j] * scale_log2 : -INFINITY;
+                mx = fmaxf(mx, sv[h][j]);
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run[h], mx);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            alpha[h] = exp2f(m_run[h] - m_use);
+            m_run[h] = m_new;
+            float rs = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { sv[h][j] = exp2f(sv[h][j] - m_use); rs += sv[h][j]; }
+            l_run[h] = l_run[h] * alpha[h] + rs;
+        }
+        pa[0] = pack2<T>(sv[0][0], sv[0][1]);
+        pa[1] = pack2<T>(sv[1][0], sv[1][1]);
+        pa[2] = pack2<T>(sv[0][2], sv[0][3]);
+        pa[3] = pack2<T>(sv[1][2], sv[1][3]);
+
+        if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n) {
+                acc[n][0] *= alpha[0]; acc[n][1] *= alpha[0];
+                acc[n][2] *= alpha[1]; acc[n][3] *= alpha[1];
+            }
+        }
+
+        // ---- O += P V ----
+#pragma unroll
+        for (int np = 0; np < HD / 16; ++np) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, v_addr + np * 32);
+            mma_16816<T>(acc[2 * np], pa, b[0], b[1]);
+            mma_16816<T>(acc[2 * np + 1], pa, b[2], b[3]);
+        }
+        __syncwarp();  // every lane is done with this stage before it is refilled
+    }
+
+    if (timed_out && lane == 0) atomicOr(status, TT_DEV_WAIT_TIMEOUT);
+
+    // quad-reduce the row sums
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+
+    // ---- merge the warps' states through shared memory (the ring is idle now) ----
+    __syncthreads();
+    float *mo = reinterpret_cast<float *>(ring);              // [16][HD] of this warp
+    float *mm = mo + 16 * HD;                                 // [16] m, [16] l
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        const int col = n * 8 + (lane & 3) * 2;
+        const int r0 = lane >> 2, r1 = r0 + 8;
+        *reinterpret_cast<float2 *>(mo + r0 * HD + col) = make_float2(acc[n][0], acc[n][1]);
+        *reinterpret_cast<float2 *>(mo + r1 * HD + col) = make_float2(acc[n][2], acc[n][3]);
+    }
+    if ((lane & 3) == 0) {
+        mm[(lane >> 2)] = m_run[0];          mm[16 + (lane >> 2)] = l_run[0];
+        mm[(lane >> 2) + 8] = m_run[1];      mm[16 + (lane >> 2) + 8] = l_run[1];
+    }
+    __syncthreads();
+
+    const uint32_t rows_total = ses.q_rows * n_q_heads;
+    for (int r = warp; r < (int)item.row_count; r += NW) {
+        float mw[NW], m_all = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float *wm = reinterpret_cast<const float *>(smem + S::kQBytes + w * S::kWarpBytes) + 16 * HD;
+            mw[w] = wm[r];
+            m_all = fmaxf(m_all, mw[w]);
+        }
+        float wgt[NW], l_all = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float *wm = reinterpret_cast<const float *>(smem + S::kQBytes + w * S::kWarpBytes) + 16 * HD;
+            wgt[w] = (m_all == -INFINITY) ? 0.f : exp2f(mw[w] - m_all);
+            l_all += wm[16 + r] * wgt[w];
+        }
+        const uint32_t packed = item.row_begin + r;
+        const uint32_t wq = packed / group, g = packed % group;
+        const uint32_t rho = wq * n_q_heads + item.kv_head * group + g;
+        const size_t prow = (size_t)ses.partial_base + (size_t)item.part_index * rows_total + rho;
+        for (int c = lane; c < HD; c += 32) {
+            float o = 0.f;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) {
+                const float *wo = reinterpret_cast<const float *>(smem + S::kQBytes + w * S::kWarpBytes);
+                o += wo[r * HD + c] * wgt[w];
+            }
+            part_o[prow * HD + c] = o;
+        }
+        if (lane == 0) {
+            part_m[prow] = m_all * kLn2;   // natural-log domain, the reference's partial format
+            part_l[prow] = l_all;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Pass 2. grid = (sessions, rows per session), block = HD/4 threads (one float4 column each).
+// mode 0: normalised output in the I/O dtype; mode 1: merged unnormalised (m, d, o) triple.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions,
+                                           const float *__restrict__ part_o,
+                                           const float *__restrict__ part_m,
+                                           const float *__restrict__ part_l, uint32_t n_q_heads,
+                                           uint32_t head_dim, uint32_t out_row_stride, int mode,
+                                           float *__restrict__ m_out, float *__restrict__ d_out,
+                                           float *__restrict__ o_out) {
+    const TTDecodeSession ses = sessions[blockIdx.x];
+    const uint32_t rows_total = ses.q_rows * n_q_heads;
+    const uint32_t rho = blockIdx.y;
+    if (rho >= rows_total) return;
+    const uint32_t n_parts = ses.n_parts;
+    const size_t base = (size_t)ses.partial_base + rho;
+
+    float mg = -INFINITY;
+    for (uint32_t c = 0; c < n_parts; ++c) mg = fmaxf(mg, part_m[base + (size_t)c * rows_total]);
+    float D = 0.f;
+    if (mg != -INFINITY)
+        for (uint32_t c = 0; c < n_parts; ++c) {
+            const size_t pr = base + (size_t)c * rows_total;
+            D += part_l[pr] * __expf(part_m[pr] - mg);
+        }
+    const uint32_t w = rho / n_q_heads, h = rho % n_q_heads;
+    for (uint32_t col = threadIdx.x * 4; col < head_dim; col += blockDim.x * 4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (mg != -INFINITY) {
+            for (uint32_t c = 0; c < n_parts; ++c) {
+                const size_t pr = base + (size_t)c * rows_total;
+                const float e = __expf(part_m[pr] - mg);
+                const float4 o = *reinterpret_cast<const float4 *>(part_o + pr * head_dim + col);
+                acc.x += o.x * e; acc.y += o.y * e; acc.z += o.z * e; acc.w += o.w * e;
+            }
+        }
+        if (mode == 0) {
+            const float inv = D > 0.f ? 1.f / D : 0.f;
+            T *dst = reinterpret_cast<T *>(ses.out) + (size_t)w * out_row_stride + (size_t)h * head_dim + col;
+            uint2 packed;
+            packed.x = pack2<T>(acc.x * inv, acc.y * inv);
+            packed.y = pack2<T>(acc.z * inv, acc.w * inv);
+            *reinterpret_cast<uint2 *>(dst) = packed;
+        } else {
+            *reinterpret_cast<float4 *>(o_out + (size_t)rho * head_dim + col) = acc;
+        }
+    }
+    if (mode != 0 && threadIdx.x == 0) {
+        m_out[rho] = mg;
+        d_out[rho] = D;
+    }
+}
+
+// Merge of externally supplied triples: m,d [n_parts][H]; o [n_parts][H][hd].
+template <typename T>
+__global__ void attn_combine_parts_kernel(const float *__restrict__ m, const float *__restrict__ d,
+                                          const float *__restrict__ o, uint32_t n_parts,
+                                          uint32_t n_q_heads, uint32_t head_dim, T *__restrict__ out) {
+    const uint32_t h = blockIdx.x;
+    float mg = -INFINITY;
+    for (uint32_t c = 0; c < n_parts; ++c) mg = fmaxf(mg, m[(size_t)c * n_q_heads + h]);
+    float D = 0.f;
+    if (mg != -INFINITY)
+        for (uint32_t c = 0; c < n_parts; ++c)
+            D += d[(size_t)c * n_q_heads + h] * __expf(m[(size_t)c * n_q_heads + h] - mg);
+    const float inv = D > 0.f ? 1.f / D : 0.f;
+    for (uint32_t col = threadIdx.x; col < head_dim; col += blockDim.x) {
+        float acc = 0.f;
+        if (mg != -INFINITY)
+            for (uint32_t c = 0; c < n_parts; ++c)
+                acc += o[((size_t)c * n_q_heads + h) * head_dim + col] *
+                       __expf(m[(size_t)c * n_q_heads + h] - mg);
+        out[(size_t)h * head_dim + col] = static_cast<T>(acc * inv);
+    }
+}
+
+template <int HD, int NW, typename T>
+cudaError_t launch_partial(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
+                           const TTDecodeSession *sessions, float *part_o, float *part_m,
+                           float *part_l, const tt_attn_batch_params *p, uint32_t *status) {
+    auto kernel = attn_decode_partial_kernel<HD, NW, T>;
+    const int smem = DecodeSmem<HD>::total(NW);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    kernel<<<n_items, NW * 32, smem, stream>>>(items, sessions, part_o, part_m, part_l, p->n_q_heads,
+                                               p->n_kv_heads, p->kv_token_stride_elements * 2u,
+                                               p->q_row_stride_elements, p->scale * kLog2e, status);
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_partial_hd(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
+                              const TTDecodeSession *sessions, float *part_o, float *part_m,
+                              float *part_l, const tt_attn_batch_params *p, uint32_t *status) {
+    switch (p->head_dim) {
+        case 64: return launch_partial<64, 4, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status);
+        case 128: return launch_partial<128, 4, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status);
+        case 256: return launch_partial<256, 2, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+// Host side: split planning (pure arithmetic) and the launcher.
+// ---------------------------------------------------------------------------------------
+static uint32_t ceil_div_u32(uint64_t a, uint64_t b) { return (uint32_t)((a + b - 1) / b); }
+
+TT_API int tt_attn_plan_splits(const uint32_t *keys_per_session, const uint32_t *q_rows_per_session,
+                               uint32_t n_sessions, uint32_t head_dim, uint32_t n_q_heads,
+                               uint32_t n_kv_heads, uint32_t sm_count, size_t workspace_bytes,
+                               uint32_t *out_keys_per_item, uint32_t *out_n_items) {
+    if (keys_per_session == nullptr || n_sessions == 0 || n_kv_heads == 0 || n_q_heads % n_kv_heads != 0 ||
+        head_dim == 0 || sm_count == 0)
+        return TT_ERR_INVALID_ARG;
+    const uint32_t group = n_q_heads / n_kv_heads;
+    // Streams of keys to be read: one per (session, kv head, 16-row tile).
+    uint64_t key_rows = 0, max_rows = 0;
+    for (uint32_t i = 0; i < n_sessions; ++i) {
+        const uint32_t qr = q_rows_per_session ? q_rows_per_session[i] : 1u;
+        const uint32_t tiles = ceil_div_u32((uint64_t)qr * group, 16);
+        key_rows += (uint64_t)keys_per_session[i] * n_kv_heads * tiles;
+        max_rows += (uint64_t)qr * n_q_heads;
+    }
+    // Aim at ~8 items per SM so that the hardware scheduler can balance ragged sessions, but
+    // keep an item long enough (>= 256 keys) to amortise its pipeline fill and its merge.
+    uint64_t target = key_rows / ((uint64_t)sm_count * 8u);
+    uint32_t keys = (uint32_t)((target + 63) / 64 * 64);
+    if (keys < 256) keys = 256;
+    if (keys > 16384) keys = 16384;
+    for (;;) {
+        uint64_t items = 0, prows = 0;
+        for (uint32_t i = 0; i < n_sessions; ++i) {
+            const uint32_t qr = q_rows_per_session ? q_rows_per_session[i] : 1u;
+            const uint32_t tiles = ceil_div_u32((uint64_t)qr * group, 16);
+            uint32_t parts = ceil_div_u32(keys_per_session[i], keys);
+            if (parts == 0) parts = 1;  // an empty range still produces its (-inf, 0, 0) partial
+            items += (uint64_t)parts * n_kv_heads * tiles;
+            prows += (uint64_t)parts * qr * n_q_heads;
+        }
+        const uint64_t need = prows * ((uint64_t)head_dim + 2) * sizeof(float);
+        if (workspace_bytes == 0 || need <= workspace_bytes || keys >= (1u << 30)) {
+            if (workspace_bytes != 0 && need > workspace_bytes) return TT_ERR_OOM;
+            if (out_keys_per_item) *out_keys_per_item = keys;
+            if (out_n_items) *out_n_items = (uint32_t)items;
+            return TT_OK;
+        }
+        keys *= 2;
+    }
+}
+
+TT_API void tt_attn_reference_split_geometry(uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t seq_len,
+                                             uint32_t kv_start, int prefer_gqa_swa,
+                                             tt_split_geometry *out) {
+    // Attention.swift:59-64 (defaultFullChunks 16, defaultGQASWAChunks 8, maxChunks 64), :196-227.
+    if (out == nullptr || n_kv_heads == 0) return;
+    const int q_per_kv = (int)(n_q_heads / n_kv_heads);
+    const bool swa_grouped = prefer_gqa_swa && q_per_kv <= 2;
+    const int eff = (int)seq_len - (int)kv_start;
+    const int eff1 = eff < 1 ? 1 : eff;
+    const int def = swa_grouped ? 8 : 16;
+    int base = def < 64 ? def : 64;
+    if (eff1 < base) base = eff1;
+    if (base < 1) base = 1;
+    int chunks = base;
+    if (swa_grouped) {
+        int widened = base * q_per_kv;
+        if (widened > 64) widened = 64;
+        if (widened > chunks) chunks = widened;
+    }
+    out->effective_length = (uint32_t)eff;
+    out->num_chunks = (uint32_t)chunks;
+    out->chunk_length = (uint32_t)((eff1 + chunks - 1) / chunks);
+    out->partial_threadgroups = (uint32_t)((swa_grouped ? (int)n_kv_heads : (int)n_q_heads) * chunks);
+    out->use_swa_grouped_partial = swa_grouped ? 1u : 0u;
+}
+
+// mode 0: write normalised outputs to the sessions' `out`; mode 1: one merged triple for a
+// single session (m_out/d_out/o_out).
+int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession *in_sessions,
+                     uint32_t n_sessions, const tt_attn_batch_params *p, int mode, float *m_out,
+                     float *d_out, float *o_out) {
+    if (n_sessions == 0) return TT_OK;
+    if (n_sessions > ctx->max_sessions)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "n_sessions %u exceeds the context's max_sessions %u",
+                            n_sessions, ctx->max_sessions);
+    if (p->n_kv_heads == 0 || p->n_q_heads == 0 || p->n_q_heads % p->n_kv_heads != 0)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "n_q_heads must be a multiple of n_kv_heads");
+    if (p->head_dim != 64 && p->head_dim != 128 && p->head_dim != 256)
+        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "decode attention supports head_dim 64/128/256, got %u",
+                            p->head_dim);
+    if (p->io_dtype != TT_F16 && p->io_dtype != TT_BF16)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "io_dtype must be TT_F16 or TT_BF16");
+    if (p->kv_token_stride_elements < p->n_kv_heads * p->head_dim ||
+        p->q_row_stride_elements < p->n_q_heads * p->head_dim ||
+        p->out_row_stride_elements < p->n_q_heads * p->head_dim)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "a row stride is smaller than its tight width");
+    if ((p->kv_token_stride_elements % 8) || (p->q_row_stride_elements % 8) || (p->out_row_stride_elements % 4))
+        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "row strides must keep rows 16-byte aligned");
+    const uint32_t group = p->n_q_heads / p->n_kv_heads;
+
+    uint32_t *keys = ctx->h_keys, *rows = ctx->h_rows;
+    for (uint32_t i = 0; i < n_sessions; ++i) {
+        const TTDecodeSession &s = in_sessions[i];
+        if (s.q == nullptr || s.k == nullptr || s.v == nullptr || (mode == 0 && s.out == nullptr))
+            return tt_set_error(ctx, TT_ERR_INVALID_ARG, "session %u has a null buffer", i);
+        if (s.q_rows == 0 || s.q_rows > 64)
+            return tt_set_error(ctx, TT_ERR_INVALID_ARG, "session %u: q_rows must be in 1..64", i);
+        if (s.seq_len + 1 < s.q_rows)
+            return tt_set_error(ctx, TT_ERR_INVALID_ARG, "session %u: seq_len %u cannot hold %u query rows", i,
+                                s.seq_len, s.q_rows);
+        if (((uintptr_t)s.q | (uintptr_t)s.k | (uintptr_t)s.v | (uintptr_t)s.out) & 15)
+            return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "session %u: buffers must be 16-byte aligned", i);
+        keys[i] = s.seq_len > s.kv_start ? s.seq_len - s.kv_start : 0u;
+        rows[i] = s.q_rows;
+    }
+    uint32_t keys_per_item = 0, n_items = 0;
+    int rc = tt_attn_plan_splits(keys, rows, n_sessions, p->head_dim, p->n_q_heads, p->n_kv_heads,
+                                 (uint32_t)ctx->sm_count, ctx->workspace_bytes, &keys_per_item, &n_items);
+    if (rc != TT_OK) return tt_set_error(ctx, rc, "split-KV partials do not fit the context workspace");
+    if (n_items > ctx->max_items)
+        return tt_set_error(ctx, TT_ERR_OOM, "%u work items exceed the context's item table (%u)", n_items,
+                            ctx->max_items);
+
+    // Build the session and item tables.
+    uint32_t partial_cursor = 0, item_cursor = 0, max_rows = 0;
+    for (uint32_t i = 0; i < n_sessions; ++i) {
+        TTDecodeSession s = in_sessions[i];
+        uint32_t parts = ceil_div_u32(keys[i], keys_per_item);
+        if (parts == 0) parts = 1;
+        const uint32_t rows_total = s.q_rows * p->n_q_heads;
+        s.n_parts = parts;
+        s.partial_base = partial_cursor;
+        ctx->h_sessions[i] = s;
+        if (rows_total > max_rows) max_rows = rows_total;
+        const uint32_t packed_rows = s.q_rows * group;
+        for (uint32_t part = 0; part < parts; ++part) {
+            const uint32_t kb = s.kv_start + part * keys_per_item;
+            uint32_t ke = kb + keys_per_item;
+            if (ke > s.seq_len) ke = s.seq_len;
+            if (ke < kb) ke = kb;
+            for (uint32_t kvh = 0; kvh < p->n_kv_heads; ++kvh)
+                for (uint32_t rb = 0; rb < packed_rows; rb += 16) {
+                    TTDecodeItem &it = ctx->h_items[item_cursor++];
+                    it.session = i; it.kv_head = kvh; it.key_begin = kb; it.key_end = ke;
+                    it.part_index = part; it.row_begin = rb;
+                    it.row_count = packed_rows - rb < 16 ? packed_rows - rb : 16;
+                    it.partial_base = s.partial_base;
+                }
+        }
+        partial_cursor += parts * rows_total;
+    }
+    if (item_cursor != n_items) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "internal: item count mismatch");
+
+    float *part_o = ctx->partials;
+    float *part_m = part_o + (size_t)partial_cursor * p->head_dim;
+    float *part_l = part_m + partial_cursor;
+
+    cudaError_t e = cudaMemcpyAsync(ctx->sessions, ctx->h_sessions, sizeof(TTDecodeSession) * n_sessions,
+                                    cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "copy session table");
+    e = cudaMemcpyAsync(ctx->items, ctx->h_items, sizeof(TTDecodeItem) * n_items, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "copy item table");
+
+    const bool timed = ctx->profiling && ctx->profile_count < tt_context::kProfileSlots;
+    if (timed) cudaEventRecord(ctx->profile_begin[ctx->profile_count], stream);
+    if (p->io_dtype == TT_F16)
+        e = launch_partial_hd<__half>(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status);
+    else
+        e = launch_partial_hd<__nv_bfloat16>(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status);
+    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_decode_partial launch");
+    if (timed) cudaEventRecord(ctx->profile_end[ctx->profile_count++], stream);
+    ctx->launches++;
+
+    const dim3 grid(n_sessions, max_rows);
+    const uint32_t threads = p->head_dim / 4;
+    if (p->io_dtype == TT_F16)
+        attn_decode_combine_kernel<__half><<<grid, threads, 0, stream>>>(
+            ctx->sessions, part_o, part_m, part_l, p->n_q_heads, p->head_dim, p->out_row_stride_elements, mode,
+            m_out, d_out, o_out);
+    else
+        attn_decode_combine_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+            ctx->sessions, part_o, part_m, part_l, p->n_q_heads, p->head_dim, p->out_row_stride_elements, mode,
+            m_out, d_out, o_out);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_decode_combine launch");
+    ctx->launches++;
+    return TT_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// C entry points.
+// ---------------------------------------------------------------------------------------
+TT_API int tt_attn_decode_batched(tt_context *ctx, tt_stream stream, const tt_attn_session *sessions,
+                                  uint32_t n_sessions, const tt_attn_batch_params *params) {
+    TT_ENTER(ctx);
+    if (sessions == nullptr || params == nullptr)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "sessions and params must not be null");
+    if (n_sessions > ctx->max_sessions)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "n_sessions %u exceeds the context's max_sessions %u",
+                            n_sessions, ctx->max_sessions);
+    TTDecodeSession *tmp = ctx->h_sessions_in;
+    for (uint32_t i = 0; i < n_sessions; ++i) {
+        TTDecodeSession &d = tmp[i];
+        d.q = sessions[i].q; d.out = sessions[i].out; d.k = sessions[i].k; d.v = sessions[i].v;
+        d.seq_len = sessions[i].seq_len; d.q_rows = sessions[i].q_rows; d.kv_start = sessions[i].kv_start;
+        d.n_parts = 0; d.partial_base = 0; d.ring_capacity = 0; d.keep = nullptr;
+    }
+    return tt_launch_decode(ctx, (cudaStream_t)stream, tmp, n_sessions, params, 0, nullptr, nullptr, nullptr);
+}
+
+TT_API int tt_attn_decode(tt_context *ctx, tt_stream stream, const void *q, const void *k, const void *v,
+                          void *out, uint32_t head_dim, uint32_t n_q_heads, uint32_t n_kv_heads,
+                          uint32_t seq_len, uint32_t kv_start, float scale, const tt_kv_format *kv_format,
+                          const uint8_t *keep_mask, uint32_t ring_capacity) {
+    TT_ENTER(ctx);
+    if (head_dim > 512) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "head_dim must be <= 512");
+    if (n_kv_heads == 0 || n_q_heads % n_kv_heads != 0)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "n_q_heads must be a multiple of n_kv_heads for GQA");
+    if (n_q_heads > 96) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "n_q_heads exceeds 96");
+    uint32_t stride_elems = n_kv_heads * head_dim;
+    if (kv_format != nullptr) {
+        if (kv_format->bits != 16)
+            return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "quantised KV rows (%u bits) are not implemented",
+                                kv_format->bits);
+        if (kv_format->stride_bytes != 0) {
+            if (kv_format->stride_bytes % 2) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "odd KV stride");
+            stride_elems = kv_format->stride_bytes / 2;
+        }
+    }
+    tt_attn_batch_params p;
+    p.head_dim = head_dim; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
+    p.kv_token_stride_elements = stride_elems; p.q_row_stride_elements = n_q_heads * head_dim;
+    p.out_row_stride_elements = n_q_heads * head_dim; p.scale = scale; p.io_dtype = TT_F16;
+    TTDecodeSession s;
+    s.q = q; s.out = out; s.k = k; s.v = v; s.seq_len = seq_len; s.q_rows = 1;
+    s.kv_start = kv_start < seq_len ? kv_start : seq_len;
+    s.n_parts = 0; s.partial_base = 0; s.ring_capacity = ring_capacity; s.keep = keep_mask;
+    return tt_launch_decode(ctx, (cudaStream_t)stream, &s, 1, &p, 0, nullptr, nullptr, nullptr);
+}
+
+TT_API int tt_attn_decode_partial(tt_context *ctx, tt_stream stream, const void *q, const void *k,
+                                  const void *v, uint32_t head_dim, uint32_t n_q_heads, uint32_t n_kv_heads,
+                                  uint32_t seq_len, uint32_t kv_start, float scale,
+                                  uint32_t kv_token_stride_elements, uint32_t io_dtype, float *m_out,
+                                  float *d_out, float *o_out) {
+    TT_ENTER(ctx);
+    if (m_out == nullptr || d_out == nullptr || o_out == nullptr)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "partial outputs must not be null");
+    tt_attn_batch_params p;
+    p.head_dim = head_dim; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
+    p.kv_token_stride_elements = kv_token_stride_elements ? kv_token_stride_elements : n_kv_heads * head_dim;
+    p.q_row_stride_elements = n_q_heads * head_dim; p.out_row_stride_elements = n_q_heads * head_dim;
+    p.scale = scale; p.io_dtype = io_dtype;
+    TTDecodeSession s;
+    s.q = q; s.out = nullptr; s.k = k; s.v = v; s.seq_len = seq_len; s.q_rows = 1;
+    s.kv_start = kv_start < seq_len ? kv_start : seq_len;
+    s.n_parts = 0; s.partial_base = 0; s.ring_capacity = 0; s.keep = nullptr;
+    return tt_launch_decode(ctx, (cudaStream_t)stream, &s, 1, &p, 1, m_out, d_out, o_out);
+}
+
+TT_API int tt_attn_combine(tt_context *ctx, tt_stream stream, const float *m, const float *d, const float *o,
+                           uint32_t n_parts, uint32_t n_q_heads, uint32_t head_dim, void *out,
+                           uint32_t io_dtype) {
+    TT_ENTER(ctx);
+    if (m == nullptr || d == nullptr || o == nullptr || out == nullptr || n_parts == 0 || n_q_heads == 0 ||
+        head_dim == 0)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "combine needs non-null buffers and positive sizes");
+    const uint32_t threads = head_dim < 256 ? ((head_dim + 31) / 32) * 32 : 256;
+    if (io_dtype == TT_F16)
+        attn_combine_parts_kernel<__half><<<n_q_heads, threads, 0, (cudaStream_t)stream>>>(
+            m, d, o, n_parts, n_q_heads, head_dim, reinterpret_cast<__half *>(out));
+    else if (io_dtype == TT_BF16)
+        attn_combine_parts_kernel<__nv_bfloat16><<<n_q_heads, threads, 0, (cudaStream_t)stream>>>(
+            m, d, o, n_parts, n_q_heads, head_dim, reinterpret_cast<__nv_bfloat16 *>(out));
+    else
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "io_dtype must be TT_F16 or TT_BF16");
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_combine launch");
+    ctx->launches++;
+    return TT_OK;
+}

@@ -1,0 +1,173 @@
+// Causal prefill attention: dispatch + the generic CUDA kernel.
+//
+// Replaces PrefillAttention.encodeCausal
+// (sources/TinyTitan/Kernels/Attention/PrefillAttention.swift:165-258) and the kernels
+// attention_prefill_causal_tiled / _q8 (sources/TinyTitanCore/Metal/Prefill/prefill.metal:
+// 1056-1313). The generic kernel takes any head_dim <= 512 and any element strides / 2-byte
+// aligned base pointers (the reference's tests use padded strides and odd buffer offsets); the
+// tcgen05 kernel in attn_prefill_tc.cu takes the aligned head_dim-256 case.
+#include "tt_common.h"
+
+int tt_launch_prefill_tc(tt_context *ctx, cudaStream_t stream, const void *q, const void *k, const void *v,
+                         void *out, const tt_prefill_params *p, uint32_t io_dtype);
+
+namespace {
+
+constexpr int kGenericWarps = 4;
+constexpr int kMaxHeadDim = 512;
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T x);
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T>
+__device__ __forceinline__ T from_f32(float x);
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// One warp per (query row, q head). Keys are taken 32 at a time: lane j scores key j (a full
+// head_dim dot product against the query held in shared memory), the tile's softmax update is
+// done with warp reductions, then every lane accumulates its own output dimensions over the
+// 32 probabilities (broadcast by shuffle).
+template <typename T>
+__global__ void __launch_bounds__(kGenericWarps * 32)
+attn_prefill_generic_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
+                            T *__restrict__ out, tt_prefill_params p, uint32_t ring) {
+    __shared__ float q_s[kGenericWarps][kMaxHeadDim];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t pair = blockIdx.x * kGenericWarps + warp;
+    if (pair >= p.query_count * p.n_q_heads) return;
+    const uint32_t t = pair / p.n_q_heads, h = pair % p.n_q_heads;
+    const uint32_t hd = p.head_dim;
+    const uint32_t kvh = h / (p.n_q_heads / p.n_kv_heads);
+    const uint32_t abs_q = p.start_position + t;
+    uint32_t first = 0;
+    if (p.sliding_window != 0 && abs_q + 1 > p.sliding_window) first = abs_q + 1 - p.sliding_window;
+    const uint32_t last = min(p.kv_valid_count, abs_q + 1);
+
+    const T *qr = q + (size_t)t * p.q_token_stride_elements + (size_t)h * hd;
+    for (uint32_t d = lane; d < hd; d += 32) q_s[warp][d] = to_f32<T>(qr[d]) * p.scale;
+    __syncwarp();
+
+    constexpr int kPerLane = kMaxHeadDim / 32;
+    float acc[kPerLane];
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) acc[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+
+    for (uint32_t key0 = first; key0 < last; key0 += 32) {
+        const uint32_t key = key0 + lane;
+        float s = -INFINITY;
+        if (key < last) {
+            const uint32_t phys = ring ? key % ring : key;
+            const T *kr = k + (size_t)phys * p.kv_token_stride_elements + (size_t)kvh * hd;
+            float dot = 0.f;
+            for (uint32_t d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], to_f32<T>(kr[d]), dot);
+            s = dot;
+        }
+        float mx = s;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float m_new = fmaxf(m_run, mx);          // finite: at least one key of the tile is valid
+        const float alpha = __expf(m_run - m_new);     // exp(-inf) == 0 on the first tile
+        const float pe = (key < last) ? __expf(s - m_new) : 0.f;
+        float ps = pe;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+        l_run = l_run * alpha + ps;
+        m_run = m_new;
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) acc[i] *= alpha;
+        const uint32_t n = min(32u, last - key0);
+        for (uint32_t j = 0; j < n; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, pe, j);
+            const uint32_t kj = key0 + j;
+            const uint32_t phys = ring ? kj % ring : kj;
+            const T *vr = v + (size_t)phys * p.kv_token_stride_elements + (size_t)kvh * hd;
+#pragma unroll
+            for (int i = 0; i < kPerLane; ++i) {
+                const uint32_t d = lane + 32 * i;
+                if (d < hd) acc[i] = fmaf(pj, to_f32<T>(vr[d]), acc[i]);
+            }
+        }
+    }
+    T *orow = out + (size_t)t * p.o_token_stride_elements + (size_t)h * hd;
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;   // row_sum == 0 -> 0 (prefill.metal:1154-1157)
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+        const uint32_t d = lane + 32 * i;
+        if (d < hd) orow[d] = from_f32<T>(acc[i] * inv);
+    }
+}
+
+int validate_prefill(tt_context *ctx, const void *q, const void *k, const void *v, const void *out,
+                     const tt_prefill_params *p, uint32_t io_dtype) {
+    // PrefillAttention.validate (PrefillAttention.swift:334-363)
+    if (p == nullptr || q == nullptr || k == nullptr || v == nullptr || out == nullptr)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "prefill attention needs non-null buffers and params");
+    if (p->head_dim == 0) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "headDim must be positive");
+    if (p->query_count == 0) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "queryCount must be positive");
+    if (p->n_q_heads == 0 || p->n_kv_heads == 0)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "numQHeads and numKVHeads must be positive");
+    if (p->n_q_heads % p->n_kv_heads != 0)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "numQHeads must be divisible by numKVHeads");
+    if (p->q_token_stride_elements < p->n_q_heads * p->head_dim)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "q token stride is too small");
+    if (p->o_token_stride_elements < p->n_q_heads * p->head_dim)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "output token stride is too small");
+    if (p->kv_bits != 16) {
+        if (p->kv_bits != 4 && p->kv_bits != 8)
+            return tt_set_error(ctx, TT_ERR_INVALID_ARG, "KV bits must be 4, 8, or 16");
+        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "quantised KV rows (%u bits) are not implemented",
+                            p->kv_bits);
+    }
+    if (p->kv_token_stride_elements < p->n_kv_heads * p->head_dim)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "KV token stride is too small");
+    if ((uint64_t)p->start_position + p->query_count > p->kv_valid_count)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "kvValidCount must include all in-flight query rows");
+    if (p->head_dim > (uint32_t)kMaxHeadDim)
+        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "head_dim %u exceeds %d", p->head_dim, kMaxHeadDim);
+    if (io_dtype != TT_F16 && io_dtype != TT_BF16)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "io_dtype must be TT_F16 or TT_BF16");
+    if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 1)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "buffers must be 2-byte aligned");
+    return TT_OK;
+}
+
+}  // namespace
+
+TT_API int tt_attn_prefill_path(const void *q, const void *k, const void *v, const void *out,
+                                const tt_prefill_params *p, uint32_t kv_ring_capacity) {
+    if (p == nullptr) return 0;
+    const bool aligned = ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) == 0) &&
+                         (p->q_token_stride_elements % 8 == 0) && (p->kv_token_stride_elements % 8 == 0) &&
+                         (p->o_token_stride_elements % 8 == 0);
+    return (aligned && p->head_dim == 256 && kv_ring_capacity == 0 && p->kv_bits == 16) ? 1 : 0;
+}
+
+TT_API int tt_attn_prefill_causal(tt_context *ctx, tt_stream stream, const void *q, const void *k, const void *v,
+                                  void *out, const tt_prefill_params *params, uint32_t kv_ring_capacity,
+                                  uint32_t io_dtype) {
+    TT_ENTER(ctx);
+    int rc = validate_prefill(ctx, q, k, v, out, params, io_dtype);
+    if (rc != TT_OK) return rc;
+    if (tt_attn_prefill_path(q, k, v, out, params, kv_ring_capacity) == 1 && getenv("TT_PREFILL_FORCE_GENERIC") == nullptr)
+        return tt_launch_prefill_tc(ctx, (cudaStream_t)stream, q, k, v, out, params, io_dtype);
+    const uint32_t pairs = params->query_count * params->n_q_heads;
+    const uint32_t blocks = (pairs + kGenericWarps - 1) / kGenericWarps;
+    if (io_dtype == TT_F16)
+        attn_prefill_generic_kernel<__half><<<blocks, kGenericWarps * 32, 0, (cudaStream_t)stream>>>(
+            (const __half *)q, (const __half *)k, (const __half *)v, (__half *)out, *params, kv_ring_capacity);
+    else
+        attn_prefill_generic_kernel<__nv_bfloat16><<<blocks, kGenericWarps * 32, 0, (cudaStream_t)stream>>>(
+            (const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v, (__nv_bfloat16 *)out,
+            *params, kv_ring_capacity);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_prefill_generic launch");
+    ctx->launches++;
+    return TT_OK;
+}

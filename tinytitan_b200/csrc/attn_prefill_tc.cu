@@ -1,0 +1,488 @@
+// Causal prefill attention on the sm_100a tensor cores (tcgen05 + TMEM + TMA), head_dim 256.
+//
+// One CTA owns 128 consecutive query rows of one q head. Warp 0 is the TMA producer (Q once,
+// then 64-key K and V tiles through two-stage rings), warp 1 issues the tcgen05 MMAs and owns
+// the TMEM allocation, warps 2-5 (one thread per query row) run the online softmax:
+//
+//   S[j%2]  = Q . K_j^T        SS MMA  M128 N64  K16 x16   (TMEM columns 256.. / 320..)
+//   P_j     = exp2(S - m)      tcgen05.ld -> registers -> tcgen05.st, aliased over S[j%2]
+//   O      += P_j . V_j        TS MMA  M128 N256 K16 x4    (TMEM columns 0..255)
+//
+// The running maximum is only raised when it moved by more than 2^8 ("lazy rescale"); O and the
+// row sum then share one stale reference maximum, which cancels in O / l. Every mbarrier wait
+// is bounded: when a wait runs out the role sets TT_DEV_WAIT_TIMEOUT in the status word and
+// falls through to the common exit, where TMEM is released.
+//
+// Arithmetic semantics: sources/TinyTitanCore/Metal/Prefill/prefill.metal:1056-1158 (visible
+// keys [first, min(kvValid, start+t+1)), fp32 accumulation, row_sum == 0 -> 0).
+#include "tt_common.h"
+
+#include <cuda.h>
+#include <cstdlib>
+
+namespace {
+
+constexpr int kHD = 256;
+constexpr int kBM = 128;              // query rows per CTA
+constexpr int kBN = 64;               // keys per tile
+constexpr int kThreads = 192;
+constexpr uint32_t kWaitLimit = 2000000u;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f;
+
+constexpr int kQBytes = kBM * kHD * 2;         // 65536: 4 sub-tiles [128][64] swizzle-128B
+constexpr int kQSub = kBM * 64 * 2;            // 16384
+constexpr int kKVStage = kBN * kHD * 2;        // 32768: 4 sub-tiles [64][64]
+constexpr int kKVSub = kBN * 64 * 2;           // 8192
+constexpr int kSmemBytes = kQBytes + 4 * kKVStage + 1024 /*align*/ + 256 /*barriers*/;
+
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColO = 0, kColS0 = 256, kColS1 = 320;
+
+struct Barriers {
+    uint64_t q_full;
+    uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+    uint64_t s_full[2], p_ready[2];
+    uint64_t o_ready;
+    uint32_t tmem_base;
+    uint32_t pad;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < kWaitLimit; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field set.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;   // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// A wait result every lane of the warp agrees on (the tcgen05 ld/st that follow are warp-wide).
+__device__ __forceinline__ bool warp_all(bool ok) { return __all_sync(0xffffffffu, ok) != 0; }
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+struct PrefillTcParams {
+    uint32_t start_position, query_count, n_q_heads, n_kv_heads, kv_valid_count, sliding_window;
+    uint32_t o_token_stride;   // elements
+    uint32_t n_q_tiles;
+    float scale_log2;
+    uint32_t idesc_qk, idesc_pv;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                       const __grid_constant__ CUtensorMap v_map, T *__restrict__ out, PrefillTcParams p,
+                       uint32_t *__restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char *q_s = smem;
+    unsigned char *k_s = smem + kQBytes;                  // 2 stages
+    unsigned char *v_s = smem + kQBytes + 2 * kKVStage;   // 2 stages
+    Barriers *bars = reinterpret_cast<Barriers *>(smem + kQBytes + 4 * kKVStage);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // heavy (late) query tiles first; the heads of one KV group are adjacent so they share K/V in L2
+    const uint32_t head = blockIdx.x % p.n_q_heads;
+    const uint32_t q_tile = p.n_q_tiles - 1 - blockIdx.x / p.n_q_heads;
+    const uint32_t kv_head = head / (p.n_q_heads / p.n_kv_heads);
+    const uint32_t row0 = q_tile * kBM;                              // first query row of the tile
+    const uint32_t rows_here = min((uint32_t)kBM, p.query_count - row0);
+    const uint32_t abs_lo = p.start_position + row0;                 // absolute position of row 0
+    const uint32_t abs_hi = abs_lo + rows_here - 1;                  // ... of the last valid row
+    uint32_t key_lo = 0;
+    if (p.sliding_window != 0 && abs_lo + 1 > p.sliding_window) key_lo = abs_lo + 1 - p.sliding_window;
+    const uint32_t key_hi = min(p.kv_valid_count, abs_hi + 1);       // exclusive
+    const uint32_t tile_lo = key_lo / kBN;
+    const uint32_t n_tiles = (key_hi + kBN - 1) / kBN - tile_lo;     // >= 1
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars->q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars->k_full[s], 1);
+            mbar_init(&bars->k_empty[s], 1);
+            mbar_init(&bars->v_full[s], 1);
+            mbar_init(&bars->v_empty[s], 1);
+            mbar_init(&bars->s_full[s], 1);
+            mbar_init(&bars->p_ready[s], 128);
+        }
+        mbar_init(&bars->o_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&bars->tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+    bool failed = false;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_expect_tx(&bars->q_full, kQBytes);
+            for (int sub = 0; sub < 4; ++sub)
+                tma_load_2d(q_s + sub * kQSub, &q_map, (int)(head * kHD + sub * 64), (int)row0, &bars->q_full);
+            auto load_k = [&](uint32_t j) {
+                const int st = j & 1;
+                if (j >= 2 && !mbar_wait(&bars->k_empty[st], ((j >> 1) - 1) & 1)) return false;
+                mbar_expect_tx(&bars->k_full[st], kKVStage);
+                for (int sub = 0; sub < 4; ++sub)
+                    tma_load_2d(k_s + st * kKVStage + sub * kKVSub, &k_map, (int)(kv_head * kHD + sub * 64),
+                                (int)((tile_lo + j) * kBN), &bars->k_full[st]);
+                return true;
+            };
+            auto load_v = [&](uint32_t j) {
+                const int st = j & 1;
+                if (j >= 2 && !mbar_wait(&bars->v_empty[st], ((j >> 1) - 1) & 1)) return false;
+                mbar_expect_tx(&bars->v_full[st], kKVStage);
+                for (int sub = 0; sub < 4; ++sub)
+                    tma_load_2d(v_s + st * kKVStage + sub * kKVSub, &v_map, (int)(kv_head * kHD + sub * 64),
+                                (int)((tile_lo + j) * kBN), &bars->v_full[st]);
+                return true;
+            };
+            bool ok = load_k(0);
+            if (ok && n_tiles > 1) ok = load_k(1);
+            for (uint32_t j = 0; ok && j < n_tiles; ++j) {
+                ok = load_v(j);
+                if (ok && j + 2 < n_tiles) ok = load_k(j + 2);
+            }
+            failed = !ok;
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+            auto issue_qk = [&](uint32_t j) {
+                const int st = j & 1;
+                if (!mbar_wait(&bars->k_full[st], (j >> 1) & 1)) return false;
+                tc_fence_after();
+                const uint32_t d = tmem + (st ? kColS1 : kColS0);
+#pragma unroll
+                for (int ks = 0; ks < kHD / 16; ++ks) {
+                    const uint64_t ad = make_desc(q_addr + (ks >> 2) * kQSub + (ks & 3) * 32, 16, 1024);
+                    const uint64_t bd = make_desc(k_addr + st * kKVStage + (ks >> 2) * kKVSub + (ks & 3) * 32, 16, 1024);
+                    mma_ss(d, ad, bd, p.idesc_qk, ks > 0 ? 1u : 0u);
+                }
+                mma_commit(&bars->k_empty[st]);
+                mma_commit(&bars->s_full[st]);
+                return true;
+            };
+            bool ok = mbar_wait(&bars->q_full, 0);
+            if (ok) ok = issue_qk(0);
+            for (uint32_t j = 0; ok && j < n_tiles; ++j) {
+                if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+                const int st = j & 1;
+                if (ok) ok = mbar_wait(&bars->p_ready[st], (j >> 1) & 1);
+                if (ok) ok = mbar_wait(&bars->v_full[st], (j >> 1) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_tmem = tmem + (st ? kColS1 : kColS0);
+#pragma unroll
+                for (int kk = 0; kk < kBN / 16; ++kk) {
+                    // V tile as the MN-major B operand: 64-wide head-dim atoms 8192 B apart (LBO),
+                    // 8-key groups 1024 B apart (SBO)
+                    const uint64_t bd = make_desc(v_addr + st * kKVStage + kk * 2048, kKVSub, 1024);
+                    mma_ts(tmem + kColO, a_tmem + kk * 8, bd, p.idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                mma_commit(&bars->v_empty[st]);
+                mma_commit(&bars->o_ready);
+            }
+            failed = !ok;
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax, one row per thread
+        const uint32_t quarter = warp & 3;                       // TMEM lane quarter this warp may touch
+        const uint32_t row = quarter * 32 + lane;                // row inside the tile
+        const uint32_t lane_addr = (quarter * 32) << 16;
+        const bool row_valid = row < rows_here;
+        const uint32_t abs_q = abs_lo + row;
+        uint32_t first = 0;
+        if (p.sliding_window != 0 && abs_q + 1 > p.sliding_window) first = abs_q + 1 - p.sliding_window;
+        const uint32_t last = min(p.kv_valid_count, abs_q + 1);  // exclusive
+
+        float m_ref = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (uint32_t j = 0; j < n_tiles; ++j) {
+            const int st = j & 1;
+            ok = warp_all(mbar_wait(&bars->s_full[st], (j >> 1) & 1));
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t s_addr = tmem + lane_addr + (st ? kColS1 : kColS0);
+            uint32_t raw[2][32];
+            tmem_ld32(s_addr, raw[0]);
+            tmem_ld32(s_addr + 32, raw[1]);
+            tmem_wait_ld();
+
+            const uint32_t key0 = (tile_lo + j) * kBN;
+            const bool need_mask = (key0 + kBN > abs_lo + 1) || (key0 < first) || (key0 + kBN > p.kv_valid_count);
+            float mx = -INFINITY;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    float s = __uint_as_float(raw[h][c]) * p.scale_log2;
+                    if (need_mask) {
+                        const uint32_t key = key0 + h * 32 + c;
+                        if (key < first || key >= last) s = -INFINITY;
+                    }
+                    raw[h][c] = __float_as_uint(s);
+                    mx = fmaxf(mx, s);
+                }
+            float m_new = fmaxf(m_ref, mx);
+            // lazy rescale: keep the stale reference while it is within 2^8 of the true maximum
+            const bool raise = (m_new - m_ref > kRescaleThreshold) || (m_ref == -INFINITY && m_new != -INFINITY);
+            if (j == 0) {
+                m_ref = m_new;
+            } else if (__any_sync(0xffffffffu, raise)) {
+                // O holds sum over tiles < j; it may only be touched once P.V of tile j-1 retired
+                ok = warp_all(mbar_wait(&bars->o_ready, (j - 1) & 1));
+                if (!ok) break;
+                tc_fence_after();
+                const float factor = raise ? fast_exp2(m_ref - m_new) : 1.f;   // exp2(-inf) == 0: O was all zero
+                if (raise) { l_run *= factor; m_ref = m_new; }
+#pragma unroll 1
+                for (int c0 = 0; c0 < kHD; c0 += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem + lane_addr + kColO + c0, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
+                    tmem_st32(tmem + lane_addr + kColO + c0, o);
+                }
+                tmem_wait_st();
+            }
+            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            uint32_t pk[32];
+            float rs = 0.f;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const float p0 = fast_exp2(__uint_as_float(raw[c >> 4][(2 * c) & 31]) - m_use);
+                const float p1 = fast_exp2(__uint_as_float(raw[c >> 4][(2 * c + 1) & 31]) - m_use);
+                rs += p0 + p1;
+                pk[c] = pack2<T>(p0, p1);
+            }
+            l_run += rs;
+            tmem_st32(s_addr, pk);          // P (16-bit pairs) over the first 32 columns of S[j%2]
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bars->p_ready[st]);
+        }
+        if (ok) ok = mbar_wait(&bars->o_ready, (n_tiles - 1) & 1);
+        ok = warp_all(ok);
+        if (ok) {
+            tc_fence_after();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            T *orow = out + (size_t)(row0 + row) * p.o_token_stride + (size_t)head * kHD;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kHD; c0 += 32) {
+                uint32_t o[32];
+                tmem_ld32(tmem + lane_addr + kColO + c0, o);
+                tmem_wait_ld();
+                if (row_valid) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 w;
+                        w.x = pack2<T>(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+                        w.y = pack2<T>(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+                        w.z = pack2<T>(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+                        w.w = pack2<T>(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+                        *reinterpret_cast<uint4 *>(orow + c0 + c) = w;
+                    }
+                }
+            }
+        }
+        failed = !ok;
+    }
+
+    if (failed) atomicOr(status, TT_DEV_WAIT_TIMEOUT);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// 2-D map over [rows][width] 16-bit elements, rows `stride_elems` apart, box [box_rows][64].
+bool make_map(CUtensorMap *map, const void *base, uint32_t io_dtype, uint64_t width, uint64_t rows,
+              uint64_t stride_elems, uint32_t box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {width, rows};
+    const cuuint64_t strides[1] = {stride_elems * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt = io_dtype == TT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    return fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+uint32_t make_idesc(uint32_t io_dtype, uint32_t n, bool b_mn_major) {
+    const uint32_t fmt = io_dtype == TT_BF16 ? 1u : 0u;
+    uint32_t d = 0;
+    d |= 1u << 4;            // D format f32
+    d |= fmt << 7;           // A format
+    d |= fmt << 10;          // B format
+    d |= (b_mn_major ? 1u : 0u) << 16;
+    d |= (n >> 3) << 17;
+    d |= (128u >> 4) << 24;  // M = 128
+    return d;
+}
+
+}  // namespace
+
+int tt_launch_prefill_tc(tt_context *ctx, cudaStream_t stream, const void *q, const void *k, const void *v,
+                         void *out, const tt_prefill_params *p, uint32_t io_dtype) {
+    CUtensorMap q_map, k_map, v_map;
+    const bool ok = make_map(&q_map, q, io_dtype, (uint64_t)p->n_q_heads * kHD, p->query_count,
+                             p->q_token_stride_elements, kBM) &&
+                    make_map(&k_map, k, io_dtype, (uint64_t)p->n_kv_heads * kHD, p->kv_valid_count,
+                             p->kv_token_stride_elements, kBN) &&
+                    make_map(&v_map, v, io_dtype, (uint64_t)p->n_kv_heads * kHD, p->kv_valid_count,
+                             p->kv_token_stride_elements, kBN);
+    if (!ok) return tt_set_error(ctx, TT_ERR_CUDA, "cuTensorMapEncodeTiled failed for the prefill operands");
+    PrefillTcParams kp;
+    kp.start_position = p->start_position; kp.query_count = p->query_count; kp.n_q_heads = p->n_q_heads;
+    kp.n_kv_heads = p->n_kv_heads; kp.kv_valid_count = p->kv_valid_count; kp.sliding_window = p->sliding_window;
+    kp.o_token_stride = p->o_token_stride_elements;
+    kp.n_q_tiles = (p->query_count + kBM - 1) / kBM;
+    kp.scale_log2 = p->scale * kLog2e;
+    kp.idesc_qk = make_idesc(io_dtype, kBN, false);
+    kp.idesc_pv = make_idesc(io_dtype, kHD, true);
+    const uint32_t grid = kp.n_q_tiles * p->n_q_heads;
+    cudaError_t e;
+    if (io_dtype == TT_F16) {
+        auto kernel = attn_prefill_tc_kernel<__half>;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return tt_check_cuda(ctx, e, "prefill smem attribute");
+        kernel<<<grid, kThreads, kSmemBytes, stream>>>(q_map, k_map, v_map, reinterpret_cast<__half *>(out), kp, ctx->status);
+    } else {
+        auto kernel = attn_prefill_tc_kernel<__nv_bfloat16>;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return tt_check_cuda(ctx, e, "prefill smem attribute");
+        kernel<<<grid, kThreads, kSmemBytes, stream>>>(q_map, k_map, v_map, reinterpret_cast<__nv_bfloat16 *>(out), kp, ctx->status);
+    }
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_prefill_tc launch");
+    ctx->launches++;
+    return TT_OK;
+}

@@ -1,0 +1,250 @@
+// Gated delta rule, token-ordered: decode step (rows == 1) and the exact sequential
+// multi-row form (verify rows / sequential prefill), batched over independent sessions.
+//
+// Replaces gdn_delta_step_decode and gdn_delta_step_prefill
+// (sources/TinyTitanCore/Metal/GDN/gdn.metal:529-669) and their host wrappers
+// GDN.encodeDeltaStepDecode / encodeDeltaStepPrefill
+// (sources/TinyTitan/Kernels/GDN/GDN.swift:318-396).
+//
+// HBM-bound design: the fp32 state [Hv][Dv][Dk] is read once and written once per call
+// whatever the number of rows. A CTA owns 32 state rows of one (session, head); each of its 4
+// warps holds 8 rows in registers (a lane owns Dk/32 consecutive floats of each row), so the
+// eight 16-byte loads of a lane are in flight together. Per token the two dot products of a
+// row (S.k and S.q) are warp-shuffle reductions; the state never leaves registers between
+// tokens.
+#include "tt_common.h"
+
+namespace {
+
+constexpr int kRowsPerWarp = 8;
+constexpr int kWarps = 4;
+constexpr int kRowsPerCta = kRowsPerWarp * kWarps;
+
+struct GdnParams {
+    const tt_gdn_session *sessions;
+    const __nv_bfloat16 *a_log;
+    const __nv_bfloat16 *dt_bias;
+    uint32_t hk, hv, dk, dv, rows, row_stride, flags;
+    float readout_scale;
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <int NPL>
+__device__ __forceinline__ void load_vec(float (&dst)[NPL], const float *src) {
+    if constexpr (NPL == 4) {
+        const float4 t = *reinterpret_cast<const float4 *>(src);
+        dst[0] = t.x; dst[1] = t.y; dst[2] = t.z; dst[3] = t.w;
+    } else if constexpr (NPL == 2) {
+        const float2 t = *reinterpret_cast<const float2 *>(src);
+        dst[0] = t.x; dst[1] = t.y;
+    } else {
+        dst[0] = *src;
+    }
+}
+
+template <int NPL>
+__device__ __forceinline__ void store_vec(float *dst, const float (&src)[NPL]) {
+    if constexpr (NPL == 4) {
+        *reinterpret_cast<float4 *>(dst) = make_float4(src[0], src[1], src[2], src[3]);
+    } else if constexpr (NPL == 2) {
+        *reinterpret_cast<float2 *>(dst) = make_float2(src[0], src[1]);
+    } else {
+        *dst = src[0];
+    }
+}
+
+template <int NPL>
+__device__ __forceinline__ void load_half_vec(float (&dst)[NPL], const __half *src) {
+    if constexpr (NPL == 4) {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(src);
+        const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+        const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+        dst[0] = lo.x; dst[1] = lo.y; dst[2] = hi.x; dst[3] = hi.y;
+    } else if constexpr (NPL == 2) {
+        const float2 t = __half22float2(*reinterpret_cast<const __half2 *>(src));
+        dst[0] = t.x; dst[1] = t.y;
+    } else {
+        dst[0] = __half2float(*src);
+    }
+}
+
+// grid = (dv blocks, Hv, sessions), block = 128.
+template <int NPL>
+__global__ void __launch_bounds__(kWarps * 32) gdn_step_kernel(GdnParams p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t h = blockIdx.y;
+    const tt_gdn_session ses = p.sessions[blockIdx.z];
+    const uint32_t dv0 = blockIdx.x * kRowsPerCta + warp * kRowsPerWarp;
+    const uint32_t hk = (p.flags & TT_GDN_V_TILED) ? h % p.hk : h / (p.hv / p.hk);
+    const uint32_t col = lane * NPL;
+
+    float *state = ses.state + ((size_t)h * p.dv) * p.dk;
+    float s[kRowsPerWarp][NPL];
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+        if (dv0 + r < p.dv) {
+            load_vec<NPL>(s[r], state + (size_t)(dv0 + r) * p.dk + col);
+        } else {
+#pragma unroll
+            for (int i = 0; i < NPL; ++i) s[r][i] = 0.f;
+        }
+    }
+
+    const float a_param = __bfloat162float(p.a_log[h]);
+    const float dtb = __bfloat162float(p.dt_bias[h]);
+
+    for (uint32_t t = 0; t < p.rows; ++t) {
+        const __half *row = reinterpret_cast<const __half *>(ses.conv_out) + (size_t)t * p.row_stride;
+        float q[NPL], k[NPL];
+        load_half_vec<NPL>(q, row + (size_t)hk * p.dk + col);
+        load_half_vec<NPL>(k, row + (size_t)p.hk * p.dk + (size_t)hk * p.dk + col);
+        const __half *vrow = row + (size_t)2 * p.hk * p.dk + (size_t)h * p.dv;
+
+        float g, beta;
+        if (p.flags & TT_GDN_GATES_F32) {
+            g = reinterpret_cast<const float *>(ses.a)[(size_t)t * p.hv + h];
+            beta = reinterpret_cast<const float *>(ses.b)[(size_t)t * p.hv + h];
+        } else {
+            const float av = __half2float(reinterpret_cast<const __half *>(ses.a)[(size_t)t * p.hv + h]);
+            const float bv = __half2float(reinterpret_cast<const __half *>(ses.b)[(size_t)t * p.hv + h]);
+            const float x = av + dtb;
+            const float sp = x > 20.f ? x : logf(1.f + expf(x));
+            g = (p.flags & TT_GDN_A_LOG_PREEXP) ? expf(a_param * sp) : expf(-expf(a_param) * sp);
+            beta = 1.f / (1.f + expf(-bv));
+        }
+
+        float kv[kRowsPerWarp];
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < NPL; ++i) {
+                s[r][i] *= g;
+                acc = fmaf(s[r][i], k[i], acc);
+            }
+            kv[r] = acc;
+        }
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) kv[r] = warp_sum(kv[r]);
+
+        float out[kRowsPerWarp];
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+            const float vv = (dv0 + r < p.dv) ? __half2float(vrow[dv0 + r]) : 0.f;
+            const float delta = (vv - kv[r]) * beta;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < NPL; ++i) {
+                s[r][i] = fmaf(k[i], delta, s[r][i]);
+                acc = fmaf(s[r][i], q[i], acc);
+            }
+            out[r] = acc;
+        }
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) out[r] = warp_sum(out[r]);
+
+        // lanes 0..7 each store one row's readout
+        float mine = 0.f;
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) mine = (lane == r) ? out[r] : mine;
+        if (lane < kRowsPerWarp && dv0 + lane < p.dv) {
+            __half *y = reinterpret_cast<__half *>(ses.y) + (size_t)t * p.hv * p.dv + (size_t)h * p.dv;
+            y[dv0 + lane] = __float2half_rn(mine * p.readout_scale);
+        }
+
+        if (t == 0 && ses.checkpoint_state != nullptr) {
+            float *ck = ses.checkpoint_state + ((size_t)h * p.dv) * p.dk;
+#pragma unroll
+            for (int r = 0; r < kRowsPerWarp; ++r)
+                if (dv0 + r < p.dv) store_vec<NPL>(ck + (size_t)(dv0 + r) * p.dk + col, s[r]);
+        }
+    }
+
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r)
+        if (dv0 + r < p.dv) store_vec<NPL>(state + (size_t)(dv0 + r) * p.dk + col, s[r]);
+}
+
+int validate_shape(tt_context *ctx, const tt_gdn_shape *shape, uint32_t rows, uint32_t row_stride) {
+    if (shape == nullptr) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "shape must not be null");
+    if (shape->n_k_heads == 0 || shape->n_v_heads == 0 || shape->n_v_heads % shape->n_k_heads != 0)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "n_v_heads must be a positive multiple of n_k_heads");
+    if (shape->key_dim != 32 && shape->key_dim != 64 && shape->key_dim != 128)
+        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "key_dim must be 32, 64 or 128, got %u", shape->key_dim);
+    if (shape->value_dim == 0 || shape->value_dim % 8 != 0)
+        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "value_dim must be a multiple of 8");
+    if (rows == 0) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "rows must be positive");
+    const uint32_t tight = 2 * shape->n_k_heads * shape->key_dim + shape->n_v_heads * shape->value_dim;
+    if (row_stride < tight)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "row_stride %u is smaller than the qkv width %u", row_stride, tight);
+    if (row_stride % 4 != 0)
+        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "row_stride must be a multiple of 4 elements");
+    return TT_OK;
+}
+
+int launch_step(tt_context *ctx, cudaStream_t stream, const tt_gdn_session *h_sessions, uint32_t n,
+                const void *a_log, const void *dt_bias, const tt_gdn_shape *shape, uint32_t rows,
+                uint32_t row_stride) {
+    int rc = validate_shape(ctx, shape, rows, row_stride);
+    if (rc != TT_OK) return rc;
+    if (n == 0) return TT_OK;
+    if (n > ctx->max_sessions)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "n_sessions %u exceeds the context's max_sessions %u", n,
+                            ctx->max_sessions);
+    const bool f32_gates = (shape->flags & TT_GDN_GATES_F32) != 0;
+    if (!f32_gates && (a_log == nullptr || dt_bias == nullptr))
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "a_log and dt_bias must not be null");
+    for (uint32_t i = 0; i < n; ++i) {
+        const tt_gdn_session &s = h_sessions[i];
+        if (!s.conv_out || !s.a || !s.b || !s.state || !s.y)
+            return tt_set_error(ctx, TT_ERR_INVALID_ARG, "session %u has a null buffer", i);
+        if (((uintptr_t)s.conv_out & 7) || ((uintptr_t)s.state & 15) || ((uintptr_t)s.checkpoint_state & 15))
+            return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "session %u: misaligned buffer", i);
+    }
+    cudaError_t e = cudaMemcpyAsync(ctx->gdn_sessions, h_sessions, sizeof(tt_gdn_session) * n,
+                                    cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "copy gdn session table");
+    GdnParams p;
+    p.sessions = reinterpret_cast<const tt_gdn_session *>(ctx->gdn_sessions);
+    // with fp32 gates the decay parameters are unused; point them at the session table so the
+    // two scalar loads stay in bounds
+    p.a_log = reinterpret_cast<const __nv_bfloat16 *>(f32_gates && !a_log ? ctx->gdn_sessions : a_log);
+    p.dt_bias = reinterpret_cast<const __nv_bfloat16 *>(f32_gates && !dt_bias ? ctx->gdn_sessions : dt_bias);
+    p.hk = shape->n_k_heads; p.hv = shape->n_v_heads; p.dk = shape->key_dim; p.dv = shape->value_dim;
+    p.rows = rows; p.row_stride = row_stride; p.flags = shape->flags; p.readout_scale = shape->readout_scale;
+    const dim3 grid((shape->value_dim + kRowsPerCta - 1) / kRowsPerCta, shape->n_v_heads, n);
+    switch (shape->key_dim) {
+        case 128: gdn_step_kernel<4><<<grid, kWarps * 32, 0, stream>>>(p); break;
+        case 64: gdn_step_kernel<2><<<grid, kWarps * 32, 0, stream>>>(p); break;
+        default: gdn_step_kernel<1><<<grid, kWarps * 32, 0, stream>>>(p); break;
+    }
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn_step launch");
+    ctx->launches++;
+    return TT_OK;
+}
+
+}  // namespace
+
+TT_API int tt_gdn_step(tt_context *ctx, tt_stream stream, const void *conv_out, const void *a, const void *b,
+                       const void *a_log, const void *dt_bias, float *state, void *y, const tt_gdn_shape *shape,
+                       uint32_t rows, uint32_t row_stride, float *checkpoint_state) {
+    TT_ENTER(ctx);
+    tt_gdn_session s;
+    s.conv_out = conv_out; s.a = a; s.b = b; s.state = state; s.y = y; s.checkpoint_state = checkpoint_state;
+    return launch_step(ctx, (cudaStream_t)stream, &s, 1, a_log, dt_bias, shape, rows, row_stride);
+}
+
+TT_API int tt_gdn_step_batched(tt_context *ctx, tt_stream stream, const tt_gdn_session *sessions,
+                               uint32_t n_sessions, const void *a_log, const void *dt_bias,
+                               const tt_gdn_shape *shape, uint32_t rows, uint32_t row_stride) {
+    TT_ENTER(ctx);
+    if (sessions == nullptr && n_sessions != 0)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "sessions must not be null");
+    return launch_step(ctx, (cudaStream_t)stream, sessions, n_sessions, a_log, dt_bias, shape, rows, row_stride);
+}

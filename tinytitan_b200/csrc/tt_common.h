@@ -1,0 +1,111 @@
+// Internal declarations shared by the translation units of libtinytitan_cuda.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+
+#include "tinytitan_cuda.h"
+
+#define TT_API extern "C" __attribute__((visibility("default")))
+
+// Device-side status bits (tt_ctx_poll_status).
+enum : uint32_t {
+    TT_DEV_WAIT_TIMEOUT = 1u,   // a bounded mbarrier / flag wait ran out
+    TT_DEV_BAD_ITEM = 2u,       // a work item failed its own bounds check
+};
+
+// One split-KV work item of the batched decode kernel (device + host view).
+struct TTDecodeItem {
+    uint32_t session;
+    uint32_t kv_head;
+    uint32_t key_begin;   // first key of this item (absolute position)
+    uint32_t key_end;     // one past the last key
+    uint32_t part_index;  // index of this item's partial among the session's parts
+    uint32_t row_begin;   // first packed row (w*G + g) this item serves
+    uint32_t row_count;   // rows served (<= 16 per CTA pass)
+    uint32_t partial_base; // first partial row of this item in the workspace
+};
+
+// One session of the batched decode kernel (device view).
+struct TTDecodeSession {
+    const void *q;
+    void *out;
+    const void *k;
+    const void *v;
+    uint32_t seq_len;
+    uint32_t q_rows;
+    uint32_t kv_start;
+    uint32_t n_parts;        // key splits of this session
+    uint32_t partial_base;   // first partial row of this session in the workspace
+    uint32_t ring_capacity;
+    const uint8_t *keep;     // nullable
+};
+
+struct tt_context {
+    int device = 0;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    size_t workspace_bytes = 0;
+    uint32_t max_sessions = 0;
+    uint32_t max_items = 0;
+    // device scratch, allocated once at creation
+    float *partials = nullptr;          // [rows][head_dim + 2] fp32 split partials
+    TTDecodeItem *items = nullptr;
+    TTDecodeSession *sessions = nullptr;
+    void *gdn_sessions = nullptr;       // tt_gdn_session[max_sessions]
+    uint32_t *status = nullptr;         // device status word
+    // host staging (pageable; async copies from it are staged by the driver before returning)
+    TTDecodeItem *h_items = nullptr;
+    TTDecodeSession *h_sessions = nullptr;
+    TTDecodeSession *h_sessions_in = nullptr;
+    uint32_t *h_keys = nullptr;
+    uint32_t *h_rows = nullptr;
+    uint64_t launches = 0;
+    // optional per-launch timing of the dominant (split-KV pass 1) kernel
+    static constexpr uint32_t kProfileSlots = 256;
+    bool profiling = false;
+    uint32_t profile_count = 0;
+    cudaEvent_t *profile_begin = nullptr;
+    cudaEvent_t *profile_end = nullptr;
+    volatile int busy = 0;
+    char err[512] = {0};
+};
+
+int tt_set_error(tt_context *ctx, int code, const char *fmt, ...);
+int tt_check_cuda(tt_context *ctx, cudaError_t e, const char *what);
+
+struct TTBusyGuard {
+    tt_context *ctx;
+    bool ok;
+    explicit TTBusyGuard(tt_context *c) : ctx(c) {
+        ok = (__sync_lock_test_and_set(&c->busy, 1) == 0);
+    }
+    ~TTBusyGuard() { if (ok) __sync_lock_release(&ctx->busy); }
+};
+
+#define TT_ENTER(ctx)                                                                 \
+    if ((ctx) == nullptr) return TT_ERR_INVALID_ARG;                                  \
+    TTBusyGuard tt_guard_(ctx);                                                       \
+    if (!tt_guard_.ok) return TT_ERR_BUSY;                                            \
+    {                                                                                 \
+        cudaError_t tt_e_ = cudaSetDevice((ctx)->device);                             \
+        if (tt_e_ != cudaSuccess) return tt_check_cuda((ctx), tt_e_, "cudaSetDevice"); \
+    }
+
+// Host-side planner shared by the C entry point and the launcher.
+struct TTPlan {
+    uint32_t keys_per_item;
+    uint32_t n_items;
+    uint32_t n_partial_rows;
+};
+
+// Launchers implemented in the .cu files.
+int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession *h_sessions,
+                     uint32_t n_sessions, const tt_attn_batch_params *p, int mode,
+                     float *m_out, float *d_out, float *o_out);

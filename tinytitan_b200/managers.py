@@ -1,0 +1,261 @@
+"""Host-side mirror of KVCacheManager and GDNStateManager over the C ABI.
+
+  KVCacheManager   sources/TinyTitan/Runtime/KVCache/KVCacheManager.swift:62-333 (+Storage, +Views)
+  GDNStateManager  sources/TinyTitan/Runtime/KVCache/GDNStateManager.swift:18-354
+
+Accessors return integer device addresses (the reference returns MTLBuffer + byte offset).
+`allocator="host"` backs the managers with host memory so that the bookkeeping can be tested
+without a GPU; the default is CUDA device memory.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+from . import _lib as L
+from .operators import LinearAttentionConfig
+
+SWA, FULL, LINEAR = 0, 1, 2
+
+
+@dataclass
+class ArchConfig:
+    """The fields of ArchConfig the two managers read."""
+    layer_kinds: List[int]                      # fullAttentionLayerMask: 0 swa, 1 full, 2 linear
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    num_full_kv_heads: int = 0
+    full_head_dim: int = 0
+    sliding_window: int = 0
+    linear_attention: LinearAttentionConfig = field(default_factory=lambda: LinearAttentionConfig(0, 0, 0, 0, 0))
+
+    @property
+    def num_layers(self) -> int:
+        return len(self.layer_kinds)
+
+    def to_c(self):
+        kinds = (C.c_uint8 * len(self.layer_kinds))(*self.layer_kinds)
+        la = self.linear_attention
+        arch = L.Arch(len(self.layer_kinds), kinds, self.num_kv_heads, self.head_dim, self.num_full_kv_heads,
+                      self.full_head_dim, self.sliding_window, la.num_k_heads, la.num_v_heads, la.key_head_dim,
+                      la.value_head_dim, la.conv_kernel_size)
+        arch._keepalive = kinds
+        return arch
+
+    @staticmethod
+    def qwen36_35b_a3b() -> "ArchConfig":
+        """Qwen3.6-35B-A3B geometry (sources/TinyTitan/Infrastructure/ModelIO/ModelTypes.swift:9-43)."""
+        kinds = [FULL if (i + 1) % 4 == 0 else LINEAR for i in range(40)]
+        return ArchConfig(kinds, 2, 256, 2, 256, 0, LinearAttentionConfig(16, 32, 128, 128, 4))
+
+
+@dataclass
+class KVView:
+    buffer: int
+    offset: int
+    stride: int
+    valid_token_count: int
+    precision_bits: int
+    value_bytes: int
+    group_size: int
+    ring_capacity: int
+
+    @property
+    def address(self) -> int:
+        return self.buffer + self.offset
+
+
+def _host_allocator():
+    libc = C.CDLL(None)
+    libc.malloc.restype = C.c_void_p
+    libc.malloc.argtypes = [C.c_size_t]
+    libc.free.argtypes = [C.c_void_p]
+    live = {}
+
+    def alloc(_user, n):
+        p = libc.malloc(max(int(n), 1))
+        live[p] = int(n)
+        return p
+
+    def release(_user, p):
+        live.pop(p, None)
+        libc.free(p)
+
+    def copy(_user, dst, src, n):
+        C.memmove(dst, src, n)
+        return 0
+
+    def zero(_user, dst, n):
+        C.memset(dst, 0, n)
+        return 0
+
+    a = L.Allocator(None, L.ALLOC_FN(alloc), L.RELEASE_FN(release), L.COPY_FN(copy), L.ZERO_FN(zero))
+    a._live = live
+    return a
+
+
+class KVCacheManager:
+    maximum_slots = 256
+    initial_capacity_tokens = 8192
+    quantization_group_size = 64
+
+    def __init__(self, config: ArchConfig, max_context: int, slots: int = 1, fp16_ring_enabled: bool = False,
+                 precision: int = 16, max_prefill_chunk_tokens: int = 128, allocator: Optional[str] = None):
+        if max_context <= 0:
+            raise L.InvalidArgument(L.TT_ERR_INVALID_ARG, "maxContext must be positive")
+        if not (0 < slots <= self.maximum_slots):
+            raise L.InvalidArgument(L.TT_ERR_INVALID_ARG, f"slots must be between 1 and {self.maximum_slots}")
+        self.config, self.max_context, self.slots, self.precision = config, max_context, slots, precision
+        self._allocator = _host_allocator() if allocator == "host" else None
+        self._arch = config.to_c()
+        err = C.c_int(0)
+        self.handle = L.lib().tt_kv_cache_create(
+            C.byref(self._arch), max_context, slots, precision, int(fp16_ring_enabled), max_prefill_chunk_tokens,
+            C.byref(self._allocator) if self._allocator is not None else None, C.byref(err))
+        if not self.handle:
+            L.check(err.value or L.TT_ERR_OOM)
+
+    def close(self):
+        if getattr(self, "handle", None):
+            L.lib().tt_kv_cache_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @staticmethod
+    def row_layout(elements: int, precision: int):
+        s, v = C.c_uint32(0), C.c_uint32(0)
+        L.lib().tt_kv_row_layout(elements, precision, C.byref(s), C.byref(v))
+        return s.value, v.value
+
+    @staticmethod
+    def worst_case_bytes(config: ArchConfig, max_context: int, precision: int = 16, slots: int = 1) -> int:
+        arch = config.to_c()
+        return int(L.lib().tt_kv_cache_worst_case_bytes(C.byref(arch), max_context, precision, slots))
+
+    def reserve(self, tokens: int, slot: int = 0):
+        L.check(L.lib().tt_kv_cache_reserve(self.handle, tokens, slot))
+
+    def k_slot(self, layer: int, position: int, slot: int = 0) -> int:
+        p = C.c_void_p(0)
+        L.check(L.lib().tt_kv_cache_k_slot(self.handle, layer, position, slot, C.byref(p)))
+        return p.value or 0
+
+    def v_slot(self, layer: int, position: int, slot: int = 0) -> int:
+        p = C.c_void_p(0)
+        L.check(L.lib().tt_kv_cache_v_slot(self.handle, layer, position, slot, C.byref(p)))
+        return p.value or 0
+
+    def _view(self, fn, layer, slot, valid) -> KVView:
+        v = L.KVViewC()
+        L.check(fn(self.handle, layer, slot, self.position(slot) if valid is None else valid, C.byref(v)))
+        return KVView(v.buffer or 0, v.offset, v.stride, v.valid_token_count, v.precision_bits, v.value_bytes,
+                      v.group_size, v.ring_capacity)
+
+    def key_view(self, layer: int, slot: int = 0, valid_token_count: Optional[int] = None) -> KVView:
+        return self._view(L.lib().tt_kv_cache_key_view, layer, slot, valid_token_count)
+
+    def value_view(self, layer: int, slot: int = 0, valid_token_count: Optional[int] = None) -> KVView:
+        return self._view(L.lib().tt_kv_cache_value_view, layer, slot, valid_token_count)
+
+    def advance(self, slot: int = 0, by: int = 1):
+        L.check(L.lib().tt_kv_cache_advance(self.handle, slot, by))
+
+    def rewind(self, to: int, slot: int = 0):
+        L.check(L.lib().tt_kv_cache_rewind(self.handle, slot, to))
+
+    def reset(self, slot: Optional[int] = None):
+        if slot is None:
+            L.check(L.lib().tt_kv_cache_reset(self.handle))
+        else:
+            L.check(L.lib().tt_kv_cache_reset_slot(self.handle, slot))
+
+    def position(self, slot: int = 0) -> int:
+        if not (0 <= slot < self.slots):
+            raise L.InvalidArgument(L.TT_ERR_INVALID_ARG, f"slot {slot} is out of range 0..<{self.slots}")
+        return int(L.lib().tt_kv_cache_position(self.handle, slot))
+
+    def capacity(self, layer: int) -> int:
+        return int(L.lib().tt_kv_cache_capacity(self.handle, layer))
+
+    def stride(self, layer: int) -> int:
+        return int(L.lib().tt_kv_cache_stride(self.handle, layer))
+
+    def layer_kind(self, layer: int) -> int:
+        return int(L.lib().tt_kv_cache_layer_kind(self.handle, layer))
+
+    def buffer_length(self, layer: int) -> int:
+        return int(L.lib().tt_kv_cache_buffer_length(self.handle, layer))
+
+
+class GDNStateManager:
+    maximum_slots = KVCacheManager.maximum_slots
+
+    def __init__(self, config: ArchConfig, slots: int = 1, enable_speculative_checkpoint: bool = False,
+                 allocator: Optional[str] = None):
+        if not (0 < slots <= self.maximum_slots):
+            raise L.InvalidArgument(L.TT_ERR_INVALID_ARG, f"slots must be between 1 and {self.maximum_slots}")
+        self.config, self.slots = config, slots
+        self._allocator = _host_allocator() if allocator == "host" else None
+        self._arch = config.to_c()
+        err = C.c_int(0)
+        self.handle = L.lib().tt_gdn_state_create(
+            C.byref(self._arch), slots, int(enable_speculative_checkpoint),
+            C.byref(self._allocator) if self._allocator is not None else None, C.byref(err))
+        if not self.handle:
+            L.check(err.value or L.TT_ERR_OOM)
+
+    def close(self):
+        if getattr(self, "handle", None):
+            L.lib().tt_gdn_state_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @staticmethod
+    def worst_case_bytes(config: ArchConfig, slots: int = 1) -> int:
+        arch = config.to_c()
+        return int(L.lib().tt_gdn_state_worst_case_bytes(C.byref(arch), slots))
+
+    @property
+    def state_bytes_per_layer(self) -> int:
+        return int(L.lib().tt_gdn_state_bytes_per_layer(self.handle))
+
+    @property
+    def conv_tail_bytes_per_layer(self) -> int:
+        return int(L.lib().tt_gdn_state_conv_tail_bytes_per_layer(self.handle))
+
+    def is_linear(self, layer: int) -> bool:
+        return bool(L.lib().tt_gdn_state_is_linear(self.handle, layer))
+
+    def _slot(self, fn, layer, slot) -> int:
+        p = C.c_void_p(0)
+        L.check(fn(self.handle, layer, slot, C.byref(p)))
+        return p.value or 0
+
+    def state_slot(self, layer: int, slot: int = 0) -> int:
+        return self._slot(L.lib().tt_gdn_state_state_slot, layer, slot)
+
+    def conv_tail_slot(self, layer: int, slot: int = 0) -> int:
+        return self._slot(L.lib().tt_gdn_state_conv_tail_slot, layer, slot)
+
+    def speculative_state_slot(self, layer: int, slot: int = 0) -> int:
+        return self._slot(L.lib().tt_gdn_state_speculative_state_slot, layer, slot)
+
+    def reset(self, slot: Optional[int] = None):
+        if slot is None:
+            L.check(L.lib().tt_gdn_state_reset(self.handle))
+        else:
+            L.check(L.lib().tt_gdn_state_reset_slot(self.handle, slot))
+
+    def speculative_restore(self):
+        L.check(L.lib().tt_gdn_state_speculative_restore(self.handle))

@@ -1,0 +1,351 @@
+"""Host-side mirror of the reference's attention operator classes over the C ABI.
+
+The classes keep the names, argument meaning and error behaviour of the Swift operators they
+stand in for, so call sites and tests read like the reference's:
+
+  Attention         sources/TinyTitan/Kernels/Attention/Attention.swift:270-470
+  PrefillAttention  sources/TinyTitan/Kernels/Attention/PrefillAttention.swift:5-55, :165-258
+  GDN               sources/TinyTitan/Kernels/GDN/GDN.swift:318-396
+
+A "buffer" is a torch CUDA tensor or an integer device address; `*_offset` arguments are byte
+offsets as in the reference. `command_buffer` is the CUDA stream handle (default: torch's
+current stream); every encode* call enqueues and returns.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+from . import _lib as L
+
+
+def _addr(buf, offset: int = 0) -> int:
+    if buf is None:
+        return 0
+    base = buf.data_ptr() if hasattr(buf, "data_ptr") else int(buf)
+    return base + int(offset)
+
+
+def _stream(command_buffer) -> int:
+    if command_buffer is not None:
+        return int(getattr(command_buffer, "cuda_stream", command_buffer))
+    import torch
+    return int(torch.cuda.current_stream().cuda_stream)
+
+
+def _dtype_of(buf, default=L.TT_F16) -> int:
+    dt = getattr(buf, "dtype", None)
+    if dt is None:
+        return default
+    import torch
+    if dt == torch.bfloat16:
+        return L.TT_BF16
+    return L.TT_F16
+
+
+class Context:
+    """One per device and per runner: device scratch allocated once, not re-entrant."""
+
+    def __init__(self, device: int = 0, workspace_bytes: int = 0, max_sessions: int = 0):
+        err = C.c_int(0)
+        opts = L.ContextOptions(workspace_bytes, max_sessions, 0)
+        self.handle = L.lib().tt_context_create(device, C.byref(opts), C.byref(err))
+        if not self.handle:
+            L.check(err.value or L.TT_ERR_CUDA)
+            raise L.TinyTitanError(L.TT_ERR_CUDA, "tt_context_create failed")
+        self.device = device
+
+    def close(self):
+        if getattr(self, "handle", None):
+            L.lib().tt_context_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def check(self, status: int):
+        L.check(status, self.handle)
+
+    def poll_status(self, command_buffer=None) -> int:
+        flags = C.c_uint32(0)
+        self.check(L.lib().tt_ctx_poll_status(self.handle, _stream(command_buffer), C.byref(flags)))
+        return flags.value
+
+    def synchronize(self, command_buffer=None):
+        self.check(L.lib().tt_stream_synchronize(self.handle, _stream(command_buffer)))
+
+    def profile_enable(self, enabled: bool = True):
+        self.check(L.lib().tt_ctx_profile_enable(self.handle, int(enabled)))
+
+    def profile_collect(self):
+        """Durations (ms) of the split-KV pass-1 launches recorded since the last collect."""
+        buf = (C.c_float * 256)()
+        n = C.c_uint32(0)
+        self.check(L.lib().tt_ctx_profile_collect(self.handle, buf, 256, C.byref(n)))
+        return [buf[i] for i in range(n.value)]
+
+    @property
+    def launch_count(self) -> int:
+        return int(L.lib().tt_ctx_launch_count(self.handle))
+
+
+@dataclass
+class KVFormat:
+    bits: int = 16
+    stride: int = 0
+    value_bytes: int = 0
+    group_size: int = 64
+
+
+@dataclass
+class AttentionSplitGeometry:
+    effective_length: int
+    num_chunks: int
+    chunk_length: int
+    partial_threadgroups: int
+    use_swa_grouped_partial: bool
+
+
+@dataclass
+class DecodeSession:
+    """One row group of a batched / few-token decode step (tt_attn_session)."""
+    q: object
+    out: object
+    k: object
+    v: object
+    seq_len: int
+    q_rows: int = 1
+    kv_start: int = 0
+    q_offset: int = 0
+    out_offset: int = 0
+    k_offset: int = 0
+    v_offset: int = 0
+
+
+class Attention:
+    max_q_heads = 96
+    max_head_dim = 512
+
+    def __init__(self, context: Context):
+        self.context = context
+
+    @staticmethod
+    def default_scale(head_dim: int) -> float:
+        return 1.0 / math.sqrt(head_dim)
+
+    @staticmethod
+    def split_geometry(num_q_heads: int, num_kv_heads: int, seq_len: int, kv_start: int,
+                       prefer_gqa_swa: bool) -> AttentionSplitGeometry:
+        g = L.SplitGeometry()
+        L.lib().tt_attn_reference_split_geometry(num_q_heads, num_kv_heads, seq_len, kv_start,
+                                                 int(prefer_gqa_swa), C.byref(g))
+        return AttentionSplitGeometry(g.effective_length, g.num_chunks, g.chunk_length,
+                                      g.partial_threadgroups, bool(g.use_swa_grouped_partial))
+
+    def _encode(self, command_buffer, q, q_offset, k, k_offset, v, v_offset, out, out_offset, head_dim,
+                num_q_heads, num_kv_heads, seq_len, kv_start, scale, kv_format, keep_mask, ring_capacity):
+        if num_kv_heads <= 0 or num_q_heads % num_kv_heads != 0:
+            raise L.InvalidArgument(L.TT_ERR_INVALID_ARG, "numQHeads must be a multiple of numKVHeads for GQA")
+        if head_dim > self.max_head_dim:
+            raise L.InvalidArgument(L.TT_ERR_INVALID_ARG, "head_dim must be <= 512")
+        fmt = None
+        if kv_format is not None:
+            fmt = L.KVFormat(kv_format.bits, kv_format.stride, kv_format.value_bytes, kv_format.group_size)
+        sc = self.default_scale(head_dim) if scale is None else scale
+        self.context.check(L.lib().tt_attn_decode(
+            self.context.handle, _stream(command_buffer), _addr(q, q_offset), _addr(k, k_offset),
+            _addr(v, v_offset), _addr(out, out_offset), head_dim, num_q_heads, num_kv_heads, seq_len, kv_start,
+            sc, C.byref(fmt) if fmt is not None else None, _addr(keep_mask), ring_capacity))
+
+    def encode_full(self, q, k, v, out, head_dim, num_q_heads, num_kv_heads, seq_len, scale=None,
+                    kv_format: Optional[KVFormat] = None, keep_mask=None, command_buffer=None, q_offset=0,
+                    k_offset=0, v_offset=0, out_offset=0):
+        """Attention.encodeFull (Attention.swift:270-307)."""
+        if seq_len <= 0:
+            raise L.InvalidArgument(L.TT_ERR_INVALID_ARG, "full attention requires at least one KV position")
+        self._encode(command_buffer, q, q_offset, k, k_offset, v, v_offset, out, out_offset, head_dim, num_q_heads,
+                     num_kv_heads, seq_len, 0, scale, kv_format, keep_mask, 0)
+
+    def encode_swa(self, q, k, v, out, head_dim, num_q_heads, num_kv_heads, seq_len, window, scale=None,
+                   ring_capacity=0, kv_format: Optional[KVFormat] = None, command_buffer=None, q_offset=0,
+                   k_offset=0, v_offset=0, out_offset=0):
+        """Attention.encodeSWA (Attention.swift:233-266): keys [max(0, seqLen-window), seqLen)."""
+        kv_start = seq_len - window if seq_len > window else 0
+        self._encode(command_buffer, q, q_offset, k, k_offset, v, v_offset, out, out_offset, head_dim, num_q_heads,
+                     num_kv_heads, seq_len, kv_start, scale, kv_format, None, ring_capacity)
+
+    def encode_batched(self, sessions: Sequence[DecodeSession], head_dim, num_q_heads, num_kv_heads,
+                       kv_token_stride_elements=None, q_row_stride_elements=None, out_row_stride_elements=None,
+                       scale=None, io_dtype=None, command_buffer=None):
+        """All rows of a batched decode / verify step in one launch pair (tt_attn_decode_batched)."""
+        n = len(sessions)
+        arr = (L.AttnSession * max(n, 1))()
+        for i, s in enumerate(sessions):
+            arr[i] = L.AttnSession(_addr(s.q, s.q_offset), _addr(s.out, s.out_offset), _addr(s.k, s.k_offset),
+                                   _addr(s.v, s.v_offset), s.seq_len, s.q_rows, s.kv_start, 0)
+        tight_q = num_q_heads * head_dim
+        p = L.AttnBatchParams(head_dim, num_q_heads, num_kv_heads,
+                              kv_token_stride_elements or num_kv_heads * head_dim,
+                              q_row_stride_elements or tight_q, out_row_stride_elements or tight_q,
+                              self.default_scale(head_dim) if scale is None else scale,
+                              io_dtype if io_dtype is not None else (_dtype_of(sessions[0].q) if n else L.TT_F16))
+        self.context.check(L.lib().tt_attn_decode_batched(self.context.handle, _stream(command_buffer), arr, n,
+                                                          C.byref(p)))
+
+    def encode_partial(self, q, k, v, head_dim, num_q_heads, num_kv_heads, seq_len, kv_start, m_out, d_out, o_out,
+                       scale=None, kv_token_stride_elements=0, io_dtype=None, command_buffer=None):
+        """Pass 1 alone: one unnormalised (m, d, o) triple per q head for this device's keys."""
+        self.context.check(L.lib().tt_attn_decode_partial(
+            self.context.handle, _stream(command_buffer), _addr(q), _addr(k), _addr(v), head_dim, num_q_heads,
+            num_kv_heads, seq_len, kv_start, self.default_scale(head_dim) if scale is None else scale,
+            kv_token_stride_elements, io_dtype if io_dtype is not None else _dtype_of(q), _addr(m_out), _addr(d_out),
+            _addr(o_out)))
+
+    def encode_combine(self, m, d, o, n_parts, num_q_heads, head_dim, out, io_dtype=None, command_buffer=None):
+        """Pass 2 alone: log-sum-exp merge of n_parts triples."""
+        self.context.check(L.lib().tt_attn_combine(
+            self.context.handle, _stream(command_buffer), _addr(m), _addr(d), _addr(o), n_parts, num_q_heads,
+            head_dim, _addr(out), io_dtype if io_dtype is not None else _dtype_of(out)))
+
+
+@dataclass
+class PrefillAttentionParams:
+    """PrefillAttentionParams (PrefillAttention.swift:5-55), same fields and defaults."""
+    start_position: int
+    query_count: int
+    head_dim: int
+    num_q_heads: int
+    num_kv_heads: int
+    kv_valid_count: int
+    sliding_window: int
+    kv_token_stride_elements: int
+    q_token_stride_elements: int
+    o_token_stride_elements: int
+    scale: float
+    kv_bits: int = 16
+    kv_token_stride_bytes: int = 0
+    kv_value_bytes: int = 0
+    kv_group_size: int = 64
+
+    def to_c(self) -> "L.PrefillParams":
+        return L.PrefillParams(self.start_position, self.query_count, self.head_dim, self.num_q_heads,
+                               self.num_kv_heads, self.kv_valid_count, self.sliding_window,
+                               self.kv_token_stride_elements, self.q_token_stride_elements,
+                               self.o_token_stride_elements, self.scale, self.kv_bits,
+                               self.kv_token_stride_bytes, self.kv_value_bytes, self.kv_group_size)
+
+
+class PrefillAttention:
+    def __init__(self, context: Context):
+        self.context = context
+
+    def encode_causal(self, q, k, v, out, params: PrefillAttentionParams, kv_ring_capacity=0, io_dtype=None,
+                      command_buffer=None, q_offset=0, k_offset=0, v_offset=0, out_offset=0):
+        """PrefillAttention.encodeCausal (PrefillAttention.swift:165-258)."""
+        cp = params.to_c()
+        self.context.check(L.lib().tt_attn_prefill_causal(
+            self.context.handle, _stream(command_buffer), _addr(q, q_offset), _addr(k, k_offset),
+            _addr(v, v_offset), _addr(out, out_offset), C.byref(cp), kv_ring_capacity,
+            io_dtype if io_dtype is not None else _dtype_of(q)))
+
+    @staticmethod
+    def selected_path(q, k, v, out, params: PrefillAttentionParams, kv_ring_capacity=0, q_offset=0, k_offset=0,
+                      v_offset=0, out_offset=0) -> str:
+        cp = params.to_c()
+        path = L.lib().tt_attn_prefill_path(_addr(q, q_offset), _addr(k, k_offset), _addr(v, v_offset),
+                                            _addr(out, out_offset), C.byref(cp), kv_ring_capacity)
+        return "tcgen05" if path == 1 else "generic"
+
+
+@dataclass(frozen=True)
+class LinearAttentionConfig:
+    """LinearAttentionConfig (sources/TinyTitanCore/Format/ModelTypes+Configs.swift:147-188)."""
+    num_k_heads: int
+    num_v_heads: int
+    key_head_dim: int
+    value_head_dim: int
+    conv_kernel_size: int = 4
+
+    @property
+    def qkv_dim(self) -> int:
+        return 2 * self.num_k_heads * self.key_head_dim + self.num_v_heads * self.value_head_dim
+
+    @property
+    def value_dim(self) -> int:
+        return self.num_v_heads * self.value_head_dim
+
+
+@dataclass
+class GDNSession:
+    conv_out: object
+    a_proj: object
+    b_proj: object
+    state: object
+    y: object
+    checkpoint_state: object = None
+    conv_out_offset: int = 0
+    a_proj_offset: int = 0
+    b_proj_offset: int = 0
+    state_offset: int = 0
+    y_offset: int = 0
+    checkpoint_state_offset: int = 0
+
+
+class GDN:
+    def __init__(self, context: Context, config: LinearAttentionConfig, a_log_preexp=False, v_tiled=False,
+                 readout_scale=1.0, gates_f32=False):
+        self.context = context
+        self.config = config
+        flags = (L.TT_GDN_A_LOG_PREEXP if a_log_preexp else 0) | (L.TT_GDN_V_TILED if v_tiled else 0) | \
+                (L.TT_GDN_GATES_F32 if gates_f32 else 0)
+        self.shape = L.GdnShape(config.num_k_heads, config.num_v_heads, config.key_head_dim,
+                                config.value_head_dim, flags, readout_scale)
+
+    def encode_delta_step_decode(self, conv_out, a_proj, b_proj, a_log, dt_bias, state, y, command_buffer=None,
+                                 conv_out_offset=0, a_proj_offset=0, b_proj_offset=0, a_log_offset=0,
+                                 dt_bias_offset=0, state_offset=0, y_offset=0):
+        """GDN.encodeDeltaStepDecode (GDN.swift:318-347)."""
+        self.encode_delta_step_prefill(conv_out, a_proj, b_proj, a_log, dt_bias, state, y, rows=1,
+                                       command_buffer=command_buffer, conv_out_offset=conv_out_offset,
+                                       a_proj_offset=a_proj_offset, b_proj_offset=b_proj_offset,
+                                       a_log_offset=a_log_offset, dt_bias_offset=dt_bias_offset,
+                                       state_offset=state_offset, y_offset=y_offset)
+
+    def encode_delta_step_prefill(self, conv_out, a_proj, b_proj, a_log, dt_bias, state, y, rows,
+                                  checkpoint_state=None, row_stride=None, command_buffer=None, conv_out_offset=0,
+                                  a_proj_offset=0, b_proj_offset=0, a_log_offset=0, dt_bias_offset=0,
+                                  state_offset=0, checkpoint_state_offset=0, y_offset=0):
+        """GDN.encodeDeltaStepPrefill (GDN.swift:351-396): rows applied in order, exact arithmetic."""
+        self.context.check(L.lib().tt_gdn_step(
+            self.context.handle, _stream(command_buffer), _addr(conv_out, conv_out_offset),
+            _addr(a_proj, a_proj_offset), _addr(b_proj, b_proj_offset), _addr(a_log, a_log_offset),
+            _addr(dt_bias, dt_bias_offset), _addr(state, state_offset), _addr(y, y_offset), C.byref(self.shape),
+            rows, row_stride or self.config.qkv_dim,
+            _addr(checkpoint_state, checkpoint_state_offset) if checkpoint_state is not None else None))
+
+    def encode_delta_step_batched(self, sessions: Sequence[GDNSession], a_log, dt_bias, rows=1, row_stride=None,
+                                  command_buffer=None):
+        n = len(sessions)
+        arr = (L.GdnSession * max(n, 1))()
+        for i, s in enumerate(sessions):
+            arr[i] = L.GdnSession(_addr(s.conv_out, s.conv_out_offset), _addr(s.a_proj, s.a_proj_offset),
+                                  _addr(s.b_proj, s.b_proj_offset), _addr(s.state, s.state_offset),
+                                  _addr(s.y, s.y_offset),
+                                  _addr(s.checkpoint_state, s.checkpoint_state_offset)
+                                  if s.checkpoint_state is not None else None)
+        self.context.check(L.lib().tt_gdn_step_batched(
+            self.context.handle, _stream(command_buffer), arr, n, _addr(a_log), _addr(dt_bias),
+            C.byref(self.shape), rows, row_stride or self.config.qkv_dim))
+
+    def encode_delta_scan_chunked(self, conv_out, a_proj, b_proj, a_log, dt_bias, state, y, rows, chunk=64,
+                                  row_stride=None, command_buffer=None, state_offset=0):
+        """Chunk-parallel form of encode_delta_step_prefill (tt_gdn_scan_chunked)."""
+        self.context.check(L.lib().tt_gdn_scan_chunked(
+            self.context.handle, _stream(command_buffer), _addr(conv_out), _addr(a_proj), _addr(b_proj),
+            _addr(a_log), _addr(dt_bias), _addr(state, state_offset), _addr(y), C.byref(self.shape), rows,
+            row_stride or self.config.qkv_dim, chunk))
