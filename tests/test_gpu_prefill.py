@@ -122,19 +122,20 @@ def test_tcgen05_large_scores_rescale_path():
     assert np.abs(got - want).max() <= TOL
 
 
-def test_tcgen05_equals_generic_at_config3_size_and_is_byte_stable():
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_tcgen05_equals_generic_at_config3_size_and_is_byte_stable(dtype):
     # Full config-3 shape (8192 tokens, 16/2/256, bf16). The oracle would need minutes; the two
     # independent CUDA kernels must agree, and the tcgen05 kernel must be run-to-run byte-stable
     # (PrefillAttentionTests.swift:144-180).
     import os
     g = torch.Generator(device="cuda"); g.manual_seed(3)
     T, hq, hkv, hd = 8192, 16, 2, 256
-    q = torch.randn(T, hq * hd, device="cuda", generator=g).bfloat16()
-    k = torch.randn(T, hkv * hd, device="cuda", generator=g).bfloat16()
-    v = torch.randn(T, hkv * hd, device="cuda", generator=g).bfloat16()
+    q = torch.randn(T, hq * hd, device="cuda", generator=g).to(dtype)
+    k = torch.randn(T, hkv * hd, device="cuda", generator=g).to(dtype)
+    v = torch.randn(T, hkv * hd, device="cuda", generator=g).to(dtype)
     p = tt.PrefillAttentionParams(0, T, hd, hq, hkv, T, 0, hkv * hd, hq * hd, hq * hd, 0.0625)
     pa = tt.PrefillAttention(context())
-    o1 = torch.empty(T, hq * hd, device="cuda", dtype=torch.bfloat16); o2 = torch.empty_like(o1); o3 = torch.empty_like(o1)
+    o1 = torch.empty(T, hq * hd, device="cuda", dtype=dtype); o2 = torch.empty_like(o1); o3 = torch.empty_like(o1)
     pa.encode_causal(q, k, v, o1, p)
     pa.encode_causal(q, k, v, o2, p)
     os.environ["TT_PREFILL_FORCE_GENERIC"] = "1"
@@ -145,8 +146,14 @@ def test_tcgen05_equals_generic_at_config3_size_and_is_byte_stable():
     torch.cuda.synchronize()
     assert context().poll_status() == 0
     assert torch.equal(o1, o2)
-    diff = (o1.float() - o3.float()).abs()
-    assert torch.all(diff <= 2e-3 + o3.float().abs() * 2.0 ** -7)
+    # bf16 I/O: both outputs carry one bf16 rounding (2^-8 relative each) and the tensor-core
+    # kernel's probabilities are bf16 (2^-9 relative on |v| <= ~4.5); fp16 I/O is held to 2e-3.
+    if dtype == torch.bfloat16:
+        excess = (o1.float() - o3.float()).abs() - (1e-2 + o3.float().abs() * 2.0 ** -7)
+    else:
+        excess = (o1.float() - o3.float()).abs() - (2e-3 + o3.float().abs() * 2.0 ** -10)
+    assert excess.max().item() <= 0, excess.max().item()
+    assert (o1.float() - o3.float()).abs().mean().item() < 5e-4
     # causality as a property: the first 128 rows only depend on the first 128 keys
     k2 = k.clone(); k2[128:] = 0
     o4 = torch.empty_like(o1)

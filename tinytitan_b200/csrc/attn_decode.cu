@@ -110,6 +110,19 @@ __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
+template <typename T>
+__device__ __forceinline__ float sum2(uint32_t packed);
+template <>
+__device__ __forceinline__ float sum2<__half>(uint32_t packed) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&packed));
+    return f.x + f.y;
+}
+template <>
+__device__ __forceinline__ float sum2<__nv_bfloat16>(uint32_t packed) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&packed));
+    return f.x + f.y;
+}
+
 template <int HD>
 struct DecodeSmem {
     static constexpr int kPitch = HD + 8;                          // elements per staged row
@@ -269,15 +282,16 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
             alpha[h] = exp2f(m_run[h] - m_use);
             m_run[h] = m_new;
-            float rs = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) { sv[h][j] = exp2f(sv[h][j] - m_use); rs += sv[h][j]; }
-            l_run[h] = l_run[h] * alpha[h] + rs;
+            for (int j = 0; j < 4; ++j) sv[h][j] = exp2f(sv[h][j] - m_use);
         }
         pa[0] = pack2<T>(sv[0][0], sv[0][1]);
         pa[1] = pack2<T>(sv[1][0], sv[1][1]);
         pa[2] = pack2<T>(sv[0][2], sv[0][3]);
         pa[3] = pack2<T>(sv[1][2], sv[1][3]);
+        // row sums from the ROUNDED weights the MMA consumes: O / l stays a convex combination
+        l_run[0] = l_run[0] * alpha[0] + sum2<T>(pa[0]) + sum2<T>(pa[2]);
+        l_run[1] = l_run[1] * alpha[1] + sum2<T>(pa[1]) + sum2<T>(pa[3]);
 
         if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll

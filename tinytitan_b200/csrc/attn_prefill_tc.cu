@@ -144,6 +144,19 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __device__ __forceinline__ bool warp_all(bool ok) { return __all_sync(0xffffffffu, ok) != 0; }
 
 template <typename T>
+__device__ __forceinline__ float sum2(uint32_t packed);
+template <>
+__device__ __forceinline__ float sum2<__half>(uint32_t packed) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&packed));
+    return f.x + f.y;
+}
+template <>
+__device__ __forceinline__ float sum2<__nv_bfloat16>(uint32_t packed) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&packed));
+    return f.x + f.y;
+}
+
+template <typename T>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi);
 template <>
 __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
@@ -358,8 +371,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             for (int c = 0; c < 32; ++c) {
                 const float p0 = fast_exp2(__uint_as_float(raw[c >> 4][(2 * c) & 31]) - m_use);
                 const float p1 = fast_exp2(__uint_as_float(raw[c >> 4][(2 * c + 1) & 31]) - m_use);
-                rs += p0 + p1;
                 pk[c] = pack2<T>(p0, p1);
+                rs += sum2<T>(pk[c]);   // the row sum uses the ROUNDED weights the MMA will see, so
+                                        // O / l stays an exact convex combination of V rows   // P takes V's type: A and B of one tcgen05.mma must share a format
             }
             l_run += rs;
             tmem_st32(s_addr, pk);          // P (16-bit pairs) over the first 32 columns of S[j%2]
@@ -436,6 +450,7 @@ bool make_map(CUtensorMap *map, const void *base, uint32_t io_dtype, uint64_t wi
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// A and B always share one format: an fp16 A against a bf16 B is an illegal instruction on sm_100a.
 uint32_t make_idesc(uint32_t io_dtype, uint32_t n, bool b_mn_major) {
     const uint32_t fmt = io_dtype == TT_BF16 ? 1u : 0u;
     uint32_t d = 0;

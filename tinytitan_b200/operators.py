@@ -197,6 +197,29 @@ class Attention:
         self.context.check(L.lib().tt_attn_decode_batched(self.context.handle, _stream(command_buffer), arr, n,
                                                           C.byref(p)))
 
+    def prepare_batch(self, sessions: Sequence[DecodeSession], head_dim, num_q_heads, num_kv_heads,
+                      kv_token_stride_elements=None, q_row_stride_elements=None, out_row_stride_elements=None,
+                      scale=None, io_dtype=None):
+        """The argument block of encode_batched built once, for a step that is replayed with the
+        same buffers (the reference re-encodes the same bindings every token as well)."""
+        n = len(sessions)
+        arr = (L.AttnSession * max(n, 1))()
+        for i, s in enumerate(sessions):
+            arr[i] = L.AttnSession(_addr(s.q, s.q_offset), _addr(s.out, s.out_offset), _addr(s.k, s.k_offset),
+                                   _addr(s.v, s.v_offset), s.seq_len, s.q_rows, s.kv_start, 0)
+        tight_q = num_q_heads * head_dim
+        p = L.AttnBatchParams(head_dim, num_q_heads, num_kv_heads,
+                              kv_token_stride_elements or num_kv_heads * head_dim,
+                              q_row_stride_elements or tight_q, out_row_stride_elements or tight_q,
+                              self.default_scale(head_dim) if scale is None else scale,
+                              io_dtype if io_dtype is not None else (_dtype_of(sessions[0].q) if n else L.TT_F16))
+        return (arr, n, p)
+
+    def encode_prepared(self, batch, command_buffer=None):
+        arr, n, p = batch
+        self.context.check(L.lib().tt_attn_decode_batched(self.context.handle, _stream(command_buffer), arr, n,
+                                                          C.byref(p)))
+
     def encode_partial(self, q, k, v, head_dim, num_q_heads, num_kv_heads, seq_len, kv_start, m_out, d_out, o_out,
                        scale=None, kv_token_stride_elements=0, io_dtype=None, command_buffer=None):
         """Pass 1 alone: one unnormalised (m, d, o) triple per q head for this device's keys."""
@@ -338,6 +361,23 @@ class GDN:
                                   _addr(s.y, s.y_offset),
                                   _addr(s.checkpoint_state, s.checkpoint_state_offset)
                                   if s.checkpoint_state is not None else None)
+        self.context.check(L.lib().tt_gdn_step_batched(
+            self.context.handle, _stream(command_buffer), arr, n, _addr(a_log), _addr(dt_bias),
+            C.byref(self.shape), rows, row_stride or self.config.qkv_dim))
+
+    def prepare_batch(self, sessions: Sequence[GDNSession]):
+        n = len(sessions)
+        arr = (L.GdnSession * max(n, 1))()
+        for i, s in enumerate(sessions):
+            arr[i] = L.GdnSession(_addr(s.conv_out, s.conv_out_offset), _addr(s.a_proj, s.a_proj_offset),
+                                  _addr(s.b_proj, s.b_proj_offset), _addr(s.state, s.state_offset),
+                                  _addr(s.y, s.y_offset),
+                                  _addr(s.checkpoint_state, s.checkpoint_state_offset)
+                                  if s.checkpoint_state is not None else None)
+        return (arr, n)
+
+    def encode_prepared(self, batch, a_log, dt_bias, rows=1, row_stride=None, command_buffer=None):
+        arr, n = batch
         self.context.check(L.lib().tt_gdn_step_batched(
             self.context.handle, _stream(command_buffer), arr, n, _addr(a_log), _addr(dt_bias),
             C.byref(self.shape), rows, row_stride or self.config.qkv_dim))
