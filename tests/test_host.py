@@ -58,12 +58,12 @@ def test_split_planner():
     rng = np.random.default_rng(0)
     keys = [int(x) for x in rng.integers(1024, 32769, size=32)]
     rc, per, items = _plan(keys, [1] * 32)
-    assert rc == 0 and per % 64 == 0 and 256 <= per <= 16384
+    assert rc == 0 and per % 64 == 0 and 64 <= per <= 16384
     assert items == sum(-(-k // per) for k in keys) * 2
-    assert 4 * 148 <= items <= 16 * 148            # enough items to balance, not so many that merges dominate
+    assert 8 * 148 <= items <= 20 * 148            # enough items to balance, not so many that merges dominate
     # a single short session is not split below the minimum item length
     rc, per, items = _plan([4096], [1], hq=8)
-    assert rc == 0 and per == 256 and items == 16 * 2
+    assert rc == 0 and per == 64 and items == 64 * 2
     # an empty range still yields one (empty) item per kv head
     rc, per, items = _plan([0], [1])
     assert rc == 0 and items == 2

@@ -129,22 +129,40 @@ struct DecodeSmem {
     static constexpr int kRowBytes = kPitch * 2;
     static constexpr int kTileBytes = kKeysPerBlock * kRowBytes;   // one K (or V) block
     static constexpr int kStageBytes = 2 * kTileBytes;             // K block + V block
-    static constexpr int kWarpBytes = kStages * kStageBytes;
-    static constexpr int kQBytes = 16 * kRowBytes;
-    static constexpr int total(int warps) { return kQBytes + warps * kWarpBytes + 64 * warps; }
+    static constexpr int kRingBytes = kStages * kStageBytes;
+    static constexpr int kXchgBytes = 2 * 2 * 32 * 9 * 4;          // [buffer][warp][lane][8 scores + flag]
+    static constexpr int kTotal = kRingBytes + kXchgBytes + 64;
 };
 
+__device__ __forceinline__ void pair_barrier() { asm volatile("bar.sync 1, 64;" ::: "memory"); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // ---------------------------------------------------------------------------------------
-// Pass 1. grid = items, block = NW warps.
+// Pass 1. grid = items, block = one warp pair (64 threads), 4 CTAs per SM.
+//
+// Both warps of the pair stream the SAME 16-key blocks through one 3-stage ring; warp h owns
+// head-dim half h: it holds that half of the 16-row Q tile in registers, computes the partial
+// scores over its half, the two halves are added through a double-buffered exchange in shared
+// memory (one named barrier per block), both warps run the identical softmax update, and each
+// accumulates P.V for its own half of the output columns. The pair therefore ends with one
+// consistent (m, l) and the two halves of O -- no merge.
 // ---------------------------------------------------------------------------------------
-template <int HD, int NW, typename T>
-__global__ void __launch_bounds__(NW * 32, (HD >= 256 ? (NW <= 2 ? 2 : 1) : 2))
+template <int HD, typename T>
+__global__ void __launch_bounds__(64, 4)
 attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
                            const TTDecodeSession *__restrict__ sessions, float *__restrict__ part_o,
                            float *__restrict__ part_m, float *__restrict__ part_l,
                            uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t kv_stride_bytes,
                            uint32_t q_row_stride, float scale_log2, uint32_t *__restrict__ status) {
     using S = DecodeSmem<HD>;
+    constexpr int HH = HD / 2;          // head-dim half per warp
+    constexpr int KS = HH / 16;         // k-steps of the partial Q.K^T
+    constexpr int NT = HH / 8;          // n-tiles of this warp's half of O
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -152,139 +170,161 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
     const TTDecodeSession ses = sessions[item.session];
     const uint32_t group = n_q_heads / n_kv_heads;
 
-    unsigned char *q_smem = smem;
-    unsigned char *ring = smem + S::kQBytes + warp * S::kWarpBytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::kQBytes + NW * S::kWarpBytes) + warp * kStages;
+    unsigned char *ring = smem;
+    float *xchg = reinterpret_cast<float *>(smem + S::kRingBytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::kRingBytes + S::kXchgBytes);
 
-    // ---- stage the 16-row Q tile (zero rows past row_count) ----
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+
+    // ---- this warp's half of the Q tile, straight into mma A fragments ----
+    uint32_t qf[KS][4];
     {
-        constexpr int kVecPerRow = HD / 8;  // 16-byte vectors per row
-        for (int idx = threadIdx.x; idx < 16 * kVecPerRow; idx += NW * 32) {
-            const int r = idx / kVecPerRow, c = idx % kVecPerRow;
-            uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (r < (int)item.row_count) {
-                const uint32_t packed = item.row_begin + r;     // w * group + g
-                const uint32_t w = packed / group, g = packed % group;
-                const T *src = reinterpret_cast<const T *>(ses.q) + (size_t)w * q_row_stride +
-                               (size_t)(item.kv_head * group + g) * HD;
-                val = reinterpret_cast<const uint4 *>(src)[c];
-            }
-            *reinterpret_cast<uint4 *>(q_smem + r * S::kRowBytes + c * 16) = val;
+        const uint32_t r0 = lane >> 2, r1 = r0 + 8;
+        const T *q0 = nullptr, *q1 = nullptr;
+        if (r0 < item.row_count) {
+            const uint32_t packed = item.row_begin + r0;
+            q0 = reinterpret_cast<const T *>(ses.q) + (size_t)(packed / group) * q_row_stride +
+                 (size_t)(item.kv_head * group + packed % group) * HD + warp * HH + (lane & 3) * 2;
+        }
+        if (r1 < item.row_count) {
+            const uint32_t packed = item.row_begin + r1;
+            q1 = reinterpret_cast<const T *>(ses.q) + (size_t)(packed / group) * q_row_stride +
+                 (size_t)(item.kv_head * group + packed % group) * HD + warp * HH + (lane & 3) * 2;
+        }
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qf[ks][0] = q0 ? *reinterpret_cast<const uint32_t *>(q0 + ks * 16) : 0u;
+            qf[ks][1] = q1 ? *reinterpret_cast<const uint32_t *>(q1 + ks * 16) : 0u;
+            qf[ks][2] = q0 ? *reinterpret_cast<const uint32_t *>(q0 + ks * 16 + 8) : 0u;
+            qf[ks][3] = q1 ? *reinterpret_cast<const uint32_t *>(q1 + ks * 16 + 8) : 0u;
         }
     }
-    if (lane == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    __syncthreads();
 
-    // ---- this warp's 16-key blocks: warp, warp+NW, ... ----
     const uint32_t n_keys = item.key_end - item.key_begin;
     const uint32_t n_blocks = (n_keys + kKeysPerBlock - 1) / kKeysPerBlock;
-    const uint32_t my_blocks = n_blocks > (uint32_t)warp ? (n_blocks - warp + NW - 1) / NW : 0u;
-
     const unsigned char *kbase = reinterpret_cast<const unsigned char *>(ses.k) + (size_t)item.kv_head * HD * 2;
     const unsigned char *vbase = reinterpret_cast<const unsigned char *>(ses.v) + (size_t)item.kv_head * HD * 2;
 
+    auto block_valid = [&](uint32_t i) {
+        return min((uint32_t)kKeysPerBlock, n_keys - i * kKeysPerBlock);
+    };
+    // thread 0 announces the bytes of block i; ordered before the copies by a barrier
+    auto announce = [&](uint32_t i) {
+        mbar_expect_tx(&bars[i % kStages], block_valid(i) * 2u * (uint32_t)(HD * 2));
+    };
+    // warp 0 fetches the K rows of block i, warp 1 the V rows (lanes 0..15, one row each)
     auto issue = [&](uint32_t i) {
-        // block i of this warp -> stage i % kStages; lanes 0-15 fetch K rows, 16-31 V rows.
-        const uint32_t blk = warp + i * NW;
-        const uint32_t key0 = item.key_begin + blk * kKeysPerBlock;
-        const uint32_t valid = min((uint32_t)kKeysPerBlock, item.key_end - key0);
-        unsigned char *stage = ring + (i % kStages) * S::kStageBytes;
-        uint64_t *bar = &bars[i % kStages];
-        if (lane == 0) mbar_expect_tx(bar, valid * 2u * (uint32_t)(HD * 2));
-        __syncwarp();
-        const uint32_t r = lane & 15;
-        const bool is_v = lane >= 16;
-        unsigned char *dst = stage + (is_v ? S::kTileBytes : 0) + r * S::kRowBytes;
-        if (r < valid) {
-            uint32_t p = key0 + r;
-            if (ses.ring_capacity) p %= ses.ring_capacity;
-            const unsigned char *src = (is_v ? vbase : kbase) + (size_t)p * kv_stride_bytes;
-            bulk_copy_g2s(dst, src, HD * 2, bar);
-        } else if (is_v) {
-            // a V row that is never fetched must still be finite: it meets p == 0 in P.V
-            uint4 z = make_uint4(0u, 0u, 0u, 0u);
-            for (int c = 0; c < HD / 8; ++c) reinterpret_cast<uint4 *>(dst)[c] = z;
+        if (lane < kKeysPerBlock) {
+            const uint32_t valid = block_valid(i);
+            unsigned char *dst = ring + (i % kStages) * S::kStageBytes + warp * S::kTileBytes + lane * S::kRowBytes;
+            if ((uint32_t)lane < valid) {
+                uint32_t p = item.key_begin + i * kKeysPerBlock + lane;
+                if (ses.ring_capacity) p %= ses.ring_capacity;
+                bulk_copy_g2s(dst, (warp ? vbase : kbase) + (size_t)p * kv_stride_bytes, HD * 2, &bars[i % kStages]);
+            } else if (warp == 1) {
+                // a V row that is never fetched must still be finite: it meets p == 0 in P.V
+                const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                for (int c = 0; c < HD / 8; ++c) reinterpret_cast<uint4 *>(dst)[c] = z;
+            }
         }
     };
 
-    // per-thread softmax state for rows (lane/4) and (lane/4 + 8)
     float m_run[2] = {-INFINITY, -INFINITY};
     float l_run[2] = {0.f, 0.f};
-    float acc[HD / 8][4];
+    float acc[NT][4];
 #pragma unroll
-    for (int n = 0; n < HD / 8; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
+    for (int n = 0; n < NT; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
 
-    // visible-key limit of the two rows this thread owns
+    // visible-key limit of the two rows this thread owns; rows past row_count are never
+    // written, so they take the tile's smallest limit and need no masking of their own
+    const uint32_t w_first = item.row_begin / group;
+    const uint32_t limit_min = ses.seq_len - (ses.q_rows - 1 - w_first);
     uint32_t limit[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const uint32_t r = (lane >> 2) + 8 * h;
-        if (r < item.row_count) {
-            const uint32_t w = (item.row_begin + r) / group;
-            limit[h] = ses.seq_len - (ses.q_rows - 1 - w);
-        } else {
-            limit[h] = 0;
-        }
+        limit[h] = r < item.row_count ? ses.seq_len - (ses.q_rows - 1 - (item.row_begin + r) / group) : limit_min;
     }
 
-    bool timed_out = false;
-    const uint32_t prologue = min(my_blocks, (uint32_t)(kStages - 1));
+    const uint32_t prologue = min(n_blocks, (uint32_t)(kStages - 1));
+    if (threadIdx.x == 0)
+        for (uint32_t i = 0; i < prologue; ++i) announce(i);
+    __syncthreads();
     for (uint32_t i = 0; i < prologue; ++i) issue(i);
 
-    const uint32_t q_addr = smem_u32(q_smem) + (lane & 15) * S::kRowBytes + (lane >> 4) * 16;
+    bool timed_out = false;
+    const uint32_t k_off = ((lane & 7) + ((lane >> 4) << 3)) * S::kRowBytes + ((lane >> 3) & 1) * 16 + warp * HH * 2;
+    const uint32_t v_off = S::kTileBytes + ((lane & 7) + ((lane >> 3) & 1) * 8) * S::kRowBytes + (lane >> 4) * 16 +
+                           warp * HH * 2;
 
-    for (uint32_t i = 0; i < my_blocks; ++i) {
-        if (i + kStages - 1 < my_blocks) issue(i + kStages - 1);
-        if (!mbar_wait(&bars[i % kStages], (i / kStages) & 1)) { timed_out = true; break; }
+    for (uint32_t i = 0; i < n_blocks; ++i) {
+        const uint32_t nxt = i + kStages - 1;
+        if (threadIdx.x == 0 && nxt < n_blocks) announce(nxt);
+        const bool got = __all_sync(0xffffffffu, mbar_wait(&bars[i % kStages], (i / kStages) & 1)) != 0;
 
-        const unsigned char *stage = ring + (i % kStages) * S::kStageBytes;
-        const uint32_t k_addr = smem_u32(stage) + ((lane & 7) + ((lane >> 4) << 3)) * S::kRowBytes +
-                                ((lane >> 3) & 1) * 16;
-        const uint32_t v_addr = smem_u32(stage) + S::kTileBytes +
-                                ((lane & 7) + ((lane >> 3) & 1) * 8) * S::kRowBytes + (lane >> 4) * 16;
-
-        // ---- S = Q K^T for 16 rows x 16 keys ----
+        const uint32_t stage = smem_u32(ring + (i % kStages) * S::kStageBytes);
+        // ---- partial S over this warp's head-dim half: two independent chains per n-tile ----
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+        float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-            uint32_t a[4], b[4];
-            ldmatrix_x4(a, q_addr + ks * 32);
-            ldmatrix_x4(b, k_addr + ks * 32);
-            mma_16816<T>(s0, a, b[0], b[1]);
-            mma_16816<T>(s1, a, b[2], b[3]);
+        for (int ks = 0; ks < KS; ks += 2) {
+            uint32_t b[4], c[4];
+            ldmatrix_x4(b, stage + k_off + ks * 32);
+            ldmatrix_x4(c, stage + k_off + (ks + 1) * 32);
+            mma_16816<T>(s0, qf[ks], b[0], b[1]);
+            mma_16816<T>(s1, qf[ks], b[2], b[3]);
+            mma_16816<T>(t0, qf[ks + 1], c[0], c[1]);
+            mma_16816<T>(t1, qf[ks + 1], c[2], c[3]);
         }
-
-        // ---- mask, online softmax ----
-        const uint32_t blk = warp + i * NW;
-        const uint32_t key0 = item.key_begin + blk * kKeysPerBlock + (lane & 3) * 2;
+        float *mine = xchg + (((i & 1) * 2 + warp) * 32 + lane) * 9;
+        const float *theirs = xchg + (((i & 1) * 2 + (warp ^ 1)) * 32 + lane) * 9;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { mine[j] = s0[j] + t0[j]; mine[4 + j] = s1[j] + t1[j]; }
+        mine[8] = got ? 1.f : 0.f;
+        pair_barrier();
+        if (!(got && theirs[8] != 0.f)) { timed_out = true; break; }   // same decision in both warps
         float sv[2][4];  // [row half][key: n0c0 n0c1 n1c0 n1c1]
-        sv[0][0] = s0[0]; sv[0][1] = s0[1]; sv[0][2] = s1[0]; sv[0][3] = s1[1];
-        sv[1][0] = s0[2]; sv[1][1] = s0[3]; sv[1][2] = s1[2]; sv[1][3] = s1[3];
-        uint32_t pa[4];
+        sv[0][0] = mine[0] + theirs[0]; sv[0][1] = mine[1] + theirs[1];
+        sv[1][0] = mine[2] + theirs[2]; sv[1][1] = mine[3] + theirs[3];
+        sv[0][2] = mine[4] + theirs[4]; sv[0][3] = mine[5] + theirs[5];
+        sv[1][2] = mine[6] + theirs[6]; sv[1][3] = mine[7] + theirs[7];
+
+        // every lane of the pair is past block i-1 now: its stage may be refilled
+        if (nxt < n_blocks) issue(nxt);
+
+        // ---- mask + online softmax (identical in both warps) ----
+        const uint32_t blk_key0 = item.key_begin + i * kKeysPerBlock;
+        const bool plain = (blk_key0 + kKeysPerBlock <= limit_min) && (blk_key0 + kKeysPerBlock <= item.key_end) &&
+                           (ses.keep == nullptr);
         float alpha[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             float mx = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint32_t key = key0 + (j >> 1) * 8 + (j & 1);
-                bool ok = key < limit[h] && key < item.key_end;
-                if (ok && ses.keep != nullptr) ok = ses.keep[key] != 0;
-                sv[h][j] = ok ? sv[h][j] * scale_log2 : -INFINITY;
-                mx = fmaxf(mx, sv[h][j]);
+                float s = sv[h][j] * scale_log2;
+                if (!plain) {
+                    const uint32_t key = blk_key0 + (lane & 3) * 2 + (j >> 1) * 8 + (j & 1);
+                    bool ok = key < limit[h] && key < item.key_end;
+                    if (ok && ses.keep != nullptr) ok = ses.keep[key] != 0;
+                    s = ok ? s : -INFINITY;
+                }
+                sv[h][j] = s;
+                mx = fmaxf(mx, s);
             }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const float m_new = fmaxf(m_run[h], mx);
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            alpha[h] = exp2f(m_run[h] - m_use);
+            alpha[h] = fast_exp2(m_run[h] - m_use);
             m_run[h] = m_new;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) sv[h][j] = exp2f(sv[h][j] - m_use);
+            for (int j = 0; j < 4; ++j) sv[h][j] = fast_exp2(sv[h][j] - m_use);
         }
+        uint32_t pa[4];
         pa[0] = pack2<T>(sv[0][0], sv[0][1]);
         pa[1] = pack2<T>(sv[1][0], sv[1][1]);
         pa[2] = pack2<T>(sv[0][2], sv[0][3]);
@@ -295,81 +335,46 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
 
         if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-            for (int n = 0; n < HD / 8; ++n) {
+            for (int n = 0; n < NT; ++n) {
                 acc[n][0] *= alpha[0]; acc[n][1] *= alpha[0];
                 acc[n][2] *= alpha[1]; acc[n][3] *= alpha[1];
             }
         }
 
-        // ---- O += P V ----
+        // ---- O(own half) += P V ----
 #pragma unroll
-        for (int np = 0; np < HD / 16; ++np) {
+        for (int np = 0; np < NT / 2; ++np) {
             uint32_t b[4];
-            ldmatrix_x4_trans(b, v_addr + np * 32);
+            ldmatrix_x4_trans(b, stage + v_off + np * 32);
             mma_16816<T>(acc[2 * np], pa, b[0], b[1]);
             mma_16816<T>(acc[2 * np + 1], pa, b[2], b[3]);
         }
-        __syncwarp();  // every lane is done with this stage before it is refilled
     }
 
     if (timed_out && lane == 0) atomicOr(status, TT_DEV_WAIT_TIMEOUT);
 
-    // quad-reduce the row sums
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
     }
 
-    // ---- merge the warps' states through shared memory (the ring is idle now) ----
-    __syncthreads();
-    float *mo = reinterpret_cast<float *>(ring);              // [16][HD] of this warp
-    float *mm = mo + 16 * HD;                                 // [16] m, [16] l
-#pragma unroll
-    for (int n = 0; n < HD / 8; ++n) {
-        const int col = n * 8 + (lane & 3) * 2;
-        const int r0 = lane >> 2, r1 = r0 + 8;
-        *reinterpret_cast<float2 *>(mo + r0 * HD + col) = make_float2(acc[n][0], acc[n][1]);
-        *reinterpret_cast<float2 *>(mo + r1 * HD + col) = make_float2(acc[n][2], acc[n][3]);
-    }
-    if ((lane & 3) == 0) {
-        mm[(lane >> 2)] = m_run[0];          mm[16 + (lane >> 2)] = l_run[0];
-        mm[(lane >> 2) + 8] = m_run[1];      mm[16 + (lane >> 2) + 8] = l_run[1];
-    }
-    __syncthreads();
-
+    // ---- write the partial: this warp's half of O, and (warp 0) m and l ----
     const uint32_t rows_total = ses.q_rows * n_q_heads;
-    for (int r = warp; r < (int)item.row_count; r += NW) {
-        float mw[NW], m_all = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < NW; ++w) {
-            const float *wm = reinterpret_cast<const float *>(smem + S::kQBytes + w * S::kWarpBytes) + 16 * HD;
-            mw[w] = wm[r];
-            m_all = fmaxf(m_all, mw[w]);
-        }
-        float wgt[NW], l_all = 0.f;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-            const float *wm = reinterpret_cast<const float *>(smem + S::kQBytes + w * S::kWarpBytes) + 16 * HD;
-            wgt[w] = (m_all == -INFINITY) ? 0.f : exp2f(mw[w] - m_all);
-            l_all += wm[16 + r] * wgt[w];
-        }
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t r = (lane >> 2) + 8 * h;
+        if (r >= item.row_count) continue;
         const uint32_t packed = item.row_begin + r;
-        const uint32_t wq = packed / group, g = packed % group;
-        const uint32_t rho = wq * n_q_heads + item.kv_head * group + g;
+        const uint32_t rho = (packed / group) * n_q_heads + item.kv_head * group + packed % group;
         const size_t prow = (size_t)ses.partial_base + (size_t)item.part_index * rows_total + rho;
-        for (int c = lane; c < HD; c += 32) {
-            float o = 0.f;
+        float *dst = part_o + prow * HD + warp * HH + (lane & 3) * 2;
 #pragma unroll
-            for (int w = 0; w < NW; ++w) {
-                const float *wo = reinterpret_cast<const float *>(smem + S::kQBytes + w * S::kWarpBytes);
-                o += wo[r * HD + c] * wgt[w];
-            }
-            part_o[prow * HD + c] = o;
-        }
-        if (lane == 0) {
-            part_m[prow] = m_all * kLn2;   // natural-log domain, the reference's partial format
-            part_l[prow] = l_all;
+        for (int n = 0; n < NT; ++n)
+            *reinterpret_cast<float2 *>(dst + n * 8) = make_float2(acc[n][2 * h], acc[n][2 * h + 1]);
+        if (warp == 0 && (lane & 3) == 0) {
+            part_m[prow] = m_run[h] * kLn2;   // natural-log domain, the reference's partial format
+            part_l[prow] = l_run[h];
         }
     }
 }
@@ -379,37 +384,64 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
 // mode 0: normalised output in the I/O dtype; mode 1: merged unnormalised (m, d, o) triple.
 // ---------------------------------------------------------------------------------------
 template <typename T>
-__global__ void attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions,
-                                           const float *__restrict__ part_o,
-                                           const float *__restrict__ part_m,
-                                           const float *__restrict__ part_l, uint32_t n_q_heads,
-                                           uint32_t head_dim, uint32_t out_row_stride, int mode,
-                                           float *__restrict__ m_out, float *__restrict__ d_out,
-                                           float *__restrict__ o_out) {
+__global__ void __launch_bounds__(64)
+attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions, const float *__restrict__ part_o,
+                           const float *__restrict__ part_m, const float *__restrict__ part_l,
+                           uint32_t n_q_heads, uint32_t head_dim, uint32_t out_row_stride, int mode,
+                           float *__restrict__ m_out, float *__restrict__ d_out, float *__restrict__ o_out) {
+    __shared__ float red[4];
     const TTDecodeSession ses = sessions[blockIdx.x];
     const uint32_t rows_total = ses.q_rows * n_q_heads;
     const uint32_t rho = blockIdx.y;
     if (rho >= rows_total) return;
     const uint32_t n_parts = ses.n_parts;
     const size_t base = (size_t)ses.partial_base + rho;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
+    // global maximum and denominator: the parts are read in parallel, not one after another
     float mg = -INFINITY;
-    for (uint32_t c = 0; c < n_parts; ++c) mg = fmaxf(mg, part_m[base + (size_t)c * rows_total]);
+    for (uint32_t c = threadIdx.x; c < n_parts; c += blockDim.x) mg = fmaxf(mg, part_m[base + (size_t)c * rows_total]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
+    if (lane == 0) red[warp] = mg;
+    __syncthreads();
+    mg = fmaxf(red[0], red[1]);
     float D = 0.f;
     if (mg != -INFINITY)
-        for (uint32_t c = 0; c < n_parts; ++c) {
+        for (uint32_t c = threadIdx.x; c < n_parts; c += blockDim.x) {
             const size_t pr = base + (size_t)c * rows_total;
             D += part_l[pr] * __expf(part_m[pr] - mg);
         }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) D += __shfl_xor_sync(0xffffffffu, D, o);
+    if (lane == 0) red[2 + warp] = D;
+    __syncthreads();
+    D = red[2] + red[3];
+
     const uint32_t w = rho / n_q_heads, h = rho % n_q_heads;
     for (uint32_t col = threadIdx.x * 4; col < head_dim; col += blockDim.x * 4) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         if (mg != -INFINITY) {
-            for (uint32_t c = 0; c < n_parts; ++c) {
+            uint32_t c = 0;
+            for (; c + 4 <= n_parts; c += 4) {   // four independent loads in flight
+                float e[4]; float4 o[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const size_t pr = base + (size_t)(c + u) * rows_total;
+                    e[u] = part_m[pr];
+                    o[u] = *reinterpret_cast<const float4 *>(part_o + pr * head_dim + col);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float wgt = __expf(e[u] - mg);
+                    acc.x += o[u].x * wgt; acc.y += o[u].y * wgt; acc.z += o[u].z * wgt; acc.w += o[u].w * wgt;
+                }
+            }
+            for (; c < n_parts; ++c) {
                 const size_t pr = base + (size_t)c * rows_total;
-                const float e = __expf(part_m[pr] - mg);
+                const float wgt = __expf(part_m[pr] - mg);
                 const float4 o = *reinterpret_cast<const float4 *>(part_o + pr * head_dim + col);
-                acc.x += o.x * e; acc.y += o.y * e; acc.z += o.z * e; acc.w += o.w * e;
+                acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
             }
         }
         if (mode == 0) {
@@ -452,17 +484,17 @@ __global__ void attn_combine_parts_kernel(const float *__restrict__ m, const flo
     }
 }
 
-template <int HD, int NW, typename T>
+template <int HD, typename T>
 cudaError_t launch_partial(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
                            const TTDecodeSession *sessions, float *part_o, float *part_m,
                            float *part_l, const tt_attn_batch_params *p, uint32_t *status) {
-    auto kernel = attn_decode_partial_kernel<HD, NW, T>;
-    const int smem = DecodeSmem<HD>::total(NW);
+    auto kernel = attn_decode_partial_kernel<HD, T>;
+    const int smem = DecodeSmem<HD>::kTotal;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    kernel<<<n_items, NW * 32, smem, stream>>>(items, sessions, part_o, part_m, part_l, p->n_q_heads,
-                                               p->n_kv_heads, p->kv_token_stride_elements * 2u,
-                                               p->q_row_stride_elements, p->scale * kLog2e, status);
+    kernel<<<n_items, 64, smem, stream>>>(items, sessions, part_o, part_m, part_l, p->n_q_heads,
+                                          p->n_kv_heads, p->kv_token_stride_elements * 2u,
+                                          p->q_row_stride_elements, p->scale * kLog2e, status);
     return cudaGetLastError();
 }
 
@@ -471,9 +503,9 @@ cudaError_t launch_partial_hd(cudaStream_t stream, uint32_t n_items, const TTDec
                               const TTDecodeSession *sessions, float *part_o, float *part_m,
                               float *part_l, const tt_attn_batch_params *p, uint32_t *status) {
     switch (p->head_dim) {
-        case 64: return launch_partial<64, 4, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status);
-        case 128: return launch_partial<128, 4, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status);
-        case 256: return launch_partial<256, 2, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status);
+        case 64: return launch_partial<64, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status);
+        case 128: return launch_partial<128, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status);
+        case 256: return launch_partial<256, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -501,11 +533,12 @@ TT_API int tt_attn_plan_splits(const uint32_t *keys_per_session, const uint32_t 
         key_rows += (uint64_t)keys_per_session[i] * n_kv_heads * tiles;
         max_rows += (uint64_t)qr * n_q_heads;
     }
-    // Aim at ~8 items per SM so that the hardware scheduler can balance ragged sessions, but
-    // keep an item long enough (>= 256 keys) to amortise its pipeline fill and its merge.
-    uint64_t target = key_rows / ((uint64_t)sm_count * 8u);
+    // Four 64-thread CTAs are resident per SM; ~12 items per SM give the hardware scheduler three
+    // waves to even out ragged sessions, while an item stays long enough (>= 64 keys, i.e. four
+    // pipeline blocks) to amortise its pipeline fill, which the co-resident CTAs overlap anyway.
+    uint64_t target = key_rows / ((uint64_t)sm_count * 12u);
     uint32_t keys = (uint32_t)((target + 63) / 64 * 64);
-    if (keys < 256) keys = 256;
+    if (keys < 64) keys = 64;
     if (keys > 16384) keys = 16384;
     for (;;) {
         uint64_t items = 0, prows = 0;
@@ -652,7 +685,7 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     ctx->launches++;
 
     const dim3 grid(n_sessions, max_rows);
-    const uint32_t threads = p->head_dim / 4;
+    const uint32_t threads = 64;
     if (p->io_dtype == TT_F16)
         attn_decode_combine_kernel<__half><<<grid, threads, 0, stream>>>(
             ctx->sessions, part_o, part_m, part_l, p->n_q_heads, p->head_dim, p->out_row_stride_elements, mode,
