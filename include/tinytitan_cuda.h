@@ -151,6 +151,22 @@ int tt_attn_combine(tt_context *ctx, tt_stream stream, const float *m, const flo
                     const float *o, uint32_t n_parts, uint32_t n_q_heads, uint32_t head_dim,
                     void *out, uint32_t io_dtype);
 
+/* No counterpart in the reference. One query row against one session's fp16 cache
+ * ([kv_start, seq_len), tight K/V rows), computed exactly like tt_attn_decode, for
+ * callers that must not allocate device memory -- code running where cudaMalloc is off
+ * limits (inside another component's latency-critical or capture-restricted section, or
+ * after the host has handed out its whole memory budget). It needs no context and calls no
+ * allocator: the split-KV scratch is a fixed 8 MiB array inside the library image, present
+ * on every GPU that loads the library until the process exits. Shapes whose scratch would
+ * not fit (more than 4096 work items, or partial triples beyond the array) are refused with
+ * TT_ERR_UNSUPPORTED_SHAPE; head_dim must be 64, 128 or 256 and the buffers 16-byte aligned.
+ * The first call on a device looks the array's device address up; make that call outside
+ * stream capture. All calls on a device share the array: calls that overlap on the GPU race,
+ * so keep them ordered (one stream, or events). Runs on the current device. */
+int tt_attn_decode_noalloc(tt_stream stream, const void *q, const void *k, const void *v, void *out,
+                           uint32_t head_dim, uint32_t n_q_heads, uint32_t n_kv_heads,
+                           uint32_t seq_len, uint32_t kv_start, float scale);
+
 /* Split geometry of the reference, kept for callers and tests that pin it
  * (Attention.splitGeometry, Attention.swift:196-227). This library's own split
  * is chosen per call from the byte count; any partition of the key range is

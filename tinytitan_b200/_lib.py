@@ -115,6 +115,7 @@ SIGNATURES = {
     "tt_attn_decode_partial": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.c_float, _u32,
                                          _u32, _vp, _vp, _vp]),
     "tt_attn_combine": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _u32]),
+    "tt_attn_decode_noalloc": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.c_float]),
     "tt_attn_reference_split_geometry": (None, [_u32, _u32, _u32, _u32, C.c_int, C.POINTER(SplitGeometry)]),
     "tt_attn_plan_splits": (C.c_int, [C.POINTER(_u32), C.POINTER(_u32), _u32, _u32, _u32, _u32, _u32, C.c_size_t,
                                       C.POINTER(_u32), C.POINTER(_u32)]),

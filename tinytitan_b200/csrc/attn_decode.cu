@@ -792,3 +792,130 @@ TT_API int tt_attn_combine(tt_context *ctx, tt_stream stream, const float *m, co
     ctx->launches++;
     return TT_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Single-query decode attention that allocates nothing.
+//
+// Some callers cannot allocate device memory: a plugin that runs inside another process's
+// real-time or capture-restricted section, a host whose memory budget was handed out in full
+// before this library was loaded (the reference sizes every buffer up front against a memory
+// budget and treats a later allocation as a bug), or a thread that must not take the driver's
+// allocation lock. For them this one entry point runs the same two kernels as tt_attn_decode
+// with the split-KV scratch (session + item tables, partial triples, status word) carved out
+// of a fixed array that lives in the library image on every device that loads it.
+//
+// The array's name is only a stand-in on the host side, so the device address is looked up
+// once per device with cudaGetSymbolAddress while that device is current. That lookup happens
+// inside the first call on a device: make that first call outside any stream capture.
+// All calls on a device share the array and it keeps what the last call left behind; nothing
+// in it has to start at zero except the status word, which every call clears. Two calls that
+// overlap on the GPU (different streams, no ordering) race on the array and give wrong
+// results: order them.
+// ---------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kNoAllocScratchBytes = (size_t)8 << 20;   // 8 MiB per device, held until exit
+constexpr uint32_t kNoAllocMaxItems = 4096;
+constexpr size_t kNoAllocTableBytes = 256 + sizeof(TTDecodeSession) + sizeof(TTDecodeItem) * kNoAllocMaxItems;
+constexpr size_t kNoAllocPartialOffset = (kNoAllocTableBytes + 255) / 256 * 256;
+constexpr int kNoAllocMaxDevices = 64;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+unsigned char *g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+volatile int g_noalloc_lock = 0;
+
+// Device address of the scratch array on the current device (looked up once per device).
+cudaError_t noalloc_scratch(int device, unsigned char **out) {
+    while (__sync_lock_test_and_set(&g_noalloc_lock, 1)) {}
+    cudaError_t e = cudaSuccess;
+    if (g_noalloc_ptr[device] == nullptr) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e == cudaSuccess) g_noalloc_ptr[device] = static_cast<unsigned char *>(p);
+    }
+    *out = g_noalloc_ptr[device];
+    __sync_lock_release(&g_noalloc_lock);
+    return e;
+}
+
+}  // namespace
+
+TT_API int tt_attn_decode_noalloc(tt_stream stream, const void *q, const void *k, const void *v, void *out,
+                                  uint32_t head_dim, uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t seq_len,
+                                  uint32_t kv_start, float scale) {
+    if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return TT_ERR_INVALID_ARG;
+    if (n_kv_heads == 0 || n_q_heads == 0 || n_q_heads % n_kv_heads != 0 || n_q_heads > 96) return TT_ERR_INVALID_ARG;
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256) return TT_ERR_UNSUPPORTED_SHAPE;
+    if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) != 0) return TT_ERR_UNSUPPORTED_SHAPE;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return TT_ERR_CUDA;
+    if (device < 0 || device >= kNoAllocMaxDevices) return TT_ERR_UNSUPPORTED_SHAPE;
+    int sm_count = 0;
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return TT_ERR_CUDA;
+    unsigned char *scratch = nullptr;
+    if (noalloc_scratch(device, &scratch) != cudaSuccess || scratch == nullptr) return TT_ERR_CUDA;
+
+    if (kv_start > seq_len) kv_start = seq_len;
+    const uint32_t keys = seq_len - kv_start, one = 1;
+    uint32_t keys_per_item = 0, n_items = 0;
+    // the planner grows the items until the partial triples fit the fixed array
+    int rc = tt_attn_plan_splits(&keys, &one, 1, head_dim, n_q_heads, n_kv_heads, (uint32_t)sm_count,
+                                 kNoAllocScratchBytes - kNoAllocPartialOffset, &keys_per_item, &n_items);
+    if (rc != TT_OK) return TT_ERR_UNSUPPORTED_SHAPE;       // does not fit the 8 MiB array
+    while (n_items > kNoAllocMaxItems) {                    // keep the item table inside its region
+        keys_per_item *= 2;
+        uint32_t parts = ceil_div_u32(keys, keys_per_item);
+        if (parts == 0) parts = 1;
+        n_items = parts * n_kv_heads * ceil_div_u32(n_q_heads / n_kv_heads, 16);
+    }
+
+    struct { TTDecodeSession ses; TTDecodeItem items[kNoAllocMaxItems]; } host;   // stack, no heap
+    uint32_t parts = ceil_div_u32(keys, keys_per_item);
+    if (parts == 0) parts = 1;
+    const size_t partial_rows = (size_t)parts * n_q_heads;
+    if (partial_rows * (head_dim + 2) * sizeof(float) > kNoAllocScratchBytes - kNoAllocPartialOffset)
+        return TT_ERR_UNSUPPORTED_SHAPE;
+    host.ses.q = q; host.ses.out = out; host.ses.k = k; host.ses.v = v;
+    host.ses.seq_len = seq_len; host.ses.q_rows = 1; host.ses.kv_start = kv_start;
+    host.ses.n_parts = parts; host.ses.partial_base = 0; host.ses.ring_capacity = 0; host.ses.keep = nullptr;
+    const uint32_t group = n_q_heads / n_kv_heads;
+    uint32_t cursor = 0;
+    for (uint32_t part = 0; part < parts; ++part) {
+        const uint32_t kb = kv_start + part * keys_per_item;
+        uint32_t ke = kb + keys_per_item;
+        if (ke > seq_len) ke = seq_len;
+        if (ke < kb) ke = kb;
+        for (uint32_t kvh = 0; kvh < n_kv_heads; ++kvh)
+            for (uint32_t rb = 0; rb < group; rb += 16) {
+                if (cursor >= kNoAllocMaxItems) return TT_ERR_UNSUPPORTED_SHAPE;
+                TTDecodeItem &it = host.items[cursor++];
+                it.session = 0; it.kv_head = kvh; it.key_begin = kb; it.key_end = ke; it.part_index = part;
+                it.row_begin = rb; it.row_count = group - rb < 16 ? group - rb : 16; it.partial_base = 0;
+            }
+    }
+
+    cudaStream_t s = (cudaStream_t)stream;
+    uint32_t *status = reinterpret_cast<uint32_t *>(scratch);
+    TTDecodeSession *d_ses = reinterpret_cast<TTDecodeSession *>(scratch + 256);
+    TTDecodeItem *d_items = reinterpret_cast<TTDecodeItem *>(scratch + 256 + sizeof(TTDecodeSession));
+    float *part_o = reinterpret_cast<float *>(scratch + kNoAllocPartialOffset);
+    float *part_m = part_o + partial_rows * head_dim;
+    float *part_l = part_m + partial_rows;
+    if (cudaMemsetAsync(status, 0, sizeof(uint32_t), s) != cudaSuccess) return TT_ERR_CUDA;
+    // host.ses and host.items are contiguous on the host and in the array: one copy (the source is
+    // pageable stack memory, so the driver has staged it by the time the call returns)
+    if (cudaMemcpyAsync(d_ses, &host, sizeof(TTDecodeSession) + sizeof(TTDecodeItem) * cursor, cudaMemcpyHostToDevice, s) !=
+        cudaSuccess)
+        return TT_ERR_CUDA;
+    tt_attn_batch_params p;
+    p.head_dim = head_dim; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
+    p.kv_token_stride_elements = n_kv_heads * head_dim; p.q_row_stride_elements = n_q_heads * head_dim;
+    p.out_row_stride_elements = n_q_heads * head_dim; p.scale = scale; p.io_dtype = TT_F16;
+    if (launch_partial_hd<__half>(s, cursor, d_items, d_ses, part_o, part_m, part_l, &p, status) != cudaSuccess)
+        return TT_ERR_CUDA;
+    attn_decode_combine_kernel<__half><<<dim3(1, n_q_heads), 64, 0, s>>>(d_ses, part_o, part_m, part_l, n_q_heads,
+                                                                         head_dim, n_q_heads * head_dim, 0, nullptr,
+                                                                         nullptr, nullptr);
+    return cudaGetLastError() == cudaSuccess ? TT_OK : TT_ERR_CUDA;
+}
