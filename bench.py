@@ -352,9 +352,11 @@ def aux_measurements(w, pk):
     return aux
 
 
-# ncu dram__bytes_read.sum + dram__bytes_write.sum of attn_decode_partial_kernel per algorithmic
-# byte, from the capture summarised under profiles/ (None until a capture has been taken).
-TRAFFIC_PER_ALGORITHMIC_BYTE = None
+# ncu (dram__bytes_read.sum + dram__bytes_write.sum) of attn_decode_partial_kernel per algorithmic
+# byte, from the 8-session capture summarised in profiles/decode_partial_8sessions_ncu_full.md
+# (227.1 MB of DRAM traffic for 216.9 MB of algorithmic bytes). Traffic grows in proportion to
+# the keys processed, so a full launch is this ratio times its algorithmic bytes.
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.047
 
 
 def run_gpu_arm(args):
