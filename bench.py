@@ -55,6 +55,16 @@ def peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def config_dict(world, lens):
+    """The workload description both arms print (same string for the GPU and the CPU arm)."""
+    alg = algorithmic_bytes(lens)
+    return {"workload": "C2: Qwen3.6-35B-A3B-shaped batched decode, 32 sessions per GPU, S~U[1024,32768] "
+                        "(seeded), SDPA 16/2/256 fp16 KV + GDN step 16/32/128 fp32 state, one layer of each per step",
+            "sessions_per_gpu": len(lens), "sum_context": sum(lens),
+            "l2": "inputs larger than L2: %.2f GB of KV + 0.13 GB of GDN state streamed per step" % (alg / 1e9),
+            "parallelism": f"sessions x{world} (no collective)"}
+
+
 def algorithmic_bytes(lens):
     """Decode SDPA bytes per step: K and V rows once per KV head, plus q and out rows."""
     return sum(lens) * HKV * HD * 2 * 2 + len(lens) * HQ * HD * 2 * 2
@@ -125,8 +135,7 @@ def run_reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": res["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "C2: Qwen3.6-35B-A3B-shaped batched decode, 32 sessions S~U[1024,32768], "
-                               "SDPA 16/2/256 + GDN step 16/32/128 (CPU sample, see cpu_baseline.sample)"},
+        "config": config_dict(args.gpus, lens),
         "cpu_baseline": {"value": res["value"], "unit": UNIT, "cores": res["cores"], "kind": "port",
                          "sample": res["sample"]},
         "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -331,6 +340,28 @@ def aux_measurements(w, pk):
         del q, k, v, o
     except Exception as exc:  # reported, never hidden
         aux["prefill_c3_bf16"] = {"error": str(exc)}
+    # config 3: GDN prefill over 8192 tokens, 16/32 heads, d 128: chunk-parallel scan vs the exact sequential kernel
+    try:
+        T = 8192
+        g = torch.Generator(device="cuda"); g.manual_seed(5)
+        cfg = tt.LinearAttentionConfig(GK, GV, GD, GD)
+        qk = torch.randn(T, 2 * GK, GD, device="cuda", generator=g)
+        qk = qk / qk.norm(dim=-1, keepdim=True); qk[:, :GK] *= GD ** -0.5
+        conv = torch.cat([qk.reshape(T, -1), torch.randn(T, GV * GD, device="cuda", generator=g)], 1).half().contiguous()
+        a = (-torch.randn(T, GV, device="cuda", generator=g)).half(); b = torch.randn(T, GV, device="cuda", generator=g).half()
+        st = 0.02 * torch.randn(GV, GD, GD, device="cuda", generator=g)
+        y = torch.empty(T, GV * GD, device="cuda", dtype=torch.float16)
+        gdn = tt.GDN(w.ctx, cfg)
+        ms_scan = ev_time(lambda: gdn.encode_delta_scan_chunked(conv, a, b, w.a_log, w.dt_bias, st, y, T), 5, warm=2)
+        ms_seq = ev_time(lambda: gdn.encode_delta_step_prefill(conv, a, b, w.a_log, w.dt_bias, st, y, T), 3, warm=1)
+        scan_bytes = T * (2 * GK * GD + GV * GD) * 2 + T * GV * GD * 2 + 2 * GV * GD * GD * 4 + T * GV * 4
+        scan_flops = (T / 64) * GV * 9.44e6
+        aux["gdn_scan_c3"] = {"ms": ms_scan, "GBps_algorithmic": scan_bytes / ms_scan / 1e6,
+                              "frac_hbm": scan_bytes / ms_scan / 1e6 / pk["hbm_gbs"], "TFLOPs": scan_flops / ms_scan / 1e9,
+                              "sequential_kernel_ms": ms_seq, "tokens_per_s": T / ms_scan * 1e3}
+        del conv, y
+    except Exception as exc:
+        aux["gdn_scan_c3"] = {"error": str(exc)}
     # config 1: one session, S = 4096, 8/2/256; 32 distinct caches are rotated so HBM is really read
     try:
         s1, hq1 = 4096, 8
@@ -409,11 +440,7 @@ def run_gpu_arm(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": "C2: Qwen3.6-35B-A3B-shaped batched decode, 32 sessions per GPU, S~U[1024,32768] "
-                                   "(seeded), SDPA 16/2/256 fp16 KV + GDN step 16/32/128 fp32 state, one layer of each per step",
-                       "sessions_per_gpu": N_SESSIONS, "sum_context": sum(w.lens),
-                       "l2": "inputs larger than L2: %.2f GB of KV + 0.13 GB of GDN state streamed per step" % (alg / 1e9),
-                       "parallelism": f"sessions x{world} (no collective)"},
+            "config": config_dict(world, w.lens),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h,
                     "steps": e2e_steps, "ms_per_step": ms_e2e / e2e_steps},
             "gpu_launches": int(launches),

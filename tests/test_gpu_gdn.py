@@ -182,3 +182,85 @@ def test_rejects_bad_shapes():
     gdn = tt.GDN(context(), tt.LinearAttentionConfig(2, 4, 48, 64))
     with pytest.raises(tt.UnsupportedShape):
         gdn.encode_delta_step_decode(x, x, x, x, x, s, x)
+
+
+# ------------------------------------------------------------------ chunk-parallel scan
+def run_scan(cfg, conv, a, b, a_log, dt_bias, state, rows, **gdn_kw):
+    gdn = tt.GDN(context(), cfg, **gdn_kw)
+    f32 = gdn_kw.get("gates_f32", False)
+    conv_d = dev(conv)
+    a_d, b_d = (dev(a, torch.float32), dev(b, torch.float32)) if f32 else (dev(a), dev(b))
+    al_d = dev(a_log, torch.bfloat16) if a_log is not None else None
+    dt_d = dev(dt_bias, torch.bfloat16) if dt_bias is not None else None
+    st_d = dev(state, torch.float32)
+    y = torch.full((rows, cfg.value_dim), float("nan"), device="cuda", dtype=torch.float16)
+    gdn.encode_delta_scan_chunked(conv_d, a_d, b_d, al_d, dt_d, st_d, y, rows, row_stride=conv.shape[1])
+    torch.cuda.synchronize()
+    return host(y), host(st_d)
+
+
+@pytest.mark.parametrize("rows,hk,hv", [(64, 1, 1), (200, 2, 4), (1, 1, 2), (513, 2, 2)])
+def test_chunked_scan_matches_sequential_oracle(rows, hk, hv):
+    r = np.random.default_rng(rows + hv)
+    d = 128
+    cfg = tt.LinearAttentionConfig(hk, hv, d, d)
+    conv, a, b, a_log, dt_bias, state = make_inputs(r, rows, hk, hv, d, d, extra_stride=8)
+    want_y, want_s, _ = oracle.gdn_step_rows(conv, a, b, a_log, dt_bias, hk, hv, d, d, state)
+    got_y, got_s = run_scan(cfg, conv, a, b, a_log, dt_bias, state, rows)
+    assert np.isfinite(got_y).all()
+    assert np.abs(got_y - want_y).max() <= TOL
+    assert np.abs(got_s - want_s).max() <= 2e-3 * max(1.0, np.abs(want_s).max())
+
+
+def test_chunked_scan_against_reference_chunk_kernel():
+    # the tinytitan_delta_rule_chunk calling form (alpha, beta given), checked against the
+    # reference's own chunk kernel at chunk 64 and its token kernel (via the oracle drivers)
+    r = np.random.default_rng(31)
+    hk, hv, d, rows = 2, 4, 128, 256
+    cfg = tt.LinearAttentionConfig(hk, hv, d, d)
+    conv, _, _, _, _, state = make_inputs(r, rows, hk, hv, d, d)
+    alpha = r.uniform(0.5, 1.0, size=(rows, hv)).astype(np.float32)
+    beta = r.uniform(0.1, 0.9, size=(rows, hv)).astype(np.float32)
+    got_y, got_s = run_scan(cfg, conv, alpha, beta, None, None, state, rows, gates_f32=True)
+    q = conv[:, :hk * d]; k = conv[:, hk * d:2 * hk * d]; v = conv[:, 2 * hk * d:]
+    use_ref = oracle.ref() is not None
+    want_y, want_s = oracle.gdn_scan_heads(q, k, v, alpha, beta, hk, hv, d, d, 64, state, threads=4, use_ref=use_ref)
+    assert np.abs(got_y - want_y).max() <= TOL
+    assert np.abs(got_s - want_s).max() <= 2e-3 * max(1.0, np.abs(want_s).max())
+
+
+def test_chunked_scan_equals_sequential_kernel_at_config3_size():
+    # 8192 tokens, 16/32 heads (config 3): the oracle needs minutes, so the exact sequential
+    # CUDA kernel is the comparison; also the scan over [0,T) equals two scans over [0,T1),[T1,T)
+    g = torch.Generator(device="cuda"); g.manual_seed(17)
+    T, hk, hv, d = 8192, 16, 32, 128
+    cfg = tt.LinearAttentionConfig(hk, hv, d, d)
+    qk = torch.randn(T, 2 * hk, d, device="cuda", generator=g)
+    qk = qk / qk.norm(dim=-1, keepdim=True); qk[:, :hk] *= d ** -0.5
+    conv = torch.cat([qk.reshape(T, -1), torch.randn(T, hv * d, device="cuda", generator=g)], 1).half().contiguous()
+    a = (-torch.randn(T, hv, device="cuda", generator=g)).half(); b = torch.randn(T, hv, device="cuda", generator=g).half()
+    z = torch.zeros(hv, device="cuda", dtype=torch.bfloat16)
+    s0 = (0.02 * torch.randn(hv, d, d, device="cuda", generator=g))
+    gdn = tt.GDN(context(), cfg)
+    s_seq, s_scan, s_two = s0.clone(), s0.clone(), s0.clone()
+    y_seq = torch.empty(T, hv * d, device="cuda", dtype=torch.float16); y_scan = torch.empty_like(y_seq); y_two = torch.empty_like(y_seq)
+    gdn.encode_delta_step_prefill(conv, a, b, z, z, s_seq, y_seq, T)
+    gdn.encode_delta_scan_chunked(conv, a, b, z, z, s_scan, y_scan, T)
+    T1 = 3000   # not a multiple of the chunk: the second call starts mid-chunk of the first
+    gdn.encode_delta_scan_chunked(conv, a, b, z, z, s_two, y_two, T1)
+    gdn.encode_delta_scan_chunked(conv[T1:], a[T1:], b[T1:], z, z, s_two, y_two[T1:], T - T1)
+    torch.cuda.synchronize()
+    assert (y_scan.float() - y_seq.float()).abs().max().item() <= TOL
+    assert (s_scan - s_seq).abs().max().item() <= 2e-3 * max(1.0, s_seq.abs().max().item())
+    assert (y_two.float() - y_seq.float()).abs().max().item() <= TOL
+    assert (s_two - s_seq).abs().max().item() <= 2e-3 * max(1.0, s_seq.abs().max().item())
+
+
+def test_chunked_scan_rejects_other_shapes():
+    gdn = tt.GDN(context(), tt.LinearAttentionConfig(2, 4, 64, 64))
+    x = torch.zeros(1 << 14, device="cuda", dtype=torch.float16); s = torch.zeros(4 * 64 * 64, device="cuda")
+    with pytest.raises(tt.UnsupportedShape):
+        gdn.encode_delta_scan_chunked(x, x, x, x, x, s, x, 64)
+    gdn = tt.GDN(context(), tt.LinearAttentionConfig(2, 4, 128, 128))
+    with pytest.raises(tt.UnsupportedShape):
+        gdn.encode_delta_scan_chunked(x, x, x, x, x, torch.zeros(4 * 128 * 128, device="cuda"), x, 64, chunk=32)

@@ -1,11 +1,524 @@
-// Chunk-parallel Gated-DeltaNet prefill scan (placeholder translation unit; filled in below).
+// Chunk-parallel Gated-DeltaNet prefill scan (chunk = 64 tokens, Dk = Dv = 128).
+//
+// The recurrence of gdn_delta_step_prefill (sources/TinyTitanCore/Metal/GDN/gdn.metal:590-669)
+// evaluated chunk by chunk, following the algebra of tinytitan_delta_rule_chunk
+// (sources/TinyTitanKernelsC/gdn_chunk.c:72-195, benchmark/gdn_chunked_scan.py:70-97):
+//
+//   S_t = a_t S_{t-1} + c_t k_t^T,  c_t = b_t (v_t - a_t S_{t-1} k_t),  o_t = S_t q_t
+//
+// With A_t = prod_{i<=t} a_i inside a chunk and S_0 the state entering it, the corrections of
+// the whole chunk solve (I + L) C = diag(b) (V - diag(A) K S_0^T), L[t,s] = b_t (A_t/A_s)(k_t.k_s)
+// for s < t. Writing T = (I + L)^-1:
+//
+//   C = U - W S_0^T           U = T diag(b) V,  W = T diag(b A) K       (state independent)
+//   O = diag(A) Q S_0^T + M C     M[t,s] = (A_t/A_s)(q_t.k_s), s <= t   (state independent)
+//   S_C = A_C S_0 + (diag(A_C/A_s) C)^T K
+//
+// Decay ratios are exp(logA_t - logA_s) of cumulative log-decays (never A_t / A_s, cf.
+// gdn_chunk.c:141-147). Two kernels per segment of chunks:
+//   gdn_scan_prepare_kernel  one CTA per (chunk, value head), fully parallel: Gram matrices on
+//                            mma.sync, T by forward substitution in fp32, U (fp32), W, M (fp16)
+//   gdn_scan_state_kernel    one CTA per (32 state rows, value head), chunks in order: the fp32
+//                            state lives in mma accumulator registers for the whole segment
+// The rows of S (value dimension) are independent of one another, which is what lets the state
+// be split over CTAs with no communication.
 #include "tt_common.h"
+
+namespace {
+
+constexpr int kC = 64;          // tokens per chunk
+constexpr int kD = 128;         // Dk == Dv
+constexpr int kPitch = kD + 8;  // fp16 row pitch of [*][128] tiles (272 B: ldmatrix conflict-free)
+constexpr int kPitchC = kC + 8; // fp16 row pitch of [*][64] tiles (144 B)
+constexpr int kDvb = 32;        // state rows per CTA of the state kernel
+
+// Per (chunk, value head) record in the workspace.
+struct ChunkRecord {
+    float u[kC][kD];        // U, fp32 (enters C by a plain subtraction, so it keeps full precision)
+    __half w[kC][kD];       // W
+    __half m[kC][kC];       // M (lower triangle incl. diagonal, zeros above)
+    float decay_a[kC];      // A_t
+    float decay_w[kC];      // A_C / A_t
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+__device__ __forceinline__ void cp_async16(void *dst, const void *src, bool valid) {
+    const uint32_t n = valid ? 16u : 0u;   // src-size 0 zero-fills the destination
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// ldmatrix addressing helpers for a row-major fp16 tile with `pitch` elements per row.
+// A operand (16 rows x 16 k) at (row0, k0); B operand for two n-tiles from a [n][k] tile
+// (k contiguous) at (n0, k0); transposed variants read [k][n] tiles (n contiguous).
+__device__ __forceinline__ uint32_t addr_a(uint32_t base, int pitch, int row0, int k0, int lane) {
+    return base + ((row0 + (lane & 15)) * pitch + k0 + (lane >> 4) * 8) * 2;
+}
+__device__ __forceinline__ uint32_t addr_b(uint32_t base, int pitch, int n0, int k0, int lane) {
+    return base + ((n0 + (lane & 7) + ((lane >> 4) << 3)) * pitch + k0 + ((lane >> 3) & 1) * 8) * 2;
+}
+__device__ __forceinline__ uint32_t addr_bt(uint32_t base, int pitch, int k0, int n0, int lane) {
+    return base + ((k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * pitch + n0 + (lane >> 4) * 8) * 2;
+}
+// A operand (16 m x 16 k) read from a [k][m] tile (m contiguous) with .trans:
+// matrices: (k 0-7, m 0-7) -> a0, (k 0-7, m 8-15) -> a1, (k 8-15, m 0-7) -> a2, (k 8-15, m 8-15) -> a3
+__device__ __forceinline__ uint32_t addr_at(uint32_t base, int pitch, int k0, int m0, int lane) {
+    return base + ((k0 + (lane & 7) + (lane >> 4) * 8) * pitch + m0 + ((lane >> 3) & 1) * 8) * 2;
+}
+
+struct ScanParams {
+    const __half *conv_out;
+    const void *a;
+    const void *b;
+    const __nv_bfloat16 *a_log;
+    const __nv_bfloat16 *dt_bias;
+    float *state;
+    __half *y;
+    ChunkRecord *records;     // [chunks in segment][Hv]
+    uint32_t hk, hv, rows, row_stride, flags;
+    uint32_t token0;          // first token of the segment
+    uint32_t n_chunks;        // chunks in the segment
+    float readout_scale;
+};
+
+// ---------------------------------------------------------------------------------------
+// Phase 1: state-independent quantities of one chunk of one value head.
+// grid = (chunks in segment, Hv), block = 256.
+// ---------------------------------------------------------------------------------------
+struct PrepSmem {
+    __half k[kC][kPitch];
+    __half q[kC][kPitch];
+    __half v[kC][kPitch];
+    float l[kC][kC + 4];            // strictly lower triangle of L, then reused for T
+    __half tb_hi[kC][kPitchC], tb_lo[kC][kPitchC];   // T diag(b)      as fp16 hi + lo
+    __half ta_hi[kC][kPitchC], ta_lo[kC][kPitchC];   // T diag(b A)
+    float log_a[kC];                // cumulative log decay (inclusive)
+    float beta[kC];
+};
+
+__global__ void __launch_bounds__(256) gdn_scan_prepare_kernel(ScanParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    PrepSmem &s = *reinterpret_cast<PrepSmem *>(smem_raw);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t chunk = blockIdx.x, h = blockIdx.y;
+    const uint32_t hk = (p.flags & TT_GDN_V_TILED) ? h % p.hk : h / (p.hv / p.hk);
+    const uint32_t t0 = p.token0 + chunk * kC;
+    const uint32_t n_tok = min((uint32_t)kC, p.rows - t0);
+    ChunkRecord &rec = p.records[(size_t)chunk * p.hv + h];
+
+    // ---- K, Q, V tiles (tokens past the end are zero rows) ----
+    for (int idx = tid; idx < kC * (kD / 8); idx += 256) {
+        const int t = idx / (kD / 8), c = idx % (kD / 8);
+        const bool ok = (uint32_t)t < n_tok;
+        const __half *row = p.conv_out + (size_t)(t0 + (ok ? t : 0)) * p.row_stride;
+        cp_async16(&s.q[t][c * 8], row + (size_t)hk * kD + c * 8, ok);
+        cp_async16(&s.k[t][c * 8], row + (size_t)p.hk * kD + (size_t)hk * kD + c * 8, ok);
+        cp_async16(&s.v[t][c * 8], row + (size_t)2 * p.hk * kD + (size_t)h * kD + c * 8, ok);
+    }
+    cp_async_commit();
+
+    // ---- per-token gates: log decay and beta (padding tokens: decay 1, beta 0) ----
+    if (tid < kC) {
+        float la = 0.f, be = 0.f;
+        if ((uint32_t)tid < n_tok) {
+            const size_t gi = (size_t)(t0 + tid) * p.hv + h;
+            if (p.flags & TT_GDN_GATES_F32) {
+                la = logf(fmaxf(reinterpret_cast<const float *>(p.a)[gi], 1e-37f));
+                be = reinterpret_cast<const float *>(p.b)[gi];
+            } else {
+                const float x = __half2float(reinterpret_cast<const __half *>(p.a)[gi]) + __bfloat162float(p.dt_bias[h]);
+                const float sp = x > 20.f ? x : logf(1.f + expf(x));
+                const float al = __bfloat162float(p.a_log[h]);
+                la = (p.flags & TT_GDN_A_LOG_PREEXP) ? al * sp : -expf(al) * sp;
+                be = 1.f / (1.f + expf(-__half2float(reinterpret_cast<const __half *>(p.b)[gi])));
+            }
+        }
+        s.log_a[tid] = la;
+        s.beta[tid] = be;
+    }
+    __syncthreads();
+    if (tid == 0) {   // inclusive running sum of 64 values
+        float run = 0.f;
+        for (int t = 0; t < kC; ++t) { run += s.log_a[t]; s.log_a[t] = run; }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    if (tid < kC) {
+        rec.decay_a[tid] = expf(s.log_a[tid]);
+        rec.decay_w[tid] = expf(s.log_a[kC - 1] - s.log_a[tid]);
+    }
+
+    // ---- Gram matrices: warp w -> rows 16*(w&3), columns 32*(w>>2) of K K^T and Q K^T ----
+    {
+        const int r0 = 16 * (warp & 3), c0 = 32 * (warp >> 2);
+        float gk[4][4], gq[4][4];
+#pragma unroll
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { gk[n][j] = 0.f; gq[n][j] = 0.f; }
+        const uint32_t kb = smem_u32(&s.k[0][0]), qb = smem_u32(&s.q[0][0]);
+#pragma unroll
+        for (int ks = 0; ks < kD / 16; ++ks) {
+            uint32_t ak[4], aq[4], b0[4], b1[4];
+            ldsm_x4(ak, addr_a(kb, kPitch, r0, ks * 16, lane));
+            ldsm_x4(aq, addr_a(qb, kPitch, r0, ks * 16, lane));
+            ldsm_x4(b0, addr_b(kb, kPitch, c0, ks * 16, lane));
+            ldsm_x4(b1, addr_b(kb, kPitch, c0 + 16, ks * 16, lane));
+            mma16816(gk[0], ak, b0[0], b0[1]); mma16816(gk[1], ak, b0[2], b0[3]);
+            mma16816(gk[2], ak, b1[0], b1[1]); mma16816(gk[3], ak, b1[2], b1[3]);
+            mma16816(gq[0], aq, b0[0], b0[1]); mma16816(gq[1], aq, b0[2], b0[3]);
+            mma16816(gq[2], aq, b1[0], b1[1]); mma16816(gq[3], aq, b1[2], b1[3]);
+        }
+        // L[t][s] = b_t (A_t/A_s)(k_t.k_s) for s < t ;  M[t][s] = (A_t/A_s)(q_t.k_s) for s <= t
+#pragma unroll
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int t = r0 + (lane >> 2) + (j >> 1) * 8;
+                const int sx = c0 + n * 8 + (lane & 3) * 2 + (j & 1);
+                const float ratio = sx <= t ? expf(s.log_a[t] - s.log_a[sx]) : 0.f;
+                s.l[t][sx] = sx < t ? s.beta[t] * ratio * gk[n][j] : 0.f;
+                rec.m[t][sx] = __float2half_rn(ratio * gq[n][j]);
+            }
+    }
+    __syncthreads();
+
+    // ---- T = (I + L)^-1 by forward substitution: thread j owns column j in registers ----
+    if (tid < kC) {
+        float x[kC];
+#pragma unroll
+        for (int t = 0; t < kC; ++t) {
+            float acc = (t == tid) ? 1.f : 0.f;
+#pragma unroll
+            for (int sx = 0; sx < t; ++sx) acc = fmaf(-s.l[t][sx], x[sx], acc);   // x[sx] == 0 for sx < j
+            x[t] = acc;
+        }
+        // column j of T diag(b) and T diag(b A), split into fp16 hi + lo
+        const float bj = s.beta[tid], baj = s.beta[tid] * expf(s.log_a[tid]);
+#pragma unroll
+        for (int t = 0; t < kC; ++t) {
+            const float vb = x[t] * bj, va = x[t] * baj;
+            const __half hb = __float2half_rn(vb), ha = __float2half_rn(va);
+            s.tb_hi[t][tid] = hb; s.tb_lo[t][tid] = __float2half_rn(vb - __half2float(hb));
+            s.ta_hi[t][tid] = ha; s.ta_lo[t][tid] = __float2half_rn(va - __half2float(ha));
+        }
+    }
+    __syncthreads();
+
+    // ---- U = (T diag b) V and W = (T diag(b A)) K : warp w -> rows 16*(w&3), columns 64*(w>>2) ----
+    {
+        const int r0 = 16 * (warp & 3), c0 = 64 * (warp >> 2);
+        float u[8][4], w[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { u[n][j] = 0.f; w[n][j] = 0.f; }
+        const uint32_t vb = smem_u32(&s.v[0][0]), kb = smem_u32(&s.k[0][0]);
+        const uint32_t tbh = smem_u32(&s.tb_hi[0][0]), tbl = smem_u32(&s.tb_lo[0][0]);
+        const uint32_t tah = smem_u32(&s.ta_hi[0][0]), tal = smem_u32(&s.ta_lo[0][0]);
+#pragma unroll
+        for (int ks = 0; ks < kC / 16; ++ks) {
+            uint32_t abh[4], abl[4], aah[4], aal[4];
+            ldsm_x4(abh, addr_a(tbh, kPitchC, r0, ks * 16, lane));
+            ldsm_x4(abl, addr_a(tbl, kPitchC, r0, ks * 16, lane));
+            ldsm_x4(aah, addr_a(tah, kPitchC, r0, ks * 16, lane));
+            ldsm_x4(aal, addr_a(tal, kPitchC, r0, ks * 16, lane));
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                uint32_t bv[4], bk[4];
+                ldsm_x4_t(bv, addr_bt(vb, kPitch, ks * 16, c0 + np * 16, lane));
+                ldsm_x4_t(bk, addr_bt(kb, kPitch, ks * 16, c0 + np * 16, lane));
+                mma16816(u[2 * np], abh, bv[0], bv[1]); mma16816(u[2 * np + 1], abh, bv[2], bv[3]);
+                mma16816(u[2 * np], abl, bv[0], bv[1]); mma16816(u[2 * np + 1], abl, bv[2], bv[3]);
+                mma16816(w[2 * np], aah, bk[0], bk[1]); mma16816(w[2 * np + 1], aah, bk[2], bk[3]);
+                mma16816(w[2 * np], aal, bk[0], bk[1]); mma16816(w[2 * np + 1], aal, bk[2], bk[3]);
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const int col = c0 + n * 8 + (lane & 3) * 2;
+            const int ra = r0 + (lane >> 2), rb = ra + 8;
+            *reinterpret_cast<float2 *>(&rec.u[ra][col]) = make_float2(u[n][0], u[n][1]);
+            *reinterpret_cast<float2 *>(&rec.u[rb][col]) = make_float2(u[n][2], u[n][3]);
+            *reinterpret_cast<uint32_t *>(&rec.w[ra][col]) = pack_h2(w[n][0], w[n][1]);
+            *reinterpret_cast<uint32_t *>(&rec.w[rb][col]) = pack_h2(w[n][2], w[n][3]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Phase 2: the chunks of a segment in order, for 32 state rows of one value head.
+// grid = (Dv / 32, Hv), block = 128 (4 warps). Warp w owns token rows 16w..16w+15 of the
+// per-chunk products and state columns 32w..32w+31 (all 32 state rows) as accumulators.
+// ---------------------------------------------------------------------------------------
+struct StateStage {
+    __half q[kC][kPitch];
+    __half k[kC][kPitch];
+    __half w[kC][kPitch];
+    __half m[kC][kPitchC];
+    float u[kC][kDvb + 4];
+    float decay_a[kC];
+    float decay_w[kC];
+};
+struct StateSmem {
+    StateStage stage[2];
+    __half s16[kDvb][kPitch];      // the state slice as an fp16 MMA operand
+    __half c16[kC][kDvb + 8];      // corrections C (tokens x state rows)
+    __half cw16[kC][kDvb + 8];     // diag(A_C/A_t) C, the operand of the state update
+};
+
+__device__ __forceinline__ void state_load_chunk(StateStage &st, const ScanParams &p, uint32_t chunk, uint32_t h,
+                                                 uint32_t hk, uint32_t dv0, int tid) {
+    const uint32_t t0 = p.token0 + chunk * kC;
+    const uint32_t n_tok = min((uint32_t)kC, p.rows - t0);
+    const ChunkRecord &rec = p.records[(size_t)chunk * p.hv + h];
+    for (int idx = tid; idx < kC * (kD / 8); idx += 128) {
+        const int t = idx / (kD / 8), c = idx % (kD / 8);
+        const bool ok = (uint32_t)t < n_tok;
+        const __half *row = p.conv_out + (size_t)(t0 + (ok ? t : 0)) * p.row_stride;
+        cp_async16(&st.q[t][c * 8], row + (size_t)hk * kD + c * 8, ok);
+        cp_async16(&st.k[t][c * 8], row + (size_t)p.hk * kD + (size_t)hk * kD + c * 8, ok);
+        cp_async16(&st.w[t][c * 8], &rec.w[t][c * 8], true);
+    }
+    for (int idx = tid; idx < kC * (kC / 8); idx += 128) {
+        const int t = idx / (kC / 8), c = idx % (kC / 8);
+        cp_async16(&st.m[t][c * 8], &rec.m[t][c * 8], true);
+    }
+    for (int idx = tid; idx < kC * (kDvb / 4); idx += 128) {
+        const int t = idx / (kDvb / 4), c = idx % (kDvb / 4);
+        cp_async16(&st.u[t][c * 4], &rec.u[t][dv0 + c * 4], true);
+    }
+    if (tid < 32) {
+        const int t = (tid & 15) * 4;
+        cp_async16(tid < 16 ? &st.decay_a[t] : &st.decay_w[t], tid < 16 ? &rec.decay_a[t] : &rec.decay_w[t], true);
+    }
+    cp_async_commit();
+}
+
+__global__ void __launch_bounds__(128) gdn_scan_state_kernel(ScanParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    StateSmem &s = *reinterpret_cast<StateSmem *>(smem_raw);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t h = blockIdx.y, dv0 = blockIdx.x * kDvb;
+    const uint32_t hk = (p.flags & TT_GDN_V_TILED) ? h % p.hk : h / (p.hv / p.hk);
+    float *state = p.state + ((size_t)h * kD + dv0) * kD;
+
+    // state slice [32 rows][128] -> accumulator fragments: m-tile mt (rows 16mt..), n-tile nt of
+    // this warp's 32 columns; c0,c1 -> row g, c2,c3 -> row g+8, columns 2*(lane&3)
+    float sacc[2][4][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int col = warp * 32 + nt * 8 + (lane & 3) * 2;
+            const float2 lo = *reinterpret_cast<const float2 *>(state + (size_t)(mt * 16 + (lane >> 2)) * kD + col);
+            const float2 hi = *reinterpret_cast<const float2 *>(state + (size_t)(mt * 16 + (lane >> 2) + 8) * kD + col);
+            sacc[mt][nt][0] = lo.x; sacc[mt][nt][1] = lo.y; sacc[mt][nt][2] = hi.x; sacc[mt][nt][3] = hi.y;
+        }
+
+    state_load_chunk(s.stage[0], p, 0, h, hk, dv0, tid);
+
+    for (uint32_t c = 0; c < p.n_chunks; ++c) {
+        StateStage &st = s.stage[c & 1];
+        // publish the current state as an fp16 operand
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const int col = warp * 32 + nt * 8 + (lane & 3) * 2;
+                *reinterpret_cast<uint32_t *>(&s.s16[mt * 16 + (lane >> 2)][col]) = pack_h2(sacc[mt][nt][0], sacc[mt][nt][1]);
+                *reinterpret_cast<uint32_t *>(&s.s16[mt * 16 + (lane >> 2) + 8][col]) = pack_h2(sacc[mt][nt][2], sacc[mt][nt][3]);
+            }
+        cp_async_wait<0>();
+        __syncthreads();   // (1) stage c and s16 are complete; everyone is done with chunk c-1
+        // only now may the other stage be refilled: chunk c-1's M C and state update read it
+        if (c + 1 < p.n_chunks) state_load_chunk(s.stage[(c + 1) & 1], p, c + 1, h, hk, dv0, tid);
+
+        // ---- P = W S^T and R = Q S^T for this warp's 16 tokens x 32 state rows ----
+        const int r0 = warp * 16;
+        float pw[4][4], rq[4][4];
+#pragma unroll
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { pw[n][j] = 0.f; rq[n][j] = 0.f; }
+        const uint32_t wb = smem_u32(&st.w[0][0]), qb = smem_u32(&st.q[0][0]), sb = smem_u32(&s.s16[0][0]);
+#pragma unroll
+        for (int ks = 0; ks < kD / 16; ++ks) {
+            uint32_t aw[4], aq[4], b0[4], b1[4];
+            ldsm_x4(aw, addr_a(wb, kPitch, r0, ks * 16, lane));
+            ldsm_x4(aq, addr_a(qb, kPitch, r0, ks * 16, lane));
+            ldsm_x4(b0, addr_b(sb, kPitch, 0, ks * 16, lane));
+            ldsm_x4(b1, addr_b(sb, kPitch, 16, ks * 16, lane));
+            mma16816(pw[0], aw, b0[0], b0[1]); mma16816(pw[1], aw, b0[2], b0[3]);
+            mma16816(pw[2], aw, b1[0], b1[1]); mma16816(pw[3], aw, b1[2], b1[3]);
+            mma16816(rq[0], aq, b0[0], b0[1]); mma16816(rq[1], aq, b0[2], b0[3]);
+            mma16816(rq[2], aq, b1[0], b1[1]); mma16816(rq[3], aq, b1[2], b1[3]);
+        }
+        // C = U - P (fp32), stored as fp16 twice: plain (for M C) and scaled by A_C/A_t (for the state)
+#pragma unroll
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int t = r0 + (lane >> 2) + hh * 8;
+                const int col = n * 8 + (lane & 3) * 2;
+                const float2 u = *reinterpret_cast<const float2 *>(&st.u[t][col]);
+                const float c0v = u.x - pw[n][2 * hh], c1v = u.y - pw[n][2 * hh + 1];
+                const float wgt = st.decay_w[t];
+                *reinterpret_cast<uint32_t *>(&s.c16[t][col]) = pack_h2(c0v, c1v);
+                *reinterpret_cast<uint32_t *>(&s.cw16[t][col]) = pack_h2(c0v * wgt, c1v * wgt);
+            }
+        __syncthreads();   // (2) C of all 64 tokens is visible
+
+        // ---- O = diag(A) R + M C ; write y ----
+        {
+            float o[4][4];
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const float a = st.decay_a[r0 + (lane >> 2) + hh * 8];
+                    o[n][2 * hh] = rq[n][2 * hh] * a; o[n][2 * hh + 1] = rq[n][2 * hh + 1] * a;
+                }
+            const uint32_t mb = smem_u32(&st.m[0][0]), cb = smem_u32(&s.c16[0][0]);
+#pragma unroll
+            for (int ks = 0; ks < kC / 16; ++ks) {
+                uint32_t am[4], b0[4], b1[4];
+                ldsm_x4(am, addr_a(mb, kPitchC, r0, ks * 16, lane));
+                ldsm_x4_t(b0, addr_bt(cb, kDvb + 8, ks * 16, 0, lane));
+                ldsm_x4_t(b1, addr_bt(cb, kDvb + 8, ks * 16, 16, lane));
+                mma16816(o[0], am, b0[0], b0[1]); mma16816(o[1], am, b0[2], b0[3]);
+                mma16816(o[2], am, b1[0], b1[1]); mma16816(o[3], am, b1[2], b1[3]);
+            }
+            const uint32_t t0 = p.token0 + c * kC;
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const uint32_t t = t0 + r0 + (lane >> 2) + hh * 8;
+                    if (t < p.rows) {
+                        __half *dst = p.y + (size_t)t * p.hv * kD + (size_t)h * kD + dv0 + n * 8 + (lane & 3) * 2;
+                        *reinterpret_cast<uint32_t *>(dst) =
+                            pack_h2(o[n][2 * hh] * p.readout_scale, o[n][2 * hh + 1] * p.readout_scale);
+                    }
+                }
+        }
+
+        // ---- S = A_C S + (diag(A_C/A_t) C)^T K : 32 rows x this warp's 32 columns ----
+        {
+            const float a_c = st.decay_a[kC - 1];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) sacc[mt][nt][j] *= a_c;
+            const uint32_t cwb = smem_u32(&s.cw16[0][0]), kb = smem_u32(&st.k[0][0]);
+#pragma unroll
+            for (int ks = 0; ks < kC / 16; ++ks) {
+                uint32_t a0[4], a1[4], b0[4], b1[4];
+                ldsm_x4_t(a0, addr_at(cwb, kDvb + 8, ks * 16, 0, lane));
+                ldsm_x4_t(a1, addr_at(cwb, kDvb + 8, ks * 16, 16, lane));
+                ldsm_x4_t(b0, addr_bt(kb, kPitch, ks * 16, warp * 32, lane));
+                ldsm_x4_t(b1, addr_bt(kb, kPitch, ks * 16, warp * 32 + 16, lane));
+                mma16816(sacc[0][0], a0, b0[0], b0[1]); mma16816(sacc[0][1], a0, b0[2], b0[3]);
+                mma16816(sacc[0][2], a0, b1[0], b1[1]); mma16816(sacc[0][3], a0, b1[2], b1[3]);
+                mma16816(sacc[1][0], a1, b0[0], b0[1]); mma16816(sacc[1][1], a1, b0[2], b0[3]);
+                mma16816(sacc[1][2], a1, b1[0], b1[1]); mma16816(sacc[1][3], a1, b1[2], b1[3]);
+            }
+        }
+        // the next iteration's barrier (1) orders these reads of stage c / c16 / cw16 against
+        // their next writes; s16 is rewritten before it, but only after barrier (2) of this chunk
+    }
+
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int col = warp * 32 + nt * 8 + (lane & 3) * 2;
+            *reinterpret_cast<float2 *>(state + (size_t)(mt * 16 + (lane >> 2)) * kD + col) =
+                make_float2(sacc[mt][nt][0], sacc[mt][nt][1]);
+            *reinterpret_cast<float2 *>(state + (size_t)(mt * 16 + (lane >> 2) + 8) * kD + col) =
+                make_float2(sacc[mt][nt][2], sacc[mt][nt][3]);
+        }
+}
+
+}  // namespace
 
 TT_API int tt_gdn_scan_chunked(tt_context *ctx, tt_stream stream, const void *conv_out, const void *a,
                                const void *b, const void *a_log, const void *dt_bias, float *state, void *y,
                                const tt_gdn_shape *shape, uint32_t rows, uint32_t row_stride, uint32_t chunk) {
     TT_ENTER(ctx);
-    (void)stream; (void)conv_out; (void)a; (void)b; (void)a_log; (void)dt_bias; (void)state; (void)y;
-    (void)shape; (void)rows; (void)row_stride; (void)chunk;
-    return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "chunked scan is not built yet");
+    if (shape == nullptr || conv_out == nullptr || a == nullptr || b == nullptr || state == nullptr || y == nullptr)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "chunked scan needs non-null buffers and shape");
+    const bool f32_gates = (shape->flags & TT_GDN_GATES_F32) != 0;
+    if (!f32_gates && (a_log == nullptr || dt_bias == nullptr))
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "a_log and dt_bias must not be null");
+    if (shape->n_k_heads == 0 || shape->n_v_heads == 0 || shape->n_v_heads % shape->n_k_heads != 0)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "n_v_heads must be a positive multiple of n_k_heads");
+    if (rows == 0) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "rows must be positive");
+    if (chunk != (uint32_t)kC)
+        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "chunk must be %d, got %u", kC, chunk);
+    if (shape->key_dim != (uint32_t)kD || shape->value_dim != (uint32_t)kD)
+        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE,
+                            "the chunked scan is built for key_dim == value_dim == %d (use tt_gdn_step otherwise)", kD);
+    const uint32_t tight = 2 * shape->n_k_heads * kD + shape->n_v_heads * kD;
+    if (row_stride < tight) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "row_stride %u is smaller than the qkv width %u", row_stride, tight);
+    if (row_stride % 8 != 0 || ((uintptr_t)conv_out & 15) || ((uintptr_t)state & 15) || ((uintptr_t)y & 3))
+        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "chunked scan needs 16-byte aligned rows and state");
+    const size_t per_chunk = sizeof(ChunkRecord) * shape->n_v_heads;
+    const uint32_t seg_chunks = (uint32_t)(ctx->workspace_bytes / per_chunk);
+    if (seg_chunks == 0) return tt_set_error(ctx, TT_ERR_OOM, "context workspace too small for one chunk of the scan");
+
+    static bool attrs_set = false;
+    if (!attrs_set) {
+        cudaError_t e = cudaFuncSetAttribute(gdn_scan_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)sizeof(PrepSmem));
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gdn_scan_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)sizeof(StateSmem));
+        if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn scan smem attribute");
+        attrs_set = true;
+    }
+    ScanParams p;
+    p.conv_out = reinterpret_cast<const __half *>(conv_out); p.a = a; p.b = b;
+    p.a_log = reinterpret_cast<const __nv_bfloat16 *>(a_log); p.dt_bias = reinterpret_cast<const __nv_bfloat16 *>(dt_bias);
+    p.state = state; p.y = reinterpret_cast<__half *>(y);
+    p.records = reinterpret_cast<ChunkRecord *>(ctx->partials);
+    p.hk = shape->n_k_heads; p.hv = shape->n_v_heads; p.rows = rows; p.row_stride = row_stride; p.flags = shape->flags;
+    p.readout_scale = shape->readout_scale;
+    const uint32_t total_chunks = (rows + kC - 1) / kC;
+    for (uint32_t c0 = 0; c0 < total_chunks; c0 += seg_chunks) {
+        p.token0 = c0 * kC;
+        p.n_chunks = total_chunks - c0 < seg_chunks ? total_chunks - c0 : seg_chunks;
+        gdn_scan_prepare_kernel<<<dim3(p.n_chunks, p.hv), 256, sizeof(PrepSmem), (cudaStream_t)stream>>>(p);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn_scan_prepare launch");
+        gdn_scan_state_kernel<<<dim3(kD / kDvb, p.hv), 128, sizeof(StateSmem), (cudaStream_t)stream>>>(p);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn_scan_state launch");
+        ctx->launches += 2;
+    }
+    return TT_OK;
 }
