@@ -42,7 +42,8 @@ UNIT = "tok/s"
 
 
 def session_lengths(rank: int):
-    rng = np.random.default_rng(20261125 + rank)
+    """The same drawn lengths on every rank: per-GPU work is fixed as N grows (weak scaling)."""
+    rng = np.random.default_rng(20261125)
     return [int(x) for x in rng.integers(1024, 32769, size=32)][:N_SESSIONS]
 
 
@@ -362,6 +363,50 @@ def aux_measurements(w, pk):
         del conv, y
     except Exception as exc:
         aux["gdn_scan_c3"] = {"error": str(exc)}
+    # config 4 on one GPU: one session, S = 262144, 16/2/256 (the per-GPU share at N GPUs is S/N of this)
+    try:
+        s4 = 262144
+        g = torch.Generator(device="cuda"); g.manual_seed(6)
+        k4 = torch.randn(s4, HKV * HD, device="cuda", generator=g).half()
+        v4 = torch.randn(s4, HKV * HD, device="cuda", generator=g).half()
+        q4 = torch.randn(HQ, HD, device="cuda", generator=g).half(); o4 = torch.empty_like(q4)
+        ms = ev_time(lambda: w.attn.encode_full(q4, k4, v4, o4, HD, HQ, HKV, s4, scale=SCALE), 30)
+        b4 = s4 * HKV * HD * 2 * 2 + HQ * HD * 2 * 2
+        aux["decode_c4_1gpu"] = {"ms": ms, "GBps": b4 / ms / 1e6, "frac_hbm": b4 / ms / 1e6 / pk["hbm_gbs"]}
+        del k4, v4
+    except Exception as exc:
+        aux["decode_c4_1gpu"] = {"error": str(exc)}
+    # config 5 on one GPU: 64 sessions x 4 draft rows, S = 16384 (+3), 32/2/256; GDN 4-row step with 64 value heads
+    try:
+        n5, w5, s5, hq5 = 64, 4, 16384 + 3, 32
+        g = torch.Generator(device="cuda"); g.manual_seed(8)
+        k5 = torch.randn(n5, s5, HKV * HD, device="cuda", generator=g).half()
+        v5 = torch.randn(n5, s5, HKV * HD, device="cuda", generator=g).half()
+        q5 = torch.randn(n5, w5, hq5 * HD, device="cuda", generator=g).half(); o5 = torch.empty_like(q5)
+        ses = [tt.DecodeSession(q5[i], o5[i], k5[i], v5[i], s5, w5) for i in range(n5)]
+        batch = w.attn.prepare_batch(ses, HD, hq5, HKV, scale=SCALE, io_dtype=tt.TT_F16)
+        ms = ev_time(lambda: w.attn.encode_prepared(batch), 10)
+        b5 = n5 * s5 * HKV * HD * 2 * 2 + 2 * n5 * w5 * hq5 * HD * 2
+        aux["verify_c5_1gpu"] = {"ms": ms, "GBps": b5 / ms / 1e6, "frac_hbm": b5 / ms / 1e6 / pk["hbm_gbs"],
+                                 "tok_per_s": n5 * w5 / ms * 1e3}
+        del k5, v5
+        cfg5 = tt.LinearAttentionConfig(GK, 64, GD, GD)
+        st5 = 0.02 * torch.randn(n5, 64 * GD * GD, device="cuda", generator=g)
+        qk = torch.randn(n5 * w5, 2 * GK, GD, device="cuda", generator=g)
+        qk = qk / qk.norm(dim=-1, keepdim=True); qk[:, :GK] *= GD ** -0.5
+        conv5 = torch.cat([qk.reshape(n5 * w5, -1), torch.randn(n5 * w5, 64 * GD, device="cuda", generator=g)], 1).half().contiguous()
+        a5 = (-torch.randn(n5 * w5, 64, device="cuda", generator=g)).half(); b5g = torch.randn(n5 * w5, 64, device="cuda", generator=g).half()
+        y5 = torch.empty(n5 * w5, 64 * GD, device="cuda", dtype=torch.float16)
+        z5 = torch.zeros(64, device="cuda", dtype=torch.bfloat16)
+        gdn5 = tt.GDN(w.ctx, cfg5)
+        gs = [tt.GDNSession(conv5[i * w5:(i + 1) * w5], a5[i * w5:(i + 1) * w5], b5g[i * w5:(i + 1) * w5], st5[i],
+                            y5[i * w5:(i + 1) * w5]) for i in range(n5)]
+        gb = gdn5.prepare_batch(gs)
+        ms = ev_time(lambda: gdn5.encode_prepared(gb, z5, z5, rows=w5), 10)
+        bg = n5 * 64 * GD * GD * 4 * 2 + n5 * w5 * (cfg5.qkv_dim + 64 * GD) * 2
+        aux["gdn_verify_c5_1gpu"] = {"ms": ms, "GBps": bg / ms / 1e6, "frac_hbm": bg / ms / 1e6 / pk["hbm_gbs"]}
+    except Exception as exc:
+        aux["verify_c5_1gpu_error"] = str(exc)
     # config 1: one session, S = 4096, 8/2/256; 32 distinct caches are rotated so HBM is really read
     try:
         s1, hq1 = 4096, 8

@@ -1,0 +1,63 @@
+"""Worker of tests/test_gpu_multi.py: one process per GPU (launched by torch.distributed.run)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import tinytitan_b200 as tt
+from tinytitan_b200 import sharding
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = tt.Context(local)
+    attn = tt.Attention(ctx)
+    hq, hkv, hd, s = 16, 2, 256, int(os.environ.get("TT_TEST_SEQ", "50001"))
+
+    # the same seeded session on every rank; each rank then keeps only its slice of the rows
+    g = torch.Generator(device="cuda"); g.manual_seed(99)
+    q = torch.randn(hq, hd, device="cuda", generator=g).half()
+    k = torch.randn(s, hkv * hd, device="cuda", generator=g).half()
+    v = torch.randn(s, hkv * hd, device="cuda", generator=g).half()
+    lo, hi = sharding.kv_split_ranges(s, world)[rank]
+    k_local, v_local = k[lo:hi].contiguous(), v[lo:hi].contiguous()
+
+    lc = sharding.LongContextDecode(attn, hd, hq, hkv, 0.0625)
+    out = torch.empty(hq, hd, device="cuda", dtype=torch.float16)
+    for _ in range(3):
+        lc.step(q, k_local, v_local, hi - lo, out)
+    torch.cuda.synchronize()
+
+    full = torch.empty_like(out)
+    attn.encode_full(q, k, v, full, hd, hq, hkv, s, scale=0.0625)      # single-GPU answer over all rows
+    torch.cuda.synchronize()
+    err = (out.float() - full.float()).abs().max().item()
+    assert err <= 1e-3, f"rank {rank}: split-KV merge differs from single-GPU attention by {err}"
+    # every rank ends with the same merged row
+    gathered = [torch.empty_like(out) for _ in range(world)]
+    dist.all_gather(gathered, out)
+    assert all(torch.equal(gathered[0], t) for t in gathered)
+
+    # independent sessions: each is decoded on exactly one rank, nothing is exchanged on the data path
+    lens = [257 * (i + 1) for i in range(8)]
+    mine = sharding.shard_sessions(lens, world)[rank]
+    done = torch.zeros(len(lens), device="cuda")
+    for i in mine:
+        kk = torch.randn(lens[i], hkv * hd, device="cuda", generator=g).half()
+        o = torch.empty(hq, hd, device="cuda", dtype=torch.float16)
+        attn.encode_full(q, kk, kk, o, hd, hq, hkv, lens[i], scale=0.0625)
+        done[i] = 1
+    dist.all_reduce(done)
+    assert torch.all(done == 1)
+    assert ctx.poll_status() == 0
+    dist.barrier()
+    dist.destroy_process_group()
+    print(f"RANK_OK {rank}")
+
+
+if __name__ == "__main__":
+    main()
