@@ -125,6 +125,42 @@ def time_cpu(lens, steps, warmup):
             "sample": desc, "ms_per_step": dt * 1e3, "gdn_kernel": kind}
 
 
+def cpu_side_baselines():
+    """The reference's CPU path for the other kernels, on bounded samples (reported only)."""
+    import oracle
+    out = {}
+    threads = oracle.max_threads()
+    rng = np.random.default_rng(11)
+    # prefill attention: CPUQwen35 attentionHead (gather + scores GEMM + masked softmax + PV GEMM) for all 16
+    # heads over a 1024-token prompt; the GEMM is a plain loop (the reference calls Accelerate's cblas_sgemm)
+    t = 1024
+    q = rng.standard_normal((t, HQ, HD), dtype=np.float32)
+    k = rng.standard_normal((t, HKV * HD), dtype=np.float32); v = rng.standard_normal((t, HKV * HD), dtype=np.float32)
+    t0 = time.perf_counter()
+    oracle.cpu_engine_attention_batch(q, k, v, HKV, 0, SCALE, threads=threads)
+    dt = time.perf_counter() - t0
+    flops = 4.0 * HQ * HD * (t * (t + 1) / 2)
+    out["prefill_attention"] = {"TFLOPs_causal": flops / dt / 1e12, "seconds": dt, "cores": threads, "kind": "port",
+                                "sample": f"{t}-token prompt, 16/2/256, all heads over {threads} threads, loop GEMM"}
+    # GDN prefill scan: the reference's tinytitan_delta_rule_chunk at its default chunk 8 and at 64
+    t = 512
+    unit = lambda x: x / np.sqrt((x * x).sum(-1, keepdims=True) + 1e-6)
+    gq = unit(rng.standard_normal((t, GK, GD), dtype=np.float32)).reshape(t, -1)
+    gk = unit(rng.standard_normal((t, GK, GD), dtype=np.float32)).reshape(t, -1)
+    gv = rng.standard_normal((t, GV * GD), dtype=np.float32)
+    al = rng.uniform(0.5, 1.0, size=(t, GV)).astype(np.float32); be = rng.uniform(0.1, 0.9, size=(t, GV)).astype(np.float32)
+    st = (0.02 * rng.standard_normal((GV, GD, GD))).astype(np.float32)
+    use_ref = oracle.ref() is not None
+    for chunk in (8, 64):
+        t0 = time.perf_counter()
+        oracle.gdn_scan_heads(gq, gk, gv, al, be, GK, GV, GD, GD, chunk, st, threads=threads, use_ref=use_ref)
+        dt = time.perf_counter() - t0
+        out[f"gdn_scan_chunk{chunk}"] = {"tokens_per_s": t / dt, "seconds": dt, "cores": threads,
+                                         "kind": "reference" if use_ref else "port",
+                                         "sample": f"{t} tokens, 16/32 heads d128, tinytitan_delta_rule_chunk, heads over threads"}
+    return out
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -501,6 +537,7 @@ def run_gpu_arm(args):
             line["aux"] = aux_measurements(w, pk)
             cpu = time_cpu(w.lens, 3, 1)
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            line["aux"]["cpu"] = cpu_side_baselines()
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line))
