@@ -384,12 +384,16 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
 // mode 0: normalised output in the I/O dtype; mode 1: merged unnormalised (m, d, o) triple.
 // ---------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(64)
+__global__ void __launch_bounds__(256)
 attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions, const float *__restrict__ part_o,
                            const float *__restrict__ part_m, const float *__restrict__ part_l,
                            uint32_t n_q_heads, uint32_t head_dim, uint32_t out_row_stride, int mode,
                            float *__restrict__ m_out, float *__restrict__ d_out, float *__restrict__ o_out) {
-    __shared__ float red[4];
+    // 256 threads = 4 groups of 64 column threads (one float4 of the row each); group g merges
+    // parts g, g+4, ... so that a long session's hundreds of parts are read with many loads in
+    // flight instead of one after another.
+    __shared__ float red[16];
+    __shared__ float4 accs[4][64];
     const TTDecodeSession ses = sessions[blockIdx.x];
     const uint32_t rows_total = ses.q_rows * n_q_heads;
     const uint32_t rho = blockIdx.y;
@@ -397,67 +401,78 @@ attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions, const f
     const uint32_t n_parts = ses.n_parts;
     const size_t base = (size_t)ses.partial_base + rho;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t grp = threadIdx.x >> 6, ct = threadIdx.x & 63;
 
-    // global maximum and denominator: the parts are read in parallel, not one after another
     float mg = -INFINITY;
-    for (uint32_t c = threadIdx.x; c < n_parts; c += blockDim.x) mg = fmaxf(mg, part_m[base + (size_t)c * rows_total]);
+    for (uint32_t c = threadIdx.x; c < n_parts; c += 256) mg = fmaxf(mg, part_m[base + (size_t)c * rows_total]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
     if (lane == 0) red[warp] = mg;
     __syncthreads();
-    mg = fmaxf(red[0], red[1]);
+    mg = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) mg = fmaxf(mg, red[i]);
     float D = 0.f;
     if (mg != -INFINITY)
-        for (uint32_t c = threadIdx.x; c < n_parts; c += blockDim.x) {
+        for (uint32_t c = threadIdx.x; c < n_parts; c += 256) {
             const size_t pr = base + (size_t)c * rows_total;
             D += part_l[pr] * __expf(part_m[pr] - mg);
         }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) D += __shfl_xor_sync(0xffffffffu, D, o);
-    if (lane == 0) red[2 + warp] = D;
+    if (lane == 0) red[8 + warp] = D;
     __syncthreads();
-    D = red[2] + red[3];
+    D = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) D += red[8 + i];
 
-    const uint32_t w = rho / n_q_heads, h = rho % n_q_heads;
-    for (uint32_t col = threadIdx.x * 4; col < head_dim; col += blockDim.x * 4) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (mg != -INFINITY) {
-            uint32_t c = 0;
-            for (; c + 4 <= n_parts; c += 4) {   // four independent loads in flight
-                float e[4]; float4 o[4];
+    const uint32_t col = ct * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (mg != -INFINITY && col < head_dim) {
+        uint32_t c = grp;
+        for (; c + 12 < n_parts; c += 16) {   // four independent loads in flight per thread
+            float e[4]; float4 o[4];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const size_t pr = base + (size_t)(c + u) * rows_total;
-                    e[u] = part_m[pr];
-                    o[u] = *reinterpret_cast<const float4 *>(part_o + pr * head_dim + col);
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const float wgt = __expf(e[u] - mg);
-                    acc.x += o[u].x * wgt; acc.y += o[u].y * wgt; acc.z += o[u].z * wgt; acc.w += o[u].w * wgt;
-                }
+            for (int u = 0; u < 4; ++u) {
+                const size_t pr = base + (size_t)(c + 4 * u) * rows_total;
+                e[u] = part_m[pr];
+                o[u] = *reinterpret_cast<const float4 *>(part_o + pr * head_dim + col);
             }
-            for (; c < n_parts; ++c) {
-                const size_t pr = base + (size_t)c * rows_total;
-                const float wgt = __expf(part_m[pr] - mg);
-                const float4 o = *reinterpret_cast<const float4 *>(part_o + pr * head_dim + col);
-                acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float wgt = __expf(e[u] - mg);
+                acc.x += o[u].x * wgt; acc.y += o[u].y * wgt; acc.z += o[u].z * wgt; acc.w += o[u].w * wgt;
             }
         }
-        if (mode == 0) {
-            const float inv = D > 0.f ? 1.f / D : 0.f;
-            T *dst = reinterpret_cast<T *>(ses.out) + (size_t)w * out_row_stride + (size_t)h * head_dim + col;
-            uint2 packed;
-            packed.x = pack2<T>(acc.x * inv, acc.y * inv);
-            packed.y = pack2<T>(acc.z * inv, acc.w * inv);
-            *reinterpret_cast<uint2 *>(dst) = packed;
-        } else {
-            *reinterpret_cast<float4 *>(o_out + (size_t)rho * head_dim + col) = acc;
+        for (; c < n_parts; c += 4) {
+            const size_t pr = base + (size_t)c * rows_total;
+            const float wgt = __expf(part_m[pr] - mg);
+            const float4 o = *reinterpret_cast<const float4 *>(part_o + pr * head_dim + col);
+            acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
         }
     }
-    if (mode != 0 && threadIdx.x == 0) {
-        m_out[rho] = mg;
-        d_out[rho] = D;
+    accs[grp][ct] = acc;
+    __syncthreads();
+    if (grp != 0 || col >= head_dim) return;
+#pragma unroll
+    for (int g = 1; g < 4; ++g) {
+        const float4 o = accs[g][ct];
+        acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
+    }
+    const uint32_t w = rho / n_q_heads, h = rho % n_q_heads;
+    if (mode == 0) {
+        const float inv = D > 0.f ? 1.f / D : 0.f;
+        T *dst = reinterpret_cast<T *>(ses.out) + (size_t)w * out_row_stride + (size_t)h * head_dim + col;
+        uint2 packed;
+        packed.x = pack2<T>(acc.x * inv, acc.y * inv);
+        packed.y = pack2<T>(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2 *>(dst) = packed;
+    } else {
+        *reinterpret_cast<float4 *>(o_out + (size_t)rho * head_dim + col) = acc;
+        if (ct == 0) {
+            m_out[rho] = mg;
+            d_out[rho] = D;
+        }
     }
 }
 
@@ -685,7 +700,7 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     ctx->launches++;
 
     const dim3 grid(n_sessions, max_rows);
-    const uint32_t threads = 64;
+    const uint32_t threads = 256;
     if (p->io_dtype == TT_F16)
         attn_decode_combine_kernel<__half><<<grid, threads, 0, stream>>>(
             ctx->sessions, part_o, part_m, part_l, p->n_q_heads, p->head_dim, p->out_row_stride_elements, mode,
@@ -914,7 +929,7 @@ TT_API int tt_attn_decode_noalloc(tt_stream stream, const void *q, const void *k
     p.out_row_stride_elements = n_q_heads * head_dim; p.scale = scale; p.io_dtype = TT_F16;
     if (launch_partial_hd<__half>(s, cursor, d_items, d_ses, part_o, part_m, part_l, &p, status) != cudaSuccess)
         return TT_ERR_CUDA;
-    attn_decode_combine_kernel<__half><<<dim3(1, n_q_heads), 64, 0, s>>>(d_ses, part_o, part_m, part_l, n_q_heads,
+    attn_decode_combine_kernel<__half><<<dim3(1, n_q_heads), 256, 0, s>>>(d_ses, part_o, part_m, part_l, n_q_heads,
                                                                          head_dim, n_q_heads * head_dim, 0, nullptr,
                                                                          nullptr, nullptr);
     return cudaGetLastError() == cudaSuccess ? TT_OK : TT_ERR_CUDA;

@@ -97,26 +97,51 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_step_kernel(GdnParams p) {
 
     const float a_param = __bfloat162float(p.a_log[h]);
     const float dtb = __bfloat162float(p.dt_bias[h]);
+    const bool rows_valid = dv0 < p.dv;   // value_dim is a multiple of 8: a warp's 8 rows are all in or all out
 
-    for (uint32_t t = 0; t < p.rows; ++t) {
+    // One token's inputs; the next token's are fetched while the current one is being applied,
+    // so the multi-row form does not pay a global-load latency per token.
+    struct Tok { float q[NPL], k[NPL], v[kRowsPerWarp], g, beta; };
+    auto load_tok = [&](uint32_t t, Tok &tok) {
         const __half *row = reinterpret_cast<const __half *>(ses.conv_out) + (size_t)t * p.row_stride;
-        float q[NPL], k[NPL];
-        load_half_vec<NPL>(q, row + (size_t)hk * p.dk + col);
-        load_half_vec<NPL>(k, row + (size_t)p.hk * p.dk + (size_t)hk * p.dk + col);
+        load_half_vec<NPL>(tok.q, row + (size_t)hk * p.dk + col);
+        load_half_vec<NPL>(tok.k, row + (size_t)p.hk * p.dk + (size_t)hk * p.dk + col);
         const __half *vrow = row + (size_t)2 * p.hk * p.dk + (size_t)h * p.dv;
-
-        float g, beta;
+        if (rows_valid) {
+            const uint2 lo = *reinterpret_cast<const uint2 *>(vrow + dv0);
+            const uint2 hi = *reinterpret_cast<const uint2 *>(vrow + dv0 + 4);
+            const float2 v0 = __half22float2(*reinterpret_cast<const __half2 *>(&lo.x));
+            const float2 v1 = __half22float2(*reinterpret_cast<const __half2 *>(&lo.y));
+            const float2 v2 = __half22float2(*reinterpret_cast<const __half2 *>(&hi.x));
+            const float2 v3 = __half22float2(*reinterpret_cast<const __half2 *>(&hi.y));
+            tok.v[0] = v0.x; tok.v[1] = v0.y; tok.v[2] = v1.x; tok.v[3] = v1.y;
+            tok.v[4] = v2.x; tok.v[5] = v2.y; tok.v[6] = v3.x; tok.v[7] = v3.y;
+        } else {
+#pragma unroll
+            for (int r = 0; r < kRowsPerWarp; ++r) tok.v[r] = 0.f;
+        }
         if (p.flags & TT_GDN_GATES_F32) {
-            g = reinterpret_cast<const float *>(ses.a)[(size_t)t * p.hv + h];
-            beta = reinterpret_cast<const float *>(ses.b)[(size_t)t * p.hv + h];
+            tok.g = reinterpret_cast<const float *>(ses.a)[(size_t)t * p.hv + h];
+            tok.beta = reinterpret_cast<const float *>(ses.b)[(size_t)t * p.hv + h];
         } else {
             const float av = __half2float(reinterpret_cast<const __half *>(ses.a)[(size_t)t * p.hv + h]);
             const float bv = __half2float(reinterpret_cast<const __half *>(ses.b)[(size_t)t * p.hv + h]);
             const float x = av + dtb;
             const float sp = x > 20.f ? x : logf(1.f + expf(x));
-            g = (p.flags & TT_GDN_A_LOG_PREEXP) ? expf(a_param * sp) : expf(-expf(a_param) * sp);
-            beta = 1.f / (1.f + expf(-bv));
+            tok.g = (p.flags & TT_GDN_A_LOG_PREEXP) ? expf(a_param * sp) : expf(-expf(a_param) * sp);
+            tok.beta = 1.f / (1.f + expf(-bv));
         }
+    };
+
+    Tok cur;
+    load_tok(0, cur);
+    for (uint32_t t = 0; t < p.rows; ++t) {
+        Tok nxt = cur;
+        if (t + 1 < p.rows) load_tok(t + 1, nxt);
+        float q[NPL], k[NPL];
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) { q[i] = cur.q[i]; k[i] = cur.k[i]; }
+        const float g = cur.g, beta = cur.beta;
 
         float kv[kRowsPerWarp];
 #pragma unroll
@@ -135,7 +160,7 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_step_kernel(GdnParams p) {
         float out[kRowsPerWarp];
 #pragma unroll
         for (int r = 0; r < kRowsPerWarp; ++r) {
-            const float vv = (dv0 + r < p.dv) ? __half2float(vrow[dv0 + r]) : 0.f;
+            const float vv = cur.v[r];
             const float delta = (vv - kv[r]) * beta;
             float acc = 0.f;
 #pragma unroll
@@ -163,6 +188,7 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_step_kernel(GdnParams p) {
             for (int r = 0; r < kRowsPerWarp; ++r)
                 if (dv0 + r < p.dv) store_vec<NPL>(ck + (size_t)(dv0 + r) * p.dk + col, s[r]);
         }
+        cur = nxt;
     }
 
 #pragma unroll
