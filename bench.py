@@ -458,7 +458,27 @@ def aux_measurements(w, pk):
         ms = ev_time(one, 64)
         b1 = s1 * HKV * HD * 2 * 2 + hq1 * HD * 2 * 2
         aux["decode_c1"] = {"ms": ms, "GBps": b1 / ms / 1e6, "frac_hbm": b1 / ms / 1e6 / pk["hbm_gbs"],
-                            "note": "32 rotating caches (268 MB) so the 8 MiB working set does not sit in L2"}
+                            "note": "32 rotating caches (268 MB) so the 8 MiB working set does not sit in L2; "
+                                    "one Python call per step, so this includes ~10 us of host overhead"}
+        # the same 32 calls replayed from one CUDA graph: device-side time per call without the host
+        try:
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(32):
+                    one()
+                torch.cuda.synchronize()
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(32):
+                        one()
+            torch.cuda.synchronize()
+            msg = ev_time(graph.replay, 20) / 32
+            aux["decode_c1"]["graph_ms"] = msg
+            aux["decode_c1"]["graph_GBps"] = b1 / msg / 1e6
+            aux["decode_c1"]["graph_frac_hbm"] = b1 / msg / 1e6 / pk["hbm_gbs"]
+        except Exception as exc:
+            aux["decode_c1"]["graph_error"] = str(exc)
     except Exception as exc:
         aux["decode_c1"] = {"error": str(exc)}
     return aux

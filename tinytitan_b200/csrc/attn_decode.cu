@@ -6,12 +6,14 @@
 //
 // HBM-bound design. A work item is (session, kv head, 16-row tile of packed query rows, key
 // range). Every K/V row of the range is read from HBM once per KV head and serves all query
-// rows of the group (the reference re-reads it per q head). Each warp of a CTA streams its own
-// 16-key blocks through a private 3-stage shared-memory ring filled by bulk async copies
-// (cp.async.bulk + mbarrier complete_tx), so there is no CTA-wide barrier in the key loop;
-// Q.K^T and P.V run on mma.sync m16n8k16 with fp32 accumulation, the softmax is done on the
-// accumulator fragments with quad shuffles, and the warps' (m, l, O) states are merged once at
-// the end. Pass 2 merges the items of a session by log-sum-exp.
+// rows of the group (the reference re-reads it per q head). A CTA is one warp pair: both warps
+// stream the same 16-key blocks through a 3-stage shared-memory ring filled by bulk async
+// copies (cp.async.bulk + mbarrier complete_tx), each warp owns one half of the head dimension
+// (its half of Q in registers, its half of the output columns), Q.K^T and P.V run on
+// mma.sync m16n8k16 with fp32 accumulation, the softmax is done on the accumulator fragments
+// with quad shuffles. Pass 2 merges the items of a session by log-sum-exp. A call with one
+// session carries it in the kernel parameters (no table upload), which also makes that call
+// capturable in a CUDA graph.
 #include "tt_common.h"
 
 namespace {
@@ -158,7 +160,8 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
                            const TTDecodeSession *__restrict__ sessions, float *__restrict__ part_o,
                            float *__restrict__ part_m, float *__restrict__ part_l,
                            uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t kv_stride_bytes,
-                           uint32_t q_row_stride, float scale_log2, uint32_t *__restrict__ status) {
+                           uint32_t q_row_stride, float scale_log2, uint32_t *__restrict__ status,
+                           const TTDecodeSession single, uint32_t single_keys_per_item) {
     using S = DecodeSmem<HD>;
     constexpr int HH = HD / 2;          // head-dim half per warp
     constexpr int KS = HH / 16;         // k-steps of the partial Q.K^T
@@ -166,9 +169,26 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    const TTDecodeItem item = items[blockIdx.x];
-    const TTDecodeSession ses = sessions[item.session];
     const uint32_t group = n_q_heads / n_kv_heads;
+    // One-session calls carry the session in the kernel parameters and derive the work item from
+    // the block index (all items are equal slices), so no table has to be copied to the device.
+    TTDecodeItem item;
+    TTDecodeSession ses;
+    if (single_keys_per_item != 0) {
+        ses = single;
+        const uint32_t packed_rows = ses.q_rows * group;
+        const uint32_t row_tiles = (packed_rows + 15) / 16;
+        const uint32_t rt = blockIdx.x % row_tiles, kvh = (blockIdx.x / row_tiles) % n_kv_heads;
+        const uint32_t part = blockIdx.x / (row_tiles * n_kv_heads);
+        item.session = 0; item.kv_head = kvh; item.part_index = part; item.partial_base = 0;
+        item.key_begin = min(ses.seq_len, ses.kv_start + part * single_keys_per_item);
+        item.key_end = min(ses.seq_len, item.key_begin + single_keys_per_item);
+        item.row_begin = rt * 16;
+        item.row_count = min(16u, packed_rows - rt * 16);
+    } else {
+        item = items[blockIdx.x];
+        ses = sessions[item.session];
+    }
 
     unsigned char *ring = smem;
     float *xchg = reinterpret_cast<float *>(smem + S::kRingBytes);
@@ -388,13 +408,14 @@ __global__ void __launch_bounds__(256)
 attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions, const float *__restrict__ part_o,
                            const float *__restrict__ part_m, const float *__restrict__ part_l,
                            uint32_t n_q_heads, uint32_t head_dim, uint32_t out_row_stride, int mode,
-                           float *__restrict__ m_out, float *__restrict__ d_out, float *__restrict__ o_out) {
+                           float *__restrict__ m_out, float *__restrict__ d_out, float *__restrict__ o_out,
+                           const TTDecodeSession single, int use_single) {
     // 256 threads = 4 groups of 64 column threads (one float4 of the row each); group g merges
     // parts g, g+4, ... so that a long session's hundreds of parts are read with many loads in
     // flight instead of one after another.
     __shared__ float red[16];
     __shared__ float4 accs[4][64];
-    const TTDecodeSession ses = sessions[blockIdx.x];
+    const TTDecodeSession ses = use_single ? single : sessions[blockIdx.x];
     const uint32_t rows_total = ses.q_rows * n_q_heads;
     const uint32_t rho = blockIdx.y;
     if (rho >= rows_total) return;
@@ -502,25 +523,27 @@ __global__ void attn_combine_parts_kernel(const float *__restrict__ m, const flo
 template <int HD, typename T>
 cudaError_t launch_partial(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
                            const TTDecodeSession *sessions, float *part_o, float *part_m,
-                           float *part_l, const tt_attn_batch_params *p, uint32_t *status) {
+                           float *part_l, const tt_attn_batch_params *p, uint32_t *status,
+                           const TTDecodeSession &single, uint32_t single_keys) {
     auto kernel = attn_decode_partial_kernel<HD, T>;
     const int smem = DecodeSmem<HD>::kTotal;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     kernel<<<n_items, 64, smem, stream>>>(items, sessions, part_o, part_m, part_l, p->n_q_heads,
                                           p->n_kv_heads, p->kv_token_stride_elements * 2u,
-                                          p->q_row_stride_elements, p->scale * kLog2e, status);
+                                          p->q_row_stride_elements, p->scale * kLog2e, status, single, single_keys);
     return cudaGetLastError();
 }
 
 template <typename T>
 cudaError_t launch_partial_hd(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
                               const TTDecodeSession *sessions, float *part_o, float *part_m,
-                              float *part_l, const tt_attn_batch_params *p, uint32_t *status) {
+                              float *part_l, const tt_attn_batch_params *p, uint32_t *status,
+                              const TTDecodeSession &single = TTDecodeSession(), uint32_t single_keys = 0) {
     switch (p->head_dim) {
-        case 64: return launch_partial<64, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status);
-        case 128: return launch_partial<128, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status);
-        case 256: return launch_partial<256, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status);
+        case 64: return launch_partial<64, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, single, single_keys);
+        case 128: return launch_partial<128, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, single, single_keys);
+        case 256: return launch_partial<256, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, single, single_keys);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -540,18 +563,19 @@ TT_API int tt_attn_plan_splits(const uint32_t *keys_per_session, const uint32_t 
         head_dim == 0 || sm_count == 0)
         return TT_ERR_INVALID_ARG;
     const uint32_t group = n_q_heads / n_kv_heads;
-    // Streams of keys to be read: one per (session, kv head, 16-row tile).
+    const uint32_t rows_per_item = 16u, items_per_sm = 12u;
+    // Streams of keys to be read: one per (session, kv head, row tile).
     uint64_t key_rows = 0, max_rows = 0;
     for (uint32_t i = 0; i < n_sessions; ++i) {
         const uint32_t qr = q_rows_per_session ? q_rows_per_session[i] : 1u;
-        const uint32_t tiles = ceil_div_u32((uint64_t)qr * group, 16);
+        const uint32_t tiles = ceil_div_u32((uint64_t)qr * group, rows_per_item);
         key_rows += (uint64_t)keys_per_session[i] * n_kv_heads * tiles;
         max_rows += (uint64_t)qr * n_q_heads;
     }
     // Four 64-thread CTAs are resident per SM; ~12 items per SM give the hardware scheduler three
     // waves to even out ragged sessions, while an item stays long enough (>= 64 keys, i.e. four
     // pipeline blocks) to amortise its pipeline fill, which the co-resident CTAs overlap anyway.
-    uint64_t target = key_rows / ((uint64_t)sm_count * 12u);
+    uint64_t target = key_rows / ((uint64_t)sm_count * items_per_sm);
     uint32_t keys = (uint32_t)((target + 63) / 64 * 64);
     if (keys < 64) keys = 64;
     if (keys > 16384) keys = 16384;
@@ -559,7 +583,7 @@ TT_API int tt_attn_plan_splits(const uint32_t *keys_per_session, const uint32_t 
         uint64_t items = 0, prows = 0;
         for (uint32_t i = 0; i < n_sessions; ++i) {
             const uint32_t qr = q_rows_per_session ? q_rows_per_session[i] : 1u;
-            const uint32_t tiles = ceil_div_u32((uint64_t)qr * group, 16);
+            const uint32_t tiles = ceil_div_u32((uint64_t)qr * group, rows_per_item);
             uint32_t parts = ceil_div_u32(keys_per_session[i], keys);
             if (parts == 0) parts = 1;  // an empty range still produces its (-inf, 0, 0) partial
             items += (uint64_t)parts * n_kv_heads * tiles;
@@ -649,6 +673,8 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
         return tt_set_error(ctx, TT_ERR_OOM, "%u work items exceed the context's item table (%u)", n_items,
                             ctx->max_items);
 
+    const uint32_t rows_per_item = 16u;
+
     // Build the session and item tables.
     uint32_t partial_cursor = 0, item_cursor = 0, max_rows = 0;
     for (uint32_t i = 0; i < n_sessions; ++i) {
@@ -667,11 +693,11 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
             if (ke > s.seq_len) ke = s.seq_len;
             if (ke < kb) ke = kb;
             for (uint32_t kvh = 0; kvh < p->n_kv_heads; ++kvh)
-                for (uint32_t rb = 0; rb < packed_rows; rb += 16) {
+                for (uint32_t rb = 0; rb < packed_rows; rb += rows_per_item) {
                     TTDecodeItem &it = ctx->h_items[item_cursor++];
                     it.session = i; it.kv_head = kvh; it.key_begin = kb; it.key_end = ke;
                     it.part_index = part; it.row_begin = rb;
-                    it.row_count = packed_rows - rb < 16 ? packed_rows - rb : 16;
+                    it.row_count = packed_rows - rb < rows_per_item ? packed_rows - rb : rows_per_item;
                     it.partial_base = s.partial_base;
                 }
         }
@@ -683,18 +709,28 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     float *part_m = part_o + (size_t)partial_cursor * p->head_dim;
     float *part_l = part_m + partial_cursor;
 
-    cudaError_t e = cudaMemcpyAsync(ctx->sessions, ctx->h_sessions, sizeof(TTDecodeSession) * n_sessions,
-                                    cudaMemcpyHostToDevice, stream);
-    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "copy session table");
-    e = cudaMemcpyAsync(ctx->items, ctx->h_items, sizeof(TTDecodeItem) * n_items, cudaMemcpyHostToDevice, stream);
-    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "copy item table");
+    // One session: its descriptor travels in the kernel parameters and the items are derived from
+    // the block index, so the two table uploads (and their latency) are skipped.
+    const bool single = n_sessions == 1;
+    const TTDecodeSession single_ses = ctx->h_sessions[0];
+    const uint32_t single_keys = single ? keys_per_item : 0u;
+    cudaError_t e = cudaSuccess;
+    if (!single) {
+        e = cudaMemcpyAsync(ctx->sessions, ctx->h_sessions, sizeof(TTDecodeSession) * n_sessions,
+                            cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return tt_check_cuda(ctx, e, "copy session table");
+        e = cudaMemcpyAsync(ctx->items, ctx->h_items, sizeof(TTDecodeItem) * n_items, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return tt_check_cuda(ctx, e, "copy item table");
+    }
 
     const bool timed = ctx->profiling && ctx->profile_count < tt_context::kProfileSlots;
     if (timed) cudaEventRecord(ctx->profile_begin[ctx->profile_count], stream);
     if (p->io_dtype == TT_F16)
-        e = launch_partial_hd<__half>(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status);
+        e = launch_partial_hd<__half>(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status,
+                                      single_ses, single_keys);
     else
-        e = launch_partial_hd<__nv_bfloat16>(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status);
+        e = launch_partial_hd<__nv_bfloat16>(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p,
+                                             ctx->status, single_ses, single_keys);
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_decode_partial launch");
     if (timed) cudaEventRecord(ctx->profile_end[ctx->profile_count++], stream);
     ctx->launches++;
@@ -704,11 +740,11 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     if (p->io_dtype == TT_F16)
         attn_decode_combine_kernel<__half><<<grid, threads, 0, stream>>>(
             ctx->sessions, part_o, part_m, part_l, p->n_q_heads, p->head_dim, p->out_row_stride_elements, mode,
-            m_out, d_out, o_out);
+            m_out, d_out, o_out, single_ses, single ? 1 : 0);
     else
         attn_decode_combine_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
             ctx->sessions, part_o, part_m, part_l, p->n_q_heads, p->head_dim, p->out_row_stride_elements, mode,
-            m_out, d_out, o_out);
+            m_out, d_out, o_out, single_ses, single ? 1 : 0);
     e = cudaGetLastError();
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_decode_combine launch");
     ctx->launches++;
@@ -931,6 +967,6 @@ TT_API int tt_attn_decode_noalloc(tt_stream stream, const void *q, const void *k
         return TT_ERR_CUDA;
     attn_decode_combine_kernel<__half><<<dim3(1, n_q_heads), 256, 0, s>>>(d_ses, part_o, part_m, part_l, n_q_heads,
                                                                          head_dim, n_q_heads * head_dim, 0, nullptr,
-                                                                         nullptr, nullptr);
+                                                                         nullptr, nullptr, host.ses, 0);
     return cudaGetLastError() == cudaSuccess ? TT_OK : TT_ERR_CUDA;
 }
