@@ -282,6 +282,37 @@ int tt_gdn_scan_chunked(tt_context *ctx, tt_stream stream, const void *conv_out,
                         void *y, const tt_gdn_shape *shape, uint32_t rows, uint32_t row_stride,
                         uint32_t chunk);
 
+/* The elementwise kernels around the delta rule (first "next" row of the scope).
+ * conv_mix: causal depthwise conv + SiLU over [tail rows | rows of qkv]; tail fp16
+ * [taps-1][channels], qkv fp16 [rows][channels], conv_weight bf16 [channels][taps],
+ * out fp16 [rows][channels]. update_tail != 0 is GDN.encodeConvDecode ->
+ * gdn_conv_mix_decode (rows must be 1; the tail is shifted in place), 0 is
+ * GDN.encodeConvPrefill -> gdn_conv_mix_prefill with the tail read-only
+ * (sources/TinyTitan/Kernels/GDN/GDN.swift:185-236,
+ * sources/TinyTitanCore/Metal/GDN/gdn.metal:330-393). */
+int tt_gdn_conv_mix(tt_context *ctx, tt_stream stream, void *tail, const void *qkv,
+                    const void *conv_weight, void *out, uint32_t channels, uint32_t taps,
+                    uint32_t rows, int update_tail);
+/* GDN.encodeConvTailUpdate -> gdn_conv_tail_update (GDN.swift:238-262, gdn.metal:396-447):
+ * tail := last taps-1 raw rows of [old tail | rows of qkv]. */
+int tt_gdn_conv_tail_update(tt_context *ctx, tt_stream stream, void *tail, const void *qkv,
+                            uint32_t channels, uint32_t taps, uint32_t rows);
+/* GDN.encodeConvTailCheckpoint -> gdn_conv_tail_checkpoint (GDN.swift:264-286,
+ * gdn.metal:449-464): the tail as it stands after qkv row 0 alone. */
+int tt_gdn_conv_tail_checkpoint(tt_context *ctx, tt_stream stream, const void *tail, const void *qkv,
+                                void *checkpoint, uint32_t channels, uint32_t taps);
+/* GDN.encodeQKNorm -> gdn_qk_norm (GDN.swift:288-313, gdn.metal:472-521): per key head,
+ * in place on the q and k slices of conv_out rows: x * rsqrt(mean(x^2) + 1e-6) * (q: 1/Dk,
+ * k: 1/sqrt(Dk)). */
+int tt_gdn_qk_norm(tt_context *ctx, tt_stream stream, void *conv_out, uint32_t n_k_heads,
+                   uint32_t key_dim, uint32_t row_stride, uint32_t rows);
+/* GDN.encodeGatedNorm -> gdn_gated_norm (GDN.swift:399-427, gdn.metal:678-727):
+ * out = rmsnorm(y per value head) * weight * gate(z), gate = SiLU or sigmoid
+ * (LinearAttentionConfig.OutputGate). y,z,out fp16 [rows][Hv*Dv], weight bf16 [Dv]. */
+int tt_gdn_gated_norm(tt_context *ctx, tt_stream stream, const void *y, const void *z,
+                      const void *weight, void *out, uint32_t n_v_heads, uint32_t value_dim,
+                      uint32_t rows, int sigmoid_gate);
+
 /* ------------------------------------------------------------- allocators */
 
 /* Where the managers get memory. NULL selects CUDA device memory on the

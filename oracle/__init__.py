@@ -288,3 +288,59 @@ def delta_rule_sessions(query, key, value, a, b, decay_log, decay_bias, key_head
                                         C.c_float(inverse), threads or max_threads(), _p(state),
                                         _p(ro))
     return ro, state
+
+
+# --------------------------------------------------------------------------
+# the whole Gated-DeltaNet chain of one layer, token by token (numpy, fp32 with the GPU path's
+# fp16 rounding points). Follows sources/TinyTitanValidation/Support/Reference/GDN/
+# GDNReference.swift:45-123: conv + SiLU (rounded to fp16, :55-64), tail shift (:65-66), q/k RMS
+# norm with folded scales 1/Dk and 1/sqrt(Dk) (rounded, :68-81), delta rule (y rounded, :84-107),
+# gated output norm rmsnorm(y) * w * silu(z) (:109-121).
+# --------------------------------------------------------------------------
+class GDNChainReference:
+    def __init__(self, hk, hv, dk, dv, taps, conv_w, a_log, dt_bias, norm_w):
+        self.hk, self.hv, self.dk, self.dv, self.taps = hk, hv, dk, dv, taps
+        self.c = 2 * hk * dk + hv * dv
+        self.conv_w = _f(conv_w).reshape(self.c, taps)
+        self.a_log, self.dt_bias, self.norm_w = _f(a_log), _f(dt_bias), _f(norm_w)
+        self.tail = np.zeros((taps - 1, self.c), np.float32)
+        self.state = np.zeros((hv, dv, dk), np.float32)
+
+    @staticmethod
+    def _h(x):
+        return np.asarray(x, np.float32).astype(np.float16).astype(np.float32)
+
+    def conv(self, qkv_raw):
+        x = _f(qkv_raw)
+        acc = x * self.conv_w[:, self.taps - 1]
+        for j in range(self.taps - 1):
+            acc = acc + self.tail[j] * self.conv_w[:, j]
+        acc = acc.astype(np.float32)
+        out = self._h(acc / (1 + np.exp(-acc)))
+        self.tail = np.concatenate([self.tail[1:], self._h(x)[None]], 0)
+        return out
+
+    def qk_norm(self, conv):
+        n = conv.copy()
+        for hi in range(2 * self.hk):
+            is_q = hi < self.hk
+            head = hi if is_q else hi - self.hk
+            base = (0 if is_q else self.hk * self.dk) + head * self.dk
+            sl = conv[base:base + self.dk]
+            inv = np.float32(1) / np.sqrt(np.float32((sl * sl).sum(dtype=np.float32) / self.dk + 1e-6))
+            scale = np.float32(1 / self.dk) if is_q else np.float32(1 / np.sqrt(self.dk))
+            n[base:base + self.dk] = self._h(sl * inv * scale)
+        return n
+
+    def gated_norm(self, y, z, sigmoid_gate=False):
+        y, z = _f(y).reshape(self.hv, self.dv), _f(z).reshape(self.hv, self.dv)
+        inv = 1 / np.sqrt((y * y).sum(-1, keepdims=True, dtype=np.float32) / self.dv + 1e-6)
+        gate = 1 / (1 + np.exp(-z)) if sigmoid_gate else z / (1 + np.exp(-z))
+        return (y * inv * self.norm_w[None] * gate).astype(np.float32).reshape(-1)
+
+    def step(self, qkv_raw, a, b, z):
+        normed = self.qk_norm(self.conv(qkv_raw))
+        y, self.state, _ = gdn_step_rows(normed[None], _f(a)[None], _f(b)[None], self.a_log, self.dt_bias,
+                                         self.hk, self.hv, self.dk, self.dv, self.state)
+        y = self._h(y[0])
+        return self.gated_norm(y, z), y, normed

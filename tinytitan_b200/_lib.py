@@ -126,6 +126,11 @@ SIGNATURES = {
                                       _u32]),
     "tt_gdn_scan_chunked": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(GdnShape), _u32, _u32,
                                       _u32]),
+    "tt_gdn_conv_mix": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, C.c_int]),
+    "tt_gdn_conv_tail_update": (C.c_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32]),
+    "tt_gdn_conv_tail_checkpoint": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32]),
+    "tt_gdn_qk_norm": (C.c_int, [_vp, _vp, _vp, _u32, _u32, _u32, _u32]),
+    "tt_gdn_gated_norm": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, C.c_int]),
     "tt_kv_row_layout": (None, [_u32, _u32, C.POINTER(_u32), C.POINTER(_u32)]),
     "tt_kv_cache_create": (_vp, [C.POINTER(Arch), _u32, _u32, _u32, C.c_int, _u32, C.POINTER(Allocator),
                                  C.POINTER(C.c_int)]),

@@ -329,6 +329,50 @@ class GDN:
         self.shape = L.GdnShape(config.num_k_heads, config.num_v_heads, config.key_head_dim,
                                 config.value_head_dim, flags, readout_scale)
 
+    # ---- the elementwise kernels around the delta rule (GDN.swift:185-313, :399-427) ----
+    def encode_conv_decode(self, tail, qkv, conv_weight, out, command_buffer=None, tail_offset=0, qkv_offset=0,
+                           conv_weight_offset=0, out_offset=0):
+        """GDN.encodeConvDecode: conv + SiLU of one row, the tail shifted in place."""
+        self.context.check(L.lib().tt_gdn_conv_mix(
+            self.context.handle, _stream(command_buffer), _addr(tail, tail_offset), _addr(qkv, qkv_offset),
+            _addr(conv_weight, conv_weight_offset), _addr(out, out_offset), self.config.qkv_dim,
+            self.config.conv_kernel_size, 1, 1))
+
+    def encode_conv_prefill(self, tail, qkv_rows, conv_weight, out, rows, command_buffer=None, tail_offset=0,
+                            qkv_rows_offset=0, conv_weight_offset=0, out_offset=0):
+        """GDN.encodeConvPrefill: conv over [tail | chunk rows]; the tail is read-only here."""
+        self.context.check(L.lib().tt_gdn_conv_mix(
+            self.context.handle, _stream(command_buffer), _addr(tail, tail_offset), _addr(qkv_rows, qkv_rows_offset),
+            _addr(conv_weight, conv_weight_offset), _addr(out, out_offset), self.config.qkv_dim,
+            self.config.conv_kernel_size, rows, 0))
+
+    def encode_conv_tail_update(self, tail, qkv_rows, rows, command_buffer=None, tail_offset=0, qkv_rows_offset=0):
+        """GDN.encodeConvTailUpdate: tail := last (kernel-1) raw rows of [tail | chunk]."""
+        self.context.check(L.lib().tt_gdn_conv_tail_update(
+            self.context.handle, _stream(command_buffer), _addr(tail, tail_offset), _addr(qkv_rows, qkv_rows_offset),
+            self.config.qkv_dim, self.config.conv_kernel_size, rows))
+
+    def encode_conv_tail_checkpoint(self, tail, qkv, checkpoint, command_buffer=None, tail_offset=0, qkv_offset=0,
+                                    checkpoint_offset=0):
+        """GDN.encodeConvTailCheckpoint: the tail as it stands after row 0 alone."""
+        self.context.check(L.lib().tt_gdn_conv_tail_checkpoint(
+            self.context.handle, _stream(command_buffer), _addr(tail, tail_offset), _addr(qkv, qkv_offset),
+            _addr(checkpoint, checkpoint_offset), self.config.qkv_dim, self.config.conv_kernel_size))
+
+    def encode_qk_norm(self, conv_out, rows=1, row_stride=None, command_buffer=None, conv_out_offset=0):
+        """GDN.encodeQKNorm: per-head RMS norm of the q and k slices, delta-rule scales folded in."""
+        self.context.check(L.lib().tt_gdn_qk_norm(
+            self.context.handle, _stream(command_buffer), _addr(conv_out, conv_out_offset), self.config.num_k_heads,
+            self.config.key_head_dim, row_stride or self.config.qkv_dim, rows))
+
+    def encode_gated_norm(self, y, z, norm_weight, out, rows=1, sigmoid_gate=False, command_buffer=None, y_offset=0,
+                          z_offset=0, norm_weight_offset=0, out_offset=0):
+        """GDN.encodeGatedNorm: rmsnorm(y) * weight * silu(z) (or sigmoid(z)) per value head."""
+        self.context.check(L.lib().tt_gdn_gated_norm(
+            self.context.handle, _stream(command_buffer), _addr(y, y_offset), _addr(z, z_offset),
+            _addr(norm_weight, norm_weight_offset), _addr(out, out_offset), self.config.num_v_heads,
+            self.config.value_head_dim, rows, int(sigmoid_gate)))
+
     def encode_delta_step_decode(self, conv_out, a_proj, b_proj, a_log, dt_bias, state, y, command_buffer=None,
                                  conv_out_offset=0, a_proj_offset=0, b_proj_offset=0, a_log_offset=0,
                                  dt_bias_offset=0, state_offset=0, y_offset=0):
