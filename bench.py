@@ -264,20 +264,35 @@ class Workload:
         n_state = GV * GD * GD
         self.state_all = device_view(self.gdn_state.state_slot(1, 0), N_SESSIONS * n_state, torch.float32)
         self.state_all.normal_(0.0, 0.02, generator=gen)
-        self.q = torch.randn(N_SESSIONS, HQ * HD, device="cuda", generator=gen).half()
-        self.out = torch.empty(N_SESSIONS, HQ * HD, device="cuda", dtype=torch.float16)
         la = arch.linear_attention
+        # The step's inputs live in ONE device buffer and its outputs in another, so the end-to-end
+        # step moves them with a single host->device and a single device->host copy.
+        n_q, n_conv, n_g, n_kv = N_SESSIONS * HQ * HD, N_SESSIONS * la.qkv_dim, N_SESSIONS * GV, 2 * N_SESSIONS * self.row_elems
+        self.d_in = torch.empty(n_q + n_conv + 2 * n_g + n_kv, device="cuda", dtype=torch.float16)
+        o = 0
+        def take(n, shape):
+            nonlocal o
+            v = self.d_in[o:o + n].view(*shape); o += n
+            return v
+        self.q = take(n_q, (N_SESSIONS, HQ * HD))
+        self.conv = take(n_conv, (N_SESSIONS, la.qkv_dim))
+        self.a = take(n_g, (N_SESSIONS, GV))
+        self.b = take(n_g, (N_SESSIONS, GV))
+        self.d_newkv = take(n_kv, (2, N_SESSIONS, self.row_elems))
+        self.d_out = torch.empty(N_SESSIONS * (HQ * HD + GV * GD), device="cuda", dtype=torch.float16)
+        self.out = self.d_out[:N_SESSIONS * HQ * HD].view(N_SESSIONS, HQ * HD)
+        self.y = self.d_out[N_SESSIONS * HQ * HD:].view(N_SESSIONS, GV * GD)
+        self.q.copy_(torch.randn(N_SESSIONS, HQ * HD, device="cuda", generator=gen).half())
         qk = torch.randn(N_SESSIONS, 2 * GK, GD, device="cuda", generator=gen)
         qk = qk / qk.norm(dim=-1, keepdim=True)
         qk[:, :GK] *= GD ** -0.5
         vv = torch.randn(N_SESSIONS, GV * GD, device="cuda", generator=gen)
-        self.conv = torch.cat([qk.reshape(N_SESSIONS, -1), vv], dim=1).half().contiguous()
+        self.conv.copy_(torch.cat([qk.reshape(N_SESSIONS, -1), vv], dim=1).half())
         # g = sigmoid(n) and beta = sigmoid(n') through the raw parameters: A_log = 0, dt_bias = 0, a = -n
-        self.a = (-torch.randn(N_SESSIONS, GV, device="cuda", generator=gen)).half()
-        self.b = torch.randn(N_SESSIONS, GV, device="cuda", generator=gen).half()
+        self.a.copy_((-torch.randn(N_SESSIONS, GV, device="cuda", generator=gen)).half())
+        self.b.copy_(torch.randn(N_SESSIONS, GV, device="cuda", generator=gen).half())
         self.a_log = torch.zeros(GV, device="cuda", dtype=torch.bfloat16)
         self.dt_bias = torch.zeros(GV, device="cuda", dtype=torch.bfloat16)
-        self.y = torch.empty(N_SESSIONS, GV * GD, device="cuda", dtype=torch.float16)
         self.attn = tt.Attention(self.ctx)
         self.gdn = tt.GDN(self.ctx, la)
         esz = 2
@@ -293,14 +308,11 @@ class Workload:
         # rows of the KV store that receive each session's newest token (position S_i - 1)
         self.new_rows = torch.tensor([s * cap + n - 1 for s, n in enumerate(self.lens)], device="cuda")
         # pinned host side of the end-to-end step
-        pin = lambda t: torch.empty(t.shape, dtype=t.dtype).pin_memory().copy_(t.cpu())
-        self.h_q, self.h_conv, self.h_a, self.h_b = pin(self.q), pin(self.conv), pin(self.a), pin(self.b)
-        self.h_newkv = pin(torch.randn(2, N_SESSIONS, self.row_elems, device="cuda", generator=gen).half())
-        self.d_newkv = torch.empty(2, N_SESSIONS, self.row_elems, device="cuda", dtype=torch.float16)
-        self.h_out = torch.empty(self.out.shape, dtype=torch.float16).pin_memory()
-        self.h_y = torch.empty(self.y.shape, dtype=torch.float16).pin_memory()
-        self.h2d = sum(t.numel() * t.element_size() for t in (self.h_q, self.h_conv, self.h_a, self.h_b, self.h_newkv))
-        self.d2h = sum(t.numel() * t.element_size() for t in (self.h_out, self.h_y))
+        self.d_newkv.copy_(torch.randn(2, N_SESSIONS, self.row_elems, device="cuda", generator=gen).half())
+        self.h_in = torch.empty(self.d_in.shape, dtype=torch.float16).pin_memory().copy_(self.d_in.cpu())
+        self.h_out = torch.empty(self.d_out.shape, dtype=torch.float16).pin_memory()
+        self.h2d = self.h_in.numel() * 2
+        self.d2h = self.h_out.numel() * 2
         torch.cuda.synchronize()
 
     def step(self):
@@ -309,16 +321,11 @@ class Workload:
 
     def step_e2e(self):
         t = self.torch
-        self.q.copy_(self.h_q, non_blocking=True)
-        self.d_newkv.copy_(self.h_newkv, non_blocking=True)
+        self.d_in.copy_(self.h_in, non_blocking=True)                # q, conv/a/b rows, new K/V rows: one copy
         self.k_all.index_copy_(0, self.new_rows, self.d_newkv[0])   # the projection's write into kSlot/vSlot
         self.v_all.index_copy_(0, self.new_rows, self.d_newkv[1])
-        self.conv.copy_(self.h_conv, non_blocking=True)
-        self.a.copy_(self.h_a, non_blocking=True)
-        self.b.copy_(self.h_b, non_blocking=True)
         self.step()
-        self.h_out.copy_(self.out, non_blocking=True)
-        self.h_y.copy_(self.y, non_blocking=True)
+        self.h_out.copy_(self.d_out, non_blocking=True)              # attention rows and GDN y: one copy
         t.cuda.current_stream().synchronize()   # the caller reads the step's result
 
 

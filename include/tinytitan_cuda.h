@@ -82,8 +82,11 @@ int tt_ctx_profile_collect(tt_context *ctx, float *out_ms, uint32_t capacity, ui
 
 /* ------------------------------------------------- decode attention (SDPA) */
 
-/* KVView's format fields (KVCacheManager.swift:20-43). Only bits == 16 (fp16 or
- * bf16 rows) is implemented; 8 / 4 are refused with TT_ERR_UNSUPPORTED_SHAPE. */
+/* KVView's format fields (KVCacheManager.swift:20-43). bits 16 = fp16 rows; 8 / 4 =
+ * affine-quantised rows [packed codes | fp16 scale per 64-element group | fp16 bias per
+ * group] (KVCacheManager+Validation.swift:30-41), decoded as code*scale+bias
+ * (attn_load_kv, attention.metal:89-117). Quantised rows need head_dim 128 or 256,
+ * group_size 64, fp16 queries, 16-byte aligned strides, no keep mask and no ring. */
 typedef struct tt_kv_format {
     uint32_t bits;
     uint32_t stride_bytes; /* bytes per token row; 0 means n_kv_heads*head_dim*2 */
@@ -187,6 +190,15 @@ int tt_attn_plan_splits(const uint32_t *keys_per_session, const uint32_t *q_rows
                         uint32_t n_kv_heads, uint32_t sm_count, size_t workspace_bytes,
                         uint32_t *out_keys_per_item, uint32_t *out_n_items);
 
+/* Replaces kv_cache_quantize_affine
+ * (sources/TinyTitanCore/Metal/Quant/kv_cache_quantize.metal:4-72): fp16 rows
+ * [tokens][source_stride_elements] -> packed rows of destination_stride_bytes with the
+ * codes in the first values_bytes bytes, then one fp16 scale and one fp16 bias per group. */
+int tt_kv_quantize_affine(tt_context *ctx, tt_stream stream, const void *source, void *destination,
+                          uint32_t source_stride_elements, uint32_t destination_stride_bytes,
+                          uint32_t values_bytes, uint32_t element_count, uint32_t bits,
+                          uint32_t group_size, uint32_t tokens);
+
 /* ------------------------------------------------------- prefill attention */
 
 /* Field for field the reference's PrefillAttentionParams
@@ -204,7 +216,7 @@ typedef struct tt_prefill_params {
     uint32_t q_token_stride_elements;
     uint32_t o_token_stride_elements;
     float scale;
-    uint32_t kv_bits; /* 16 only */
+    uint32_t kv_bits; /* 16, or 8 / 4 (quantised rows run on the generic kernel) */
     uint32_t kv_token_stride_bytes;
     uint32_t kv_value_bytes;
     uint32_t kv_group_size;

@@ -344,3 +344,42 @@ class GDNChainReference:
                                          self.hk, self.hv, self.dk, self.dv, self.state)
         y = self._h(y[0])
         return self.gated_norm(y, z), y, normed
+
+
+# --------------------------------------------------------------------------
+# affine KV quantisation (numpy). Follows
+# sources/TinyTitanCore/Metal/Quant/kv_cache_quantize.metal:4-72 (bias = group min, scale =
+# (max-min)/levels in fp32, code = round-half-away(clamp((x-bias)/scale)), fp16 scale/bias stored
+# after the packed codes) and the loader attn_load_kv (attention.metal:89-117).
+# --------------------------------------------------------------------------
+def kv_quantize_rows(rows, bits: int, group_size: int = 64):
+    """rows fp32 [tokens, elements] (fp16-representable). Returns (packed uint8 rows, dequantised fp32)."""
+    x = _f(rows)
+    tokens, n = x.shape
+    groups = (n + group_size - 1) // group_size
+    packed_bytes = (n * bits + 7) // 8
+    value_bytes = (packed_bytes + 1) & ~1
+    stride = value_bytes + groups * 4
+    levels = np.float32(15 if bits == 4 else 255)
+    out = np.zeros((tokens, stride), np.uint8)
+    deq = np.zeros_like(x)
+    for g in range(groups):
+        sl = x[:, g * group_size:(g + 1) * group_size]
+        mn, mx = sl.min(1, keepdims=True), sl.max(1, keepdims=True)
+        scale = np.where(mx > mn, (mx - mn) / levels, np.float32(0)).astype(np.float32)
+        safe = np.where(scale > 0, scale, np.float32(1))
+        q = np.where(scale > 0, np.floor(np.clip((sl - mn) / safe, 0, levels).astype(np.float32) + np.float32(0.5)), 0)
+        q = q.astype(np.uint8)
+        s16, b16 = scale.astype(np.float16), mn.astype(np.float16)
+        out[:, value_bytes + 2 * g:value_bytes + 2 * g + 2] = s16.view(np.uint8).reshape(tokens, 2)
+        out[:, value_bytes + 2 * (groups + g):value_bytes + 2 * (groups + g) + 2] = b16.view(np.uint8).reshape(tokens, 2)
+        deq[:, g * group_size:(g + 1) * group_size] = q.astype(np.float32) * s16.astype(np.float32) + b16.astype(np.float32)
+        cols = np.arange(g * group_size, min(n, (g + 1) * group_size))
+        if bits == 8:
+            out[:, cols] = q
+        else:
+            lo, hi = q[:, 0::2], q[:, 1::2]
+            byte = lo.copy()
+            byte[:, :hi.shape[1]] |= (hi << 4)
+            out[:, cols[0] // 2:cols[0] // 2 + byte.shape[1]] = byte
+    return out, deq, stride, value_bytes

@@ -173,5 +173,5 @@ def test_validation_errors():
                 dict(kv_bits=5)):
         with pytest.raises(tt.InvalidArgument):
             pa.encode_causal(x, x, x, x, tt.PrefillAttentionParams(**{**ok, **bad}))
-    with pytest.raises(tt.UnsupportedShape):
+    with pytest.raises(tt.InvalidArgument):   # quantised stride without room for the values and groups
         pa.encode_causal(x, x, x, x, tt.PrefillAttentionParams(**{**ok, "kv_bits": 8, "kv_token_stride_bytes": 72}))

@@ -119,6 +119,7 @@ SIGNATURES = {
     "tt_attn_reference_split_geometry": (None, [_u32, _u32, _u32, _u32, C.c_int, C.POINTER(SplitGeometry)]),
     "tt_attn_plan_splits": (C.c_int, [C.POINTER(_u32), C.POINTER(_u32), _u32, _u32, _u32, _u32, _u32, C.c_size_t,
                                       C.POINTER(_u32), C.POINTER(_u32)]),
+    "tt_kv_quantize_affine": (C.c_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32]),
     "tt_attn_prefill_causal": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(PrefillParams), _u32, _u32]),
     "tt_attn_prefill_path": (C.c_int, [_vp, _vp, _vp, _vp, C.POINTER(PrefillParams), _u32]),
     "tt_gdn_step": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(GdnShape), _u32, _u32, _vp]),

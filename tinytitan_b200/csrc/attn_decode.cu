@@ -399,6 +399,335 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
     }
 }
 
+// Shared memory of the quantised-KV variant: a ring of RAW rows (this head's packed values followed by
+// the row's scale/bias block), plus one private fp16 tile pair per warp holding the dequantised halves.
+template <int HD, int BITS>
+struct QuantSmem {
+    static constexpr int kValBytes = HD * BITS / 8;                // packed values of one head in a row
+    static constexpr int kRowBytes = kValBytes + 64;               // + up to 64 B of scales and biases
+    static constexpr int kTileBytes = kKeysPerBlock * kRowBytes;   // K (or V) raw block
+    static constexpr int kStageBytes = 2 * kTileBytes;
+    static constexpr int kRingBytes = kStages * kStageBytes;
+    static constexpr int kHalfRowBytes = (HD / 2 + 8) * 2;         // fp16 half-row, padded for ldmatrix
+    static constexpr int kHalfTileBytes = kKeysPerBlock * kHalfRowBytes;
+    static constexpr int kWarpTileBytes = 2 * kHalfTileBytes;      // K half + V half
+    static constexpr int kXchgBytes = 2 * 2 * 32 * 9 * 4;
+    static constexpr int kTotal = kRingBytes + 2 * kWarpTileBytes + kXchgBytes + 64;
+};
+
+// ---------------------------------------------------------------------------------------
+// Pass 1 over affine-quantised K/V rows (8 or 4 bits, 64-element groups, fp16 scale and bias
+// stored after the packed values of each row: KVCacheManager.rowLayout,
+// KVCacheManager+Validation.swift:30-41; loader semantics attn_load_kv, attention.metal:89-117).
+// Same structure as the fp16 kernel above; the ring carries the raw rows (half or a quarter of
+// the bytes), and each warp dequantises its own head-dim halves of the landed K and V block into
+// private fp16 tiles before the MMAs: value = code * scale + bias in fp32, rounded to fp16.
+// ---------------------------------------------------------------------------------------
+template <int HD, int BITS>
+__global__ void __launch_bounds__(64, 4)
+attn_decode_partial_quant_kernel(const TTDecodeItem *__restrict__ items,
+                           const TTDecodeSession *__restrict__ sessions, float *__restrict__ part_o,
+                           float *__restrict__ part_m, float *__restrict__ part_l,
+                           uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t kv_stride_bytes,
+                           uint32_t q_row_stride, float scale_log2, uint32_t *__restrict__ status,
+                           const TTDecodeSession single, uint32_t single_keys_per_item, uint32_t value_bytes,
+                           uint32_t meta_bytes) {
+    using T = __half;
+    using S = QuantSmem<HD, BITS>;
+    constexpr int HH = HD / 2;          // head-dim half per warp
+    constexpr int KS = HH / 16;         // k-steps of the partial Q.K^T
+    constexpr int NT = HH / 8;          // n-tiles of this warp's half of O
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const uint32_t group = n_q_heads / n_kv_heads;
+    // One-session calls carry the session in the kernel parameters and derive the work item from
+    // the block index (all items are equal slices), so no table has to be copied to the device.
+    TTDecodeItem item;
+    TTDecodeSession ses;
+    if (single_keys_per_item != 0) {
+        ses = single;
+        const uint32_t packed_rows = ses.q_rows * group;
+        const uint32_t row_tiles = (packed_rows + 15) / 16;
+        const uint32_t rt = blockIdx.x % row_tiles, kvh = (blockIdx.x / row_tiles) % n_kv_heads;
+        const uint32_t part = blockIdx.x / (row_tiles * n_kv_heads);
+        item.session = 0; item.kv_head = kvh; item.part_index = part; item.partial_base = 0;
+        item.key_begin = min(ses.seq_len, ses.kv_start + part * single_keys_per_item);
+        item.key_end = min(ses.seq_len, item.key_begin + single_keys_per_item);
+        item.row_begin = rt * 16;
+        item.row_count = min(16u, packed_rows - rt * 16);
+    } else {
+        item = items[blockIdx.x];
+        ses = sessions[item.session];
+    }
+
+    unsigned char *ring = smem;                                   // raw (quantised) K/V rows, 3 stages
+    unsigned char *tiles = smem + S::kRingBytes + warp * S::kWarpTileBytes;   // this warp's fp16 K and V halves
+    float *xchg = reinterpret_cast<float *>(smem + S::kRingBytes + 2 * S::kWarpTileBytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::kRingBytes + 2 * S::kWarpTileBytes + S::kXchgBytes);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+
+    // ---- this warp's half of the Q tile, straight into mma A fragments ----
+    uint32_t qf[KS][4];
+    {
+        const uint32_t r0 = lane >> 2, r1 = r0 + 8;
+        const T *q0 = nullptr, *q1 = nullptr;
+        if (r0 < item.row_count) {
+            const uint32_t packed = item.row_begin + r0;
+            q0 = reinterpret_cast<const T *>(ses.q) + (size_t)(packed / group) * q_row_stride +
+                 (size_t)(item.kv_head * group + packed % group) * HD + warp * HH + (lane & 3) * 2;
+        }
+        if (r1 < item.row_count) {
+            const uint32_t packed = item.row_begin + r1;
+            q1 = reinterpret_cast<const T *>(ses.q) + (size_t)(packed / group) * q_row_stride +
+                 (size_t)(item.kv_head * group + packed % group) * HD + warp * HH + (lane & 3) * 2;
+        }
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qf[ks][0] = q0 ? *reinterpret_cast<const uint32_t *>(q0 + ks * 16) : 0u;
+            qf[ks][1] = q1 ? *reinterpret_cast<const uint32_t *>(q1 + ks * 16) : 0u;
+            qf[ks][2] = q0 ? *reinterpret_cast<const uint32_t *>(q0 + ks * 16 + 8) : 0u;
+            qf[ks][3] = q1 ? *reinterpret_cast<const uint32_t *>(q1 + ks * 16 + 8) : 0u;
+        }
+    }
+
+    const uint32_t n_keys = item.key_end - item.key_begin;
+    const uint32_t n_blocks = (n_keys + kKeysPerBlock - 1) / kKeysPerBlock;
+    // a key's row: [packed values of all heads | fp16 scale per 64-element group | fp16 bias per group]
+    const unsigned char *kbase = reinterpret_cast<const unsigned char *>(ses.k);
+    const unsigned char *vbase = reinterpret_cast<const unsigned char *>(ses.v);
+    const uint32_t head_value_offset = item.kv_head * S::kValBytes;
+    const uint32_t groups_total = n_kv_heads * HD / 64;
+
+    auto block_valid = [&](uint32_t i) {
+        return min((uint32_t)kKeysPerBlock, n_keys - i * kKeysPerBlock);
+    };
+    // thread 0 announces the bytes of block i; ordered before the copies by a barrier
+    auto announce = [&](uint32_t i) {
+        mbar_expect_tx(&bars[i % kStages], block_valid(i) * 2u * (uint32_t)(S::kValBytes + meta_bytes));
+    };
+    // warp 0 fetches the K rows of block i, warp 1 the V rows (lanes 0..15, one row each)
+    auto issue = [&](uint32_t i) {
+        if (lane < kKeysPerBlock) {
+            const uint32_t valid = block_valid(i);
+            unsigned char *dst = ring + (i % kStages) * S::kStageBytes + warp * S::kTileBytes + lane * S::kRowBytes;
+            if ((uint32_t)lane < valid) {
+                uint32_t p = item.key_begin + i * kKeysPerBlock + lane;
+                if (ses.ring_capacity) p %= ses.ring_capacity;
+                const unsigned char *src = (warp ? vbase : kbase) + (size_t)p * kv_stride_bytes;
+                bulk_copy_g2s(dst, src + head_value_offset, S::kValBytes, &bars[i % kStages]);
+                bulk_copy_g2s(dst + S::kValBytes, src + value_bytes, meta_bytes, &bars[i % kStages]);
+            }
+        }
+    };
+
+    float m_run[2] = {-INFINITY, -INFINITY};
+    float l_run[2] = {0.f, 0.f};
+    float acc[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
+
+    // visible-key limit of the two rows this thread owns; rows past row_count are never
+    // written, so they take the tile's smallest limit and need no masking of their own
+    const uint32_t w_first = item.row_begin / group;
+    const uint32_t limit_min = ses.seq_len - (ses.q_rows - 1 - w_first);
+    uint32_t limit[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t r = (lane >> 2) + 8 * h;
+        limit[h] = r < item.row_count ? ses.seq_len - (ses.q_rows - 1 - (item.row_begin + r) / group) : limit_min;
+    }
+
+    const uint32_t prologue = min(n_blocks, (uint32_t)(kStages - 1));
+    if (threadIdx.x == 0)
+        for (uint32_t i = 0; i < prologue; ++i) announce(i);
+    __syncthreads();
+    for (uint32_t i = 0; i < prologue; ++i) issue(i);
+
+    bool timed_out = false;
+    const uint32_t k_off = ((lane & 7) + ((lane >> 4) << 3)) * S::kHalfRowBytes + ((lane >> 3) & 1) * 16;
+    const uint32_t v_off = S::kHalfTileBytes + ((lane & 7) + ((lane >> 3) & 1) * 8) * S::kHalfRowBytes + (lane >> 4) * 16;
+    // dequantisation duty of this lane: key lane/2, E = HH/2 consecutive elements of this warp's half
+    constexpr int E = HH / 2;
+    const uint32_t dq_key = lane >> 1, dq_sub = lane & 1;
+    const uint32_t dq_group = (item.kv_head * HD + warp * HH + dq_sub * E) / 64;
+    const uint32_t dq_src = dq_key * S::kRowBytes + (warp * HH + dq_sub * E) * BITS / 8;
+    const uint32_t dq_dst = dq_key * S::kHalfRowBytes + dq_sub * E * 2;
+
+    for (uint32_t i = 0; i < n_blocks; ++i) {
+        const uint32_t nxt = i + kStages - 1;
+        if (threadIdx.x == 0 && nxt < n_blocks) announce(nxt);
+        const bool got = __all_sync(0xffffffffu, mbar_wait(&bars[i % kStages], (i / kStages) & 1)) != 0;
+
+        // ---- dequantise this warp's halves of the landed K and V rows into its fp16 tiles ----
+        if (got) {
+            const uint32_t valid = block_valid(i);
+#pragma unroll
+            for (int kv = 0; kv < 2; ++kv) {
+                const unsigned char *raw = ring + (i % kStages) * S::kStageBytes + kv * S::kTileBytes;
+                unsigned char *dst = tiles + kv * S::kHalfTileBytes + dq_dst;
+                if (dq_key < valid) {
+                    const unsigned char *row = raw + dq_key * S::kRowBytes;
+                    const float sc = __half2float(*reinterpret_cast<const __half *>(row + S::kValBytes + dq_group * 2));
+                    const float bi = __half2float(*reinterpret_cast<const __half *>(row + S::kValBytes + (groups_total + dq_group) * 2));
+                    const unsigned char *src = raw + dq_src;
+#pragma unroll
+                    for (int c = 0; c < E * BITS / 8 / 16; ++c) {
+                        const uint4 pk = *reinterpret_cast<const uint4 *>(src + c * 16);
+                        const uint32_t wds[4] = {pk.x, pk.y, pk.z, pk.w};
+                        if constexpr (BITS == 8) {
+                            uint32_t o[8];
+#pragma unroll
+                            for (int q4 = 0; q4 < 4; ++q4) {
+                                const uint32_t u = wds[q4];
+                                o[2 * q4] = pack2<__half>(fmaf((float)(u & 0xffu), sc, bi), fmaf((float)((u >> 8) & 0xffu), sc, bi));
+                                o[2 * q4 + 1] = pack2<__half>(fmaf((float)((u >> 16) & 0xffu), sc, bi), fmaf((float)(u >> 24), sc, bi));
+                            }
+                            reinterpret_cast<uint4 *>(dst)[2 * c] = make_uint4(o[0], o[1], o[2], o[3]);
+                            reinterpret_cast<uint4 *>(dst)[2 * c + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+                        } else {
+                            uint32_t o[16];
+#pragma unroll
+                            for (int q4 = 0; q4 < 4; ++q4) {
+                                const uint32_t u = wds[q4];
+#pragma unroll
+                                for (int b2 = 0; b2 < 4; ++b2) {   // byte b2: low nibble = even element, high = odd
+                                    const uint32_t byte = (u >> (8 * b2)) & 0xffu;
+                                    o[4 * q4 + b2] = pack2<__half>(fmaf((float)(byte & 0xfu), sc, bi), fmaf((float)(byte >> 4), sc, bi));
+                                }
+                            }
+#pragma unroll
+                            for (int v4 = 0; v4 < 4; ++v4)
+                                reinterpret_cast<uint4 *>(dst)[4 * c + v4] = make_uint4(o[4 * v4], o[4 * v4 + 1], o[4 * v4 + 2], o[4 * v4 + 3]);
+                        }
+                    }
+                } else {
+                    // keys past the end of the item: finite zeros (their scores are masked, P is 0)
+                    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                    for (int c = 0; c < E * 2 / 16; ++c) reinterpret_cast<uint4 *>(dst)[c] = z;
+                }
+            }
+        }
+        __syncwarp();
+        const uint32_t stage = smem_u32(tiles);
+        // ---- partial S over this warp's head-dim half: two independent chains per n-tile ----
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+        float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < KS; ks += 2) {
+            uint32_t b[4], c[4];
+            ldmatrix_x4(b, stage + k_off + ks * 32);
+            ldmatrix_x4(c, stage + k_off + (ks + 1) * 32);
+            mma_16816<T>(s0, qf[ks], b[0], b[1]);
+            mma_16816<T>(s1, qf[ks], b[2], b[3]);
+            mma_16816<T>(t0, qf[ks + 1], c[0], c[1]);
+            mma_16816<T>(t1, qf[ks + 1], c[2], c[3]);
+        }
+        float *mine = xchg + (((i & 1) * 2 + warp) * 32 + lane) * 9;
+        const float *theirs = xchg + (((i & 1) * 2 + (warp ^ 1)) * 32 + lane) * 9;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { mine[j] = s0[j] + t0[j]; mine[4 + j] = s1[j] + t1[j]; }
+        mine[8] = got ? 1.f : 0.f;
+        pair_barrier();
+        if (!(got && theirs[8] != 0.f)) { timed_out = true; break; }   // same decision in both warps
+        float sv[2][4];  // [row half][key: n0c0 n0c1 n1c0 n1c1]
+        sv[0][0] = mine[0] + theirs[0]; sv[0][1] = mine[1] + theirs[1];
+        sv[1][0] = mine[2] + theirs[2]; sv[1][1] = mine[3] + theirs[3];
+        sv[0][2] = mine[4] + theirs[4]; sv[0][3] = mine[5] + theirs[5];
+        sv[1][2] = mine[6] + theirs[6]; sv[1][3] = mine[7] + theirs[7];
+
+        // every lane of the pair is past block i-1 now: its stage may be refilled
+        if (nxt < n_blocks) issue(nxt);
+
+        // ---- mask + online softmax (identical in both warps) ----
+        const uint32_t blk_key0 = item.key_begin + i * kKeysPerBlock;
+        const bool plain = (blk_key0 + kKeysPerBlock <= limit_min) && (blk_key0 + kKeysPerBlock <= item.key_end) &&
+                           (ses.keep == nullptr);
+        float alpha[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float s = sv[h][j] * scale_log2;
+                if (!plain) {
+                    const uint32_t key = blk_key0 + (lane & 3) * 2 + (j >> 1) * 8 + (j & 1);
+                    bool ok = key < limit[h] && key < item.key_end;
+                    if (ok && ses.keep != nullptr) ok = ses.keep[key] != 0;
+                    s = ok ? s : -INFINITY;
+                }
+                sv[h][j] = s;
+                mx = fmaxf(mx, s);
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run[h], mx);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            alpha[h] = fast_exp2(m_run[h] - m_use);
+            m_run[h] = m_new;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sv[h][j] = fast_exp2(sv[h][j] - m_use);
+        }
+        uint32_t pa[4];
+        pa[0] = pack2<T>(sv[0][0], sv[0][1]);
+        pa[1] = pack2<T>(sv[1][0], sv[1][1]);
+        pa[2] = pack2<T>(sv[0][2], sv[0][3]);
+        pa[3] = pack2<T>(sv[1][2], sv[1][3]);
+        // row sums from the ROUNDED weights the MMA consumes: O / l stays a convex combination
+        l_run[0] = l_run[0] * alpha[0] + sum2<T>(pa[0]) + sum2<T>(pa[2]);
+        l_run[1] = l_run[1] * alpha[1] + sum2<T>(pa[1]) + sum2<T>(pa[3]);
+
+        if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                acc[n][0] *= alpha[0]; acc[n][1] *= alpha[0];
+                acc[n][2] *= alpha[1]; acc[n][3] *= alpha[1];
+            }
+        }
+
+        // ---- O(own half) += P V ----
+#pragma unroll
+        for (int np = 0; np < NT / 2; ++np) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, stage + v_off + np * 32);
+            mma_16816<T>(acc[2 * np], pa, b[0], b[1]);
+            mma_16816<T>(acc[2 * np + 1], pa, b[2], b[3]);
+        }
+    }
+
+    if (timed_out && lane == 0) atomicOr(status, TT_DEV_WAIT_TIMEOUT);
+
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+
+    // ---- write the partial: this warp's half of O, and (warp 0) m and l ----
+    const uint32_t rows_total = ses.q_rows * n_q_heads;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t r = (lane >> 2) + 8 * h;
+        if (r >= item.row_count) continue;
+        const uint32_t packed = item.row_begin + r;
+        const uint32_t rho = (packed / group) * n_q_heads + item.kv_head * group + packed % group;
+        const size_t prow = (size_t)ses.partial_base + (size_t)item.part_index * rows_total + rho;
+        float *dst = part_o + prow * HD + warp * HH + (lane & 3) * 2;
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+            *reinterpret_cast<float2 *>(dst + n * 8) = make_float2(acc[n][2 * h], acc[n][2 * h + 1]);
+        if (warp == 0 && (lane & 3) == 0) {
+            part_m[prow] = m_run[h] * kLn2;   // natural-log domain, the reference's partial format
+            part_l[prow] = l_run[h];
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // Pass 2. grid = (sessions, rows per session), block = HD/4 threads (one float4 column each).
 // mode 0: normalised output in the I/O dtype; mode 1: merged unnormalised (m, d, o) triple.
@@ -535,6 +864,32 @@ cudaError_t launch_partial(cudaStream_t stream, uint32_t n_items, const TTDecode
     return cudaGetLastError();
 }
 
+template <int HD, int BITS>
+cudaError_t launch_partial_quant_one(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
+                                     const TTDecodeSession *sessions, float *part_o, float *part_m, float *part_l,
+                                     const tt_attn_batch_params *p, uint32_t *status, const TTDecodeSession &single,
+                                     uint32_t single_keys, const TTKvQuant *quant, uint32_t meta_bytes) {
+    auto kernel = attn_decode_partial_quant_kernel<HD, BITS>;
+    const int smem = QuantSmem<HD, BITS>::kTotal;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    kernel<<<n_items, 64, smem, stream>>>(items, sessions, part_o, part_m, part_l, p->n_q_heads, p->n_kv_heads,
+                                          quant->stride_bytes, p->q_row_stride_elements, p->scale * kLog2e, status,
+                                          single, single_keys, quant->value_bytes, meta_bytes);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_partial_quant(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
+                                 const TTDecodeSession *sessions, float *part_o, float *part_m, float *part_l,
+                                 const tt_attn_batch_params *p, uint32_t *status, const TTDecodeSession &single,
+                                 uint32_t single_keys, const TTKvQuant *quant, uint32_t meta_bytes) {
+#define TT_Q(HD, BITS) launch_partial_quant_one<HD, BITS>(stream, n_items, items, sessions, part_o, part_m, part_l, p, \
+                                                          status, single, single_keys, quant, meta_bytes)
+    if (p->head_dim == 256) return quant->bits == 8 ? TT_Q(256, 8) : TT_Q(256, 4);
+    return quant->bits == 8 ? TT_Q(128, 8) : TT_Q(128, 4);
+#undef TT_Q
+}
+
 template <typename T>
 cudaError_t launch_partial_hd(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
                               const TTDecodeSession *sessions, float *part_o, float *part_m,
@@ -630,7 +985,7 @@ TT_API void tt_attn_reference_split_geometry(uint32_t n_q_heads, uint32_t n_kv_h
 // single session (m_out/d_out/o_out).
 int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession *in_sessions,
                      uint32_t n_sessions, const tt_attn_batch_params *p, int mode, float *m_out,
-                     float *d_out, float *o_out) {
+                     float *d_out, float *o_out, const TTKvQuant *quant) {
     if (n_sessions == 0) return TT_OK;
     if (n_sessions > ctx->max_sessions)
         return tt_set_error(ctx, TT_ERR_INVALID_ARG, "n_sessions %u exceeds the context's max_sessions %u",
@@ -642,7 +997,23 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
                             p->head_dim);
     if (p->io_dtype != TT_F16 && p->io_dtype != TT_BF16)
         return tt_set_error(ctx, TT_ERR_INVALID_ARG, "io_dtype must be TT_F16 or TT_BF16");
-    if (p->kv_token_stride_elements < p->n_kv_heads * p->head_dim ||
+    const bool quantised = quant != nullptr && quant->bits != 16;
+    uint32_t meta_bytes = 0;
+    if (quantised) {
+        if (quant->bits != 8 && quant->bits != 4) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "KV bits must be 4, 8, or 16");
+        if (p->head_dim != 128 && p->head_dim != 256)
+            return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "quantised KV rows need head_dim 128 or 256");
+        if (p->io_dtype != TT_F16) return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "quantised KV rows need fp16 queries");
+        const uint32_t groups = p->n_kv_heads * p->head_dim / 64;
+        meta_bytes = (groups * 4 + 15) / 16 * 16;
+        const uint32_t packed = p->n_kv_heads * p->head_dim * quant->bits / 8;
+        if (meta_bytes > 64 || quant->value_bytes != packed || quant->value_bytes % 16 != 0 ||
+            quant->stride_bytes % 16 != 0 || quant->stride_bytes < quant->value_bytes + meta_bytes)
+            return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE,
+                                "quantised KV row layout not supported (stride %u, values %u, %u groups)",
+                                quant->stride_bytes, quant->value_bytes, groups);
+    }
+    if ((!quantised && p->kv_token_stride_elements < p->n_kv_heads * p->head_dim) ||
         p->q_row_stride_elements < p->n_q_heads * p->head_dim ||
         p->out_row_stride_elements < p->n_q_heads * p->head_dim)
         return tt_set_error(ctx, TT_ERR_INVALID_ARG, "a row stride is smaller than its tight width");
@@ -725,7 +1096,10 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
 
     const bool timed = ctx->profiling && ctx->profile_count < tt_context::kProfileSlots;
     if (timed) cudaEventRecord(ctx->profile_begin[ctx->profile_count], stream);
-    if (p->io_dtype == TT_F16)
+    if (quantised)
+        e = launch_partial_quant(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status,
+                                 single_ses, single_keys, quant, meta_bytes);
+    else if (p->io_dtype == TT_F16)
         e = launch_partial_hd<__half>(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status,
                                       single_ses, single_keys);
     else
@@ -782,10 +1156,17 @@ TT_API int tt_attn_decode(tt_context *ctx, tt_stream stream, const void *q, cons
         return tt_set_error(ctx, TT_ERR_INVALID_ARG, "n_q_heads must be a multiple of n_kv_heads for GQA");
     if (n_q_heads > 96) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "n_q_heads exceeds 96");
     uint32_t stride_elems = n_kv_heads * head_dim;
+    TTKvQuant quant;
     if (kv_format != nullptr) {
-        if (kv_format->bits != 16)
-            return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "quantised KV rows (%u bits) are not implemented",
-                                kv_format->bits);
+        if (kv_format->bits != 16 && kv_format->bits != 8 && kv_format->bits != 4)
+            return tt_set_error(ctx, TT_ERR_INVALID_ARG, "KV bits must be 4, 8, or 16");
+        if (kv_format->bits != 16) {
+            if (keep_mask != nullptr || ring_capacity != 0)
+                return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "quantised KV rows with a keep mask or ring are not implemented");
+            if (kv_format->group_size != 64)
+                return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "quantisation group size must be 64");
+            quant.bits = kv_format->bits; quant.stride_bytes = kv_format->stride_bytes; quant.value_bytes = kv_format->value_bytes;
+        }
         if (kv_format->stride_bytes != 0) {
             if (kv_format->stride_bytes % 2) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "odd KV stride");
             stride_elems = kv_format->stride_bytes / 2;
@@ -799,7 +1180,7 @@ TT_API int tt_attn_decode(tt_context *ctx, tt_stream stream, const void *q, cons
     s.q = q; s.out = out; s.k = k; s.v = v; s.seq_len = seq_len; s.q_rows = 1;
     s.kv_start = kv_start < seq_len ? kv_start : seq_len;
     s.n_parts = 0; s.partial_base = 0; s.ring_capacity = ring_capacity; s.keep = keep_mask;
-    return tt_launch_decode(ctx, (cudaStream_t)stream, &s, 1, &p, 0, nullptr, nullptr, nullptr);
+    return tt_launch_decode(ctx, (cudaStream_t)stream, &s, 1, &p, 0, nullptr, nullptr, nullptr, &quant);
 }
 
 TT_API int tt_attn_decode_partial(tt_context *ctx, tt_stream stream, const void *q, const void *k,

@@ -29,6 +29,28 @@ __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2hal
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
+// Element `flat` of a cache row: fp16/bf16 rows directly, affine-quantised rows as
+// code * scale[group] + bias[group] with the scales and biases stored after the packed codes
+// (attn_load_kv, sources/TinyTitanCore/Metal/Attention/attention.metal:89-117;
+// prefill.metal:772-797).
+template <typename T>
+__device__ __forceinline__ float load_kv(const T *cache, uint32_t row, uint32_t flat, const tt_prefill_params &p) {
+    if (p.kv_bits == 16) return to_f32<T>(cache[(size_t)row * p.kv_token_stride_elements + flat]);
+    const unsigned char *r = reinterpret_cast<const unsigned char *>(cache) + (size_t)row * p.kv_token_stride_bytes;
+    uint32_t code;
+    if (p.kv_bits == 8) {
+        code = r[flat];
+    } else {
+        const unsigned char packed = r[flat >> 1];
+        code = (flat & 1u) ? (packed >> 4) : (packed & 0x0fu);
+    }
+    const uint32_t elems = p.n_kv_heads * p.head_dim;
+    const uint32_t groups = (elems + p.kv_group_size - 1) / p.kv_group_size;
+    const __half *scales = reinterpret_cast<const __half *>(r + p.kv_value_bytes);
+    const uint32_t g = flat / p.kv_group_size;
+    return (float)code * __half2float(scales[g]) + __half2float(scales[groups + g]);
+}
+
 // One warp per (query row, q head). Keys are taken 32 at a time: lane j scores key j (a full
 // head_dim dot product against the query held in shared memory), the tile's softmax update is
 // done with warp reductions, then every lane accumulates its own output dimensions over the
@@ -64,9 +86,13 @@ attn_prefill_generic_kernel(const T *__restrict__ q, const T *__restrict__ k, co
         float s = -INFINITY;
         if (key < last) {
             const uint32_t phys = ring ? key % ring : key;
-            const T *kr = k + (size_t)phys * p.kv_token_stride_elements + (size_t)kvh * hd;
             float dot = 0.f;
-            for (uint32_t d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], to_f32<T>(kr[d]), dot);
+            if (p.kv_bits == 16) {
+                const T *kr = k + (size_t)phys * p.kv_token_stride_elements + (size_t)kvh * hd;
+                for (uint32_t d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], to_f32<T>(kr[d]), dot);
+            } else {
+                for (uint32_t d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], load_kv<T>(k, phys, kvh * hd + d, p), dot);
+            }
             s = dot;
         }
         float mx = s;
@@ -87,11 +113,10 @@ attn_prefill_generic_kernel(const T *__restrict__ q, const T *__restrict__ k, co
             const float pj = __shfl_sync(0xffffffffu, pe, j);
             const uint32_t kj = key0 + j;
             const uint32_t phys = ring ? kj % ring : kj;
-            const T *vr = v + (size_t)phys * p.kv_token_stride_elements + (size_t)kvh * hd;
 #pragma unroll
             for (int i = 0; i < kPerLane; ++i) {
                 const uint32_t d = lane + 32 * i;
-                if (d < hd) acc[i] = fmaf(pj, to_f32<T>(vr[d]), acc[i]);
+                if (d < hd) acc[i] = fmaf(pj, load_kv<T>(v, phys, kvh * hd + d, p), acc[i]);
             }
         }
     }
@@ -122,11 +147,15 @@ int validate_prefill(tt_context *ctx, const void *q, const void *k, const void *
     if (p->kv_bits != 16) {
         if (p->kv_bits != 4 && p->kv_bits != 8)
             return tt_set_error(ctx, TT_ERR_INVALID_ARG, "KV bits must be 4, 8, or 16");
-        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "quantised KV rows (%u bits) are not implemented",
-                            p->kv_bits);
-    }
-    if (p->kv_token_stride_elements < p->n_kv_heads * p->head_dim)
+        if (p->kv_token_stride_bytes == 0)
+            return tt_set_error(ctx, TT_ERR_INVALID_ARG, "quantized KV token stride must be positive");
+        const uint32_t elems = p->n_kv_heads * p->head_dim;
+        if (p->kv_group_size == 0 || p->kv_value_bytes < (elems * p->kv_bits + 7) / 8 ||
+            p->kv_token_stride_bytes < p->kv_value_bytes + (elems + p->kv_group_size - 1) / p->kv_group_size * 4)
+            return tt_set_error(ctx, TT_ERR_INVALID_ARG, "quantized KV row layout is too small for its values and groups");
+    } else if (p->kv_token_stride_elements < p->n_kv_heads * p->head_dim) {
         return tt_set_error(ctx, TT_ERR_INVALID_ARG, "KV token stride is too small");
+    }
     if ((uint64_t)p->start_position + p->query_count > p->kv_valid_count)
         return tt_set_error(ctx, TT_ERR_INVALID_ARG, "kvValidCount must include all in-flight query rows");
     if (p->head_dim > (uint32_t)kMaxHeadDim)

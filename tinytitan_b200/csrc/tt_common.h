@@ -105,7 +105,14 @@ struct TTPlan {
     uint32_t n_partial_rows;
 };
 
+// Affine-quantised KV rows (8 or 4 bits); bits == 16 means plain fp16/bf16 rows.
+struct TTKvQuant {
+    uint32_t bits = 16;
+    uint32_t stride_bytes = 0;   // bytes per token row
+    uint32_t value_bytes = 0;    // packed values of the whole row; scales and biases follow
+};
+
 // Launchers implemented in the .cu files.
 int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession *h_sessions,
                      uint32_t n_sessions, const tt_attn_batch_params *p, int mode,
-                     float *m_out, float *d_out, float *o_out);
+                     float *m_out, float *d_out, float *o_out, const TTKvQuant *quant = nullptr);

@@ -236,6 +236,19 @@ class Attention:
             head_dim, _addr(out), io_dtype if io_dtype is not None else _dtype_of(out)))
 
 
+def quantize_kv_rows(context: Context, source, destination, element_count: int, bits: int, tokens: int,
+                     source_stride_elements=None, destination_stride_bytes=None, values_bytes=None, group_size=64,
+                     command_buffer=None, source_offset=0, destination_offset=0):
+    """kv_cache_quantize_affine: fp16 rows -> the cache's packed row format (codes, scales, biases)."""
+    packed = (element_count * bits + 7) // 8
+    vb = values_bytes if values_bytes is not None else (packed + 1) & ~1
+    groups = (element_count + group_size - 1) // group_size
+    context.check(L.lib().tt_kv_quantize_affine(
+        context.handle, _stream(command_buffer), _addr(source, source_offset), _addr(destination, destination_offset),
+        source_stride_elements or element_count, destination_stride_bytes or vb + groups * 4, vb, element_count, bits,
+        group_size, tokens))
+
+
 @dataclass
 class PrefillAttentionParams:
     """PrefillAttentionParams (PrefillAttention.swift:5-55), same fields and defaults."""
