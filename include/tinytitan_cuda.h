@@ -199,6 +199,23 @@ int tt_kv_quantize_affine(tt_context *ctx, tt_stream stream, const void *source,
                           uint32_t values_bytes, uint32_t element_count, uint32_t bits,
                           uint32_t group_size, uint32_t tokens);
 
+/* The elementwise step before full-attention SDPA in the gated-attention layer, one launch for
+ * the reference's five (RealForwardRunner.encodeGatedFullPostProjection,
+ * sources/TinyTitan/Runtime/Inference/RealForwardRunner+DecodeFullAttention.swift:123-185):
+ * split per-head [query ; gate] (split_q_gate_fp16, Primitives/utility.metal:142-160), per-head
+ * RMS norm of q and of the just-written K rows with bf16 weights (rmsnorm_bf16w_perhead,
+ * Primitives/rmsnorm.metal:101-128), NeoX partial RoPE over the first rotary_dim elements
+ * (rope_neox_subdim, Primitives/rope.metal:80-108). q_packed fp16 [rows][H][2D]; q_out, gate_out
+ * fp16 [rows][H][D]; K row r ([Hkv][D], in place) at k_rows + r*k_row_stride_elements; row r is at
+ * position `position + r`. */
+int tt_attn_pre(tt_context *ctx, tt_stream stream, const void *q_packed, void *q_out, void *gate_out,
+                void *k_rows, const void *q_norm_weight, const void *k_norm_weight, uint32_t head_dim,
+                uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t rotary_dim, float theta, float eps,
+                uint32_t position, uint32_t rows, uint32_t k_row_stride_elements);
+/* out[i] *= sigmoid(gate[i]) (sigmoid_gate_mul_fp16, Primitives/utility.metal:48-58), the
+ * full-attention output gate (RealForwardRunner+DecodeFullAttention.swift:84-88). */
+int tt_attn_gate_mul(tt_context *ctx, tt_stream stream, void *out, const void *gate, uint32_t count);
+
 /* ------------------------------------------------------- prefill attention */
 
 /* Field for field the reference's PrefillAttentionParams
@@ -336,6 +353,10 @@ typedef struct tt_allocator {
     void (*release)(void *user, void *ptr);
     int (*copy)(void *user, void *dst, const void *src, size_t bytes);
     int (*zero)(void *user, void *dst, size_t bytes);
+    /* managed memory <-> host memory, used by the snapshot calls only; may be NULL, in
+     * which case snapshots are refused with TT_ERR_UNSUPPORTED_SHAPE */
+    int (*download)(void *user, void *host_dst, const void *src, size_t bytes);
+    int (*upload)(void *user, void *dst, const void *host_src, size_t bytes);
 } tt_allocator;
 
 /* The part of ArchConfig the managers read. layer_kind[i]: 0 sliding-window,
@@ -402,6 +423,17 @@ size_t tt_kv_cache_buffer_length(const tt_kv_cache *cache, uint32_t layer);
 size_t tt_kv_cache_worst_case_bytes(const tt_arch *arch, uint32_t max_context,
                                     uint32_t precision_bits, uint32_t slots);
 
+/* Inference-state snapshot of slot 0, the segment layout of
+ * KVCacheManager+Snapshot.swift:12-121: for every non-linear layer in order, the first
+ * min(position, capacity) rows of K, then of V. _bytes gives the payload size at a position;
+ * _export writes slot 0's prefix at its current cursor to host memory; _restore grows the
+ * stores to `position` first (the lengths depend on capacity), resets every cursor, copies the
+ * segments in and sets slot 0's cursor. A payload of the wrong size is TT_ERR_INVALID_ARG
+ * (InferenceStateSnapshotError.invalidLayout). */
+size_t tt_kv_cache_snapshot_bytes(const tt_kv_cache *cache, uint32_t position);
+int tt_kv_cache_snapshot_export(tt_kv_cache *cache, void *host_dst, size_t capacity, size_t *out_bytes);
+int tt_kv_cache_snapshot_restore(tt_kv_cache *cache, uint32_t position, const void *host_src, size_t bytes);
+
 /* GDNStateManager (sources/TinyTitan/Runtime/KVCache/GDNStateManager.swift:
  * 18-354): per linear layer a zero-initialised fp32 state buffer of
  * slots*Hv*Dv*Dk*4 bytes and an fp16 conv-tail buffer of
@@ -423,6 +455,11 @@ size_t tt_gdn_state_bytes_per_layer(const tt_gdn_state *state);
 size_t tt_gdn_state_conv_tail_bytes_per_layer(const tt_gdn_state *state);
 int tt_gdn_state_is_linear(const tt_gdn_state *state, uint32_t layer);
 size_t tt_gdn_state_worst_case_bytes(const tt_arch *arch, uint32_t slots);
+/* Snapshot segments of slot 0 (GDNStateManager.swift:228-344): for every linear layer in
+ * order, the fp32 state then the fp16 conv tail. _restore zeroes everything first. */
+size_t tt_gdn_state_snapshot_bytes(const tt_gdn_state *state);
+int tt_gdn_state_snapshot_export(tt_gdn_state *state, void *host_dst, size_t capacity, size_t *out_bytes);
+int tt_gdn_state_snapshot_restore(tt_gdn_state *state, const void *host_src, size_t bytes);
 
 #ifdef __cplusplus
 }

@@ -44,3 +44,27 @@ def test_growth_preserves_rows_and_attention_reads_views():
     kv.rewind(10, slot=0)
     assert kv.position(0) == 10 and kv.position(2) == 8192
     kv.close()
+
+
+def test_snapshot_round_trip_on_device_memory():
+    cfg = tt.ArchConfig([tt.FULL, tt.LINEAR], 2, 256, 2, 256, 0, tt.LinearAttentionConfig(16, 32, 128, 128, 4))
+    a = tt.KVCacheManager(cfg, max_context=4096)
+    g = tt.GDNStateManager(cfg)
+    n = 300
+    k = torch.randn(n, 512, device="cuda").half(); v = torch.randn(n, 512, device="cuda").half()
+    device_view(a.k_slot(0, 0), n * 512, torch.float16).copy_(k.view(-1))
+    device_view(a.v_slot(0, 0), n * 512, torch.float16).copy_(v.view(-1))
+    a.advance(0, n)
+    st = torch.randn(32 * 128 * 128, device="cuda")
+    device_view(g.state_slot(1, 0), st.numel()).copy_(st)
+    torch.cuda.synchronize()
+    kv_payload, gdn_payload = a.snapshot(), g.snapshot()
+    assert len(kv_payload) == 2 * n * 1024 and len(gdn_payload) == g.state_bytes_per_layer + g.conv_tail_bytes_per_layer
+    b = tt.KVCacheManager(cfg, max_context=4096); g2 = tt.GDNStateManager(cfg)
+    b.restore_snapshot(n, kv_payload); g2.restore_snapshot(gdn_payload)
+    assert b.position(0) == n
+    assert torch.equal(device_view(b.k_slot(0, 0), n * 512, torch.float16), k.view(-1))
+    assert torch.equal(device_view(b.v_slot(0, 0), n * 512, torch.float16), v.view(-1))
+    assert torch.equal(device_view(g2.state_slot(1, 0), st.numel()), st)
+    for m in (a, b, g, g2):
+        m.close()

@@ -213,3 +213,46 @@ def test_session_sharding_and_kv_ranges():
         assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
     assert sharding.kv_split_ranges(3, 8)[4:] == [(3, 3)] * 4             # empty trailing ranks
     assert sharding.kv_split_ranges(10, 2, kv_start=4) == [(4, 7), (7, 10)]
+
+
+def test_snapshot_round_trip_on_host_memory():
+    # KVCacheManager+Snapshot.swift:12-121 and GDNStateManager.swift:228-344: slot 0's prefix, per layer K then
+    # V; restore grows the receiver first; a payload of another size is refused.
+    cfg = tt.ArchConfig([tt.LINEAR, tt.FULL, tt.LINEAR, tt.FULL], 2, 64, 2, 64, 0, tt.LinearAttentionConfig(2, 4, 32, 32, 4))
+    a = tt.KVCacheManager(cfg, max_context=20000, slots=2, allocator="host")
+    n = 9000
+    a.reserve(n)
+    stride = a.stride(1)
+    rng = np.random.default_rng(0)
+    blobs = {}
+    for layer in (1, 3):
+        for name, fn in (("k", a.k_slot), ("v", a.v_slot)):
+            data = rng.integers(0, 256, size=n * stride, dtype=np.uint8).tobytes()
+            _write(fn(layer, 0, 0), data)
+            blobs[(layer, name)] = data
+    a.advance(0, n)
+    payload = a.snapshot()
+    assert len(payload) == 2 * 2 * n * stride
+    assert payload[:n * stride] == blobs[(1, "k")] and payload[n * stride:2 * n * stride] == blobs[(1, "v")]
+    b = tt.KVCacheManager(cfg, max_context=20000, slots=2, allocator="host")     # fresh receiver at capacity 8192
+    b.advance(1, 5)
+    b.restore_snapshot(n, payload)
+    assert b.capacity(1) == 16384 and b.position(0) == n and b.position(1) == 0
+    assert _read(b.v_slot(3, 0, 0), n * stride) == blobs[(3, "v")]
+    with pytest.raises(tt.InvalidArgument):
+        b.restore_snapshot(n, payload[:-1])
+    with pytest.raises(tt.InvalidArgument):
+        b.restore_snapshot(0, payload)
+    g = tt.GDNStateManager(cfg, slots=2, allocator="host")
+    _write(g.state_slot(0, 0), b"\x21" * 100); _write(g.conv_tail_slot(2, 0), b"\x43" * 50); _write(g.state_slot(0, 1), b"\x99" * 8)
+    snap = g.snapshot()
+    assert len(snap) == 2 * (g.state_bytes_per_layer + g.conv_tail_bytes_per_layer)
+    g2 = tt.GDNStateManager(cfg, slots=2, allocator="host")
+    _write(g2.state_slot(2, 1), b"\x77" * 8)
+    g2.restore_snapshot(snap)
+    assert _read(g2.state_slot(0, 0), 100) == b"\x21" * 100 and _read(g2.conv_tail_slot(2, 0), 50) == b"\x43" * 50
+    assert _read(g2.state_slot(2, 1), 8) == b"\0" * 8                            # restore resets everything first
+    with pytest.raises(tt.InvalidArgument):
+        g2.restore_snapshot(snap + b"x")
+    for m in (a, b, g, g2):
+        m.close()

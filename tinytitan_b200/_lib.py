@@ -82,7 +82,7 @@ ZERO_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_size_t)
 
 class Allocator(C.Structure):
     _fields_ = [("user", C.c_void_p), ("alloc", ALLOC_FN), ("release", RELEASE_FN), ("copy", COPY_FN),
-                ("zero", ZERO_FN)]
+                ("zero", ZERO_FN), ("download", COPY_FN), ("upload", COPY_FN)]
 
 
 class Arch(C.Structure):
@@ -119,6 +119,9 @@ SIGNATURES = {
     "tt_attn_reference_split_geometry": (None, [_u32, _u32, _u32, _u32, C.c_int, C.POINTER(SplitGeometry)]),
     "tt_attn_plan_splits": (C.c_int, [C.POINTER(_u32), C.POINTER(_u32), _u32, _u32, _u32, _u32, _u32, C.c_size_t,
                                       C.POINTER(_u32), C.POINTER(_u32)]),
+    "tt_attn_pre": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, C.c_float, C.c_float,
+                              _u32, _u32, _u32]),
+    "tt_attn_gate_mul": (C.c_int, [_vp, _vp, _vp, _vp, _u32]),
     "tt_kv_quantize_affine": (C.c_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32]),
     "tt_attn_prefill_causal": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(PrefillParams), _u32, _u32]),
     "tt_attn_prefill_path": (C.c_int, [_vp, _vp, _vp, _vp, C.POINTER(PrefillParams), _u32]),
@@ -151,6 +154,12 @@ SIGNATURES = {
     "tt_kv_cache_layer_kind": (_u32, [_vp, _u32]),
     "tt_kv_cache_buffer_length": (C.c_size_t, [_vp, _u32]),
     "tt_kv_cache_worst_case_bytes": (C.c_size_t, [C.POINTER(Arch), _u32, _u32, _u32]),
+    "tt_kv_cache_snapshot_bytes": (C.c_size_t, [_vp, _u32]),
+    "tt_kv_cache_snapshot_export": (C.c_int, [_vp, _vp, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "tt_kv_cache_snapshot_restore": (C.c_int, [_vp, _u32, _vp, C.c_size_t]),
+    "tt_gdn_state_snapshot_bytes": (C.c_size_t, [_vp]),
+    "tt_gdn_state_snapshot_export": (C.c_int, [_vp, _vp, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "tt_gdn_state_snapshot_restore": (C.c_int, [_vp, _vp, C.c_size_t]),
     "tt_gdn_state_create": (_vp, [C.POINTER(Arch), _u32, C.c_int, C.POINTER(Allocator), C.POINTER(C.c_int)]),
     "tt_gdn_state_destroy": (None, [_vp]),
     "tt_gdn_state_state_slot": (C.c_int, [_vp, _u32, _u32, C.POINTER(_vp)]),

@@ -25,7 +25,14 @@ int cuda_copy(void *, void *dst, const void *src, size_t bytes) {
 }
 int cuda_zero(void *, void *dst, size_t bytes) { return cudaMemset(dst, 0, bytes) == cudaSuccess ? 0 : 1; }
 
-const tt_allocator kCudaAllocator = {nullptr, cuda_alloc, cuda_release, cuda_copy, cuda_zero};
+int cuda_download(void *, void *host_dst, const void *src, size_t bytes) {
+    return cudaMemcpy(host_dst, src, bytes, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 1;
+}
+int cuda_upload(void *, void *dst, const void *host_src, size_t bytes) {
+    return cudaMemcpy(dst, host_src, bytes, cudaMemcpyHostToDevice) == cudaSuccess ? 0 : 1;
+}
+
+const tt_allocator kCudaAllocator = {nullptr, cuda_alloc, cuda_release, cuda_copy, cuda_zero, cuda_download, cuda_upload};
 
 constexpr uint32_t kMaximumSlots = 256;            // KVCacheManager.maximumSlots
 constexpr uint32_t kInitialCapacityTokens = 8192;  // KVCacheManager.initialCapacityTokens
@@ -268,6 +275,62 @@ TT_API size_t tt_kv_cache_worst_case_bytes(const tt_arch *arch, uint32_t max_con
     return total;
 }
 
+TT_API size_t tt_kv_cache_snapshot_bytes(const tt_kv_cache *c, uint32_t position) {
+    if (c == nullptr) return 0;
+    size_t total = 0;
+    for (size_t layer = 0; layer < c->kind.size(); ++layer) {
+        if (c->kind[layer] == 2) continue;
+        const uint32_t stored = position < c->capacity[layer] ? position : c->capacity[layer];
+        total += (size_t)stored * c->stride[layer] * 2;
+    }
+    return total;
+}
+
+TT_API int tt_kv_cache_snapshot_export(tt_kv_cache *c, void *host_dst, size_t capacity, size_t *out_bytes) {
+    if (c == nullptr || host_dst == nullptr) return TT_ERR_INVALID_ARG;
+    if (c->alloc.download == nullptr) return TT_ERR_UNSUPPORTED_SHAPE;
+    const uint32_t position = c->position[0];
+    if (position == 0 || position > c->max_context) return TT_ERR_INVALID_ARG;   // invalidPosition
+    const size_t need = tt_kv_cache_snapshot_bytes(c, position);
+    if (capacity < need) return TT_ERR_INVALID_ARG;
+    char *dst = static_cast<char *>(host_dst);
+    for (size_t layer = 0; layer < c->kind.size(); ++layer) {
+        if (c->kind[layer] == 2) continue;
+        const uint32_t stored = position < c->capacity[layer] ? position : c->capacity[layer];
+        const size_t len = (size_t)stored * c->stride[layer];
+        // slot 0's region starts at offset 0 of the layer's buffers
+        if (c->alloc.download(c->alloc.user, dst, c->k[layer], len)) return TT_ERR_CUDA;
+        dst += len;
+        if (c->alloc.download(c->alloc.user, dst, c->v[layer], len)) return TT_ERR_CUDA;
+        dst += len;
+    }
+    if (out_bytes) *out_bytes = need;
+    return TT_OK;
+}
+
+TT_API int tt_kv_cache_snapshot_restore(tt_kv_cache *c, uint32_t position, const void *host_src, size_t bytes) {
+    if (c == nullptr || host_src == nullptr) return TT_ERR_INVALID_ARG;
+    if (c->alloc.upload == nullptr) return TT_ERR_UNSUPPORTED_SHAPE;
+    if (position == 0 || position > c->max_context) return TT_ERR_INVALID_ARG;
+    // grow first: the segment lengths are a function of capacity
+    int rc = tt_kv_cache_reserve(c, position, 0);
+    if (rc != TT_OK) return rc;
+    if (bytes != tt_kv_cache_snapshot_bytes(c, position)) return TT_ERR_INVALID_ARG;   // invalidLayout
+    tt_kv_cache_reset(c);
+    const char *src = static_cast<const char *>(host_src);
+    for (size_t layer = 0; layer < c->kind.size(); ++layer) {
+        if (c->kind[layer] == 2) continue;
+        const uint32_t stored = position < c->capacity[layer] ? position : c->capacity[layer];
+        const size_t len = (size_t)stored * c->stride[layer];
+        if (c->alloc.upload(c->alloc.user, c->k[layer], src, len)) return TT_ERR_CUDA;
+        src += len;
+        if (c->alloc.upload(c->alloc.user, c->v[layer], src, len)) return TT_ERR_CUDA;
+        src += len;
+    }
+    c->position[0] = position;
+    return TT_OK;
+}
+
 // ------------------------------------------------------------------ GDN state
 
 struct tt_gdn_state {
@@ -407,4 +470,45 @@ TT_API size_t tt_gdn_state_bytes_per_layer(const tt_gdn_state *g) { return g ? g
 TT_API size_t tt_gdn_state_conv_tail_bytes_per_layer(const tt_gdn_state *g) { return g ? g->tail_bytes : 0; }
 TT_API int tt_gdn_state_is_linear(const tt_gdn_state *g, uint32_t layer) {
     return (g && layer < g->state.size() && g->state[layer] != nullptr) ? 1 : 0;
+}
+
+TT_API size_t tt_gdn_state_snapshot_bytes(const tt_gdn_state *g) {
+    if (g == nullptr) return 0;
+    size_t linear = 0;
+    for (void *p : g->state) linear += p != nullptr;
+    return linear * (g->state_bytes + g->tail_bytes);
+}
+
+TT_API int tt_gdn_state_snapshot_export(tt_gdn_state *g, void *host_dst, size_t capacity, size_t *out_bytes) {
+    if (g == nullptr || host_dst == nullptr) return TT_ERR_INVALID_ARG;
+    if (g->alloc.download == nullptr) return TT_ERR_UNSUPPORTED_SHAPE;
+    const size_t need = tt_gdn_state_snapshot_bytes(g);
+    if (capacity < need) return TT_ERR_INVALID_ARG;
+    char *dst = static_cast<char *>(host_dst);
+    for (size_t i = 0; i < g->state.size(); ++i) {
+        if (!g->state[i]) continue;
+        if (g->alloc.download(g->alloc.user, dst, g->state[i], g->state_bytes)) return TT_ERR_CUDA;
+        dst += g->state_bytes;
+        if (g->alloc.download(g->alloc.user, dst, g->tail[i], g->tail_bytes)) return TT_ERR_CUDA;
+        dst += g->tail_bytes;
+    }
+    if (out_bytes) *out_bytes = need;
+    return TT_OK;
+}
+
+TT_API int tt_gdn_state_snapshot_restore(tt_gdn_state *g, const void *host_src, size_t bytes) {
+    if (g == nullptr || host_src == nullptr) return TT_ERR_INVALID_ARG;
+    if (g->alloc.upload == nullptr) return TT_ERR_UNSUPPORTED_SHAPE;
+    if (bytes != tt_gdn_state_snapshot_bytes(g)) return TT_ERR_INVALID_ARG;   // invalidLayout
+    int rc = tt_gdn_state_reset(g);
+    if (rc != TT_OK) return rc;
+    const char *src = static_cast<const char *>(host_src);
+    for (size_t i = 0; i < g->state.size(); ++i) {
+        if (!g->state[i]) continue;
+        if (g->alloc.upload(g->alloc.user, g->state[i], src, g->state_bytes)) return TT_ERR_CUDA;
+        src += g->state_bytes;
+        if (g->alloc.upload(g->alloc.user, g->tail[i], src, g->tail_bytes)) return TT_ERR_CUDA;
+        src += g->tail_bytes;
+    }
+    return TT_OK;
 }

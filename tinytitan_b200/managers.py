@@ -90,7 +90,8 @@ def _host_allocator():
         C.memset(dst, 0, n)
         return 0
 
-    a = L.Allocator(None, L.ALLOC_FN(alloc), L.RELEASE_FN(release), L.COPY_FN(copy), L.ZERO_FN(zero))
+    a = L.Allocator(None, L.ALLOC_FN(alloc), L.RELEASE_FN(release), L.COPY_FN(copy), L.ZERO_FN(zero), L.COPY_FN(copy),
+                    L.COPY_FN(copy))
     a._live = live
     return a
 
@@ -192,6 +193,18 @@ class KVCacheManager:
     def buffer_length(self, layer: int) -> int:
         return int(L.lib().tt_kv_cache_buffer_length(self.handle, layer))
 
+    def snapshot(self) -> bytes:
+        """Slot 0's K/V prefix at its cursor (KVCacheManager+Snapshot.swift:38-65)."""
+        n = int(L.lib().tt_kv_cache_snapshot_bytes(self.handle, self.position(0)))
+        buf = C.create_string_buffer(max(n, 1))
+        out = C.c_size_t(0)
+        L.check(L.lib().tt_kv_cache_snapshot_export(self.handle, buf, n, C.byref(out)))
+        return buf.raw[:out.value]
+
+    def restore_snapshot(self, position: int, payload: bytes):
+        """restoreSnapshot (KVCacheManager+Snapshot.swift:67-121)."""
+        L.check(L.lib().tt_kv_cache_snapshot_restore(self.handle, position, payload, len(payload)))
+
 
 class GDNStateManager:
     maximum_slots = KVCacheManager.maximum_slots
@@ -259,3 +272,14 @@ class GDNStateManager:
 
     def speculative_restore(self):
         L.check(L.lib().tt_gdn_state_speculative_restore(self.handle))
+
+    def snapshot(self) -> bytes:
+        """[state, conv tail] of slot 0 for every linear layer (GDNStateManager.swift:228-261)."""
+        n = int(L.lib().tt_gdn_state_snapshot_bytes(self.handle))
+        buf = C.create_string_buffer(max(n, 1))
+        out = C.c_size_t(0)
+        L.check(L.lib().tt_gdn_state_snapshot_export(self.handle, buf, n, C.byref(out)))
+        return buf.raw[:out.value]
+
+    def restore_snapshot(self, payload: bytes):
+        L.check(L.lib().tt_gdn_state_snapshot_restore(self.handle, payload, len(payload)))

@@ -220,6 +220,20 @@ class Attention:
         self.context.check(L.lib().tt_attn_decode_batched(self.context.handle, _stream(command_buffer), arr, n,
                                                           C.byref(p)))
 
+    def encode_pre(self, q_packed, q_out, gate_out, k_rows, q_norm_weight, k_norm_weight, head_dim, num_q_heads,
+                   num_kv_heads, rotary_dim, theta, eps, position, rows=1, k_row_stride_elements=None,
+                   command_buffer=None):
+        """Split [query; gate], per-head q/k RMS norm, NeoX partial RoPE (encodeGatedFullPostProjection)."""
+        self.context.check(L.lib().tt_attn_pre(
+            self.context.handle, _stream(command_buffer), _addr(q_packed), _addr(q_out), _addr(gate_out), _addr(k_rows),
+            _addr(q_norm_weight), _addr(k_norm_weight), head_dim, num_q_heads, num_kv_heads, rotary_dim, theta, eps,
+            position, rows, k_row_stride_elements or num_kv_heads * head_dim))
+
+    def encode_gate_mul(self, out, gate, count, command_buffer=None):
+        """out *= sigmoid(gate): the full-attention output gate."""
+        self.context.check(L.lib().tt_attn_gate_mul(self.context.handle, _stream(command_buffer), _addr(out),
+                                                    _addr(gate), count))
+
     def encode_partial(self, q, k, v, head_dim, num_q_heads, num_kv_heads, seq_len, kv_start, m_out, d_out, o_out,
                        scale=None, kv_token_stride_elements=0, io_dtype=None, command_buffer=None):
         """Pass 1 alone: one unnormalised (m, d, o) triple per q head for this device's keys."""
