@@ -108,6 +108,15 @@ int tt_attn_decode(tt_context *ctx, tt_stream stream, const void *q, const void 
                    const tt_kv_format *kv_format, const uint8_t *keep_mask,
                    uint32_t ring_capacity);
 
+/* Attention over a compact selection with row indirection: key s of sel_count lives at
+ * physical row sel_rows[s] of the K / V buffers (device array). Replaces
+ * Attention.encodeFull(windowSelection:) -> attention_decode_window_partial
+ * (attention.metal:612-870), the read side of the host-KV window. */
+int tt_attn_decode_window(tt_context *ctx, tt_stream stream, const void *q, const void *k,
+                          const void *v, void *out, uint32_t head_dim, uint32_t n_q_heads,
+                          uint32_t n_kv_heads, uint32_t sel_count, float scale,
+                          const tt_kv_format *kv_format, const uint32_t *sel_rows);
+
 /* One session of a batched / few-token decode step. Row r of `q_rows` sits at
  * base position seq_len - q_rows + r and attends keys
  * [kv_start, seq_len - (q_rows - 1 - r)), which is the decode-order verify rule

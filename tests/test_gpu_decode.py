@@ -219,3 +219,18 @@ def test_large_batch_property_partition_invariance():
     sc = torch.einsum("hd,shd->hs", q.double(), k.double().repeat_interleave(hq // hkv, dim=1)) * 0.0625
     ref = torch.einsum("hs,shd->hd", torch.softmax(sc, dim=1), v.double().repeat_interleave(hq // hkv, dim=1))
     assert (out_a.double() - ref).abs().max().item() <= TOL
+
+
+def test_windowed_selection_with_row_indirection():
+    # attention_decode_window_partial (attention.metal:612-870): key s of the selection lives at row sel_row[s]
+    r = np.random.default_rng(13)
+    hq, hkv, hd, rows, count = 16, 2, 256, 5000, 2049
+    q = rounded(r.normal(size=(hq, hd)))
+    k = rounded(r.normal(size=(rows, hkv, hd))); v = rounded(r.normal(size=(rows, hkv, hd)))
+    sel = r.permutation(rows)[:count].astype(np.uint32)
+    out = torch.full((hq, hd), float("nan"), device="cuda", dtype=torch.float16)
+    tt.Attention(context()).encode_window(dev(q), dev(k), dev(v), out, hd, hq, hkv,
+                                          torch.from_numpy(sel.astype(np.int64)).to(torch.int32).cuda(), count, scale=0.0625)
+    torch.cuda.synchronize()
+    want = oracle.attn_decode(q, k[sel], v[sel], hkv, 0.0625)
+    assert np.abs(host(out) - want).max() <= TOL

@@ -111,6 +111,8 @@ SIGNATURES = {
     "tt_ctx_profile_collect": (C.c_int, [_vp, _f32p, _u32, C.POINTER(_u32)]),
     "tt_attn_decode": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.c_float,
                                  C.POINTER(KVFormat), _vp, _u32]),
+    "tt_attn_decode_window": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, C.c_float,
+                                        C.POINTER(KVFormat), _vp]),
     "tt_attn_decode_batched": (C.c_int, [_vp, _vp, C.POINTER(AttnSession), _u32, C.POINTER(AttnBatchParams)]),
     "tt_attn_decode_partial": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.c_float, _u32,
                                          _u32, _vp, _vp, _vp]),

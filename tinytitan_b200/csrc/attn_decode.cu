@@ -242,6 +242,7 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
             unsigned char *dst = ring + (i % kStages) * S::kStageBytes + warp * S::kTileBytes + lane * S::kRowBytes;
             if ((uint32_t)lane < valid) {
                 uint32_t p = item.key_begin + i * kKeysPerBlock + lane;
+                if (ses.row_index != nullptr) p = ses.row_index[p];
                 if (ses.ring_capacity) p %= ses.ring_capacity;
                 bulk_copy_g2s(dst, (warp ? vbase : kbase) + (size_t)p * kv_stride_bytes, HD * 2, &bars[i % kStages]);
             } else if (warp == 1) {
@@ -517,6 +518,7 @@ attn_decode_partial_quant_kernel(const TTDecodeItem *__restrict__ items,
             unsigned char *dst = ring + (i % kStages) * S::kStageBytes + warp * S::kTileBytes + lane * S::kRowBytes;
             if ((uint32_t)lane < valid) {
                 uint32_t p = item.key_begin + i * kKeysPerBlock + lane;
+                if (ses.row_index != nullptr) p = ses.row_index[p];
                 if (ses.ring_capacity) p %= ses.ring_capacity;
                 const unsigned char *src = (warp ? vbase : kbase) + (size_t)p * kv_stride_bytes;
                 bulk_copy_g2s(dst, src + head_value_offset, S::kValBytes, &bars[i % kStages]);
@@ -1141,16 +1143,15 @@ TT_API int tt_attn_decode_batched(tt_context *ctx, tt_stream stream, const tt_at
         TTDecodeSession &d = tmp[i];
         d.q = sessions[i].q; d.out = sessions[i].out; d.k = sessions[i].k; d.v = sessions[i].v;
         d.seq_len = sessions[i].seq_len; d.q_rows = sessions[i].q_rows; d.kv_start = sessions[i].kv_start;
-        d.n_parts = 0; d.partial_base = 0; d.ring_capacity = 0; d.keep = nullptr;
+        d.n_parts = 0; d.partial_base = 0; d.ring_capacity = 0; d.keep = nullptr; d.row_index = nullptr;
     }
     return tt_launch_decode(ctx, (cudaStream_t)stream, tmp, n_sessions, params, 0, nullptr, nullptr, nullptr);
 }
 
-TT_API int tt_attn_decode(tt_context *ctx, tt_stream stream, const void *q, const void *k, const void *v,
-                          void *out, uint32_t head_dim, uint32_t n_q_heads, uint32_t n_kv_heads,
-                          uint32_t seq_len, uint32_t kv_start, float scale, const tt_kv_format *kv_format,
-                          const uint8_t *keep_mask, uint32_t ring_capacity) {
-    TT_ENTER(ctx);
+static int decode_one(tt_context *ctx, tt_stream stream, const void *q, const void *k, const void *v,
+                      void *out, uint32_t head_dim, uint32_t n_q_heads, uint32_t n_kv_heads,
+                      uint32_t seq_len, uint32_t kv_start, float scale, const tt_kv_format *kv_format,
+                      const uint8_t *keep_mask, uint32_t ring_capacity, const uint32_t *row_index) {
     if (head_dim > 512) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "head_dim must be <= 512");
     if (n_kv_heads == 0 || n_q_heads % n_kv_heads != 0)
         return tt_set_error(ctx, TT_ERR_INVALID_ARG, "n_q_heads must be a multiple of n_kv_heads for GQA");
@@ -1179,8 +1180,27 @@ TT_API int tt_attn_decode(tt_context *ctx, tt_stream stream, const void *q, cons
     TTDecodeSession s;
     s.q = q; s.out = out; s.k = k; s.v = v; s.seq_len = seq_len; s.q_rows = 1;
     s.kv_start = kv_start < seq_len ? kv_start : seq_len;
-    s.n_parts = 0; s.partial_base = 0; s.ring_capacity = ring_capacity; s.keep = keep_mask;
+    s.n_parts = 0; s.partial_base = 0; s.ring_capacity = ring_capacity; s.keep = keep_mask; s.row_index = row_index;
     return tt_launch_decode(ctx, (cudaStream_t)stream, &s, 1, &p, 0, nullptr, nullptr, nullptr, &quant);
+}
+
+TT_API int tt_attn_decode(tt_context *ctx, tt_stream stream, const void *q, const void *k, const void *v,
+                          void *out, uint32_t head_dim, uint32_t n_q_heads, uint32_t n_kv_heads,
+                          uint32_t seq_len, uint32_t kv_start, float scale, const tt_kv_format *kv_format,
+                          const uint8_t *keep_mask, uint32_t ring_capacity) {
+    TT_ENTER(ctx);
+    return decode_one(ctx, stream, q, k, v, out, head_dim, n_q_heads, n_kv_heads, seq_len, kv_start, scale, kv_format,
+                      keep_mask, ring_capacity, nullptr);
+}
+
+TT_API int tt_attn_decode_window(tt_context *ctx, tt_stream stream, const void *q, const void *k, const void *v,
+                                 void *out, uint32_t head_dim, uint32_t n_q_heads, uint32_t n_kv_heads,
+                                 uint32_t sel_count, float scale, const tt_kv_format *kv_format,
+                                 const uint32_t *sel_rows) {
+    TT_ENTER(ctx);
+    if (sel_rows == nullptr) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "a windowed selection needs its row list");
+    return decode_one(ctx, stream, q, k, v, out, head_dim, n_q_heads, n_kv_heads, sel_count, 0, scale, kv_format,
+                      nullptr, 0, sel_rows);
 }
 
 TT_API int tt_attn_decode_partial(tt_context *ctx, tt_stream stream, const void *q, const void *k,
@@ -1199,7 +1219,7 @@ TT_API int tt_attn_decode_partial(tt_context *ctx, tt_stream stream, const void 
     TTDecodeSession s;
     s.q = q; s.out = nullptr; s.k = k; s.v = v; s.seq_len = seq_len; s.q_rows = 1;
     s.kv_start = kv_start < seq_len ? kv_start : seq_len;
-    s.n_parts = 0; s.partial_base = 0; s.ring_capacity = 0; s.keep = nullptr;
+    s.n_parts = 0; s.partial_base = 0; s.ring_capacity = 0; s.keep = nullptr; s.row_index = nullptr;
     return tt_launch_decode(ctx, (cudaStream_t)stream, &s, 1, &p, 1, m_out, d_out, o_out);
 }
 
@@ -1311,6 +1331,7 @@ TT_API int tt_attn_decode_noalloc(tt_stream stream, const void *q, const void *k
     host.ses.q = q; host.ses.out = out; host.ses.k = k; host.ses.v = v;
     host.ses.seq_len = seq_len; host.ses.q_rows = 1; host.ses.kv_start = kv_start;
     host.ses.n_parts = parts; host.ses.partial_base = 0; host.ses.ring_capacity = 0; host.ses.keep = nullptr;
+    host.ses.row_index = nullptr;
     const uint32_t group = n_q_heads / n_kv_heads;
     uint32_t cursor = 0;
     for (uint32_t part = 0; part < parts; ++part) {

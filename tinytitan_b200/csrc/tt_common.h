@@ -45,6 +45,7 @@ struct TTDecodeSession {
     uint32_t partial_base;   // first partial row of this session in the workspace
     uint32_t ring_capacity;
     const uint8_t *keep;     // nullable
+    const uint32_t *row_index;  // nullable: key s lives at row row_index[s] (compact selection)
 };
 
 struct tt_context {

@@ -171,6 +171,17 @@ class Attention:
         self._encode(command_buffer, q, q_offset, k, k_offset, v, v_offset, out, out_offset, head_dim, num_q_heads,
                      num_kv_heads, seq_len, 0, scale, kv_format, keep_mask, 0)
 
+    def encode_window(self, q, k, v, out, head_dim, num_q_heads, num_kv_heads, sel_rows, sel_count, scale=None,
+                      kv_format: Optional[KVFormat] = None, command_buffer=None):
+        """encodeFull(windowSelection:): attention over sel_count keys, key s at row sel_rows[s]."""
+        fmt = None
+        if kv_format is not None:
+            fmt = L.KVFormat(kv_format.bits, kv_format.stride, kv_format.value_bytes, kv_format.group_size)
+        self.context.check(L.lib().tt_attn_decode_window(
+            self.context.handle, _stream(command_buffer), _addr(q), _addr(k), _addr(v), _addr(out), head_dim,
+            num_q_heads, num_kv_heads, sel_count, self.default_scale(head_dim) if scale is None else scale,
+            C.byref(fmt) if fmt is not None else None, _addr(sel_rows)))
+
     def encode_swa(self, q, k, v, out, head_dim, num_q_heads, num_kv_heads, seq_len, window, scale=None,
                    ring_capacity=0, kv_format: Optional[KVFormat] = None, command_buffer=None, q_offset=0,
                    k_offset=0, v_offset=0, out_offset=0):
