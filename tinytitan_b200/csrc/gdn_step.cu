@@ -9,9 +9,10 @@
 // HBM-bound design: the fp32 state [Hv][Dv][Dk] is read once and written once per call
 // whatever the number of rows. A CTA owns 32 state rows of one (session, head); each of its 4
 // warps holds 8 rows in registers (a lane owns Dk/32 consecutive floats of each row), so the
-// eight 16-byte loads of a lane are in flight together. Per token the two dot products of a
-// row (S.k and S.q) are warp-shuffle reductions; the state never leaves registers between
-// tokens.
+// eight 16-byte loads of a lane are in flight together. Per token the two dot products of the
+// eight rows (S.k and S.q) are reduced together with a 9-shuffle transposing butterfly; the state
+// never leaves registers between tokens, and the next token's inputs are fetched while the
+// current one is applied.
 #include "tt_common.h"
 
 namespace {
@@ -28,10 +29,30 @@ struct GdnParams {
     float readout_scale;
 };
 
-__device__ __forceinline__ float warp_sum(float v) {
+// Sums of 8 per-lane values over the warp in 9 shuffles instead of 40: at each of the first three
+// butterfly steps a lane hands the half of its values the partner keeps and adds the half it keeps,
+// then the single remaining value is summed over the last four lanes. Lane L ends with the total
+// of value index 4*bit4(L) + 2*bit3(L) + bit2(L), i.e. index r is held by lanes 4r..4r+3.
+__device__ __forceinline__ float warp_sum8(const float (&v)[8], int lane) {
+    float a[4], b[2];
+    bool up = (lane & 16) != 0;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
+    for (int i = 0; i < 4; ++i) {
+        const float send = up ? v[i] : v[i + 4], keep = up ? v[i + 4] : v[i];
+        a[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+    up = (lane & 8) != 0;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float send = up ? a[i] : a[i + 2], keep = up ? a[i + 2] : a[i];
+        b[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+    up = (lane & 4) != 0;
+    const float send = up ? b[0] : b[1], keep = up ? b[1] : b[0];
+    float c = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    c += __shfl_xor_sync(0xffffffffu, c, 2);
+    c += __shfl_xor_sync(0xffffffffu, c, 1);
+    return c;
 }
 
 template <int NPL>
@@ -154,8 +175,11 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_step_kernel(GdnParams p) {
             }
             kv[r] = acc;
         }
+        {   // all eight S.k sums, then every lane fetches the eight totals (row r sits in lane 4r)
+            const float mine = warp_sum8(kv, lane);
 #pragma unroll
-        for (int r = 0; r < kRowsPerWarp; ++r) kv[r] = warp_sum(kv[r]);
+            for (int r = 0; r < kRowsPerWarp; ++r) kv[r] = __shfl_sync(0xffffffffu, mine, r << 2);
+        }
 
         float out[kRowsPerWarp];
 #pragma unroll
@@ -170,16 +194,11 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_step_kernel(GdnParams p) {
             }
             out[r] = acc;
         }
-#pragma unroll
-        for (int r = 0; r < kRowsPerWarp; ++r) out[r] = warp_sum(out[r]);
-
-        // lanes 0..7 each store one row's readout
-        float mine = 0.f;
-#pragma unroll
-        for (int r = 0; r < kRowsPerWarp; ++r) mine = (lane == r) ? out[r] : mine;
-        if (lane < kRowsPerWarp && dv0 + lane < p.dv) {
+        // S.q sums: lane 4r holds row r's readout and stores it
+        const float mine = warp_sum8(out, lane);
+        if ((lane & 3) == 0 && rows_valid) {
             __half *y = reinterpret_cast<__half *>(ses.y) + (size_t)t * p.hv * p.dv + (size_t)h * p.dv;
-            y[dv0 + lane] = __float2half_rn(mine * p.readout_scale);
+            y[dv0 + (lane >> 2)] = __float2half_rn(mine * p.readout_scale);
         }
 
         if (t == 0 && ses.checkpoint_state != nullptr) {
