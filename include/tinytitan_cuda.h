@@ -73,10 +73,14 @@ uint64_t tt_ctx_launch_count(const tt_context *ctx);
 /* Per-kernel device timing, the counterpart of the reference's per-command-buffer
  * GPU timestamps (EngineRunner.kernelGPUTimingSummary, EngineRunner.swift:58-66;
  * TINYTITAN_KERNEL_SPLIT in RealForwardRunner+DecodeGEMV.swift:29-50). While
- * enabled, every split-KV pass-1 launch is bracketed by a pair of events on its
- * own stream (up to 256 launches are kept). tt_ctx_profile_collect waits for the
- * recorded events, writes the durations in milliseconds, returns how many there
- * were in *out_count and clears the record. */
+ * enabled, every launch of the selected kernel classes is bracketed by a pair of
+ * events on its own stream (up to 256 launches are kept). `enabled` is 0 (off) or a
+ * mask of TT_PROFILE_*; 1 selects the split-KV pass-1 kernel.
+ * tt_ctx_profile_collect waits for the recorded events, writes the durations in
+ * milliseconds in launch order, returns how many there were in *out_count and
+ * clears the record. */
+#define TT_PROFILE_DECODE_PARTIAL 1
+#define TT_PROFILE_GDN_STEP 2
 int tt_ctx_profile_enable(tt_context *ctx, int enabled);
 int tt_ctx_profile_collect(tt_context *ctx, float *out_ms, uint32_t capacity, uint32_t *out_count);
 

@@ -14,7 +14,7 @@
 // with quad shuffles. Pass 2 merges the items of a session by log-sum-exp. A call with one
 // session carries it in the kernel parameters (no table upload), which also makes that call
 // capturable in a CUDA graph.
-#include "tt_common.h"
+#include "tt_sm100.h"
 
 namespace {
 
@@ -22,46 +22,6 @@ constexpr int kKeysPerBlock = 16;   // keys per warp pipeline stage
 constexpr int kStages = 3;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
-constexpr uint32_t kWaitLimit = 4000000u;  // mbarrier polls before a wait gives up
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
-                 "r"(bytes)
-                 : "memory");
-}
-
-// Bounded wait: false when the poll limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t it = 0; it < kWaitLimit; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void bulk_copy_g2s(void *dst, const void *src, uint32_t bytes,
-                                              uint64_t *bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
-        : "memory");
-}
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -99,32 +59,6 @@ __device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&c)[4], const ui
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <typename T>
-__device__ __forceinline__ uint32_t pack2(float lo, float hi);
-template <>
-__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&h);
-}
-template <>
-__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&h);
-}
-
-template <typename T>
-__device__ __forceinline__ float sum2(uint32_t packed);
-template <>
-__device__ __forceinline__ float sum2<__half>(uint32_t packed) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&packed));
-    return f.x + f.y;
-}
-template <>
-__device__ __forceinline__ float sum2<__nv_bfloat16>(uint32_t packed) {
-    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&packed));
-    return f.x + f.y;
-}
-
 template <int HD>
 struct DecodeSmem {
     static constexpr int kPitch = HD + 8;                          // elements per staged row
@@ -137,12 +71,6 @@ struct DecodeSmem {
 };
 
 __device__ __forceinline__ void pair_barrier() { asm volatile("bar.sync 1, 64;" ::: "memory"); }
-
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 
 // ---------------------------------------------------------------------------------------
 // Pass 1. grid = items, block = one warp pair (64 threads), 4 CTAs per SM.
@@ -1096,8 +1024,7 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "copy item table");
     }
 
-    const bool timed = ctx->profiling && ctx->profile_count < tt_context::kProfileSlots;
-    if (timed) cudaEventRecord(ctx->profile_begin[ctx->profile_count], stream);
+    TTLaunchTimer timer(ctx, stream, TT_PROFILE_DECODE_PARTIAL);
     if (quantised)
         e = launch_partial_quant(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status,
                                  single_ses, single_keys, quant, meta_bytes);
@@ -1108,7 +1035,7 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
         e = launch_partial_hd<__nv_bfloat16>(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p,
                                              ctx->status, single_ses, single_keys);
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_decode_partial launch");
-    if (timed) cudaEventRecord(ctx->profile_end[ctx->profile_count++], stream);
+    timer.stop();
     ctx->launches++;
 
     const dim3 grid(n_sessions, max_rows);

@@ -15,9 +15,8 @@
 //
 // Arithmetic semantics: sources/TinyTitanCore/Metal/Prefill/prefill.metal:1056-1158 (visible
 // keys [first, min(kvValid, start+t+1)), fp32 accumulation, row_sum == 0 -> 0).
-#include "tt_common.h"
+#include "tt_sm100.h"
 
-#include <cuda.h>
 #include <cstdlib>
 
 namespace {
@@ -26,7 +25,6 @@ constexpr int kHD = 256;
 constexpr int kBM = 128;              // query rows per CTA
 constexpr int kBN = 64;               // keys per tile
 constexpr int kThreads = 192;
-constexpr uint32_t kWaitLimit = 2000000u;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
 
@@ -47,127 +45,6 @@ struct Barriers {
     uint32_t tmem_base;
     uint32_t pad;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t it = 0; it < kWaitLimit; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
-
-// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field set.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-    d |= (uint64_t)1 << 46;   // descriptor version (Blackwell)
-    d |= (uint64_t)2 << 61;   // SWIZZLE_128B
-    return d;
-}
-
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-// A wait result every lane of the warp agrees on (the tcgen05 ld/st that follow are warp-wide).
-__device__ __forceinline__ bool warp_all(bool ok) { return __all_sync(0xffffffffu, ok) != 0; }
-
-template <typename T>
-__device__ __forceinline__ float sum2(uint32_t packed);
-template <>
-__device__ __forceinline__ float sum2<__half>(uint32_t packed) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&packed));
-    return f.x + f.y;
-}
-template <>
-__device__ __forceinline__ float sum2<__nv_bfloat16>(uint32_t packed) {
-    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&packed));
-    return f.x + f.y;
-}
-
-template <typename T>
-__device__ __forceinline__ uint32_t pack2(float lo, float hi);
-template <>
-__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&h);
-}
-template <>
-__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&h);
-}
 
 struct PrefillTcParams {
     uint32_t start_position, query_count, n_q_heads, n_kv_heads, kv_valid_count, sliding_window;
@@ -216,12 +93,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             mbar_init(&bars->p_ready[s], 128);
         }
         mbar_init(&bars->o_ready, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_fence_init();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&bars->tmem_base)), "r"(kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tmem_alloc(&bars->tmem_base, kTmemCols);
     }
     tc_fence_before();
     __syncthreads();
@@ -414,7 +289,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+        tmem_dealloc(tmem, kTmemCols);
     }
 }
 
@@ -435,8 +310,10 @@ EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
+}  // namespace
+
 // 2-D map over [rows][width] 16-bit elements, rows `stride_elems` apart, box [box_rows][64].
-bool make_map(CUtensorMap *map, const void *base, uint32_t io_dtype, uint64_t width, uint64_t rows,
+bool tt_make_tensor_map_2d(CUtensorMap *map, const void *base, uint32_t io_dtype, uint64_t width, uint64_t rows,
               uint64_t stride_elems, uint32_t box_rows) {
     EncodeTiledFn fn = get_encode_fn();
     if (fn == nullptr) return false;
@@ -450,29 +327,14 @@ bool make_map(CUtensorMap *map, const void *base, uint32_t io_dtype, uint64_t wi
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// A and B always share one format: an fp16 A against a bf16 B is an illegal instruction on sm_100a.
-uint32_t make_idesc(uint32_t io_dtype, uint32_t n, bool b_mn_major) {
-    const uint32_t fmt = io_dtype == TT_BF16 ? 1u : 0u;
-    uint32_t d = 0;
-    d |= 1u << 4;            // D format f32
-    d |= fmt << 7;           // A format
-    d |= fmt << 10;          // B format
-    d |= (b_mn_major ? 1u : 0u) << 16;
-    d |= (n >> 3) << 17;
-    d |= (128u >> 4) << 24;  // M = 128
-    return d;
-}
-
-}  // namespace
-
 int tt_launch_prefill_tc(tt_context *ctx, cudaStream_t stream, const void *q, const void *k, const void *v,
                          void *out, const tt_prefill_params *p, uint32_t io_dtype) {
     CUtensorMap q_map, k_map, v_map;
-    const bool ok = make_map(&q_map, q, io_dtype, (uint64_t)p->n_q_heads * kHD, p->query_count,
+    const bool ok = tt_make_tensor_map_2d(&q_map, q, io_dtype, (uint64_t)p->n_q_heads * kHD, p->query_count,
                              p->q_token_stride_elements, kBM) &&
-                    make_map(&k_map, k, io_dtype, (uint64_t)p->n_kv_heads * kHD, p->kv_valid_count,
+                    tt_make_tensor_map_2d(&k_map, k, io_dtype, (uint64_t)p->n_kv_heads * kHD, p->kv_valid_count,
                              p->kv_token_stride_elements, kBN) &&
-                    make_map(&v_map, v, io_dtype, (uint64_t)p->n_kv_heads * kHD, p->kv_valid_count,
+                    tt_make_tensor_map_2d(&v_map, v, io_dtype, (uint64_t)p->n_kv_heads * kHD, p->kv_valid_count,
                              p->kv_token_stride_elements, kBN);
     if (!ok) return tt_set_error(ctx, TT_ERR_CUDA, "cuTensorMapEncodeTiled failed for the prefill operands");
     PrefillTcParams kp;
@@ -481,8 +343,8 @@ int tt_launch_prefill_tc(tt_context *ctx, cudaStream_t stream, const void *q, co
     kp.o_token_stride = p->o_token_stride_elements;
     kp.n_q_tiles = (p->query_count + kBM - 1) / kBM;
     kp.scale_log2 = p->scale * kLog2e;
-    kp.idesc_qk = make_idesc(io_dtype, kBN, false);
-    kp.idesc_pv = make_idesc(io_dtype, kHD, true);
+    kp.idesc_qk = tt_make_idesc_f16(io_dtype, kBN, false);
+    kp.idesc_pv = tt_make_idesc_f16(io_dtype, kHD, true);
     const uint32_t grid = kp.n_q_tiles * p->n_q_heads;
     cudaError_t e;
     if (io_dtype == TT_F16) {

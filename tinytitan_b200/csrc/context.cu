@@ -138,7 +138,7 @@ TT_API int tt_ctx_profile_enable(tt_context *ctx, int enabled) {
             if (e != cudaSuccess) return tt_check_cuda(ctx, e, "cudaEventCreate");
         }
     }
-    ctx->profiling = enabled != 0;
+    ctx->profiling = enabled;
     ctx->profile_count = 0;
     return TT_OK;
 }

@@ -7,212 +7,329 @@
 // (sources/TinyTitan/Kernels/GDN/GDN.swift:318-396).
 //
 // HBM-bound design: the fp32 state [Hv][Dv][Dk] is read once and written once per call
-// whatever the number of rows. A CTA owns 32 state rows of one (session, head); each of its 4
-// warps holds 8 rows in registers (a lane owns Dk/32 consecutive floats of each row), so the
-// eight 16-byte loads of a lane are in flight together. Per token the two dot products of the
-// eight rows (S.k and S.q) are reduced together with a 9-shuffle transposing butterfly; the state
-// never leaves registers between tokens, and the next token's inputs are fetched while the
-// current one is applied.
-#include "tt_common.h"
+// whatever the number of rows. A warp owns 8 state rows at a time in registers: 8 lanes share two
+// rows, so the two dot products of a token (S.k and S.q) are 3 shuffles each, and the state never
+// leaves registers between tokens. The kernel is persistent: each warp walks a list of 8-row
+// items, the rows arrive through a per-warp ring of bulk copies (three items ahead), and the next
+// token's inputs are fetched while the current one is applied.
+#include "tt_sm100.h"
+
+#include <algorithm>
 
 namespace {
 
 constexpr int kRowsPerWarp = 8;
 constexpr int kWarps = 4;
-constexpr int kRowsPerCta = kRowsPerWarp * kWarps;
+constexpr uint32_t kSlots = 2;        // state items in flight per warp
+constexpr uint32_t kTokDepth = 8;     // (item, token) pairs whose inputs are requested ahead
+constexpr uint32_t kSmemSessions = 64, kSmemHeads = 128;   // tables staged in shared memory up to these sizes
+constexpr int kCtasPerSm = 4;
 
 struct GdnParams {
     const tt_gdn_session *sessions;
     const __nv_bfloat16 *a_log;
     const __nv_bfloat16 *dt_bias;
     uint32_t hk, hv, dk, dv, rows, row_stride, flags;
+    uint32_t shift_blocks, shift_heads;   // log2 of dv/8 and of hv when both are powers of two, else 0xff
     float readout_scale;
 };
 
-// Sums of 8 per-lane values over the warp in 9 shuffles instead of 40: at each of the first three
-// butterfly steps a lane hands the half of its values the partner keeps and adds the half it keeps,
-// then the single remaining value is summed over the last four lanes. Lane L ends with the total
-// of value index 4*bit4(L) + 2*bit3(L) + bit2(L), i.e. index r is held by lanes 4r..4r+3.
-__device__ __forceinline__ float warp_sum8(const float (&v)[8], int lane) {
-    float a[4], b[2];
-    bool up = (lane & 16) != 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float send = up ? v[i] : v[i + 4], keep = up ? v[i + 4] : v[i];
-        a[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-    }
-    up = (lane & 8) != 0;
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const float send = up ? a[i] : a[i + 2], keep = up ? a[i + 2] : a[i];
-        b[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-    }
-    up = (lane & 4) != 0;
-    const float send = up ? b[0] : b[1], keep = up ? b[1] : b[0];
+// The two dot products a lane takes part in (its rows A and B) summed over the 8 lanes that share
+// the rows, in 3 shuffles: the lanes first swap the half they do not keep, then butterfly over the
+// remaining four. Lanes 0-3 of the group end with row A's total, lanes 4-7 with row B's.
+__device__ __forceinline__ float group_sum2(float a, float b, bool upper) {
+    const float send = upper ? a : b, keep = upper ? b : a;
     float c = keep + __shfl_xor_sync(0xffffffffu, send, 4);
     c += __shfl_xor_sync(0xffffffffu, c, 2);
     c += __shfl_xor_sync(0xffffffffu, c, 1);
     return c;
 }
 
-template <int NPL>
-__device__ __forceinline__ void load_vec(float (&dst)[NPL], const float *src) {
-    if constexpr (NPL == 4) {
-        const float4 t = *reinterpret_cast<const float4 *>(src);
-        dst[0] = t.x; dst[1] = t.y; dst[2] = t.z; dst[3] = t.w;
-    } else if constexpr (NPL == 2) {
-        const float2 t = *reinterpret_cast<const float2 *>(src);
-        dst[0] = t.x; dst[1] = t.y;
-    } else {
-        dst[0] = *src;
-    }
+__device__ __forceinline__ float4 ld_f4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ void st_f4(float *p, const float4 &v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ float4 half4_to_float4(const uint2 &raw) {
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+    const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ float dot4(const float4 &s, const float4 &k, float acc) {
+    acc = fmaf(s.x, k.x, acc); acc = fmaf(s.y, k.y, acc);
+    acc = fmaf(s.z, k.z, acc); acc = fmaf(s.w, k.w, acc);
+    return acc;
 }
 
-template <int NPL>
-__device__ __forceinline__ void store_vec(float *dst, const float (&src)[NPL]) {
-    if constexpr (NPL == 4) {
-        *reinterpret_cast<float4 *>(dst) = make_float4(src[0], src[1], src[2], src[3]);
-    } else if constexpr (NPL == 2) {
-        *reinterpret_cast<float2 *>(dst) = make_float2(src[0], src[1]);
-    } else {
-        *dst = src[0];
-    }
+// exp(x) in about 8 instructions, ~2 ulp: the product x*log2(e) is carried as hi + lo so that
+// the only error left is that of ex2.approx (2^-22 relative); libm's expf costs three times as
+// much and this kernel is bound by instruction issue once several tokens share a state read.
+__device__ __forceinline__ float exp_2ulp(float x) {
+    constexpr float kL2eHi = 1.4426950408889634f, kL2eLo = 1.92596299112661746e-8f;
+    const float hi = x * kL2eHi;
+    float lo = fmaf(x, kL2eHi, -hi);
+    lo = fmaf(x, kL2eLo, lo);
+    const float r = fast_exp2(hi);
+    return fmaf(r, lo * 0.6931471805599453f, r);
+}
+// softplus(x) = log(1 + exp(x)), evaluated like the reference (gdn.metal:134-157: the sum is
+// formed in fp32 first), with lg2.approx (2^-22 absolute in log2 units on (0.5, 2), relative beyond).
+__device__ __forceinline__ float softplus_fast(float x) {
+    if (x > 20.f) return x;
+    return __log2f(1.f + exp_2ulp(x)) * 0.6931471805599453f;
 }
 
-template <int NPL>
-__device__ __forceinline__ void load_half_vec(float (&dst)[NPL], const __half *src) {
-    if constexpr (NPL == 4) {
-        const uint2 raw = *reinterpret_cast<const uint2 *>(src);
-        const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
-        const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
-        dst[0] = lo.x; dst[1] = lo.y; dst[2] = hi.x; dst[3] = hi.y;
-    } else if constexpr (NPL == 2) {
-        const float2 t = __half22float2(*reinterpret_cast<const __half2 *>(src));
-        dst[0] = t.x; dst[1] = t.y;
-    } else {
-        dst[0] = __half2float(*src);
-    }
+__device__ __forceinline__ void cp_async8(void *dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async4(void *dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// grid = (dv blocks, Hv, sessions), block = 128.
-template <int NPL>
-__global__ void __launch_bounds__(kWarps * 32) gdn_step_kernel(GdnParams p) {
+// Persistent, warp-granular pipeline. A work item is 8 consecutive state rows of one (session,
+// head): 8*Dk*4 contiguous bytes. Warp w of CTA c takes items (iter*gridDim.x + c)*4 + w, so the four
+// warps of a CTA stream adjacent pieces. Every warp owns two rings in shared memory:
+//   * state ring, kSlots items: lane 0 fills a slot with one bulk copy (completion on the slot's
+//     mbarrier); a slot is free again as soon as its rows sit in registers, so kSlots items are in
+//     flight while one more is applied;
+//   * token ring, kTokDepth (item, token) pairs ahead: each pair's q, k and v pieces arrive by
+//     8-byte cp.async, its two gate scalars as the aligned 4-byte words that contain them (a
+//     register destination would make every later read of that register wait for the load).
+// Token inputs are requested kTokDepth tokens before they are used because under a saturated
+// memory system one token of arithmetic (a few hundred cycles) hides nothing of a load.
+// The warps never synchronise with each other after the tables below are staged.
+//
+// Register layout: the 8 lanes of group g = lane/8 share rows 2g and 2g+1; lane l of the group owns
+// the 16-byte column chunks l, l+8, l+16, ... of both rows (Dk/8 floats per row), so a row's dot
+// product is 3 shuffles away and shared-memory / global accesses of a group are 128 contiguous bytes.
+//
+// grid = min(ceil(items / 4), 3 * SMs), block = 128.
+template <int DK>
+__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm)
+gdn_step_kernel(GdnParams p, uint32_t n_sessions, uint32_t n_items, uint32_t *__restrict__ status) {
+    constexpr int C = DK / 32;                       // 16-byte chunks per lane per row
+    constexpr uint32_t kItemFloats = kRowsPerWarp * DK;
+    constexpr uint32_t kItemBytes = kItemFloats * 4;
+    constexpr uint32_t kTokHalves = 2 * DK + kRowsPerWarp + 4;   // q | k | v of the 8 rows | a word | b word
+    constexpr uint32_t kWarpBytes = kSlots * kItemBytes + kTokDepth * kTokHalves * 2;
+    extern __shared__ __align__(128) unsigned char gdn_smem[];
+    __shared__ uint64_t bars_all[kWarps][kSlots];
+    __shared__ tt_gdn_session ses_tab[kSmemSessions];
+    __shared__ float2 head_tab[kSmemHeads];          // (decay coefficient, dt_bias) per value head
+
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t h = blockIdx.y;
-    const tt_gdn_session ses = p.sessions[blockIdx.z];
-    const uint32_t dv0 = blockIdx.x * kRowsPerCta + warp * kRowsPerWarp;
-    const uint32_t hk = (p.flags & TT_GDN_V_TILED) ? h % p.hk : h / (p.hv / p.hk);
-    const uint32_t col = lane * NPL;
+    const int l = lane & 7;
+    const bool upper = (lane & 4) != 0;
+    const uint32_t row_a = (lane >> 3) * 2;          // this lane's rows inside the item: row_a, row_a + 1
+    float *ring = reinterpret_cast<float *>(gdn_smem + (size_t)warp * kWarpBytes);
+    __half *tok_ring = reinterpret_cast<__half *>(gdn_smem + (size_t)warp * kWarpBytes + kSlots * kItemBytes);
+    uint64_t *bars = bars_all[warp];
+    const uint32_t blocks_per_head = p.dv / kRowsPerWarp;
+    const uint32_t stride = gridDim.x * kWarps;
+    const uint32_t first = blockIdx.x * kWarps + warp;
+    const bool f32_gates = (p.flags & TT_GDN_GATES_F32) != 0;
+    const uint32_t gate_bytes = f32_gates ? 4 : 2;
 
-    float *state = ses.state + ((size_t)h * p.dv) * p.dk;
-    float s[kRowsPerWarp][NPL];
-#pragma unroll
-    for (int r = 0; r < kRowsPerWarp; ++r) {
-        if (dv0 + r < p.dv) {
-            load_vec<NPL>(s[r], state + (size_t)(dv0 + r) * p.dk + col);
-        } else {
-#pragma unroll
-            for (int i = 0; i < NPL; ++i) s[r][i] = 0.f;
-        }
-    }
+    // session table and per-head decay parameters: staged once so that the item loop never waits
+    // on a dependent global load for a pointer
+    const bool tab_in_smem = n_sessions <= kSmemSessions;
+    const bool heads_in_smem = !f32_gates && p.hv <= kSmemHeads;
+    auto head_params = [&](uint32_t h) {
+        float a = __bfloat162float(p.a_log[h]);
+        if (!(p.flags & TT_GDN_A_LOG_PREEXP)) a = -expf(a);
+        return make_float2(a, __bfloat162float(p.dt_bias[h]));
+    };
+    const tt_gdn_session *tab = p.sessions;   // switched to the staged copy once it is complete
 
-    const float a_param = __bfloat162float(p.a_log[h]);
-    const float dtb = __bfloat162float(p.dt_bias[h]);
-    const bool rows_valid = dv0 < p.dv;   // value_dim is a multiple of 8: a warp's 8 rows are all in or all out
-
-    // One token's inputs; the next token's are fetched while the current one is being applied,
-    // so the multi-row form does not pay a global-load latency per token.
-    struct Tok { float q[NPL], k[NPL], v[kRowsPerWarp], g, beta; };
-    auto load_tok = [&](uint32_t t, Tok &tok) {
-        const __half *row = reinterpret_cast<const __half *>(ses.conv_out) + (size_t)t * p.row_stride;
-        load_half_vec<NPL>(tok.q, row + (size_t)hk * p.dk + col);
-        load_half_vec<NPL>(tok.k, row + (size_t)p.hk * p.dk + (size_t)hk * p.dk + col);
-        const __half *vrow = row + (size_t)2 * p.hk * p.dk + (size_t)h * p.dv;
-        if (rows_valid) {
-            const uint2 lo = *reinterpret_cast<const uint2 *>(vrow + dv0);
-            const uint2 hi = *reinterpret_cast<const uint2 *>(vrow + dv0 + 4);
-            const float2 v0 = __half22float2(*reinterpret_cast<const __half2 *>(&lo.x));
-            const float2 v1 = __half22float2(*reinterpret_cast<const __half2 *>(&lo.y));
-            const float2 v2 = __half22float2(*reinterpret_cast<const __half2 *>(&hi.x));
-            const float2 v3 = __half22float2(*reinterpret_cast<const __half2 *>(&hi.y));
-            tok.v[0] = v0.x; tok.v[1] = v0.y; tok.v[2] = v1.x; tok.v[3] = v1.y;
-            tok.v[4] = v2.x; tok.v[5] = v2.y; tok.v[6] = v3.x; tok.v[7] = v3.y;
+    // item -> (session, head, first row)
+    struct Where { uint32_t z, h, dv0; };
+    auto where = [&](uint32_t item) {
+        Where w;
+        if (p.shift_blocks != 0xffu) {      // both divisors are powers of two (the usual shapes)
+            const uint32_t hb = item >> p.shift_blocks;
+            w.dv0 = (item & (blocks_per_head - 1)) * kRowsPerWarp;
+            w.z = hb >> p.shift_heads;
+            w.h = hb & (p.hv - 1);
         } else {
-#pragma unroll
-            for (int r = 0; r < kRowsPerWarp; ++r) tok.v[r] = 0.f;
+            const uint32_t hb = item / blocks_per_head;
+            w.dv0 = (item - hb * blocks_per_head) * kRowsPerWarp;
+            w.z = hb / p.hv;
+            w.h = hb - w.z * p.hv;
         }
-        if (p.flags & TT_GDN_GATES_F32) {
-            tok.g = reinterpret_cast<const float *>(ses.a)[(size_t)t * p.hv + h];
-            tok.beta = reinterpret_cast<const float *>(ses.b)[(size_t)t * p.hv + h];
-        } else {
-            const float av = __half2float(reinterpret_cast<const __half *>(ses.a)[(size_t)t * p.hv + h]);
-            const float bv = __half2float(reinterpret_cast<const __half *>(ses.b)[(size_t)t * p.hv + h]);
-            const float x = av + dtb;
-            const float sp = x > 20.f ? x : logf(1.f + expf(x));
-            tok.g = (p.flags & TT_GDN_A_LOG_PREEXP) ? expf(a_param * sp) : expf(-expf(a_param) * sp);
-            tok.beta = 1.f / (1.f + expf(-bv));
-        }
+        return w;
+    };
+    auto issue = [&](uint32_t item, uint32_t slot) {      // lane 0 only
+        const Where w = where(item);
+        const float *src = tab[w.z].state + ((size_t)w.h * p.dv + w.dv0) * DK;
+        mbar_expect_tx(&bars[slot], kItemBytes);
+        bulk_copy_g2s(ring + slot * kItemFloats, src, kItemBytes, &bars[slot]);
     };
 
-    Tok cur;
-    load_tok(0, cur);
-    for (uint32_t t = 0; t < p.rows; ++t) {
-        Tok nxt = cur;
-        if (t + 1 < p.rows) load_tok(t + 1, nxt);
-        float q[NPL], k[NPL];
-#pragma unroll
-        for (int i = 0; i < NPL; ++i) { q[i] = cur.q[i]; k[i] = cur.k[i]; }
-        const float g = cur.g, beta = cur.beta;
+    // the first state copies leave before anything else; the tables are staged while they fly
+    if (lane == 0) {
+        for (uint32_t s = 0; s < kSlots; ++s) mbar_init(&bars[s], 1);
+        mbar_fence_init();
+        for (uint32_t s = 0; s < kSlots; ++s)
+            if (first + s * stride < n_items) issue(first + s * stride, s);
+    }
+    if (tab_in_smem)
+        for (uint32_t i = threadIdx.x; i < n_sessions; i += blockDim.x) ses_tab[i] = p.sessions[i];
+    if (heads_in_smem)
+        for (uint32_t h = threadIdx.x; h < p.hv; h += blockDim.x) head_tab[h] = head_params(h);
+    __syncthreads();
+    if (tab_in_smem) tab = ses_tab;
 
-        float kv[kRowsPerWarp];
+    // ---- token prefetch cursor: walks the (item, token) pairs kTokDepth ahead of the consumer
+    struct Cursor {
+        uint32_t item, t;
+        const __half *q;       // q piece base of token 0: conv_out + hk*DK
+        const __half *v;       // v base of token 0 for this item's rows
+        const char *a, *b;     // gate scalars of token 0 for this item's head
+    } pf;
+    auto cursor_set = [&](uint32_t item) {
+        pf.item = item; pf.t = 0;
+        if (item >= n_items) return;
+        const Where w = where(item);
+        const uint32_t hk = (p.flags & TT_GDN_V_TILED) ? w.h % p.hk : w.h / (p.hv / p.hk);
+        const tt_gdn_session &ses = tab[w.z];
+        const __half *conv = reinterpret_cast<const __half *>(ses.conv_out);
+        pf.q = conv + (size_t)hk * DK;
+        pf.v = conv + (size_t)2 * p.hk * DK + (size_t)w.h * p.dv + w.dv0;
+        pf.a = reinterpret_cast<const char *>(ses.a) + (size_t)w.h * gate_bytes;
+        pf.b = reinterpret_cast<const char *>(ses.b) + (size_t)w.h * gate_bytes;
+    };
+    auto prefetch = [&](uint32_t pair) {
+        if (pf.item < n_items) {
+            __half *entry = tok_ring + (pair % kTokDepth) * kTokHalves;
+            const size_t row = (size_t)pf.t * p.row_stride;
+            const __half *qk = pf.q + row;
 #pragma unroll
-        for (int r = 0; r < kRowsPerWarp; ++r) {
-            float acc = 0.f;
-#pragma unroll
-            for (int i = 0; i < NPL; ++i) {
-                s[r][i] *= g;
-                acc = fmaf(s[r][i], k[i], acc);
+            for (int piece = lane; piece < DK / 2; piece += 32) {
+                // pieces [0, DK/4) are q, [DK/4, DK/2) are k (which sits hk_count*DK after q)
+                const __half *src = qk + 4 * piece + (4 * piece < DK ? 0 : (size_t)p.hk * DK - DK);
+                cp_async8(entry + 4 * piece, src);
             }
-            kv[r] = acc;
-        }
-        {   // all eight S.k sums, then every lane fetches the eight totals (row r sits in lane 4r)
-            const float mine = warp_sum8(kv, lane);
-#pragma unroll
-            for (int r = 0; r < kRowsPerWarp; ++r) kv[r] = __shfl_sync(0xffffffffu, mine, r << 2);
-        }
-
-        float out[kRowsPerWarp];
-#pragma unroll
-        for (int r = 0; r < kRowsPerWarp; ++r) {
-            const float vv = cur.v[r];
-            const float delta = (vv - kv[r]) * beta;
-            float acc = 0.f;
-#pragma unroll
-            for (int i = 0; i < NPL; ++i) {
-                s[r][i] = fmaf(k[i], delta, s[r][i]);
-                acc = fmaf(s[r][i], q[i], acc);
+            if (lane < 2) cp_async8(entry + 2 * DK + 4 * lane, pf.v + row + 4 * lane);
+            if (lane == 2 || lane == 3) {
+                // the aligned word holding the scalar: it shares the scalar's page, so the two
+                // neighbouring bytes of a 16-bit gate are always readable
+                const char *g = (lane == 2 ? pf.a : pf.b) + (size_t)pf.t * p.hv * gate_bytes;
+                cp_async4(entry + 2 * DK + kRowsPerWarp + 2 * (lane - 2),
+                          reinterpret_cast<const char *>(reinterpret_cast<uintptr_t>(g) & ~(uintptr_t)3));
             }
-            out[r] = acc;
+            if (++pf.t == p.rows) cursor_set(pf.item + stride);
         }
-        // S.q sums: lane 4r holds row r's readout and stores it
-        const float mine = warp_sum8(out, lane);
-        if ((lane & 3) == 0 && rows_valid) {
-            __half *y = reinterpret_cast<__half *>(ses.y) + (size_t)t * p.hv * p.dv + (size_t)h * p.dv;
-            y[dv0 + (lane >> 2)] = __float2half_rn(mine * p.readout_scale);
+        cp_async_commit();   // one group per pair, empty or not, so the wait below counts pairs
+    };
+
+    cursor_set(first);
+    for (uint32_t j = 0; j < kTokDepth; ++j) prefetch(j);
+
+    bool timed_out = false;
+    uint32_t iter = 0, pair = 0;
+    for (uint32_t item = first; item < n_items; item += stride, ++iter) {
+        const uint32_t slot = iter % kSlots;
+        const Where w = where(item);
+        const tt_gdn_session ses = tab[w.z];
+        float2 hp = make_float2(0.f, 0.f);
+        if (!f32_gates) hp = heads_in_smem ? head_tab[w.h] : head_params(w.h);
+        if (!warp_all(mbar_wait(&bars[slot], (iter / kSlots) & 1))) { timed_out = true; break; }
+
+        float4 sa[C], sb[C];
+        {
+            const float *src = ring + slot * kItemFloats + row_a * DK + 4 * l;
+#pragma unroll
+            for (int j = 0; j < C; ++j) { sa[j] = ld_f4(src + 32 * j); sb[j] = ld_f4(src + DK + 32 * j); }
+        }
+        __syncwarp();   // every lane holds its part of the slot: it may be refilled
+        const uint32_t refill = item + kSlots * stride;
+        if (lane == 0 && refill < n_items) issue(refill, slot);
+
+        const size_t lane_off = ((size_t)w.h * p.dv + w.dv0 + row_a) * DK + 4 * l;
+
+        for (uint32_t t = 0; t < p.rows; ++t, ++pair) {
+            cp_async_wait<kTokDepth - 1>();   // this lane's pieces of `pair` have landed ...
+            __syncwarp();                     // ... and so have everyone else's
+            const __half *entry = tok_ring + (pair % kTokDepth) * kTokHalves;
+            const uint2 gw = *reinterpret_cast<const uint2 *>(entry + 2 * DK + kRowsPerWarp);
+            float g, beta;
+            if (f32_gates) {
+                g = __uint_as_float(gw.x); beta = __uint_as_float(gw.y);
+            } else {
+                const size_t gi = ((size_t)t * p.hv + w.h) * 2;
+                const uint32_t sh_a = ((reinterpret_cast<uintptr_t>(ses.a) + gi) & 2) * 8;
+                const uint32_t sh_b = ((reinterpret_cast<uintptr_t>(ses.b) + gi) & 2) * 8;
+                const float raw_a = __half2float(__ushort_as_half((unsigned short)(gw.x >> sh_a)));
+                const float raw_b = __half2float(__ushort_as_half((unsigned short)(gw.y >> sh_b)));
+                const float x = raw_a + hp.y;
+                g = exp_2ulp(hp.x * softplus_fast(x));
+                beta = __frcp_rn(1.f + exp_2ulp(-raw_b));
+            }
+            const float2 vv = __half22float2(*reinterpret_cast<const __half2 *>(entry + 2 * DK + row_a));
+            const __half *qs = entry + 4 * l, *ks = entry + DK + 4 * l;
+
+            // decay, then S.k for both rows
+            float4 k4[C];
+            float ka = 0.f, kb = 0.f;
+#pragma unroll
+            for (int j = 0; j < C; ++j) {
+                k4[j] = half4_to_float4(*reinterpret_cast<const uint2 *>(ks + 32 * j));
+                sa[j].x *= g; sa[j].y *= g; sa[j].z *= g; sa[j].w *= g;
+                sb[j].x *= g; sb[j].y *= g; sb[j].z *= g; sb[j].w *= g;
+                ka = dot4(sa[j], k4[j], ka);
+                kb = dot4(sb[j], k4[j], kb);
+            }
+            const float mine = group_sum2(ka, kb, upper);
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 4);
+            const float da = (vv.x - (upper ? other : mine)) * beta;
+            const float db = (vv.y - (upper ? mine : other)) * beta;
+
+            // rank-one update, then the readout S.q
+            float ya = 0.f, yb = 0.f;
+#pragma unroll
+            for (int j = 0; j < C; ++j) {
+                const float4 q4 = half4_to_float4(*reinterpret_cast<const uint2 *>(qs + 32 * j));
+                sa[j].x = fmaf(k4[j].x, da, sa[j].x); sa[j].y = fmaf(k4[j].y, da, sa[j].y);
+                sa[j].z = fmaf(k4[j].z, da, sa[j].z); sa[j].w = fmaf(k4[j].w, da, sa[j].w);
+                sb[j].x = fmaf(k4[j].x, db, sb[j].x); sb[j].y = fmaf(k4[j].y, db, sb[j].y);
+                sb[j].z = fmaf(k4[j].z, db, sb[j].z); sb[j].w = fmaf(k4[j].w, db, sb[j].w);
+                ya = dot4(sa[j], q4, ya);
+                yb = dot4(sb[j], q4, yb);
+            }
+            __syncwarp();                       // every lane has read the entry: it may be refilled
+            prefetch(pair + kTokDepth);
+
+            const float y_mine = group_sum2(ya, yb, upper);
+            if ((lane & 3) == 0) {     // lane 0 of the group holds row A's readout, lane 4 row B's
+                __half *y = reinterpret_cast<__half *>(ses.y) + (size_t)t * p.hv * p.dv + (size_t)w.h * p.dv;
+                y[w.dv0 + row_a + (upper ? 1 : 0)] = __float2half_rn(y_mine * p.readout_scale);
+            }
+
+            if (t == 0 && ses.checkpoint_state != nullptr) {
+                float *ck = ses.checkpoint_state + lane_off;
+#pragma unroll
+                for (int j = 0; j < C; ++j) { st_f4(ck + 32 * j, sa[j]); st_f4(ck + DK + 32 * j, sb[j]); }
+            }
         }
 
-        if (t == 0 && ses.checkpoint_state != nullptr) {
-            float *ck = ses.checkpoint_state + ((size_t)h * p.dv) * p.dk;
+        float *dst = ses.state + lane_off;
 #pragma unroll
-            for (int r = 0; r < kRowsPerWarp; ++r)
-                if (dv0 + r < p.dv) store_vec<NPL>(ck + (size_t)(dv0 + r) * p.dk + col, s[r]);
-        }
-        cur = nxt;
+        for (int j = 0; j < C; ++j) { st_f4(dst + 32 * j, sa[j]); st_f4(dst + DK + 32 * j, sb[j]); }
     }
 
-#pragma unroll
-    for (int r = 0; r < kRowsPerWarp; ++r)
-        if (dv0 + r < p.dv) store_vec<NPL>(state + (size_t)(dv0 + r) * p.dk + col, s[r]);
+    cp_async_wait<0>();
+    if (timed_out) {
+        // leave the state of the unprocessed items untouched; give the copies still in flight a
+        // bounded chance to land before the shared memory is released
+        if (lane == 0) {
+            atomicOr(status, TT_DEV_WAIT_TIMEOUT);
+            for (uint32_t k = 0; k < kSlots; ++k) {
+                const uint32_t it = iter + k;
+                if (first + (size_t)it * stride < n_items) mbar_wait(&bars[it % kSlots], (it / kSlots) & 1, 1u << 16);
+            }
+        }
+        __syncwarp();
+    }
 }
 
 int validate_shape(tt_context *ctx, const tt_gdn_shape *shape, uint32_t rows, uint32_t row_stride) {
@@ -262,14 +379,32 @@ int launch_step(tt_context *ctx, cudaStream_t stream, const tt_gdn_session *h_se
     p.dt_bias = reinterpret_cast<const __nv_bfloat16 *>(f32_gates && !dt_bias ? ctx->gdn_sessions : dt_bias);
     p.hk = shape->n_k_heads; p.hv = shape->n_v_heads; p.dk = shape->key_dim; p.dv = shape->value_dim;
     p.rows = rows; p.row_stride = row_stride; p.flags = shape->flags; p.readout_scale = shape->readout_scale;
-    const dim3 grid((shape->value_dim + kRowsPerCta - 1) / kRowsPerCta, shape->n_v_heads, n);
-    switch (shape->key_dim) {
-        case 128: gdn_step_kernel<4><<<grid, kWarps * 32, 0, stream>>>(p); break;
-        case 64: gdn_step_kernel<2><<<grid, kWarps * 32, 0, stream>>>(p); break;
-        default: gdn_step_kernel<1><<<grid, kWarps * 32, 0, stream>>>(p); break;
+    {
+        const uint32_t nb = shape->value_dim / kRowsPerWarp, nh = shape->n_v_heads;
+        const bool pow2 = (nb & (nb - 1)) == 0 && (nh & (nh - 1)) == 0;
+        p.shift_blocks = pow2 ? (uint32_t)__builtin_ctz(nb) : 0xffu;
+        p.shift_heads = pow2 ? (uint32_t)__builtin_ctz(nh) : 0xffu;
     }
+    const uint32_t n_items = n * shape->n_v_heads * (shape->value_dim / kRowsPerWarp);
+    const uint32_t grid = std::min((n_items + kWarps - 1) / kWarps, (uint32_t)(kCtasPerSm * ctx->sm_count));
+    const size_t smem = (size_t)kWarps * (kSlots * kRowsPerWarp * shape->key_dim * sizeof(float) +
+                                          kTokDepth * (2 * shape->key_dim + kRowsPerWarp + 4) * sizeof(__half));
+    TTLaunchTimer timer(ctx, stream, TT_PROFILE_GDN_STEP);
+    auto launch = [&](auto kernel) {
+        cudaError_t le = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (le != cudaSuccess) return le;
+        kernel<<<grid, kWarps * 32, smem, stream>>>(p, n, n_items, ctx->status);
+        return cudaSuccess;
+    };
+    switch (shape->key_dim) {
+        case 128: e = launch(gdn_step_kernel<128>); break;
+        case 64: e = launch(gdn_step_kernel<64>); break;
+        default: e = launch(gdn_step_kernel<32>); break;
+    }
+    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn_step shared memory attribute");
     e = cudaGetLastError();
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn_step launch");
+    timer.stop();
     ctx->launches++;
     return TT_OK;
 }

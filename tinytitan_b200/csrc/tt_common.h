@@ -68,9 +68,9 @@ struct tt_context {
     uint32_t *h_keys = nullptr;
     uint32_t *h_rows = nullptr;
     uint64_t launches = 0;
-    // optional per-launch timing of the dominant (split-KV pass 1) kernel
+    // optional per-launch timing of the selected kernel classes (mask of TT_PROFILE_*)
     static constexpr uint32_t kProfileSlots = 256;
-    bool profiling = false;
+    int profiling = 0;
     uint32_t profile_count = 0;
     cudaEvent_t *profile_begin = nullptr;
     cudaEvent_t *profile_end = nullptr;
@@ -79,6 +79,22 @@ struct tt_context {
 };
 
 int tt_set_error(tt_context *ctx, int code, const char *fmt, ...);
+
+// Brackets one kernel launch with an event pair when the context profiles its class.
+struct TTLaunchTimer {
+    tt_context *ctx;
+    cudaStream_t stream;
+    bool timed;
+    TTLaunchTimer(tt_context *c, cudaStream_t s, int kernel_class)
+        : ctx(c), stream(s),
+          timed((c->profiling & kernel_class) != 0 && c->profile_count < tt_context::kProfileSlots) {
+        if (timed) cudaEventRecord(c->profile_begin[c->profile_count], s);
+    }
+    void stop() {
+        if (timed) cudaEventRecord(ctx->profile_end[ctx->profile_count++], stream);
+        timed = false;
+    }
+};
 int tt_check_cuda(tt_context *ctx, cudaError_t e, const char *what);
 
 struct TTBusyGuard {

@@ -79,11 +79,15 @@ class Context:
     def synchronize(self, command_buffer=None):
         self.check(L.lib().tt_stream_synchronize(self.handle, _stream(command_buffer)))
 
-    def profile_enable(self, enabled: bool = True):
+    PROFILE_DECODE_PARTIAL = 1
+    PROFILE_GDN_STEP = 2
+
+    def profile_enable(self, enabled=True):
+        """`enabled`: False/0 off, True/1 the split-KV pass-1 kernel, or a mask of PROFILE_*."""
         self.check(L.lib().tt_ctx_profile_enable(self.handle, int(enabled)))
 
     def profile_collect(self):
-        """Durations (ms) of the split-KV pass-1 launches recorded since the last collect."""
+        """Durations (ms), in launch order, of the profiled launches recorded since the last collect."""
         buf = (C.c_float * 256)()
         n = C.c_uint32(0)
         self.check(L.lib().tt_ctx_profile_collect(self.handle, buf, 256, C.byref(n)))
