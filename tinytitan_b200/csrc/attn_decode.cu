@@ -16,6 +16,8 @@
 // capturable in a CUDA graph.
 #include "tt_sm100.h"
 
+#include <cstdlib>
+
 namespace {
 
 constexpr int kKeysPerBlock = 16;   // keys per warp pipeline stage
@@ -911,6 +913,65 @@ TT_API void tt_attn_reference_split_geometry(uint32_t n_q_heads, uint32_t n_kv_h
     out->use_swa_grouped_partial = swa_grouped ? 1u : 0u;
 }
 
+int tt_launch_verify_tc(tt_context *ctx, cudaStream_t stream, uint32_t n_sessions, uint32_t n_items, float *part_o,
+                        float *part_m, float *part_l, const tt_attn_batch_params *p);
+
+// Split plan of the tensor-core verify pass: one item per (session, kv head, key range) serving all
+// packed rows. One CTA is resident per SM, so ~3 items per SM; an item is at least four 128-key tiles
+// so that staging Q and filling the pipeline stay a small part of it, and the parts of one session
+// are of equal length. False when the partials or the items do not fit the context.
+static bool plan_wide(tt_context *ctx, const TTDecodeSession *in_sessions, uint32_t n_sessions,
+                      const tt_attn_batch_params *p, const uint32_t *keys, uint32_t *out_items,
+                      uint32_t *out_partial_rows, uint32_t *out_max_rows) {
+    uint64_t key_rows = 0;
+    for (uint32_t i = 0; i < n_sessions; ++i) key_rows += (uint64_t)keys[i] * p->n_kv_heads;
+    uint64_t target = key_rows / ((uint64_t)ctx->sm_count * 3u);
+    target = (target + 127) / 128 * 128;
+    if (target < 512) target = 512;
+    for (;;) {
+        uint64_t items = 0, prows = 0;
+        bool all_single = true;
+        for (uint32_t i = 0; i < n_sessions; ++i) {
+            uint32_t parts = ceil_div_u32(keys[i], target);
+            if (parts == 0) parts = 1;
+            if (parts > 1) all_single = false;
+            items += (uint64_t)parts * p->n_kv_heads;
+            prows += (uint64_t)parts * in_sessions[i].q_rows * p->n_q_heads;
+        }
+        if (prows * ((uint64_t)p->head_dim + 2) * sizeof(float) <= ctx->workspace_bytes && items <= ctx->max_items) break;
+        if (all_single) return false;
+        target *= 2;
+    }
+    uint32_t partial_cursor = 0, item_cursor = 0, max_rows = 0;
+    const uint32_t group = p->n_q_heads / p->n_kv_heads;
+    for (uint32_t i = 0; i < n_sessions; ++i) {
+        TTDecodeSession s = in_sessions[i];
+        uint32_t parts = ceil_div_u32(keys[i], target);
+        if (parts == 0) parts = 1;
+        const uint32_t len = (ceil_div_u32(keys[i], parts) + 127) / 128 * 128;
+        const uint32_t rows_total = s.q_rows * p->n_q_heads;
+        s.n_parts = parts;
+        s.partial_base = partial_cursor;
+        ctx->h_sessions[i] = s;
+        if (rows_total > max_rows) max_rows = rows_total;
+        for (uint32_t part = 0; part < parts; ++part) {
+            const uint32_t kb = s.kv_start + part * len;
+            uint32_t ke = kb + len;
+            if (ke > s.seq_len) ke = s.seq_len;
+            if (ke < kb) ke = kb;
+            for (uint32_t kvh = 0; kvh < p->n_kv_heads; ++kvh) {
+                TTDecodeItem &it = ctx->h_items[item_cursor++];
+                it.session = i; it.kv_head = kvh; it.key_begin = kb; it.key_end = ke;
+                it.part_index = part; it.row_begin = 0; it.row_count = s.q_rows * group;
+                it.partial_base = s.partial_base;
+            }
+        }
+        partial_cursor += parts * rows_total;
+    }
+    *out_items = item_cursor; *out_partial_rows = partial_cursor; *out_max_rows = max_rows;
+    return true;
+}
+
 // mode 0: write normalised outputs to the sessions' `out`; mode 1: one merged triple for a
 // single session (m_out/d_out/o_out).
 int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession *in_sessions,
@@ -966,45 +1027,56 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
         keys[i] = s.seq_len > s.kv_start ? s.seq_len - s.kv_start : 0u;
         rows[i] = s.q_rows;
     }
-    uint32_t keys_per_item = 0, n_items = 0;
-    int rc = tt_attn_plan_splits(keys, rows, n_sessions, p->head_dim, p->n_q_heads, p->n_kv_heads,
-                                 (uint32_t)ctx->sm_count, ctx->workspace_bytes, &keys_per_item, &n_items);
-    if (rc != TT_OK) return tt_set_error(ctx, rc, "split-KV partials do not fit the context workspace");
-    if (n_items > ctx->max_items)
-        return tt_set_error(ctx, TT_ERR_OOM, "%u work items exceed the context's item table (%u)", n_items,
-                            ctx->max_items);
-
-    const uint32_t rows_per_item = 16u;
-
-    // Build the session and item tables.
-    uint32_t partial_cursor = 0, item_cursor = 0, max_rows = 0;
-    for (uint32_t i = 0; i < n_sessions; ++i) {
-        TTDecodeSession s = in_sessions[i];
-        uint32_t parts = ceil_div_u32(keys[i], keys_per_item);
-        if (parts == 0) parts = 1;
-        const uint32_t rows_total = s.q_rows * p->n_q_heads;
-        s.n_parts = parts;
-        s.partial_base = partial_cursor;
-        ctx->h_sessions[i] = s;
-        if (rows_total > max_rows) max_rows = rows_total;
-        const uint32_t packed_rows = s.q_rows * group;
-        for (uint32_t part = 0; part < parts; ++part) {
-            const uint32_t kb = s.kv_start + part * keys_per_item;
-            uint32_t ke = kb + keys_per_item;
-            if (ke > s.seq_len) ke = s.seq_len;
-            if (ke < kb) ke = kb;
-            for (uint32_t kvh = 0; kvh < p->n_kv_heads; ++kvh)
-                for (uint32_t rb = 0; rb < packed_rows; rb += rows_per_item) {
-                    TTDecodeItem &it = ctx->h_items[item_cursor++];
-                    it.session = i; it.kv_head = kvh; it.key_begin = kb; it.key_end = ke;
-                    it.part_index = part; it.row_begin = rb;
-                    it.row_count = packed_rows - rb < rows_per_item ? packed_rows - rb : rows_per_item;
-                    it.partial_base = s.partial_base;
-                }
-        }
-        partial_cursor += parts * rows_total;
+    // Verify batches (17..64 packed rows per KV head, head_dim 256, plain 16-bit rows) take the
+    // tensor-core pass 1: one item serves all packed rows of a (session, kv head, key range).
+    bool wide = !quantised && p->head_dim == 256 && getenv("TT_VERIFY_FORCE_MMA_SYNC") == nullptr;
+    for (uint32_t i = 0; wide && i < n_sessions; ++i) {
+        const TTDecodeSession &s = in_sessions[i];
+        const uint32_t packed = s.q_rows * group;
+        wide = packed > 16 && packed <= 64 && s.ring_capacity == 0 && s.keep == nullptr && s.row_index == nullptr;
     }
-    if (item_cursor != n_items) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "internal: item count mismatch");
+
+    uint32_t keys_per_item = 0, n_items = 0;
+    uint32_t partial_cursor = 0, item_cursor = 0, max_rows = 0;
+    if (wide) wide = plan_wide(ctx, in_sessions, n_sessions, p, keys, &n_items, &partial_cursor, &max_rows);
+    if (!wide) {
+        int rc = tt_attn_plan_splits(keys, rows, n_sessions, p->head_dim, p->n_q_heads, p->n_kv_heads,
+                                     (uint32_t)ctx->sm_count, ctx->workspace_bytes, &keys_per_item, &n_items);
+        if (rc != TT_OK) return tt_set_error(ctx, rc, "split-KV partials do not fit the context workspace");
+        if (n_items > ctx->max_items)
+            return tt_set_error(ctx, TT_ERR_OOM, "%u work items exceed the context's item table (%u)", n_items,
+                                ctx->max_items);
+
+        const uint32_t rows_per_item = 16u;
+        // Build the session and item tables.
+        for (uint32_t i = 0; i < n_sessions; ++i) {
+            TTDecodeSession s = in_sessions[i];
+            uint32_t parts = ceil_div_u32(keys[i], keys_per_item);
+            if (parts == 0) parts = 1;
+            const uint32_t rows_total = s.q_rows * p->n_q_heads;
+            s.n_parts = parts;
+            s.partial_base = partial_cursor;
+            ctx->h_sessions[i] = s;
+            if (rows_total > max_rows) max_rows = rows_total;
+            const uint32_t packed_rows = s.q_rows * group;
+            for (uint32_t part = 0; part < parts; ++part) {
+                const uint32_t kb = s.kv_start + part * keys_per_item;
+                uint32_t ke = kb + keys_per_item;
+                if (ke > s.seq_len) ke = s.seq_len;
+                if (ke < kb) ke = kb;
+                for (uint32_t kvh = 0; kvh < p->n_kv_heads; ++kvh)
+                    for (uint32_t rb = 0; rb < packed_rows; rb += rows_per_item) {
+                        TTDecodeItem &it = ctx->h_items[item_cursor++];
+                        it.session = i; it.kv_head = kvh; it.key_begin = kb; it.key_end = ke;
+                        it.part_index = part; it.row_begin = rb;
+                        it.row_count = packed_rows - rb < rows_per_item ? packed_rows - rb : rows_per_item;
+                        it.partial_base = s.partial_base;
+                    }
+            }
+            partial_cursor += parts * rows_total;
+        }
+        if (item_cursor != n_items) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "internal: item count mismatch");
+    }
 
     float *part_o = ctx->partials;
     float *part_m = part_o + (size_t)partial_cursor * p->head_dim;
@@ -1012,7 +1084,7 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
 
     // One session: its descriptor travels in the kernel parameters and the items are derived from
     // the block index, so the two table uploads (and their latency) are skipped.
-    const bool single = n_sessions == 1;
+    const bool single = n_sessions == 1 && !wide;
     const TTDecodeSession single_ses = ctx->h_sessions[0];
     const uint32_t single_keys = single ? keys_per_item : 0u;
     cudaError_t e = cudaSuccess;
@@ -1025,7 +1097,10 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     }
 
     TTLaunchTimer timer(ctx, stream, TT_PROFILE_DECODE_PARTIAL);
-    if (quantised)
+    if (wide) {
+        const int rc = tt_launch_verify_tc(ctx, stream, n_sessions, n_items, part_o, part_m, part_l, p);
+        if (rc != TT_OK) return rc;
+    } else if (quantised)
         e = launch_partial_quant(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status,
                                  single_ses, single_keys, quant, meta_bytes);
     else if (p->io_dtype == TT_F16)

@@ -41,6 +41,7 @@ static void context_free(tt_context *ctx) {
     cudaFree(ctx->items);
     cudaFree(ctx->sessions);
     cudaFree(ctx->gdn_sessions);
+    cudaFree(ctx->tensor_maps);
     cudaFree(ctx->status);
     if (ctx->profile_begin) {
         for (uint32_t i = 0; i < tt_context::kProfileSlots; ++i) {
@@ -55,6 +56,7 @@ static void context_free(tt_context *ctx) {
     free(ctx->h_sessions_in);
     free(ctx->h_keys);
     free(ctx->h_rows);
+    free(ctx->h_tensor_maps);
     delete ctx;
 }
 
@@ -84,6 +86,7 @@ TT_API tt_context *tt_context_create(int device, const tt_context_options *optio
     ok = ok && cudaMalloc(&ctx->items, sizeof(TTDecodeItem) * ctx->max_items) == cudaSuccess;
     ok = ok && cudaMalloc(&ctx->sessions, sizeof(TTDecodeSession) * ctx->max_sessions) == cudaSuccess;
     ok = ok && cudaMalloc(&ctx->gdn_sessions, sizeof(tt_gdn_session) * ctx->max_sessions) == cudaSuccess;
+    ok = ok && cudaMalloc(&ctx->tensor_maps, (size_t)256 * ctx->max_sessions) == cudaSuccess;   // 2 x 128 B each
     ok = ok && cudaMalloc(&ctx->status, sizeof(uint32_t)) == cudaSuccess;
     ok = ok && cudaMemset(ctx->status, 0, sizeof(uint32_t)) == cudaSuccess;
     ctx->h_items = (TTDecodeItem *)malloc(sizeof(TTDecodeItem) * ctx->max_items);
@@ -91,7 +94,8 @@ TT_API tt_context *tt_context_create(int device, const tt_context_options *optio
     ctx->h_sessions_in = (TTDecodeSession *)malloc(sizeof(TTDecodeSession) * ctx->max_sessions);
     ctx->h_keys = (uint32_t *)malloc(sizeof(uint32_t) * ctx->max_sessions);
     ctx->h_rows = (uint32_t *)malloc(sizeof(uint32_t) * ctx->max_sessions);
-    ok = ok && ctx->h_items && ctx->h_sessions && ctx->h_sessions_in && ctx->h_keys && ctx->h_rows;
+    ctx->h_tensor_maps = aligned_alloc(128, (size_t)256 * ctx->max_sessions);
+    ok = ok && ctx->h_items && ctx->h_sessions && ctx->h_sessions_in && ctx->h_keys && ctx->h_rows && ctx->h_tensor_maps;
     if (!ok) {
         cudaGetLastError();
         context_free(ctx);

@@ -60,6 +60,7 @@ struct tt_context {
     TTDecodeItem *items = nullptr;
     TTDecodeSession *sessions = nullptr;
     void *gdn_sessions = nullptr;       // tt_gdn_session[max_sessions]
+    void *tensor_maps = nullptr;        // CUtensorMap[2 * max_sessions]: per-session K and V maps (verify kernel)
     uint32_t *status = nullptr;         // device status word
     // host staging (pageable; async copies from it are staged by the driver before returning)
     TTDecodeItem *h_items = nullptr;
@@ -67,6 +68,7 @@ struct tt_context {
     TTDecodeSession *h_sessions_in = nullptr;
     uint32_t *h_keys = nullptr;
     uint32_t *h_rows = nullptr;
+    void *h_tensor_maps = nullptr;
     uint64_t launches = 0;
     // optional per-launch timing of the selected kernel classes (mask of TT_PROFILE_*)
     static constexpr uint32_t kProfileSlots = 256;

@@ -170,14 +170,16 @@ __device__ __forceinline__ float sum2<__nv_bfloat16>(uint32_t packed) {
 bool tt_make_tensor_map_2d(CUtensorMap *map, const void *base, uint32_t io_dtype, uint64_t width, uint64_t rows,
                            uint64_t stride_elems, uint32_t box_rows);
 
-// kind::f16 instruction descriptor, fp32 accumulate, A K-major, M = 128; A and B share one 16-bit
-// format (an fp16 A against a bf16 B is an illegal instruction on sm_100a).
-inline uint32_t tt_make_idesc_f16(uint32_t io_dtype, uint32_t n, bool b_mn_major) {
+// kind::f16 instruction descriptor, fp32 accumulate, M = 128; A and B share one 16-bit format (an
+// fp16 A against a bf16 B is an illegal instruction on sm_100a). An operand is K-major unless its
+// *_mn_major flag is set.
+inline uint32_t tt_make_idesc_f16(uint32_t io_dtype, uint32_t n, bool b_mn_major, bool a_mn_major = false) {
     const uint32_t fmt = io_dtype == TT_BF16 ? 1u : 0u;
     uint32_t d = 0;
     d |= 1u << 4;            // D format f32
     d |= fmt << 7;           // A format
     d |= fmt << 10;          // B format
+    d |= (a_mn_major ? 1u : 0u) << 15;
     d |= (b_mn_major ? 1u : 0u) << 16;
     d |= (n >> 3) << 17;
     d |= (128u >> 4) << 24;  // M = 128
