@@ -348,10 +348,19 @@ def timed_loop(torch, dist, world, fn, steps):
     return float(ms.item())
 
 
-def aux_measurements(w, pk):
-    """Other kernels of the path on their own configurations (rank 0, outside the timed region)."""
+class _Skip(Exception):
+    """Raised inside a side measurement that was not asked for."""
+
+
+def aux_measurements(w, pk, only=None, c5_sessions=64):
+    """Other kernels of the path on their own configurations (rank 0, outside the timed region).
+    `only`: run just the named case (a smaller, profiler-sized run); `c5_sessions`: sessions of config 5."""
     torch, tt = w.torch, w.tt
     aux = {}
+
+    def want(name):
+        if only is not None and name != only:
+            raise _Skip()
 
     def ev_time(fn, reps, warm=3):
         for _ in range(warm):
@@ -373,14 +382,16 @@ def aux_measurements(w, pk):
         w.ctx.profile_enable(False)
         return sum(t) / max(1, len(t))
 
-    ms = ev_time(lambda: w.gdn.encode_prepared(w.gdn_batch, w.a_log, w.dt_bias), 50)
-    kms = kernel_ms(lambda: w.gdn.encode_prepared(w.gdn_batch, w.a_log, w.dt_bias), 50)
-    gdn_bytes = N_SESSIONS * GV * GD * GD * 4 * 2 + N_SESSIONS * (2 * GK * GD + GV * GD) * 2 + N_SESSIONS * GV * GD * 2
-    aux["gdn_step_c2"] = {"ms": ms, "kernel_ms": kms, "GBps": gdn_bytes / kms / 1e6,
-                          "frac_hbm": gdn_bytes / kms / 1e6 / pk["hbm_gbs"],
-                          "note": "GBps and frac_hbm from kernel_ms (per-launch events); ms is one Python call per step"}
+    if only in (None, "gdn_step_c2"):
+        ms = ev_time(lambda: w.gdn.encode_prepared(w.gdn_batch, w.a_log, w.dt_bias), 50)
+        kms = kernel_ms(lambda: w.gdn.encode_prepared(w.gdn_batch, w.a_log, w.dt_bias), 50)
+        gdn_bytes = N_SESSIONS * GV * GD * GD * 4 * 2 + N_SESSIONS * (2 * GK * GD + GV * GD) * 2 + N_SESSIONS * GV * GD * 2
+        aux["gdn_step_c2"] = {"ms": ms, "kernel_ms": kms, "GBps": gdn_bytes / kms / 1e6,
+                              "frac_hbm": gdn_bytes / kms / 1e6 / pk["hbm_gbs"],
+                              "note": "GBps and frac_hbm from kernel_ms (per-launch events); ms is one Python call per step"}
     # config 3: causal prefill, 8192 tokens, 16/2/256, bf16, tcgen05 kernel
     try:
+        want("prefill_c3")
         T = 8192
         g = torch.Generator(device="cuda"); g.manual_seed(3)
         q = torch.randn(T, HQ * HD, device="cuda", generator=g).bfloat16()
@@ -394,10 +405,13 @@ def aux_measurements(w, pk):
         aux["prefill_c3_bf16"] = {"ms": ms, "TFLOPs": flops / ms / 1e9, "frac_tensor": flops / ms / 1e9 / pk["bf16_tflops"],
                                   "path": tt.PrefillAttention.selected_path(q, k, v, o, p)}
         del q, k, v, o
+    except _Skip:
+        pass
     except Exception as exc:  # reported, never hidden
         aux["prefill_c3_bf16"] = {"error": str(exc)}
     # config 3: GDN prefill over 8192 tokens, 16/32 heads, d 128: chunk-parallel scan vs the exact sequential kernel
     try:
+        want("gdn_scan_c3")
         T = 8192
         g = torch.Generator(device="cuda"); g.manual_seed(5)
         cfg = tt.LinearAttentionConfig(GK, GV, GD, GD)
@@ -416,10 +430,13 @@ def aux_measurements(w, pk):
                               "frac_hbm": scan_bytes / ms_scan / 1e6 / pk["hbm_gbs"], "TFLOPs": scan_flops / ms_scan / 1e9,
                               "sequential_kernel_ms": ms_seq, "tokens_per_s": T / ms_scan * 1e3}
         del conv, y
+    except _Skip:
+        pass
     except Exception as exc:
         aux["gdn_scan_c3"] = {"error": str(exc)}
     # config 4 on one GPU: one session, S = 262144, 16/2/256 (the per-GPU share at N GPUs is S/N of this)
     try:
+        want("decode_c4")
         s4 = 262144
         g = torch.Generator(device="cuda"); g.manual_seed(6)
         k4 = torch.randn(s4, HKV * HD, device="cuda", generator=g).half()
@@ -429,11 +446,14 @@ def aux_measurements(w, pk):
         b4 = s4 * HKV * HD * 2 * 2 + HQ * HD * 2 * 2
         aux["decode_c4_1gpu"] = {"ms": ms, "GBps": b4 / ms / 1e6, "frac_hbm": b4 / ms / 1e6 / pk["hbm_gbs"]}
         del k4, v4
+    except _Skip:
+        pass
     except Exception as exc:
         aux["decode_c4_1gpu"] = {"error": str(exc)}
     # config 5 on one GPU: 64 sessions x 4 draft rows, S = 16384 (+3), 32/2/256; GDN 4-row step with 64 value heads
     try:
-        n5, w5, s5, hq5 = 64, 4, 16384 + 3, 32
+        want("verify_c5")
+        n5, w5, s5, hq5 = c5_sessions, 4, 16384 + 3, 32
         g = torch.Generator(device="cuda"); g.manual_seed(8)
         k5 = torch.randn(n5, s5, HKV * HD, device="cuda", generator=g).half()
         v5 = torch.randn(n5, s5, HKV * HD, device="cuda", generator=g).half()
@@ -462,10 +482,13 @@ def aux_measurements(w, pk):
         bg = n5 * 64 * GD * GD * 4 * 2 + n5 * w5 * (cfg5.qkv_dim + 64 * GD) * 2
         aux["gdn_verify_c5_1gpu"] = {"ms": ms, "kernel_ms": kms, "GBps": bg / kms / 1e6,
                                      "frac_hbm": bg / kms / 1e6 / pk["hbm_gbs"]}
+    except _Skip:
+        pass
     except Exception as exc:
         aux["verify_c5_1gpu_error"] = str(exc)
     # config 1: one session, S = 4096, 8/2/256; 32 distinct caches are rotated so HBM is really read
     try:
+        want("decode_c1")
         s1, hq1 = 4096, 8
         g = torch.Generator(device="cuda"); g.manual_seed(4)
         ks = torch.randn(32, s1, HKV * HD, device="cuda", generator=g).half()
@@ -500,6 +523,8 @@ def aux_measurements(w, pk):
             aux["decode_c1"]["graph_frac_hbm"] = b1 / msg / 1e6 / pk["hbm_gbs"]
         except Exception as exc:
             aux["decode_c1"]["graph_error"] = str(exc)
+    except _Skip:
+        pass
     except Exception as exc:
         aux["decode_c1"] = {"error": str(exc)}
     return aux
@@ -523,6 +548,12 @@ def run_gpu_arm(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     pk = peaks()
     w = Workload(rank, local_rank)
+    if args.case is not None:
+        # one side measurement alone (a small, profiler-sized run); not a benchmark line
+        if rank == 0:
+            print(json.dumps({"case": args.case, "sessions": args.sessions, "c5_sessions": args.c5_sessions,
+                              "aux": aux_measurements(w, pk, only=args.case, c5_sessions=args.c5_sessions)}))
+        return 0
     sampler = ClockSampler(local_rank)
 
     for _ in range(max(3, args.warmup)):
@@ -597,6 +628,10 @@ def main():
     ap.add_argument("--no-aux", action="store_true", help="skip the side measurements and the CPU baseline")
     ap.add_argument("--sessions", type=int, default=32,
                     help="sessions per GPU (32 is the benchmark; a smaller count is for profiler captures only)")
+    ap.add_argument("--case", default=None,
+                    choices=["gdn_step_c2", "prefill_c3", "gdn_scan_c3", "decode_c4", "verify_c5", "decode_c1"],
+                    help="run one side measurement alone and exit (for profiler captures)")
+    ap.add_argument("--c5-sessions", type=int, default=64, help="sessions of the config-5 side measurement")
     args = ap.parse_args()
     global N_SESSIONS
     N_SESSIONS = args.sessions

@@ -234,3 +234,88 @@ def test_windowed_selection_with_row_indirection():
     torch.cuda.synchronize()
     want = oracle.attn_decode(q, k[sel], v[sel], hkv, 0.0625)
     assert np.abs(host(out) - want).max() <= TOL
+
+
+def _verify_batch(r, hq, hkv, q_rows, lens, dtype=torch.float16, kv_start=None, stride_pad=0, k_gain=None,
+                  scale=0.0625):
+    """Runs one few-token batch through the C ABI; returns (outputs, per-row oracle outputs)."""
+    n, hd = len(lens), 256
+    cap, stride, kbuf, vbuf, q = _batched_case(r, n, hq, hkv, hd, lens, q_rows, dtype, stride_pad)
+    if k_gain is not None:
+        for i in range(n):   # scores that keep growing along the sequence: the reference maxima are raised again and again
+            kbuf[i * cap:(i + 1) * cap, :hkv * hd] *= k_gain(np.arange(cap))[:, None]
+        kbuf = rounded(kbuf, dtype)
+    kd, vd, qd = dev(kbuf, dtype), dev(vbuf, dtype), dev(q, dtype)
+    out = torch.full((n, q_rows, hq * hd), float("nan"), device="cuda", dtype=dtype)
+    starts = kv_start or [0] * n
+    sessions = [tt.DecodeSession(qd, out, kd, vd, lens[i], q_rows, starts[i], q_offset=i * q_rows * hq * hd * 2,
+                                 out_offset=i * q_rows * hq * hd * 2, k_offset=i * cap * stride * 2,
+                                 v_offset=i * cap * stride * 2) for i in range(n)]
+    tt.Attention(context()).encode_batched(sessions, hd, hq, hkv, kv_token_stride_elements=stride, scale=scale,
+                                           io_dtype=tt.TT_F16 if dtype == torch.float16 else tt.TT_BF16)
+    torch.cuda.synchronize()
+    assert context().poll_status() == 0
+    want = np.zeros((n, q_rows, hq * hd), np.float32)
+    for i in range(n):
+        for w in range(q_rows):
+            vis = lens[i] - (q_rows - 1 - w)
+            lo = starts[i]
+            kk = kbuf[i * cap + lo:i * cap + vis, :hkv * hd].reshape(vis - lo, hkv, hd)
+            vv = vbuf[i * cap + lo:i * cap + vis, :hkv * hd].reshape(vis - lo, hkv, hd)
+            want[i, w] = oracle.attn_decode(q[i, w].reshape(hq, hd), kk, vv, hkv, scale).reshape(-1)
+    return host(out), want
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_verify_tensor_core_ragged_multi_part(dtype):
+    # 64 and 32 packed rows per KV head over ragged contexts long enough to be cut into several
+    # parts per session, a padded row stride, and a context shorter than one 128-key tile.
+    r = np.random.default_rng(501)
+    for hq, q_rows in [(32, 4), (16, 4)]:
+        lens = [4100, 2977, 131, 128 + q_rows, q_rows, 1500]
+        got, want = _verify_batch(r, hq, 2, q_rows, lens, dtype, stride_pad=16)
+        for i in range(len(lens)):
+            tol = TOL if dtype == torch.float16 else bf16_tol(want[i])
+            if dtype == torch.bfloat16 and lens[i] < 64:
+                # bf16 softmax weights carry 8 mantissa bits; over a handful of keys their rounding does
+                # not average out (error up to |v| * 2^-8). The reference's own bar is 2e-2 absolute.
+                tol = 2e-2
+            assert np.all(np.abs(got[i] - want[i]) <= tol), (hq, i, np.abs(got[i] - want[i]).max())
+
+
+def test_verify_tensor_core_repeated_raises_and_window_start():
+    # Key norms grow along the sequence, so later tiles keep exceeding the reference maxima by more
+    # than the lazy threshold and O^T / l^T are rescaled in TMEM several times; sessions also start
+    # their window at a position that is not a multiple of the tile.
+    r = np.random.default_rng(502)
+    lens = [2300, 1111, 700]
+    got, want = _verify_batch(r, 32, 2, 4, lens, kv_start=[0, 77, 301], k_gain=lambda t: 1.0 + t / 150.0, scale=0.0625)
+    for i in range(len(lens)):
+        assert np.abs(got[i] - want[i]).max() <= TOL, (i, np.abs(got[i] - want[i]).max())
+
+
+def test_verify_tensor_core_agrees_with_mma_sync_path(monkeypatch):
+    # Two independent CUDA kernels on the same batch at a size the oracle would take minutes for:
+    # the tcgen05 pass and (forced by the A/B switch) the mma.sync pass that serves 16 rows at a time.
+    r = np.random.default_rng(503)
+    n, hq, hkv, hd, q_rows = 6, 32, 2, 256, 4
+    lens = [16384 + 3, 9000, 12001, 300, 16000, 7777]
+    cap, stride, kbuf, vbuf, q = _batched_case(r, n, hq, hkv, hd, lens, q_rows)
+    kd, vd, qd = dev(kbuf), dev(vbuf), dev(q)
+    outs = []
+    for force in (False, True):
+        if force:
+            monkeypatch.setenv("TT_VERIFY_FORCE_MMA_SYNC", "1")
+        out = torch.full((n, q_rows, hq * hd), float("nan"), device="cuda", dtype=torch.float16)
+        sessions = [tt.DecodeSession(qd, out, kd, vd, lens[i], q_rows, 0, q_offset=i * q_rows * hq * hd * 2,
+                                     out_offset=i * q_rows * hq * hd * 2, k_offset=i * cap * stride * 2,
+                                     v_offset=i * cap * stride * 2) for i in range(n)]
+        launches = context().launch_count
+        tt.Attention(context()).encode_batched(sessions, hd, hq, hkv, scale=0.0625)
+        torch.cuda.synchronize()
+        assert context().poll_status() == 0
+        assert context().launch_count - launches == 2
+        outs.append(host(out))
+    assert np.isfinite(outs[0]).all()
+    assert np.abs(outs[0] - outs[1]).max() <= 2 * TOL
+    assert not np.array_equal(outs[0], outs[1])   # different kernels: agreement to rounding, not by construction

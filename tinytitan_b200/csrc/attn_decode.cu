@@ -16,7 +16,9 @@
 // capturable in a CUDA graph.
 #include "tt_sm100.h"
 
+#include <algorithm>
 #include <cstdlib>
+#include <vector>
 
 namespace {
 
@@ -917,31 +919,71 @@ int tt_launch_verify_tc(tt_context *ctx, cudaStream_t stream, uint32_t n_session
                         float *part_m, float *part_l, const tt_attn_batch_params *p);
 
 // Split plan of the tensor-core verify pass: one item per (session, kv head, key range) serving all
-// packed rows. One CTA is resident per SM, so ~3 items per SM; an item is at least four 128-key tiles
-// so that staging Q and filling the pipeline stay a small part of it, and the parts of one session
-// are of equal length. False when the partials or the items do not fit the context.
+// packed rows, the parts of one session of equal length (a multiple of the 128-key tile). One CTA is
+// resident per SM and an item costs about two tiles of start-up on top of its own tiles, so the part
+// length is picked by simulating the hardware's in-order dispatch of the items over the SMs for a
+// few candidate lengths and keeping the shortest makespan. False when the partials or the items do
+// not fit the context.
+static uint64_t wide_makespan(const uint32_t *keys, uint32_t n_sessions, uint32_t n_kv_heads, uint32_t len,
+                              uint32_t sm_count, std::vector<uint32_t> &heap) {
+    constexpr uint32_t kStartupTiles = 2;
+    heap.assign(sm_count, 0u);   // min-heap of SM finish times (in tiles)
+    auto sift_down = [&](uint32_t i) {
+        const uint32_t n = (uint32_t)heap.size();
+        for (;;) {
+            uint32_t l = 2 * i + 1, r = l + 1, m = i;
+            if (l < n && heap[l] < heap[m]) m = l;
+            if (r < n && heap[r] < heap[m]) m = r;
+            if (m == i) return;
+            std::swap(heap[i], heap[m]);
+            i = m;
+        }
+    };
+    uint32_t makespan = 0;
+    for (uint32_t i = 0; i < n_sessions; ++i) {
+        uint32_t parts = ceil_div_u32(keys[i], len);
+        if (parts == 0) parts = 1;
+        const uint32_t part_len = (ceil_div_u32(keys[i], parts) + 127) / 128 * 128;
+        for (uint32_t part = 0; part < parts; ++part) {
+            const uint32_t begin = part * part_len;
+            const uint32_t n = keys[i] > begin ? (keys[i] - begin < part_len ? keys[i] - begin : part_len) : 0u;
+            const uint32_t cost = kStartupTiles + (n + 127) / 128;
+            for (uint32_t h = 0; h < n_kv_heads; ++h) {
+                heap[0] += cost;
+                if (heap[0] > makespan) makespan = heap[0];
+                sift_down(0);
+            }
+        }
+    }
+    return makespan;
+}
+
 static bool plan_wide(tt_context *ctx, const TTDecodeSession *in_sessions, uint32_t n_sessions,
                       const tt_attn_batch_params *p, const uint32_t *keys, uint32_t *out_items,
                       uint32_t *out_partial_rows, uint32_t *out_max_rows) {
-    uint64_t key_rows = 0;
-    for (uint32_t i = 0; i < n_sessions; ++i) key_rows += (uint64_t)keys[i] * p->n_kv_heads;
-    uint64_t target = key_rows / ((uint64_t)ctx->sm_count * 3u);
-    target = (target + 127) / 128 * 128;
-    if (target < 512) target = 512;
-    for (;;) {
+    uint32_t max_keys = 0;
+    for (uint32_t i = 0; i < n_sessions; ++i) max_keys = keys[i] > max_keys ? keys[i] : max_keys;
+    static const uint32_t kPartChoices[] = {1, 2, 3, 4, 5, 6, 8, 10, 12, 16, 20, 24, 32, 48, 64};
+    std::vector<uint32_t> heap;
+    uint64_t target = 0, best = ~(uint64_t)0;
+    for (uint32_t parts : kPartChoices) {
+        uint32_t len = (ceil_div_u32(max_keys, parts) + 127) / 128 * 128;
+        if (len < 512) len = 512;                 // at least four tiles per item
         uint64_t items = 0, prows = 0;
-        bool all_single = true;
         for (uint32_t i = 0; i < n_sessions; ++i) {
-            uint32_t parts = ceil_div_u32(keys[i], target);
-            if (parts == 0) parts = 1;
-            if (parts > 1) all_single = false;
-            items += (uint64_t)parts * p->n_kv_heads;
-            prows += (uint64_t)parts * in_sessions[i].q_rows * p->n_q_heads;
+            uint32_t np = ceil_div_u32(keys[i], len);
+            if (np == 0) np = 1;
+            items += (uint64_t)np * p->n_kv_heads;
+            prows += (uint64_t)np * in_sessions[i].q_rows * p->n_q_heads;
         }
-        if (prows * ((uint64_t)p->head_dim + 2) * sizeof(float) <= ctx->workspace_bytes && items <= ctx->max_items) break;
-        if (all_single) return false;
-        target *= 2;
+        if (prows * ((uint64_t)p->head_dim + 2) * sizeof(float) > ctx->workspace_bytes || items > ctx->max_items ||
+            items > 8192)
+            continue;
+        const uint64_t span = wide_makespan(keys, n_sessions, p->n_kv_heads, len, (uint32_t)ctx->sm_count, heap);
+        if (span < best) { best = span; target = len; }
+        if (len == 512) break;
     }
+    if (target == 0) return false;
     uint32_t partial_cursor = 0, item_cursor = 0, max_rows = 0;
     const uint32_t group = p->n_q_heads / p->n_kv_heads;
     for (uint32_t i = 0; i < n_sessions; ++i) {

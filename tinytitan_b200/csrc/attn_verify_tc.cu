@@ -110,6 +110,19 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
     const uint32_t n_tiles = (item.key_end - item.key_begin + kBK - 1) / kBK;
     const uint32_t rows_total = ses.q_rows * p.n_q_heads;
 
+    // producer state: the first ring fill leaves before the CTA-wide sync so that it overlaps the
+    // staging of Q (the thread that initialises the barriers is the one that uses them first)
+    const CUtensorMap *k_map = p.maps + 2 * item.session, *v_map = k_map + 1;
+    const uint32_t n_blocks = 4 * n_tiles;
+    auto load_block = [&](uint32_t b) {
+        const uint32_t slot = b % kSlots, kind = b & 3, j = b >> 2;
+        mbar_expect_tx(&ms->full[slot], kBlockBytes);
+        const CUtensorMap *map = kind < 2 ? k_map : v_map;
+        const int x = (int)(item.kv_head * kHD + (kind & 1) * 128);
+        const int y = (int)(item.key_begin + j * kBK);
+        tma_load_2d(ring + slot * kBlockBytes, map, x, y, &ms->full[slot]);
+        tma_load_2d(ring + slot * kBlockBytes + kSubBytes, map, x + 64, y, &ms->full[slot]);
+    };
     if (threadIdx.x == 0) {
         for (int s = 0; s < kSlots; ++s) { mbar_init(&ms->full[s], 1); mbar_init(&ms->empty[s], 1); }
         for (int s = 0; s < 2; ++s) {
@@ -121,27 +134,36 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
         mbar_init(&ms->sync, 4);
         ms->raise_tile[0] = 0; ms->raise_tile[1] = 0;
         mbar_fence_init();
+        if (n_tiles > 0) {
+            // the maps were rewritten by a host copy since the last launch that used these addresses
+            asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(k_map) : "memory");
+            asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(v_map) : "memory");
+            for (uint32_t b = 0; b < (uint32_t)kSlots && b < n_blocks; ++b) load_block(b);
+        }
     }
     if (warp == 1) tmem_alloc(&ms->tmem_base, kTmemCols);
 
-    // ---- stage Q^T's operand: packed row r = w*G + g -> q[w][kv_head*G + g][:], K-major, 128-byte swizzle
-    {
+    // ---- stage Q^T's operand: packed row r = w*G + g -> q[w][kv_head*G + g][:], K-major, 128-byte
+    // swizzle; asynchronous 16-byte copies so that all of a thread's chunks are in flight together
+    if (warp != 0) {
         const T *q = reinterpret_cast<const T *>(ses.q);
-        for (uint32_t c = threadIdx.x; c < kRows * (kHD / 8); c += kThreads) {
+        for (uint32_t c = threadIdx.x - 32; c < kRows * (kHD / 8); c += kThreads - 32) {
             const uint32_t r = c / (kHD / 8), chunk = c % (kHD / 8);       // 16-byte chunk of the row
-            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            const uint32_t sub = chunk >> 3, cc = chunk & 7;
+            unsigned char *dst = q_s + sub * kQSub + r * 128 + ((cc ^ (r & 7)) << 4);
             if (r < n_rows) {
                 const uint32_t w = r / group, g = r - w * group;
-                val = *reinterpret_cast<const uint4 *>(q + (size_t)w * p.q_row_stride +
-                                                       (size_t)(item.kv_head * group + g) * kHD + chunk * 8);
+                const T *src = q + (size_t)w * p.q_row_stride + (size_t)(item.kv_head * group + g) * kHD + chunk * 8;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+            } else {
+                *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
             }
-            const uint32_t sub = chunk >> 3, cc = chunk & 7;
-            *reinterpret_cast<uint4 *>(q_s + sub * kQSub + r * 128 + ((cc ^ (r & 7)) << 4)) = val;
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
         const uint32_t one2 = std::is_same<T, __half>::value ? 0x3C003C00u : 0x3F803F80u;   // 1.0 twice
-        for (uint32_t c = threadIdx.x; c < kOnesBytes / 16; c += kThreads)
+        for (uint32_t c = threadIdx.x - 32; c < kOnesBytes / 16; c += kThreads - 32)
             *reinterpret_cast<uint4 *>(ones_s + c * 16) = make_uint4(one2, one2, one2, one2);
-        for (uint32_t r = threadIdx.x; r < kRows; r += kThreads) {
+        for (uint32_t r = threadIdx.x - 32; r < kRows; r += kThreads - 32) {
             const uint32_t w = r / group, g = r - w * group;
             ms->mref[r] = -INFINITY;
             ms->factor[r] = 1.f;
@@ -149,6 +171,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
             const uint32_t rho = w * p.n_q_heads + item.kv_head * group + g;
             ms->prow[r] = item.partial_base + item.part_index * rows_total + rho;
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         fence_async_smem();
     }
     tc_fence_before();
@@ -160,22 +183,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0 && n_tiles > 0) {
-            const CUtensorMap *k_map = p.maps + 2 * item.session, *v_map = k_map + 1;
-            // the maps were rewritten by a host copy since the last launch that used these addresses
-            asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(k_map) : "memory");
-            asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(v_map) : "memory");
             bool ok = true;
-            const uint32_t n_blocks = 4 * n_tiles;
-            for (uint32_t b = 0; ok && b < n_blocks; ++b) {
-                const uint32_t slot = b % kSlots, kind = b & 3, j = b >> 2;
-                if (b >= kSlots) ok = mbar_wait(&ms->empty[slot], ((b / kSlots) - 1) & 1);
-                if (!ok) break;
-                mbar_expect_tx(&ms->full[slot], kBlockBytes);
-                const CUtensorMap *map = kind < 2 ? k_map : v_map;
-                const int x = (int)(item.kv_head * kHD + (kind & 1) * 128);
-                const int y = (int)(item.key_begin + j * kBK);
-                tma_load_2d(ring + slot * kBlockBytes, map, x, y, &ms->full[slot]);
-                tma_load_2d(ring + slot * kBlockBytes + kSubBytes, map, x + 64, y, &ms->full[slot]);
+            for (uint32_t b = kSlots; ok && b < n_blocks; ++b) {
+                ok = mbar_wait(&ms->empty[b % kSlots], ((b / kSlots) - 1) & 1);
+                if (ok) load_block(b);
             }
             failed = !ok;
         }
