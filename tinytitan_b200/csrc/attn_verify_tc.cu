@@ -8,15 +8,17 @@
 //   S^T[j%2] = K_j . Q^T          SS MMA  M128 (keys) N64 (rows) K16 x16    TMEM cols   0..127
 //   P^T_j    = exp2(S^T - m)      tcgen05.ld -> registers -> shared memory (B operand, N-major)
 //   O^T     += V_j^T . P^T_j      SS MMA  M128 (head-dim half) N64 K16 x8, twice   cols 128..255
-//   l^T     += 1 . P^T_j          SS MMA  against a tile of ones: the row sums of the ROUNDED
-//                                 weights, replicated over the lanes                cols 256..319
+//   l^T     += 1 . P^T_j          SS MMA  against ones: the row sums of the ROUNDED weights,
+//                                 replicated over the lanes                         cols 256..319
 //
-// K and V stream as [128 keys][128 head-dim] blocks (two TMA boxes, 32 KB) through one 4-slot ring
-// in the order K(j,lo) K(j,hi) V(j,lo) V(j,hi). Warp 0 is the TMA producer, warp 1 issues the MMAs
-// and owns TMEM, warps 2-5 (one thread per key of the tile) run the softmax. The per-row reference
-// maximum lives in shared memory and is only raised when a score exceeds it by more than 2^8; the
-// raise (rare after the first tile) rescales O^T and l^T in TMEM. Each CTA writes one unnormalised
-// (m, l, o) partial per packed row, in the layout the split-KV combine kernel merges.
+// K streams as [128 keys][64 head-dim] chunks (one TMA box, 16 KB) through a 4-slot ring and is
+// released chunk by chunk as its four MMAs retire; V streams as [128 keys][128 head-dim] blocks
+// (two boxes, 32 KB) through a 3-slot ring, so the loads of the next tile's V are in flight while
+// this tile's is consumed. Lanes 0 and 1 of warp 0 are the K and V producers, warp 1 issues the
+// MMAs and owns TMEM, warps 2-5 (one thread per key of the tile) run the softmax. The per-row
+// reference maximum lives in shared memory and is only raised when a score exceeds it by more than
+// 2^8; the raise (rare after the first tile) rescales O^T and l^T in TMEM. Each CTA writes one
+// unnormalised (m, l, o) partial per packed row, in the layout the split-KV combine kernel merges.
 //
 // Semantics: attention.metal:162-269 (partial pass over a key range, row r of a W-row group
 // masked at seq_len - (W-1-r)); every mbarrier wait is bounded.
@@ -30,28 +32,31 @@ constexpr int kHD = 256;
 constexpr int kBK = 128;                   // keys per tile
 constexpr int kRows = 64;                  // packed query rows (MMA N)
 constexpr int kThreads = 192;
-constexpr int kSlots = 4;
+constexpr int kKSlots = 4, kVSlots = 3;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRaiseThreshold = 8.0f;
 
-constexpr int kBlockBytes = kBK * 128 * 2;     // [128 keys][128 head-dim]: 2 sub-tiles [128][64]
-constexpr int kSubBytes = kBK * 64 * 2;        // 16384
+constexpr int kChunkBytes = kBK * 64 * 2;      // [128 keys][64 head-dim], 128-byte rows: 16384
+constexpr int kVBlockBytes = 2 * kChunkBytes;  // [128 keys][128 head-dim]
 constexpr int kQBytes = kRows * kHD * 2;       // 4 sub-tiles [64][64]
 constexpr int kQSub = kRows * 64 * 2;          // 8192
 constexpr int kPBytes = kBK * kRows * 2;       // [128 keys][64 rows], 128-byte rows
-constexpr int kOnesBytes = kBK * 64 * 2;       // [128][64] of 1.0
-constexpr int kOffQ = kSlots * kBlockBytes;
+constexpr int kOnesBytes = 1024;               // one 8-row group of 1.0; every group of the operand aliases it
+constexpr int kOffV = kKSlots * kChunkBytes;
+constexpr int kOffQ = kOffV + kVSlots * kVBlockBytes;
 constexpr int kOffP = kOffQ + kQBytes;
-constexpr int kOffOnes = kOffP + 2 * kPBytes;
+constexpr int kOffOnes = kOffP + kPBytes;
 constexpr int kOffMisc = kOffOnes + kOnesBytes;
 
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 128, kColL = 256;
 
 struct Misc {
-    uint64_t full[kSlots], empty[kSlots];
-    uint64_t s_full[2], p_ready[2], p_free[2];
+    uint64_t k_full[kKSlots], k_empty[kKSlots];
+    uint64_t v_full[kVSlots], v_empty[kVSlots];
+    uint64_t s_full[2];
+    uint64_t p_ready, p_free;
     uint64_t o_ready;
     uint64_t sync;              // softmax warps' own barrier (count 4: one arrive per warp)
     uint32_t tmem_base;
@@ -69,7 +74,7 @@ constexpr int kSmemBytes = kOffMisc + (int)sizeof(Misc) + 1024 /*align*/;
 struct VerifyParams {
     const TTDecodeItem *items;
     const TTDecodeSession *sessions;
-    const CUtensorMap *maps;     // [2 * session]: K map, V map
+    const CUtensorMap *maps;     // [2 * session]: K map (box 128 x 64), V map (box 128 x 64)
     float *part_o, *part_m, *part_l;
     uint32_t n_q_heads, n_kv_heads, q_row_stride;
     float scale_log2;
@@ -86,17 +91,38 @@ __device__ __forceinline__ bool softmax_sync(uint64_t *bar, uint32_t &phase, int
     return ok;
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ float warp_max(float v) {
+
+// Column maxima over the warp: every lane holds one value for each of 64 columns; afterwards lane L
+// holds the warp-wide maxima of columns 2L and 2L+1. Each butterfly step hands the partner the half
+// of the columns it keeps, so the whole reduction is 62 shuffles instead of 320.
+__device__ __forceinline__ void warp_colmax64(const uint32_t (&v)[2][32], int lane, float &m0, float &m1) {
+    float a[32], b[16], c[8], d[4];
+    bool up = (lane & 16) != 0;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
+    for (int i = 0; i < 32; ++i) {
+        const float lo = __uint_as_float(v[0][i]), hi = __uint_as_float(v[1][i]);
+        a[i] = fmaxf(up ? hi : lo, __shfl_xor_sync(0xffffffffu, up ? lo : hi, 16));
+    }
+    up = (lane & 8) != 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) b[i] = fmaxf(up ? a[i + 16] : a[i], __shfl_xor_sync(0xffffffffu, up ? a[i] : a[i + 16], 8));
+    up = (lane & 4) != 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) c[i] = fmaxf(up ? b[i + 8] : b[i], __shfl_xor_sync(0xffffffffu, up ? b[i] : b[i + 8], 4));
+    up = (lane & 2) != 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) d[i] = fmaxf(up ? c[i + 4] : c[i], __shfl_xor_sync(0xffffffffu, up ? c[i] : c[i + 4], 2));
+    up = (lane & 1) != 0;
+    m0 = fmaxf(up ? d[2] : d[0], __shfl_xor_sync(0xffffffffu, up ? d[0] : d[2], 1));
+    m1 = fmaxf(up ? d[3] : d[1], __shfl_xor_sync(0xffffffffu, up ? d[1] : d[3], 1));
 }
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParams p, uint32_t *__restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char *ring = smem;
+    unsigned char *k_ring = smem;
+    unsigned char *v_ring = smem + kOffV;
     unsigned char *q_s = smem + kOffQ;
     unsigned char *p_s = smem + kOffP;
     unsigned char *ones_s = smem + kOffOnes;
@@ -110,26 +136,30 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
     const uint32_t n_tiles = (item.key_end - item.key_begin + kBK - 1) / kBK;
     const uint32_t rows_total = ses.q_rows * p.n_q_heads;
 
-    // producer state: the first ring fill leaves before the CTA-wide sync so that it overlaps the
-    // staging of Q (the thread that initialises the barriers is the one that uses them first)
+    // K chunk kc = 4*tile + (64-wide head-dim slice); V block vb = 2*tile + head-dim half
     const CUtensorMap *k_map = p.maps + 2 * item.session, *v_map = k_map + 1;
-    const uint32_t n_blocks = 4 * n_tiles;
-    auto load_block = [&](uint32_t b) {
-        const uint32_t slot = b % kSlots, kind = b & 3, j = b >> 2;
-        mbar_expect_tx(&ms->full[slot], kBlockBytes);
-        const CUtensorMap *map = kind < 2 ? k_map : v_map;
-        const int x = (int)(item.kv_head * kHD + (kind & 1) * 128);
-        const int y = (int)(item.key_begin + j * kBK);
-        tma_load_2d(ring + slot * kBlockBytes, map, x, y, &ms->full[slot]);
-        tma_load_2d(ring + slot * kBlockBytes + kSubBytes, map, x + 64, y, &ms->full[slot]);
+    const uint32_t n_kchunks = 4 * n_tiles, n_vblocks = 2 * n_tiles;
+    auto load_k = [&](uint32_t kc) {
+        const uint32_t slot = kc % kKSlots;
+        mbar_expect_tx(&ms->k_full[slot], kChunkBytes);
+        tma_load_2d(k_ring + slot * kChunkBytes, k_map, (int)(item.kv_head * kHD + (kc & 3) * 64),
+                    (int)(item.key_begin + (kc >> 2) * kBK), &ms->k_full[slot]);
     };
+    auto load_v = [&](uint32_t vb) {
+        const uint32_t slot = vb % kVSlots;
+        mbar_expect_tx(&ms->v_full[slot], kVBlockBytes);
+        const int x = (int)(item.kv_head * kHD + (vb & 1) * 128), y = (int)(item.key_begin + (vb >> 1) * kBK);
+        tma_load_2d(v_ring + slot * kVBlockBytes, v_map, x, y, &ms->v_full[slot]);
+        tma_load_2d(v_ring + slot * kVBlockBytes + kChunkBytes, v_map, x + 64, y, &ms->v_full[slot]);
+    };
+    // The first ring fills leave before the CTA-wide sync so that they overlap the staging of Q (the
+    // thread that initialises the barriers is the one that uses them first).
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kSlots; ++s) { mbar_init(&ms->full[s], 1); mbar_init(&ms->empty[s], 1); }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&ms->s_full[s], 1);
-            mbar_init(&ms->p_ready[s], 128);
-            mbar_init(&ms->p_free[s], 1);
-        }
+        for (int s = 0; s < kKSlots; ++s) { mbar_init(&ms->k_full[s], 1); mbar_init(&ms->k_empty[s], 1); }
+        for (int s = 0; s < kVSlots; ++s) { mbar_init(&ms->v_full[s], 1); mbar_init(&ms->v_empty[s], 1); }
+        mbar_init(&ms->s_full[0], 1); mbar_init(&ms->s_full[1], 1);
+        mbar_init(&ms->p_ready, 128);
+        mbar_init(&ms->p_free, 1);
         mbar_init(&ms->o_ready, 1);
         mbar_init(&ms->sync, 4);
         ms->raise_tile[0] = 0; ms->raise_tile[1] = 0;
@@ -138,7 +168,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
             // the maps were rewritten by a host copy since the last launch that used these addresses
             asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(k_map) : "memory");
             asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(v_map) : "memory");
-            for (uint32_t b = 0; b < (uint32_t)kSlots && b < n_blocks; ++b) load_block(b);
+            for (uint32_t kc = 0; kc < (uint32_t)kKSlots && kc < n_kchunks; ++kc) load_k(kc);
+            for (uint32_t vb = 0; vb < (uint32_t)kVSlots && vb < n_vblocks; ++vb) load_v(vb);
         }
     }
     if (warp == 1) tmem_alloc(&ms->tmem_base, kTmemCols);
@@ -181,33 +212,41 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
     bool failed = false;
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer
-        if (lane == 0 && n_tiles > 0) {
+        // ------------------------------------------------------------------ TMA producers
+        if (lane == 0) {
             bool ok = true;
-            for (uint32_t b = kSlots; ok && b < n_blocks; ++b) {
-                ok = mbar_wait(&ms->empty[b % kSlots], ((b / kSlots) - 1) & 1);
-                if (ok) load_block(b);
+            for (uint32_t kc = kKSlots; ok && kc < n_kchunks; ++kc) {
+                ok = mbar_wait(&ms->k_empty[kc % kKSlots], ((kc / kKSlots) - 1) & 1);
+                if (ok) load_k(kc);
+            }
+            failed = !ok;
+        } else if (lane == 1) {
+            bool ok = true;
+            for (uint32_t vb = kVSlots; ok && vb < n_vblocks; ++vb) {
+                ok = mbar_wait(&ms->v_empty[vb % kVSlots], ((vb / kVSlots) - 1) & 1);
+                if (ok) load_v(vb);
             }
             failed = !ok;
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0 && n_tiles > 0) {
-            const uint32_t ring_a = smem_u32(ring), q_a = smem_u32(q_s), p_a = smem_u32(p_s), ones_a = smem_u32(ones_s);
-            // S^T(j) = K_j . Q^T over the two head-dim halves
+            const uint32_t k_a = smem_u32(k_ring), v_a = smem_u32(v_ring), q_a = smem_u32(q_s), p_a = smem_u32(p_s),
+                           ones_a = smem_u32(ones_s);
+            // S^T(j) = K_j . Q^T, one 64-wide head-dim slice at a time as the chunks land
             auto issue_qk = [&](uint32_t j) {
                 const uint32_t d = tmem + kColS + (j & 1) * kRows;
-                for (uint32_t half = 0; half < 2; ++half) {
-                    const uint32_t b = 4 * j + half, slot = b % kSlots;
-                    if (!mbar_wait(&ms->full[slot], (b / kSlots) & 1)) return false;
+                for (uint32_t c = 0; c < 4; ++c) {
+                    const uint32_t kc = 4 * j + c, slot = kc % kKSlots;
+                    if (!mbar_wait(&ms->k_full[slot], (kc / kKSlots) & 1)) return false;
                     tc_fence_after();
 #pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
-                        const uint64_t ad = make_desc(ring_a + slot * kBlockBytes + (ks >> 2) * kSubBytes + (ks & 3) * 32, 16, 1024);
-                        const uint64_t bd = make_desc(q_a + (half * 2 + (ks >> 2)) * kQSub + (ks & 3) * 32, 16, 1024);
-                        mma_ss(d, ad, bd, p.idesc_qk, (half > 0 || ks > 0) ? 1u : 0u);
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t ad = make_desc(k_a + slot * kChunkBytes + ks * 32, 16, 1024);
+                        const uint64_t bd = make_desc(q_a + c * kQSub + ks * 32, 16, 1024);
+                        mma_ss(d, ad, bd, p.idesc_qk, (c > 0 || ks > 0) ? 1u : 0u);
                     }
-                    mma_commit(&ms->empty[slot]);
+                    mma_commit(&ms->k_empty[slot]);
                 }
                 mma_commit(&ms->s_full[j & 1]);
                 return true;
@@ -215,36 +254,35 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
             bool ok = issue_qk(0);
             for (uint32_t j = 0; ok && j < n_tiles; ++j) {
                 if (j + 1 < n_tiles) ok = issue_qk(j + 1);
-                const uint32_t st = j & 1;
-                if (ok) ok = mbar_wait(&ms->p_ready[st], (j >> 1) & 1);
+                if (ok) ok = mbar_wait(&ms->p_ready, j & 1);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc0 = j > 0 ? 1u : 0u;
-                // l^T += 1 . P^T_j
+                // l^T += 1 . P^T_j: every 8-row group of the A operand is the same 1 KB of ones (SBO 0)
 #pragma unroll
                 for (int kk = 0; kk < kBK / 16; ++kk) {
-                    const uint64_t ad = make_desc(ones_a + (kk & 3) * 32, 16, 1024);
-                    const uint64_t bd = make_desc(p_a + st * kPBytes + kk * 2048, kPBytes, 1024);
+                    const uint64_t ad = make_desc(ones_a + (kk & 3) * 32, 16, 0);
+                    const uint64_t bd = make_desc(p_a + kk * 2048, kPBytes, 1024);
                     mma_ss(tmem + kColL, ad, bd, p.idesc_l, (acc0 || kk > 0) ? 1u : 0u);
                 }
                 // O^T(half) += V_j(half)^T . P^T_j
                 for (uint32_t half = 0; ok && half < 2; ++half) {
-                    const uint32_t b = 4 * j + 2 + half, slot = b % kSlots;
-                    ok = mbar_wait(&ms->full[slot], (b / kSlots) & 1);
+                    const uint32_t vb = 2 * j + half, slot = vb % kVSlots;
+                    ok = mbar_wait(&ms->v_full[slot], (vb / kVSlots) & 1);
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < kBK / 16; ++kk) {
-                        // V block as the M-major A operand: 64-wide head-dim atoms kSubBytes apart (LBO),
+                        // V block as the M-major A operand: 64-wide head-dim atoms kChunkBytes apart (LBO),
                         // 8-key groups 1024 B apart (SBO); P^T as the N-major B operand, one atom wide
-                        const uint64_t ad = make_desc(ring_a + slot * kBlockBytes + kk * 2048, kSubBytes, 1024);
-                        const uint64_t bd = make_desc(p_a + st * kPBytes + kk * 2048, kPBytes, 1024);
+                        const uint64_t ad = make_desc(v_a + slot * kVBlockBytes + kk * 2048, kChunkBytes, 1024);
+                        const uint64_t bd = make_desc(p_a + kk * 2048, kPBytes, 1024);
                         mma_ss(tmem + kColO + half * kRows, ad, bd, p.idesc_pv, (acc0 || kk > 0) ? 1u : 0u);
                     }
-                    mma_commit(&ms->empty[slot]);
+                    mma_commit(&ms->v_empty[slot]);
                 }
                 if (!ok) break;
-                mma_commit(&ms->p_free[st]);
+                mma_commit(&ms->p_free);
                 mma_commit(&ms->o_ready);
             }
             failed = !ok;
@@ -292,13 +330,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
             if (!ok) break;
             if (ms->raise_tile[st] == j + 1) {
                 // raise the reference maxima to the true maxima so far, rescale what is accumulated
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const float v = warp_max(__uint_as_float(raw[h][c]));
-                        if (lane == 0) ms->tile_max[quarter][h * 32 + c] = v;
-                    }
+                float m0, m1;
+                warp_colmax64(raw, lane, m0, m1);
+                *reinterpret_cast<float2 *>(&ms->tile_max[quarter][2 * lane]) = make_float2(m0, m1);
                 ok = softmax_sync(&ms->sync, sync_phase, lane);
                 if (!ok) break;
                 if (i < kRows) {
@@ -330,12 +364,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
                 }
             }
 
-            // P^T row of this key: 64 weights -> 128 bytes, chunk c at (c ^ (key & 7))
-            if (j >= 2) {
-                ok = warp_all(mbar_wait(&ms->p_free[st], ((j >> 1) - 1) & 1));
-                if (!ok) break;
-            }
-            unsigned char *prow = p_s + st * kPBytes + i * 128;
+            // P^T row of this key: 64 weights -> 128 bytes, chunk c at (c ^ (key & 7)); the exponentials are
+            // formed first, the single P buffer is only waited for when they are ready to be stored
+            uint4 w[8];
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -349,15 +380,21 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
                         const float m_use = (mm[u] == -INFINITY) ? 0.f : mm[u];
                         e[u] = fast_exp2(__uint_as_float(raw[h][c + u]) - m_use);
                     }
-                    uint4 w;
-                    w.x = pack2<T>(e[0], e[1]); w.y = pack2<T>(e[2], e[3]);
-                    w.z = pack2<T>(e[4], e[5]); w.w = pack2<T>(e[6], e[7]);
-                    const uint32_t chunk = (uint32_t)(h * 4 + (c >> 3));
-                    *reinterpret_cast<uint4 *>(prow + ((chunk ^ (i & 7)) << 4)) = w;
+                    uint4 &o = w[h * 4 + (c >> 3)];
+                    o.x = pack2<T>(e[0], e[1]); o.y = pack2<T>(e[2], e[3]);
+                    o.z = pack2<T>(e[4], e[5]); o.w = pack2<T>(e[6], e[7]);
                 }
+            if (j >= 1) {
+                ok = warp_all(mbar_wait(&ms->p_free, (j - 1) & 1));
+                if (!ok) break;
+            }
+            unsigned char *prow = p_s + i * 128;
+#pragma unroll
+            for (uint32_t chunk = 0; chunk < 8; ++chunk)
+                *reinterpret_cast<uint4 *>(prow + ((chunk ^ (i & 7)) << 4)) = w[chunk];
             fence_async_smem();
             tc_fence_before();
-            mbar_arrive(&ms->p_ready[st]);
+            mbar_arrive(&ms->p_ready);
         }
 
         // ---- partial of this item: O^T (transposed back on the way out), m, l
