@@ -314,8 +314,20 @@ def test_verify_tensor_core_agrees_with_mma_sync_path(monkeypatch):
         tt.Attention(context()).encode_batched(sessions, hd, hq, hkv, scale=0.0625)
         torch.cuda.synchronize()
         assert context().poll_status() == 0
-        assert context().launch_count - launches == 2
+        assert context().launch_count - launches in (1, 2)   # pass 1, and the merge unless every session is one part
         outs.append(host(out))
     assert np.isfinite(outs[0]).all()
     assert np.abs(outs[0] - outs[1]).max() <= 2 * TOL
     assert not np.array_equal(outs[0], outs[1])   # different kernels: agreement to rounding, not by construction
+
+
+def test_verify_tensor_core_single_part_writes_outputs_directly():
+    # Contexts that fit one part each: the tensor-core pass normalises and stores the rows itself
+    # (one launch, no merge pass); rows with a single visible key and a padded output stride included.
+    r = np.random.default_rng(504)
+    lens = [500, 300, 4, 129]
+    launches = context().launch_count
+    got, want = _verify_batch(r, 32, 2, 4, lens)
+    assert context().launch_count - launches == 1
+    for i in range(len(lens)):
+        assert np.abs(got[i] - want[i]).max() <= TOL, (i, np.abs(got[i] - want[i]).max())

@@ -915,8 +915,9 @@ TT_API void tt_attn_reference_split_geometry(uint32_t n_q_heads, uint32_t n_kv_h
     out->use_swa_grouped_partial = swa_grouped ? 1u : 0u;
 }
 
+int tt_verify_tc_encode_maps(tt_context *ctx, uint32_t n_sessions, const tt_attn_batch_params *p);
 int tt_launch_verify_tc(tt_context *ctx, cudaStream_t stream, uint32_t n_sessions, uint32_t n_items, float *part_o,
-                        float *part_m, float *part_l, const tt_attn_batch_params *p);
+                        float *part_m, float *part_l, const tt_attn_batch_params *p, bool direct);
 
 // Split plan of the tensor-core verify pass: one item per (session, kv head, key range) serving all
 // packed rows, the parts of one session of equal length (a multiple of the 128-key tile). One CTA is
@@ -1078,6 +1079,7 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
         wide = packed > 16 && packed <= 64 && s.ring_capacity == 0 && s.keep == nullptr && s.row_index == nullptr;
     }
 
+    tt_bind_decode_tables(ctx, n_sessions, wide);
     uint32_t keys_per_item = 0, n_items = 0;
     uint32_t partial_cursor = 0, item_cursor = 0, max_rows = 0;
     if (wide) wide = plan_wide(ctx, in_sessions, n_sessions, p, keys, &n_items, &partial_cursor, &max_rows);
@@ -1131,16 +1133,22 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     const uint32_t single_keys = single ? keys_per_item : 0u;
     cudaError_t e = cudaSuccess;
     if (!single) {
-        e = cudaMemcpyAsync(ctx->sessions, ctx->h_sessions, sizeof(TTDecodeSession) * n_sessions,
-                            cudaMemcpyHostToDevice, stream);
-        if (e != cudaSuccess) return tt_check_cuda(ctx, e, "copy session table");
-        e = cudaMemcpyAsync(ctx->items, ctx->h_items, sizeof(TTDecodeItem) * n_items, cudaMemcpyHostToDevice, stream);
-        if (e != cudaSuccess) return tt_check_cuda(ctx, e, "copy item table");
+        if (wide) {
+            const int rc = tt_verify_tc_encode_maps(ctx, n_sessions, p);
+            if (rc != TT_OK) return rc;
+        }
+        // sessions, maps and items sit back to back: one upload
+        const size_t bytes = (size_t)(reinterpret_cast<unsigned char *>(ctx->h_items + n_items) - ctx->h_tables);
+        e = cudaMemcpyAsync(ctx->tables, ctx->h_tables, bytes, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return tt_check_cuda(ctx, e, "copy decode tables");
     }
 
     TTLaunchTimer timer(ctx, stream, TT_PROFILE_DECODE_PARTIAL);
+    // a verify batch whose sessions are all one part needs no merge: pass 1 stores the output rows
+    bool direct = wide && mode == 0;
+    for (uint32_t i = 0; direct && i < n_sessions; ++i) direct = ctx->h_sessions[i].n_parts == 1;
     if (wide) {
-        const int rc = tt_launch_verify_tc(ctx, stream, n_sessions, n_items, part_o, part_m, part_l, p);
+        const int rc = tt_launch_verify_tc(ctx, stream, n_sessions, n_items, part_o, part_m, part_l, p, direct);
         if (rc != TT_OK) return rc;
     } else if (quantised)
         e = launch_partial_quant(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status,
@@ -1154,6 +1162,7 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_decode_partial launch");
     timer.stop();
     ctx->launches++;
+    if (direct) return TT_OK;
 
     const dim3 grid(n_sessions, max_rows);
     const uint32_t threads = 256;

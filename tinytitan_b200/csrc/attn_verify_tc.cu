@@ -77,6 +77,8 @@ struct VerifyParams {
     const CUtensorMap *maps;     // [2 * session]: K map (box 128 x 64), V map (box 128 x 64)
     float *part_o, *part_m, *part_l;
     uint32_t n_q_heads, n_kv_heads, q_row_stride;
+    uint32_t out_row_stride;     // elements
+    uint32_t direct;             // every session is one part: write the normalised rows, no partials
     float scale_log2;
     uint32_t idesc_qk, idesc_pv, idesc_l;
 };
@@ -413,7 +415,32 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
             }
             ok = softmax_sync(&ms->sync, sync_phase, lane);
         }
-        if (ok) {
+        if (ok && p.direct) {
+            // the item covers the session's whole key range: normalise and store the output rows
+            T *out = reinterpret_cast<T *>(ses.out);
+#pragma unroll 1
+            for (uint32_t half = 0; half < 2; ++half) {
+                uint32_t o0[32], o1[32];
+                if (n_tiles > 0) {
+                    tmem_ld32(tmem + lane_addr + kColO + half * kRows, o0);
+                    tmem_ld32(tmem + lane_addr + kColO + half * kRows + 32, o1);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) { o0[c] = 0u; o1[c] = 0u; }
+                }
+#pragma unroll
+                for (int c = 0; c < 64; ++c) {
+                    if ((uint32_t)c < n_rows) {
+                        const float l = n_tiles > 0 ? ms->lsum[c] : 0.f;
+                        const float inv = l > 0.f ? 1.f / l : 0.f;          // no visible key: zeros
+                        const uint32_t w = (uint32_t)c / group, g = (uint32_t)c - w * group;
+                        const float v = __uint_as_float(c < 32 ? o0[c & 31] : o1[c & 31]) * inv;
+                        out[(size_t)w * p.out_row_stride + (size_t)(item.kv_head * group + g) * kHD + half * 128 + i] = (T)v;
+                    }
+                }
+            }
+        } else if (ok) {
             if (i < n_rows) {
                 const float m = ms->mref[i];
                 p.part_m[ms->prow[i]] = n_tiles > 0 ? m * kLn2 : -INFINITY;   // natural-log domain
@@ -453,12 +480,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
 
 }  // namespace
 
-// Pass 1 of a verify batch on the tensor cores. The caller has planned the items (one per
-// (session, kv head, key range), all packed rows at once) into ctx->h_items / ctx->h_sessions and
-// copied both tables to the device; this encodes one K and one V tensor map per session
-// ([seq_len rows][n_kv_heads * 256], box 128 x 64, keys past seq_len read as zero) and launches.
-int tt_launch_verify_tc(tt_context *ctx, cudaStream_t stream, uint32_t n_sessions, uint32_t n_items, float *part_o,
-                        float *part_m, float *part_l, const tt_attn_batch_params *p) {
+// One K and one V tensor map per session of a verify batch ([seq_len rows][n_kv_heads * 256], box
+// 128 x 64, keys past seq_len read as zero), written into the staging table that the caller uploads
+// together with the session and item tables.
+int tt_verify_tc_encode_maps(tt_context *ctx, uint32_t n_sessions, const tt_attn_batch_params *p) {
     CUtensorMap *maps = reinterpret_cast<CUtensorMap *>(ctx->h_tensor_maps);
     for (uint32_t i = 0; i < n_sessions; ++i) {
         const TTDecodeSession &s = ctx->h_sessions[i];
@@ -469,15 +494,21 @@ int tt_launch_verify_tc(tt_context *ctx, cudaStream_t stream, uint32_t n_session
                                               p->kv_token_stride_elements, kBK);
         if (!ok) return tt_set_error(ctx, TT_ERR_CUDA, "cuTensorMapEncodeTiled failed for session %u", i);
     }
-    cudaError_t e = cudaMemcpyAsync(ctx->tensor_maps, maps, sizeof(CUtensorMap) * 2 * n_sessions,
-                                    cudaMemcpyHostToDevice, stream);
-    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "copy tensor maps");
+    return TT_OK;
+}
 
+// Pass 1 of a verify batch on the tensor cores: the items (one per (session, kv head, key range), all
+// packed rows at once), the sessions and the tensor maps are already on the device.
+int tt_launch_verify_tc(tt_context *ctx, cudaStream_t stream, uint32_t n_sessions, uint32_t n_items, float *part_o,
+                        float *part_m, float *part_l, const tt_attn_batch_params *p, bool direct) {
+    (void)n_sessions;
+    cudaError_t e;
     VerifyParams kp;
     kp.items = ctx->items; kp.sessions = ctx->sessions;
     kp.maps = reinterpret_cast<const CUtensorMap *>(ctx->tensor_maps);
     kp.part_o = part_o; kp.part_m = part_m; kp.part_l = part_l;
     kp.n_q_heads = p->n_q_heads; kp.n_kv_heads = p->n_kv_heads; kp.q_row_stride = p->q_row_stride_elements;
+    kp.out_row_stride = p->out_row_stride_elements; kp.direct = direct ? 1u : 0u;
     kp.scale_log2 = p->scale * kLog2e;
     kp.idesc_qk = tt_make_idesc_f16(p->io_dtype, kRows, false, false);
     kp.idesc_pv = tt_make_idesc_f16(p->io_dtype, kRows, true, true);

@@ -35,13 +35,25 @@ TT_API const char *tt_status_string(int status) {
 
 TT_API const char *tt_last_error_string(const tt_context *ctx) { return ctx ? ctx->err : "null context"; }
 
+// Lays the three tables of a decode call out back to back (128-byte aligned) in the host staging
+// buffer and, identically, in the device buffer: sessions, then (verify batches) two tensor maps per
+// session, then the items.
+void tt_bind_decode_tables(tt_context *ctx, uint32_t n_sessions, bool with_maps) {
+    const size_t off_maps = (sizeof(TTDecodeSession) * n_sessions + 127) / 128 * 128;
+    const size_t off_items = off_maps + (with_maps ? (size_t)256 * n_sessions : 0);
+    ctx->sessions = reinterpret_cast<TTDecodeSession *>(ctx->tables);
+    ctx->tensor_maps = ctx->tables + off_maps;
+    ctx->items = reinterpret_cast<TTDecodeItem *>(ctx->tables + off_items);
+    ctx->h_sessions = reinterpret_cast<TTDecodeSession *>(ctx->h_tables);
+    ctx->h_tensor_maps = ctx->h_tables + off_maps;
+    ctx->h_items = reinterpret_cast<TTDecodeItem *>(ctx->h_tables + off_items);
+}
+
 static void context_free(tt_context *ctx) {
     if (ctx == nullptr) return;
     cudaFree(ctx->partials);
-    cudaFree(ctx->items);
-    cudaFree(ctx->sessions);
+    cudaFree(ctx->tables);
     cudaFree(ctx->gdn_sessions);
-    cudaFree(ctx->tensor_maps);
     cudaFree(ctx->status);
     if (ctx->profile_begin) {
         for (uint32_t i = 0; i < tt_context::kProfileSlots; ++i) {
@@ -51,12 +63,10 @@ static void context_free(tt_context *ctx) {
         free(ctx->profile_begin);
         free(ctx->profile_end);
     }
-    free(ctx->h_items);
-    free(ctx->h_sessions);
+    free(ctx->h_tables);
     free(ctx->h_sessions_in);
     free(ctx->h_keys);
     free(ctx->h_rows);
-    free(ctx->h_tensor_maps);
     delete ctx;
 }
 
@@ -83,19 +93,18 @@ TT_API tt_context *tt_context_create(int device, const tt_context_options *optio
 
     bool ok = true;
     ok = ok && cudaMalloc(&ctx->partials, ctx->workspace_bytes) == cudaSuccess;
-    ok = ok && cudaMalloc(&ctx->items, sizeof(TTDecodeItem) * ctx->max_items) == cudaSuccess;
-    ok = ok && cudaMalloc(&ctx->sessions, sizeof(TTDecodeSession) * ctx->max_sessions) == cudaSuccess;
+    ctx->table_bytes = (sizeof(TTDecodeSession) * ctx->max_sessions + 127) / 128 * 128 + (size_t)256 * ctx->max_sessions +
+                       sizeof(TTDecodeItem) * ctx->max_items;
+    ok = ok && cudaMalloc(&ctx->tables, ctx->table_bytes) == cudaSuccess;
     ok = ok && cudaMalloc(&ctx->gdn_sessions, sizeof(tt_gdn_session) * ctx->max_sessions) == cudaSuccess;
-    ok = ok && cudaMalloc(&ctx->tensor_maps, (size_t)256 * ctx->max_sessions) == cudaSuccess;   // 2 x 128 B each
     ok = ok && cudaMalloc(&ctx->status, sizeof(uint32_t)) == cudaSuccess;
     ok = ok && cudaMemset(ctx->status, 0, sizeof(uint32_t)) == cudaSuccess;
-    ctx->h_items = (TTDecodeItem *)malloc(sizeof(TTDecodeItem) * ctx->max_items);
-    ctx->h_sessions = (TTDecodeSession *)malloc(sizeof(TTDecodeSession) * ctx->max_sessions);
+    ctx->h_tables = (unsigned char *)aligned_alloc(128, (ctx->table_bytes + 127) / 128 * 128);
     ctx->h_sessions_in = (TTDecodeSession *)malloc(sizeof(TTDecodeSession) * ctx->max_sessions);
     ctx->h_keys = (uint32_t *)malloc(sizeof(uint32_t) * ctx->max_sessions);
     ctx->h_rows = (uint32_t *)malloc(sizeof(uint32_t) * ctx->max_sessions);
-    ctx->h_tensor_maps = aligned_alloc(128, (size_t)256 * ctx->max_sessions);
-    ok = ok && ctx->h_items && ctx->h_sessions && ctx->h_sessions_in && ctx->h_keys && ctx->h_rows && ctx->h_tensor_maps;
+    ok = ok && ctx->h_tables && ctx->h_sessions_in && ctx->h_keys && ctx->h_rows;
+    if (ok) tt_bind_decode_tables(ctx, ctx->max_sessions, true);
     if (!ok) {
         cudaGetLastError();
         context_free(ctx);

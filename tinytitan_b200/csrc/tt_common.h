@@ -56,8 +56,14 @@ struct tt_context {
     uint32_t max_sessions = 0;
     uint32_t max_items = 0;
     // device scratch, allocated once at creation
+    unsigned char *tables = nullptr;    // session table | tensor maps | item table of the current decode call,
+    unsigned char *h_tables = nullptr;  // packed back to back so that one copy uploads them. Pageable on
+                                        // purpose: the driver stages small pageable copies inline in the
+                                        // command stream, which measured faster than a pinned staging ring
+                                        // (whose DMA fetch sits on the stream's critical path).
+    size_t table_bytes = 0;
     float *partials = nullptr;          // [rows][head_dim + 2] fp32 split partials
-    TTDecodeItem *items = nullptr;
+    TTDecodeItem *items = nullptr;      // views into `tables`, rebound by every decode call
     TTDecodeSession *sessions = nullptr;
     void *gdn_sessions = nullptr;       // tt_gdn_session[max_sessions]
     void *tensor_maps = nullptr;        // CUtensorMap[2 * max_sessions]: per-session K and V maps (verify kernel)
@@ -81,7 +87,7 @@ struct tt_context {
 };
 
 int tt_set_error(tt_context *ctx, int code, const char *fmt, ...);
-
+void tt_bind_decode_tables(tt_context *ctx, uint32_t n_sessions, bool with_maps);
 // Brackets one kernel launch with an event pair when the context profiles its class.
 struct TTLaunchTimer {
     tt_context *ctx;
