@@ -672,12 +672,14 @@ attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions, const f
                            const float *__restrict__ part_m, const float *__restrict__ part_l,
                            uint32_t n_q_heads, uint32_t head_dim, uint32_t out_row_stride, int mode,
                            float *__restrict__ m_out, float *__restrict__ d_out, float *__restrict__ o_out,
-                           const TTDecodeSession single, int use_single) {
-    // 256 threads = 4 groups of 64 column threads (one float4 of the row each); group g merges
-    // parts g, g+4, ... so that a long session's hundreds of parts are read with many loads in
-    // flight instead of one after another.
+                           const TTDecodeSession single, int use_single, uint32_t col_threads) {
+    // 256 threads = G groups of `col_threads` column threads (one float4 of the row each); group g
+    // merges parts g, g+G, ... so that a long session's hundreds of parts are read with many loads
+    // in flight instead of one after another. Batches with many (session, row) pairs use one CTA per
+    // row (64 column threads, G = 4); a few long sessions split the columns over gridDim.z CTAs
+    // (16 column threads, G = 16) so that the merge still fills the machine.
     __shared__ float red[16];
-    __shared__ float4 accs[4][64];
+    __shared__ float4 accs[256];
     const TTDecodeSession ses = use_single ? single : sessions[blockIdx.x];
     const uint32_t rows_total = ses.q_rows * n_q_heads;
     const uint32_t rho = blockIdx.y;
@@ -685,7 +687,8 @@ attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions, const f
     const uint32_t n_parts = ses.n_parts;
     const size_t base = (size_t)ses.partial_base + rho;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t grp = threadIdx.x >> 6, ct = threadIdx.x & 63;
+    const uint32_t grp = threadIdx.x / col_threads, ct = threadIdx.x % col_threads;
+    const uint32_t n_groups = 256 / col_threads;
 
     float mg = -INFINITY;
     for (uint32_t c = threadIdx.x; c < n_parts; c += 256) mg = fmaxf(mg, part_m[base + (size_t)c * rows_total]);
@@ -710,15 +713,15 @@ attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions, const f
 #pragma unroll
     for (int i = 0; i < 8; ++i) D += red[8 + i];
 
-    const uint32_t col = ct * 4;
+    const uint32_t col = (blockIdx.z * col_threads + ct) * 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (mg != -INFINITY && col < head_dim) {
         uint32_t c = grp;
-        for (; c + 12 < n_parts; c += 16) {   // four independent loads in flight per thread
+        for (; c + 3 * n_groups < n_parts; c += 4 * n_groups) {   // four independent loads in flight per thread
             float e[4]; float4 o[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const size_t pr = base + (size_t)(c + 4 * u) * rows_total;
+                const size_t pr = base + (size_t)(c + n_groups * u) * rows_total;
                 e[u] = part_m[pr];
                 o[u] = *reinterpret_cast<const float4 *>(part_o + pr * head_dim + col);
             }
@@ -728,19 +731,18 @@ attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions, const f
                 acc.x += o[u].x * wgt; acc.y += o[u].y * wgt; acc.z += o[u].z * wgt; acc.w += o[u].w * wgt;
             }
         }
-        for (; c < n_parts; c += 4) {
+        for (; c < n_parts; c += n_groups) {
             const size_t pr = base + (size_t)c * rows_total;
             const float wgt = __expf(part_m[pr] - mg);
             const float4 o = *reinterpret_cast<const float4 *>(part_o + pr * head_dim + col);
             acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
         }
     }
-    accs[grp][ct] = acc;
+    accs[grp * col_threads + ct] = acc;
     __syncthreads();
     if (grp != 0 || col >= head_dim) return;
-#pragma unroll
-    for (int g = 1; g < 4; ++g) {
-        const float4 o = accs[g][ct];
+    for (uint32_t g = 1; g < n_groups; ++g) {
+        const float4 o = accs[g * col_threads + ct];
         acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
     }
     const uint32_t w = rho / n_q_heads, h = rho % n_q_heads;
@@ -753,7 +755,7 @@ attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions, const f
         *reinterpret_cast<uint2 *>(dst) = packed;
     } else {
         *reinterpret_cast<float4 *>(o_out + (size_t)rho * head_dim + col) = acc;
-        if (ct == 0) {
+        if (ct == 0 && blockIdx.z == 0) {
             m_out[rho] = mg;
             d_out[rho] = D;
         }
@@ -1164,16 +1166,18 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     ctx->launches++;
     if (direct) return TT_OK;
 
-    const dim3 grid(n_sessions, max_rows);
+    // few (session, row) pairs: split the row's columns over several CTAs so the merge fills the GPU
+    const uint32_t col_threads = (uint64_t)n_sessions * max_rows * 2 <= (uint64_t)ctx->sm_count ? 16u : 64u;
+    const dim3 grid(n_sessions, max_rows, (p->head_dim / 4 + col_threads - 1) / col_threads);
     const uint32_t threads = 256;
     if (p->io_dtype == TT_F16)
         attn_decode_combine_kernel<__half><<<grid, threads, 0, stream>>>(
             ctx->sessions, part_o, part_m, part_l, p->n_q_heads, p->head_dim, p->out_row_stride_elements, mode,
-            m_out, d_out, o_out, single_ses, single ? 1 : 0);
+            m_out, d_out, o_out, single_ses, single ? 1 : 0, col_threads);
     else
         attn_decode_combine_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
             ctx->sessions, part_o, part_m, part_l, p->n_q_heads, p->head_dim, p->out_row_stride_elements, mode,
-            m_out, d_out, o_out, single_ses, single ? 1 : 0);
+            m_out, d_out, o_out, single_ses, single ? 1 : 0, col_threads);
     e = cudaGetLastError();
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_decode_combine launch");
     ctx->launches++;
@@ -1420,8 +1424,8 @@ TT_API int tt_attn_decode_noalloc(tt_stream stream, const void *q, const void *k
     p.out_row_stride_elements = n_q_heads * head_dim; p.scale = scale; p.io_dtype = TT_F16;
     if (launch_partial_hd<__half>(s, cursor, d_items, d_ses, part_o, part_m, part_l, &p, status) != cudaSuccess)
         return TT_ERR_CUDA;
-    attn_decode_combine_kernel<__half><<<dim3(1, n_q_heads), 256, 0, s>>>(d_ses, part_o, part_m, part_l, n_q_heads,
-                                                                         head_dim, n_q_heads * head_dim, 0, nullptr,
-                                                                         nullptr, nullptr, host.ses, 0);
+    attn_decode_combine_kernel<__half><<<dim3(1, n_q_heads, (head_dim / 4 + 15) / 16), 256, 0, s>>>(
+        d_ses, part_o, part_m, part_l, n_q_heads, head_dim, n_q_heads * head_dim, 0, nullptr, nullptr, nullptr, host.ses,
+        0, 16u);
     return cudaGetLastError() == cudaSuccess ? TT_OK : TT_ERR_CUDA;
 }
