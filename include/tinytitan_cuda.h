@@ -167,6 +167,32 @@ int tt_attn_combine(tt_context *ctx, tt_stream stream, const float *m, const flo
                     const float *o, uint32_t n_parts, uint32_t n_q_heads, uint32_t head_dim,
                     void *out, uint32_t io_dtype);
 
+/* The same merge when the n_parts triples live on `world` GPUs of one node, one per GPU (one
+ * process per GPU): exchange and merge in ONE kernel over peer memory instead of a collective
+ * followed by tt_attn_combine. The reference has no multi-device code; the triple is its
+ * chunk-partial format (attention.metal:146-159) and the result equals tt_attn_combine over the
+ * world triples (attention.metal:395-437).
+ *
+ * Every rank owns an exchange buffer (tt_peer_buffer_create) that the other ranks map
+ * (tt_peer_buffer_open) with the 64-byte handle the owner hands out through any host channel.
+ * tt_attn_exchange_combine stores this rank's triple into slot `rank` of every rank's buffer
+ * (plain stores over NVLink), publishes it with a release store of `epoch` to a per-head flag,
+ * waits -- with a poll limit, TT_DEV_WAIT_TIMEOUT in the status word when it runs out -- until
+ * all ranks' flags of this epoch have arrived in its own buffer, and merges. `epoch` must be
+ * the same on all ranks for one step and grow by exactly 1 per step, starting at 1 (slots are
+ * double-buffered on its parity: a rank can be at most one step ahead of another).
+ * peer_buffers[r] is rank r's buffer as mapped by THIS process (its own for r == rank).
+ * world <= 16; head_dim a multiple of 4. */
+size_t tt_attn_exchange_bytes(uint32_t world, uint32_t n_q_heads, uint32_t head_dim);
+int tt_peer_buffer_create(tt_context *ctx, size_t bytes, void **out_ptr, unsigned char out_handle[64]);
+int tt_peer_buffer_open(tt_context *ctx, const unsigned char handle[64], void **out_ptr);
+int tt_peer_buffer_close(tt_context *ctx, void *ptr);
+int tt_peer_buffer_destroy(tt_context *ctx, void *ptr);
+int tt_attn_exchange_combine(tt_context *ctx, tt_stream stream, const float *m, const float *d,
+                             const float *o, void *const *peer_buffers, uint32_t rank, uint32_t world,
+                             uint32_t n_q_heads, uint32_t head_dim, uint32_t epoch, void *out,
+                             uint32_t io_dtype);
+
 /* No counterpart in the reference. One query row against one session's fp16 cache
  * ([kv_start, seq_len), tight K/V rows), computed exactly like tt_attn_decode, for
  * callers that must not allocate device memory -- code running where cudaMalloc is off

@@ -42,6 +42,37 @@ def main():
     dist.all_gather(gathered, out)
     assert all(torch.equal(gathered[0], t) for t in gathered)
 
+    # the same merge with exchange and merge fused in one kernel over peer memory: bit-identical
+    # inputs per rank, so the result may differ from the all-gather path only by summation order
+    fused = sharding.LongContextDecode(attn, hd, hq, hkv, 0.0625, fused=True)
+    out_f = torch.empty_like(out)
+    for _ in range(5):     # several steps: both parities of the double-buffered slots are reused
+        out_f.zero_()
+        fused.step(q, k_local, v_local, hi - lo, out_f)
+    torch.cuda.synchronize()
+    assert ctx.poll_status() == 0
+    err = (out_f.float() - full.float()).abs().max().item()
+    assert err <= 1e-3, f"rank {rank}: fused exchange differs from single-GPU attention by {err}"
+    assert (out_f.float() - out.float()).abs().max().item() <= 1e-3
+    # device time of one step, both ways (max over ranks is taken by the reader of the log)
+    def timed(fn, reps=50):
+        for _ in range(5):
+            fn()
+        dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    t_nccl = timed(lambda: lc.step(q, k_local, v_local, hi - lo, out))
+    t_fused = timed(lambda: fused.step(q, k_local, v_local, hi - lo, out_f))
+    if rank == 0:
+        print(f"SPLIT_KV_STEP_MS world={world} S={s} nccl={t_nccl:.4f} fused={t_fused:.4f}")
+    fused.close()
+
     # independent sessions: each is decoded on exactly one rank, nothing is exchanged on the data path
     lens = [257 * (i + 1) for i in range(8)]
     mine = sharding.shard_sessions(lens, world)[rank]

@@ -117,6 +117,13 @@ SIGNATURES = {
     "tt_attn_decode_partial": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.c_float, _u32,
                                          _u32, _vp, _vp, _vp]),
     "tt_attn_combine": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _u32]),
+    "tt_attn_exchange_bytes": (C.c_size_t, [_u32, _u32, _u32]),
+    "tt_peer_buffer_create": (C.c_int, [_vp, C.c_size_t, C.POINTER(_vp), C.c_char_p]),
+    "tt_peer_buffer_open": (C.c_int, [_vp, C.c_char_p, C.POINTER(_vp)]),
+    "tt_peer_buffer_close": (C.c_int, [_vp, _vp]),
+    "tt_peer_buffer_destroy": (C.c_int, [_vp, _vp]),
+    "tt_attn_exchange_combine": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.POINTER(_vp), _u32, _u32, _u32, _u32, _u32, _vp,
+                                           _u32]),
     "tt_attn_decode_noalloc": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.c_float]),
     "tt_attn_reference_split_geometry": (None, [_u32, _u32, _u32, _u32, C.c_int, C.POINTER(SplitGeometry)]),
     "tt_attn_plan_splits": (C.c_int, [C.POINTER(_u32), C.POINTER(_u32), _u32, _u32, _u32, _u32, _u32, C.c_size_t,

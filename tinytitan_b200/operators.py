@@ -264,6 +264,55 @@ class Attention:
             self.context.handle, _stream(command_buffer), _addr(m), _addr(d), _addr(o), n_parts, num_q_heads,
             head_dim, _addr(out), io_dtype if io_dtype is not None else _dtype_of(out)))
 
+    def encode_exchange_combine(self, m, d, o, exchange, num_q_heads, head_dim, out, io_dtype=None, command_buffer=None):
+        """Cross-GPU merge in one kernel: this rank's triple goes to every rank's exchange buffer over
+        peer memory, the kernel waits (bounded) for the others' and merges. `exchange` is a PeerExchange."""
+        self.context.check(L.lib().tt_attn_exchange_combine(
+            self.context.handle, _stream(command_buffer), _addr(m), _addr(d), _addr(o), exchange.pointer_array,
+            exchange.rank, exchange.world, num_q_heads, head_dim, exchange.next_epoch(), _addr(out),
+            io_dtype if io_dtype is not None else _dtype_of(out)))
+
+
+class PeerExchange:
+    """One exchange buffer per rank, mapped into every rank of the group (one process per GPU, one node).
+
+    `gather_handles(handle_bytes) -> list of every rank's handle bytes` is the host channel; with
+    torch.distributed it is an all_gather_object."""
+
+    def __init__(self, context: Context, rank: int, world: int, num_q_heads: int, head_dim: int, gather_handles):
+        self.context, self.rank, self.world = context, rank, world
+        self.bytes = L.lib().tt_attn_exchange_bytes(world, num_q_heads, head_dim)
+        mine = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        context.check(L.lib().tt_peer_buffer_create(context.handle, self.bytes, C.byref(mine), handle))
+        self.local = mine.value
+        handles = gather_handles(handle.raw)
+        self.opened = []
+        ptrs = []
+        for r in range(world):
+            if r == rank:
+                ptrs.append(self.local)
+                continue
+            p = C.c_void_p()
+            context.check(L.lib().tt_peer_buffer_open(context.handle, handles[r], C.byref(p)))
+            self.opened.append(p.value)
+            ptrs.append(p.value)
+        self.pointer_array = (C.c_void_p * world)(*ptrs)
+        self.epoch = 0
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    def close(self):
+        """Unmap the peers' buffers and free this rank's (every rank must have stopped using them)."""
+        for p in self.opened:
+            L.lib().tt_peer_buffer_close(self.context.handle, p)
+        self.opened = []
+        if self.local:
+            L.lib().tt_peer_buffer_destroy(self.context.handle, self.local)
+            self.local = None
+
 
 def quantize_kv_rows(context: Context, source, destination, element_count: int, bits: int, tokens: int,
                      source_stride_elements=None, destination_stride_bytes=None, values_bytes=None, group_size=64,

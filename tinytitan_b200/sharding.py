@@ -79,11 +79,23 @@ class LongContextDecode:
     logical position lo_r). `step` runs pass 1 on the local rows, all-gathers the triples and
     merges them on every rank."""
 
-    def __init__(self, attention, head_dim: int, num_q_heads: int, num_kv_heads: int, scale: float, group=None):
+    def __init__(self, attention, head_dim: int, num_q_heads: int, num_kv_heads: int, scale: float, group=None,
+                 fused: bool = False):
         import torch
         import torch.distributed as dist
         self.attention, self.hd, self.hq, self.hkv, self.scale, self.group = attention, head_dim, num_q_heads, num_kv_heads, scale, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        # fused: the triples travel by peer stores inside the merge kernel (tt_attn_exchange_combine)
+        # instead of an NCCL all-gather followed by tt_attn_combine
+        self.exchange = None
+        if fused and self.world > 1:
+            from .operators import PeerExchange
+
+            def gather(handle: bytes):
+                handles = [None] * self.world
+                dist.all_gather_object(handles, handle, group=group)
+                return handles
+            self.exchange = PeerExchange(attention.context, dist.get_rank(group), self.world, num_q_heads, head_dim, gather)
         dev = torch.device("cuda", attention.context.device)
         self.m = torch.empty(num_q_heads, device=dev)
         self.d = torch.empty(num_q_heads, device=dev)
@@ -96,6 +108,9 @@ class LongContextDecode:
         import torch.distributed as dist
         self.attention.encode_partial(q, k_local, v_local, self.hd, self.hq, self.hkv, local_rows, 0, self.m,
                                       self.d, self.o, scale=self.scale)
+        if self.exchange is not None:
+            self.attention.encode_exchange_combine(self.m, self.d, self.o, self.exchange, self.hq, self.hd, out)
+            return out
         torch.cat([self.o, self.m.unsqueeze(1), self.d.unsqueeze(1)], dim=1, out=self.packed)
         if self.world > 1:
             dist.all_gather_into_tensor(self.gathered, self.packed, group=self.group)
@@ -104,3 +119,13 @@ class LongContextDecode:
         m, d, o = unpack_partials(self.gathered)
         self.attention.encode_combine(m, d, o, self.world, self.hq, self.hd, out)
         return out
+
+    def close(self):
+        """Collective: every rank stops using the exchange buffers, then unmaps and frees them."""
+        if self.exchange is not None:
+            import torch
+            import torch.distributed as dist
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+            self.exchange.close()
+            self.exchange = None
