@@ -545,6 +545,49 @@ def aux_measurements(w, pk, only=None, c5_sessions=64):
     return aux
 
 
+def split_kv_c4(w, torch, dist, rank, world, pk):
+    """Config 4 on `world` GPUs: one session of 262,144 keys (16/2/256 fp16) whose KV rows are split
+    along the sequence; one decode step = pass 1 on the local rows + the cross-GPU merge, once with
+    an NCCL all-gather followed by the merge kernel and once with exchange and merge fused in one
+    kernel over peer memory. Device time per step, max over ranks."""
+    from tinytitan_b200 import sharding
+    s4 = 262144
+    lo, hi = sharding.kv_split_ranges(s4, world)[rank]
+    g = torch.Generator(device="cuda"); g.manual_seed(600 + rank)
+    k = torch.randn(hi - lo, HKV * HD, device="cuda", generator=g).half()
+    v = torch.randn(hi - lo, HKV * HD, device="cuda", generator=g).half()
+    g.manual_seed(6)
+    q = torch.randn(HQ, HD, device="cuda", generator=g).half()
+    out_a, out_b = torch.empty_like(q), torch.empty_like(q)
+    plain = sharding.LongContextDecode(w.attn, HD, HQ, HKV, SCALE)
+    fused = sharding.LongContextDecode(w.attn, HD, HQ, HKV, SCALE, fused=True)
+
+    def timed(fn, reps=100):
+        for _ in range(5):
+            fn()
+        dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms_nccl = timed(lambda: plain.step(q, k, v, hi - lo, out_a))
+    ms_fused = timed(lambda: fused.step(q, k, v, hi - lo, out_b))
+    agree = float((out_a.float() - out_b.float()).abs().max().item())
+    status = w.ctx.poll_status()
+    fused.close()
+    bytes_total = s4 * HKV * HD * 2 * 2 + HQ * HD * 2 * 2
+    return {"S": s4, "keys_per_gpu": hi - lo, "ms_nccl_allgather": ms_nccl, "ms_fused_exchange": ms_fused,
+            "GBps_aggregate_fused": bytes_total / ms_fused / 1e6,
+            "frac_hbm_aggregate_fused": bytes_total / ms_fused / 1e6 / (pk["hbm_gbs"] * world),
+            "max_abs_diff_between_paths": agree, "device_status": status,
+            "note": "one Python call per step on every rank; device time, max over ranks"}
+
+
 # ncu (dram__bytes_read.sum + dram__bytes_write.sum) of attn_decode_partial_kernel per algorithmic
 # byte, from the 8-session capture summarised in profiles/decode_partial_8sessions_ncu_full.md
 # (227.1 MB of DRAM traffic for 216.9 MB of algorithmic bytes). Traffic grows in proportion to
@@ -597,6 +640,13 @@ def run_gpu_arm(args):
     clocks = sampler.stop()
     clocks["note"] = "sampled over the timed regions plus 0.7 s of the same step replayed afterwards"
 
+    c4 = None
+    if world > 1 and not args.no_aux:
+        try:
+            c4 = split_kv_c4(w, torch, dist, rank, world, pk)
+        except Exception as exc:   # the same code runs on every rank, so a failure is common to all
+            c4 = {"error": str(exc)}
+
     ms_per_step = ms_total / args.steps
     value = world * N_SESSIONS / (ms_per_step * 1e-3)
     e2e_value = world * N_SESSIONS / (ms_e2e / e2e_steps * 1e-3)
@@ -627,6 +677,8 @@ def run_gpu_arm(args):
             line["aux"]["cpu"] = cpu_side_baselines()
         else:
             line["cpu_baseline"] = None
+            if c4 is not None:
+                line["aux"] = {"decode_c4_split_kv": c4}
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
