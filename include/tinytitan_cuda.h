@@ -229,6 +229,16 @@ int tt_attn_plan_splits(const uint32_t *keys_per_session, const uint32_t *q_rows
                         uint32_t n_kv_heads, uint32_t sm_count, size_t workspace_bytes,
                         uint32_t *out_keys_per_item, uint32_t *out_n_items);
 
+/* The split plan of the tensor-core verify pass (17..64 packed rows per KV head, head_dim 256), as
+ * pure arithmetic: one work item per (session, kv head, part); the parts of a session have one
+ * common length, a multiple of the 128-key tile, chosen for the whole batch by simulating the
+ * in-order dispatch of the items over sm_count SMs. out_parts / out_part_len: [n_sessions].
+ * TT_ERR_OOM when no plan fits workspace_bytes (0 = no limit). */
+int tt_attn_plan_verify_splits(const uint32_t *keys_per_session, const uint32_t *q_rows_per_session,
+                               uint32_t n_sessions, uint32_t head_dim, uint32_t n_q_heads,
+                               uint32_t n_kv_heads, uint32_t sm_count, size_t workspace_bytes,
+                               uint32_t *out_parts, uint32_t *out_part_len, uint32_t *out_n_items);
+
 /* Replaces kv_cache_quantize_affine
  * (sources/TinyTitanCore/Metal/Quant/kv_cache_quantize.metal:4-72): fp16 rows
  * [tokens][source_stride_elements] -> packed rows of destination_stride_bytes with the

@@ -75,6 +75,39 @@ def test_split_planner():
     assert rc == L.TT_ERR_OOM
 
 
+def _plan_verify(keys, rows, hd=256, hq=32, hkv=2, sms=148, ws=192 << 20):
+    n = len(keys)
+    k = (ctypes.c_uint32 * n)(*keys); r = (ctypes.c_uint32 * n)(*rows)
+    parts, lens = (ctypes.c_uint32 * n)(), (ctypes.c_uint32 * n)()
+    items = ctypes.c_uint32(0)
+    rc = L.lib().tt_attn_plan_verify_splits(k, r, n, hd, hq, hkv, sms, ws, parts, lens, ctypes.byref(items))
+    return rc, list(parts), list(lens), items.value
+
+
+def test_verify_split_planner():
+    # config 5 on one GPU: 64 sessions x 2 kv heads = 128 streams for 148 SMs: one item per stream
+    # (a second wave of half-length items would not finish sooner)
+    rc, parts, lens, items = _plan_verify([16387] * 64, [4] * 64)
+    assert rc == 0 and parts == [1] * 64 and lens == [16512] * 64 and items == 128
+    # its per-GPU share on 8 GPUs: 16 streams are cut so that one wave fills the SMs
+    rc, parts, lens, items = _plan_verify([16387] * 8, [4] * 8)
+    assert rc == 0 and len(set(parts)) == 1 and 100 <= items <= 148
+    # ragged batch: equal parts inside a session, tile multiples, every key covered exactly once
+    rng = np.random.default_rng(1)
+    keys = [int(x) for x in rng.integers(1, 40000, size=23)] + [0]
+    rc, parts, lens, items = _plan_verify(keys, [4] * 24)
+    assert rc == 0 and items == 2 * sum(parts)
+    for k, p, l in zip(keys, parts, lens):
+        assert p >= 1 and l % 128 == 0 and p * l >= k and (p - 1) * l < max(k, 1)
+        assert l >= 128 or k == 0
+    # short contexts stay one part (the pass then stores the outputs itself)
+    rc, parts, lens, items = _plan_verify([500, 300, 4, 129], [4] * 4)
+    assert rc == 0 and parts == [1, 1, 1, 1]
+    # partials that cannot fit the workspace are refused, not truncated
+    rc, _, _, _ = _plan_verify([100000] * 8, [4] * 8, ws=1024)
+    assert rc == L.TT_ERR_OOM
+
+
 def test_context_without_gpu_fails_loudly():
     import torch
     if torch.cuda.is_available():

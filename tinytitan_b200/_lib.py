@@ -128,6 +128,8 @@ SIGNATURES = {
     "tt_attn_reference_split_geometry": (None, [_u32, _u32, _u32, _u32, C.c_int, C.POINTER(SplitGeometry)]),
     "tt_attn_plan_splits": (C.c_int, [C.POINTER(_u32), C.POINTER(_u32), _u32, _u32, _u32, _u32, _u32, C.c_size_t,
                                       C.POINTER(_u32), C.POINTER(_u32)]),
+    "tt_attn_plan_verify_splits": (C.c_int, [C.POINTER(_u32), C.POINTER(_u32), _u32, _u32, _u32, _u32, _u32, C.c_size_t,
+                                             C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32)]),
     "tt_attn_pre": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, C.c_float, C.c_float,
                               _u32, _u32, _u32]),
     "tt_attn_gate_mul": (C.c_int, [_vp, _vp, _vp, _vp, _u32]),

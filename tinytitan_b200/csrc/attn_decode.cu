@@ -961,14 +961,16 @@ static uint64_t wide_makespan(const uint32_t *keys, uint32_t n_sessions, uint32_
     return makespan;
 }
 
-static bool plan_wide(tt_context *ctx, const TTDecodeSession *in_sessions, uint32_t n_sessions,
-                      const tt_attn_batch_params *p, const uint32_t *keys, uint32_t *out_items,
-                      uint32_t *out_partial_rows, uint32_t *out_max_rows) {
+// Part length (a multiple of 128) of the tensor-core verify pass, 0 when nothing fits.
+static uint32_t wide_part_length(const uint32_t *keys, const uint32_t *q_rows, uint32_t n_sessions, uint32_t head_dim,
+                                 uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t sm_count, size_t workspace_bytes,
+                                 uint32_t max_items) {
     uint32_t max_keys = 0;
     for (uint32_t i = 0; i < n_sessions; ++i) max_keys = keys[i] > max_keys ? keys[i] : max_keys;
     static const uint32_t kPartChoices[] = {1, 2, 3, 4, 5, 6, 8, 10, 12, 16, 20, 24, 32, 48, 64};
     std::vector<uint32_t> heap;
-    uint64_t target = 0, best = ~(uint64_t)0;
+    uint64_t best = ~(uint64_t)0;
+    uint32_t target = 0;
     for (uint32_t parts : kPartChoices) {
         uint32_t len = (ceil_div_u32(max_keys, parts) + 127) / 128 * 128;
         if (len < 512) len = 512;                 // at least four tiles per item
@@ -976,16 +978,50 @@ static bool plan_wide(tt_context *ctx, const TTDecodeSession *in_sessions, uint3
         for (uint32_t i = 0; i < n_sessions; ++i) {
             uint32_t np = ceil_div_u32(keys[i], len);
             if (np == 0) np = 1;
-            items += (uint64_t)np * p->n_kv_heads;
-            prows += (uint64_t)np * in_sessions[i].q_rows * p->n_q_heads;
+            items += (uint64_t)np * n_kv_heads;
+            prows += (uint64_t)np * (q_rows ? q_rows[i] : 1u) * n_q_heads;
         }
-        if (prows * ((uint64_t)p->head_dim + 2) * sizeof(float) > ctx->workspace_bytes || items > ctx->max_items ||
-            items > 8192)
+        if ((workspace_bytes != 0 && prows * ((uint64_t)head_dim + 2) * sizeof(float) > workspace_bytes) ||
+            items > max_items || items > 8192) {
+            if (len == 512) break;
             continue;
-        const uint64_t span = wide_makespan(keys, n_sessions, p->n_kv_heads, len, (uint32_t)ctx->sm_count, heap);
+        }
+        const uint64_t span = wide_makespan(keys, n_sessions, n_kv_heads, len, sm_count, heap);
         if (span < best) { best = span; target = len; }
         if (len == 512) break;
     }
+    return target;
+}
+
+// The verify plan as pure arithmetic (what the launcher uses): for every session the number of
+// parts and their common length; sum(parts) * n_kv_heads items in all.
+TT_API int tt_attn_plan_verify_splits(const uint32_t *keys_per_session, const uint32_t *q_rows_per_session,
+                                      uint32_t n_sessions, uint32_t head_dim, uint32_t n_q_heads,
+                                      uint32_t n_kv_heads, uint32_t sm_count, size_t workspace_bytes,
+                                      uint32_t *out_parts, uint32_t *out_part_len, uint32_t *out_n_items) {
+    if (keys_per_session == nullptr || n_sessions == 0 || n_kv_heads == 0 || n_q_heads % n_kv_heads != 0 ||
+        head_dim == 0 || sm_count == 0)
+        return TT_ERR_INVALID_ARG;
+    const uint32_t target = wide_part_length(keys_per_session, q_rows_per_session, n_sessions, head_dim, n_q_heads,
+                                             n_kv_heads, sm_count, workspace_bytes, 65536u);
+    if (target == 0) return TT_ERR_OOM;
+    uint32_t items = 0;
+    for (uint32_t i = 0; i < n_sessions; ++i) {
+        uint32_t parts = ceil_div_u32(keys_per_session[i], target);
+        if (parts == 0) parts = 1;
+        if (out_parts) out_parts[i] = parts;
+        if (out_part_len) out_part_len[i] = (ceil_div_u32(keys_per_session[i], parts) + 127) / 128 * 128;
+        items += parts * n_kv_heads;
+    }
+    if (out_n_items) *out_n_items = items;
+    return TT_OK;
+}
+
+static bool plan_wide(tt_context *ctx, const TTDecodeSession *in_sessions, uint32_t n_sessions,
+                      const tt_attn_batch_params *p, const uint32_t *keys, uint32_t *out_items,
+                      uint32_t *out_partial_rows, uint32_t *out_max_rows) {
+    const uint32_t target = wide_part_length(keys, ctx->h_rows, n_sessions, p->head_dim, p->n_q_heads, p->n_kv_heads,
+                                             (uint32_t)ctx->sm_count, ctx->workspace_bytes, ctx->max_items);
     if (target == 0) return false;
     uint32_t partial_cursor = 0, item_cursor = 0, max_rows = 0;
     const uint32_t group = p->n_q_heads / p->n_kv_heads;
