@@ -193,6 +193,25 @@ int tt_attn_exchange_combine(tt_context *ctx, tt_stream stream, const float *m, 
                              uint32_t n_q_heads, uint32_t head_dim, uint32_t epoch, void *out,
                              uint32_t io_dtype);
 
+/* One decode step of a session whose KV rows are split over `world` GPUs, in two launches: the
+ * split-KV pass over this GPU's rows [kv_start, seq_len) (as tt_attn_decode_partial), then ONE
+ * kernel that merges this GPU's split partials, exchanges the result over peer memory and merges
+ * across GPUs (as tt_attn_exchange_combine, same buffers, same epoch rule); x->out receives the
+ * [n_q_heads][head_dim] output row on every rank. */
+typedef struct tt_attn_exchange {
+    void *const *peer_buffers; /* [world], as mapped by this process */
+    uint32_t rank;
+    uint32_t world;
+    uint32_t epoch;
+    uint32_t reserved;
+    void *out;
+} tt_attn_exchange;
+int tt_attn_decode_exchange(tt_context *ctx, tt_stream stream, const void *q, const void *k,
+                            const void *v, uint32_t head_dim, uint32_t n_q_heads,
+                            uint32_t n_kv_heads, uint32_t seq_len, uint32_t kv_start, float scale,
+                            uint32_t kv_token_stride_elements, uint32_t io_dtype,
+                            const tt_attn_exchange *x);
+
 /* No counterpart in the reference. One query row against one session's fp16 cache
  * ([kv_start, seq_len), tight K/V rows), computed exactly like tt_attn_decode, for
  * callers that must not allocate device memory -- code running where cudaMalloc is off

@@ -54,6 +54,15 @@ def main():
     err = (out_f.float() - full.float()).abs().max().item()
     assert err <= 1e-3, f"rank {rank}: fused exchange differs from single-GPU attention by {err}"
     assert (out_f.float() - out.float()).abs().max().item() <= 1e-3
+    # the exchange kernel alone, fed with a triple computed beforehand (the two-call form)
+    m_l = torch.empty(hq, device="cuda"); d_l = torch.empty(hq, device="cuda"); o_l = torch.empty(hq, hd, device="cuda")
+    out_t = torch.zeros_like(out)
+    for _ in range(3):
+        attn.encode_partial(q, k_local, v_local, hd, hq, hkv, hi - lo, 0, m_l, d_l, o_l, scale=0.0625)
+        attn.encode_exchange_combine(m_l, d_l, o_l, fused.exchange, hq, hd, out_t)
+    torch.cuda.synchronize()
+    assert ctx.poll_status() == 0
+    assert (out_t.float() - full.float()).abs().max().item() <= 1e-3
     # device time of one step, both ways (max over ranks is taken by the reader of the log)
     def timed(fn, reps=50):
         for _ in range(5):

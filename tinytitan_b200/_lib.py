@@ -99,6 +99,11 @@ class KVViewC(C.Structure):
 
 # name -> (restype, argtypes); every symbol include/tinytitan_cuda.h declares.
 _u32, _vp, _f32p = C.c_uint32, C.c_void_p, C.POINTER(C.c_float)
+class AttnExchange(C.Structure):
+    _fields_ = [("peer_buffers", C.POINTER(C.c_void_p)), ("rank", C.c_uint32), ("world", C.c_uint32),
+                ("epoch", C.c_uint32), ("reserved", C.c_uint32), ("out", C.c_void_p)]
+
+
 SIGNATURES = {
     "tt_context_create": (_vp, [C.c_int, C.POINTER(ContextOptions), C.POINTER(C.c_int)]),
     "tt_context_destroy": (None, [_vp]),
@@ -124,6 +129,8 @@ SIGNATURES = {
     "tt_peer_buffer_destroy": (C.c_int, [_vp, _vp]),
     "tt_attn_exchange_combine": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.POINTER(_vp), _u32, _u32, _u32, _u32, _u32, _vp,
                                            _u32]),
+    "tt_attn_decode_exchange": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.c_float, _u32, _u32,
+                                          C.POINTER(AttnExchange)]),
     "tt_attn_decode_noalloc": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.c_float]),
     "tt_attn_reference_split_geometry": (None, [_u32, _u32, _u32, _u32, C.c_int, C.POINTER(SplitGeometry)]),
     "tt_attn_plan_splits": (C.c_int, [C.POINTER(_u32), C.POINTER(_u32), _u32, _u32, _u32, _u32, _u32, C.c_size_t,

@@ -1054,11 +1054,14 @@ static bool plan_wide(tt_context *ctx, const TTDecodeSession *in_sessions, uint3
 }
 
 // mode 0: write normalised outputs to the sessions' `out`; mode 1: one merged triple for a
-// single session (m_out/d_out/o_out).
+// single session (m_out/d_out/o_out); mode 2: a single one-row session whose local merge is fused
+// with the cross-GPU exchange (`exchange`).
 int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession *in_sessions,
                      uint32_t n_sessions, const tt_attn_batch_params *p, int mode, float *m_out,
-                     float *d_out, float *o_out, const TTKvQuant *quant) {
+                     float *d_out, float *o_out, const TTKvQuant *quant, const tt_attn_exchange *exchange) {
     if (n_sessions == 0) return TT_OK;
+    if (mode == 2 && (exchange == nullptr || n_sessions != 1 || in_sessions[0].q_rows != 1))
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "the fused exchange serves one session with one query row");
     if (n_sessions > ctx->max_sessions)
         return tt_set_error(ctx, TT_ERR_INVALID_ARG, "n_sessions %u exceeds the context's max_sessions %u",
                             n_sessions, ctx->max_sessions);
@@ -1201,6 +1204,9 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     timer.stop();
     ctx->launches++;
     if (direct) return TT_OK;
+    if (mode == 2)
+        return tt_launch_merge_exchange(ctx, stream, part_o, part_m, part_l, ctx->h_sessions[0].n_parts, exchange,
+                                        p->n_q_heads, p->head_dim, p->io_dtype);
 
     // few (session, row) pairs: split the row's columns over several CTAs so the merge fills the GPU
     const uint32_t col_threads = (uint64_t)n_sessions * max_rows * 2 <= (uint64_t)ctx->sm_count ? 16u : 64u;
@@ -1314,6 +1320,24 @@ TT_API int tt_attn_decode_partial(tt_context *ctx, tt_stream stream, const void 
     s.kv_start = kv_start < seq_len ? kv_start : seq_len;
     s.n_parts = 0; s.partial_base = 0; s.ring_capacity = 0; s.keep = nullptr; s.row_index = nullptr;
     return tt_launch_decode(ctx, (cudaStream_t)stream, &s, 1, &p, 1, m_out, d_out, o_out);
+}
+
+TT_API int tt_attn_decode_exchange(tt_context *ctx, tt_stream stream, const void *q, const void *k, const void *v,
+                                   uint32_t head_dim, uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t seq_len,
+                                   uint32_t kv_start, float scale, uint32_t kv_token_stride_elements,
+                                   uint32_t io_dtype, const tt_attn_exchange *x) {
+    TT_ENTER(ctx);
+    if (x == nullptr) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "exchange descriptor must not be null");
+    tt_attn_batch_params p;
+    p.head_dim = head_dim; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
+    p.kv_token_stride_elements = kv_token_stride_elements ? kv_token_stride_elements : n_kv_heads * head_dim;
+    p.q_row_stride_elements = n_q_heads * head_dim; p.out_row_stride_elements = n_q_heads * head_dim;
+    p.scale = scale; p.io_dtype = io_dtype;
+    TTDecodeSession s;
+    s.q = q; s.out = nullptr; s.k = k; s.v = v; s.seq_len = seq_len; s.q_rows = 1;
+    s.kv_start = kv_start < seq_len ? kv_start : seq_len;
+    s.n_parts = 0; s.partial_base = 0; s.ring_capacity = 0; s.keep = nullptr; s.row_index = nullptr;
+    return tt_launch_decode(ctx, (cudaStream_t)stream, &s, 1, &p, 2, nullptr, nullptr, nullptr, nullptr, x);
 }
 
 TT_API int tt_attn_combine(tt_context *ctx, tt_stream stream, const float *m, const float *d, const float *o,

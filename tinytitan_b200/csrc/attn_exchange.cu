@@ -20,24 +20,34 @@ namespace {
 
 constexpr uint32_t kMaxWorld = 16;
 constexpr uint32_t kPollLimit = 1u << 22;   // polls of ~0.25 us before the wait gives up (about a second)
+constexpr uint32_t kColBlock = 64;          // columns per CTA: 16 threads x float4
+constexpr uint32_t kCellFloats = kColBlock + 4;   // o slice, m, d, two pads (cells stay 16-byte aligned)
 
+// One parity of an exchange buffer: cells [world][H][col blocks][kCellFloats] fp32, then flags
+// [world][H][col blocks] u32, padded to 256 B. A cell is one rank's (m, d) and 64 columns of o for
+// one head; every (head, col block) is exchanged and merged by one CTA on its own.
 struct ExchangeLayout {
-    uint32_t row_floats;     // head_dim + 4: o[head_dim], m, d, two pads (rows stay 16-byte aligned)
-    size_t parity_bytes;     // data [world][H][row_floats] fp32, then flags [world][H] u32, padded to 256 B
+    uint32_t col_blocks;
+    size_t parity_bytes;
     size_t flags_offset;
 };
 
 __host__ __device__ inline ExchangeLayout exchange_layout(uint32_t world, uint32_t n_q_heads, uint32_t head_dim) {
     ExchangeLayout l;
-    l.row_floats = head_dim + 4;
-    l.flags_offset = (size_t)world * n_q_heads * l.row_floats * sizeof(float);
-    l.parity_bytes = (l.flags_offset + (size_t)world * n_q_heads * sizeof(uint32_t) + 255) / 256 * 256;
+    l.col_blocks = (head_dim + kColBlock - 1) / kColBlock;
+    const size_t cells = (size_t)world * n_q_heads * l.col_blocks;
+    l.flags_offset = cells * kCellFloats * sizeof(float);
+    l.parity_bytes = (l.flags_offset + cells * sizeof(uint32_t) + 255) / 256 * 256;
     return l;
 }
 
 struct ExchangeParams {
     unsigned char *peer[kMaxWorld];
+    // input form 1: one merged triple per head
     const float *m, *d, *o;
+    // input form 2: the split partials of pass 1 ([part][head] rows of head_dim, m, l), merged here first
+    const float *part_o, *part_m, *part_l;
+    uint32_t n_parts;
     uint32_t rank, world, n_q_heads, head_dim, epoch;
 };
 
@@ -50,72 +60,197 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
     return v;
 }
 
-// grid = n_q_heads, block = 128
+// Steps 1-4 of the header comment for one (head, col block): threads 0..15 hold this rank's 64
+// columns (`acc`, unnormalised) and everyone its (m, d). All threads of the CTA call this.
 template <typename T>
-__global__ void __launch_bounds__(128) attn_exchange_combine_kernel(ExchangeParams p, T *__restrict__ out,
-                                                                   uint32_t *__restrict__ status) {
-    __shared__ int all_arrived;
-    const uint32_t h = blockIdx.x, tid = threadIdx.x;
+__device__ __forceinline__ void exchange_and_merge(const ExchangeParams &p, uint32_t h, uint32_t cb, float4 acc, float m,
+                                                   float d, T *__restrict__ out, uint32_t *__restrict__ status,
+                                                   int *all_arrived) {
+    const uint32_t tid = threadIdx.x;
     const ExchangeLayout l = exchange_layout(p.world, p.n_q_heads, p.head_dim);
     const size_t parity_off = (size_t)(p.epoch & 1u) * l.parity_bytes;
-    const size_t my_row = ((size_t)p.rank * p.n_q_heads + h) * l.row_floats;
+    const size_t my_cell = ((size_t)p.rank * p.n_q_heads + h) * l.col_blocks + cb;
+    const uint32_t col = cb * kColBlock + tid * 4;
 
-    // 1. this rank's triple of head h into slot `rank` of every buffer
-    for (uint32_t r = 0; r < p.world; ++r) {
-        float *dst = reinterpret_cast<float *>(p.peer[r] + parity_off) + my_row;
-        for (uint32_t c = tid * 4; c < p.head_dim; c += blockDim.x * 4)
-            *reinterpret_cast<float4 *>(dst + c) = *reinterpret_cast<const float4 *>(p.o + (size_t)h * p.head_dim + c);
-        if (tid == 0) *reinterpret_cast<float4 *>(dst + p.head_dim) = make_float4(p.m[h], p.d[h], 0.f, 0.f);
+    // 1. this rank's cell into slot `rank` of every buffer
+    if (tid < 17) {
+        for (uint32_t r = 0; r < p.world; ++r) {
+            float *dst = reinterpret_cast<float *>(p.peer[r] + parity_off) + my_cell * kCellFloats;
+            if (tid < 16) *reinterpret_cast<float4 *>(dst + tid * 4) = acc;
+            else *reinterpret_cast<float4 *>(dst + kColBlock) = make_float4(m, d, 0.f, 0.f);
+        }
     }
     // 2. publish
+    if (tid == 0) *all_arrived = 1;
     __syncthreads();
     if (tid < p.world) {
         __threadfence_system();
         uint32_t *flags = reinterpret_cast<uint32_t *>(p.peer[tid] + parity_off + l.flags_offset);
-        st_release_sys(flags + (size_t)p.rank * p.n_q_heads + h, p.epoch);
+        st_release_sys(flags + my_cell, p.epoch);
     }
-    // 3. wait for every rank's triple of this epoch in the local buffer
-    if (tid == 0) all_arrived = 1;
-    __syncthreads();
+    // 3. wait for every rank's cell of this epoch in the local buffer
     unsigned char *mine = p.peer[p.rank] + parity_off;
     if (tid < p.world) {
-        const uint32_t *flag = reinterpret_cast<const uint32_t *>(mine + l.flags_offset) + (size_t)tid * p.n_q_heads + h;
+        const uint32_t *flag = reinterpret_cast<const uint32_t *>(mine + l.flags_offset) +
+                               ((size_t)tid * p.n_q_heads + h) * l.col_blocks + cb;
         bool ok = false;
         for (uint32_t it = 0; it < kPollLimit; ++it) {
             if (ld_acquire_sys(flag) == p.epoch) { ok = true; break; }
             __nanosleep(64);
         }
-        if (!ok) all_arrived = 0;
+        if (!ok) *all_arrived = 0;
     }
     __syncthreads();
-    if (!all_arrived) {
+    if (!*all_arrived) {
         if (tid == 0) atomicOr(status, TT_DEV_WAIT_TIMEOUT);
-        return;     // the output row is left untouched
+        return;     // the output columns are left untouched
     }
     // 4. merge (attention.metal:395-437)
-    const float *rows = reinterpret_cast<const float *>(mine);
+    if (tid >= 16 || col >= p.head_dim) return;
+    const float *cells = reinterpret_cast<const float *>(mine);
     float mg = -INFINITY;
     for (uint32_t r = 0; r < p.world; ++r)
-        mg = fmaxf(mg, rows[((size_t)r * p.n_q_heads + h) * l.row_floats + p.head_dim]);
+        mg = fmaxf(mg, cells[(((size_t)r * p.n_q_heads + h) * l.col_blocks + cb) * kCellFloats + kColBlock]);
     float dsum = 0.f;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
     if (mg != -INFINITY)
         for (uint32_t r = 0; r < p.world; ++r) {
-            const float *row = rows + ((size_t)r * p.n_q_heads + h) * l.row_floats;
-            dsum += row[p.head_dim + 1] * __expf(row[p.head_dim] - mg);
+            const float *cell = cells + (((size_t)r * p.n_q_heads + h) * l.col_blocks + cb) * kCellFloats;
+            const float wgt = __expf(cell[kColBlock] - mg);
+            const float4 o = *reinterpret_cast<const float4 *>(cell + tid * 4);
+            dsum += cell[kColBlock + 1] * wgt;
+            sum.x += o.x * wgt; sum.y += o.y * wgt; sum.z += o.z * wgt; sum.w += o.w * wgt;
         }
     const float inv = dsum > 0.f ? 1.f / dsum : 0.f;
-    for (uint32_t c = tid; c < p.head_dim; c += blockDim.x) {
-        float acc = 0.f;
-        if (mg != -INFINITY)
-            for (uint32_t r = 0; r < p.world; ++r) {
-                const float *row = rows + ((size_t)r * p.n_q_heads + h) * l.row_floats;
-                acc += row[c] * __expf(row[p.head_dim] - mg);
+    uint2 packed;
+    packed.x = pack2<T>(sum.x * inv, sum.y * inv);
+    packed.y = pack2<T>(sum.z * inv, sum.w * inv);
+    *reinterpret_cast<uint2 *>(out + (size_t)h * p.head_dim + col) = packed;
+}
+
+// Input form 1. grid = (n_q_heads, col blocks), block = 32
+template <typename T>
+__global__ void __launch_bounds__(32) attn_exchange_combine_kernel(ExchangeParams p, T *__restrict__ out,
+                                                                  uint32_t *__restrict__ status) {
+    __shared__ int all_arrived;
+    const uint32_t h = blockIdx.x, cb = blockIdx.y, tid = threadIdx.x;
+    const uint32_t col = cb * kColBlock + tid * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (tid < 16 && col < p.head_dim) acc = *reinterpret_cast<const float4 *>(p.o + (size_t)h * p.head_dim + col);
+    exchange_and_merge<T>(p, h, cb, acc, p.m[h], p.d[h], out, status, &all_arrived);
+}
+
+// Input form 2: the local log-sum-exp merge of this rank's split partials (one session, one query
+// row) and the cross-GPU exchange and merge in the same kernel. grid = (n_q_heads, col blocks),
+// block = 256 = 16 part groups x 16 column threads.
+template <typename T>
+__global__ void __launch_bounds__(256) attn_merge_exchange_kernel(ExchangeParams p, T *__restrict__ out,
+                                                                 uint32_t *__restrict__ status) {
+    __shared__ int all_arrived;
+    __shared__ float red[16];
+    __shared__ float4 accs[256];
+    const uint32_t h = blockIdx.x, cb = blockIdx.y, tid = threadIdx.x;
+    const uint32_t lane = tid & 31, warp = tid >> 5, grp = tid >> 4, ct = tid & 15;
+    const uint32_t H = p.n_q_heads;
+
+    float mg = -INFINITY;
+    for (uint32_t c = tid; c < p.n_parts; c += 256) mg = fmaxf(mg, p.part_m[(size_t)c * H + h]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
+    if (lane == 0) red[warp] = mg;
+    __syncthreads();
+    mg = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) mg = fmaxf(mg, red[i]);
+    float D = 0.f;
+    if (mg != -INFINITY)
+        for (uint32_t c = tid; c < p.n_parts; c += 256) D += p.part_l[(size_t)c * H + h] * __expf(p.part_m[(size_t)c * H + h] - mg);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) D += __shfl_xor_sync(0xffffffffu, D, o);
+    if (lane == 0) red[8 + warp] = D;
+    __syncthreads();
+    D = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) D += red[8 + i];
+
+    const uint32_t col = cb * kColBlock + ct * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (mg != -INFINITY && col < p.head_dim) {
+        uint32_t c = grp;
+        for (; c + 48 < p.n_parts; c += 64) {   // four independent loads in flight per thread
+            float e[4]; float4 o[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const size_t pr = (size_t)(c + 16 * u) * H + h;
+                e[u] = p.part_m[pr];
+                o[u] = *reinterpret_cast<const float4 *>(p.part_o + pr * p.head_dim + col);
             }
-        out[(size_t)h * p.head_dim + c] = static_cast<T>(acc * inv);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float wgt = __expf(e[u] - mg);
+                acc.x += o[u].x * wgt; acc.y += o[u].y * wgt; acc.z += o[u].z * wgt; acc.w += o[u].w * wgt;
+            }
+        }
+        for (; c < p.n_parts; c += 16) {
+            const size_t pr = (size_t)c * H + h;
+            const float wgt = __expf(p.part_m[pr] - mg);
+            const float4 o = *reinterpret_cast<const float4 *>(p.part_o + pr * p.head_dim + col);
+            acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
+        }
     }
+    accs[tid] = acc;
+    __syncthreads();
+    if (tid < 16)
+        for (uint32_t g = 1; g < 16; ++g) {
+            const float4 o = accs[g * 16 + tid];
+            acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
+        }
+    exchange_and_merge<T>(p, h, cb, acc, mg, D, out, status, &all_arrived);
+}
+
+int fill_params(tt_context *ctx, ExchangeParams &p, void *const *peer_buffers, uint32_t rank, uint32_t world,
+                uint32_t n_q_heads, uint32_t head_dim, uint32_t epoch, const void *out, uint32_t io_dtype) {
+    if (!peer_buffers || !out) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "exchange: null argument");
+    if (world == 0 || world > kMaxWorld || rank >= world)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "exchange: world must be 1..%u and rank below it", kMaxWorld);
+    if (n_q_heads == 0 || head_dim == 0 || head_dim % 4 != 0)
+        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "exchange: head_dim must be a positive multiple of 4");
+    if (epoch == 0) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "exchange: epochs start at 1");
+    if (io_dtype != TT_F16 && io_dtype != TT_BF16) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "io_dtype must be TT_F16 or TT_BF16");
+    if ((uintptr_t)out & 15) return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "exchange: buffers must be 16-byte aligned");
+    for (uint32_t r = 0; r < kMaxWorld; ++r) p.peer[r] = nullptr;
+    for (uint32_t r = 0; r < world; ++r) {
+        if (peer_buffers[r] == nullptr || ((uintptr_t)peer_buffers[r] & 255))
+            return tt_set_error(ctx, TT_ERR_INVALID_ARG, "exchange: peer buffer %u is null or not 256-byte aligned", r);
+        p.peer[r] = reinterpret_cast<unsigned char *>(peer_buffers[r]);
+    }
+    p.m = p.d = p.o = p.part_o = p.part_m = p.part_l = nullptr;
+    p.n_parts = 0;
+    p.rank = rank; p.world = world; p.n_q_heads = n_q_heads; p.head_dim = head_dim; p.epoch = epoch;
+    return TT_OK;
 }
 
 }  // namespace
+
+// Local merge of one session's split partials fused with the cross-GPU exchange and merge (the
+// second launch of tt_attn_decode_exchange).
+int tt_launch_merge_exchange(tt_context *ctx, cudaStream_t stream, const float *part_o, const float *part_m,
+                             const float *part_l, uint32_t n_parts, const tt_attn_exchange *x, uint32_t n_q_heads,
+                             uint32_t head_dim, uint32_t io_dtype) {
+    ExchangeParams p;
+    int rc = fill_params(ctx, p, x->peer_buffers, x->rank, x->world, n_q_heads, head_dim, x->epoch, x->out, io_dtype);
+    if (rc != TT_OK) return rc;
+    p.part_o = part_o; p.part_m = part_m; p.part_l = part_l; p.n_parts = n_parts;
+    const dim3 grid(n_q_heads, exchange_layout(x->world, n_q_heads, head_dim).col_blocks);
+    if (io_dtype == TT_F16)
+        attn_merge_exchange_kernel<__half><<<grid, 256, 0, stream>>>(p, reinterpret_cast<__half *>(x->out), ctx->status);
+    else
+        attn_merge_exchange_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p, reinterpret_cast<__nv_bfloat16 *>(x->out), ctx->status);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_merge_exchange launch");
+    ctx->launches++;
+    return TT_OK;
+}
 
 TT_API size_t tt_attn_exchange_bytes(uint32_t world, uint32_t n_q_heads, uint32_t head_dim) {
     return 2 * exchange_layout(world, n_q_heads, head_dim).parity_bytes;
@@ -161,27 +296,17 @@ TT_API int tt_attn_exchange_combine(tt_context *ctx, tt_stream stream, const flo
                                     uint32_t n_q_heads, uint32_t head_dim, uint32_t epoch, void *out,
                                     uint32_t io_dtype) {
     TT_ENTER(ctx);
-    if (!m || !d || !o || !peer_buffers || !out) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "exchange: null argument");
-    if (world == 0 || world > kMaxWorld || rank >= world)
-        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "exchange: world must be 1..%u and rank below it", kMaxWorld);
-    if (n_q_heads == 0 || head_dim == 0 || head_dim % 4 != 0)
-        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "exchange: head_dim must be a positive multiple of 4");
-    if (epoch == 0) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "exchange: epochs start at 1");
-    if (io_dtype != TT_F16 && io_dtype != TT_BF16) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "io_dtype must be TT_F16 or TT_BF16");
-    if (((uintptr_t)o | (uintptr_t)out) & 15) return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "exchange: buffers must be 16-byte aligned");
+    if (!m || !d || !o) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "exchange: null argument");
+    if ((uintptr_t)o & 15) return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "exchange: buffers must be 16-byte aligned");
     ExchangeParams p;
-    for (uint32_t r = 0; r < kMaxWorld; ++r) p.peer[r] = nullptr;
-    for (uint32_t r = 0; r < world; ++r) {
-        if (peer_buffers[r] == nullptr || ((uintptr_t)peer_buffers[r] & 255))
-            return tt_set_error(ctx, TT_ERR_INVALID_ARG, "exchange: peer buffer %u is null or not 256-byte aligned", r);
-        p.peer[r] = reinterpret_cast<unsigned char *>(peer_buffers[r]);
-    }
+    int rc = fill_params(ctx, p, peer_buffers, rank, world, n_q_heads, head_dim, epoch, out, io_dtype);
+    if (rc != TT_OK) return rc;
     p.m = m; p.d = d; p.o = o;
-    p.rank = rank; p.world = world; p.n_q_heads = n_q_heads; p.head_dim = head_dim; p.epoch = epoch;
+    const dim3 grid(n_q_heads, exchange_layout(world, n_q_heads, head_dim).col_blocks);
     if (io_dtype == TT_F16)
-        attn_exchange_combine_kernel<__half><<<n_q_heads, 128, 0, (cudaStream_t)stream>>>(p, reinterpret_cast<__half *>(out), ctx->status);
+        attn_exchange_combine_kernel<__half><<<grid, 32, 0, (cudaStream_t)stream>>>(p, reinterpret_cast<__half *>(out), ctx->status);
     else
-        attn_exchange_combine_kernel<__nv_bfloat16><<<n_q_heads, 128, 0, (cudaStream_t)stream>>>(p, reinterpret_cast<__nv_bfloat16 *>(out), ctx->status);
+        attn_exchange_combine_kernel<__nv_bfloat16><<<grid, 32, 0, (cudaStream_t)stream>>>(p, reinterpret_cast<__nv_bfloat16 *>(out), ctx->status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_exchange_combine launch");
     ctx->launches++;

@@ -103,7 +103,7 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // the 16-byte column chunks l, l+8, l+16, ... of both rows (Dk/8 floats per row), so a row's dot
 // product is 3 shuffles away and shared-memory / global accesses of a group are 128 contiguous bytes.
 //
-// grid = min(ceil(items / 4), 3 * SMs), block = 128.
+// grid = min(ceil(items / 4), kCtasPerSm * SMs), block = 128.
 template <int DK>
 __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm)
 gdn_step_kernel(GdnParams p, uint32_t n_sessions, uint32_t n_items, uint32_t *__restrict__ status) {

@@ -140,4 +140,8 @@ struct TTKvQuant {
 // Launchers implemented in the .cu files.
 int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession *h_sessions,
                      uint32_t n_sessions, const tt_attn_batch_params *p, int mode,
-                     float *m_out, float *d_out, float *o_out, const TTKvQuant *quant = nullptr);
+                     float *m_out, float *d_out, float *o_out, const TTKvQuant *quant = nullptr,
+                     const tt_attn_exchange *exchange = nullptr);
+int tt_launch_merge_exchange(tt_context *ctx, cudaStream_t stream, const float *part_o, const float *part_m,
+                             const float *part_l, uint32_t n_parts, const tt_attn_exchange *x, uint32_t n_q_heads,
+                             uint32_t head_dim, uint32_t io_dtype);

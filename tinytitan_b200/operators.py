@@ -273,6 +273,17 @@ class Attention:
             io_dtype if io_dtype is not None else _dtype_of(out)))
 
 
+    def encode_decode_exchange(self, q, k, v, head_dim, num_q_heads, num_kv_heads, seq_len, kv_start, exchange, out,
+                               scale=None, kv_token_stride_elements=0, io_dtype=None, command_buffer=None):
+        """One step of a session split over GPUs in two launches: pass 1 over this GPU's rows, then the
+        local merge fused with the peer exchange and the cross-GPU merge."""
+        x = L.AttnExchange(exchange.pointer_array, exchange.rank, exchange.world, exchange.next_epoch(), 0, _addr(out))
+        self.context.check(L.lib().tt_attn_decode_exchange(
+            self.context.handle, _stream(command_buffer), _addr(q), _addr(k), _addr(v), head_dim, num_q_heads,
+            num_kv_heads, seq_len, kv_start, scale if scale is not None else head_dim ** -0.5,
+            kv_token_stride_elements, io_dtype if io_dtype is not None else _dtype_of(q), C.byref(x)))
+
+
 class PeerExchange:
     """One exchange buffer per rank, mapped into every rank of the group (one process per GPU, one node).
 

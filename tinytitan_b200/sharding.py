@@ -106,11 +106,12 @@ class LongContextDecode:
     def step(self, q, k_local, v_local, local_rows: int, out):
         import torch
         import torch.distributed as dist
+        if self.exchange is not None:
+            self.attention.encode_decode_exchange(q, k_local, v_local, self.hd, self.hq, self.hkv, local_rows, 0,
+                                                  self.exchange, out, scale=self.scale)
+            return out
         self.attention.encode_partial(q, k_local, v_local, self.hd, self.hq, self.hkv, local_rows, 0, self.m,
                                       self.d, self.o, scale=self.scale)
-        if self.exchange is not None:
-            self.attention.encode_exchange_combine(self.m, self.d, self.o, self.exchange, self.hq, self.hd, out)
-            return out
         torch.cat([self.o, self.m.unsqueeze(1), self.d.unsqueeze(1)], dim=1, out=self.packed)
         if self.world > 1:
             dist.all_gather_into_tensor(self.gathered, self.packed, group=self.group)
