@@ -1,12 +1,22 @@
 // Causal prefill attention on the sm_100a tensor cores (tcgen05 + TMEM + TMA), head_dim 256.
 //
-// One CTA owns 128 consecutive query rows of one q head. Warp 0 is the TMA producer (Q once,
-// then 64-key K and V tiles through two-stage rings), warp 1 issues the tcgen05 MMAs and owns
-// the TMEM allocation, warps 2-5 (one thread per query row) run the online softmax:
+// One CTA owns 128 consecutive query rows of one q head and walks the keys in tiles of 128.
+// Warp 0 is the TMA producer, warp 1 issues the Q.K^T MMAs and owns the TMEM allocation, warp 6
+// issues the P.V MMAs, warps 2-5 (one thread per query row) run the online softmax:
 //
-//   S[j%2]  = Q . K_j^T        SS MMA  M128 N64  K16 x16   (TMEM columns 256.. / 320..)
+//   S[j%2]  = Q . K_j^T        SS MMA  M128 N128 K16 x16   (TMEM columns 256..383 / 384..511)
 //   P_j     = exp2(S - m)      tcgen05.ld -> registers -> tcgen05.st, aliased over S[j%2]
-//   O      += P_j . V_j        TS MMA  M128 N256 K16 x4    (TMEM columns 0..255)
+//   O      += P_j . V_j        TS MMA  M128 N256 K16 x8    (TMEM columns 0..255)
+//
+// Tile width: an M128 K16 tcgen05.mma takes the same time for every N up to 128 (measured: the tile
+// time does not change between N = 16 and N = 128, but falls steeply with the NUMBER of
+// instructions), so at 64 keys per tile Q.K^T ran at half rate; 128 keys per instruction is as wide
+// as TMEM allows: O takes 256 columns, two score buffers of 128 columns fill the rest.
+//
+// Shared memory: Q 64 KB; K streams as [128 keys][128 head-dim] chunks (32 KB, two [128][64]
+// sub-tiles) through a 3-slot ring, each released as soon as its eight MMAs have retired; one V tile
+// (64 KB) is fetched and released in two 64-key halves, so the first half of V_{j+1} arrives while
+// the second half of V_j is still being consumed.
 //
 // The running maximum is only raised when it moved by more than 2^8 ("lazy rescale"); O and the
 // row sum then share one stale reference maximum, which cancels in O / l. Every mbarrier wait
@@ -23,28 +33,37 @@ namespace {
 
 constexpr int kHD = 256;
 constexpr int kBM = 128;              // query rows per CTA
-constexpr int kBN = 64;               // keys per tile
-constexpr int kThreads = 192;
+constexpr int kBN = 128;              // keys per tile
+constexpr int kBox = 64;              // keys per TMA box
+constexpr int kThreads = 352;             // 11 warps: producers, Q.K^T issuer, softmax A (2-5), P.V issuer, softmax B (7-10)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
 
 constexpr int kQBytes = kBM * kHD * 2;         // 65536: 4 sub-tiles [128][64] swizzle-128B
 constexpr int kQSub = kBM * 64 * 2;            // 16384
-constexpr int kKVStage = kBN * kHD * 2;        // 32768: 4 sub-tiles [64][64]
-constexpr int kKVSub = kBN * 64 * 2;           // 8192
-constexpr int kSmemBytes = kQBytes + 4 * kKVStage + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kKVTile = kBN * kHD * 2;         // 65536: 4 sub-tiles [128 keys][64]
+constexpr int kKVSub = kBN * 64 * 2;           // 16384
+constexpr int kBoxBytes = kBox * 64 * 2;       // 8192: one TMA box, half a sub-tile
+constexpr int kKSlots = 3;
+constexpr int kKChunk = kKVTile / 2;           // 32768: [128 keys][128 head-dim] = 2 sub-tiles
+constexpr int kSmemBytes = kQBytes + kKSlots * kKChunk + kKVTile + 2304 /*barriers, exchange*/;
 
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColO = 0, kColS0 = 256, kColS1 = 320;
+constexpr uint32_t kColO = 0, kColS0 = 256, kColS1 = 384;
 
 struct Barriers {
     uint64_t q_full;
-    uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+    uint64_t k_full[kKSlots], k_empty[kKSlots];   // per K chunk slot
+    uint64_t v_full[2], v_empty[2];   // per 64-key half of the V tile
     uint64_t s_full[2], p_ready[2];
+    uint64_t s_free[2];               // P.V of tile j retired: S/P buffer j%2 may take Q.K^T of tile j+2
     uint64_t o_ready;
+    uint64_t pair[4];                 // the two softmax warps of a TMEM lane quarter (count 2, bounded waits)
     uint32_t tmem_base;
     uint32_t pad;
+    float xchg[2][2][kBM];            // [buffer][key half][row]: per-tile row maxima, at the end the row sums
 };
+static_assert(sizeof(Barriers) <= 2304, "the barrier block must fit its share of shared memory");
 
 struct PrefillTcParams {
     uint32_t start_position, query_count, n_q_heads, n_kv_heads, kv_valid_count, sliding_window;
@@ -59,12 +78,19 @@ __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                        const __grid_constant__ CUtensorMap v_map, T *__restrict__ out, PrefillTcParams p,
                        uint32_t *__restrict__ status) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // every byte of the 227 KB is spoken for, so there is no slack to align the tiles by hand: the
+    // dynamic window of a kernel without static shared memory starts 1024-byte aligned, and a launch
+    // where it does not is refused rather than run with broken swizzles
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = smem_raw;
+    if (smem_u32(smem) & 1023u) {
+        if (threadIdx.x == 0) atomicOr(status, TT_DEV_BAD_ITEM);
+        return;
+    }
     unsigned char *q_s = smem;
-    unsigned char *k_s = smem + kQBytes;                  // 2 stages
-    unsigned char *v_s = smem + kQBytes + 2 * kKVStage;   // 2 stages
-    Barriers *bars = reinterpret_cast<Barriers *>(smem + kQBytes + 4 * kKVStage);
+    unsigned char *k_s = smem + kQBytes;
+    unsigned char *v_s = smem + kQBytes + kKSlots * kKChunk;
+    Barriers *bars = reinterpret_cast<Barriers *>(smem + kQBytes + kKSlots * kKChunk + kKVTile);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -84,15 +110,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 
     if (threadIdx.x == 0) {
         mbar_init(&bars->q_full, 1);
+        for (int s = 0; s < kKSlots; ++s) { mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1); }
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&bars->k_full[s], 1);
-            mbar_init(&bars->k_empty[s], 1);
             mbar_init(&bars->v_full[s], 1);
             mbar_init(&bars->v_empty[s], 1);
             mbar_init(&bars->s_full[s], 1);
-            mbar_init(&bars->p_ready[s], 128);
+            mbar_init(&bars->p_ready[s], 256);
+            mbar_init(&bars->s_free[s], 1);
         }
         mbar_init(&bars->o_ready, 1);
+        for (int s = 0; s < 4; ++s) mbar_init(&bars->pair[s], 2);
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -105,81 +132,102 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     bool failed = false;
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------------ TMA producers
+        // lane 0: Q, then the K tiles; lane 1: the V tiles in halves (independent progress).
+        // A box is [64 keys][64 elements]; sub-tile `sub` of a tile holds keys 0..127 of 64 head-dim columns.
         if (lane == 0) {
             mbar_expect_tx(&bars->q_full, kQBytes);
             for (int sub = 0; sub < 4; ++sub)
                 tma_load_2d(q_s + sub * kQSub, &q_map, (int)(head * kHD + sub * 64), (int)row0, &bars->q_full);
-            auto load_k = [&](uint32_t j) {
-                const int st = j & 1;
-                if (j >= 2 && !mbar_wait(&bars->k_empty[st], ((j >> 1) - 1) & 1)) return false;
-                mbar_expect_tx(&bars->k_full[st], kKVStage);
-                for (int sub = 0; sub < 4; ++sub)
-                    tma_load_2d(k_s + st * kKVStage + sub * kKVSub, &k_map, (int)(kv_head * kHD + sub * 64),
-                                (int)((tile_lo + j) * kBN), &bars->k_full[st]);
-                return true;
-            };
-            auto load_v = [&](uint32_t j) {
-                const int st = j & 1;
-                if (j >= 2 && !mbar_wait(&bars->v_empty[st], ((j >> 1) - 1) & 1)) return false;
-                mbar_expect_tx(&bars->v_full[st], kKVStage);
-                for (int sub = 0; sub < 4; ++sub)
-                    tma_load_2d(v_s + st * kKVStage + sub * kKVSub, &v_map, (int)(kv_head * kHD + sub * 64),
-                                (int)((tile_lo + j) * kBN), &bars->v_full[st]);
-                return true;
-            };
-            bool ok = load_k(0);
-            if (ok && n_tiles > 1) ok = load_k(1);
-            for (uint32_t j = 0; ok && j < n_tiles; ++j) {
-                ok = load_v(j);
-                if (ok && j + 2 < n_tiles) ok = load_k(j + 2);
+            bool ok = true;
+            for (uint32_t kc = 0; ok && kc < 2 * n_tiles; ++kc) {      // chunk kc = tile kc/2, head-dim half kc%2
+                const uint32_t slot = kc % kKSlots;
+                if (kc >= (uint32_t)kKSlots) ok = mbar_wait(&bars->k_empty[slot], ((kc / kKSlots) - 1) & 1);
+                if (!ok) break;
+                mbar_expect_tx(&bars->k_full[slot], kKChunk);
+                for (int sub = 0; sub < 2; ++sub)
+                    for (int half = 0; half < 2; ++half)
+                        tma_load_2d(k_s + slot * kKChunk + sub * kKVSub + half * kBoxBytes, &k_map,
+                                    (int)(kv_head * kHD + (kc & 1) * 128 + sub * 64),
+                                    (int)((tile_lo + (kc >> 1)) * kBN + half * kBox), &bars->k_full[slot]);
             }
+            failed = !ok;
+        } else if (lane == 1) {
+            bool ok = true;
+            for (uint32_t j = 0; ok && j < n_tiles; ++j)
+                for (int half = 0; ok && half < 2; ++half) {
+                    if (j >= 1) ok = mbar_wait(&bars->v_empty[half], (j - 1) & 1);
+                    if (!ok) break;
+                    mbar_expect_tx(&bars->v_full[half], kKVTile / 2);
+                    for (int sub = 0; sub < 4; ++sub)
+                        tma_load_2d(v_s + sub * kKVSub + half * kBoxBytes, &v_map, (int)(kv_head * kHD + sub * 64),
+                                    (int)((tile_lo + j) * kBN + half * kBox), &bars->v_full[half]);
+                }
             failed = !ok;
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------------ Q.K^T issuer
         if (lane == 0) {
-            const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
-            auto issue_qk = [&](uint32_t j) {
-                const int st = j & 1;
-                if (!mbar_wait(&bars->k_full[st], (j >> 1) & 1)) return false;
-                tc_fence_after();
-                const uint32_t d = tmem + (st ? kColS1 : kColS0);
-#pragma unroll
-                for (int ks = 0; ks < kHD / 16; ++ks) {
-                    const uint64_t ad = make_desc(q_addr + (ks >> 2) * kQSub + (ks & 3) * 32, 16, 1024);
-                    const uint64_t bd = make_desc(k_addr + st * kKVStage + (ks >> 2) * kKVSub + (ks & 3) * 32, 16, 1024);
-                    mma_ss(d, ad, bd, p.idesc_qk, ks > 0 ? 1u : 0u);
-                }
-                mma_commit(&bars->k_empty[st]);
-                mma_commit(&bars->s_full[st]);
-                return true;
-            };
+            const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s);
             bool ok = mbar_wait(&bars->q_full, 0);
-            if (ok) ok = issue_qk(0);
             for (uint32_t j = 0; ok && j < n_tiles; ++j) {
-                if (j + 1 < n_tiles) ok = issue_qk(j + 1);
                 const int st = j & 1;
-                if (ok) ok = mbar_wait(&bars->p_ready[st], (j >> 1) & 1);
-                if (ok) ok = mbar_wait(&bars->v_full[st], (j >> 1) & 1);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t a_tmem = tmem + (st ? kColS1 : kColS0);
+                if (j >= 2) ok = mbar_wait(&bars->s_free[st], ((j >> 1) - 1) & 1);
+                const uint32_t d = tmem + (st ? kColS1 : kColS0);
+                for (uint32_t half = 0; ok && half < 2; ++half) {
+                    const uint32_t kc = 2 * j + half, slot = kc % kKSlots;
+                    ok = mbar_wait(&bars->k_full[slot], (kc / kKSlots) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
 #pragma unroll
-                for (int kk = 0; kk < kBN / 16; ++kk) {
-                    // V tile as the MN-major B operand: 64-wide head-dim atoms 8192 B apart (LBO),
-                    // 8-key groups 1024 B apart (SBO)
-                    const uint64_t bd = make_desc(v_addr + st * kKVStage + kk * 2048, kKVSub, 1024);
-                    mma_ts(tmem + kColO, a_tmem + kk * 8, bd, p.idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint64_t ad = make_desc(q_addr + (half * 2 + (ks >> 2)) * kQSub + (ks & 3) * 32, 16, 1024);
+                        const uint64_t bd = make_desc(k_addr + slot * kKChunk + (ks >> 2) * kKVSub + (ks & 3) * 32, 16, 1024);
+                        mma_ss(d, ad, bd, p.idesc_qk, (half > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    mma_commit(&bars->k_empty[slot]);
                 }
-                mma_commit(&bars->v_empty[st]);
+                if (!ok) break;
+                mma_commit(&bars->s_full[st]);
+            }
+            failed = !ok;
+        }
+    } else if (warp == 6) {
+        // ------------------------------------------------------------------ P.V issuer
+        if (lane == 0) {
+            const uint32_t v_addr = smem_u32(v_s);
+            bool ok = true;
+            for (uint32_t j = 0; ok && j < n_tiles; ++j) {
+                const int st = j & 1;
+                ok = mbar_wait(&bars->p_ready[st], (j >> 1) & 1);
+                const uint32_t a_tmem = tmem + (st ? kColS1 : kColS0);
+                for (int half = 0; ok && half < 2; ++half) {
+                    ok = mbar_wait(&bars->v_full[half], j & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        // V tile as the MN-major B operand: 64-wide head-dim atoms kKVSub apart (LBO),
+                        // 8-key groups 1024 B apart (SBO), 16 keys (2048 B) per step
+                        const int kk = half * 4 + k4;
+                        const uint64_t bd = make_desc(v_addr + kk * 2048, kKVSub, 1024);
+                        mma_ts(tmem + kColO, a_tmem + kk * 8, bd, p.idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    mma_commit(&bars->v_empty[half]);
+                }
+                if (!ok) break;
+                mma_commit(&bars->s_free[st]);
                 mma_commit(&bars->o_ready);
             }
             failed = !ok;
         }
     } else {
-        // ------------------------------------------------------------------ softmax, one row per thread
+        // ------------------------------------------------------------------ softmax: two threads per row
+        // Warpgroup A (warps 2-5) takes keys 0..63 of every tile, warpgroup B (warps 7-10) keys 64..127;
+        // the two warps of a TMEM lane quarter exchange their row maxima through shared memory once per
+        // tile (bounded mbarrier, one arrive per warp) and then take identical decisions.
         const uint32_t quarter = warp & 3;                       // TMEM lane quarter this warp may touch
+        const uint32_t wg = warp >= 7 ? 1u : 0u;                 // key half of the tile
         const uint32_t row = quarter * 32 + lane;                // row inside the tile
         const uint32_t lane_addr = (quarter * 32) << 16;
         const bool row_valid = row < rows_here;
@@ -187,6 +235,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         uint32_t first = 0;
         if (p.sliding_window != 0 && abs_q + 1 > p.sliding_window) first = abs_q + 1 - p.sliding_window;
         const uint32_t last = min(p.kv_valid_count, abs_q + 1);  // exclusive
+        uint32_t pair_phase = 0;
+        auto pair_sync = [&]() {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->pair[quarter]);
+            const bool got = warp_all(mbar_wait(&bars->pair[quarter], pair_phase & 1));
+            pair_phase ^= 1;
+            return got;
+        };
 
         float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
@@ -197,13 +253,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             tc_fence_after();
             const uint32_t s_addr = tmem + lane_addr + (st ? kColS1 : kColS0);
             uint32_t raw[2][32];
-            tmem_ld32(s_addr, raw[0]);
-            tmem_ld32(s_addr + 32, raw[1]);
+            tmem_ld32(s_addr + wg * 64, raw[0]);
+            tmem_ld32(s_addr + wg * 64 + 32, raw[1]);
             tmem_wait_ld();
 
-            const uint32_t key0 = (tile_lo + j) * kBN;
-            const bool need_mask = (key0 + kBN > abs_lo + 1) || (key0 < first) || (key0 + kBN > p.kv_valid_count);
-            float mx = -INFINITY;
+            const uint32_t key0 = (tile_lo + j) * kBN + wg * 64;   // first key of this thread's half
+            const bool need_mask = (key0 + 64 > abs_lo + 1) || (key0 < first) || (key0 + 64 > p.kv_valid_count);
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -214,58 +270,71 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                         if (key < first || key >= last) s = -INFINITY;
                     }
                     raw[h][c] = __float_as_uint(s);
-                    mx = fmaxf(mx, s);
+                    mx4[c & 3] = fmaxf(mx4[c & 3], s);
                 }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            bars->xchg[st][wg][row] = mx;
+            ok = pair_sync();
+            if (!ok) break;
+            mx = fmaxf(mx, bars->xchg[st][wg ^ 1][row]);
             float m_new = fmaxf(m_ref, mx);
             // lazy rescale: keep the stale reference while it is within 2^8 of the true maximum
             const bool raise = (m_new - m_ref > kRescaleThreshold) || (m_ref == -INFINITY && m_new != -INFINITY);
             if (j == 0) {
                 m_ref = m_new;
             } else if (__any_sync(0xffffffffu, raise)) {
-                // O holds sum over tiles < j; it may only be touched once P.V of tile j-1 retired
+                // O holds sum over tiles < j; it may only be touched once P.V of tile j-1 retired.
+                // Both warps of the quarter see the same rows, hence the same votes: A rescales head-dim
+                // columns 0..127, B columns 128..255.
                 ok = warp_all(mbar_wait(&bars->o_ready, (j - 1) & 1));
                 if (!ok) break;
                 tc_fence_after();
                 const float factor = raise ? fast_exp2(m_ref - m_new) : 1.f;   // exp2(-inf) == 0: O was all zero
                 if (raise) { l_run *= factor; m_ref = m_new; }
 #pragma unroll 1
-                for (int c0 = 0; c0 < kHD; c0 += 32) {
+                for (int c0 = 0; c0 < kHD / 2; c0 += 32) {
                     uint32_t o[32];
-                    tmem_ld32(tmem + lane_addr + kColO + c0, o);
+                    tmem_ld32(tmem + lane_addr + kColO + wg * (kHD / 2) + c0, o);
                     tmem_wait_ld();
 #pragma unroll
                     for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
-                    tmem_st32(tmem + lane_addr + kColO + c0, o);
+                    tmem_st32(tmem + lane_addr + kColO + wg * (kHD / 2) + c0, o);
                 }
                 tmem_wait_st();
             }
             const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[32];
-            float rs = 0.f;
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
                 const float p0 = fast_exp2(__uint_as_float(raw[c >> 4][(2 * c) & 31]) - m_use);
                 const float p1 = fast_exp2(__uint_as_float(raw[c >> 4][(2 * c + 1) & 31]) - m_use);
-                pk[c] = pack2<T>(p0, p1);
-                rs += sum2<T>(pk[c]);   // the row sum uses the ROUNDED weights the MMA will see, so
-                                        // O / l stays an exact convex combination of V rows   // P takes V's type: A and B of one tcgen05.mma must share a format
+                pk[c] = pack2<T>(p0, p1);       // P takes V's type: A and B of one tcgen05.mma must share a format
+                rs4[c & 3] += sum2<T>(pk[c]);   // the row sum uses the ROUNDED weights the MMA will see, so
+                                                // O / l stays an exact convex combination of V rows
             }
-            l_run += rs;
-            tmem_st32(s_addr, pk);          // P (16-bit pairs) over the first 32 columns of S[j%2]
+            l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            tmem_st32(s_addr + wg * 32, pk);    // P (16-bit pairs): keys 64*wg.. -> columns 32*wg.. of S[j%2]
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&bars->p_ready[st]);
         }
         if (ok) ok = mbar_wait(&bars->o_ready, (n_tiles - 1) & 1);
         ok = warp_all(ok);
+        if (ok) ok = pair_sync();   // the partner is done reading the last tile's maxima
+        if (ok) {                   // total row sum = the two halves
+            bars->xchg[0][wg][row] = l_run;
+            ok = pair_sync();
+        }
         if (ok) {
             tc_fence_after();
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            T *orow = out + (size_t)(row0 + row) * p.o_token_stride + (size_t)head * kHD;
+            const float l_tot = l_run + bars->xchg[0][wg ^ 1][row];
+            const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+            T *orow = out + (size_t)(row0 + row) * p.o_token_stride + (size_t)head * kHD + wg * (kHD / 2);
 #pragma unroll 1
-            for (int c0 = 0; c0 < kHD; c0 += 32) {
+            for (int c0 = 0; c0 < kHD / 2; c0 += 32) {
                 uint32_t o[32];
-                tmem_ld32(tmem + lane_addr + kColO + c0, o);
+                tmem_ld32(tmem + lane_addr + kColO + wg * (kHD / 2) + c0, o);
                 tmem_wait_ld();
                 if (row_valid) {
 #pragma unroll
@@ -333,9 +402,9 @@ int tt_launch_prefill_tc(tt_context *ctx, cudaStream_t stream, const void *q, co
     const bool ok = tt_make_tensor_map_2d(&q_map, q, io_dtype, (uint64_t)p->n_q_heads * kHD, p->query_count,
                              p->q_token_stride_elements, kBM) &&
                     tt_make_tensor_map_2d(&k_map, k, io_dtype, (uint64_t)p->n_kv_heads * kHD, p->kv_valid_count,
-                             p->kv_token_stride_elements, kBN) &&
+                             p->kv_token_stride_elements, kBox) &&
                     tt_make_tensor_map_2d(&v_map, v, io_dtype, (uint64_t)p->n_kv_heads * kHD, p->kv_valid_count,
-                             p->kv_token_stride_elements, kBN);
+                             p->kv_token_stride_elements, kBox);
     if (!ok) return tt_set_error(ctx, TT_ERR_CUDA, "cuTensorMapEncodeTiled failed for the prefill operands");
     PrefillTcParams kp;
     kp.start_position = p->start_position; kp.query_count = p->query_count; kp.n_q_heads = p->n_q_heads;
