@@ -175,7 +175,8 @@ TT_API int tt_attn_prefill_path(const void *q, const void *k, const void *v, con
     const bool aligned = ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) == 0) &&
                          (p->q_token_stride_elements % 8 == 0) && (p->kv_token_stride_elements % 8 == 0) &&
                          (p->o_token_stride_elements % 8 == 0);
-    return (aligned && p->head_dim == 256 && kv_ring_capacity == 0 && p->kv_bits == 16) ? 1 : 0;
+    // the tensor-core kernel takes row maxima before scaling, which needs a positive scale
+    return (aligned && p->head_dim == 256 && kv_ring_capacity == 0 && p->kv_bits == 16 && p->scale > 0.f) ? 1 : 0;
 }
 
 TT_API int tt_attn_prefill_causal(tt_context *ctx, tt_stream stream, const void *q, const void *k, const void *v,

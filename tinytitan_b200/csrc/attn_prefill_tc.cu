@@ -259,20 +259,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 
             const uint32_t key0 = (tile_lo + j) * kBN + wg * 64;   // first key of this thread's half
             const bool need_mask = (key0 + 64 > abs_lo + 1) || (key0 < first) || (key0 + 64 > p.kv_valid_count);
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            // masked keys become -inf before the scale (which is positive, so they stay -inf and the row
+            // maximum can be taken on the unscaled scores, in four independent chains)
+            if (need_mask) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+                for (int h = 0; h < 2; ++h)
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    float s = __uint_as_float(raw[h][c]) * p.scale_log2;
-                    if (need_mask) {
+                    for (int c = 0; c < 32; ++c) {
                         const uint32_t key = key0 + h * 32 + c;
-                        if (key < first || key >= last) s = -INFINITY;
+                        if (key < first || key >= last) raw[h][c] = 0xff800000u;
                     }
-                    raw[h][c] = __float_as_uint(s);
-                    mx4[c & 3] = fmaxf(mx4[c & 3], s);
-                }
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            }
+            float mx4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(__uint_as_float(raw[0][u]), __uint_as_float(raw[1][u]));
+#pragma unroll
+            for (int c = 4; c < 32; ++c)
+                mx4[c & 3] = fmaxf(mx4[c & 3], fmaxf(__uint_as_float(raw[0][c]), __uint_as_float(raw[1][c])));
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
             bars->xchg[st][wg][row] = mx;
             ok = pair_sync();
             if (!ok) break;
@@ -302,13 +306,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 }
                 tmem_wait_st();
             }
-            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
             float rs4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[32];
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
-                const float p0 = fast_exp2(__uint_as_float(raw[c >> 4][(2 * c) & 31]) - m_use);
-                const float p1 = fast_exp2(__uint_as_float(raw[c >> 4][(2 * c + 1) & 31]) - m_use);
+                // one FMA per exponent argument: raw * scale - m
+                const float p0 = fast_exp2(fmaf(__uint_as_float(raw[c >> 4][(2 * c) & 31]), p.scale_log2, neg_m));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(raw[c >> 4][(2 * c + 1) & 31]), p.scale_log2, neg_m));
                 pk[c] = pack2<T>(p0, p1);       // P takes V's type: A and B of one tcgen05.mma must share a format
                 rs4[c & 3] += sum2<T>(pk[c]);   // the row sum uses the ROUNDED weights the MMA will see, so
                                                 // O / l stays an exact convex combination of V rows
