@@ -316,12 +316,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 const float p0 = fast_exp2(fmaf(__uint_as_float(raw[c >> 4][(2 * c) & 31]), p.scale_log2, neg_m));
                 const float p1 = fast_exp2(fmaf(__uint_as_float(raw[c >> 4][(2 * c + 1) & 31]), p.scale_log2, neg_m));
                 pk[c] = pack2<T>(p0, p1);       // P takes V's type: A and B of one tcgen05.mma must share a format
-                // bf16 weights (8 mantissa bits): the row sum uses the ROUNDED weights the MMA will see, so
-                // O / l stays an exact convex combination of V rows. fp16 weights round 16 times finer
-                // (relative 2^-12, unbiased), so their sum is taken before the rounding: two adds
-                // instead of two conversions and two adds.
-                if constexpr (std::is_same<T, __half>::value) rs4[c & 3] += p0 + p1;
-                else rs4[c & 3] += sum2<T>(pk[c]);
+                rs4[c & 3] += sum2<T>(pk[c]);   // the row sum uses the ROUNDED weights the MMA will see, so
+                                                // O / l stays an exact convex combination of V rows (summing
+                                                // before the rounding fails the 2e-3 bar on peaked rows, fp16 too)
             }
             l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             tmem_st32(s_addr + wg * 32, pk);    // P (16-bit pairs): keys 64*wg.. -> columns 32*wg.. of S[j%2]
