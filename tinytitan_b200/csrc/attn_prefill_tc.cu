@@ -45,9 +45,11 @@ constexpr int kQSub = kBM * 64 * 2;            // 16384
 constexpr int kKVTile = kBN * kHD * 2;         // 65536: 4 sub-tiles [128 keys][64]
 constexpr int kKVSub = kBN * 64 * 2;           // 16384
 constexpr int kBoxBytes = kBox * 64 * 2;       // 8192: one TMA box, half a sub-tile
-constexpr int kKSlots = 3;
+constexpr int kKSlots = 2;
 constexpr int kKChunk = kKVTile / 2;           // 32768: [128 keys][128 head-dim] = 2 sub-tiles
-constexpr int kSmemBytes = kQBytes + kKSlots * kKChunk + kKVTile + 2304 /*barriers, exchange*/;
+constexpr int kPBytes = kBM * kBN * 2;           // 32768: 2 sub-tiles [128 rows][64 keys], K-major A operand
+constexpr int kPSub = kBM * 64 * 2;              // 16384
+constexpr int kSmemBytes = kQBytes + kKSlots * kKChunk + kKVTile + kPBytes + 2304 /*barriers, exchange*/;
 
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS0 = 256, kColS1 = 384;
@@ -56,8 +58,11 @@ struct Barriers {
     uint64_t q_full;
     uint64_t k_full[kKSlots], k_empty[kKSlots];   // per K chunk slot
     uint64_t v_full[2], v_empty[2];   // per 64-key half of the V tile
-    uint64_t s_full[2], p_ready[2];
-    uint64_t s_free[2];               // P.V of tile j retired: S/P buffer j%2 may take Q.K^T of tile j+2
+    uint64_t s_full[2];
+    uint64_t s_read[2];               // both softmax warpgroups hold tile j's scores in registers: buffer j%2
+                                      // may take Q.K^T of tile j+2
+    uint64_t p_ready;                 // P of the tile is in shared memory
+    uint64_t p_free;                  // P.V of the tile retired: P may be overwritten
     uint64_t o_ready;
     uint64_t pair[4];                 // the two softmax warps of a TMEM lane quarter (count 2, bounded waits)
     uint32_t tmem_base;
@@ -91,7 +96,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     unsigned char *q_s = smem;
     unsigned char *k_s = smem + kQBytes;
     unsigned char *v_s = smem + kQBytes + kKSlots * kKChunk;
-    Barriers *bars = reinterpret_cast<Barriers *>(smem + kQBytes + kKSlots * kKChunk + kKVTile);
+    unsigned char *p_s = v_s + kKVTile;
+    Barriers *bars = reinterpret_cast<Barriers *>(p_s + kPBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -116,9 +122,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             mbar_init(&bars->v_full[s], 1);
             mbar_init(&bars->v_empty[s], 1);
             mbar_init(&bars->s_full[s], 1);
-            mbar_init(&bars->p_ready[s], 256);
-            mbar_init(&bars->s_free[s], 1);
+            mbar_init(&bars->s_read[s], 256);
         }
+        mbar_init(&bars->p_ready, 256);
+        mbar_init(&bars->p_free, 1);
         mbar_init(&bars->o_ready, 1);
         for (int s = 0; s < 4; ++s) mbar_init(&bars->pair[s], 2);
         mbar_fence_init();
@@ -173,7 +180,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             bool ok = mbar_wait(&bars->q_full, 0);
             for (uint32_t j = 0; ok && j < n_tiles; ++j) {
                 const int st = j & 1;
-                if (j >= 2) ok = mbar_wait(&bars->s_free[st], ((j >> 1) - 1) & 1);
+                if (j >= 2) ok = mbar_wait(&bars->s_read[st], ((j >> 1) - 1) & 1);
                 const uint32_t d = tmem + (st ? kColS1 : kColS0);
                 for (uint32_t half = 0; ok && half < 2; ++half) {
                     const uint32_t kc = 2 * j + half, slot = kc % kKSlots;
@@ -196,28 +203,28 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     } else if (warp == 6) {
         // ------------------------------------------------------------------ P.V issuer
         if (lane == 0) {
-            const uint32_t v_addr = smem_u32(v_s);
+            const uint32_t v_addr = smem_u32(v_s), p_addr = smem_u32(p_s);
             bool ok = true;
             for (uint32_t j = 0; ok && j < n_tiles; ++j) {
-                const int st = j & 1;
-                ok = mbar_wait(&bars->p_ready[st], (j >> 1) & 1);
-                const uint32_t a_tmem = tmem + (st ? kColS1 : kColS0);
+                ok = mbar_wait(&bars->p_ready, j & 1);
                 for (int half = 0; ok && half < 2; ++half) {
                     ok = mbar_wait(&bars->v_full[half], j & 1);
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll
                     for (int k4 = 0; k4 < 4; ++k4) {
-                        // V tile as the MN-major B operand: 64-wide head-dim atoms kKVSub apart (LBO),
-                        // 8-key groups 1024 B apart (SBO), 16 keys (2048 B) per step
+                        // P: K-major A operand from shared memory, sub-tile `half` = keys 64*half.., 16 keys
+                        // (32 B) per step. V: MN-major B operand, 64-wide head-dim atoms kKVSub apart (LBO),
+                        // 8-key groups 1024 B apart (SBO), 16 keys (2048 B) per step.
                         const int kk = half * 4 + k4;
+                        const uint64_t ad = make_desc(p_addr + half * kPSub + k4 * 32, 16, 1024);
                         const uint64_t bd = make_desc(v_addr + kk * 2048, kKVSub, 1024);
-                        mma_ts(tmem + kColO, a_tmem + kk * 8, bd, p.idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                        mma_ss(tmem + kColO, ad, bd, p.idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                     }
                     mma_commit(&bars->v_empty[half]);
                 }
                 if (!ok) break;
-                mma_commit(&bars->s_free[st]);
+                mma_commit(&bars->p_free);
                 mma_commit(&bars->o_ready);
             }
             failed = !ok;
@@ -257,6 +264,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             tmem_ld32(s_addr + wg * 64, raw[0]);
             tmem_ld32(s_addr + wg * 64 + 32, raw[1]);
             tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&bars->s_read[st]);    // this half of the score tile is in registers
 
             const uint32_t key0 = (tile_lo + j) * kBN + wg * 64;   // first key of this thread's half
             const bool need_mask = (key0 + 64 > abs_lo + 1) || (key0 < first) || (key0 + 64 > p.kv_valid_count);
@@ -321,10 +330,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                                                 // before the rounding fails the 2e-3 bar on peaked rows, fp16 too)
             }
             l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-            tmem_st32(s_addr + wg * 32, pk);    // P (16-bit pairs): keys 64*wg.. -> columns 32*wg.. of S[j%2]
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(&bars->p_ready[st]);
+            // P row of this query, keys 64*wg..: 128 bytes in sub-tile wg, 16-byte chunk c at (c ^ (row & 7));
+            // stored once P.V of the previous tile has retired
+            if (j >= 1) {
+                ok = warp_all(mbar_wait(&bars->p_free, (j - 1) & 1));
+                if (!ok) break;
+            }
+            unsigned char *prow = p_s + wg * kPSub + row * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4 *>(prow + ((c ^ (row & 7)) << 4)) =
+                    make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();                 // orders a rescale of O (above) before the P.V it precedes
+            mbar_arrive(&bars->p_ready);
         }
         if (ok) ok = mbar_wait(&bars->o_ready, (n_tiles - 1) & 1);
         ok = warp_all(ok);
