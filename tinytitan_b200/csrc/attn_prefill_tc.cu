@@ -1,27 +1,39 @@
 // Causal prefill attention on the sm_100a tensor cores (tcgen05 + TMEM + TMA), head_dim 256.
 //
 // One CTA owns 128 consecutive query rows of one q head and walks the keys in tiles of 128.
-// Warp 0 is the TMA producer, warp 1 issues the Q.K^T MMAs and owns the TMEM allocation, warp 6
-// issues the P.V MMAs, warps 2-5 (one thread per query row) run the online softmax:
+// Eleven warps: warp 0 holds the two TMA producers (lane 0: K, lane 1: V), warp 1 issues the
+// Q.K^T MMAs and owns the TMEM allocation, warp 6 issues the P.V MMAs, warps 2-5 and 7-10 are two
+// softmax warpgroups (two threads per query row: group A takes keys 0..63 of every tile, group B
+// keys 64..127):
 //
-//   S[j%2]  = Q . K_j^T        SS MMA  M128 N128 K16 x16   (TMEM columns 256..383 / 384..511)
-//   P_j     = exp2(S - m)      tcgen05.ld -> registers -> tcgen05.st, aliased over S[j%2]
-//   O      += P_j . V_j        TS MMA  M128 N256 K16 x8    (TMEM columns 0..255)
+//   S       = Q . K_j^T        TS MMA  M128 N128 K16 x16   A = Q in TMEM columns 384..511 (stored there
+//                                                          once by the softmax threads), D = columns 256..383
+//   P_j     = exp2(S - m)      tcgen05.ld -> registers -> shared memory (K-major A operand, 128-byte swizzle)
+//   O      += P_j . V_j        SS MMA  M128 N256 K16 x8    D = TMEM columns 0..255
 //
-// Tile width: an M128 K16 tcgen05.mma takes the same time for every N up to 128 (measured: the tile
-// time does not change between N = 16 and N = 128, but falls steeply with the NUMBER of
-// instructions), so at 64 keys per tile Q.K^T ran at half rate; 128 keys per instruction is as wide
-// as TMEM allows: O takes 256 columns, two score buffers of 128 columns fill the rest.
+// How it got here (config 3, bf16, 0.571 ms -> 0.441 ms):
+//  * An M128 K16 tcgen05.mma costs about the same for every N up to 128 (measured: the tile time is
+//    the same for N = 16 ... 128 and falls steeply with the NUMBER of instructions), so Q.K^T is
+//    issued 128 keys wide: 24 instructions per 128 keys instead of 40.
+//  * With tiles that wide one softmax warpgroup became the limit, hence two; the two warps of a TMEM
+//    lane quarter exchange their row maxima through shared memory once per tile (an mbarrier with a
+//    bounded wait, one arrive per warp) and then take identical decisions.
+//  * The score tile is released as soon as both groups hold it in registers (s_read), and P goes
+//    through shared memory instead of being aliased over S, so Q.K^T of tile j+1 overlaps the softmax
+//    of tile j with ONE score tile; the TMEM columns this frees hold Q, which takes the 4 KB of Q
+//    per instruction off the shared-memory port.
+//  * Two issuing threads, so that neither product waits behind the other's barrier.
 //
-// Shared memory: Q 64 KB; K streams as [128 keys][128 head-dim] chunks (32 KB, two [128][64]
-// sub-tiles) through a 3-slot ring, each released as soon as its eight MMAs have retired; one V tile
-// (64 KB) is fetched and released in two 64-key halves, so the first half of V_{j+1} arrives while
-// the second half of V_j is still being consumed.
+// Shared memory (all 227 KB): K streams as [128 keys][128 head-dim] chunks (32 KB, two [128][64]
+// sub-tiles) through a 4-slot ring, each released as soon as its eight MMAs have retired; one V tile
+// (64 KB) is fetched and released in two 64-key halves; P is 32 KB (two [128 rows][64 keys]
+// sub-tiles).
 //
 // The running maximum is only raised when it moved by more than 2^8 ("lazy rescale"); O and the
-// row sum then share one stale reference maximum, which cancels in O / l. Every mbarrier wait
-// is bounded: when a wait runs out the role sets TT_DEV_WAIT_TIMEOUT in the status word and
-// falls through to the common exit, where TMEM is released.
+// row sum then share one stale reference maximum, which cancels in O / l. The row sum is taken on
+// the ROUNDED weights the MMA consumes. Every mbarrier wait is bounded: when a wait runs out the
+// role sets TT_DEV_WAIT_TIMEOUT in the status word and falls through to the common exit, where
+// TMEM is released.
 //
 // Arithmetic semantics: sources/TinyTitanCore/Metal/Prefill/prefill.metal:1056-1158 (visible
 // keys [first, min(kvValid, start+t+1)), fp32 accumulation, row_sum == 0 -> 0).
@@ -40,27 +52,25 @@ constexpr int kThreads = 352;             // 11 warps: producers, Q.K^T issuer, 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
 
-constexpr int kQBytes = kBM * kHD * 2;         // 65536: 4 sub-tiles [128][64] swizzle-128B
-constexpr int kQSub = kBM * 64 * 2;            // 16384
 constexpr int kKVTile = kBN * kHD * 2;         // 65536: 4 sub-tiles [128 keys][64]
 constexpr int kKVSub = kBN * 64 * 2;           // 16384
 constexpr int kBoxBytes = kBox * 64 * 2;       // 8192: one TMA box, half a sub-tile
-constexpr int kKSlots = 2;
+constexpr int kKSlots = 4;
 constexpr int kKChunk = kKVTile / 2;           // 32768: [128 keys][128 head-dim] = 2 sub-tiles
 constexpr int kPBytes = kBM * kBN * 2;           // 32768: 2 sub-tiles [128 rows][64 keys], K-major A operand
 constexpr int kPSub = kBM * 64 * 2;              // 16384
-constexpr int kSmemBytes = kQBytes + kKSlots * kKChunk + kKVTile + kPBytes + 2304 /*barriers, exchange*/;
+constexpr int kSmemBytes = kKSlots * kKChunk + kKVTile + kPBytes + 2304 /*barriers, exchange*/;
 
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColO = 0, kColS0 = 256, kColS1 = 384;
+constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384;   // Q: 128 columns of 16-bit pairs
 
 struct Barriers {
-    uint64_t q_full;
+    uint64_t q_ready;                 // the 256 softmax threads have stored their halves of the Q rows into TMEM
     uint64_t k_full[kKSlots], k_empty[kKSlots];   // per K chunk slot
     uint64_t v_full[2], v_empty[2];   // per 64-key half of the V tile
-    uint64_t s_full[2];
-    uint64_t s_read[2];               // both softmax warpgroups hold tile j's scores in registers: buffer j%2
-                                      // may take Q.K^T of tile j+2
+    uint64_t s_full;
+    uint64_t s_read;                  // both softmax warpgroups hold the tile's scores in registers: the score
+                                      // tile may take Q.K^T of the next tile
     uint64_t p_ready;                 // P of the tile is in shared memory
     uint64_t p_free;                  // P.V of the tile retired: P may be overwritten
     uint64_t o_ready;
@@ -74,6 +84,7 @@ static_assert(sizeof(Barriers) <= 2304, "the barrier block must fit its share of
 struct PrefillTcParams {
     uint32_t start_position, query_count, n_q_heads, n_kv_heads, kv_valid_count, sliding_window;
     uint32_t o_token_stride;   // elements
+    uint32_t q_token_stride;   // elements
     uint32_t n_q_tiles;
     float scale_log2;
     uint32_t idesc_qk, idesc_pv;
@@ -81,7 +92,7 @@ struct PrefillTcParams {
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
-attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+attn_prefill_tc_kernel(const T *__restrict__ q, const __grid_constant__ CUtensorMap k_map,
                        const __grid_constant__ CUtensorMap v_map, T *__restrict__ out, PrefillTcParams p,
                        uint32_t *__restrict__ status) {
     // every byte of the 227 KB is spoken for, so there is no slack to align the tiles by hand: the
@@ -93,9 +104,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         if (threadIdx.x == 0) atomicOr(status, TT_DEV_BAD_ITEM);
         return;
     }
-    unsigned char *q_s = smem;
-    unsigned char *k_s = smem + kQBytes;
-    unsigned char *v_s = smem + kQBytes + kKSlots * kKChunk;
+    unsigned char *k_s = smem;
+    unsigned char *v_s = smem + kKSlots * kKChunk;
     unsigned char *p_s = v_s + kKVTile;
     Barriers *bars = reinterpret_cast<Barriers *>(p_s + kPBytes);
 
@@ -116,13 +126,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const uint32_t n_tiles = (key_hi + kBN - 1) / kBN - tile_lo;     // >= 1
 
     if (threadIdx.x == 0) {
-        mbar_init(&bars->q_full, 1);
+        mbar_init(&bars->q_ready, 256);
+        mbar_init(&bars->s_full, 1);
+        mbar_init(&bars->s_read, 256);
         for (int s = 0; s < kKSlots; ++s) { mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1); }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&bars->v_full[s], 1);
             mbar_init(&bars->v_empty[s], 1);
-            mbar_init(&bars->s_full[s], 1);
-            mbar_init(&bars->s_read[s], 256);
         }
         mbar_init(&bars->p_ready, 256);
         mbar_init(&bars->p_free, 1);
@@ -144,9 +154,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         // lane 0: Q, then the K tiles; lane 1: the V tiles in halves (independent progress).
         // A box is [64 keys][64 elements]; sub-tile `sub` of a tile holds keys 0..127 of 64 head-dim columns.
         if (lane == 0) {
-            mbar_expect_tx(&bars->q_full, kQBytes);
-            for (int sub = 0; sub < 4; ++sub)
-                tma_load_2d(q_s + sub * kQSub, &q_map, (int)(head * kHD + sub * 64), (int)row0, &bars->q_full);
             bool ok = true;
             for (uint32_t kc = 0; ok && kc < 2 * n_tiles; ++kc) {      // chunk kc = tile kc/2, head-dim half kc%2
                 const uint32_t slot = kc % kKSlots;
@@ -176,12 +183,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     } else if (warp == 1) {
         // ------------------------------------------------------------------ Q.K^T issuer
         if (lane == 0) {
-            const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s);
-            bool ok = mbar_wait(&bars->q_full, 0);
+            const uint32_t k_addr = smem_u32(k_s);
+            bool ok = mbar_wait(&bars->q_ready, 0);
             for (uint32_t j = 0; ok && j < n_tiles; ++j) {
-                const int st = j & 1;
-                if (j >= 2) ok = mbar_wait(&bars->s_read[st], ((j >> 1) - 1) & 1);
-                const uint32_t d = tmem + (st ? kColS1 : kColS0);
+                if (j >= 1) ok = mbar_wait(&bars->s_read, (j - 1) & 1);
                 for (uint32_t half = 0; ok && half < 2; ++half) {
                     const uint32_t kc = 2 * j + half, slot = kc % kKSlots;
                     ok = mbar_wait(&bars->k_full[slot], (kc / kKSlots) & 1);
@@ -189,14 +194,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < 8; ++ks) {
-                        const uint64_t ad = make_desc(q_addr + (half * 2 + (ks >> 2)) * kQSub + (ks & 3) * 32, 16, 1024);
+                        // A = Q from TMEM (8 columns per 16-wide step), B = the K chunk
                         const uint64_t bd = make_desc(k_addr + slot * kKChunk + (ks >> 2) * kKVSub + (ks & 3) * 32, 16, 1024);
-                        mma_ss(d, ad, bd, p.idesc_qk, (half > 0 || ks > 0) ? 1u : 0u);
+                        mma_ts(tmem + kColS, tmem + kColQ + (half * 8 + ks) * 8, bd, p.idesc_qk, (half > 0 || ks > 0) ? 1u : 0u);
                     }
                     mma_commit(&bars->k_empty[slot]);
                 }
                 if (!ok) break;
-                mma_commit(&bars->s_full[st]);
+                mma_commit(&bars->s_full);
             }
             failed = !ok;
         }
@@ -252,20 +257,39 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             return got;
         };
 
+        // this thread's half of its query row -> TMEM lane `row`, columns kColQ + 64*wg.. (two 16-bit
+        // elements per column)
+        {
+            const T *qrow = q + (size_t)(row0 + row) * p.q_token_stride + (size_t)head * kHD + wg * (kHD / 2);
+#pragma unroll 1
+            for (int c0 = 0; c0 < kHD / 4; c0 += 32) {
+                uint32_t w[32];
+#pragma unroll
+                for (int c = 0; c < 32; c += 4) {
+                    uint4 x = make_uint4(0u, 0u, 0u, 0u);
+                    if (row_valid) x = *reinterpret_cast<const uint4 *>(qrow + 2 * (c0 + c));
+                    w[c] = x.x; w[c + 1] = x.y; w[c + 2] = x.z; w[c + 3] = x.w;
+                }
+                tmem_st32(tmem + lane_addr + kColQ + wg * (kHD / 4) + c0, w);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bars->q_ready);
+        }
         float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (uint32_t j = 0; j < n_tiles; ++j) {
             const int st = j & 1;
-            ok = warp_all(mbar_wait(&bars->s_full[st], (j >> 1) & 1));
+            ok = warp_all(mbar_wait(&bars->s_full, j & 1));
             if (!ok) break;
             tc_fence_after();
-            const uint32_t s_addr = tmem + lane_addr + (st ? kColS1 : kColS0);
+            const uint32_t s_addr = tmem + lane_addr + kColS;
             uint32_t raw[2][32];
             tmem_ld32(s_addr + wg * 64, raw[0]);
             tmem_ld32(s_addr + wg * 64 + 32, raw[1]);
             tmem_wait_ld();
             tc_fence_before();
-            mbar_arrive(&bars->s_read[st]);    // this half of the score tile is in registers
+            mbar_arrive(&bars->s_read);        // this half of the score tile is in registers
 
             const uint32_t key0 = (tile_lo + j) * kBN + wg * 64;   // first key of this thread's half
             const bool need_mask = (key0 + 64 > abs_lo + 1) || (key0 < first) || (key0 + 64 > p.kv_valid_count);
@@ -424,10 +448,8 @@ bool tt_make_tensor_map_2d(CUtensorMap *map, const void *base, uint32_t io_dtype
 
 int tt_launch_prefill_tc(tt_context *ctx, cudaStream_t stream, const void *q, const void *k, const void *v,
                          void *out, const tt_prefill_params *p, uint32_t io_dtype) {
-    CUtensorMap q_map, k_map, v_map;
-    const bool ok = tt_make_tensor_map_2d(&q_map, q, io_dtype, (uint64_t)p->n_q_heads * kHD, p->query_count,
-                             p->q_token_stride_elements, kBM) &&
-                    tt_make_tensor_map_2d(&k_map, k, io_dtype, (uint64_t)p->n_kv_heads * kHD, p->kv_valid_count,
+    CUtensorMap k_map, v_map;
+    const bool ok = tt_make_tensor_map_2d(&k_map, k, io_dtype, (uint64_t)p->n_kv_heads * kHD, p->kv_valid_count,
                              p->kv_token_stride_elements, kBox) &&
                     tt_make_tensor_map_2d(&v_map, v, io_dtype, (uint64_t)p->n_kv_heads * kHD, p->kv_valid_count,
                              p->kv_token_stride_elements, kBox);
@@ -436,6 +458,7 @@ int tt_launch_prefill_tc(tt_context *ctx, cudaStream_t stream, const void *q, co
     kp.start_position = p->start_position; kp.query_count = p->query_count; kp.n_q_heads = p->n_q_heads;
     kp.n_kv_heads = p->n_kv_heads; kp.kv_valid_count = p->kv_valid_count; kp.sliding_window = p->sliding_window;
     kp.o_token_stride = p->o_token_stride_elements;
+    kp.q_token_stride = p->q_token_stride_elements;
     kp.n_q_tiles = (p->query_count + kBM - 1) / kBM;
     kp.scale_log2 = p->scale * kLog2e;
     kp.idesc_qk = tt_make_idesc_f16(io_dtype, kBN, false);
@@ -446,12 +469,12 @@ int tt_launch_prefill_tc(tt_context *ctx, cudaStream_t stream, const void *q, co
         auto kernel = attn_prefill_tc_kernel<__half>;
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "prefill smem attribute");
-        kernel<<<grid, kThreads, kSmemBytes, stream>>>(q_map, k_map, v_map, reinterpret_cast<__half *>(out), kp, ctx->status);
+        kernel<<<grid, kThreads, kSmemBytes, stream>>>(reinterpret_cast<const __half *>(q), k_map, v_map, reinterpret_cast<__half *>(out), kp, ctx->status);
     } else {
         auto kernel = attn_prefill_tc_kernel<__nv_bfloat16>;
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "prefill smem attribute");
-        kernel<<<grid, kThreads, kSmemBytes, stream>>>(q_map, k_map, v_map, reinterpret_cast<__nv_bfloat16 *>(out), kp, ctx->status);
+        kernel<<<grid, kThreads, kSmemBytes, stream>>>(reinterpret_cast<const __nv_bfloat16 *>(q), k_map, v_map, reinterpret_cast<__nv_bfloat16 *>(out), kp, ctx->status);
     }
     e = cudaGetLastError();
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_prefill_tc launch");
