@@ -264,3 +264,34 @@ def test_chunked_scan_rejects_other_shapes():
     gdn = tt.GDN(context(), tt.LinearAttentionConfig(2, 4, 128, 128))
     with pytest.raises(tt.UnsupportedShape):
         gdn.encode_delta_scan_chunked(x, x, x, x, x, torch.zeros(4 * 128 * 128, device="cuda"), x, 64, chunk=32)
+
+
+@pytest.mark.parametrize("n,hk,hv,dk,dv,rows", [(70, 3, 6, 64, 24, 3), (3, 2, 132, 32, 8, 2), (40, 16, 32, 128, 128, 1)])
+def test_persistent_step_other_paths(n, hk, hv, dk, dv, rows):
+    # More sessions than the kernel stages in shared memory (70 > 64), more value heads than it
+    # stages decay parameters for (132 > 128), head and row-block counts that are not powers of two
+    # (the division path of the item decode), and enough items that every warp walks several.
+    r = np.random.default_rng(n * 1000 + hv)
+    cfg = tt.LinearAttentionConfig(hk, hv, dk, dv)
+    ctx = tt.Context(0, max_sessions=128)
+    try:
+        gdn = tt.GDN(ctx, cfg)
+        ins = [make_inputs(r, rows, hk, hv, dk, dv) for _ in range(n)]
+        a_log, dt_bias = ins[0][3], ins[0][4]
+        al_d, dt_d = dev(a_log, torch.bfloat16), dev(dt_bias, torch.bfloat16)
+        keep, sessions, ys, sts = [], [], [], []
+        for conv, a, b, _, _, state in ins:
+            cd, ad, bd, sd = dev(conv), dev(a), dev(b), dev(state, torch.float32)
+            y = torch.full((rows, cfg.value_dim), float("nan"), device="cuda", dtype=torch.float16)
+            keep += [cd, ad, bd]; ys.append(y); sts.append(sd)
+            sessions.append(tt.GDNSession(cd, ad, bd, sd, y))
+        gdn.encode_delta_step_batched(sessions, al_d, dt_d, rows=rows)
+        torch.cuda.synchronize()
+        assert ctx.poll_status() == 0
+        for i in (0, n // 2, n - 1):
+            conv, a, b, _, _, state = ins[i]
+            wy, ws, _ = oracle.gdn_step_rows(conv, a, b, a_log, dt_bias, hk, hv, dk, dv, state)
+            assert np.abs(host(ys[i]) - wy).max() <= TOL, i
+            assert np.abs(host(sts[i]) - ws).max() <= 1e-5, i
+    finally:
+        ctx.close()
