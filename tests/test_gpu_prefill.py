@@ -90,7 +90,10 @@ def tc_case(r, start, chunk, hq, hkv, window=0, dtype=torch.float16, pad=0, extr
 
 @pytest.mark.parametrize("start,chunk,hq,hkv,window,pad,extra", [
     (0, 128, 2, 1, 0, 0, 0), (0, 64, 2, 2, 0, 0, 0), (0, 1, 2, 1, 0, 0, 0), (0, 300, 4, 2, 0, 8, 0),
-    (77, 200, 2, 1, 0, 0, 0), (0, 513, 2, 1, 0, 0, 0), (130, 129, 4, 1, 100, 0, 5), (0, 1024, 16, 2, 0, 0, 0)])
+    (77, 200, 2, 1, 0, 0, 0), (0, 513, 2, 1, 0, 0, 0), (130, 129, 4, 1, 100, 0, 5), (0, 1024, 16, 2, 0, 0, 0),
+    # around the 128-key tile and the 64-key halves the two softmax groups and the V loads work in
+    (0, 127, 2, 1, 0, 0, 0), (0, 255, 2, 1, 0, 0, 0), (0, 257, 2, 2, 0, 0, 0), (128, 128, 2, 1, 0, 0, 0),
+    (65, 190, 2, 1, 0, 0, 0), (0, 600, 2, 1, 200, 0, 0), (300, 77, 2, 1, 65, 8, 3)])
 def test_tcgen05_kernel_matches_oracle(start, chunk, hq, hkv, window, pad, extra):
     r = np.random.default_rng(start * 7 + chunk)
     q, k, v, p = tc_case(r, start, chunk, hq, hkv, window, pad=pad, extra_valid=extra)
@@ -175,3 +178,16 @@ def test_validation_errors():
             pa.encode_causal(x, x, x, x, tt.PrefillAttentionParams(**{**ok, **bad}))
     with pytest.raises(tt.InvalidArgument):   # quantised stride without room for the values and groups
         pa.encode_causal(x, x, x, x, tt.PrefillAttentionParams(**{**ok, "kv_bits": 8, "kv_token_stride_bytes": 72}))
+
+
+def test_non_positive_scale_takes_the_generic_kernel():
+    # the tensor-core kernel takes row maxima before scaling, which needs a positive scale
+    r = np.random.default_rng(8)
+    q, k, v, p = tc_case(r, 0, 130, 2, 1)
+    p = tt.PrefillAttentionParams(p.start_position, p.query_count, p.head_dim, p.num_q_heads, p.num_kv_heads,
+                                  p.kv_valid_count, p.sliding_window, p.kv_token_stride_elements,
+                                  p.q_token_stride_elements, p.o_token_stride_elements, -0.0625)
+    want = oracle.attn_prefill(q, k, v, p.q_token_stride_elements, p.kv_token_stride_elements, 256, 2, 1, 0, 130,
+                               p.kv_valid_count, 0, -0.0625)
+    got = run_prefill(q, k, v, p, expect="generic")
+    assert np.abs(got - want).max() <= TOL
