@@ -388,7 +388,9 @@ def aux_measurements(w, pk, only=None, c5_sessions=64):
         gdn_bytes = N_SESSIONS * GV * GD * GD * 4 * 2 + N_SESSIONS * (2 * GK * GD + GV * GD) * 2 + N_SESSIONS * GV * GD * 2
         aux["gdn_step_c2"] = {"ms": ms, "kernel_ms": kms, "GBps": gdn_bytes / kms / 1e6,
                               "frac_hbm": gdn_bytes / kms / 1e6 / pk["hbm_gbs"],
-                              "note": "GBps and frac_hbm from kernel_ms (per-launch events); ms is one Python call per step"}
+                              "note": "GBps and frac_hbm from kernel_ms (per-launch events); ms is one Python call per step; "
+                                      "launched back to back, so about half of the 134 MB state is still in L2 -- "
+                                      "the cold-L2 figure is gdn_step_in_step in the main line"}
     # config 3: causal prefill, 8192 tokens, 16/2/256, bf16, tcgen05 kernel
     try:
         want("prefill_c3")
@@ -620,11 +622,13 @@ def run_gpu_arm(args):
     sampler.start()
     launches0 = w.ctx.launch_count
     # per-launch device time of the dominant kernel is recorded for the first <= 256 steps
-    w.ctx.profile_enable(True)
+    w.ctx.profile_enable(w.ctx.PROFILE_DECODE_PARTIAL | w.ctx.PROFILE_GDN_STEP)
     ms_total = timed_loop(torch, dist, world, w.step, args.steps)
     launches = w.ctx.launch_count - launches0
-    partial_ms = w.ctx.profile_collect()
+    both_ms = w.ctx.profile_collect()
     w.ctx.profile_enable(False)
+    # a step launches the decode pass 1 and then the GDN step: the record alternates
+    partial_ms, gdn_ms = both_ms[0::2], both_ms[1::2]
     assert w.ctx.poll_status() == 0, "device status word is not clean"
 
     for _ in range(3):
@@ -669,6 +673,10 @@ def run_gpu_arm(args):
                          "launches_timed": len(partial_ms),
                          "traffic": (TRAFFIC_PER_ALGORITHMIC_BYTE * alg) if TRAFFIC_PER_ALGORITHMIC_BYTE else None},
             "hbm_GBps_step": (alg + N_SESSIONS * GV * GD * GD * 8) / ms_per_step / 1e6,
+            "gdn_step_in_step": ({"kernel_ms": statistics.mean(gdn_ms),
+                                  "frac_hbm": N_SESSIONS * GV * GD * GD * 8 / statistics.mean(gdn_ms) / 1e6 / pk["hbm_gbs"],
+                                  "note": "the GDN step kernel between two decode passes (cold L2), state bytes only"}
+                                 if gdn_ms else None),
         }
         if world == 1 and not args.no_aux:
             line["aux"] = aux_measurements(w, pk)
