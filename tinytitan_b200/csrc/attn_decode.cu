@@ -967,11 +967,26 @@ static uint32_t wide_part_length(const uint32_t *keys, const uint32_t *q_rows, u
                                  uint32_t max_items) {
     uint32_t max_keys = 0;
     for (uint32_t i = 0; i < n_sessions; ++i) max_keys = keys[i] > max_keys ? keys[i] : max_keys;
-    static const uint32_t kPartChoices[] = {1, 2, 3, 4, 5, 6, 8, 10, 12, 16, 20, 24, 32, 48, 64};
+    // Part counts tried for the longest session (every candidate costs a simulation on the host, so
+    // there are few). Few streams (fewer than SMs) are best cut so that ONE wave of items just fills
+    // the machine, i.e. into about SMs / streams parts: the counts around that value are tried next
+    // to the coarse ladder.
+    static const uint32_t kCoarse[] = {1, 2, 3, 4, 5, 6, 8, 10, 12, 16, 20, 24, 32, 48, 64};
+    std::vector<uint32_t> choices;
+    const uint32_t streams = n_sessions * n_kv_heads;
+    if (streams < sm_count) {
+        const uint32_t fill = sm_count / streams;
+        for (uint32_t c = fill > 2 ? fill - 2 : 1; c <= fill + 1 && c <= 64; ++c) choices.push_back(c);
+        for (uint32_t c : kCoarse)
+            if (c < fill && std::find(choices.begin(), choices.end(), c) == choices.end()) choices.push_back(c);
+    } else {
+        choices.assign(kCoarse, kCoarse + sizeof(kCoarse) / sizeof(kCoarse[0]));
+    }
+    std::sort(choices.begin(), choices.end());
     std::vector<uint32_t> heap;
     uint64_t best = ~(uint64_t)0;
     uint32_t target = 0;
-    for (uint32_t parts : kPartChoices) {
+    for (uint32_t parts : choices) {
         uint32_t len = (ceil_div_u32(max_keys, parts) + 127) / 128 * 128;
         if (len < 512) len = 512;                 // at least four tiles per item
         uint64_t items = 0, prows = 0;
@@ -1020,8 +1035,25 @@ TT_API int tt_attn_plan_verify_splits(const uint32_t *keys_per_session, const ui
 static bool plan_wide(tt_context *ctx, const TTDecodeSession *in_sessions, uint32_t n_sessions,
                       const tt_attn_batch_params *p, const uint32_t *keys, uint32_t *out_items,
                       uint32_t *out_partial_rows, uint32_t *out_max_rows) {
-    const uint32_t target = wide_part_length(keys, ctx->h_rows, n_sessions, p->head_dim, p->n_q_heads, p->n_kv_heads,
-                                             (uint32_t)ctx->sm_count, ctx->workspace_bytes, ctx->max_items);
+    // the simulation behind the part length costs tens of microseconds on the host: reuse the last
+    // plan while its inputs (tile counts, row counts, head geometry) are unchanged
+    std::vector<uint32_t> &key = ctx->verify_plan_key;
+    bool same = key.size() == 2 * (size_t)n_sessions + 3 && key[0] == p->n_q_heads && key[1] == p->n_kv_heads &&
+                key[2] == p->head_dim;
+    for (uint32_t i = 0; same && i < n_sessions; ++i)
+        same = key[3 + 2 * i] == (keys[i] + 127) / 128 && key[4 + 2 * i] == ctx->h_rows[i];
+    if (!same) {
+        ctx->verify_plan_target = wide_part_length(keys, ctx->h_rows, n_sessions, p->head_dim, p->n_q_heads,
+                                                   p->n_kv_heads, (uint32_t)ctx->sm_count, ctx->workspace_bytes,
+                                                   ctx->max_items);
+        key.resize(2 * (size_t)n_sessions + 3);
+        key[0] = p->n_q_heads; key[1] = p->n_kv_heads; key[2] = p->head_dim;
+        for (uint32_t i = 0; i < n_sessions; ++i) {
+            key[3 + 2 * i] = (keys[i] + 127) / 128;
+            key[4 + 2 * i] = ctx->h_rows[i];
+        }
+    }
+    const uint32_t target = ctx->verify_plan_target;
     if (target == 0) return false;
     uint32_t partial_cursor = 0, item_cursor = 0, max_rows = 0;
     const uint32_t group = p->n_q_heads / p->n_kv_heads;

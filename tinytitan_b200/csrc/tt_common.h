@@ -7,6 +7,7 @@
 
 #include <cstdarg>
 #include <cstdint>
+#include <vector>
 #include <cstdio>
 #include <cstring>
 
@@ -76,6 +77,10 @@ struct tt_context {
     uint32_t *h_rows = nullptr;
     void *h_tensor_maps = nullptr;
     uint64_t launches = 0;
+    // last verify split plan: the part length only depends on the sessions' 128-key tile counts and
+    // row counts, which stay the same for up to 128 consecutive decode steps
+    std::vector<uint32_t> verify_plan_key;
+    uint32_t verify_plan_target = 0;
     // optional per-launch timing of the selected kernel classes (mask of TT_PROFILE_*)
     static constexpr uint32_t kProfileSlots = 256;
     int profiling = 0;
