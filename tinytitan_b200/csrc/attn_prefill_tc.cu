@@ -446,6 +446,20 @@ bool tt_make_tensor_map_2d(CUtensorMap *map, const void *base, uint32_t io_dtype
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 2-D map over 4-byte floats: [rows][width], rows `stride_bytes` apart, box [box_rows][32 floats].
+bool tt_make_tensor_map_2d_f32(CUtensorMap *map, const void *base, uint64_t width, uint64_t rows,
+                               uint64_t stride_bytes, uint32_t box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {width, rows};
+    const cuuint64_t strides[1] = {stride_bytes};
+    const cuuint32_t box[2] = {32, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int tt_launch_prefill_tc(tt_context *ctx, cudaStream_t stream, const void *q, const void *k, const void *v,
                          void *out, const tt_prefill_params *p, uint32_t io_dtype) {
     CUtensorMap k_map, v_map;

@@ -22,7 +22,7 @@
 //                            state lives in mma accumulator registers for the whole segment
 // The rows of S (value dimension) are independent of one another, which is what lets the state
 // be split over CTAs with no communication.
-#include "tt_common.h"
+#include "tt_sm100.h"
 
 namespace {
 
@@ -31,6 +31,7 @@ constexpr int kD = 128;         // Dk == Dv
 constexpr int kPitch = kD + 8;  // fp16 row pitch of [*][128] tiles (272 B: ldmatrix conflict-free)
 constexpr int kPitchC = kC + 8; // fp16 row pitch of [*][64] tiles (144 B)
 constexpr int kDvb = 32;        // state rows per CTA of the state kernel
+constexpr int kStateThreads = 256;   // 8 warps: (token tile / column group) x (half of the state rows)
 
 // Per (chunk, value head) record in the workspace.
 struct ChunkRecord {
@@ -41,9 +42,6 @@ struct ChunkRecord {
     float decay_w[kC];      // A_C / A_t
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -101,6 +99,7 @@ struct ScanParams {
     uint32_t token0;          // first token of the segment
     uint32_t n_chunks;        // chunks in the segment
     float readout_scale;
+    uint32_t *status;         // device status word of the context
 };
 
 // ---------------------------------------------------------------------------------------
@@ -270,182 +269,214 @@ __global__ void __launch_bounds__(256) gdn_scan_prepare_kernel(ScanParams p) {
 
 // ---------------------------------------------------------------------------------------
 // Phase 2: the chunks of a segment in order, for 32 state rows of one value head.
-// grid = (Dv / 32, Hv), block = 128 (4 warps). Warp w owns token rows 16w..16w+15 of the
-// per-chunk products and state columns 32w..32w+31 (all 32 state rows) as accumulators.
+// grid = (Dv / 32, Hv), block = 256 (8 warps). Warp w = (tt = w % 4, sh = w / 4) owns token rows
+// 16tt..16tt+15 x state rows 16sh..16sh+15 of the per-chunk products, and state rows 16sh..16sh+15 x
+// columns 32tt..32tt+31 as accumulators (four warps alone left the SM's MMA issue mostly idle: one CTA
+// per SM, 6 % of the warp slots).
 // ---------------------------------------------------------------------------------------
+// Operand tiles arrive by TMA in the 128-byte swizzle: a [64 tokens][128] fp16 tile is two boxes of
+// [64][64] (8 KB each, 16-byte piece c of row r at (c ^ (r & 7)) << 4), U is one box of [64][32] fp32.
 struct StateStage {
-    __half q[kC][kPitch];
-    __half k[kC][kPitch];
-    __half w[kC][kPitch];
-    __half m[kC][kPitchC];
-    float u[kC][kDvb + 4];
+    __half q[2][kC][64];
+    __half k[2][kC][64];
+    __half w[2][kC][64];
+    __half m[kC][64];
+    float u[kC][kDvb];
     float decay_a[kC];
     float decay_w[kC];
+    unsigned char pad[512];        // keeps every stage (and so every tile) 1024-byte aligned
 };
+constexpr int kStages = 3;
+constexpr uint32_t kStageTxBytes = 3 * 2 * kC * 64 * 2 + kC * 64 * 2 + kC * kDvb * 4 + 2 * kC * 4;
+static_assert(sizeof(StateStage) % 1024 == 0, "stage tiles must stay 1024-byte aligned");
 struct StateSmem {
-    StateStage stage[2];
+    StateStage stage[kStages];
     __half s16[kDvb][kPitch];      // the state slice as an fp16 MMA operand
     __half c16[kC][kDvb + 8];      // corrections C (tokens x state rows)
     __half cw16[kC][kDvb + 8];     // diag(A_C/A_t) C, the operand of the state update
+    uint64_t full[kStages];        // one mbarrier per stage, completed by the copies' byte count
 };
+static_assert(sizeof(StateSmem) <= 227 * 1024, "state kernel shared memory");
 
-__device__ __forceinline__ void state_load_chunk(StateStage &st, const ScanParams &p, uint32_t chunk, uint32_t h,
-                                                 uint32_t hk, uint32_t dv0, int tid) {
-    const uint32_t t0 = p.token0 + chunk * kC;
-    const uint32_t n_tok = min((uint32_t)kC, p.rows - t0);
-    const ChunkRecord &rec = p.records[(size_t)chunk * p.hv + h];
-    for (int idx = tid; idx < kC * (kD / 8); idx += 128) {
-        const int t = idx / (kD / 8), c = idx % (kD / 8);
-        const bool ok = (uint32_t)t < n_tok;
-        const __half *row = p.conv_out + (size_t)(t0 + (ok ? t : 0)) * p.row_stride;
-        cp_async16(&st.q[t][c * 8], row + (size_t)hk * kD + c * 8, ok);
-        cp_async16(&st.k[t][c * 8], row + (size_t)p.hk * kD + (size_t)hk * kD + c * 8, ok);
-        cp_async16(&st.w[t][c * 8], &rec.w[t][c * 8], true);
-    }
-    for (int idx = tid; idx < kC * (kC / 8); idx += 128) {
-        const int t = idx / (kC / 8), c = idx % (kC / 8);
-        cp_async16(&st.m[t][c * 8], &rec.m[t][c * 8], true);
-    }
-    for (int idx = tid; idx < kC * (kDvb / 4); idx += 128) {
-        const int t = idx / (kDvb / 4), c = idx % (kDvb / 4);
-        cp_async16(&st.u[t][c * 4], &rec.u[t][dv0 + c * 4], true);
-    }
-    if (tid < 32) {
-        const int t = (tid & 15) * 4;
-        cp_async16(tid < 16 ? &st.decay_a[t] : &st.decay_w[t], tid < 16 ? &rec.decay_a[t] : &rec.decay_w[t], true);
-    }
-    cp_async_commit();
+// Address of the 16-byte piece holding column `col` (a multiple of 8) of row `row` in a swizzled tile.
+__device__ __forceinline__ uint32_t sw_piece(uint32_t base, int row, int col) {
+    return base + ((col >> 6) << 13) + (row << 7) + ((((col >> 3) & 7) ^ (row & 7)) << 4);
+}
+// ldmatrix row addresses on swizzled tiles, lane roles as in addr_a / addr_bt
+__device__ __forceinline__ uint32_t sw_a(uint32_t base, int row0, int k0, int lane) {
+    return sw_piece(base, row0 + (lane & 15), k0 + (lane >> 4) * 8);
+}
+__device__ __forceinline__ uint32_t sw_bt(uint32_t base, int k0, int n0, int lane) {
+    return sw_piece(base, k0 + (lane & 7) + ((lane >> 3) & 1) * 8, n0 + (lane >> 4) * 8);
 }
 
-__global__ void __launch_bounds__(128) gdn_scan_state_kernel(ScanParams p) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    StateSmem &s = *reinterpret_cast<StateSmem *>(smem_raw);
+// Records seen as 2-D tensors: a record is 226 rows of 256 bytes (W), 452 rows of 128 bytes (M) or
+// 113 rows of 512 bytes (U), so one map per field covers the whole workspace.
+static_assert(sizeof(ChunkRecord) % 512 == 0, "record rows");
+constexpr uint32_t kRecRowsW = sizeof(ChunkRecord) / 256, kRecRowsM = sizeof(ChunkRecord) / 128,
+                   kRecRowsU = sizeof(ChunkRecord) / 512;
+
+// One thread issues the ten copies of a chunk; they complete on the stage's mbarrier.
+__device__ __forceinline__ void state_issue_chunk(StateStage &st, uint64_t *bar, const ScanParams &p,
+                                                  const CUtensorMap *conv_map, const CUtensorMap *w_map,
+                                                  const CUtensorMap *m_map, const CUtensorMap *u_map,
+                                                  uint32_t chunk, uint32_t h, uint32_t hk, uint32_t dv0) {
+    const int t0 = (int)(p.token0 + chunk * kC);      // rows past the sequence read as zeros
+    const uint32_t rec = chunk * p.hv + h;
+    const int xq = (int)(hk * kD), xk = (int)((p.hk + hk) * kD);
+    mbar_expect_tx(bar, kStageTxBytes);
+    tma_load_2d(&st.w[0][0][0], w_map, 0, (int)(rec * kRecRowsW), bar);
+    tma_load_2d(&st.w[1][0][0], w_map, 64, (int)(rec * kRecRowsW), bar);
+    tma_load_2d(&st.q[0][0][0], conv_map, xq, t0, bar);
+    tma_load_2d(&st.q[1][0][0], conv_map, xq + 64, t0, bar);
+    tma_load_2d(&st.u[0][0], u_map, (int)dv0, (int)(rec * kRecRowsU), bar);
+    bulk_copy_g2s(&st.decay_a[0], &p.records[rec].decay_a[0], 2 * kC * 4, bar);
+    tma_load_2d(&st.m[0][0], m_map, 0, (int)(rec * kRecRowsM), bar);
+    tma_load_2d(&st.k[0][0][0], conv_map, xk, t0, bar);
+    tma_load_2d(&st.k[1][0][0], conv_map, xk + 64, t0, bar);
+}
+
+__global__ void __launch_bounds__(kStateThreads)
+gdn_scan_state_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_map,
+                      const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap m_map,
+                      const __grid_constant__ CUtensorMap u_map) {
+    extern __shared__ __align__(1024) unsigned char state_smem_raw[];
+    StateSmem &s = *reinterpret_cast<StateSmem *>(state_smem_raw);
+    if ((smem_u32(state_smem_raw) & 1023u) != 0) {   // the swizzled tiles need the alignment the attribute asks for
+        if (threadIdx.x == 0) atomicOr(p.status, TT_DEV_BAD_ITEM);
+        return;
+    }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tt = warp & 3;     // token tile of the per-chunk products, column group of the state update
+    const int sh = warp >> 2;    // which 16 of the CTA's 32 state rows
     const uint32_t h = blockIdx.y, dv0 = blockIdx.x * kDvb;
     const uint32_t hk = (p.flags & TT_GDN_V_TILED) ? h % p.hk : h / (p.hv / p.hk);
     float *state = p.state + ((size_t)h * kD + dv0) * kD;
+    const int g = lane >> 2, q2 = (lane & 3) * 2;
 
-    // state slice [32 rows][128] -> accumulator fragments: m-tile mt (rows 16mt..), n-tile nt of
-    // this warp's 32 columns; c0,c1 -> row g, c2,c3 -> row g+8, columns 2*(lane&3)
-    float sacc[2][4][4];
+    // state rows sh*16 + g (+8), columns tt*32 + nt*8 + q2 (+1) -> accumulator fragments
+    float sacc[4][4];
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            const int col = warp * 32 + nt * 8 + (lane & 3) * 2;
-            const float2 lo = *reinterpret_cast<const float2 *>(state + (size_t)(mt * 16 + (lane >> 2)) * kD + col);
-            const float2 hi = *reinterpret_cast<const float2 *>(state + (size_t)(mt * 16 + (lane >> 2) + 8) * kD + col);
-            sacc[mt][nt][0] = lo.x; sacc[mt][nt][1] = lo.y; sacc[mt][nt][2] = hi.x; sacc[mt][nt][3] = hi.y;
-        }
+    for (int nt = 0; nt < 4; ++nt) {
+        const int col = tt * 32 + nt * 8 + q2;
+        const float2 lo = *reinterpret_cast<const float2 *>(state + (size_t)(sh * 16 + g) * kD + col);
+        const float2 hi = *reinterpret_cast<const float2 *>(state + (size_t)(sh * 16 + g + 8) * kD + col);
+        sacc[nt][0] = lo.x; sacc[nt][1] = lo.y; sacc[nt][2] = hi.x; sacc[nt][3] = hi.y;
+    }
 
-    state_load_chunk(s.stage[0], p, 0, h, hk, dv0, tid);
+    if (tid == 0) {
+        for (int i = 0; i < kStages; ++i) mbar_init(&s.full[i], 1);
+        mbar_fence_init();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (uint32_t c = 0; c < (uint32_t)(kStages - 1) && c < p.n_chunks; ++c)
+            state_issue_chunk(s.stage[c], &s.full[c], p, &conv_map, &w_map, &m_map, &u_map, c, h, hk, dv0);
+    }
+    __syncthreads();
 
     for (uint32_t c = 0; c < p.n_chunks; ++c) {
-        StateStage &st = s.stage[c & 1];
+        const uint32_t slot = c % kStages;
+        StateStage &st = s.stage[slot];
         // publish the current state as an fp16 operand
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                const int col = warp * 32 + nt * 8 + (lane & 3) * 2;
-                *reinterpret_cast<uint32_t *>(&s.s16[mt * 16 + (lane >> 2)][col]) = pack_h2(sacc[mt][nt][0], sacc[mt][nt][1]);
-                *reinterpret_cast<uint32_t *>(&s.s16[mt * 16 + (lane >> 2) + 8][col]) = pack_h2(sacc[mt][nt][2], sacc[mt][nt][3]);
-            }
-        cp_async_wait<0>();
-        __syncthreads();   // (1) stage c and s16 are complete; everyone is done with chunk c-1
-        // only now may the other stage be refilled: chunk c-1's M C and state update read it
-        if (c + 1 < p.n_chunks) state_load_chunk(s.stage[(c + 1) & 1], p, c + 1, h, hk, dv0, tid);
+        for (int nt = 0; nt < 4; ++nt) {
+            const int col = tt * 32 + nt * 8 + q2;
+            *reinterpret_cast<uint32_t *>(&s.s16[sh * 16 + g][col]) = pack_h2(sacc[nt][0], sacc[nt][1]);
+            *reinterpret_cast<uint32_t *>(&s.s16[sh * 16 + g + 8][col]) = pack_h2(sacc[nt][2], sacc[nt][3]);
+        }
+        const bool landed = mbar_wait(&s.full[slot], (c / kStages) & 1);
+        // (1) stage c and s16 are complete; everyone is done with chunk c-1
+        if (__syncthreads_or(!landed)) {
+            if (tid == 0) atomicOr(p.status, TT_DEV_WAIT_TIMEOUT);
+            return;
+        }
+        // only now may chunk c-1's stage be refilled: its M C and state update read it
+        if (tid == 0 && c + kStages - 1 < p.n_chunks) {
+            const uint32_t nxt = (c + kStages - 1) % kStages;
+            state_issue_chunk(s.stage[nxt], &s.full[nxt], p, &conv_map, &w_map, &m_map, &u_map, c + kStages - 1, h,
+                              hk, dv0);
+        }
 
-        // ---- P = W S^T and R = Q S^T for this warp's 16 tokens x 32 state rows ----
-        const int r0 = warp * 16;
-        float pw[4][4], rq[4][4];
+        // ---- P = W S^T and R = Q S^T for this warp's 16 tokens x 16 state rows ----
+        const int r0 = tt * 16;
+        float pw[2][4], rq[2][4];
 #pragma unroll
-        for (int n = 0; n < 4; ++n)
+        for (int n = 0; n < 2; ++n)
 #pragma unroll
             for (int j = 0; j < 4; ++j) { pw[n][j] = 0.f; rq[n][j] = 0.f; }
-        const uint32_t wb = smem_u32(&st.w[0][0]), qb = smem_u32(&st.q[0][0]), sb = smem_u32(&s.s16[0][0]);
+        const uint32_t wb = smem_u32(&st.w[0][0][0]), qb = smem_u32(&st.q[0][0][0]), sb = smem_u32(&s.s16[0][0]);
 #pragma unroll
         for (int ks = 0; ks < kD / 16; ++ks) {
-            uint32_t aw[4], aq[4], b0[4], b1[4];
-            ldsm_x4(aw, addr_a(wb, kPitch, r0, ks * 16, lane));
-            ldsm_x4(aq, addr_a(qb, kPitch, r0, ks * 16, lane));
-            ldsm_x4(b0, addr_b(sb, kPitch, 0, ks * 16, lane));
-            ldsm_x4(b1, addr_b(sb, kPitch, 16, ks * 16, lane));
-            mma16816(pw[0], aw, b0[0], b0[1]); mma16816(pw[1], aw, b0[2], b0[3]);
-            mma16816(pw[2], aw, b1[0], b1[1]); mma16816(pw[3], aw, b1[2], b1[3]);
-            mma16816(rq[0], aq, b0[0], b0[1]); mma16816(rq[1], aq, b0[2], b0[3]);
-            mma16816(rq[2], aq, b1[0], b1[1]); mma16816(rq[3], aq, b1[2], b1[3]);
+            uint32_t aw[4], aq[4], bs[4];
+            ldsm_x4(aw, sw_a(wb, r0, ks * 16, lane));
+            ldsm_x4(aq, sw_a(qb, r0, ks * 16, lane));
+            ldsm_x4(bs, addr_b(sb, kPitch, sh * 16, ks * 16, lane));
+            mma16816(pw[0], aw, bs[0], bs[1]); mma16816(pw[1], aw, bs[2], bs[3]);
+            mma16816(rq[0], aq, bs[0], bs[1]); mma16816(rq[1], aq, bs[2], bs[3]);
         }
         // C = U - P (fp32), stored as fp16 twice: plain (for M C) and scaled by A_C/A_t (for the state)
 #pragma unroll
-        for (int n = 0; n < 4; ++n)
+        for (int n = 0; n < 2; ++n)
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
-                const int t = r0 + (lane >> 2) + hh * 8;
-                const int col = n * 8 + (lane & 3) * 2;
-                const float2 u = *reinterpret_cast<const float2 *>(&st.u[t][col]);
+                const int t = r0 + g + hh * 8;
+                const int col = sh * 16 + n * 8 + q2;
+                const float2 u = *reinterpret_cast<const float2 *>(
+                    reinterpret_cast<const unsigned char *>(&st.u[t][0]) + ((((col >> 2) ^ (t & 7)) << 4) | ((col & 3) << 2)));
                 const float c0v = u.x - pw[n][2 * hh], c1v = u.y - pw[n][2 * hh + 1];
                 const float wgt = st.decay_w[t];
                 *reinterpret_cast<uint32_t *>(&s.c16[t][col]) = pack_h2(c0v, c1v);
                 *reinterpret_cast<uint32_t *>(&s.cw16[t][col]) = pack_h2(c0v * wgt, c1v * wgt);
             }
-        __syncthreads();   // (2) C of all 64 tokens is visible
+        __syncthreads();   // (2) C of all 64 tokens and 32 state rows is visible
 
         // ---- O = diag(A) R + M C ; write y ----
         {
-            float o[4][4];
+            float o[2][4];
 #pragma unroll
-            for (int n = 0; n < 4; ++n)
+            for (int n = 0; n < 2; ++n)
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
-                    const float a = st.decay_a[r0 + (lane >> 2) + hh * 8];
+                    const float a = st.decay_a[r0 + g + hh * 8];
                     o[n][2 * hh] = rq[n][2 * hh] * a; o[n][2 * hh + 1] = rq[n][2 * hh + 1] * a;
                 }
             const uint32_t mb = smem_u32(&st.m[0][0]), cb = smem_u32(&s.c16[0][0]);
 #pragma unroll
             for (int ks = 0; ks < kC / 16; ++ks) {
-                uint32_t am[4], b0[4], b1[4];
-                ldsm_x4(am, addr_a(mb, kPitchC, r0, ks * 16, lane));
-                ldsm_x4_t(b0, addr_bt(cb, kDvb + 8, ks * 16, 0, lane));
-                ldsm_x4_t(b1, addr_bt(cb, kDvb + 8, ks * 16, 16, lane));
-                mma16816(o[0], am, b0[0], b0[1]); mma16816(o[1], am, b0[2], b0[3]);
-                mma16816(o[2], am, b1[0], b1[1]); mma16816(o[3], am, b1[2], b1[3]);
+                uint32_t am[4], bc[4];
+                ldsm_x4(am, sw_a(mb, r0, ks * 16, lane));
+                ldsm_x4_t(bc, addr_bt(cb, kDvb + 8, ks * 16, sh * 16, lane));
+                mma16816(o[0], am, bc[0], bc[1]); mma16816(o[1], am, bc[2], bc[3]);
             }
             const uint32_t t0 = p.token0 + c * kC;
 #pragma unroll
-            for (int n = 0; n < 4; ++n)
+            for (int n = 0; n < 2; ++n)
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
-                    const uint32_t t = t0 + r0 + (lane >> 2) + hh * 8;
+                    const uint32_t t = t0 + r0 + g + hh * 8;
                     if (t < p.rows) {
-                        __half *dst = p.y + (size_t)t * p.hv * kD + (size_t)h * kD + dv0 + n * 8 + (lane & 3) * 2;
+                        __half *dst = p.y + (size_t)t * p.hv * kD + (size_t)h * kD + dv0 + sh * 16 + n * 8 + q2;
                         *reinterpret_cast<uint32_t *>(dst) =
                             pack_h2(o[n][2 * hh] * p.readout_scale, o[n][2 * hh + 1] * p.readout_scale);
                     }
                 }
         }
 
-        // ---- S = A_C S + (diag(A_C/A_t) C)^T K : 32 rows x this warp's 32 columns ----
+        // ---- S = A_C S + (diag(A_C/A_t) C)^T K : this warp's 16 rows x 32 columns ----
         {
             const float a_c = st.decay_a[kC - 1];
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
+            for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) sacc[mt][nt][j] *= a_c;
-            const uint32_t cwb = smem_u32(&s.cw16[0][0]), kb = smem_u32(&st.k[0][0]);
+                for (int j = 0; j < 4; ++j) sacc[nt][j] *= a_c;
+            const uint32_t cwb = smem_u32(&s.cw16[0][0]), kb = smem_u32(&st.k[0][0][0]);
 #pragma unroll
             for (int ks = 0; ks < kC / 16; ++ks) {
-                uint32_t a0[4], a1[4], b0[4], b1[4];
-                ldsm_x4_t(a0, addr_at(cwb, kDvb + 8, ks * 16, 0, lane));
-                ldsm_x4_t(a1, addr_at(cwb, kDvb + 8, ks * 16, 16, lane));
-                ldsm_x4_t(b0, addr_bt(kb, kPitch, ks * 16, warp * 32, lane));
-                ldsm_x4_t(b1, addr_bt(kb, kPitch, ks * 16, warp * 32 + 16, lane));
-                mma16816(sacc[0][0], a0, b0[0], b0[1]); mma16816(sacc[0][1], a0, b0[2], b0[3]);
-                mma16816(sacc[0][2], a0, b1[0], b1[1]); mma16816(sacc[0][3], a0, b1[2], b1[3]);
-                mma16816(sacc[1][0], a1, b0[0], b0[1]); mma16816(sacc[1][1], a1, b0[2], b0[3]);
-                mma16816(sacc[1][2], a1, b1[0], b1[1]); mma16816(sacc[1][3], a1, b1[2], b1[3]);
+                uint32_t ac[4], b0[4], b1[4];
+                ldsm_x4_t(ac, addr_at(cwb, kDvb + 8, ks * 16, sh * 16, lane));
+                ldsm_x4_t(b0, sw_bt(kb, ks * 16, tt * 32, lane));
+                ldsm_x4_t(b1, sw_bt(kb, ks * 16, tt * 32 + 16, lane));
+                mma16816(sacc[0], ac, b0[0], b0[1]); mma16816(sacc[1], ac, b0[2], b0[3]);
+                mma16816(sacc[2], ac, b1[0], b1[1]); mma16816(sacc[3], ac, b1[2], b1[3]);
             }
         }
         // the next iteration's barrier (1) orders these reads of stage c / c16 / cw16 against
@@ -453,15 +484,11 @@ __global__ void __launch_bounds__(128) gdn_scan_state_kernel(ScanParams p) {
     }
 
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            const int col = warp * 32 + nt * 8 + (lane & 3) * 2;
-            *reinterpret_cast<float2 *>(state + (size_t)(mt * 16 + (lane >> 2)) * kD + col) =
-                make_float2(sacc[mt][nt][0], sacc[mt][nt][1]);
-            *reinterpret_cast<float2 *>(state + (size_t)(mt * 16 + (lane >> 2) + 8) * kD + col) =
-                make_float2(sacc[mt][nt][2], sacc[mt][nt][3]);
-        }
+    for (int nt = 0; nt < 4; ++nt) {
+        const int col = tt * 32 + nt * 8 + q2;
+        *reinterpret_cast<float2 *>(state + (size_t)(sh * 16 + g) * kD + col) = make_float2(sacc[nt][0], sacc[nt][1]);
+        *reinterpret_cast<float2 *>(state + (size_t)(sh * 16 + g + 8) * kD + col) = make_float2(sacc[nt][2], sacc[nt][3]);
+    }
 }
 
 }  // namespace
@@ -501,6 +528,17 @@ TT_API int tt_gdn_scan_chunked(tt_context *ctx, tt_stream stream, const void *co
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn scan smem attribute");
         attrs_set = true;
     }
+    CUtensorMap conv_map, w_map, m_map, u_map;
+    {
+        ChunkRecord *rec0 = reinterpret_cast<ChunkRecord *>(ctx->partials);
+        const uint64_t n_rec = (uint64_t)seg_chunks * shape->n_v_heads;
+        const bool ok =
+            tt_make_tensor_map_2d(&conv_map, conv_out, TT_F16, tight, rows, row_stride, kC) &&
+            tt_make_tensor_map_2d(&w_map, &rec0->w[0][0], TT_F16, kD, (n_rec - 1) * kRecRowsW + kC, kD, kC) &&
+            tt_make_tensor_map_2d(&m_map, &rec0->m[0][0], TT_F16, kC, (n_rec - 1) * kRecRowsM + kC, kC, kC) &&
+            tt_make_tensor_map_2d_f32(&u_map, &rec0->u[0][0], kD, (n_rec - 1) * kRecRowsU + kC, kD * 4, kC);
+        if (!ok) return tt_set_error(ctx, TT_ERR_CUDA, "cuTensorMapEncodeTiled failed for the scan operands");
+    }
     ScanParams p;
     p.conv_out = reinterpret_cast<const __half *>(conv_out); p.a = a; p.b = b;
     p.a_log = reinterpret_cast<const __nv_bfloat16 *>(a_log); p.dt_bias = reinterpret_cast<const __nv_bfloat16 *>(dt_bias);
@@ -508,6 +546,7 @@ TT_API int tt_gdn_scan_chunked(tt_context *ctx, tt_stream stream, const void *co
     p.records = reinterpret_cast<ChunkRecord *>(ctx->partials);
     p.hk = shape->n_k_heads; p.hv = shape->n_v_heads; p.rows = rows; p.row_stride = row_stride; p.flags = shape->flags;
     p.readout_scale = shape->readout_scale;
+    p.status = ctx->status;
     const uint32_t total_chunks = (rows + kC - 1) / kC;
     for (uint32_t c0 = 0; c0 < total_chunks; c0 += seg_chunks) {
         p.token0 = c0 * kC;
@@ -515,7 +554,8 @@ TT_API int tt_gdn_scan_chunked(tt_context *ctx, tt_stream stream, const void *co
         gdn_scan_prepare_kernel<<<dim3(p.n_chunks, p.hv), 256, sizeof(PrepSmem), (cudaStream_t)stream>>>(p);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn_scan_prepare launch");
-        gdn_scan_state_kernel<<<dim3(kD / kDvb, p.hv), 128, sizeof(StateSmem), (cudaStream_t)stream>>>(p);
+        gdn_scan_state_kernel<<<dim3(kD / kDvb, p.hv), kStateThreads, sizeof(StateSmem), (cudaStream_t)stream>>>(
+            p, conv_map, w_map, m_map, u_map);
         e = cudaGetLastError();
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn_scan_state launch");
         ctx->launches += 2;

@@ -169,6 +169,9 @@ __device__ __forceinline__ float sum2<__nv_bfloat16>(uint32_t packed) {
 // not 16-byte aligned, stride not a multiple of 16 bytes).
 bool tt_make_tensor_map_2d(CUtensorMap *map, const void *base, uint32_t io_dtype, uint64_t width, uint64_t rows,
                            uint64_t stride_elems, uint32_t box_rows);
+// The same over 4-byte floats, rows `stride_bytes` apart, box [box_rows][32 floats] (128-byte rows).
+bool tt_make_tensor_map_2d_f32(CUtensorMap *map, const void *base, uint64_t width, uint64_t rows,
+                               uint64_t stride_bytes, uint32_t box_rows);
 
 // kind::f16 instruction descriptor, fp32 accumulate, M = 128; A and B share one 16-bit format (an
 // fp16 A against a bf16 B is an illegal instruction on sm_100a). An operand is K-major unless its
