@@ -60,13 +60,6 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&h);
 }
-__device__ __forceinline__ void cp_async16(void *dst, const void *src, bool valid) {
-    const uint32_t n = valid ? 16u : 0u;   // src-size 0 zero-fills the destination
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // ldmatrix addressing helpers for a row-major fp16 tile with `pitch` elements per row.
 // A operand (16 rows x 16 k) at (row0, k0); B operand for two n-tiles from a [n][k] tile
@@ -84,6 +77,23 @@ __device__ __forceinline__ uint32_t addr_bt(uint32_t base, int pitch, int k0, in
 // matrices: (k 0-7, m 0-7) -> a0, (k 0-7, m 8-15) -> a1, (k 8-15, m 0-7) -> a2, (k 8-15, m 8-15) -> a3
 __device__ __forceinline__ uint32_t addr_at(uint32_t base, int pitch, int k0, int m0, int lane) {
     return base + ((k0 + (lane & 7) + (lane >> 4) * 8) * pitch + m0 + ((lane >> 3) & 1) * 8) * 2;
+}
+
+// Operand tiles that arrive by TMA use the 128-byte swizzle: a [64 tokens][128] fp16 tile is two boxes
+// of [64][64] (8 KB each), the 16-byte piece c of row r sitting at (c ^ (r & 7)) << 4 within the row.
+// Address of the 16-byte piece holding column `col` (a multiple of 8) of row `row` in a swizzled tile.
+__device__ __forceinline__ uint32_t sw_piece(uint32_t base, int row, int col) {
+    return base + ((col >> 6) << 13) + (row << 7) + ((((col >> 3) & 7) ^ (row & 7)) << 4);
+}
+// ldmatrix row addresses on swizzled tiles, lane roles as in addr_a / addr_b / addr_bt
+__device__ __forceinline__ uint32_t sw_a(uint32_t base, int row0, int k0, int lane) {
+    return sw_piece(base, row0 + (lane & 15), k0 + (lane >> 4) * 8);
+}
+__device__ __forceinline__ uint32_t sw_b(uint32_t base, int n0, int k0, int lane) {
+    return sw_piece(base, n0 + (lane & 7) + ((lane >> 4) << 3), k0 + ((lane >> 3) & 1) * 8);
+}
+__device__ __forceinline__ uint32_t sw_bt(uint32_t base, int k0, int n0, int lane) {
+    return sw_piece(base, k0 + (lane & 7) + ((lane >> 3) & 1) * 8, n0 + (lane >> 4) * 8);
 }
 
 struct ScanParams {
@@ -107,19 +117,25 @@ struct ScanParams {
 // grid = (chunks in segment, Hv), block = 256.
 // ---------------------------------------------------------------------------------------
 struct PrepSmem {
-    __half k[kC][kPitch];
-    __half q[kC][kPitch];
-    __half v[kC][kPitch];
+    __half k[2][kC][64];            // swizzled boxes, filled by TMA
+    __half q[2][kC][64];
+    __half v[2][kC][64];
     float l[kC][kC + 4];            // strictly lower triangle of L, then reused for T
     __half tb_hi[kC][kPitchC], tb_lo[kC][kPitchC];   // T diag(b)      as fp16 hi + lo
     __half ta_hi[kC][kPitchC], ta_lo[kC][kPitchC];   // T diag(b A)
     float log_a[kC];                // cumulative log decay (inclusive)
     float beta[kC];
+    uint64_t full;                  // completes when the three tiles have landed
 };
 
-__global__ void __launch_bounds__(256) gdn_scan_prepare_kernel(ScanParams p) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+__global__ void __launch_bounds__(256)
+gdn_scan_prepare_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_map) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
     PrepSmem &s = *reinterpret_cast<PrepSmem *>(smem_raw);
+    if ((smem_u32(smem_raw) & 1023u) != 0) {   // the swizzled tiles need the alignment the attribute asks for
+        if (threadIdx.x == 0) atomicOr(p.status, TT_DEV_BAD_ITEM);
+        return;
+    }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t chunk = blockIdx.x, h = blockIdx.y;
     const uint32_t hk = (p.flags & TT_GDN_V_TILED) ? h % p.hk : h / (p.hv / p.hk);
@@ -127,16 +143,20 @@ __global__ void __launch_bounds__(256) gdn_scan_prepare_kernel(ScanParams p) {
     const uint32_t n_tok = min((uint32_t)kC, p.rows - t0);
     ChunkRecord &rec = p.records[(size_t)chunk * p.hv + h];
 
-    // ---- K, Q, V tiles (tokens past the end are zero rows) ----
-    for (int idx = tid; idx < kC * (kD / 8); idx += 256) {
-        const int t = idx / (kD / 8), c = idx % (kD / 8);
-        const bool ok = (uint32_t)t < n_tok;
-        const __half *row = p.conv_out + (size_t)(t0 + (ok ? t : 0)) * p.row_stride;
-        cp_async16(&s.q[t][c * 8], row + (size_t)hk * kD + c * 8, ok);
-        cp_async16(&s.k[t][c * 8], row + (size_t)p.hk * kD + (size_t)hk * kD + c * 8, ok);
-        cp_async16(&s.v[t][c * 8], row + (size_t)2 * p.hk * kD + (size_t)h * kD + c * 8, ok);
+    // ---- K, Q, V tiles by TMA (tokens past the end of the sequence read as zero rows) ----
+    if (tid == 0) {
+        mbar_init(&s.full, 1);
+        mbar_fence_init();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        const int xq = (int)(hk * kD), xk = (int)((p.hk + hk) * kD), xv = (int)((2 * p.hk + h) * kD);
+        mbar_expect_tx(&s.full, 3 * kC * kD * 2);
+        tma_load_2d(&s.k[0][0][0], &conv_map, xk, (int)t0, &s.full);
+        tma_load_2d(&s.k[1][0][0], &conv_map, xk + 64, (int)t0, &s.full);
+        tma_load_2d(&s.q[0][0][0], &conv_map, xq, (int)t0, &s.full);
+        tma_load_2d(&s.q[1][0][0], &conv_map, xq + 64, (int)t0, &s.full);
+        tma_load_2d(&s.v[0][0][0], &conv_map, xv, (int)t0, &s.full);
+        tma_load_2d(&s.v[1][0][0], &conv_map, xv + 64, (int)t0, &s.full);
     }
-    cp_async_commit();
 
     // ---- per-token gates: log decay and beta (padding tokens: decay 1, beta 0) ----
     if (tid < kC) {
@@ -162,8 +182,13 @@ __global__ void __launch_bounds__(256) gdn_scan_prepare_kernel(ScanParams p) {
         float run = 0.f;
         for (int t = 0; t < kC; ++t) { run += s.log_a[t]; s.log_a[t] = run; }
     }
-    cp_async_wait<0>();
-    __syncthreads();
+    {
+        const bool landed = mbar_wait(&s.full, 0);   // thread 0 initialised the barrier two __syncthreads ago
+        if (__syncthreads_or(!landed)) {
+            if (tid == 0) atomicOr(p.status, TT_DEV_WAIT_TIMEOUT);
+            return;
+        }
+    }
     if (tid < kC) {
         rec.decay_a[tid] = expf(s.log_a[tid]);
         rec.decay_w[tid] = expf(s.log_a[kC - 1] - s.log_a[tid]);
@@ -177,14 +202,14 @@ __global__ void __launch_bounds__(256) gdn_scan_prepare_kernel(ScanParams p) {
         for (int n = 0; n < 4; ++n)
 #pragma unroll
             for (int j = 0; j < 4; ++j) { gk[n][j] = 0.f; gq[n][j] = 0.f; }
-        const uint32_t kb = smem_u32(&s.k[0][0]), qb = smem_u32(&s.q[0][0]);
+        const uint32_t kb = smem_u32(&s.k[0][0][0]), qb = smem_u32(&s.q[0][0][0]);
 #pragma unroll
         for (int ks = 0; ks < kD / 16; ++ks) {
             uint32_t ak[4], aq[4], b0[4], b1[4];
-            ldsm_x4(ak, addr_a(kb, kPitch, r0, ks * 16, lane));
-            ldsm_x4(aq, addr_a(qb, kPitch, r0, ks * 16, lane));
-            ldsm_x4(b0, addr_b(kb, kPitch, c0, ks * 16, lane));
-            ldsm_x4(b1, addr_b(kb, kPitch, c0 + 16, ks * 16, lane));
+            ldsm_x4(ak, sw_a(kb, r0, ks * 16, lane));
+            ldsm_x4(aq, sw_a(qb, r0, ks * 16, lane));
+            ldsm_x4(b0, sw_b(kb, c0, ks * 16, lane));
+            ldsm_x4(b1, sw_b(kb, c0 + 16, ks * 16, lane));
             mma16816(gk[0], ak, b0[0], b0[1]); mma16816(gk[1], ak, b0[2], b0[3]);
             mma16816(gk[2], ak, b1[0], b1[1]); mma16816(gk[3], ak, b1[2], b1[3]);
             mma16816(gq[0], aq, b0[0], b0[1]); mma16816(gq[1], aq, b0[2], b0[3]);
@@ -194,12 +219,16 @@ __global__ void __launch_bounds__(256) gdn_scan_prepare_kernel(ScanParams p) {
 #pragma unroll
         for (int n = 0; n < 4; ++n)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int t = r0 + (lane >> 2) + (j >> 1) * 8;
-                const int sx = c0 + n * 8 + (lane & 3) * 2 + (j & 1);
-                const float ratio = sx <= t ? expf(s.log_a[t] - s.log_a[sx]) : 0.f;
-                s.l[t][sx] = sx < t ? s.beta[t] * ratio * gk[n][j] : 0.f;
-                rec.m[t][sx] = __float2half_rn(ratio * gq[n][j]);
+            for (int hh = 0; hh < 2; ++hh) {
+                const int t = r0 + (lane >> 2) + hh * 8;
+                const int sx = c0 + n * 8 + (lane & 3) * 2;      // this thread holds columns sx, sx + 1
+                const float la_t = s.log_a[t], be_t = s.beta[t];
+                const float2 la_s = *reinterpret_cast<const float2 *>(&s.log_a[sx]);
+                const float r0v = sx <= t ? expf(la_t - la_s.x) : 0.f;
+                const float r1v = sx + 1 <= t ? expf(la_t - la_s.y) : 0.f;
+                *reinterpret_cast<float2 *>(&s.l[t][sx]) =
+                    make_float2(sx < t ? be_t * r0v * gk[n][2 * hh] : 0.f, sx + 1 < t ? be_t * r1v * gk[n][2 * hh + 1] : 0.f);
+                *reinterpret_cast<uint32_t *>(&rec.m[t][sx]) = pack_h2(r0v * gq[n][2 * hh], r1v * gq[n][2 * hh + 1]);
             }
     }
     __syncthreads();
@@ -211,7 +240,13 @@ __global__ void __launch_bounds__(256) gdn_scan_prepare_kernel(ScanParams p) {
         for (int t = 0; t < kC; ++t) {
             float acc = (t == tid) ? 1.f : 0.f;
 #pragma unroll
-            for (int sx = 0; sx < t; ++sx) acc = fmaf(-s.l[t][sx], x[sx], acc);   // x[sx] == 0 for sx < j
+            for (int s4 = 0; s4 < t; s4 += 4) {      // row t of L, four columns per (broadcast) load
+                const float4 lv = *reinterpret_cast<const float4 *>(&s.l[t][s4]);
+                acc = fmaf(-lv.x, x[s4], acc);                       // x[sx] == 0 for sx < j
+                if (s4 + 1 < t) acc = fmaf(-lv.y, x[s4 + 1], acc);
+                if (s4 + 2 < t) acc = fmaf(-lv.z, x[s4 + 2], acc);
+                if (s4 + 3 < t) acc = fmaf(-lv.w, x[s4 + 3], acc);
+            }
             x[t] = acc;
         }
         // column j of T diag(b) and T diag(b A), split into fp16 hi + lo
@@ -234,7 +269,7 @@ __global__ void __launch_bounds__(256) gdn_scan_prepare_kernel(ScanParams p) {
         for (int n = 0; n < 8; ++n)
 #pragma unroll
             for (int j = 0; j < 4; ++j) { u[n][j] = 0.f; w[n][j] = 0.f; }
-        const uint32_t vb = smem_u32(&s.v[0][0]), kb = smem_u32(&s.k[0][0]);
+        const uint32_t vb = smem_u32(&s.v[0][0][0]), kb = smem_u32(&s.k[0][0][0]);
         const uint32_t tbh = smem_u32(&s.tb_hi[0][0]), tbl = smem_u32(&s.tb_lo[0][0]);
         const uint32_t tah = smem_u32(&s.ta_hi[0][0]), tal = smem_u32(&s.ta_lo[0][0]);
 #pragma unroll
@@ -247,8 +282,8 @@ __global__ void __launch_bounds__(256) gdn_scan_prepare_kernel(ScanParams p) {
 #pragma unroll
             for (int np = 0; np < 4; ++np) {
                 uint32_t bv[4], bk[4];
-                ldsm_x4_t(bv, addr_bt(vb, kPitch, ks * 16, c0 + np * 16, lane));
-                ldsm_x4_t(bk, addr_bt(kb, kPitch, ks * 16, c0 + np * 16, lane));
+                ldsm_x4_t(bv, sw_bt(vb, ks * 16, c0 + np * 16, lane));
+                ldsm_x4_t(bk, sw_bt(kb, ks * 16, c0 + np * 16, lane));
                 mma16816(u[2 * np], abh, bv[0], bv[1]); mma16816(u[2 * np + 1], abh, bv[2], bv[3]);
                 mma16816(u[2 * np], abl, bv[0], bv[1]); mma16816(u[2 * np + 1], abl, bv[2], bv[3]);
                 mma16816(w[2 * np], aah, bk[0], bk[1]); mma16816(w[2 * np + 1], aah, bk[2], bk[3]);
@@ -274,8 +309,7 @@ __global__ void __launch_bounds__(256) gdn_scan_prepare_kernel(ScanParams p) {
 // columns 32tt..32tt+31 as accumulators (four warps alone left the SM's MMA issue mostly idle: one CTA
 // per SM, 6 % of the warp slots).
 // ---------------------------------------------------------------------------------------
-// Operand tiles arrive by TMA in the 128-byte swizzle: a [64 tokens][128] fp16 tile is two boxes of
-// [64][64] (8 KB each, 16-byte piece c of row r at (c ^ (r & 7)) << 4), U is one box of [64][32] fp32.
+// Two swizzled boxes per [64][128] fp16 tile; U is one box of [64][32] fp32.
 struct StateStage {
     __half q[2][kC][64];
     __half k[2][kC][64];
@@ -297,18 +331,6 @@ struct StateSmem {
     uint64_t full[kStages];        // one mbarrier per stage, completed by the copies' byte count
 };
 static_assert(sizeof(StateSmem) <= 227 * 1024, "state kernel shared memory");
-
-// Address of the 16-byte piece holding column `col` (a multiple of 8) of row `row` in a swizzled tile.
-__device__ __forceinline__ uint32_t sw_piece(uint32_t base, int row, int col) {
-    return base + ((col >> 6) << 13) + (row << 7) + ((((col >> 3) & 7) ^ (row & 7)) << 4);
-}
-// ldmatrix row addresses on swizzled tiles, lane roles as in addr_a / addr_bt
-__device__ __forceinline__ uint32_t sw_a(uint32_t base, int row0, int k0, int lane) {
-    return sw_piece(base, row0 + (lane & 15), k0 + (lane >> 4) * 8);
-}
-__device__ __forceinline__ uint32_t sw_bt(uint32_t base, int k0, int n0, int lane) {
-    return sw_piece(base, k0 + (lane & 7) + ((lane >> 3) & 1) * 8, n0 + (lane >> 4) * 8);
-}
 
 // Records seen as 2-D tensors: a record is 226 rows of 256 bytes (W), 452 rows of 128 bytes (M) or
 // 113 rows of 512 bytes (U), so one map per field covers the whole workspace.
@@ -551,7 +573,7 @@ TT_API int tt_gdn_scan_chunked(tt_context *ctx, tt_stream stream, const void *co
     for (uint32_t c0 = 0; c0 < total_chunks; c0 += seg_chunks) {
         p.token0 = c0 * kC;
         p.n_chunks = total_chunks - c0 < seg_chunks ? total_chunks - c0 : seg_chunks;
-        gdn_scan_prepare_kernel<<<dim3(p.n_chunks, p.hv), 256, sizeof(PrepSmem), (cudaStream_t)stream>>>(p);
+        gdn_scan_prepare_kernel<<<dim3(p.n_chunks, p.hv), 256, sizeof(PrepSmem), (cudaStream_t)stream>>>(p, conv_map);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn_scan_prepare launch");
         gdn_scan_state_kernel<<<dim3(kD / kDvb, p.hv), kStateThreads, sizeof(StateSmem), (cudaStream_t)stream>>>(
