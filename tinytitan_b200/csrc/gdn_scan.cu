@@ -24,12 +24,13 @@
 // be split over CTAs with no communication.
 #include "tt_sm100.h"
 
+#include <cstdlib>
+
 namespace {
 
 constexpr int kC = 64;          // tokens per chunk
 constexpr int kD = 128;         // Dk == Dv
 constexpr int kPitch = kD + 8;  // fp16 row pitch of [*][128] tiles (272 B: ldmatrix conflict-free)
-constexpr int kPitchC = kC + 8; // fp16 row pitch of [*][64] tiles (144 B)
 constexpr int kDvb = 32;        // state rows per CTA of the state kernel
 constexpr int kStateThreads = 256;   // 8 warps: (token tile / column group) x (half of the state rows)
 
@@ -64,9 +65,6 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 // ldmatrix addressing helpers for a row-major fp16 tile with `pitch` elements per row.
 // A operand (16 rows x 16 k) at (row0, k0); B operand for two n-tiles from a [n][k] tile
 // (k contiguous) at (n0, k0); transposed variants read [k][n] tiles (n contiguous).
-__device__ __forceinline__ uint32_t addr_a(uint32_t base, int pitch, int row0, int k0, int lane) {
-    return base + ((row0 + (lane & 15)) * pitch + k0 + (lane >> 4) * 8) * 2;
-}
 __device__ __forceinline__ uint32_t addr_b(uint32_t base, int pitch, int n0, int k0, int lane) {
     return base + ((n0 + (lane & 7) + ((lane >> 4) << 3)) * pitch + k0 + ((lane >> 3) & 1) * 8) * 2;
 }
@@ -118,17 +116,17 @@ struct ScanParams {
 // ---------------------------------------------------------------------------------------
 struct PrepSmem {
     __half k[2][kC][64];            // swizzled boxes, filled by TMA
-    __half q[2][kC][64];
     __half v[2][kC][64];
-    float l[kC][kC + 4];            // strictly lower triangle of L, then reused for T
-    __half tb_hi[kC][kPitchC], tb_lo[kC][kPitchC];   // T diag(b)      as fp16 hi + lo
-    __half ta_hi[kC][kPitchC], ta_lo[kC][kPitchC];   // T diag(b A)
+    __half q[2][kC][64];            // after the Gram phase: T diag(b) as fp16 hi (box 0) and lo (box 1)
+    float l[kC][kC + 4];            // strictly lower triangle of L; after the solve: T diag(b A), hi and lo
     float log_a[kC];                // cumulative log decay (inclusive)
     float beta[kC];
     uint64_t full;                  // completes when the three tiles have landed
 };
+static_assert(sizeof(float) * kC * (kC + 4) >= 2 * kC * 64 * sizeof(__half), "T diag(b A) reuses L");
+static_assert(3 * (sizeof(PrepSmem) + 1024) <= 228 * 1024, "three CTAs of the prepare kernel per SM");
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 gdn_scan_prepare_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_map) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     PrepSmem &s = *reinterpret_cast<PrepSmem *>(smem_raw);
@@ -234,8 +232,8 @@ gdn_scan_prepare_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_m
     __syncthreads();
 
     // ---- T = (I + L)^-1 by forward substitution: thread j owns column j in registers ----
+    float x[kC];
     if (tid < kC) {
-        float x[kC];
 #pragma unroll
         for (int t = 0; t < kC; ++t) {
             float acc = (t == tid) ? 1.f : 0.f;
@@ -249,14 +247,19 @@ gdn_scan_prepare_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_m
             }
             x[t] = acc;
         }
+    }
+    __syncthreads();   // every column is solved: L (and, since the Gram phase, Q) may be overwritten
+    __half *tb = &s.q[0][0][0], *ta = reinterpret_cast<__half *>(&s.l[0][0]);   // [hi, lo][64][64], swizzled
+    if (tid < kC) {
         // column j of T diag(b) and T diag(b A), split into fp16 hi + lo
         const float bj = s.beta[tid], baj = s.beta[tid] * expf(s.log_a[tid]);
 #pragma unroll
         for (int t = 0; t < kC; ++t) {
             const float vb = x[t] * bj, va = x[t] * baj;
             const __half hb = __float2half_rn(vb), ha = __float2half_rn(va);
-            s.tb_hi[t][tid] = hb; s.tb_lo[t][tid] = __float2half_rn(vb - __half2float(hb));
-            s.ta_hi[t][tid] = ha; s.ta_lo[t][tid] = __float2half_rn(va - __half2float(ha));
+            const int at = t * 64 + ((((tid >> 3) ^ (t & 7)) << 3) | (tid & 7));   // element (t, tid) of a swizzled box
+            tb[at] = hb; tb[kC * 64 + at] = __float2half_rn(vb - __half2float(hb));
+            ta[at] = ha; ta[kC * 64 + at] = __float2half_rn(va - __half2float(ha));
         }
     }
     __syncthreads();
@@ -270,15 +273,14 @@ gdn_scan_prepare_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_m
 #pragma unroll
             for (int j = 0; j < 4; ++j) { u[n][j] = 0.f; w[n][j] = 0.f; }
         const uint32_t vb = smem_u32(&s.v[0][0][0]), kb = smem_u32(&s.k[0][0][0]);
-        const uint32_t tbh = smem_u32(&s.tb_hi[0][0]), tbl = smem_u32(&s.tb_lo[0][0]);
-        const uint32_t tah = smem_u32(&s.ta_hi[0][0]), tal = smem_u32(&s.ta_lo[0][0]);
+        const uint32_t tbh = smem_u32(tb), tbl = tbh + kC * 64 * 2, tah = smem_u32(ta), tal = tah + kC * 64 * 2;
 #pragma unroll
         for (int ks = 0; ks < kC / 16; ++ks) {
             uint32_t abh[4], abl[4], aah[4], aal[4];
-            ldsm_x4(abh, addr_a(tbh, kPitchC, r0, ks * 16, lane));
-            ldsm_x4(abl, addr_a(tbl, kPitchC, r0, ks * 16, lane));
-            ldsm_x4(aah, addr_a(tah, kPitchC, r0, ks * 16, lane));
-            ldsm_x4(aal, addr_a(tal, kPitchC, r0, ks * 16, lane));
+            ldsm_x4(abh, sw_a(tbh, r0, ks * 16, lane));
+            ldsm_x4(abl, sw_a(tbl, r0, ks * 16, lane));
+            ldsm_x4(aah, sw_a(tah, r0, ks * 16, lane));
+            ldsm_x4(aal, sw_a(tal, r0, ks * 16, lane));
 #pragma unroll
             for (int np = 0; np < 4; ++np) {
                 uint32_t bv[4], bk[4];
@@ -513,6 +515,280 @@ gdn_scan_state_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_map
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Phase 2 on tcgen05. One CTA per (32 state rows, value head); chunks in order. The state slice is
+// kept TRANSPOSED in tensor memory as an fp32 accumulator (lane = state column, TMEM column = state
+// row) for the whole segment. Per chunk, three chains of MMAs (M = 128, N = 32):
+//   D1 = [Q; W] S_0^T          A: 128 token rows (Q rows 0-63, W rows 64-127) x 128, K-major
+//                              B: S_0^T as fp16 [128 columns][32 rows], N-major, rewritten every chunk
+//   D3 = a_C S_0^T + K^T Cw    A: K [64 tokens][128] read M-major; B: Cw [64 tokens][32 rows], N-major;
+//                              a_C S_0^T is put there beforehand by the threads that publish S_0
+//   D2 = M C                   A: M [64][64] K-major (rows 64-127 of the operand are whatever follows
+//                              it in shared memory; those accumulator lanes are never read)
+//                              B: C [64 tokens][32 rows], N-major
+// The N-major B operands are what a thread that owns one TMEM lane can write as whole 16-byte pieces
+// (its 32 values are 32 consecutive n). The recurrence is one dependent chain per chunk,
+//   publish S_0 -> D1 -> C = U - P -> D3 -> publish ...,
+// so everything else is kept off it: D2 is issued after D3, the next operands are requested after
+// D1 is under way, U is in registers before P arrives.
+// Warps 0-3 own the TMEM lanes (warp w lanes 32w..32w+31): all four publish S_0 and rescale the
+// accumulator; warps 0-1 (lanes = R rows) combine R and D2 into y, warps 2-3 (lanes = P rows) form
+// C = U - P. Warp 4, one lane, loads the operands by TMA and issues the MMAs. Every wait is bounded.
+// ---------------------------------------------------------------------------------------
+struct TcStage {
+    __half qw[2][2 * kC][64];      // per 64-column box: Q rows, then W rows
+    __half k[2][kC][64];
+    __half m[kC][64];
+    float u[kC][kDvb];             // directly after m (see D2 above)
+    float decay_a[kC];
+    float decay_w[kC];
+    unsigned char pad[512];
+};
+static_assert(sizeof(TcStage) % 1024 == 0, "stage tiles must stay 1024-byte aligned");
+constexpr int kTcStages = 3;
+constexpr int kTcThreads = 160;
+constexpr uint32_t kTcCols = 128, kColPR = 0, kColO = 32, kColS = 64;
+struct TcSmem {
+    TcStage stage[kTcStages];
+    __half s16[kD][64];            // S_0^T: row = state column, halves 0-31 = state rows (32-63 unused)
+    __half ccw[kC][64];            // row = token: halves 0-31 = C, 32-63 = diag(A_C/A_t) C
+    uint64_t full[kTcStages];      // operands of a chunk have landed
+    uint64_t s16_ready;            // 128 arrivals: S_0 published
+    uint64_t pr_done;              // D1 complete
+    uint64_t c_ready;              // 128 arrivals: accumulator rescaled (all), C and Cw written (warps 2-3)
+    uint64_t o_done;               // D2 complete
+    uint64_t s_done;               // D3 complete
+    uint32_t tmem_base;
+};
+static_assert(sizeof(TcSmem) + 1024 <= 227 * 1024, "tcgen05 state kernel shared memory");
+
+__device__ __forceinline__ void tc_issue_chunk(TcStage &st, uint64_t *bar, const ScanParams &p,
+                                               const CUtensorMap *conv_map, const CUtensorMap *w_map,
+                                               const CUtensorMap *m_map, const CUtensorMap *u_map, uint32_t chunk,
+                                               uint32_t h, uint32_t hk, uint32_t dv0) {
+    const int t0 = (int)(p.token0 + chunk * kC);      // rows past the sequence read as zeros
+    const uint32_t rec = chunk * p.hv + h;
+    const int xq = (int)(hk * kD), xk = (int)((p.hk + hk) * kD);
+    mbar_expect_tx(bar, kStageTxBytes);
+    tma_load_2d(&st.qw[0][0][0], conv_map, xq, t0, bar);
+    tma_load_2d(&st.qw[1][0][0], conv_map, xq + 64, t0, bar);
+    tma_load_2d(&st.qw[0][kC][0], w_map, 0, (int)(rec * kRecRowsW), bar);
+    tma_load_2d(&st.qw[1][kC][0], w_map, 64, (int)(rec * kRecRowsW), bar);
+    bulk_copy_g2s(&st.decay_a[0], &p.records[rec].decay_a[0], 2 * kC * 4, bar);
+    tma_load_2d(&st.u[0][0], u_map, (int)dv0, (int)(rec * kRecRowsU), bar);
+    tma_load_2d(&st.m[0][0], m_map, 0, (int)(rec * kRecRowsM), bar);
+    tma_load_2d(&st.k[0][0][0], conv_map, xk, t0, bar);
+    tma_load_2d(&st.k[1][0][0], conv_map, xk + 64, t0, bar);
+}
+
+__global__ void __launch_bounds__(kTcThreads)
+gdn_scan_state_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_map,
+                         const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap m_map,
+                         const __grid_constant__ CUtensorMap u_map, uint32_t idesc_kn, uint32_t idesc_mn) {
+    extern __shared__ __align__(1024) unsigned char tc_smem_raw[];
+    TcSmem &s = *reinterpret_cast<TcSmem *>(tc_smem_raw);
+    if ((smem_u32(tc_smem_raw) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicOr(p.status, TT_DEV_BAD_ITEM);
+        return;
+    }
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t h = blockIdx.y, dv0 = blockIdx.x * kDvb;
+    const uint32_t hk = (p.flags & TT_GDN_V_TILED) ? h % p.hk : h / (p.hv / p.hk);
+    float *state = p.state + ((size_t)h * kD + dv0) * kD;
+
+    if (tid == 4 * 32) {
+        for (int i = 0; i < kTcStages; ++i) mbar_init(&s.full[i], 1);
+        mbar_init(&s.s16_ready, 128);
+        mbar_init(&s.pr_done, 1);
+        mbar_init(&s.c_ready, 128);
+        mbar_init(&s.o_done, 1);
+        mbar_init(&s.s_done, 1);
+        mbar_fence_init();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (uint32_t c = 0; c < 2 && c < p.n_chunks; ++c)
+            tc_issue_chunk(s.stage[c], &s.full[c], p, &conv_map, &w_map, &m_map, &u_map, c, h, hk, dv0);
+    }
+    if (warp == 4) {
+        __syncwarp();
+        tmem_alloc(&s.tmem_base, kTcCols);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s.tmem_base;
+    bool ok = true;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            const uint32_t s16_a = smem_u32(&s.s16[0][0]), ccw_a = smem_u32(&s.ccw[0][0]);
+            for (uint32_t c = 0; c < p.n_chunks && ok; ++c) {
+                const uint32_t slot = c % kTcStages;
+                TcStage &st = s.stage[slot];
+                const uint32_t qw_a = smem_u32(&st.qw[0][0][0]), m_a = smem_u32(&st.m[0][0]),
+                               k_a = smem_u32(&st.k[0][0][0]);
+                ok = mbar_wait(&s.full[slot], (c / kTcStages) & 1) && mbar_wait(&s.s16_ready, c & 1);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < kD / 16; ++ks) {
+                    const uint64_t ad = make_desc(qw_a + (ks >> 2) * (2 * kC * 128) + (ks & 3) * 32, 16, 1024);
+                    const uint64_t bd = make_desc(s16_a + ks * 2048, kD * 128, 1024);
+                    mma_ss(tmem + kColPR, ad, bd, idesc_kn, ks > 0 ? 1u : 0u);
+                }
+                mma_commit(&s.pr_done);
+                // every consumer is past chunk c-1 (it published S_0 of chunk c): that stage may take chunk c+2
+                if (c + 2 < p.n_chunks) {
+                    const uint32_t nxt = (c + 2) % kTcStages;
+                    tc_issue_chunk(s.stage[nxt], &s.full[nxt], p, &conv_map, &w_map, &m_map, &u_map, c + 2, h, hk, dv0);
+                }
+                ok = mbar_wait(&s.c_ready, c & 1);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kC / 16; ++kk) {
+                    // K as the M-major operand: 64-column groups 8 KB apart (LBO), 8-token groups 1 KB apart (SBO)
+                    const uint64_t ad = make_desc(k_a + kk * 2048, kC * 128, 1024);
+                    const uint64_t bd = make_desc(ccw_a + kk * 2048 + 64, kC * 128, 1024);   // the Cw half of each row
+                    mma_ss(tmem + kColS, ad, bd, idesc_mn, 1u);
+                }
+                mma_commit(&s.s_done);
+#pragma unroll
+                for (int ks = 0; ks < kC / 16; ++ks) {
+                    const uint64_t ad = make_desc(m_a + ks * 32, 16, 1024);
+                    const uint64_t bd = make_desc(ccw_a + ks * 2048, kC * 128, 1024);
+                    mma_ss(tmem + kColO, ad, bd, idesc_kn, ks > 0 ? 1u : 0u);
+                }
+                mma_commit(&s.o_done);
+            }
+        }
+    } else {
+        const uint32_t i = warp * 32 + lane;                 // TMEM lane: state column, or operand row of D1 / D2
+        const uint32_t lane_addr = (warp * 32) << 16;
+        uint32_t sv[32];
+#pragma unroll
+        for (int r = 0; r < 32; ++r) sv[r] = __float_as_uint(state[(size_t)r * kD + i]);
+        unsigned char *s16_row = reinterpret_cast<unsigned char *>(&s.s16[i][0]);
+        const uint32_t t = i & 63;                           // token of this lane in D1 / D2
+        unsigned char *ccw_row = reinterpret_cast<unsigned char *>(&s.ccw[t][0]);
+        for (uint32_t c = 0; c < p.n_chunks; ++c) {
+            const uint32_t slot = c % kTcStages;
+            TcStage &st = s.stage[slot];
+            if (c > 0) {
+                ok = warp_all(mbar_wait(&s.s_done, (c - 1) & 1));
+                if (!ok) break;
+                tc_fence_after();
+                tmem_ld32(tmem + lane_addr + kColS, sv);
+                tmem_wait_ld();
+            }
+            // S_0^T row i: state rows 8j..8j+7 are the 16-byte piece j
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint4 v;
+                v.x = pack_h2(__uint_as_float(sv[8 * j]), __uint_as_float(sv[8 * j + 1]));
+                v.y = pack_h2(__uint_as_float(sv[8 * j + 2]), __uint_as_float(sv[8 * j + 3]));
+                v.z = pack_h2(__uint_as_float(sv[8 * j + 4]), __uint_as_float(sv[8 * j + 5]));
+                v.w = pack_h2(__uint_as_float(sv[8 * j + 6]), __uint_as_float(sv[8 * j + 7]));
+                *reinterpret_cast<uint4 *>(s16_row + ((j ^ (i & 7)) << 4)) = v;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(&s.s16_ready);
+
+            // off the chain: the accumulator becomes a_C S_0^T before D3 adds to it
+            ok = warp_all(mbar_wait(&s.full[slot], (c / kTcStages) & 1));
+            if (!ok) break;
+            const float a_c = st.decay_a[kC - 1];
+#pragma unroll
+            for (int r = 0; r < 32; ++r) sv[r] = __float_as_uint(__uint_as_float(sv[r]) * a_c);
+            tmem_st32(tmem + lane_addr + kColS, sv);
+            tmem_wait_st();
+            tc_fence_before();
+            float uu[32];
+            float wgt = 0.f, a_t = 0.f;
+            if (warp >= 2) {
+                wgt = st.decay_w[t];
+                const unsigned char *urow = reinterpret_cast<const unsigned char *>(&st.u[t][0]);
+#pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4) {
+                    const float4 u4 = *reinterpret_cast<const float4 *>(urow + ((q4 ^ (t & 7)) << 4));
+                    uu[4 * q4] = u4.x; uu[4 * q4 + 1] = u4.y; uu[4 * q4 + 2] = u4.z; uu[4 * q4 + 3] = u4.w;
+                }
+            } else {
+                a_t = st.decay_a[t];
+                mbar_arrive(&s.c_ready);
+            }
+
+            ok = warp_all(mbar_wait(&s.pr_done, c & 1));
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t pv[32];
+            tmem_ld32(tmem + lane_addr + kColPR, pv);
+            tmem_wait_ld();
+            if (warp >= 2) {
+                // P rows: C = U - P for token t; pieces 0-3 of the row are C, pieces 4-7 are Cw
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float cv[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) cv[e] = uu[8 * j + e] - __uint_as_float(pv[8 * j + e]);
+                    uint4 v, w;
+                    v.x = pack_h2(cv[0], cv[1]); v.y = pack_h2(cv[2], cv[3]);
+                    v.z = pack_h2(cv[4], cv[5]); v.w = pack_h2(cv[6], cv[7]);
+                    w.x = pack_h2(cv[0] * wgt, cv[1] * wgt); w.y = pack_h2(cv[2] * wgt, cv[3] * wgt);
+                    w.z = pack_h2(cv[4] * wgt, cv[5] * wgt); w.w = pack_h2(cv[6] * wgt, cv[7] * wgt);
+                    *reinterpret_cast<uint4 *>(ccw_row + ((j ^ (t & 7)) << 4)) = v;
+                    *reinterpret_cast<uint4 *>(ccw_row + (((j + 4) ^ (t & 7)) << 4)) = w;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                tc_fence_before();
+                mbar_arrive(&s.c_ready);
+            } else {
+                // R rows: y_t = readout_scale (A_t R_t + (M C)_t)
+                ok = warp_all(mbar_wait(&s.o_done, c & 1));
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t ov[32];
+                tmem_ld32(tmem + lane_addr + kColO, ov);
+                tmem_wait_ld();
+                const uint32_t tok = p.token0 + c * kC + t;
+                if (tok < p.rows) {
+                    uint4 *dst = reinterpret_cast<uint4 *>(p.y + (size_t)tok * p.hv * kD + (size_t)h * kD + dv0);
+#pragma unroll
+                    for (int q8 = 0; q8 < 4; ++q8) {
+                        uint32_t w4[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int r = q8 * 8 + e * 2;
+                            const float o0 = fmaf(__uint_as_float(pv[r]), a_t, __uint_as_float(ov[r]));
+                            const float o1 = fmaf(__uint_as_float(pv[r + 1]), a_t, __uint_as_float(ov[r + 1]));
+                            w4[e] = pack_h2(o0 * p.readout_scale, o1 * p.readout_scale);
+                        }
+                        dst[q8] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                    }
+                }
+            }
+        }
+        if (ok) {
+            ok = warp_all(mbar_wait(&s.s_done, (p.n_chunks - 1) & 1));
+            if (ok) {
+                tc_fence_after();
+                tmem_ld32(tmem + lane_addr + kColS, sv);
+                tmem_wait_ld();
+#pragma unroll
+                for (int r = 0; r < 32; ++r) state[(size_t)r * kD + i] = __uint_as_float(sv[r]);
+            }
+        }
+    }
+
+    if (!ok) atomicOr(p.status, TT_DEV_WAIT_TIMEOUT);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem, kTcCols);
+    }
+}
+
 }  // namespace
 
 TT_API int tt_gdn_scan_chunked(tt_context *ctx, tt_stream stream, const void *conv_out, const void *a,
@@ -547,6 +823,9 @@ TT_API int tt_gdn_scan_chunked(tt_context *ctx, tt_stream stream, const void *co
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(gdn_scan_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)sizeof(StateSmem));
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gdn_scan_state_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)sizeof(TcSmem));
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn scan smem attribute");
         attrs_set = true;
     }
@@ -569,6 +848,15 @@ TT_API int tt_gdn_scan_chunked(tt_context *ctx, tt_stream stream, const void *co
     p.hk = shape->n_k_heads; p.hv = shape->n_v_heads; p.rows = rows; p.row_stride = row_stride; p.flags = shape->flags;
     p.readout_scale = shape->readout_scale;
     p.status = ctx->status;
+    // TT_GDN_SCAN_FORCE_MMA_SYNC=1 keeps the state recurrence on the mma.sync kernel (an A/B switch for tests)
+    static const bool use_mma_sync = [] {
+        const char *e = getenv("TT_GDN_SCAN_FORCE_MMA_SYNC");
+        return e != nullptr && e[0] == '1';
+    }();
+    if (!use_mma_sync && ((uintptr_t)y & 15))
+        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "chunked scan needs a 16-byte aligned output");
+    const uint32_t idesc_kn = tt_make_idesc_f16(TT_F16, kDvb, true, false);   // A K-major, B N-major
+    const uint32_t idesc_mn = tt_make_idesc_f16(TT_F16, kDvb, true, true);    // A M-major, B N-major
     const uint32_t total_chunks = (rows + kC - 1) / kC;
     for (uint32_t c0 = 0; c0 < total_chunks; c0 += seg_chunks) {
         p.token0 = c0 * kC;
@@ -576,8 +864,12 @@ TT_API int tt_gdn_scan_chunked(tt_context *ctx, tt_stream stream, const void *co
         gdn_scan_prepare_kernel<<<dim3(p.n_chunks, p.hv), 256, sizeof(PrepSmem), (cudaStream_t)stream>>>(p, conv_map);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn_scan_prepare launch");
-        gdn_scan_state_kernel<<<dim3(kD / kDvb, p.hv), kStateThreads, sizeof(StateSmem), (cudaStream_t)stream>>>(
-            p, conv_map, w_map, m_map, u_map);
+        if (use_mma_sync)
+            gdn_scan_state_kernel<<<dim3(kD / kDvb, p.hv), kStateThreads, sizeof(StateSmem), (cudaStream_t)stream>>>(
+                p, conv_map, w_map, m_map, u_map);
+        else
+            gdn_scan_state_tc_kernel<<<dim3(kD / kDvb, p.hv), kTcThreads, sizeof(TcSmem), (cudaStream_t)stream>>>(
+                p, conv_map, w_map, m_map, u_map, idesc_kn, idesc_mn);
         e = cudaGetLastError();
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn_scan_state launch");
         ctx->launches += 2;
