@@ -849,10 +849,8 @@ TT_API int tt_gdn_scan_chunked(tt_context *ctx, tt_stream stream, const void *co
     p.readout_scale = shape->readout_scale;
     p.status = ctx->status;
     // TT_GDN_SCAN_FORCE_MMA_SYNC=1 keeps the state recurrence on the mma.sync kernel (an A/B switch for tests)
-    static const bool use_mma_sync = [] {
-        const char *e = getenv("TT_GDN_SCAN_FORCE_MMA_SYNC");
-        return e != nullptr && e[0] == '1';
-    }();
+    const char *force = getenv("TT_GDN_SCAN_FORCE_MMA_SYNC");
+    const bool use_mma_sync = force != nullptr && force[0] == '1';
     if (!use_mma_sync && ((uintptr_t)y & 15))
         return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "chunked scan needs a 16-byte aligned output");
     const uint32_t idesc_kn = tt_make_idesc_f16(TT_F16, kDvb, true, false);   // A K-major, B N-major
