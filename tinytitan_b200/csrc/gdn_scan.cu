@@ -94,6 +94,24 @@ __device__ __forceinline__ uint32_t sw_bt(uint32_t base, int k0, int n0, int lan
     return sw_piece(base, k0 + (lane & 7) + ((lane >> 3) & 1) * 8, n0 + (lane >> 4) * 8);
 }
 
+// Records seen as 2-D tensors: a record is 226 rows of 256 bytes (W), 452 rows of 128 bytes (M) or
+// 113 rows of 512 bytes (U), so one map per field covers the whole workspace.
+static_assert(sizeof(ChunkRecord) % 512 == 0, "record rows");
+constexpr uint32_t kRecRowsW = sizeof(ChunkRecord) / 256, kRecRowsM = sizeof(ChunkRecord) / 128,
+                   kRecRowsU = sizeof(ChunkRecord) / 512;
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, const void *src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(smem_u32(src))
+                 : "memory");
+}
+// Ends the group of stores issued so far and waits until their sources have been read (the writes
+// themselves are complete by the end of the grid).
+__device__ __forceinline__ void bulk_commit_and_wait_read() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
 struct ScanParams {
     const __half *conv_out;
     const void *a;
@@ -127,7 +145,8 @@ static_assert(sizeof(float) * kC * (kC + 4) >= 2 * kC * 64 * sizeof(__half), "T 
 static_assert(3 * (sizeof(PrepSmem) + 1024) <= 228 * 1024, "three CTAs of the prepare kernel per SM");
 
 __global__ void __launch_bounds__(256, 3)
-gdn_scan_prepare_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_map) {
+gdn_scan_prepare_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_map,
+                        const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap u_map) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     PrepSmem &s = *reinterpret_cast<PrepSmem *>(smem_raw);
     if ((smem_u32(smem_raw) & 1023u) != 0) {   // the swizzled tiles need the alignment the attribute asks for
@@ -292,14 +311,36 @@ gdn_scan_prepare_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_m
                 mma16816(w[2 * np], aal, bk[0], bk[1]); mma16816(w[2 * np + 1], aal, bk[2], bk[3]);
             }
         }
+        // U and W leave through shared memory as the swizzled boxes the state kernel will load (U: four
+        // boxes of [64][32 floats] over the K and V tiles, W: two of [64][64 halves] over the T operands)
+        // and six TMA tensor stores: whole lines instead of 8- and 4-byte fragment stores from every lane.
+        __syncthreads();   // every warp is done with K, V and the T operands
+        unsigned char *ust = reinterpret_cast<unsigned char *>(&s.k[0][0][0]);
+        unsigned char *wst = reinterpret_cast<unsigned char *>(&s.q[0][0][0]);
+        static_assert(sizeof(s.k) + sizeof(s.v) == sizeof(float) * kC * kD && sizeof(s.q) == sizeof(__half) * kC * kD,
+                      "staging areas");
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
             const int col = c0 + n * 8 + (lane & 3) * 2;
-            const int ra = r0 + (lane >> 2), rb = ra + 8;
-            *reinterpret_cast<float2 *>(&rec.u[ra][col]) = make_float2(u[n][0], u[n][1]);
-            *reinterpret_cast<float2 *>(&rec.u[rb][col]) = make_float2(u[n][2], u[n][3]);
-            *reinterpret_cast<uint32_t *>(&rec.w[ra][col]) = pack_h2(w[n][0], w[n][1]);
-            *reinterpret_cast<uint32_t *>(&rec.w[rb][col]) = pack_h2(w[n][2], w[n][3]);
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int r = r0 + (lane >> 2) + hh * 8;
+                *reinterpret_cast<float2 *>(ust + (col >> 5) * (kC * 128) + r * 128 + ((((col & 31) >> 2) ^ (r & 7)) << 4) +
+                                            (col & 3) * 4) = make_float2(u[n][2 * hh], u[n][2 * hh + 1]);
+                *reinterpret_cast<uint32_t *>(wst + (col >> 6) * (kC * 128) + r * 128 + ((((col & 63) >> 3) ^ (r & 7)) << 4) +
+                                              (col & 7) * 2) = pack_h2(w[n][2 * hh], w[n][2 * hh + 1]);
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+        if (tid == 0) {
+            const uint32_t rec_index = chunk * p.hv + h;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+                tma_store_2d(&u_map, 32 * q4, (int)(rec_index * kRecRowsU), ust + q4 * (kC * 128));
+            tma_store_2d(&w_map, 0, (int)(rec_index * kRecRowsW), wst);
+            tma_store_2d(&w_map, 64, (int)(rec_index * kRecRowsW), wst + kC * 128);
+            bulk_commit_and_wait_read();
         }
     }
 }
@@ -333,12 +374,6 @@ struct StateSmem {
     uint64_t full[kStages];        // one mbarrier per stage, completed by the copies' byte count
 };
 static_assert(sizeof(StateSmem) <= 227 * 1024, "state kernel shared memory");
-
-// Records seen as 2-D tensors: a record is 226 rows of 256 bytes (W), 452 rows of 128 bytes (M) or
-// 113 rows of 512 bytes (U), so one map per field covers the whole workspace.
-static_assert(sizeof(ChunkRecord) % 512 == 0, "record rows");
-constexpr uint32_t kRecRowsW = sizeof(ChunkRecord) / 256, kRecRowsM = sizeof(ChunkRecord) / 128,
-                   kRecRowsU = sizeof(ChunkRecord) / 512;
 
 // One thread issues the ten copies of a chunk; they complete on the stage's mbarrier.
 __device__ __forceinline__ void state_issue_chunk(StateStage &st, uint64_t *bar, const ScanParams &p,
@@ -859,7 +894,8 @@ TT_API int tt_gdn_scan_chunked(tt_context *ctx, tt_stream stream, const void *co
     for (uint32_t c0 = 0; c0 < total_chunks; c0 += seg_chunks) {
         p.token0 = c0 * kC;
         p.n_chunks = total_chunks - c0 < seg_chunks ? total_chunks - c0 : seg_chunks;
-        gdn_scan_prepare_kernel<<<dim3(p.n_chunks, p.hv), 256, sizeof(PrepSmem), (cudaStream_t)stream>>>(p, conv_map);
+        gdn_scan_prepare_kernel<<<dim3(p.n_chunks, p.hv), 256, sizeof(PrepSmem), (cudaStream_t)stream>>>(
+            p, conv_map, w_map, u_map);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn_scan_prepare launch");
         if (use_mma_sync)
