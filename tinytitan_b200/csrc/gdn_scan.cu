@@ -241,8 +241,8 @@ gdn_scan_prepare_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_m
                 const int sx = c0 + n * 8 + (lane & 3) * 2;      // this thread holds columns sx, sx + 1
                 const float la_t = s.log_a[t], be_t = s.beta[t];
                 const float2 la_s = *reinterpret_cast<const float2 *>(&s.log_a[sx]);
-                const float r0v = sx <= t ? expf(la_t - la_s.x) : 0.f;
-                const float r1v = sx + 1 <= t ? expf(la_t - la_s.y) : 0.f;
+                const float r0v = sx <= t ? __expf(la_t - la_s.x) : 0.f;
+                const float r1v = sx + 1 <= t ? __expf(la_t - la_s.y) : 0.f;
                 *reinterpret_cast<float2 *>(&s.l[t][sx]) =
                     make_float2(sx < t ? be_t * r0v * gk[n][2 * hh] : 0.f, sx + 1 < t ? be_t * r1v * gk[n][2 * hh + 1] : 0.f);
                 *reinterpret_cast<uint32_t *>(&rec.m[t][sx]) = pack_h2(r0v * gq[n][2 * hh], r1v * gq[n][2 * hh + 1]);
