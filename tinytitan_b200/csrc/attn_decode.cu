@@ -677,7 +677,7 @@ attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions, const f
     // merges parts g, g+G, ... so that a long session's hundreds of parts are read with many loads
     // in flight instead of one after another. Batches with many (session, row) pairs use one CTA per
     // row (64 column threads, G = 4); a few long sessions split the columns over gridDim.z CTAs
-    // (16 column threads, G = 16) so that the merge still fills the machine.
+    // (down to 8 column threads, G = 32) so that the merge still fills the machine.
     __shared__ float red[16];
     __shared__ float4 accs[256];
     const TTDecodeSession ses = use_single ? single : sessions[blockIdx.x];
@@ -1241,7 +1241,9 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
                                         p->n_q_heads, p->head_dim, p->io_dtype);
 
     // few (session, row) pairs: split the row's columns over several CTAs so the merge fills the GPU
-    const uint32_t col_threads = (uint64_t)n_sessions * max_rows * 2 <= (uint64_t)ctx->sm_count ? 16u : 64u;
+    uint32_t col_threads = 64;
+    while (col_threads > 8 && (uint64_t)n_sessions * max_rows * (64 / col_threads) * 2 <= (uint64_t)ctx->sm_count)
+        col_threads /= 2;
     const dim3 grid(n_sessions, max_rows, (p->head_dim / 4 + col_threads - 1) / col_threads);
     const uint32_t threads = 256;
     if (p->io_dtype == TT_F16)
