@@ -678,7 +678,10 @@ attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions, const f
     // in flight instead of one after another. Batches with many (session, row) pairs use one CTA per
     // row (64 column threads, G = 4); a few long sessions split the columns over gridDim.z CTAs
     // (down to 8 column threads, G = 32) so that the merge still fills the machine.
-    __shared__ float red[16];
+    // One pass: every group keeps an online (max, sum, output) triple over its parts and the groups'
+    // triples are merged at the end, so no block-wide reduction over the parts' maxima and sums has
+    // to finish before the first output load is issued.
+    __shared__ float grp_m[32], grp_d[32];
     __shared__ float4 accs[256];
     const TTDecodeSession ses = use_single ? single : sessions[blockIdx.x];
     const uint32_t rows_total = ses.q_rows * n_q_heads;
@@ -686,65 +689,65 @@ attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions, const f
     if (rho >= rows_total) return;
     const uint32_t n_parts = ses.n_parts;
     const size_t base = (size_t)ses.partial_base + rho;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t grp = threadIdx.x / col_threads, ct = threadIdx.x % col_threads;
     const uint32_t n_groups = 256 / col_threads;
-
-    float mg = -INFINITY;
-    for (uint32_t c = threadIdx.x; c < n_parts; c += 256) mg = fmaxf(mg, part_m[base + (size_t)c * rows_total]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
-    if (lane == 0) red[warp] = mg;
-    __syncthreads();
-    mg = red[0];
-#pragma unroll
-    for (int i = 1; i < 8; ++i) mg = fmaxf(mg, red[i]);
-    float D = 0.f;
-    if (mg != -INFINITY)
-        for (uint32_t c = threadIdx.x; c < n_parts; c += 256) {
-            const size_t pr = base + (size_t)c * rows_total;
-            D += part_l[pr] * __expf(part_m[pr] - mg);
-        }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) D += __shfl_xor_sync(0xffffffffu, D, o);
-    if (lane == 0) red[8 + warp] = D;
-    __syncthreads();
-    D = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) D += red[8 + i];
-
     const uint32_t col = (blockIdx.z * col_threads + ct) * 4;
+
+    float m_run = -INFINITY, d_run = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (mg != -INFINITY && col < head_dim) {
+    if (col < head_dim) {
         uint32_t c = grp;
         for (; c + 3 * n_groups < n_parts; c += 4 * n_groups) {   // four independent loads in flight per thread
-            float e[4]; float4 o[4];
+            float e[4], l[4]; float4 o[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const size_t pr = base + (size_t)(c + n_groups * u) * rows_total;
                 e[u] = part_m[pr];
+                l[u] = part_l[pr];
                 o[u] = *reinterpret_cast<const float4 *>(part_o + pr * head_dim + col);
             }
+            const float m_new = fmaxf(m_run, fmaxf(fmaxf(e[0], e[1]), fmaxf(e[2], e[3])));
+            if (m_new != -INFINITY) {                              // exp(-inf - -inf) would be NaN
+                const float sc = __expf(m_run - m_new);            // 0 for the first finite maximum
+                acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc; d_run *= sc;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float wgt = __expf(e[u] - mg);
-                acc.x += o[u].x * wgt; acc.y += o[u].y * wgt; acc.z += o[u].z * wgt; acc.w += o[u].w * wgt;
+                for (int u = 0; u < 4; ++u) {
+                    const float wgt = __expf(e[u] - m_new);
+                    acc.x += o[u].x * wgt; acc.y += o[u].y * wgt; acc.z += o[u].z * wgt; acc.w += o[u].w * wgt;
+                    d_run += l[u] * wgt;
+                }
+                m_run = m_new;
             }
         }
         for (; c < n_parts; c += n_groups) {
             const size_t pr = base + (size_t)c * rows_total;
-            const float wgt = __expf(part_m[pr] - mg);
+            const float e = part_m[pr], l = part_l[pr];
             const float4 o = *reinterpret_cast<const float4 *>(part_o + pr * head_dim + col);
-            acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
+            const float m_new = fmaxf(m_run, e);
+            if (m_new != -INFINITY) {
+                const float sc = __expf(m_run - m_new), wgt = __expf(e - m_new);
+                acc.x = acc.x * sc + o.x * wgt; acc.y = acc.y * sc + o.y * wgt;
+                acc.z = acc.z * sc + o.z * wgt; acc.w = acc.w * sc + o.w * wgt;
+                d_run = d_run * sc + l * wgt;
+                m_run = m_new;
+            }
         }
     }
     accs[grp * col_threads + ct] = acc;
+    if (ct == 0) { grp_m[grp] = m_run; grp_d[grp] = d_run; }
     __syncthreads();
     if (grp != 0 || col >= head_dim) return;
-    for (uint32_t g = 1; g < n_groups; ++g) {
-        const float4 o = accs[g * col_threads + ct];
-        acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
-    }
+    float mg = grp_m[0];
+    for (uint32_t g = 1; g < n_groups; ++g) mg = fmaxf(mg, grp_m[g]);
+    float D = 0.f;
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (mg != -INFINITY)
+        for (uint32_t g = 0; g < n_groups; ++g) {
+            const float wgt = __expf(grp_m[g] - mg);              // 0 for a group that saw no finite maximum
+            const float4 o = accs[g * col_threads + ct];
+            acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
+            D += grp_d[g] * wgt;
+        }
     const uint32_t w = rho / n_q_heads, h = rho % n_q_heads;
     if (mode == 0) {
         const float inv = D > 0.f ? 1.f / D : 0.f;
