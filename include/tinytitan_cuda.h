@@ -51,7 +51,7 @@ enum tt_dtype { TT_F16 = 0, TT_BF16 = 1 };
 /* ---------------------------------------------------------------- context */
 
 typedef struct tt_context_options {
-    size_t workspace_bytes; /* split-KV partials; 0 selects 192 MiB */
+    size_t workspace_bytes; /* split-KV partials, scan records; 0 selects 256 MiB */
     uint32_t max_sessions;  /* rows of one batched call; 0 selects 1024 */
     uint32_t reserved;
 } tt_context_options;

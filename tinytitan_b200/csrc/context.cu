@@ -87,7 +87,7 @@ TT_API tt_context *tt_context_create(int device, const tt_context_options *optio
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
     ctx->smem_optin = prop.sharedMemPerBlockOptin;
-    ctx->workspace_bytes = (options && options->workspace_bytes) ? options->workspace_bytes : ((size_t)192 << 20);
+    ctx->workspace_bytes = (options && options->workspace_bytes) ? options->workspace_bytes : ((size_t)256 << 20);
     ctx->max_sessions = (options && options->max_sessions) ? options->max_sessions : 1024u;
     ctx->max_items = 65536u;
 
