@@ -52,10 +52,43 @@ __device__ __forceinline__ float4 half4_to_float4(const uint2 &raw) {
     const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
     return make_float4(lo.x, lo.y, hi.x, hi.y);
 }
-__device__ __forceinline__ float dot4(const float4 &s, const float4 &k, float acc) {
-    acc = fmaf(s.x, k.x, acc); acc = fmaf(s.y, k.y, acc);
-    acc = fmaf(s.z, k.z, acc); acc = fmaf(s.w, k.w, acc);
-    return acc;
+// Packed fp32 pairs (sm_100's fma/mul .f32x2: two IEEE operations per issued instruction). With
+// several tokens per state read this kernel is bound by instruction issue, and three quarters of
+// its instructions are these multiply-adds.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "mul.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+__device__ __forceinline__ void scale4(float4 &s, float2 gg) {
+    const float2 lo = mul2(make_float2(s.x, s.y), gg), hi = mul2(make_float2(s.z, s.w), gg);
+    s = make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+// s += k * d (d broadcast in both halves of dd)
+__device__ __forceinline__ void axpy4(float4 &s, const float4 &k, float2 dd) {
+    const float2 lo = fma2(make_float2(k.x, k.y), dd, make_float2(s.x, s.y));
+    const float2 hi = fma2(make_float2(k.z, k.w), dd, make_float2(s.z, s.w));
+    s = make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+// two partial sums per dot product (even and odd elements); the caller adds them
+__device__ __forceinline__ float2 dot4(const float4 &s, const float4 &k, float2 acc) {
+    acc = fma2(make_float2(s.x, s.y), make_float2(k.x, k.y), acc);
+    return fma2(make_float2(s.z, s.w), make_float2(k.z, k.w), acc);
 }
 
 // exp(x) in about 8 instructions, ~2 ulp: the product x*log2(e) is carried as hi + lo so that
@@ -270,32 +303,33 @@ gdn_step_kernel(GdnParams p, uint32_t n_sessions, uint32_t n_items, uint32_t *__
 
             // decay, then S.k for both rows
             float4 k4[C];
-            float ka = 0.f, kb = 0.f;
+            float2 ka2 = make_float2(0.f, 0.f), kb2 = make_float2(0.f, 0.f);
+            const float2 gg = make_float2(g, g);
 #pragma unroll
             for (int j = 0; j < C; ++j) {
                 k4[j] = half4_to_float4(*reinterpret_cast<const uint2 *>(ks + 32 * j));
-                sa[j].x *= g; sa[j].y *= g; sa[j].z *= g; sa[j].w *= g;
-                sb[j].x *= g; sb[j].y *= g; sb[j].z *= g; sb[j].w *= g;
-                ka = dot4(sa[j], k4[j], ka);
-                kb = dot4(sb[j], k4[j], kb);
+                scale4(sa[j], gg);
+                scale4(sb[j], gg);
+                ka2 = dot4(sa[j], k4[j], ka2);
+                kb2 = dot4(sb[j], k4[j], kb2);
             }
-            const float mine = group_sum2(ka, kb, upper);
+            const float mine = group_sum2(ka2.x + ka2.y, kb2.x + kb2.y, upper);
             const float other = __shfl_xor_sync(0xffffffffu, mine, 4);
             const float da = (vv.x - (upper ? other : mine)) * beta;
             const float db = (vv.y - (upper ? mine : other)) * beta;
 
             // rank-one update, then the readout S.q
-            float ya = 0.f, yb = 0.f;
+            float2 ya2 = make_float2(0.f, 0.f), yb2 = make_float2(0.f, 0.f);
+            const float2 dda = make_float2(da, da), ddb = make_float2(db, db);
 #pragma unroll
             for (int j = 0; j < C; ++j) {
                 const float4 q4 = half4_to_float4(*reinterpret_cast<const uint2 *>(qs + 32 * j));
-                sa[j].x = fmaf(k4[j].x, da, sa[j].x); sa[j].y = fmaf(k4[j].y, da, sa[j].y);
-                sa[j].z = fmaf(k4[j].z, da, sa[j].z); sa[j].w = fmaf(k4[j].w, da, sa[j].w);
-                sb[j].x = fmaf(k4[j].x, db, sb[j].x); sb[j].y = fmaf(k4[j].y, db, sb[j].y);
-                sb[j].z = fmaf(k4[j].z, db, sb[j].z); sb[j].w = fmaf(k4[j].w, db, sb[j].w);
-                ya = dot4(sa[j], q4, ya);
-                yb = dot4(sb[j], q4, yb);
+                axpy4(sa[j], k4[j], dda);
+                axpy4(sb[j], k4[j], ddb);
+                ya2 = dot4(sa[j], q4, ya2);
+                yb2 = dot4(sb[j], q4, yb2);
             }
+            const float ya = ya2.x + ya2.y, yb = yb2.x + yb2.y;
             __syncwarp();                       // every lane has read the entry: it may be refilled
             prefetch(pair + kTokDepth);
 
