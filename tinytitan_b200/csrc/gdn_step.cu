@@ -52,29 +52,6 @@ __device__ __forceinline__ float4 half4_to_float4(const uint2 &raw) {
     const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
     return make_float4(lo.x, lo.y, hi.x, hi.y);
 }
-// Packed fp32 pairs (sm_100's fma/mul .f32x2: two IEEE operations per issued instruction). With
-// several tokens per state read this kernel is bound by instruction issue, and three quarters of
-// its instructions are these multiply-adds.
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-    float2 d;
-    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
-        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
-        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
-        "mov.b64 {%0, %1}, rd;\n\t}"
-        : "=f"(d.x), "=f"(d.y)
-        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-    return d;
-}
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
-    float2 d;
-    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
-        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-        "mul.rn.f32x2 rd, ra, rb;\n\t"
-        "mov.b64 {%0, %1}, rd;\n\t}"
-        : "=f"(d.x), "=f"(d.y)
-        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-    return d;
-}
 __device__ __forceinline__ void scale4(float4 &s, float2 gg) {
     const float2 lo = mul2(make_float2(s.x, s.y), gg), hi = mul2(make_float2(s.z, s.w), gg);
     s = make_float4(lo.x, lo.y, hi.x, hi.y);
