@@ -97,6 +97,24 @@ def test_sliding_window_ring_and_keep_mask():
     assert np.all(got == 0)
 
 
+def test_long_session_merge_with_empty_parts():
+    # One long session, two rows: the merge pass splits the row's columns over several CTAs and walks
+    # hundreds of parts in groups, each group keeping an online (max, sum, output) triple. The keep mask
+    # leaves long stretches without any key, so whole parts (the first ones of most groups among them)
+    # arrive with a maximum of -inf and a zero sum, and must neither produce NaN nor weigh in.
+    r = np.random.default_rng(41)
+    hd, hq, hkv, s = 128, 2, 1, 60000
+    q = rounded(r.normal(size=(hq, hd))); k = rounded(r.normal(size=(s, hkv, hd))); v = rounded(r.normal(size=(s, hkv, hd)))
+    keep = np.zeros(s, np.uint8)
+    keep[20000:20300] = 1; keep[41000:41007] = 1; keep[59990:] = 1
+    keep[r.integers(30000, 36000, size=40)] = 1
+    want = oracle.attn_decode_split(q, k, v, hkv, 0.09, s, keep=keep)
+    launches = context().launch_count
+    got = _decode(q, k, v, hkv, scale=0.09, keep_mask=torch.as_tensor(keep).cuda())
+    assert context().launch_count - launches == 2
+    assert np.isfinite(got).all() and np.abs(got - want).max() <= TOL
+
+
 def _batched_case(r, n, hq, hkv, hd, lens, q_rows, dtype=torch.float16, stride_pad=0):
     """Sessions packed into one KV store of the reference layout: slot s at row s*capacity."""
     cap = max(lens) + 8
