@@ -147,63 +147,70 @@ template <typename T>
 __global__ void __launch_bounds__(256) attn_merge_exchange_kernel(ExchangeParams p, T *__restrict__ out,
                                                                  uint32_t *__restrict__ status) {
     __shared__ int all_arrived;
-    __shared__ float red[16];
+    __shared__ float grp_m[16], grp_d[16];
     __shared__ float4 accs[256];
     const uint32_t h = blockIdx.x, cb = blockIdx.y, tid = threadIdx.x;
-    const uint32_t lane = tid & 31, warp = tid >> 5, grp = tid >> 4, ct = tid & 15;
+    const uint32_t grp = tid >> 4, ct = tid & 15;
     const uint32_t H = p.n_q_heads;
-
-    float mg = -INFINITY;
-    for (uint32_t c = tid; c < p.n_parts; c += 256) mg = fmaxf(mg, p.part_m[(size_t)c * H + h]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
-    if (lane == 0) red[warp] = mg;
-    __syncthreads();
-    mg = red[0];
-#pragma unroll
-    for (int i = 1; i < 8; ++i) mg = fmaxf(mg, red[i]);
-    float D = 0.f;
-    if (mg != -INFINITY)
-        for (uint32_t c = tid; c < p.n_parts; c += 256) D += p.part_l[(size_t)c * H + h] * __expf(p.part_m[(size_t)c * H + h] - mg);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) D += __shfl_xor_sync(0xffffffffu, D, o);
-    if (lane == 0) red[8 + warp] = D;
-    __syncthreads();
-    D = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) D += red[8 + i];
-
     const uint32_t col = cb * kColBlock + ct * 4;
+
+    // One pass over this rank's parts: group g (16 column threads) walks parts g, g+16, ... four loads at
+    // a time with an online (max, sum, output) triple; the 16 triples are merged below. Nothing
+    // block-wide has to finish before the first load is issued.
+    float m_run = -INFINITY, d_run = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (mg != -INFINITY && col < p.head_dim) {
+    if (col < p.head_dim) {
         uint32_t c = grp;
-        for (; c + 48 < p.n_parts; c += 64) {   // four independent loads in flight per thread
-            float e[4]; float4 o[4];
+        for (; c + 48 < p.n_parts; c += 64) {
+            float e[4], l[4]; float4 o[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const size_t pr = (size_t)(c + 16 * u) * H + h;
                 e[u] = p.part_m[pr];
+                l[u] = p.part_l[pr];
                 o[u] = *reinterpret_cast<const float4 *>(p.part_o + pr * p.head_dim + col);
             }
+            const float m_new = fmaxf(m_run, fmaxf(fmaxf(e[0], e[1]), fmaxf(e[2], e[3])));
+            if (m_new != -INFINITY) {                              // exp(-inf - -inf) would be NaN
+                const float sc = __expf(m_run - m_new);
+                acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc; d_run *= sc;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float wgt = __expf(e[u] - mg);
-                acc.x += o[u].x * wgt; acc.y += o[u].y * wgt; acc.z += o[u].z * wgt; acc.w += o[u].w * wgt;
+                for (int u = 0; u < 4; ++u) {
+                    const float wgt = __expf(e[u] - m_new);
+                    acc.x += o[u].x * wgt; acc.y += o[u].y * wgt; acc.z += o[u].z * wgt; acc.w += o[u].w * wgt;
+                    d_run += l[u] * wgt;
+                }
+                m_run = m_new;
             }
         }
         for (; c < p.n_parts; c += 16) {
             const size_t pr = (size_t)c * H + h;
-            const float wgt = __expf(p.part_m[pr] - mg);
+            const float e = p.part_m[pr], l = p.part_l[pr];
             const float4 o = *reinterpret_cast<const float4 *>(p.part_o + pr * p.head_dim + col);
-            acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
+            const float m_new = fmaxf(m_run, e);
+            if (m_new != -INFINITY) {
+                const float sc = __expf(m_run - m_new), wgt = __expf(e - m_new);
+                acc.x = acc.x * sc + o.x * wgt; acc.y = acc.y * sc + o.y * wgt;
+                acc.z = acc.z * sc + o.z * wgt; acc.w = acc.w * sc + o.w * wgt;
+                d_run = d_run * sc + l * wgt;
+                m_run = m_new;
+            }
         }
     }
     accs[tid] = acc;
+    if (ct == 0) { grp_m[grp] = m_run; grp_d[grp] = d_run; }
     __syncthreads();
-    if (tid < 16)
-        for (uint32_t g = 1; g < 16; ++g) {
-            const float4 o = accs[g * 16 + tid];
-            acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
+    float mg = grp_m[0];
+#pragma unroll
+    for (int g = 1; g < 16; ++g) mg = fmaxf(mg, grp_m[g]);
+    float D = 0.f;
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (tid < 17 && mg != -INFINITY)      // threads 0-15 carry the columns on, thread 16 the (max, sum) pair
+        for (uint32_t g = 0; g < 16; ++g) {
+            const float wgt = __expf(grp_m[g] - mg);              // 0 for a group that saw no finite maximum
+            const float4 o = accs[g * 16 + (tid & 15)];
+            acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
+            D += grp_d[g] * wgt;
         }
     exchange_and_merge<T>(p, h, cb, acc, mg, D, out, status, &all_arrived);
 }
