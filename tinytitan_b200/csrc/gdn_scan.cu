@@ -90,6 +90,10 @@ __device__ __forceinline__ uint32_t sw_a(uint32_t base, int row0, int k0, int la
 __device__ __forceinline__ uint32_t sw_b(uint32_t base, int n0, int k0, int lane) {
     return sw_piece(base, n0 + (lane & 7) + ((lane >> 4) << 3), k0 + ((lane >> 3) & 1) * 8);
 }
+// A operand (16 m x 16 k) read with .trans from a swizzled [k][m] tile (m contiguous), lane roles as in addr_at
+__device__ __forceinline__ uint32_t sw_at(uint32_t base, int k0, int m0, int lane) {
+    return sw_piece(base, k0 + (lane & 7) + (lane >> 4) * 8, m0 + ((lane >> 3) & 1) * 8);
+}
 __device__ __forceinline__ uint32_t sw_bt(uint32_t base, int k0, int n0, int lane) {
     return sw_piece(base, k0 + (lane & 7) + ((lane >> 3) & 1) * 8, n0 + (lane >> 4) * 8);
 }
@@ -268,17 +272,34 @@ gdn_scan_prepare_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_m
         }
     }
     __syncthreads();   // every column is solved: L (and, since the Gram phase, Q) may be overwritten
-    __half *tb = &s.q[0][0][0], *ta = reinterpret_cast<__half *>(&s.l[0][0]);   // [hi, lo][64][64], swizzled
+    // The T operands are stored TRANSPOSED ([s][t], swizzled boxes, hi then lo): the thread that owns
+    // column j of T then writes one 128-byte row per box as eight 16-byte stores instead of 64 scattered
+    // 2-byte ones, and the products below read their A fragments with ldmatrix.trans.
+    __half *tb = &s.q[0][0][0], *ta = reinterpret_cast<__half *>(&s.l[0][0]);
     if (tid < kC) {
         // column j of T diag(b) and T diag(b A), split into fp16 hi + lo
         const float bj = s.beta[tid], baj = s.beta[tid] * expf(s.log_a[tid]);
+        unsigned char *rb = reinterpret_cast<unsigned char *>(tb) + tid * 128;
+        unsigned char *ra = reinterpret_cast<unsigned char *>(ta) + tid * 128;
 #pragma unroll
-        for (int t = 0; t < kC; ++t) {
-            const float vb = x[t] * bj, va = x[t] * baj;
-            const __half hb = __float2half_rn(vb), ha = __float2half_rn(va);
-            const int at = t * 64 + ((((tid >> 3) ^ (t & 7)) << 3) | (tid & 7));   // element (t, tid) of a swizzled box
-            tb[at] = hb; tb[kC * 64 + at] = __float2half_rn(vb - __half2float(hb));
-            ta[at] = ha; ta[kC * 64 + at] = __float2half_rn(va - __half2float(ha));
+        for (int pc = 0; pc < 8; ++pc) {
+            uint32_t hb[4], ha[4], lb[4], la[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float vb0 = x[8 * pc + 2 * e] * bj, vb1 = x[8 * pc + 2 * e + 1] * bj;
+                const float va0 = x[8 * pc + 2 * e] * baj, va1 = x[8 * pc + 2 * e + 1] * baj;
+                hb[e] = pack_h2(vb0, vb1);
+                ha[e] = pack_h2(va0, va1);
+                const float2 qb = __half22float2(*reinterpret_cast<const __half2 *>(&hb[e]));
+                const float2 qa = __half22float2(*reinterpret_cast<const __half2 *>(&ha[e]));
+                lb[e] = pack_h2(vb0 - qb.x, vb1 - qb.y);     // what the fp16 rounding left over
+                la[e] = pack_h2(va0 - qa.x, va1 - qa.y);
+            }
+            const uint32_t off = (pc ^ (tid & 7)) << 4;
+            *reinterpret_cast<uint4 *>(rb + off) = make_uint4(hb[0], hb[1], hb[2], hb[3]);
+            *reinterpret_cast<uint4 *>(rb + kC * 128 + off) = make_uint4(lb[0], lb[1], lb[2], lb[3]);
+            *reinterpret_cast<uint4 *>(ra + off) = make_uint4(ha[0], ha[1], ha[2], ha[3]);
+            *reinterpret_cast<uint4 *>(ra + kC * 128 + off) = make_uint4(la[0], la[1], la[2], la[3]);
         }
     }
     __syncthreads();
@@ -296,10 +317,10 @@ gdn_scan_prepare_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_m
 #pragma unroll
         for (int ks = 0; ks < kC / 16; ++ks) {
             uint32_t abh[4], abl[4], aah[4], aal[4];
-            ldsm_x4(abh, sw_a(tbh, r0, ks * 16, lane));
-            ldsm_x4(abl, sw_a(tbl, r0, ks * 16, lane));
-            ldsm_x4(aah, sw_a(tah, r0, ks * 16, lane));
-            ldsm_x4(aal, sw_a(tal, r0, ks * 16, lane));
+            ldsm_x4_t(abh, sw_at(tbh, ks * 16, r0, lane));
+            ldsm_x4_t(abl, sw_at(tbl, ks * 16, r0, lane));
+            ldsm_x4_t(aah, sw_at(tah, ks * 16, r0, lane));
+            ldsm_x4_t(aal, sw_at(tal, ks * 16, r0, lane));
 #pragma unroll
             for (int np = 0; np < 4; ++np) {
                 uint32_t bv[4], bk[4];
