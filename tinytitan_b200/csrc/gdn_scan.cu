@@ -259,16 +259,16 @@ gdn_scan_prepare_kernel(ScanParams p, const __grid_constant__ CUtensorMap conv_m
     if (tid < kC) {
 #pragma unroll
         for (int t = 0; t < kC; ++t) {
-            float acc = (t == tid) ? 1.f : 0.f;
+            float acc = (t == tid) ? 1.f : 0.f, acc1 = 0.f;   // two chains: a dependent FMA costs 4 cycles
 #pragma unroll
             for (int s4 = 0; s4 < t; s4 += 4) {      // row t of L, four columns per (broadcast) load
                 const float4 lv = *reinterpret_cast<const float4 *>(&s.l[t][s4]);
                 acc = fmaf(-lv.x, x[s4], acc);                       // x[sx] == 0 for sx < j
-                if (s4 + 1 < t) acc = fmaf(-lv.y, x[s4 + 1], acc);
+                if (s4 + 1 < t) acc1 = fmaf(-lv.y, x[s4 + 1], acc1);
                 if (s4 + 2 < t) acc = fmaf(-lv.z, x[s4 + 2], acc);
-                if (s4 + 3 < t) acc = fmaf(-lv.w, x[s4 + 3], acc);
+                if (s4 + 3 < t) acc1 = fmaf(-lv.w, x[s4 + 3], acc1);
             }
-            x[t] = acc;
+            x[t] = acc + acc1;
         }
     }
     __syncthreads();   // every column is solved: L (and, since the Gram phase, Q) may be overwritten
