@@ -16,10 +16,13 @@
 //
 // Decay ratios are exp(logA_t - logA_s) of cumulative log-decays (never A_t / A_s, cf.
 // gdn_chunk.c:141-147). Two kernels per segment of chunks:
-//   gdn_scan_prepare_kernel  one CTA per (chunk, value head), fully parallel: Gram matrices on
-//                            mma.sync, T by forward substitution in fp32, U (fp32), W, M (fp16)
-//   gdn_scan_state_kernel    one CTA per (32 state rows, value head), chunks in order: the fp32
-//                            state lives in mma accumulator registers for the whole segment
+//   gdn_scan_prepare_kernel   one CTA per (chunk, value head), fully parallel: tiles by TMA, Gram
+//                             matrices on mma.sync, T by forward substitution in fp32, U (fp32), W, M
+//                             (fp16); U and W leave through TMA tensor stores
+//   gdn_scan_state_tc_kernel  one CTA per (32 state rows, value head), chunks in order, on tcgen05:
+//                             the fp32 state lives transposed in tensor memory for the whole segment
+//   gdn_scan_state_kernel     the same recurrence on mma.sync (state in accumulator registers), kept
+//                             as the A/B partner selected by TT_GDN_SCAN_FORCE_MMA_SYNC=1
 // The rows of S (value dimension) are independent of one another, which is what lets the state
 // be split over CTAs with no communication.
 #include "tt_sm100.h"
