@@ -283,6 +283,36 @@ def test_chunked_scan_tcgen05_and_mma_sync_recurrences_agree(monkeypatch):
     assert np.abs(got[0][1] - got[1][1]).max() <= 1e-5 * max(1.0, np.abs(want_s).max())
 
 
+def test_chunked_scan_in_segments_equals_one_segment(monkeypatch):
+    # A context whose workspace holds 8 chunk records per head runs a 23-chunk prompt (ragged tail) in
+    # three segments: the state goes through global memory between them and the record indices
+    # restart, but chunk boundaries are the same, so both recurrences must reproduce the
+    # one-segment result exactly.
+    r = np.random.default_rng(91)
+    rows, hk, hv, d = 23 * 64 - 17, 2, 4, 128
+    cfg = tt.LinearAttentionConfig(hk, hv, d, d)
+    conv, a, b, a_log, dt_bias, state = make_inputs(r, rows, hk, hv, d, d)
+    record_bytes = 64 * 128 * 4 + 64 * 128 * 2 + 64 * 64 * 2 + 2 * 64 * 4
+    small = tt.Context(0, workspace_bytes=8 * hv * record_bytes + 100)
+    try:
+        for force in (False, True):
+            if force:
+                monkeypatch.setenv("TT_GDN_SCAN_FORCE_MMA_SYNC", "1")
+            want_y, want_s = run_scan(cfg, conv, a, b, a_log, dt_bias, state, rows)
+            cd, ad, bd = dev(conv), dev(a), dev(b)
+            al, dt, st = dev(a_log, torch.bfloat16), dev(dt_bias, torch.bfloat16), dev(state, torch.float32)
+            y = torch.full((rows, cfg.value_dim), float("nan"), device="cuda", dtype=torch.float16)
+            launches = small.launch_count
+            tt.GDN(small, cfg).encode_delta_scan_chunked(cd, ad, bd, al, dt, st, y, rows, row_stride=conv.shape[1])
+            torch.cuda.synchronize()
+            assert small.poll_status() == 0
+            assert small.launch_count - launches == 6
+            assert np.array_equal(host(y), want_y)
+            assert np.array_equal(host(st), want_s)
+    finally:
+        small.close()
+
+
 def test_chunked_scan_rejects_other_shapes():
     gdn = tt.GDN(context(), tt.LinearAttentionConfig(2, 4, 64, 64))
     x = torch.zeros(1 << 14, device="cuda", dtype=torch.float16); s = torch.zeros(4 * 64 * 64, device="cuda")
