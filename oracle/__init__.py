@@ -298,8 +298,12 @@ def delta_rule_sessions(query, key, value, a, b, decay_log, decay_bias, key_head
 # gated output norm rmsnorm(y) * w * silu(z) (:109-121).
 # --------------------------------------------------------------------------
 class GDNChainReference:
-    def __init__(self, hk, hv, dk, dv, taps, conv_w, a_log, dt_bias, norm_w):
+    def __init__(self, hk, hv, dk, dv, taps, conv_w, a_log, dt_bias, norm_w, fp16_points=True):
+        """fp16_points=False keeps every intermediate in fp32 (the all-fp32 model the reference's
+        numpy implementation tools/qwen35_reference.py:231-290 computes)."""
         self.hk, self.hv, self.dk, self.dv, self.taps = hk, hv, dk, dv, taps
+        if not fp16_points:
+            self._h = lambda x: np.asarray(x, np.float32)
         self.c = 2 * hk * dk + hv * dv
         self.conv_w = _f(conv_w).reshape(self.c, taps)
         self.a_log, self.dt_bias, self.norm_w = _f(a_log), _f(dt_bias), _f(norm_w)
@@ -344,6 +348,40 @@ class GDNChainReference:
                                          self.hk, self.hv, self.dk, self.dv, self.state)
         y = self._h(y[0])
         return self.gated_norm(y, z), y, normed
+
+
+# --------------------------------------------------------------------------
+# the elementwise step either side of decode attention (numpy, fp32 with the GPU path's fp16
+# rounding points). Follows Primitives/rmsnorm.metal:101-128 (per-head RMS norm, bf16 weight, fp16
+# store), Primitives/rope.metal:32-49, :80-108 (NeoX rotation of the first `rotary` elements, fp16
+# store) and Primitives/utility.metal:142-160 (out * sigmoid(gate)); the call order is
+# RealForwardRunner+DecodeFullAttention.swift:123-185.
+# --------------------------------------------------------------------------
+def _half(x):
+    return np.asarray(x, np.float32).astype(np.float16).astype(np.float32)
+
+
+def attn_norm_rope(x, weight, eps: float, rotary: int, theta: float, position: int, fp16_points: bool = True):
+    """One head: RMS norm with `weight`, then NeoX rotation of x[:rotary] at `position`."""
+    h = _half if fp16_points else (lambda a: np.asarray(a, np.float32))
+    x = np.asarray(x, np.float32)
+    inv = np.float32(1) / np.sqrt(np.float32((x * x).sum(dtype=np.float32) / x.size + eps))
+    y = h(x * inv * np.asarray(weight, np.float32))
+    half = rotary // 2
+    pair = np.arange(half, dtype=np.float32)
+    angle = np.float32(position) * np.power(np.float32(theta), -(2 * pair) / np.float32(rotary)).astype(np.float32)
+    c, s = np.cos(angle).astype(np.float32), np.sin(angle).astype(np.float32)
+    out = y.copy()
+    out[:half] = h(y[:half] * c - y[half:rotary] * s)
+    out[half:rotary] = h(y[:half] * s + y[half:rotary] * c)
+    return out
+
+
+def attn_gate_mul(out, gate, fp16_points: bool = True):
+    """Sigmoid output gate: out * 1/(1+exp(-gate))."""
+    h = _half if fp16_points else (lambda a: np.asarray(a, np.float32))
+    out, gate = np.asarray(out, np.float32), np.asarray(gate, np.float32)
+    return h(out / (np.float32(1) + np.exp(-gate)))
 
 
 # --------------------------------------------------------------------------

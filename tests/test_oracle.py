@@ -211,3 +211,85 @@ def test_threaded_drivers_equal_serial():
     if oracle.ref() is not None:
         yr, sr = oracle.gdn_scan_heads(q, k, v, al, be, hk, hv, d, d, 8, st, threads=2, use_ref=True)
         assert np.abs(y1 - yr).max() < 1e-5
+
+
+# --------------------------------------------------------------------------
+# The reference's own numpy model (tools/qwen35_reference.py, Reference.attention :292-322 and
+# Reference.gdn :231-290), run by tests/golden/make_golden_qwen35.py on seeded synthetic weights;
+# its outputs are the fixtures qwen35_attention.npz / qwen35_gdn.npz.
+# --------------------------------------------------------------------------
+import make_golden_qwen35 as mq
+
+
+def _oracle_attention_chain(c, fp16_points):
+    """Oracle statements chained as the decode path runs them: norm + RoPE on q and the new K row,
+    the row appended to the cache, decode attention over the cache, sigmoid gate."""
+    hq, hkv, hd, cached, steps = c["hq"], c["hkv"], c["hd"], c["cached"], c["steps"]
+    h = (lambda x: np.asarray(x, np.float32).astype(np.float16).astype(np.float32)) if fp16_points else (lambda x: x)
+    keys = np.concatenate([c["cache_k"], np.zeros((steps, hkv, hd), np.float32)])
+    values = np.concatenate([c["cache_v"], c["v"]])
+    out = np.empty((steps, hq * hd), np.float32)
+    for t in range(steps):
+        pos = cached + t
+        q = np.stack([oracle.attn_norm_rope(c["packed"][t, i, :hd], c["q_norm"], mq.EPS, mq.ROTARY, mq.ROPE_THETA, pos,
+                                            fp16_points) for i in range(hq)])
+        for i in range(hkv):
+            keys[pos, i] = oracle.attn_norm_rope(c["k"][t, i], c["k_norm"], mq.EPS, mq.ROTARY, mq.ROPE_THETA, pos, fp16_points)
+        att = h(oracle.attn_decode(q, keys[:pos + 1], values[:pos + 1], hkv, 1.0 / np.sqrt(hd)))
+        out[t] = oracle.attn_gate_mul(att, c["packed"][t, :, hd:], fp16_points).ravel()
+    return out, keys[cached:]
+
+
+@pytest.mark.parametrize("name", list(mq.ATTENTION_CASES))
+def test_attention_oracle_matches_reference_model(name):
+    c = mq.attention_inputs(name)
+    gold = np.load(os.path.join(GOLD, "qwen35_attention.npz"))
+    want_out, want_keys = gold[f"{name}.out"], gold[f"{name}.keys"]
+    assert want_out.shape == (c["steps"], c["hq"] * c["hd"]) and c["steps"] >= 64
+    # all-fp32 statements: only summation order and float32-vs-float64 trigonometry differ (the
+    # kernels form the angle position * inverse frequency in fp32, the reference in float64: up to
+    # position * 2^-23 radians apart, times values of magnitude ~5)
+    out, keys = _oracle_attention_chain(c, fp16_points=False)
+    fp32_bar = 2e-5 + 5 * (c["cached"] + c["steps"]) * 2.0 ** -23
+    assert np.abs(keys - want_keys).max() < fp32_bar
+    assert np.abs(out - want_out).max() < fp32_bar
+    # with the GPU path's fp16 stores (normed q/k, rotated q/k, attention row, gated row): the bar
+    # the CUDA chain is held to. Keys are O(1..5): two fp16 roundings of the value on top.
+    out, keys = _oracle_attention_chain(c, fp16_points=True)
+    assert np.abs(keys - want_keys).max() <= 2e-3 + np.abs(want_keys).max() * 2.0 ** -9
+    assert np.abs(out - want_out).max() <= 2e-3
+
+
+def _oracle_gdn_chain(c, fp16_points):
+    ch = oracle.GDNChainReference(c["hk"], c["hv"], c["dk"], c["dv"], c["conv_k"], c["conv_w"], c["a_log"], c["dt_bias"],
+                                  c["norm_w"], fp16_points=fp16_points)
+    out = np.stack([ch.step(c["qkv"][t], c["a"][t], c["b"][t], c["z"][t])[0] for t in range(c["tokens"])])
+    return out, ch
+
+
+def gdn_chain_bar(c, want):
+    z = c["z"]
+    gain = np.abs(np.tile(c["norm_w"], c["hv"])[None] * z / (1 + np.exp(-z)))
+    return 4e-3 * np.maximum(1.0, gain) + np.abs(want) * 2.0 ** -10
+
+
+def test_gdn_oracle_matches_reference_model():
+    c = mq.gdn_inputs()
+    gold = np.load(os.path.join(GOLD, "qwen35_gdn.npz"))
+    assert gold["out"].shape == (c["tokens"], c["hv"] * c["dv"]) and c["tokens"] >= 8
+    out, ch = _oracle_gdn_chain(c, fp16_points=False)
+    scale = np.maximum(1.0, np.abs(gold["out"]))
+    assert (np.abs(out - gold["out"]) / scale).max() < 1e-4
+    assert np.abs(ch.state[::8, ::32, :] - gold["state_rows"]).max() < 1e-5
+    assert abs(ch.state.astype(np.float64).sum() - gold["state_sum"][0]) < 1e-3 * gold["state_sum"][1]
+    assert np.abs(ch.tail - gold["tail"]).max() == 0
+    # With the GPU path's fp16 stores (conv output, normed q/k, y; GDNReference.swift:63, :79,
+    # :105). One fp16 rounding of a conv output moves y by up to ~1.5e-3 of the head's RMS, the
+    # gated norm divides by that RMS and multiplies by w * silu(z) (up to ~6 here), so the chain is
+    # held to 4e-3 on the normalised row times that per-element gain, and to the reference's own
+    # bar for its GPU chain, max(2e-2, 4e-2 |want|) (GDNKernelTests.swift:144-200).
+    out, ch = _oracle_gdn_chain(c, fp16_points=True)
+    err = np.abs(out - gold["out"])
+    assert (err <= gdn_chain_bar(c, gold["out"])).all()
+    assert (err <= np.maximum(2e-2, 4e-2 * np.abs(gold["out"]))).all()
+    assert np.abs(ch.state[::8, ::32, :] - gold["state_rows"]).max() < 5e-4
