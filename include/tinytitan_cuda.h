@@ -58,7 +58,16 @@ typedef struct tt_context_options {
 
 /* Replaces MetalContext + the per-operator scratch the Swift classes own
  * (sources/TinyTitan/Kernels/Attention/Attention.swift:140-156): all device
- * scratch is allocated here, never on the decode path. */
+ * scratch is allocated here, never on the decode path.
+ *
+ * A context serves ONE stream at a time. Its scratch (the tables and split partials of the
+ * current call, the status word) belongs to the operation that was enqueued last: TT_ERR_BUSY
+ * only rejects host calls that overlap in time, and it is released when the enqueue returns,
+ * while the kernels may still be running. Two operations through one context on different
+ * streams with no ordering between them would overwrite each other's scratch; use one context
+ * per stream (contexts are independent and cheap next to a KV cache), or order the streams
+ * with events. The reference's Attention has the same rule for its shared partial scratch
+ * (Attention.swift:173-192: one encode in flight per instance). */
 tt_context *tt_context_create(int device, const tt_context_options *options, int *out_err);
 void tt_context_destroy(tt_context *ctx);
 /* Text of the last failure seen through this context (never NULL). */
@@ -184,6 +193,12 @@ int tt_attn_combine(tt_context *ctx, tt_stream stream, const float *m, const flo
  * peer_buffers[r] is rank r's buffer as mapped by THIS process (its own for r == rank).
  * world <= 16; head_dim a multiple of 4. */
 size_t tt_attn_exchange_bytes(uint32_t world, uint32_t n_q_heads, uint32_t head_dim);
+/* No counterpart in the reference. How many polls (about 0.25 us each) the exchange kernels of
+ * this context wait for the other ranks' flags before they give up, set TT_DEV_WAIT_TIMEOUT in
+ * the status word and leave the output untouched; 0 restores the default (about one second).
+ * A short limit lets a host that already knows a peer is gone (a heartbeat, a store) get its
+ * stream back quickly; the status is read with tt_ctx_poll_status (TT_ERR_TIMEOUT). */
+int tt_ctx_set_exchange_poll_limit(tt_context *ctx, uint32_t polls);
 int tt_peer_buffer_create(tt_context *ctx, size_t bytes, void **out_ptr, unsigned char out_handle[64]);
 int tt_peer_buffer_open(tt_context *ctx, const unsigned char handle[64], void **out_ptr);
 int tt_peer_buffer_close(tt_context *ctx, void *ptr);
@@ -218,15 +233,25 @@ int tt_attn_decode_exchange(tt_context *ctx, tt_stream stream, const void *q, co
  * limits (inside another component's latency-critical or capture-restricted section, or
  * after the host has handed out its whole memory budget). It needs no context and calls no
  * allocator: the split-KV scratch is a fixed 8 MiB array inside the library image, present
- * on every GPU that loads the library until the process exits. Shapes whose scratch would
- * not fit (more than 4096 work items, or partial triples beyond the array) are refused with
- * TT_ERR_UNSUPPORTED_SHAPE; head_dim must be 64, 128 or 256 and the buffers 16-byte aligned.
- * The first call on a device looks the array's device address up; make that call outside
- * stream capture. All calls on a device share the array: calls that overlap on the GPU race,
- * so keep them ordered (one stream, or events). Runs on the current device. */
+ * on every GPU that loads the library until the process exits. The session is passed to the
+ * kernels by value and nothing is copied from host memory. Limits: at most
+ * TT_NOALLOC_MAX_KEYS keys in [kv_start, seq_len) (a longer range is refused with
+ * TT_ERR_UNSUPPORTED_SHAPE before anything is launched; below it the split is coarsened
+ * until the partial triples fit the array); head_dim 64, 128 or 256; n_q_heads <= 96;
+ * buffers 16-byte aligned. The first call on a device looks the array's device address up;
+ * make that call outside stream capture. All calls on a device share the array: calls that
+ * overlap on the GPU race, so keep them ordered (one stream, or events). Runs on the
+ * current device. A bounded wait that runs out inside a kernel cannot be reported through
+ * the return value of an asynchronous call: read it with tt_attn_decode_noalloc_status. */
+#define TT_NOALLOC_MAX_KEYS (1u << 22)
 int tt_attn_decode_noalloc(tt_stream stream, const void *q, const void *k, const void *v, void *out,
                            uint32_t head_dim, uint32_t n_q_heads, uint32_t n_kv_heads,
                            uint32_t seq_len, uint32_t kv_start, float scale);
+/* No counterpart in the reference. Waits for `stream`, then stores the device status word of
+ * the allocation-free entry point on the current device in *out_flags: 0, or bit 0 when a
+ * bounded wait in the last call's kernels gave up (that call's output is then not valid).
+ * Allocates nothing either. */
+int tt_attn_decode_noalloc_status(tt_stream stream, uint32_t *out_flags);
 
 /* Split geometry of the reference, kept for callers and tests that pin it
  * (Attention.splitGeometry, Attention.swift:196-227). This library's own split
@@ -466,6 +491,13 @@ void tt_kv_cache_destroy(tt_kv_cache *cache);
  * that keeps min(capacity, position[s]) rows of every slot. Views and slot
  * pointers fetched earlier are invalid afterwards. */
 int tt_kv_cache_reserve(tt_kv_cache *cache, uint32_t tokens, uint32_t slot);
+/* The reference's managers are touched by the CPU between command buffers (unified memory); here
+ * their row copies (reserve) are device work. Unbound, they are synchronous calls on the legacy
+ * default stream, which non-blocking streams do not wait for. After _bind_stream they are enqueued
+ * on `stream`, in order with the kernels launched there; reserve then synchronises that stream
+ * before it releases the old buffers. Only for managers on the built-in CUDA allocator
+ * (TT_ERR_UNSUPPORTED_SHAPE otherwise). */
+int tt_kv_cache_bind_stream(tt_kv_cache *cache, tt_stream stream);
 /* kSlot / vSlot (:161-211): where the projection writes position `position`. */
 int tt_kv_cache_k_slot(tt_kv_cache *cache, uint32_t layer, uint32_t position, uint32_t slot,
                        void **out_ptr);
@@ -515,10 +547,15 @@ int tt_gdn_state_conv_tail_slot(tt_gdn_state *state, uint32_t layer, uint32_t sl
                                 void **out_ptr);
 int tt_gdn_state_speculative_state_slot(tt_gdn_state *state, uint32_t layer, uint32_t slot,
                                         void **out_ptr);
+/* reset() / reset(slot:) (:207-226) zero-fill; like the KV manager's copies they run on the legacy
+ * default stream until _bind_stream names the stream they are enqueued on. */
 int tt_gdn_state_reset(tt_gdn_state *state);
 int tt_gdn_state_reset_slot(tt_gdn_state *state, uint32_t slot);
-/* encodeSpeculativeRestore (:265-292): checkpoint twins -> live buffers. */
-int tt_gdn_state_speculative_restore(tt_gdn_state *state);
+int tt_gdn_state_bind_stream(tt_gdn_state *state, tt_stream stream);
+/* encodeSpeculativeRestore(commandBuffer:) (:265-292): checkpoint twins -> live buffers of slot 0,
+ * enqueued on `stream` (the stream of the verify pass that wrote the checkpoint), so it is ordered
+ * with that pass exactly as the reference's blit is ordered inside its command buffer. */
+int tt_gdn_state_speculative_restore(tt_gdn_state *state, tt_stream stream);
 size_t tt_gdn_state_bytes_per_layer(const tt_gdn_state *state);
 size_t tt_gdn_state_conv_tail_bytes_per_layer(const tt_gdn_state *state);
 int tt_gdn_state_is_linear(const tt_gdn_state *state, uint32_t layer);

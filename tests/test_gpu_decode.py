@@ -349,3 +349,31 @@ def test_verify_tensor_core_single_part_writes_outputs_directly():
     assert context().launch_count - launches == 1
     for i in range(len(lens)):
         assert np.abs(got[i] - want[i]).max() <= TOL, (i, np.abs(got[i] - want[i]).max())
+
+
+def test_exchange_wait_runs_out_and_reports_timeout():
+    # The cross-GPU merge waits for every rank's flag with a poll limit. Here "rank 1" never
+    # publishes (both exchange buffers are plain local allocations of this one GPU and nothing ever
+    # writes rank 1's flag), the limit is tiny, so the wait gives up: the kernel returns, the status
+    # word reads TT_ERR_TIMEOUT on the host and the output row is left untouched. A context of its
+    # own, so the suite's shared context keeps a clean status word.
+    import ctypes as C
+    from tinytitan_b200 import _lib as L
+    ctx = tt.Context(0)
+    try:
+        ctx.set_exchange_poll_limit(1000)
+        hq, hd, world = 4, 128, 2
+        nbytes = L.lib().tt_attn_exchange_bytes(world, hq, hd)
+        bufs = [torch.zeros(nbytes + 256, device="cuda", dtype=torch.uint8) for _ in range(world)]
+        ptrs = (C.c_void_p * world)(*[(b.data_ptr() + 255) // 256 * 256 for b in bufs])
+        m = torch.zeros(hq, device="cuda"); d = torch.ones(hq, device="cuda"); o = torch.ones(hq, hd, device="cuda")
+        out = torch.full((hq, hd), 7.0, device="cuda", dtype=torch.float16)
+        stream = torch.cuda.current_stream().cuda_stream
+        ctx.check(L.lib().tt_attn_exchange_combine(ctx.handle, stream, m.data_ptr(), d.data_ptr(), o.data_ptr(), ptrs, 0,
+                                                   world, hq, hd, 1, out.data_ptr(), tt.TT_F16))
+        flags = C.c_uint32(0)
+        rc = L.lib().tt_ctx_poll_status(ctx.handle, stream, C.byref(flags))
+        assert rc == L.TT_ERR_TIMEOUT and flags.value & 1
+        assert torch.all(out == 7.0)
+    finally:
+        ctx.close()

@@ -68,3 +68,63 @@ def test_snapshot_round_trip_on_device_memory():
     assert torch.equal(device_view(g2.state_slot(1, 0), st.numel()), st)
     for m in (a, b, g, g2):
         m.close()
+
+
+def test_speculative_restore_is_ordered_on_a_non_blocking_stream():
+    # GDNStateManager.encodeSpeculativeRestore(commandBuffer:) (GDNStateManager.swift:265-292) is a blit
+    # in the verify pass's command buffer. Here: a 3-row verify step that checkpoints the state after
+    # row 0, then the restore, then a read-back, all enqueued on one NON-blocking stream with no host
+    # synchronisation in between -- the legacy default stream would not be ordered with any of it.
+    r = np.random.default_rng(77)
+    lin = tt.LinearAttentionConfig(2, 4, 128, 128, 4)
+    cfg = tt.ArchConfig([tt.LINEAR], 2, 256, 2, 256, 0, lin)
+    g = tt.GDNStateManager(cfg, enable_speculative_checkpoint=True)
+    n_state = 4 * 128 * 128
+    rows = 3
+    unit = lambda x: x / np.sqrt((x * x).sum(-1, keepdims=True) + 1e-6)
+    conv = rounded(np.concatenate([unit(r.normal(size=(rows, 2, 128))).reshape(rows, -1) / np.sqrt(128),
+                                   unit(r.normal(size=(rows, 2, 128))).reshape(rows, -1),
+                                   r.normal(size=(rows, 4 * 128))], 1))
+    a, b = rounded(r.normal(size=(rows, 4))), rounded(r.normal(size=(rows, 4)))
+    s0 = (0.02 * r.normal(size=(4, 128, 128))).astype(np.float32)
+    state = device_view(g.state_slot(0), n_state)
+    spec = device_view(g.speculative_state_slot(0), n_state)
+    conv_d, a_d, b_d = dev(conv), dev(a), dev(b)
+    z = torch.zeros(4, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty(rows, 4 * 128, device="cuda", dtype=torch.float16)
+    after = torch.empty(n_state, device="cuda")
+    big = torch.empty(64 << 20, device="cuda")
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()            # torch side streams are created non-blocking
+    with torch.cuda.stream(side):
+        state.copy_(dev(s0, torch.float32).view(-1))
+        big.normal_()                     # keeps the stream busy so that an unordered copy would run early
+        tt.GDN(context(), lin).encode_delta_step_prefill(conv_d, a_d, b_d, z, z, state, y, rows, checkpoint_state=spec)
+        g.speculative_restore(side)
+        after.copy_(state)
+    side.synchronize()
+    assert context().poll_status() == 0
+    _, want_all, want_ck = oracle.gdn_step_rows(conv, a, b, np.zeros(4), np.zeros(4), 2, 4, 128, 128, s0, want_checkpoint=True)
+    got = host(after).reshape(4, 128, 128)
+    assert np.abs(got - want_ck).max() <= 1e-5            # the state after row 0 alone, not after all three rows
+    assert np.abs(got - want_all).max() > 1e-4
+    g.close()
+
+
+def test_reserve_on_a_bound_stream_keeps_rows_written_there():
+    cfg = tt.ArchConfig([tt.FULL], 2, 256, 2, 256, 0, tt.LinearAttentionConfig(16, 32, 128, 128, 4))
+    kv = tt.KVCacheManager(cfg, max_context=20000)
+    side = torch.cuda.Stream()
+    kv.bind_stream(side)
+    n = 8192
+    rows = torch.randn(n, 512, device="cuda").half()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        device_view(kv.k_slot(0, 0), n * 512, torch.float16).copy_(rows.view(-1))   # enqueued, not yet done
+        kv.advance(0, n)
+        kv.reserve(n + 1)                                                            # grows: the copy must follow the write
+        assert kv.capacity(0) == 16384
+        back = device_view(kv.k_slot(0, 0), n * 512, torch.float16).clone()
+    side.synchronize()
+    assert torch.equal(back.view(n, 512), rows)
+    kv.close()

@@ -132,6 +132,8 @@ SIGNATURES = {
     "tt_attn_decode_exchange": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.c_float, _u32, _u32,
                                           C.POINTER(AttnExchange)]),
     "tt_attn_decode_noalloc": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.c_float]),
+    "tt_ctx_set_exchange_poll_limit": (C.c_int, [_vp, _u32]),
+    "tt_attn_decode_noalloc_status": (C.c_int, [_vp, C.POINTER(_u32)]),
     "tt_attn_reference_split_geometry": (None, [_u32, _u32, _u32, _u32, C.c_int, C.POINTER(SplitGeometry)]),
     "tt_attn_plan_splits": (C.c_int, [C.POINTER(_u32), C.POINTER(_u32), _u32, _u32, _u32, _u32, _u32, C.c_size_t,
                                       C.POINTER(_u32), C.POINTER(_u32)]),
@@ -185,7 +187,9 @@ SIGNATURES = {
     "tt_gdn_state_speculative_state_slot": (C.c_int, [_vp, _u32, _u32, C.POINTER(_vp)]),
     "tt_gdn_state_reset": (C.c_int, [_vp]),
     "tt_gdn_state_reset_slot": (C.c_int, [_vp, _u32]),
-    "tt_gdn_state_speculative_restore": (C.c_int, [_vp]),
+    "tt_gdn_state_speculative_restore": (C.c_int, [_vp, _vp]),
+    "tt_gdn_state_bind_stream": (C.c_int, [_vp, _vp]),
+    "tt_kv_cache_bind_stream": (C.c_int, [_vp, _vp]),
     "tt_gdn_state_bytes_per_layer": (C.c_size_t, [_vp]),
     "tt_gdn_state_conv_tail_bytes_per_layer": (C.c_size_t, [_vp]),
     "tt_gdn_state_is_linear": (C.c_int, [_vp, _u32]),

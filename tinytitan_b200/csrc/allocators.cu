@@ -20,10 +20,28 @@ void *cuda_alloc(void *, size_t bytes) {
     return p;
 }
 void cuda_release(void *, void *p) { cudaFree(p); }
-int cuda_copy(void *, void *dst, const void *src, size_t bytes) {
+
+// The stream a manager backed by the built-in CUDA allocator orders its copies and fills on. Unbound
+// (the default) they are synchronous calls on the legacy default stream, which only blocking streams
+// wait for; once bound (tt_kv_cache_bind_stream / tt_gdn_state_bind_stream) they are enqueued on that
+// stream, in order with the kernels the caller launches there. `user` of the built-in allocator
+// points at the manager's own CudaBinding.
+struct CudaBinding {
+    cudaStream_t stream = nullptr;
+    bool bound = false;
+};
+
+int cuda_copy(void *user, void *dst, const void *src, size_t bytes) {
+    const CudaBinding *b = static_cast<const CudaBinding *>(user);
+    if (b != nullptr && b->bound)
+        return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, b->stream) == cudaSuccess ? 0 : 1;
     return cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToDevice) == cudaSuccess ? 0 : 1;
 }
-int cuda_zero(void *, void *dst, size_t bytes) { return cudaMemset(dst, 0, bytes) == cudaSuccess ? 0 : 1; }
+int cuda_zero(void *user, void *dst, size_t bytes) {
+    const CudaBinding *b = static_cast<const CudaBinding *>(user);
+    if (b != nullptr && b->bound) return cudaMemsetAsync(dst, 0, bytes, b->stream) == cudaSuccess ? 0 : 1;
+    return cudaMemset(dst, 0, bytes) == cudaSuccess ? 0 : 1;
+}
 
 int cuda_download(void *, void *host_dst, const void *src, size_t bytes) {
     return cudaMemcpy(host_dst, src, bytes, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 1;
@@ -62,6 +80,8 @@ TT_API void tt_kv_row_layout(uint32_t elements, uint32_t precision_bits, uint32_
 
 struct tt_kv_cache {
     tt_allocator alloc;
+    CudaBinding binding;   // used when `alloc` is the built-in CUDA allocator
+    bool builtin = false;
     uint32_t max_context = 0, slots = 0, precision_bits = 16;
     bool ring = false;
     std::vector<void *> k, v;
@@ -87,6 +107,8 @@ TT_API tt_kv_cache *tt_kv_cache_create(const tt_arch *arch, uint32_t max_context
     tt_kv_cache *c = new (std::nothrow) tt_kv_cache();
     if (c == nullptr) { *err = TT_ERR_OOM; return nullptr; }
     c->alloc = allocator ? *allocator : kCudaAllocator;
+    c->builtin = allocator == nullptr;
+    if (c->builtin) c->alloc.user = &c->binding;
     c->max_context = max_context;
     c->slots = slots;
     c->precision_bits = precision_bits;
@@ -170,11 +192,26 @@ TT_API int tt_kv_cache_reserve(tt_kv_cache *c, uint32_t tokens, uint32_t slot) {
                 return TT_ERR_CUDA;
             }
         }
+        // the row copies above may still be in flight on the bound stream, and kernels enqueued
+        // there earlier may still read the old buffers
+        if (c->builtin && c->binding.bound && cudaStreamSynchronize(c->binding.stream) != cudaSuccess) {
+            c->alloc.release(c->alloc.user, nk);
+            c->alloc.release(c->alloc.user, nv);
+            return TT_ERR_CUDA;
+        }
         c->alloc.release(c->alloc.user, c->k[layer]);
         c->alloc.release(c->alloc.user, c->v[layer]);
         c->k[layer] = nk; c->v[layer] = nv;
         c->capacity[layer] = (uint32_t)target;
     }
+    return TT_OK;
+}
+
+TT_API int tt_kv_cache_bind_stream(tt_kv_cache *c, tt_stream stream) {
+    if (c == nullptr) return TT_ERR_INVALID_ARG;
+    if (!c->builtin) return TT_ERR_UNSUPPORTED_SHAPE;   // a caller-supplied allocator orders its own copies
+    c->binding.stream = (cudaStream_t)stream;
+    c->binding.bound = true;
     return TT_OK;
 }
 
@@ -335,6 +372,8 @@ TT_API int tt_kv_cache_snapshot_restore(tt_kv_cache *c, uint32_t position, const
 
 struct tt_gdn_state {
     tt_allocator alloc;
+    CudaBinding binding;   // used when `alloc` is the built-in CUDA allocator
+    bool builtin = false;
     uint32_t slots = 0;
     size_t state_bytes = 0, tail_bytes = 0;
     std::vector<void *> state, tail, spec_state, spec_tail;  // null for non-linear layers
@@ -363,6 +402,8 @@ TT_API tt_gdn_state *tt_gdn_state_create(const tt_arch *arch, uint32_t slots, in
     tt_gdn_state *g = new (std::nothrow) tt_gdn_state();
     if (g == nullptr) { *err = TT_ERR_OOM; return nullptr; }
     g->alloc = allocator ? *allocator : kCudaAllocator;
+    g->builtin = allocator == nullptr;
+    if (g->builtin) g->alloc.user = &g->binding;
     g->slots = slots;
     g->state_bytes = (size_t)arch->gdn_v_heads * arch->gdn_value_dim * arch->gdn_key_dim * 4;
     const uint32_t qkv = 2 * arch->gdn_k_heads * arch->gdn_key_dim + arch->gdn_v_heads * arch->gdn_value_dim;
@@ -452,16 +493,32 @@ TT_API int tt_gdn_state_reset_slot(tt_gdn_state *g, uint32_t slot) {
     return bad ? TT_ERR_CUDA : TT_OK;
 }
 
-TT_API int tt_gdn_state_speculative_restore(tt_gdn_state *g) {
+TT_API int tt_gdn_state_bind_stream(tt_gdn_state *g, tt_stream stream) {
+    if (g == nullptr) return TT_ERR_INVALID_ARG;
+    if (!g->builtin) return TT_ERR_UNSUPPORTED_SHAPE;
+    g->binding.stream = (cudaStream_t)stream;
+    g->binding.bound = true;
+    return TT_OK;
+}
+
+TT_API int tt_gdn_state_speculative_restore(tt_gdn_state *g, tt_stream stream) {
     if (g == nullptr) return TT_ERR_INVALID_ARG;
     for (size_t i = 0; i < g->state.size(); ++i)
         if (g->state[i] && (!g->spec_state[i] || !g->spec_tail[i])) return TT_ERR_INVALID_ARG;  // invalidLayout
+    // Enqueued on the caller's stream like the reference's blit, which is encoded into the same command
+    // buffer as the verify pass (GDNStateManager.swift:265-292): it runs after the step kernels that wrote
+    // the checkpoint and before whatever the caller enqueues next. A caller-supplied allocator copies in
+    // its own way (the host allocator of the CPU tests is synchronous).
+    CudaBinding on_stream;
+    on_stream.stream = (cudaStream_t)stream;
+    on_stream.bound = true;
+    void *user = g->builtin ? &on_stream : g->alloc.user;
     int bad = 0;
     for (size_t i = 0; i < g->state.size(); ++i) {
         if (!g->state[i]) continue;
         // slot 0's segment, as the reference copies stateBytesPerLayer from offset 0
-        bad |= g->alloc.copy(g->alloc.user, g->state[i], g->spec_state[i], g->state_bytes);
-        bad |= g->alloc.copy(g->alloc.user, g->tail[i], g->spec_tail[i], g->tail_bytes);
+        bad |= g->alloc.copy(user, g->state[i], g->spec_state[i], g->state_bytes);
+        bad |= g->alloc.copy(user, g->tail[i], g->spec_tail[i], g->tail_bytes);
     }
     return bad ? TT_ERR_CUDA : TT_OK;
 }

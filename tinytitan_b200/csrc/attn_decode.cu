@@ -209,6 +209,7 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
     for (uint32_t i = 0; i < prologue; ++i) issue(i);
 
     bool timed_out = false;
+    uint32_t timed_block = 0;
     const uint32_t k_off = ((lane & 7) + ((lane >> 4) << 3)) * S::kRowBytes + ((lane >> 3) & 1) * 16 + warp * HH * 2;
     const uint32_t v_off = S::kTileBytes + ((lane & 7) + ((lane >> 3) & 1) * 8) * S::kRowBytes + (lane >> 4) * 16 +
                            warp * HH * 2;
@@ -238,7 +239,7 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
         for (int j = 0; j < 4; ++j) { mine[j] = s0[j] + t0[j]; mine[4 + j] = s1[j] + t1[j]; }
         mine[8] = got ? 1.f : 0.f;
         pair_barrier();
-        if (!(got && theirs[8] != 0.f)) { timed_out = true; break; }   // same decision in both warps
+        if (!(got && theirs[8] != 0.f)) { timed_out = true; timed_block = i; break; }   // same decision in both warps
         float sv[2][4];  // [row half][key: n0c0 n0c1 n1c0 n1c1]
         sv[0][0] = mine[0] + theirs[0]; sv[0][1] = mine[1] + theirs[1];
         sv[1][0] = mine[2] + theirs[2]; sv[1][1] = mine[3] + theirs[3];
@@ -304,7 +305,13 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
         }
     }
 
-    if (timed_out && lane == 0) atomicOr(status, TT_DEV_WAIT_TIMEOUT);
+    if (timed_out) {
+        // the block that gave up and the one issued behind it may still be landing in this CTA's
+        // shared memory: give them a short, bounded chance to finish before the CTA exits
+        for (uint32_t b = timed_block; b < n_blocks && b < timed_block + 2; ++b)
+            mbar_wait(&bars[b % kStages], (b / kStages) & 1, 1u << 16);
+        if (lane == 0) atomicOr(status, TT_DEV_WAIT_TIMEOUT);
+    }
 
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -483,6 +490,7 @@ attn_decode_partial_quant_kernel(const TTDecodeItem *__restrict__ items,
     for (uint32_t i = 0; i < prologue; ++i) issue(i);
 
     bool timed_out = false;
+    uint32_t timed_block = 0;
     const uint32_t k_off = ((lane & 7) + ((lane >> 4) << 3)) * S::kHalfRowBytes + ((lane >> 3) & 1) * 16;
     const uint32_t v_off = S::kHalfTileBytes + ((lane & 7) + ((lane >> 3) & 1) * 8) * S::kHalfRowBytes + (lane >> 4) * 16;
     // dequantisation duty of this lane: key lane/2, E = HH/2 consecutive elements of this warp's half
@@ -568,7 +576,7 @@ attn_decode_partial_quant_kernel(const TTDecodeItem *__restrict__ items,
         for (int j = 0; j < 4; ++j) { mine[j] = s0[j] + t0[j]; mine[4 + j] = s1[j] + t1[j]; }
         mine[8] = got ? 1.f : 0.f;
         pair_barrier();
-        if (!(got && theirs[8] != 0.f)) { timed_out = true; break; }   // same decision in both warps
+        if (!(got && theirs[8] != 0.f)) { timed_out = true; timed_block = i; break; }   // same decision in both warps
         float sv[2][4];  // [row half][key: n0c0 n0c1 n1c0 n1c1]
         sv[0][0] = mine[0] + theirs[0]; sv[0][1] = mine[1] + theirs[1];
         sv[1][0] = mine[2] + theirs[2]; sv[1][1] = mine[3] + theirs[3];
@@ -634,7 +642,13 @@ attn_decode_partial_quant_kernel(const TTDecodeItem *__restrict__ items,
         }
     }
 
-    if (timed_out && lane == 0) atomicOr(status, TT_DEV_WAIT_TIMEOUT);
+    if (timed_out) {
+        // the block that gave up and the one issued behind it may still be landing in this CTA's
+        // shared memory: give them a short, bounded chance to finish before the CTA exits
+        for (uint32_t b = timed_block; b < n_blocks && b < timed_block + 2; ++b)
+            mbar_wait(&bars[b % kStages], (b / kStages) & 1, 1u << 16);
+        if (lane == 0) atomicOr(status, TT_DEV_WAIT_TIMEOUT);
+    }
 
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -1407,12 +1421,14 @@ TT_API int tt_attn_combine(tt_context *ctx, tt_stream stream, const float *m, co
 // before this library was loaded (the reference sizes every buffer up front against a memory
 // budget and treats a later allocation as a bug), or a thread that must not take the driver's
 // allocation lock. For them this one entry point runs the same two kernels as tt_attn_decode
-// with the split-KV scratch (session + item tables, partial triples, status word) carved out
-// of a fixed array that lives in the library image on every device that loads it.
+// with the split-KV scratch (partial triples, status word) carved out of a fixed array that
+// lives in the library image on every device that loads it.
 //
 // The array's name is only a stand-in on the host side, so the device address is looked up
 // once per device with cudaGetSymbolAddress while that device is current. That lookup happens
 // inside the first call on a device: make that first call outside any stream capture.
+// The session travels in the kernel parameters and every work item is derived from the block
+// index, so nothing is copied from host memory and no table lives on the caller's stack.
 // All calls on a device share the array and it keeps what the last call left behind; nothing
 // in it has to start at zero except the status word, which every call clears. Two calls that
 // overlap on the GPU (different streams, no ordering) race on the array and give wrong
@@ -1421,9 +1437,8 @@ TT_API int tt_attn_combine(tt_context *ctx, tt_stream stream, const float *m, co
 namespace {
 
 constexpr size_t kNoAllocScratchBytes = (size_t)8 << 20;   // 8 MiB per device, held until exit
-constexpr uint32_t kNoAllocMaxItems = 4096;
-constexpr size_t kNoAllocTableBytes = 256 + sizeof(TTDecodeSession) + sizeof(TTDecodeItem) * kNoAllocMaxItems;
-constexpr size_t kNoAllocPartialOffset = (kNoAllocTableBytes + 255) / 256 * 256;
+constexpr size_t kNoAllocPartialOffset = 256;              // the status word has the first 256 bytes
+constexpr uint32_t kNoAllocMaxKeys = 1u << 22;             // longest key range served (TT_NOALLOC_MAX_KEYS)
 constexpr int kNoAllocMaxDevices = 64;
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
@@ -1464,65 +1479,54 @@ TT_API int tt_attn_decode_noalloc(tt_stream stream, const void *q, const void *k
 
     if (kv_start > seq_len) kv_start = seq_len;
     const uint32_t keys = seq_len - kv_start, one = 1;
+    if (keys > kNoAllocMaxKeys) return TT_ERR_UNSUPPORTED_SHAPE;   // beyond the stated maximum
     uint32_t keys_per_item = 0, n_items = 0;
-    // the planner grows the items until the partial triples fit the fixed array
+    // the planner lengthens the items until the partial triples fit the fixed array
     int rc = tt_attn_plan_splits(&keys, &one, 1, head_dim, n_q_heads, n_kv_heads, (uint32_t)sm_count,
                                  kNoAllocScratchBytes - kNoAllocPartialOffset, &keys_per_item, &n_items);
     if (rc != TT_OK) return TT_ERR_UNSUPPORTED_SHAPE;       // does not fit the 8 MiB array
-    while (n_items > kNoAllocMaxItems) {                    // keep the item table inside its region
-        keys_per_item *= 2;
-        uint32_t parts = ceil_div_u32(keys, keys_per_item);
-        if (parts == 0) parts = 1;
-        n_items = parts * n_kv_heads * ceil_div_u32(n_q_heads / n_kv_heads, 16);
-    }
-
-    struct { TTDecodeSession ses; TTDecodeItem items[kNoAllocMaxItems]; } host;   // stack, no heap
     uint32_t parts = ceil_div_u32(keys, keys_per_item);
     if (parts == 0) parts = 1;
     const size_t partial_rows = (size_t)parts * n_q_heads;
     if (partial_rows * (head_dim + 2) * sizeof(float) > kNoAllocScratchBytes - kNoAllocPartialOffset)
         return TT_ERR_UNSUPPORTED_SHAPE;
-    host.ses.q = q; host.ses.out = out; host.ses.k = k; host.ses.v = v;
-    host.ses.seq_len = seq_len; host.ses.q_rows = 1; host.ses.kv_start = kv_start;
-    host.ses.n_parts = parts; host.ses.partial_base = 0; host.ses.ring_capacity = 0; host.ses.keep = nullptr;
-    host.ses.row_index = nullptr;
+    TTDecodeSession ses;
+    ses.q = q; ses.out = out; ses.k = k; ses.v = v;
+    ses.seq_len = seq_len; ses.q_rows = 1; ses.kv_start = kv_start;
+    ses.n_parts = parts; ses.partial_base = 0; ses.ring_capacity = 0; ses.keep = nullptr; ses.row_index = nullptr;
     const uint32_t group = n_q_heads / n_kv_heads;
-    uint32_t cursor = 0;
-    for (uint32_t part = 0; part < parts; ++part) {
-        const uint32_t kb = kv_start + part * keys_per_item;
-        uint32_t ke = kb + keys_per_item;
-        if (ke > seq_len) ke = seq_len;
-        if (ke < kb) ke = kb;
-        for (uint32_t kvh = 0; kvh < n_kv_heads; ++kvh)
-            for (uint32_t rb = 0; rb < group; rb += 16) {
-                if (cursor >= kNoAllocMaxItems) return TT_ERR_UNSUPPORTED_SHAPE;
-                TTDecodeItem &it = host.items[cursor++];
-                it.session = 0; it.kv_head = kvh; it.key_begin = kb; it.key_end = ke; it.part_index = part;
-                it.row_begin = rb; it.row_count = group - rb < 16 ? group - rb : 16; it.partial_base = 0;
-            }
-    }
+    const uint32_t grid = parts * n_kv_heads * ceil_div_u32(group, 16);
 
     cudaStream_t s = (cudaStream_t)stream;
     uint32_t *status = reinterpret_cast<uint32_t *>(scratch);
-    TTDecodeSession *d_ses = reinterpret_cast<TTDecodeSession *>(scratch + 256);
-    TTDecodeItem *d_items = reinterpret_cast<TTDecodeItem *>(scratch + 256 + sizeof(TTDecodeSession));
     float *part_o = reinterpret_cast<float *>(scratch + kNoAllocPartialOffset);
     float *part_m = part_o + partial_rows * head_dim;
     float *part_l = part_m + partial_rows;
     if (cudaMemsetAsync(status, 0, sizeof(uint32_t), s) != cudaSuccess) return TT_ERR_CUDA;
-    // host.ses and host.items are contiguous on the host and in the array: one copy (the source is
-    // pageable stack memory, so the driver has staged it by the time the call returns)
-    if (cudaMemcpyAsync(d_ses, &host, sizeof(TTDecodeSession) + sizeof(TTDecodeItem) * cursor, cudaMemcpyHostToDevice, s) !=
-        cudaSuccess)
-        return TT_ERR_CUDA;
     tt_attn_batch_params p;
     p.head_dim = head_dim; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
     p.kv_token_stride_elements = n_kv_heads * head_dim; p.q_row_stride_elements = n_q_heads * head_dim;
     p.out_row_stride_elements = n_q_heads * head_dim; p.scale = scale; p.io_dtype = TT_F16;
-    if (launch_partial_hd<__half>(s, cursor, d_items, d_ses, part_o, part_m, part_l, &p, status) != cudaSuccess)
+    if (launch_partial_hd<__half>(s, grid, nullptr, nullptr, part_o, part_m, part_l, &p, status, ses, keys_per_item) !=
+        cudaSuccess)
         return TT_ERR_CUDA;
     attn_decode_combine_kernel<__half><<<dim3(1, n_q_heads, (head_dim / 4 + 15) / 16), 256, 0, s>>>(
-        d_ses, part_o, part_m, part_l, n_q_heads, head_dim, n_q_heads * head_dim, 0, nullptr, nullptr, nullptr, host.ses,
-        0, 16u);
+        nullptr, part_o, part_m, part_l, n_q_heads, head_dim, n_q_heads * head_dim, 0, nullptr, nullptr, nullptr, ses,
+        1, 16u);
     return cudaGetLastError() == cudaSuccess ? TT_OK : TT_ERR_CUDA;
+}
+
+// The status word of the allocation-free entry point on the current device: waits for `stream`,
+// then reads the word the last tt_attn_decode_noalloc call on this device cleared and its kernels
+// may have set (bit 0: a bounded wait inside a kernel ran out and that call's output is not valid).
+TT_API int tt_attn_decode_noalloc_status(tt_stream stream, uint32_t *out_flags) {
+    if (out_flags == nullptr) return TT_ERR_INVALID_ARG;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return TT_ERR_CUDA;
+    if (device < 0 || device >= kNoAllocMaxDevices) return TT_ERR_UNSUPPORTED_SHAPE;
+    unsigned char *scratch = nullptr;
+    if (noalloc_scratch(device, &scratch) != cudaSuccess || scratch == nullptr) return TT_ERR_CUDA;
+    if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) return TT_ERR_CUDA;
+    if (cudaMemcpy(out_flags, scratch, sizeof(uint32_t), cudaMemcpyDeviceToHost) != cudaSuccess) return TT_ERR_CUDA;
+    return TT_OK;
 }

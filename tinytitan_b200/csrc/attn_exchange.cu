@@ -49,6 +49,7 @@ struct ExchangeParams {
     const float *part_o, *part_m, *part_l;
     uint32_t n_parts;
     uint32_t rank, world, n_q_heads, head_dim, epoch;
+    uint32_t poll_limit;   // polls of ~0.25 us before the flag wait gives up
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
@@ -94,7 +95,7 @@ __device__ __forceinline__ void exchange_and_merge(const ExchangeParams &p, uint
         const uint32_t *flag = reinterpret_cast<const uint32_t *>(mine + l.flags_offset) +
                                ((size_t)tid * p.n_q_heads + h) * l.col_blocks + cb;
         bool ok = false;
-        for (uint32_t it = 0; it < kPollLimit; ++it) {
+        for (uint32_t it = 0; it < p.poll_limit; ++it) {
             if (ld_acquire_sys(flag) == p.epoch) { ok = true; break; }
             __nanosleep(64);
         }
@@ -234,6 +235,7 @@ int fill_params(tt_context *ctx, ExchangeParams &p, void *const *peer_buffers, u
     p.m = p.d = p.o = p.part_o = p.part_m = p.part_l = nullptr;
     p.n_parts = 0;
     p.rank = rank; p.world = world; p.n_q_heads = n_q_heads; p.head_dim = head_dim; p.epoch = epoch;
+    p.poll_limit = ctx->exchange_poll_limit ? ctx->exchange_poll_limit : kPollLimit;
     return TT_OK;
 }
 
@@ -256,6 +258,12 @@ int tt_launch_merge_exchange(tt_context *ctx, cudaStream_t stream, const float *
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_merge_exchange launch");
     ctx->launches++;
+    return TT_OK;
+}
+
+TT_API int tt_ctx_set_exchange_poll_limit(tt_context *ctx, uint32_t polls) {
+    if (ctx == nullptr) return TT_ERR_INVALID_ARG;
+    ctx->exchange_poll_limit = polls;   // 0 selects the default
     return TT_OK;
 }
 

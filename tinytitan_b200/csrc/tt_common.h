@@ -77,6 +77,7 @@ struct tt_context {
     uint32_t *h_rows = nullptr;
     void *h_tensor_maps = nullptr;
     uint64_t launches = 0;
+    uint32_t exchange_poll_limit = 0;   // 0: the exchange kernels' default (about a second)
     // last verify split plan: the part length only depends on the sessions' 128-key tile counts and
     // row counts, which stay the same for up to 128 consecutive decode steps
     std::vector<uint32_t> verify_plan_key;

@@ -14,7 +14,7 @@ from dataclasses import dataclass, field
 from typing import List, Optional
 
 from . import _lib as L
-from .operators import LinearAttentionConfig
+from .operators import LinearAttentionConfig, _stream
 
 SWA, FULL, LINEAR = 0, 1, 2
 
@@ -138,6 +138,10 @@ class KVCacheManager:
     def worst_case_bytes(config: ArchConfig, max_context: int, precision: int = 16, slots: int = 1) -> int:
         arch = config.to_c()
         return int(L.lib().tt_kv_cache_worst_case_bytes(C.byref(arch), max_context, precision, slots))
+
+    def bind_stream(self, command_buffer):
+        """Row copies of reserve() are enqueued on this stream from now on instead of the legacy default stream."""
+        L.check(L.lib().tt_kv_cache_bind_stream(self.handle, _stream(command_buffer)))
 
     def reserve(self, tokens: int, slot: int = 0):
         L.check(L.lib().tt_kv_cache_reserve(self.handle, tokens, slot))
@@ -270,8 +274,14 @@ class GDNStateManager:
         else:
             L.check(L.lib().tt_gdn_state_reset_slot(self.handle, slot))
 
-    def speculative_restore(self):
-        L.check(L.lib().tt_gdn_state_speculative_restore(self.handle))
+    def speculative_restore(self, command_buffer=None):
+        """encodeSpeculativeRestore(commandBuffer:): enqueued on the verify pass's stream."""
+        stream = 0 if self._allocator is not None else _stream(command_buffer)   # host-backed: no stream
+        L.check(L.lib().tt_gdn_state_speculative_restore(self.handle, stream))
+
+    def bind_stream(self, command_buffer):
+        """Zero fills (reset) are enqueued on this stream from now on instead of the legacy default stream."""
+        L.check(L.lib().tt_gdn_state_bind_stream(self.handle, _stream(command_buffer)))
 
     def snapshot(self) -> bytes:
         """[state, conv tail] of slot 0 for every linear layer (GDNStateManager.swift:228-261)."""

@@ -93,6 +93,10 @@ class Context:
         self.check(L.lib().tt_ctx_profile_collect(self.handle, buf, 256, C.byref(n)))
         return [buf[i] for i in range(n.value)]
 
+    def set_exchange_poll_limit(self, polls: int):
+        """Polls (~0.25 us each) the exchange kernels wait for peers before giving up; 0 = default."""
+        self.check(L.lib().tt_ctx_set_exchange_poll_limit(self.handle, polls))
+
     @property
     def launch_count(self) -> int:
         return int(L.lib().tt_ctx_launch_count(self.handle))
