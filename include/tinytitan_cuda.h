@@ -344,6 +344,63 @@ int tt_attn_prefill_causal(tt_context *ctx, tt_stream stream, const void *q, con
 /* Which kernel the call above would take: 0 generic, 1 tcgen05. */
 int tt_attn_prefill_path(const void *q, const void *k, const void *v, const void *out,
                          const tt_prefill_params *params, uint32_t kv_ring_capacity);
+/* PrefillAttention.encodeCausal with a per-query key selection (its keepMask / keepIndices /
+ * keepCounts / keepRows arguments, PrefillAttention.swift:165-258; kernel
+ * attention_prefill_causal_qsa_tiled, prefill.metal:898-1054). What is bound selects the form, as
+ * in the reference: keep_indices + keep_counts = a compact list of logical keys per query row
+ * (keep_indices[t * keep_index_stride + i], i < keep_counts[t]; entries outside the row's visible
+ * range [first, last) are dropped); with keep_rows as well, keep_rows[...] names the cache row
+ * that holds each listed key (host-KV window, tt_kv_window_prepare_prefill); otherwise keep_mask
+ * is one byte per key, keep_mask[t * keep_stride + key] != 0 keeps it. All NULL = the dense call.
+ * A row whose keys are all dropped is written as zeros. Selections run on the generic kernel. */
+int tt_attn_prefill_causal_selected(tt_context *ctx, tt_stream stream, const void *q, const void *k,
+                                    const void *v, void *out, const tt_prefill_params *params,
+                                    uint32_t kv_ring_capacity, uint32_t io_dtype,
+                                    const uint8_t *keep_mask, uint32_t keep_stride,
+                                    const uint32_t *keep_indices, uint32_t keep_index_stride,
+                                    const uint32_t *keep_counts, const uint32_t *keep_rows);
+
+/* ----------------------------------------- sparse-attention block indexer */
+
+/* QSAIndexer's device work (sources/TinyTitan/Kernels/Attention/QSAIndexer.swift,
+ * QSAIndexer+Scratch.swift; kernels sources/TinyTitanCore/Metal/Attention/qsa.metal:1-226).
+ * The caller owns the caches, as the Swift class does: raw indexer keys fp16 [cells][head_dim]
+ * (before norm and rotation), pooled blocks fp16 [cells / ratio + 1][head_dim], scores fp32.
+ *
+ * tt_qsa_pool_blocks: blocks first_block .. first_block + block_count - 1 become the mean of
+ * their raw members present below n_kv (a ragged last block divides by its own count), then --
+ * when key_norm_weight (bf16 [head_dim]) is given -- the RMS norm and the NeoX rotation over
+ * the whole row at position block * ratio, the three launches of encodePoolPrefill
+ * (QSAIndexer.swift:196-238) / encodeAppendKey (QSAIndexer+Scratch.swift:92-122) in one.
+ * head_dim a multiple of 64, at most 512. */
+int tt_qsa_pool_blocks(tt_context *ctx, tt_stream stream, const void *raw_keys, void *pooled,
+                       uint32_t head_dim, uint32_t first_block, uint32_t block_count,
+                       uint32_t ratio, uint32_t n_kv, const void *key_norm_weight, float eps,
+                       float theta);
+/* The indexer query after its projection: per-head RMS norm (bf16 weight) and NeoX rotation of
+ * the whole head, in place over fp16 [rows][heads][head_dim]; row r is at position + r
+ * (encodeScores / encodeScoresPrefill, QSAIndexer.swift:259-274, :322-337). */
+int tt_qsa_query_norm_rope(tt_context *ctx, tt_stream stream, void *query, uint32_t head_dim,
+                           uint32_t heads, uint32_t rows, uint32_t position,
+                           const void *query_norm_weight, float eps, float theta);
+/* qsa_block_scores / qsa_block_scores_rows (qsa.metal:67-126): scores[t * score_stride + b] =
+ * sum over heads of max(0, query[t][h] . pooled[b]) for b < blocks, t < rows. */
+int tt_qsa_block_scores(tt_context *ctx, tt_stream stream, const void *query, const void *pooled,
+                        float *scores, uint32_t head_dim, uint32_t heads, uint32_t blocks,
+                        uint32_t rows, uint32_t score_stride);
+/* The key selection of `rows` query rows, row r seeing keys [0, start_position + r + 1)
+ * (selectKeys / selectKeysCompact, QSAIndexer+Scratch.swift:178-251; selectKeysPrefill,
+ * QSAIndexer.swift:391-498; qsa_select_decode, qsa.metal:128-226). A row with at most `width`
+ * (= budget + ratio - 1) visible keys keeps them all. Otherwise the ragged tail of its own block
+ * is kept, then complete blocks by score descending (ties to the lower block index) while the
+ * cell budget lasts, the last admitted block cut to the cells that remain. Outputs, each
+ * optional: keep[r * keep_stride + key] bytes (cells past the row's position are cleared up to
+ * keep_stride); indices[r * index_stride + i] the kept keys in ascending order, at most
+ * index_stride of them, with counts[r]. One decode step is rows = 1, start_position = visible - 1. */
+int tt_qsa_select_keys(tt_context *ctx, tt_stream stream, const float *scores,
+                       uint32_t score_stride, uint32_t start_position, uint32_t rows,
+                       uint32_t ratio, uint32_t width, uint8_t *keep, uint32_t keep_stride,
+                       uint32_t *indices, uint32_t index_stride, uint32_t *counts);
 
 /* ------------------------------------------------------ Gated DeltaNet ops */
 
@@ -533,6 +590,63 @@ size_t tt_kv_cache_worst_case_bytes(const tt_arch *arch, uint32_t max_context,
 size_t tt_kv_cache_snapshot_bytes(const tt_kv_cache *cache, uint32_t position);
 int tt_kv_cache_snapshot_export(tt_kv_cache *cache, void *host_dst, size_t capacity, size_t *out_bytes);
 int tt_kv_cache_snapshot_restore(tt_kv_cache *cache, uint32_t position, const void *host_src, size_t bytes);
+
+/* Host-KV streaming tier (KVCacheManager+HostStreaming.swift:33-364,
+ * KVCacheManager+HostStreamingPrefill.swift:12-436): for `n_layers` streamed (full-attention)
+ * layers the authoritative K/V rows live in a host arena [slots][max_context][stride]; device
+ * memory holds only a window of min(window_tokens, max_context) rows per (layer, slot), filled
+ * on demand with clock-hand eviction and write-back of dirty rows. Attention reads the window
+ * through (logical key, window row) lists: tt_attn_decode_window takes the rows of a decode step,
+ * tt_attn_prefill_causal_selected (keep_rows) those of a prefill chunk. `allocator` supplies the
+ * window and staging memory and the arena<->window copies (NULL = CUDA device memory, synchronous
+ * copies on the legacy default stream; the bookkeeping runs between steps, like the reference's,
+ * which touches its shared buffers from the CPU between command buffers).
+ *   _write_slot      kSlot / vSlot of a streamed layer: where the projection writes a position
+ *                    (a window row, made dirty and pinned for the step; inside an active prefill
+ *                    staging range, the staging row)
+ *   _prepare_decode  prepareDecodeWindow: `indices` (host, ascending logical keys; NULL = all keys
+ *                    0..count-1) made resident; out_indices / out_rows (host, count entries).
+ *                    TT_ERR_OOM when the selection does not fit the window
+ *   _begin_prefill   beginPrefillWrite: staging rows for a chunk, [token_count][stride]
+ *   _prepare_prefill preparePrefillWindow: the union of the chunk's per-row selections
+ *                    (sel_indices[t * sel_index_stride + i], i < sel_counts[t]; NULL = dense) made
+ *                    resident, staged rows copied into the window, per-row lists written with
+ *                    out_index_stride entries per row
+ *   _commit          commitStreamedRows (called with advance): rows reach the arena
+ *   _reset_slot      resetStreamedWindow
+ *   _host_row        one arena row (hostRowBytes); _counters: evictions, rows copied in, bytes */
+typedef struct tt_kv_window tt_kv_window;
+tt_kv_window *tt_kv_window_create(uint32_t n_layers, uint32_t stride_bytes, uint32_t max_context,
+                                  uint32_t slots, uint32_t window_tokens,
+                                  const tt_allocator *allocator, int *out_err);
+void tt_kv_window_destroy(tt_kv_window *window);
+size_t tt_kv_window_bytes(const tt_kv_window *window);
+size_t tt_kv_window_host_arena_bytes(const tt_kv_window *window);
+uint32_t tt_kv_window_tokens(const tt_kv_window *window);
+uint32_t tt_kv_window_prefill_chunk_tokens(const tt_kv_window *window, uint32_t configured,
+                                           uint32_t selection_width);
+int tt_kv_window_base(tt_kv_window *window, uint32_t layer, uint32_t slot, void **out_k, void **out_v);
+int tt_kv_window_write_slot(tt_kv_window *window, uint32_t layer, uint32_t position, uint32_t slot,
+                            void **out_k, void **out_v);
+int tt_kv_window_row_of(tt_kv_window *window, uint32_t layer, uint32_t slot, uint32_t position,
+                        int64_t *out_row);
+int tt_kv_window_prepare_decode(tt_kv_window *window, uint32_t layer, uint32_t slot, uint32_t position,
+                                const uint32_t *indices, uint32_t count, uint32_t *out_indices,
+                                uint32_t *out_rows);
+int tt_kv_window_begin_prefill(tt_kv_window *window, uint32_t layer, uint32_t slot,
+                               uint32_t start_position, uint32_t token_count, void **out_stage_k,
+                               void **out_stage_v);
+int tt_kv_window_prepare_prefill(tt_kv_window *window, uint32_t layer, uint32_t slot,
+                                 uint32_t start_position, uint32_t token_count,
+                                 const uint32_t *sel_indices, uint32_t sel_index_stride,
+                                 const uint32_t *sel_counts, uint32_t *out_indices,
+                                 uint32_t *out_rows, uint32_t *out_counts, uint32_t out_index_stride);
+int tt_kv_window_commit(tt_kv_window *window, uint32_t slot, uint32_t position, uint32_t count);
+int tt_kv_window_reset_slot(tt_kv_window *window, uint32_t slot);
+int tt_kv_window_host_row(tt_kv_window *window, uint32_t layer, uint32_t slot, uint32_t position,
+                          int key, void *dst);
+void tt_kv_window_counters(const tt_kv_window *window, uint64_t *out_evictions,
+                           uint64_t *out_row_copies, uint64_t *out_copy_bytes);
 
 /* GDNStateManager (sources/TinyTitan/Runtime/KVCache/GDNStateManager.swift:
  * 18-354): per linear layer a zero-initialised fp32 state buffer of

@@ -421,3 +421,83 @@ def kv_quantize_rows(rows, bits: int, group_size: int = 64):
             byte[:, :hi.shape[1]] |= (hi << 4)
             out[:, cols[0] // 2:cols[0] // 2 + byte.shape[1]] = byte
     return out, deq, stride, value_bytes
+
+
+# --------------------------------------------------------------------------
+# Qwen Sparse Attention's block indexer (numpy). Follows
+# sources/TinyTitanCore/Metal/Attention/qsa.metal:14-126 (pool: mean of the raw members present,
+# stored fp16; scores: sum over heads of max(0, q.pooled)), the norm and rotation the host encodes
+# after pooling (QSAIndexer.swift:196-238: rmsnorm_bf16w_perhead then rope_neox_subdim_strided with
+# rotary = head_dim at position block * ratio) and the selection rule of
+# QSAIndexer+Scratch.swift:211-251 (selectKeys) / QSAIndexer.swift:391-498 (selectKeysPrefill).
+# --------------------------------------------------------------------------
+def qsa_pool_blocks(raw, ratio: int, n_kv: int, first_block: int, block_count: int, weight=None,
+                    eps: float = 1e-6, theta: float = 1e7):
+    """raw fp32 [cells, D] (fp16-representable). Returns {block: pooled row} for the blocks that exist."""
+    raw = _f(raw)
+    out = {}
+    for block in range(first_block, first_block + block_count):
+        first = block * ratio
+        if first >= n_kv:
+            continue
+        count = min(ratio, n_kv - first)
+        acc = np.zeros(raw.shape[1], np.float32)
+        for m in range(count):
+            acc = acc + raw[first + m]
+        row = _half(acc / np.float32(count))
+        if weight is not None:
+            row = attn_norm_rope(row, weight, eps, raw.shape[1], theta, block * ratio)
+        out[block] = row
+    return out
+
+
+def qsa_block_scores(query, pooled):
+    """query [T, H, D], pooled [B, D] -> scores [T, B] = sum_h max(0, q[t,h] . pooled[b])."""
+    q, p = _f(query), _f(pooled)
+    dots = np.einsum("thd,bd->thb", q.astype(np.float64), p.astype(np.float64))
+    return np.maximum(dots, 0.0).sum(axis=1).astype(np.float32)
+
+
+def qsa_select_keys(scores, visible: int, ratio: int, width: int):
+    """One query's selection. Returns (keep uint8 [visible], ascending kept indices capped at `width`)."""
+    keep = np.zeros(visible, np.uint8)
+    if visible <= width:
+        keep[:] = 1
+        return keep, np.arange(visible, dtype=np.uint32)
+    complete = (visible // ratio) * ratio
+    keep[complete:] = 1                                   # the query's own ragged tail
+    remaining = width - (visible - complete)
+    if remaining > 0:
+        blocks = complete // ratio
+        s = np.asarray(scores, np.float32)[:blocks] + np.float32(0)   # -0.0 ties +0.0
+        ranked = sorted(range(blocks), key=lambda b: (-float(s[b]), b))
+        for block in ranked:
+            if remaining <= 0:
+                break
+            take = min(ratio, remaining)
+            keep[block * ratio:block * ratio + take] = 1
+            remaining -= take
+    return keep, np.nonzero(keep)[0].astype(np.uint32)[:width]
+
+
+def attn_prefill_selected(q, k, v, head_dim, q_heads, kv_heads, start, kv_valid, window, scale, keys_of_row,
+                          rows_of_row=None):
+    """Causal prefill where query row t attends only the logical keys keys_of_row[t] that fall in its
+    visible range; rows_of_row[t][i] (optional) is the cache row holding keys_of_row[t][i]
+    (attention_prefill_causal_qsa_tiled, prefill.metal:914-1054). q [T, Hq*hd], k/v [rows, Hkv*hd]."""
+    q, k, v = _f(q), _f(k), _f(v)
+    t_count = q.shape[0]
+    out = np.zeros((t_count, q_heads, head_dim), np.float32)
+    for t in range(t_count):
+        abs_q = start + t
+        first = abs_q + 1 - window if (window != 0 and abs_q + 1 > window) else 0
+        last = min(kv_valid, abs_q + 1)
+        keys = np.asarray(keys_of_row[t], np.int64)
+        phys = keys if rows_of_row is None else np.asarray(rows_of_row[t], np.int64)
+        ok = (keys >= first) & (keys < last)
+        if not ok.any():
+            continue
+        kk = k[phys[ok]].reshape(-1, kv_heads, head_dim)
+        vv = v[phys[ok]].reshape(-1, kv_heads, head_dim)
+        out[t] = attn_decode(q[t].reshape(q_heads, head_dim), kk, vv, kv_heads, scale)
+    return out

@@ -143,7 +143,10 @@ def test_config3_prefill_sampled_rows_both_kernels(dtype):
         want = oracle.attn_prefill(f32(q[start:start + 64]), kf, vf, hq * hd, hkv * hd, hd, hq, hkv, start, 64, T, 0,
                                    SCALE).reshape(64, -1)
         for name, o in outs.items():
-            tol = TOL if dtype == torch.float16 else bf16_tol(want)
+            # bf16 I/O: the output carries one bf16 rounding of its own value, and the tensor-core kernel's
+            # softmax weights are bf16 too (both operands of one tcgen05.mma share a format): 2^-9
+            # relative on each weight, which over a row's few keys does not average out
+            tol = TOL if dtype == torch.float16 else bf16_tol(want) + 2.0 ** -9 * np.abs(vf).max()
             report(f"config 3 prefill {name} {str(dtype)[6:]} rows {start}..{start + 63}", f32(o[start:start + 64]), want,
                    tol=tol, ref_abs=2e-2, ref_rel=2e-2)
 

@@ -132,6 +132,28 @@ SIGNATURES = {
     "tt_attn_decode_exchange": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.c_float, _u32, _u32,
                                           C.POINTER(AttnExchange)]),
     "tt_attn_decode_noalloc": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.c_float]),
+    "tt_attn_prefill_causal_selected": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(PrefillParams), _u32, _u32, _vp, _u32,
+                                                  _vp, _u32, _vp, _vp]),
+    "tt_qsa_pool_blocks": (C.c_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, C.c_float, C.c_float]),
+    "tt_qsa_query_norm_rope": (C.c_int, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, C.c_float, C.c_float]),
+    "tt_qsa_block_scores": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32]),
+    "tt_qsa_select_keys": (C.c_int, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _u32, _vp, _u32, _vp]),
+    "tt_kv_window_create": (_vp, [_u32, _u32, _u32, _u32, _u32, C.POINTER(Allocator), C.POINTER(C.c_int)]),
+    "tt_kv_window_destroy": (None, [_vp]),
+    "tt_kv_window_bytes": (C.c_size_t, [_vp]),
+    "tt_kv_window_host_arena_bytes": (C.c_size_t, [_vp]),
+    "tt_kv_window_tokens": (_u32, [_vp]),
+    "tt_kv_window_prefill_chunk_tokens": (_u32, [_vp, _u32, _u32]),
+    "tt_kv_window_base": (C.c_int, [_vp, _u32, _u32, C.POINTER(_vp), C.POINTER(_vp)]),
+    "tt_kv_window_write_slot": (C.c_int, [_vp, _u32, _u32, _u32, C.POINTER(_vp), C.POINTER(_vp)]),
+    "tt_kv_window_row_of": (C.c_int, [_vp, _u32, _u32, _u32, C.POINTER(C.c_int64)]),
+    "tt_kv_window_prepare_decode": (C.c_int, [_vp, _u32, _u32, _u32, _vp, _u32, _vp, _vp]),
+    "tt_kv_window_begin_prefill": (C.c_int, [_vp, _u32, _u32, _u32, _u32, C.POINTER(_vp), C.POINTER(_vp)]),
+    "tt_kv_window_prepare_prefill": (C.c_int, [_vp, _u32, _u32, _u32, _u32, _vp, _u32, _vp, _vp, _vp, _vp, _u32]),
+    "tt_kv_window_commit": (C.c_int, [_vp, _u32, _u32, _u32]),
+    "tt_kv_window_reset_slot": (C.c_int, [_vp, _u32]),
+    "tt_kv_window_host_row": (C.c_int, [_vp, _u32, _u32, _u32, C.c_int, _vp]),
+    "tt_kv_window_counters": (None, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "tt_ctx_set_exchange_poll_limit": (C.c_int, [_vp, _u32]),
     "tt_attn_decode_noalloc_status": (C.c_int, [_vp, C.POINTER(_u32)]),
     "tt_attn_reference_split_geometry": (None, [_u32, _u32, _u32, _u32, C.c_int, C.POINTER(SplitGeometry)]),

@@ -51,6 +51,21 @@ __device__ __forceinline__ float load_kv(const T *cache, uint32_t row, uint32_t 
     return (float)code * __half2float(scales[g]) + __half2float(scales[groups + g]);
 }
 
+// A per-query key selection (the `useKeep` modes of attention_prefill_causal_qsa_tiled,
+// sources/TinyTitanCore/Metal/Prefill/prefill.metal:914-1054): 0 every visible key; 1 a byte mask
+// keep[t * keep_stride + key]; 2 a compact list indices[t * index_stride + i], i < counts[t], of logical
+// keys (entries outside the row's visible range are dropped); 3 the same list with rows[...] giving the
+// cache row that holds each key (host-KV window).
+struct PrefillSelection {
+    uint32_t mode;
+    const uint8_t *keep;
+    uint32_t keep_stride;
+    const uint32_t *indices;
+    const uint32_t *counts;
+    uint32_t index_stride;
+    const uint32_t *rows;
+};
+
 // One warp per (query row, q head). Keys are taken 32 at a time: lane j scores key j (a full
 // head_dim dot product against the query held in shared memory), the tile's softmax update is
 // done with warp reductions, then every lane accumulates its own output dimensions over the
@@ -58,7 +73,7 @@ __device__ __forceinline__ float load_kv(const T *cache, uint32_t row, uint32_t 
 template <typename T>
 __global__ void __launch_bounds__(kGenericWarps * 32)
 attn_prefill_generic_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
-                            T *__restrict__ out, tt_prefill_params p, uint32_t ring) {
+                            T *__restrict__ out, tt_prefill_params p, uint32_t ring, PrefillSelection sel) {
     __shared__ float q_s[kGenericWarps][kMaxHeadDim];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t pair = blockIdx.x * kGenericWarps + warp;
@@ -81,26 +96,43 @@ attn_prefill_generic_kernel(const T *__restrict__ q, const T *__restrict__ k, co
     for (int i = 0; i < kPerLane; ++i) acc[i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
 
-    for (uint32_t key0 = first; key0 < last; key0 += 32) {
-        const uint32_t key = key0 + lane;
+    // steps of the row: visible keys, or the entries of its compact list
+    const bool compact = sel.mode >= 2;
+    const uint32_t steps = compact ? sel.counts[t] : (last > first ? last - first : 0u);
+    for (uint32_t step0 = 0; step0 < steps; step0 += 32) {
+        const uint32_t step = step0 + lane;
         float s = -INFINITY;
-        if (key < last) {
-            const uint32_t phys = ring ? key % ring : key;
-            float dot = 0.f;
-            if (p.kv_bits == 16) {
-                const T *kr = k + (size_t)phys * p.kv_token_stride_elements + (size_t)kvh * hd;
-                for (uint32_t d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], to_f32<T>(kr[d]), dot);
+        uint32_t phys = 0;
+        if (step < steps) {
+            uint32_t key;
+            bool valid;
+            if (compact) {
+                key = sel.indices[(size_t)t * sel.index_stride + step];
+                valid = key >= first && key < last;
+                phys = sel.mode == 3 ? sel.rows[(size_t)t * sel.index_stride + step] : (ring ? key % ring : key);
             } else {
-                for (uint32_t d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], load_kv<T>(k, phys, kvh * hd + d, p), dot);
+                key = first + step;
+                valid = sel.mode == 0 || sel.keep[(size_t)t * sel.keep_stride + key] != 0;
+                phys = ring ? key % ring : key;
             }
-            s = dot;
+            if (valid) {
+                float dot = 0.f;
+                if (p.kv_bits == 16) {
+                    const T *kr = k + (size_t)phys * p.kv_token_stride_elements + (size_t)kvh * hd;
+                    for (uint32_t d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], to_f32<T>(kr[d]), dot);
+                } else {
+                    for (uint32_t d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], load_kv<T>(k, phys, kvh * hd + d, p), dot);
+                }
+                s = dot;
+            }
         }
         float mx = s;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        const float m_new = fmaxf(m_run, mx);          // finite: at least one key of the tile is valid
-        const float alpha = __expf(m_run - m_new);     // exp(-inf) == 0 on the first tile
-        const float pe = (key < last) ? __expf(s - m_new) : 0.f;
+        const float m_new = fmaxf(m_run, mx);
+        if (m_new == -INFINITY) continue;              // every key so far was dropped: nothing to carry (prefill.metal:1013-1020)
+        const float alpha = __expf(m_run - m_new);     // exp(-inf) == 0 on the first contributing tile
+        const float pe = (s != -INFINITY) ? __expf(s - m_new) : 0.f;
         float ps = pe;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
@@ -108,15 +140,15 @@ attn_prefill_generic_kernel(const T *__restrict__ q, const T *__restrict__ k, co
         m_run = m_new;
 #pragma unroll
         for (int i = 0; i < kPerLane; ++i) acc[i] *= alpha;
-        const uint32_t n = min(32u, last - key0);
+        const uint32_t n = min(32u, steps - step0);
         for (uint32_t j = 0; j < n; ++j) {
             const float pj = __shfl_sync(0xffffffffu, pe, j);
-            const uint32_t kj = key0 + j;
-            const uint32_t phys = ring ? kj % ring : kj;
+            const uint32_t pr = __shfl_sync(0xffffffffu, phys, j);
+            if (pj == 0.f) continue;                   // dropped keys are never read
 #pragma unroll
             for (int i = 0; i < kPerLane; ++i) {
                 const uint32_t d = lane + 32 * i;
-                if (d < hd) acc[i] = fmaf(pj, load_kv<T>(v, phys, kvh * hd + d, p), acc[i]);
+                if (d < hd) acc[i] = fmaf(pj, load_kv<T>(v, pr, kvh * hd + d, p), acc[i]);
             }
         }
     }
@@ -179,6 +211,24 @@ TT_API int tt_attn_prefill_path(const void *q, const void *k, const void *v, con
     return (aligned && p->head_dim == 256 && kv_ring_capacity == 0 && p->kv_bits == 16 && p->scale > 0.f) ? 1 : 0;
 }
 
+static int launch_generic(tt_context *ctx, cudaStream_t stream, const void *q, const void *k, const void *v, void *out,
+                          const tt_prefill_params *params, uint32_t kv_ring_capacity, uint32_t io_dtype,
+                          const PrefillSelection &sel) {
+    const uint32_t pairs = params->query_count * params->n_q_heads;
+    const uint32_t blocks = (pairs + kGenericWarps - 1) / kGenericWarps;
+    if (io_dtype == TT_F16)
+        attn_prefill_generic_kernel<__half><<<blocks, kGenericWarps * 32, 0, stream>>>(
+            (const __half *)q, (const __half *)k, (const __half *)v, (__half *)out, *params, kv_ring_capacity, sel);
+    else
+        attn_prefill_generic_kernel<__nv_bfloat16><<<blocks, kGenericWarps * 32, 0, stream>>>(
+            (const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v, (__nv_bfloat16 *)out,
+            *params, kv_ring_capacity, sel);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_prefill_generic launch");
+    ctx->launches++;
+    return TT_OK;
+}
+
 TT_API int tt_attn_prefill_causal(tt_context *ctx, tt_stream stream, const void *q, const void *k, const void *v,
                                   void *out, const tt_prefill_params *params, uint32_t kv_ring_capacity,
                                   uint32_t io_dtype) {
@@ -187,17 +237,32 @@ TT_API int tt_attn_prefill_causal(tt_context *ctx, tt_stream stream, const void 
     if (rc != TT_OK) return rc;
     if (tt_attn_prefill_path(q, k, v, out, params, kv_ring_capacity) == 1 && getenv("TT_PREFILL_FORCE_GENERIC") == nullptr)
         return tt_launch_prefill_tc(ctx, (cudaStream_t)stream, q, k, v, out, params, io_dtype);
-    const uint32_t pairs = params->query_count * params->n_q_heads;
-    const uint32_t blocks = (pairs + kGenericWarps - 1) / kGenericWarps;
-    if (io_dtype == TT_F16)
-        attn_prefill_generic_kernel<__half><<<blocks, kGenericWarps * 32, 0, (cudaStream_t)stream>>>(
-            (const __half *)q, (const __half *)k, (const __half *)v, (__half *)out, *params, kv_ring_capacity);
-    else
-        attn_prefill_generic_kernel<__nv_bfloat16><<<blocks, kGenericWarps * 32, 0, (cudaStream_t)stream>>>(
-            (const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v, (__nv_bfloat16 *)out,
-            *params, kv_ring_capacity);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_prefill_generic launch");
-    ctx->launches++;
-    return TT_OK;
+    PrefillSelection none = {0, nullptr, 0, nullptr, nullptr, 0, nullptr};
+    return launch_generic(ctx, (cudaStream_t)stream, q, k, v, out, params, kv_ring_capacity, io_dtype, none);
+}
+
+TT_API int tt_attn_prefill_causal_selected(tt_context *ctx, tt_stream stream, const void *q, const void *k, const void *v,
+                                           void *out, const tt_prefill_params *params, uint32_t kv_ring_capacity,
+                                           uint32_t io_dtype, const uint8_t *keep_mask, uint32_t keep_stride,
+                                           const uint32_t *keep_indices, uint32_t keep_index_stride,
+                                           const uint32_t *keep_counts, const uint32_t *keep_rows) {
+    TT_ENTER(ctx);
+    int rc = validate_prefill(ctx, q, k, v, out, params, io_dtype);
+    if (rc != TT_OK) return rc;
+    // the mode follows from what was bound, as in PrefillAttention.encodeCausal (PrefillAttention.swift:214-226)
+    PrefillSelection sel = {0, keep_mask, keep_stride, keep_indices, keep_counts, keep_index_stride, keep_rows};
+    const bool compacted = keep_indices != nullptr && keep_counts != nullptr;
+    if (compacted) sel.mode = keep_rows != nullptr ? 3u : 2u;
+    else if (keep_mask != nullptr) sel.mode = 1u;
+    else if (keep_indices != nullptr || keep_counts != nullptr || keep_rows != nullptr)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "a compact selection needs both its index list and its counts");
+    if (sel.mode == 1 && keep_stride < params->kv_valid_count && keep_stride < params->start_position + params->query_count)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "keep mask stride does not cover the visible keys");
+    if (sel.mode >= 2 && keep_index_stride == 0)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "compact selection with a zero index stride");
+    if (sel.mode == 0) {
+        if (tt_attn_prefill_path(q, k, v, out, params, kv_ring_capacity) == 1 && getenv("TT_PREFILL_FORCE_GENERIC") == nullptr)
+            return tt_launch_prefill_tc(ctx, (cudaStream_t)stream, q, k, v, out, params, io_dtype);
+    }
+    return launch_generic(ctx, (cudaStream_t)stream, q, k, v, out, params, kv_ring_capacity, io_dtype, sel);
 }

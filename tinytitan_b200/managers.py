@@ -293,3 +293,110 @@ class GDNStateManager:
 
     def restore_snapshot(self, payload: bytes):
         L.check(L.lib().tt_gdn_state_snapshot_restore(self.handle, payload, len(payload)))
+
+
+class KVWindow:
+    """Host-KV streaming tier of KVCacheManager (KVCacheManager+HostStreaming.swift,
+    +HostStreamingPrefill.swift) for `layers` streamed layers: host arena + device window + the
+    (logical key, window row) lists attention reads. numpy uint32 arrays cross the boundary."""
+
+    def __init__(self, layers: int, stride_bytes: int, max_context: int, window_tokens: int, slots: int = 1,
+                 allocator: Optional[str] = None):
+        self._allocator = _host_allocator() if allocator == "host" else None
+        err = C.c_int(0)
+        self.handle = L.lib().tt_kv_window_create(
+            layers, stride_bytes, max_context, slots, window_tokens,
+            C.byref(self._allocator) if self._allocator is not None else None, C.byref(err))
+        if not self.handle:
+            L.check(err.value or L.TT_ERR_OOM)
+        self.stride, self.max_context, self.slots = stride_bytes, max_context, slots
+        self.window_tokens = int(L.lib().tt_kv_window_tokens(self.handle))
+
+    def close(self):
+        if getattr(self, "handle", None):
+            L.lib().tt_kv_window_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def window_bytes(self) -> int:
+        return int(L.lib().tt_kv_window_bytes(self.handle))
+
+    @property
+    def host_arena_bytes(self) -> int:
+        return int(L.lib().tt_kv_window_host_arena_bytes(self.handle))
+
+    def streaming_prefill_chunk_tokens(self, configured: int, selection_width: int) -> int:
+        return int(L.lib().tt_kv_window_prefill_chunk_tokens(self.handle, configured, selection_width))
+
+    def base(self, layer: int, slot: int = 0):
+        k, v = C.c_void_p(), C.c_void_p()
+        L.check(L.lib().tt_kv_window_base(self.handle, layer, slot, C.byref(k), C.byref(v)))
+        return k.value, v.value
+
+    def write_slot(self, layer: int, position: int, slot: int = 0):
+        """kSlot / vSlot of a streamed layer: addresses the projection writes this position's row to."""
+        k, v = C.c_void_p(), C.c_void_p()
+        L.check(L.lib().tt_kv_window_write_slot(self.handle, layer, position, slot, C.byref(k), C.byref(v)))
+        return k.value, v.value
+
+    def window_row(self, layer: int, position: int, slot: int = 0):
+        row = C.c_int64(-1)
+        L.check(L.lib().tt_kv_window_row_of(self.handle, layer, slot, position, C.byref(row)))
+        return None if row.value < 0 else int(row.value)
+
+    def prepare_decode_window(self, layer: int, position: int, indices=None, count: Optional[int] = None, slot: int = 0):
+        """prepareDecodeWindow: (indices, rows) uint32 arrays of the step's selection."""
+        import numpy as np
+        if indices is not None:
+            indices = np.ascontiguousarray(indices, dtype=np.uint32)
+            count = len(indices) if count is None else count
+        out_i, out_r = np.empty(count, np.uint32), np.empty(count, np.uint32)
+        L.check(L.lib().tt_kv_window_prepare_decode(
+            self.handle, layer, slot, position, indices.ctypes.data if indices is not None else None, count,
+            out_i.ctypes.data, out_r.ctypes.data))
+        return out_i, out_r
+
+    def begin_prefill_write(self, layer: int, start_position: int, token_count: int, slot: int = 0):
+        k, v = C.c_void_p(), C.c_void_p()
+        L.check(L.lib().tt_kv_window_begin_prefill(self.handle, layer, slot, start_position, token_count, C.byref(k), C.byref(v)))
+        return k.value, v.value
+
+    def prepare_prefill_window(self, layer: int, start_position: int, token_count: int, indices=None, counts=None,
+                               slot: int = 0):
+        """preparePrefillWindow: (indices, rows, counts) with the [token, index_stride] layout of the selection."""
+        import numpy as np
+        if indices is not None:
+            indices = np.ascontiguousarray(indices, dtype=np.uint32)
+            counts = np.ascontiguousarray(counts, dtype=np.uint32)
+            stride = indices.shape[1]
+        else:
+            stride = start_position + token_count
+        out_i = np.zeros((token_count, stride), np.uint32); out_r = np.zeros((token_count, stride), np.uint32)
+        out_c = np.zeros(token_count, np.uint32)
+        L.check(L.lib().tt_kv_window_prepare_prefill(
+            self.handle, layer, slot, start_position, token_count, indices.ctypes.data if indices is not None else None,
+            stride if indices is not None else 0, counts.ctypes.data if indices is not None else None,
+            out_i.ctypes.data, out_r.ctypes.data, out_c.ctypes.data, stride))
+        return out_i, out_r, out_c
+
+    def commit(self, position: int, count: int = 1, slot: int = 0):
+        L.check(L.lib().tt_kv_window_commit(self.handle, slot, position, count))
+
+    def reset_slot(self, slot: int = 0):
+        L.check(L.lib().tt_kv_window_reset_slot(self.handle, slot))
+
+    def host_row(self, layer: int, position: int, key: bool = True, slot: int = 0) -> bytes:
+        buf = C.create_string_buffer(self.stride)
+        L.check(L.lib().tt_kv_window_host_row(self.handle, layer, slot, position, int(key), buf))
+        return buf.raw
+
+    def counters(self):
+        e, r, b = C.c_uint64(0), C.c_uint64(0), C.c_uint64(0)
+        L.lib().tt_kv_window_counters(self.handle, C.byref(e), C.byref(r), C.byref(b))
+        return {"evictions": e.value, "row_copies": r.value, "copy_bytes": b.value}

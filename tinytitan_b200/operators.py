@@ -374,9 +374,18 @@ class PrefillAttention:
         self.context = context
 
     def encode_causal(self, q, k, v, out, params: PrefillAttentionParams, kv_ring_capacity=0, io_dtype=None,
-                      command_buffer=None, q_offset=0, k_offset=0, v_offset=0, out_offset=0):
-        """PrefillAttention.encodeCausal (PrefillAttention.swift:165-258)."""
+                      command_buffer=None, q_offset=0, k_offset=0, v_offset=0, out_offset=0, keep_mask=None,
+                      keep_stride=0, keep_indices=None, keep_index_stride=0, keep_counts=None, keep_rows=None):
+        """PrefillAttention.encodeCausal (PrefillAttention.swift:165-258); the keep* arguments are its
+        per-query key selection (mask, compact index list with counts, window rows)."""
         cp = params.to_c()
+        if keep_mask is not None or keep_indices is not None or keep_counts is not None or keep_rows is not None:
+            self.context.check(L.lib().tt_attn_prefill_causal_selected(
+                self.context.handle, _stream(command_buffer), _addr(q, q_offset), _addr(k, k_offset),
+                _addr(v, v_offset), _addr(out, out_offset), C.byref(cp), kv_ring_capacity,
+                io_dtype if io_dtype is not None else _dtype_of(q), _addr(keep_mask) or None, keep_stride,
+                _addr(keep_indices) or None, keep_index_stride, _addr(keep_counts) or None, _addr(keep_rows) or None))
+            return
         self.context.check(L.lib().tt_attn_prefill_causal(
             self.context.handle, _stream(command_buffer), _addr(q, q_offset), _addr(k, k_offset),
             _addr(v, v_offset), _addr(out, out_offset), C.byref(cp), kv_ring_capacity,
@@ -389,6 +398,68 @@ class PrefillAttention:
         path = L.lib().tt_attn_prefill_path(_addr(q, q_offset), _addr(k, k_offset), _addr(v, v_offset),
                                             _addr(out, out_offset), C.byref(cp), kv_ring_capacity)
         return "tcgen05" if path == 1 else "generic"
+
+
+@dataclass(frozen=True)
+class SparseIndexerConfig:
+    """SparseIndexerConfig of the reference's ArchConfig (ModelTypes.swift:129-133)."""
+    num_heads: int = 4
+    head_dim: int = 128
+    budget: int = 2048
+    compress_ratio: int = 4
+
+
+class QSAIndexer:
+    """Device side of QSAIndexer (sources/TinyTitan/Kernels/Attention/QSAIndexer.swift): pooled-key cache
+    maintenance, block scores and the key selection. The caller owns the buffers (raw keys, pooled
+    blocks, scores, selection), like the Swift class; projections are the caller's GEMVs."""
+
+    def __init__(self, context: Context, config: SparseIndexerConfig, rope_theta: float = 1e7, eps: float = 1e-6,
+                 budget: Optional[int] = None):
+        self.context, self.config = context, config
+        self.heads, self.head_dim, self.compress_ratio = config.num_heads, config.head_dim, config.compress_ratio
+        self.budget = config.budget if budget is None else budget
+        self.rope_theta, self.eps = rope_theta, eps
+
+    @property
+    def selection_width(self) -> int:
+        """Cells a query keeps: the budget plus the tail block's extra members."""
+        return self.budget + self.compress_ratio - 1
+
+    def encode_pool(self, raw_keys, pooled, first_block, block_count, visible_keys, key_norm_weight=None,
+                    command_buffer=None):
+        """encodePoolPrefill / the repool of encodeAppendKey: pool + norm + rotation of a block range."""
+        self.context.check(L.lib().tt_qsa_pool_blocks(
+            self.context.handle, _stream(command_buffer), _addr(raw_keys), _addr(pooled), self.head_dim, first_block,
+            block_count, self.compress_ratio, visible_keys, _addr(key_norm_weight) or None, self.eps, self.rope_theta))
+
+    def encode_pool_prefill(self, raw_keys, pooled, start_position, tokens, key_norm_weight, command_buffer=None):
+        first = start_position // self.compress_ratio
+        last = (start_position + tokens - 1) // self.compress_ratio
+        self.encode_pool(raw_keys, pooled, first, last - first + 1, start_position + tokens, key_norm_weight, command_buffer)
+
+    def encode_append_key(self, raw_keys, pooled, position, key_norm_weight, command_buffer=None):
+        """Repool the block token `position` joined (its raw key is already in the cache)."""
+        self.encode_pool(raw_keys, pooled, position // self.compress_ratio, 1, position + 1, key_norm_weight, command_buffer)
+
+    def encode_query(self, query, rows, position, query_norm_weight, command_buffer=None):
+        self.context.check(L.lib().tt_qsa_query_norm_rope(
+            self.context.handle, _stream(command_buffer), _addr(query), self.head_dim, self.heads, rows, position,
+            _addr(query_norm_weight), self.eps, self.rope_theta))
+
+    def encode_scores(self, query, pooled, scores, blocks, rows=1, score_stride=None, command_buffer=None):
+        """encodeScores (rows = 1) / encodeScoresPrefill after the query's norm and rotation."""
+        self.context.check(L.lib().tt_qsa_block_scores(
+            self.context.handle, _stream(command_buffer), _addr(query), _addr(pooled), _addr(scores), self.head_dim,
+            self.heads, blocks, rows, score_stride or blocks))
+
+    def encode_select_keys(self, scores, score_stride, start_position, rows, keep=None, keep_stride=0, indices=None,
+                           index_stride=0, counts=None, command_buffer=None):
+        """encodeSelectKeys / selectKeysCompact (rows = 1) and selectKeysPrefill, mask and compact list at once."""
+        self.context.check(L.lib().tt_qsa_select_keys(
+            self.context.handle, _stream(command_buffer), _addr(scores), score_stride, start_position, rows,
+            self.compress_ratio, self.selection_width, _addr(keep) or None, keep_stride, _addr(indices) or None,
+            index_stride, _addr(counts) or None))
 
 
 @dataclass(frozen=True)
