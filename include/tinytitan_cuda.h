@@ -90,6 +90,7 @@ uint64_t tt_ctx_launch_count(const tt_context *ctx);
  * clears the record. */
 #define TT_PROFILE_DECODE_PARTIAL 1
 #define TT_PROFILE_GDN_STEP 2
+#define TT_PROFILE_EXCHANGE 4 /* the merge + peer exchange kernel of tt_attn_decode_exchange */
 int tt_ctx_profile_enable(tt_context *ctx, int enabled);
 int tt_ctx_profile_collect(tt_context *ctx, float *out_ms, uint32_t capacity, uint32_t *out_count);
 
@@ -560,6 +561,14 @@ int tt_kv_cache_k_slot(tt_kv_cache *cache, uint32_t layer, uint32_t position, ui
                        void **out_ptr);
 int tt_kv_cache_v_slot(tt_kv_cache *cache, uint32_t layer, uint32_t position, uint32_t slot,
                        void **out_ptr);
+/* kSlot / vSlot for a whole decode batch: row i of k_rows / v_rows (device memory,
+ * src_stride_bytes apart, the K and V projections' outputs) is written to slot slots[i] at
+ * position positions[i] of `layer`, one launch for up to 256 rows (the reference's projection
+ * kernels write through kSlot / vSlot one session at a time). Cursors are not moved: advance
+ * stays the caller's call, as in the reference. slots / positions are host arrays. */
+int tt_kv_cache_write_rows(tt_kv_cache *cache, tt_stream stream, uint32_t layer, const uint32_t *slots,
+                           const uint32_t *positions, uint32_t n, const void *k_rows,
+                           const void *v_rows, uint32_t src_stride_bytes);
 /* keyView / valueView (KVCacheManager+Views.swift:11-72). */
 int tt_kv_cache_key_view(tt_kv_cache *cache, uint32_t layer, uint32_t slot,
                          uint32_t valid_token_count, tt_kv_view *out_view);

@@ -128,3 +128,24 @@ def test_reserve_on_a_bound_stream_keeps_rows_written_there():
     side.synchronize()
     assert torch.equal(back.view(n, 512), rows)
     kv.close()
+
+
+def test_write_rows_scatters_a_decode_batch_in_one_launch():
+    cfg = tt.ArchConfig([tt.FULL], 2, 256, 2, 256, 0, tt.LinearAttentionConfig(16, 32, 128, 128, 4))
+    slots_n = 40
+    kv = tt.KVCacheManager(cfg, max_context=5000, slots=slots_n)
+    r = np.random.default_rng(4)
+    k = torch.randn(slots_n, 512, device="cuda").half(); v = torch.randn(slots_n, 512, device="cuda").half()
+    slots = r.permutation(slots_n).astype(np.uint32); positions = r.integers(0, 5000, size=slots_n).astype(np.uint32)
+    before = device_view(kv.k_slot(0, 0, 0), slots_n * 5000 * 512, torch.float16).clone()
+    kv.write_rows(0, slots, positions, k, v, 1024)
+    torch.cuda.synchronize()
+    after = device_view(kv.k_slot(0, 0, 0), slots_n * 5000 * 512, torch.float16).view(slots_n, 5000, 512)
+    changed = torch.zeros(slots_n, 5000, dtype=torch.bool, device="cuda")
+    for i in range(slots_n):
+        s, p = int(slots[i]), int(positions[i])
+        assert torch.equal(after[s, p], k[i])
+        assert torch.equal(device_view(kv.v_slot(0, p, s), 512, torch.float16), v[i])
+        changed[s, p] = True
+    assert torch.equal(after[~changed], before.view(slots_n, 5000, 512)[~changed])   # nothing else was touched
+    kv.close()

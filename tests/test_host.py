@@ -298,3 +298,28 @@ def test_snapshot_round_trip_on_host_memory():
         g2.restore_snapshot(snap + b"x")
     for m in (a, b, g, g2):
         m.close()
+
+
+def test_kv_cache_write_rows_on_host_memory():
+    # the batched kSlot / vSlot write: row i lands at (slots[i], positions[i]), other rows untouched
+    import numpy as np
+    cfg = tt.ArchConfig([tt.FULL], 2, 256, 2, 256, 0, tt.LinearAttentionConfig(16, 32, 128, 128, 4))
+    kv = tt.KVCacheManager(cfg, max_context=100, slots=4, allocator="host")
+    stride = kv.stride(0)
+    src_stride = stride + 32
+    n = 3
+    ksrc = (ctypes.c_ubyte * (n * src_stride))(*([0] * (n * src_stride))); vsrc = (ctypes.c_ubyte * (n * src_stride))()
+    for i in range(n):
+        ctypes.memset(ctypes.addressof(ksrc) + i * src_stride, 0x10 + i, stride)
+        ctypes.memset(ctypes.addressof(vsrc) + i * src_stride, 0x20 + i, stride)
+    slots = np.array([3, 0, 2], np.uint32); positions = np.array([7, 99, 0], np.uint32)
+    kv.write_rows(0, slots, positions, ctypes.addressof(ksrc), ctypes.addressof(vsrc), src_stride)
+    for i in range(n):
+        assert _read(kv.k_slot(0, int(positions[i]), int(slots[i])), stride) == bytes([0x10 + i]) * stride
+        assert _read(kv.v_slot(0, int(positions[i]), int(slots[i])), stride) == bytes([0x20 + i]) * stride
+    assert kv.position(3) == 0                                        # cursors do not move
+    with pytest.raises(tt.InvalidArgument):
+        kv.write_rows(0, np.array([4], np.uint32), np.array([0], np.uint32), ctypes.addressof(ksrc), ctypes.addressof(vsrc), src_stride)
+    with pytest.raises(tt.InvalidArgument):
+        kv.write_rows(0, np.array([0], np.uint32), np.array([100], np.uint32), ctypes.addressof(ksrc), ctypes.addressof(vsrc), src_stride)
+    kv.close()

@@ -212,6 +212,7 @@ SIGNATURES = {
     "tt_gdn_state_speculative_restore": (C.c_int, [_vp, _vp]),
     "tt_gdn_state_bind_stream": (C.c_int, [_vp, _vp]),
     "tt_kv_cache_bind_stream": (C.c_int, [_vp, _vp]),
+    "tt_kv_cache_write_rows": (C.c_int, [_vp, _vp, _u32, _vp, _vp, _u32, _vp, _vp, _u32]),
     "tt_gdn_state_bytes_per_layer": (C.c_size_t, [_vp]),
     "tt_gdn_state_conv_tail_bytes_per_layer": (C.c_size_t, [_vp]),
     "tt_gdn_state_is_linear": (C.c_int, [_vp, _u32]),

@@ -52,6 +52,21 @@ int cuda_upload(void *, void *dst, const void *host_src, size_t bytes) {
 
 const tt_allocator kCudaAllocator = {nullptr, cuda_alloc, cuda_release, cuda_copy, cuda_zero, cuda_download, cuda_upload};
 
+// Up to kMaxWriteRows cache rows written by one launch: block i copies row i of the K and V sources to
+// the byte offsets the host worked out (slot region + position), 16 bytes per thread and step.
+constexpr uint32_t kMaxWriteRows = 256;
+struct WriteRowsTable { unsigned long long offset[kMaxWriteRows]; };
+__global__ void __launch_bounds__(128)
+kv_write_rows_kernel(unsigned char *__restrict__ k_dst, unsigned char *__restrict__ v_dst, const unsigned char *__restrict__ k_src,
+                     const unsigned char *__restrict__ v_src, uint32_t row_bytes, uint32_t src_stride_bytes,
+                     const __grid_constant__ WriteRowsTable table) {
+    const size_t off = table.offset[blockIdx.x];
+    const uint4 *ks = reinterpret_cast<const uint4 *>(k_src + (size_t)blockIdx.x * src_stride_bytes);
+    const uint4 *vs = reinterpret_cast<const uint4 *>(v_src + (size_t)blockIdx.x * src_stride_bytes);
+    uint4 *kd = reinterpret_cast<uint4 *>(k_dst + off), *vd = reinterpret_cast<uint4 *>(v_dst + off);
+    for (uint32_t i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) { kd[i] = ks[i]; vd[i] = vs[i]; }
+}
+
 constexpr uint32_t kMaximumSlots = 256;            // KVCacheManager.maximumSlots
 constexpr uint32_t kInitialCapacityTokens = 8192;  // KVCacheManager.initialCapacityTokens
 constexpr uint32_t kQuantGroup = 64;               // KVCacheManager.quantizationGroupSize
@@ -203,6 +218,44 @@ TT_API int tt_kv_cache_reserve(tt_kv_cache *c, uint32_t tokens, uint32_t slot) {
         c->alloc.release(c->alloc.user, c->v[layer]);
         c->k[layer] = nk; c->v[layer] = nv;
         c->capacity[layer] = (uint32_t)target;
+    }
+    return TT_OK;
+}
+
+TT_API int tt_kv_cache_write_rows(tt_kv_cache *c, tt_stream stream, uint32_t layer, const uint32_t *slots,
+                                  const uint32_t *positions, uint32_t n, const void *k_rows, const void *v_rows,
+                                  uint32_t src_stride_bytes) {
+    if (c == nullptr || layer >= c->kind.size() || c->kind[layer] == 2 || slots == nullptr || positions == nullptr ||
+        k_rows == nullptr || v_rows == nullptr)
+        return TT_ERR_INVALID_ARG;
+    const uint32_t stride = c->stride[layer], cap = c->capacity[layer];
+    if (src_stride_bytes < stride) return TT_ERR_INVALID_ARG;
+    const bool ring_layer = c->ring && c->kind[layer] == 0;
+    for (uint32_t base = 0; base < n; base += kMaxWriteRows) {
+        const uint32_t count = n - base < kMaxWriteRows ? n - base : kMaxWriteRows;
+        static thread_local WriteRowsTable table;
+        for (uint32_t i = 0; i < count; ++i) {
+            const uint32_t slot = slots[base + i], position = positions[base + i];
+            if (slot >= c->slots || (uint64_t)position + 1 > c->max_context) return TT_ERR_INVALID_ARG;
+            if (!ring_layer && position >= cap) return TT_ERR_INVALID_ARG;      // reserve() first
+            table.offset[i] = ((size_t)slot * cap + position % cap) * stride;
+        }
+        const unsigned char *ks = static_cast<const unsigned char *>(k_rows) + (size_t)base * src_stride_bytes;
+        const unsigned char *vs = static_cast<const unsigned char *>(v_rows) + (size_t)base * src_stride_bytes;
+        if (!c->builtin) {     // caller-supplied memory (host memory in the CPU tests): plain copies through the allocator
+            for (uint32_t i = 0; i < count; ++i) {
+                int bad = c->alloc.copy(c->alloc.user, (char *)c->k[layer] + table.offset[i], ks + (size_t)i * src_stride_bytes, stride);
+                bad |= c->alloc.copy(c->alloc.user, (char *)c->v[layer] + table.offset[i], vs + (size_t)i * src_stride_bytes, stride);
+                if (bad) return TT_ERR_CUDA;
+            }
+            continue;
+        }
+        if (stride % 16 != 0 || src_stride_bytes % 16 != 0 || (((uintptr_t)k_rows | (uintptr_t)v_rows) & 15))
+            return TT_ERR_UNSUPPORTED_SHAPE;
+        kv_write_rows_kernel<<<count, 128, 0, (cudaStream_t)stream>>>(static_cast<unsigned char *>(c->k[layer]),
+                                                                     static_cast<unsigned char *>(c->v[layer]), ks, vs, stride,
+                                                                     src_stride_bytes, table);
+        if (cudaGetLastError() != cudaSuccess) return TT_ERR_CUDA;
     }
     return TT_OK;
 }

@@ -93,7 +93,7 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
                            float *__restrict__ part_m, float *__restrict__ part_l,
                            uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t kv_stride_bytes,
                            uint32_t q_row_stride, float scale_log2, uint32_t *__restrict__ status,
-                           const TTDecodeSession single, uint32_t single_keys_per_item) {
+                           const __grid_constant__ TTSessionTable table, uint32_t table_keys_per_item) {
     using S = DecodeSmem<HD>;
     constexpr int HH = HD / 2;          // head-dim half per warp
     constexpr int KS = HH / 16;         // k-steps of the partial Q.K^T
@@ -102,19 +102,28 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     const uint32_t group = n_q_heads / n_kv_heads;
-    // One-session calls carry the session in the kernel parameters and derive the work item from
-    // the block index (all items are equal slices), so no table has to be copied to the device.
+    // Calls with up to kParamSessions sessions carry them in the kernel parameters and derive the
+    // work item from the block index (the items of a session are equal slices, item_prefix says
+    // where each session's items start), so no table is copied to the device and a CTA starts
+    // without two dependent global loads.
+    pdl_launch_dependents();
     TTDecodeItem item;
     TTDecodeSession ses;
-    if (single_keys_per_item != 0) {
-        ses = single;
+    if (table.n != 0) {
+        uint32_t lo = 0, hi = table.n;
+        while (hi - lo > 1) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (table.item_prefix[mid] <= blockIdx.x) lo = mid; else hi = mid;
+        }
+        ses = table.s[lo];
+        const uint32_t local = blockIdx.x - table.item_prefix[lo];
         const uint32_t packed_rows = ses.q_rows * group;
         const uint32_t row_tiles = (packed_rows + 15) / 16;
-        const uint32_t rt = blockIdx.x % row_tiles, kvh = (blockIdx.x / row_tiles) % n_kv_heads;
-        const uint32_t part = blockIdx.x / (row_tiles * n_kv_heads);
-        item.session = 0; item.kv_head = kvh; item.part_index = part; item.partial_base = 0;
-        item.key_begin = min(ses.seq_len, ses.kv_start + part * single_keys_per_item);
-        item.key_end = min(ses.seq_len, item.key_begin + single_keys_per_item);
+        const uint32_t rt = local % row_tiles, kvh = (local / row_tiles) % n_kv_heads;
+        const uint32_t part = local / (row_tiles * n_kv_heads);
+        item.session = lo; item.kv_head = kvh; item.part_index = part; item.partial_base = ses.partial_base;
+        item.key_begin = min(ses.seq_len, ses.kv_start + part * table_keys_per_item);
+        item.key_end = min(ses.seq_len, item.key_begin + table_keys_per_item);
         item.row_begin = rt * 16;
         item.row_count = min(16u, packed_rows - rt * 16);
     } else {
@@ -131,6 +140,9 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
 
+    // everything above overlapped the tail of the kernel before this one in the stream; its
+    // results (the query rows, the newest K/V rows, partials being merged) are read from here on
+    pdl_wait();
     // ---- this warp's half of the Q tile, straight into mma A fragments ----
     uint32_t qf[KS][4];
     {
@@ -370,8 +382,8 @@ attn_decode_partial_quant_kernel(const TTDecodeItem *__restrict__ items,
                            float *__restrict__ part_m, float *__restrict__ part_l,
                            uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t kv_stride_bytes,
                            uint32_t q_row_stride, float scale_log2, uint32_t *__restrict__ status,
-                           const TTDecodeSession single, uint32_t single_keys_per_item, uint32_t value_bytes,
-                           uint32_t meta_bytes) {
+                           const __grid_constant__ TTSessionTable table, uint32_t table_keys_per_item,
+                           uint32_t value_bytes, uint32_t meta_bytes) {
     using T = __half;
     using S = QuantSmem<HD, BITS>;
     constexpr int HH = HD / 2;          // head-dim half per warp
@@ -381,19 +393,28 @@ attn_decode_partial_quant_kernel(const TTDecodeItem *__restrict__ items,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     const uint32_t group = n_q_heads / n_kv_heads;
-    // One-session calls carry the session in the kernel parameters and derive the work item from
-    // the block index (all items are equal slices), so no table has to be copied to the device.
+    // Calls with up to kParamSessions sessions carry them in the kernel parameters and derive the
+    // work item from the block index (the items of a session are equal slices, item_prefix says
+    // where each session's items start), so no table is copied to the device and a CTA starts
+    // without two dependent global loads.
+    pdl_launch_dependents();
     TTDecodeItem item;
     TTDecodeSession ses;
-    if (single_keys_per_item != 0) {
-        ses = single;
+    if (table.n != 0) {
+        uint32_t lo = 0, hi = table.n;
+        while (hi - lo > 1) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (table.item_prefix[mid] <= blockIdx.x) lo = mid; else hi = mid;
+        }
+        ses = table.s[lo];
+        const uint32_t local = blockIdx.x - table.item_prefix[lo];
         const uint32_t packed_rows = ses.q_rows * group;
         const uint32_t row_tiles = (packed_rows + 15) / 16;
-        const uint32_t rt = blockIdx.x % row_tiles, kvh = (blockIdx.x / row_tiles) % n_kv_heads;
-        const uint32_t part = blockIdx.x / (row_tiles * n_kv_heads);
-        item.session = 0; item.kv_head = kvh; item.part_index = part; item.partial_base = 0;
-        item.key_begin = min(ses.seq_len, ses.kv_start + part * single_keys_per_item);
-        item.key_end = min(ses.seq_len, item.key_begin + single_keys_per_item);
+        const uint32_t rt = local % row_tiles, kvh = (local / row_tiles) % n_kv_heads;
+        const uint32_t part = local / (row_tiles * n_kv_heads);
+        item.session = lo; item.kv_head = kvh; item.part_index = part; item.partial_base = ses.partial_base;
+        item.key_begin = min(ses.seq_len, ses.kv_start + part * table_keys_per_item);
+        item.key_end = min(ses.seq_len, item.key_begin + table_keys_per_item);
         item.row_begin = rt * 16;
         item.row_count = min(16u, packed_rows - rt * 16);
     } else {
@@ -411,6 +432,9 @@ attn_decode_partial_quant_kernel(const TTDecodeItem *__restrict__ items,
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
 
+    // everything above overlapped the tail of the kernel before this one in the stream; its
+    // results (the query rows, the newest K/V rows, partials being merged) are read from here on
+    pdl_wait();
     // ---- this warp's half of the Q tile, straight into mma A fragments ----
     uint32_t qf[KS][4];
     {
@@ -686,7 +710,7 @@ attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions, const f
                            const float *__restrict__ part_m, const float *__restrict__ part_l,
                            uint32_t n_q_heads, uint32_t head_dim, uint32_t out_row_stride, int mode,
                            float *__restrict__ m_out, float *__restrict__ d_out, float *__restrict__ o_out,
-                           const TTDecodeSession single, int use_single, uint32_t col_threads) {
+                           const __grid_constant__ TTSessionTable table, uint32_t col_threads) {
     // 256 threads = G groups of `col_threads` column threads (one float4 of the row each); group g
     // merges parts g, g+G, ... so that a long session's hundreds of parts are read with many loads
     // in flight instead of one after another. Batches with many (session, row) pairs use one CTA per
@@ -697,7 +721,9 @@ attn_decode_combine_kernel(const TTDecodeSession *__restrict__ sessions, const f
     // to finish before the first output load is issued.
     __shared__ float grp_m[32], grp_d[32];
     __shared__ float4 accs[256];
-    const TTDecodeSession ses = use_single ? single : sessions[blockIdx.x];
+    pdl_launch_dependents();
+    pdl_wait();                       // pass 1 has finished and its partials are visible
+    const TTDecodeSession ses = table.n != 0 ? table.s[blockIdx.x] : sessions[blockIdx.x];
     const uint32_t rows_total = ses.q_rows * n_q_heads;
     const uint32_t rho = blockIdx.y;
     if (rho >= rows_total) return;
@@ -806,38 +832,36 @@ template <int HD, typename T>
 cudaError_t launch_partial(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
                            const TTDecodeSession *sessions, float *part_o, float *part_m,
                            float *part_l, const tt_attn_batch_params *p, uint32_t *status,
-                           const TTDecodeSession &single, uint32_t single_keys) {
+                           const TTSessionTable &table, uint32_t table_keys) {
     auto kernel = attn_decode_partial_kernel<HD, T>;
     const int smem = DecodeSmem<HD>::kTotal;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    kernel<<<n_items, 64, smem, stream>>>(items, sessions, part_o, part_m, part_l, p->n_q_heads,
-                                          p->n_kv_heads, p->kv_token_stride_elements * 2u,
-                                          p->q_row_stride_elements, p->scale * kLog2e, status, single, single_keys);
-    return cudaGetLastError();
+    return tt_launch_pdl(kernel, dim3(n_items), dim3(64), (size_t)smem, stream, items, sessions, part_o, part_m, part_l,
+                         p->n_q_heads, p->n_kv_heads, p->kv_token_stride_elements * 2u, p->q_row_stride_elements,
+                         p->scale * kLog2e, status, table, table_keys);
 }
 
 template <int HD, int BITS>
 cudaError_t launch_partial_quant_one(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
                                      const TTDecodeSession *sessions, float *part_o, float *part_m, float *part_l,
-                                     const tt_attn_batch_params *p, uint32_t *status, const TTDecodeSession &single,
-                                     uint32_t single_keys, const TTKvQuant *quant, uint32_t meta_bytes) {
+                                     const tt_attn_batch_params *p, uint32_t *status, const TTSessionTable &table,
+                                     uint32_t table_keys, const TTKvQuant *quant, uint32_t meta_bytes) {
     auto kernel = attn_decode_partial_quant_kernel<HD, BITS>;
     const int smem = QuantSmem<HD, BITS>::kTotal;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    kernel<<<n_items, 64, smem, stream>>>(items, sessions, part_o, part_m, part_l, p->n_q_heads, p->n_kv_heads,
-                                          quant->stride_bytes, p->q_row_stride_elements, p->scale * kLog2e, status,
-                                          single, single_keys, quant->value_bytes, meta_bytes);
-    return cudaGetLastError();
+    return tt_launch_pdl(kernel, dim3(n_items), dim3(64), (size_t)smem, stream, items, sessions, part_o, part_m, part_l,
+                         p->n_q_heads, p->n_kv_heads, quant->stride_bytes, p->q_row_stride_elements, p->scale * kLog2e,
+                         status, table, table_keys, quant->value_bytes, meta_bytes);
 }
 
 cudaError_t launch_partial_quant(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
                                  const TTDecodeSession *sessions, float *part_o, float *part_m, float *part_l,
-                                 const tt_attn_batch_params *p, uint32_t *status, const TTDecodeSession &single,
-                                 uint32_t single_keys, const TTKvQuant *quant, uint32_t meta_bytes) {
+                                 const tt_attn_batch_params *p, uint32_t *status, const TTSessionTable &table,
+                                 uint32_t table_keys, const TTKvQuant *quant, uint32_t meta_bytes) {
 #define TT_Q(HD, BITS) launch_partial_quant_one<HD, BITS>(stream, n_items, items, sessions, part_o, part_m, part_l, p, \
-                                                          status, single, single_keys, quant, meta_bytes)
+                                                          status, table, table_keys, quant, meta_bytes)
     if (p->head_dim == 256) return quant->bits == 8 ? TT_Q(256, 8) : TT_Q(256, 4);
     return quant->bits == 8 ? TT_Q(128, 8) : TT_Q(128, 4);
 #undef TT_Q
@@ -847,11 +871,11 @@ template <typename T>
 cudaError_t launch_partial_hd(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
                               const TTDecodeSession *sessions, float *part_o, float *part_m,
                               float *part_l, const tt_attn_batch_params *p, uint32_t *status,
-                              const TTDecodeSession &single = TTDecodeSession(), uint32_t single_keys = 0) {
+                              const TTSessionTable &table, uint32_t table_keys) {
     switch (p->head_dim) {
-        case 64: return launch_partial<64, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, single, single_keys);
-        case 128: return launch_partial<128, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, single, single_keys);
-        case 256: return launch_partial<256, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, single, single_keys);
+        case 64: return launch_partial<64, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys);
+        case 128: return launch_partial<128, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys);
+        case 256: return launch_partial<256, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -1173,16 +1197,21 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     uint32_t keys_per_item = 0, n_items = 0;
     uint32_t partial_cursor = 0, item_cursor = 0, max_rows = 0;
     if (wide) wide = plan_wide(ctx, in_sessions, n_sessions, p, keys, &n_items, &partial_cursor, &max_rows);
+    // Up to kParamSessions sessions travel in the kernel parameters: nothing is uploaded and the
+    // item table is never built (a CTA derives its item from the block index).
+    const bool in_params = !wide && n_sessions <= kParamSessions;
+    TTSessionTable &table = ctx->session_table;
+    table.n = 0;
     if (!wide) {
         int rc = tt_attn_plan_splits(keys, rows, n_sessions, p->head_dim, p->n_q_heads, p->n_kv_heads,
                                      (uint32_t)ctx->sm_count, ctx->workspace_bytes, &keys_per_item, &n_items);
         if (rc != TT_OK) return tt_set_error(ctx, rc, "split-KV partials do not fit the context workspace");
-        if (n_items > ctx->max_items)
+        if (!in_params && n_items > ctx->max_items)
             return tt_set_error(ctx, TT_ERR_OOM, "%u work items exceed the context's item table (%u)", n_items,
                                 ctx->max_items);
 
         const uint32_t rows_per_item = 16u;
-        // Build the session and item tables.
+        // Build the session table and, for the device-table form, the item table.
         for (uint32_t i = 0; i < n_sessions; ++i) {
             TTDecodeSession s = in_sessions[i];
             uint32_t parts = ceil_div_u32(keys[i], keys_per_item);
@@ -1193,36 +1222,42 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
             ctx->h_sessions[i] = s;
             if (rows_total > max_rows) max_rows = rows_total;
             const uint32_t packed_rows = s.q_rows * group;
-            for (uint32_t part = 0; part < parts; ++part) {
-                const uint32_t kb = s.kv_start + part * keys_per_item;
-                uint32_t ke = kb + keys_per_item;
-                if (ke > s.seq_len) ke = s.seq_len;
-                if (ke < kb) ke = kb;
-                for (uint32_t kvh = 0; kvh < p->n_kv_heads; ++kvh)
-                    for (uint32_t rb = 0; rb < packed_rows; rb += rows_per_item) {
-                        TTDecodeItem &it = ctx->h_items[item_cursor++];
-                        it.session = i; it.kv_head = kvh; it.key_begin = kb; it.key_end = ke;
-                        it.part_index = part; it.row_begin = rb;
-                        it.row_count = packed_rows - rb < rows_per_item ? packed_rows - rb : rows_per_item;
-                        it.partial_base = s.partial_base;
-                    }
+            if (in_params) {
+                table.s[i] = s;
+                table.item_prefix[i] = item_cursor;
+                item_cursor += parts * p->n_kv_heads * ceil_div_u32(packed_rows, rows_per_item);
+            } else {
+                for (uint32_t part = 0; part < parts; ++part) {
+                    const uint32_t kb = s.kv_start + part * keys_per_item;
+                    uint32_t ke = kb + keys_per_item;
+                    if (ke > s.seq_len) ke = s.seq_len;
+                    if (ke < kb) ke = kb;
+                    for (uint32_t kvh = 0; kvh < p->n_kv_heads; ++kvh)
+                        for (uint32_t rb = 0; rb < packed_rows; rb += rows_per_item) {
+                            TTDecodeItem &it = ctx->h_items[item_cursor++];
+                            it.session = i; it.kv_head = kvh; it.key_begin = kb; it.key_end = ke;
+                            it.part_index = part; it.row_begin = rb;
+                            it.row_count = packed_rows - rb < rows_per_item ? packed_rows - rb : rows_per_item;
+                            it.partial_base = s.partial_base;
+                        }
+                }
             }
             partial_cursor += parts * rows_total;
         }
         if (item_cursor != n_items) return tt_set_error(ctx, TT_ERR_INVALID_ARG, "internal: item count mismatch");
+        if (in_params) {
+            table.item_prefix[n_sessions] = item_cursor;
+            table.n = n_sessions;
+        }
     }
 
     float *part_o = ctx->partials;
     float *part_m = part_o + (size_t)partial_cursor * p->head_dim;
     float *part_l = part_m + partial_cursor;
 
-    // One session: its descriptor travels in the kernel parameters and the items are derived from
-    // the block index, so the two table uploads (and their latency) are skipped.
-    const bool single = n_sessions == 1 && !wide;
-    const TTDecodeSession single_ses = ctx->h_sessions[0];
-    const uint32_t single_keys = single ? keys_per_item : 0u;
+    const uint32_t table_keys = in_params ? keys_per_item : 0u;
     cudaError_t e = cudaSuccess;
-    if (!single) {
+    if (!in_params) {
         if (wide) {
             const int rc = tt_verify_tc_encode_maps(ctx, n_sessions, p);
             if (rc != TT_OK) return rc;
@@ -1242,13 +1277,13 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
         if (rc != TT_OK) return rc;
     } else if (quantised)
         e = launch_partial_quant(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status,
-                                 single_ses, single_keys, quant, meta_bytes);
+                                 table, table_keys, quant, meta_bytes);
     else if (p->io_dtype == TT_F16)
         e = launch_partial_hd<__half>(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status,
-                                      single_ses, single_keys);
+                                      table, table_keys);
     else
         e = launch_partial_hd<__nv_bfloat16>(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p,
-                                             ctx->status, single_ses, single_keys);
+                                             ctx->status, table, table_keys);
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_decode_partial launch");
     timer.stop();
     ctx->launches++;
@@ -1262,15 +1297,15 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     while (col_threads > 8 && (uint64_t)n_sessions * max_rows * (64 / col_threads) * 2 <= (uint64_t)ctx->sm_count)
         col_threads /= 2;
     const dim3 grid(n_sessions, max_rows, (p->head_dim / 4 + col_threads - 1) / col_threads);
-    const uint32_t threads = 256;
+    const dim3 threads(256);
     if (p->io_dtype == TT_F16)
-        attn_decode_combine_kernel<__half><<<grid, threads, 0, stream>>>(
-            ctx->sessions, part_o, part_m, part_l, p->n_q_heads, p->head_dim, p->out_row_stride_elements, mode,
-            m_out, d_out, o_out, single_ses, single ? 1 : 0, col_threads);
+        e = tt_launch_pdl(attn_decode_combine_kernel<__half>, grid, threads, 0, stream, ctx->sessions, part_o, part_m, part_l,
+                          p->n_q_heads, p->head_dim, p->out_row_stride_elements, mode, m_out, d_out, o_out, table, col_threads);
     else
-        attn_decode_combine_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
-            ctx->sessions, part_o, part_m, part_l, p->n_q_heads, p->head_dim, p->out_row_stride_elements, mode,
-            m_out, d_out, o_out, single_ses, single ? 1 : 0, col_threads);
+        e = tt_launch_pdl(attn_decode_combine_kernel<__nv_bfloat16>, grid, threads, 0, stream, ctx->sessions, part_o, part_m,
+                          part_l, p->n_q_heads, p->head_dim, p->out_row_stride_elements, mode, m_out, d_out, o_out, table,
+                          col_threads);
+    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_decode_combine launch");
     e = cudaGetLastError();
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_decode_combine launch");
     ctx->launches++;
@@ -1490,12 +1525,16 @@ TT_API int tt_attn_decode_noalloc(tt_stream stream, const void *q, const void *k
     const size_t partial_rows = (size_t)parts * n_q_heads;
     if (partial_rows * (head_dim + 2) * sizeof(float) > kNoAllocScratchBytes - kNoAllocPartialOffset)
         return TT_ERR_UNSUPPORTED_SHAPE;
-    TTDecodeSession ses;
+    // one session in the kernels' parameter table (a member of a thread-local object: no allocation,
+    // and no 5 KB object on the caller's stack)
+    static thread_local TTSessionTable table;
+    TTDecodeSession &ses = table.s[0];
     ses.q = q; ses.out = out; ses.k = k; ses.v = v;
     ses.seq_len = seq_len; ses.q_rows = 1; ses.kv_start = kv_start;
     ses.n_parts = parts; ses.partial_base = 0; ses.ring_capacity = 0; ses.keep = nullptr; ses.row_index = nullptr;
     const uint32_t group = n_q_heads / n_kv_heads;
     const uint32_t grid = parts * n_kv_heads * ceil_div_u32(group, 16);
+    table.item_prefix[0] = 0; table.item_prefix[1] = grid; table.n = 1;
 
     cudaStream_t s = (cudaStream_t)stream;
     uint32_t *status = reinterpret_cast<uint32_t *>(scratch);
@@ -1507,12 +1546,12 @@ TT_API int tt_attn_decode_noalloc(tt_stream stream, const void *q, const void *k
     p.head_dim = head_dim; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
     p.kv_token_stride_elements = n_kv_heads * head_dim; p.q_row_stride_elements = n_q_heads * head_dim;
     p.out_row_stride_elements = n_q_heads * head_dim; p.scale = scale; p.io_dtype = TT_F16;
-    if (launch_partial_hd<__half>(s, grid, nullptr, nullptr, part_o, part_m, part_l, &p, status, ses, keys_per_item) !=
+    if (launch_partial_hd<__half>(s, grid, nullptr, nullptr, part_o, part_m, part_l, &p, status, table, keys_per_item) !=
         cudaSuccess)
         return TT_ERR_CUDA;
     attn_decode_combine_kernel<__half><<<dim3(1, n_q_heads, (head_dim / 4 + 15) / 16), 256, 0, s>>>(
-        nullptr, part_o, part_m, part_l, n_q_heads, head_dim, n_q_heads * head_dim, 0, nullptr, nullptr, nullptr, ses,
-        1, 16u);
+        nullptr, part_o, part_m, part_l, n_q_heads, head_dim, n_q_heads * head_dim, 0, nullptr, nullptr, nullptr, table,
+        16u);
     return cudaGetLastError() == cudaSuccess ? TT_OK : TT_ERR_CUDA;
 }
 

@@ -136,6 +136,8 @@ __global__ void __launch_bounds__(32) attn_exchange_combine_kernel(ExchangeParam
     __shared__ int all_arrived;
     const uint32_t h = blockIdx.x, cb = blockIdx.y, tid = threadIdx.x;
     const uint32_t col = cb * kColBlock + tid * 4;
+    pdl_launch_dependents();
+    pdl_wait();                       // the kernel that produced (m, d, o) has completed
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (tid < 16 && col < p.head_dim) acc = *reinterpret_cast<const float4 *>(p.o + (size_t)h * p.head_dim + col);
     exchange_and_merge<T>(p, h, cb, acc, p.m[h], p.d[h], out, status, &all_arrived);
@@ -154,6 +156,8 @@ __global__ void __launch_bounds__(256) attn_merge_exchange_kernel(ExchangeParams
     const uint32_t grp = tid >> 4, ct = tid & 15;
     const uint32_t H = p.n_q_heads;
     const uint32_t col = cb * kColBlock + ct * 4;
+    pdl_launch_dependents();
+    pdl_wait();                       // pass 1 has completed and its partials are visible
 
     // One pass over this rank's parts: group g (16 column threads) walks parts g, g+16, ... four loads at
     // a time with an online (max, sum, output) triple; the 16 triples are merged below. Nothing
@@ -251,12 +255,15 @@ int tt_launch_merge_exchange(tt_context *ctx, cudaStream_t stream, const float *
     if (rc != TT_OK) return rc;
     p.part_o = part_o; p.part_m = part_m; p.part_l = part_l; p.n_parts = n_parts;
     const dim3 grid(n_q_heads, exchange_layout(x->world, n_q_heads, head_dim).col_blocks);
+    cudaError_t e;
+    TTLaunchTimer timer(ctx, stream, TT_PROFILE_EXCHANGE);
     if (io_dtype == TT_F16)
-        attn_merge_exchange_kernel<__half><<<grid, 256, 0, stream>>>(p, reinterpret_cast<__half *>(x->out), ctx->status);
+        e = tt_launch_pdl(attn_merge_exchange_kernel<__half>, grid, dim3(256), 0, stream, p, reinterpret_cast<__half *>(x->out), ctx->status);
     else
-        attn_merge_exchange_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p, reinterpret_cast<__nv_bfloat16 *>(x->out), ctx->status);
-    cudaError_t e = cudaGetLastError();
+        e = tt_launch_pdl(attn_merge_exchange_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, p,
+                          reinterpret_cast<__nv_bfloat16 *>(x->out), ctx->status);
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_merge_exchange launch");
+    timer.stop();
     ctx->launches++;
     return TT_OK;
 }

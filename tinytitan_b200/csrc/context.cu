@@ -14,6 +14,11 @@ int tt_set_error(tt_context *ctx, int code, const char *fmt, ...) {
     return code;
 }
 
+bool tt_pdl_enabled() {
+    static const bool enabled = getenv("TT_NO_PDL") == nullptr;
+    return enabled;
+}
+
 int tt_check_cuda(tt_context *ctx, cudaError_t e, const char *what) {
     if (e == cudaSuccess) return TT_OK;
     const int code = (e == cudaErrorMemoryAllocation) ? TT_ERR_OOM : TT_ERR_CUDA;

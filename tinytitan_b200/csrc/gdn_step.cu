@@ -114,9 +114,17 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // product is 3 shuffles away and shared-memory / global accesses of a group are 128 contiguous bytes.
 //
 // grid = min(ceil(items / 4), kCtasPerSm * SMs), block = 128.
+// Up to kSmemSessions sessions travel in the kernel parameters (n != 0), so a batched step uploads
+// no table; larger batches read the table the host copied to device memory.
+struct GdnSessionTable {
+    tt_gdn_session s[kSmemSessions];
+    uint32_t n;
+};
+
 template <int DK>
 __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm)
-gdn_step_kernel(GdnParams p, uint32_t n_sessions, uint32_t n_items, uint32_t *__restrict__ status) {
+gdn_step_kernel(GdnParams p, uint32_t n_sessions, uint32_t n_items, uint32_t *__restrict__ status,
+                const __grid_constant__ GdnSessionTable ptab) {
     constexpr int C = DK / 32;                       // 16-byte chunks per lane per row
     constexpr uint32_t kItemFloats = kRowsPerWarp * DK;
     constexpr uint32_t kItemBytes = kItemFloats * 4;
@@ -149,7 +157,8 @@ gdn_step_kernel(GdnParams p, uint32_t n_sessions, uint32_t n_items, uint32_t *__
         if (!(p.flags & TT_GDN_A_LOG_PREEXP)) a = -expf(a);
         return make_float2(a, __bfloat162float(p.dt_bias[h]));
     };
-    const tt_gdn_session *tab = p.sessions;   // switched to the staged copy once it is complete
+    const tt_gdn_session *src_tab = ptab.n != 0 ? ptab.s : p.sessions;
+    const tt_gdn_session *tab = src_tab;      // switched to the staged copy once it is complete
 
     // item -> (session, head, first row)
     struct Where { uint32_t z, h, dv0; };
@@ -176,14 +185,18 @@ gdn_step_kernel(GdnParams p, uint32_t n_sessions, uint32_t n_items, uint32_t *__
     };
 
     // the first state copies leave before anything else; the tables are staged while they fly
+    pdl_launch_dependents();
     if (lane == 0) {
         for (uint32_t s = 0; s < kSlots; ++s) mbar_init(&bars[s], 1);
         mbar_fence_init();
+    }
+    pdl_wait();     // the kernel before this one in the stream (it may have written state or inputs) is complete
+    if (lane == 0) {
         for (uint32_t s = 0; s < kSlots; ++s)
             if (first + s * stride < n_items) issue(first + s * stride, s);
     }
     if (tab_in_smem)
-        for (uint32_t i = threadIdx.x; i < n_sessions; i += blockDim.x) ses_tab[i] = p.sessions[i];
+        for (uint32_t i = threadIdx.x; i < n_sessions; i += blockDim.x) ses_tab[i] = src_tab[i];
     if (heads_in_smem)
         for (uint32_t h = threadIdx.x; h < p.hv; h += blockDim.x) head_tab[h] = head_params(h);
     __syncthreads();
@@ -379,9 +392,16 @@ int launch_step(tt_context *ctx, cudaStream_t stream, const tt_gdn_session *h_se
         if (((uintptr_t)s.conv_out & 7) || ((uintptr_t)s.state & 15) || ((uintptr_t)s.checkpoint_state & 15))
             return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "session %u: misaligned buffer", i);
     }
-    cudaError_t e = cudaMemcpyAsync(ctx->gdn_sessions, h_sessions, sizeof(tt_gdn_session) * n,
-                                    cudaMemcpyHostToDevice, stream);
-    if (e != cudaSuccess) return tt_check_cuda(ctx, e, "copy gdn session table");
+    cudaError_t e = cudaSuccess;
+    static thread_local GdnSessionTable ptab;
+    ptab.n = 0;
+    if (n <= kSmemSessions) {
+        memcpy(ptab.s, h_sessions, sizeof(tt_gdn_session) * n);
+        ptab.n = n;
+    } else {
+        e = cudaMemcpyAsync(ctx->gdn_sessions, h_sessions, sizeof(tt_gdn_session) * n, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return tt_check_cuda(ctx, e, "copy gdn session table");
+    }
     GdnParams p;
     p.sessions = reinterpret_cast<const tt_gdn_session *>(ctx->gdn_sessions);
     // with fp32 gates the decay parameters are unused; point them at the session table so the
@@ -404,8 +424,7 @@ int launch_step(tt_context *ctx, cudaStream_t stream, const tt_gdn_session *h_se
     auto launch = [&](auto kernel) {
         cudaError_t le = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (le != cudaSuccess) return le;
-        kernel<<<grid, kWarps * 32, smem, stream>>>(p, n, n_items, ctx->status);
-        return cudaSuccess;
+        return tt_launch_pdl(kernel, dim3(grid), dim3(kWarps * 32), smem, stream, p, n, n_items, ctx->status, ptab);
     };
     switch (shape->key_dim) {
         case 128: e = launch(gdn_step_kernel<128>); break;

@@ -49,6 +49,16 @@ struct TTDecodeSession {
     const uint32_t *row_index;  // nullable: key s lives at row row_index[s] (compact selection)
 };
 
+// Sessions of a batched decode call that travel in the kernel parameters instead of a device
+// table: calls with up to kParamSessions sessions upload nothing (the work item of a CTA is derived
+// from its block index and item_prefix). n == 0 selects the device tables.
+constexpr uint32_t kParamSessions = 64;
+struct TTSessionTable {
+    TTDecodeSession s[kParamSessions];
+    uint32_t item_prefix[kParamSessions + 1];   // work items of the sessions before session i
+    uint32_t n;
+};
+
 struct tt_context {
     int device = 0;
     int sm_count = 0;
@@ -76,6 +86,7 @@ struct tt_context {
     uint32_t *h_keys = nullptr;
     uint32_t *h_rows = nullptr;
     void *h_tensor_maps = nullptr;
+    TTSessionTable session_table;       // the parameter form of the current decode call's sessions
     uint64_t launches = 0;
     uint32_t exchange_poll_limit = 0;   // 0: the exchange kernels' default (about a second)
     // last verify split plan: the part length only depends on the sessions' 128-key tile counts and
@@ -110,6 +121,22 @@ struct TTLaunchTimer {
     }
 };
 int tt_check_cuda(tt_context *ctx, cudaError_t e, const char *what);
+
+// Launch with programmatic stream serialization: the kernel may start while its predecessor in the
+// stream drains and must call pdl_wait() before it touches anything the predecessor wrote.
+// TT_NO_PDL=1 in the environment launches plainly (an A/B switch).
+bool tt_pdl_enabled();
+template <typename... KArgs, typename... Args>
+cudaError_t tt_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tt_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 struct TTBusyGuard {
     tt_context *ctx;

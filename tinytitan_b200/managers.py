@@ -143,6 +143,14 @@ class KVCacheManager:
         """Row copies of reserve() are enqueued on this stream from now on instead of the legacy default stream."""
         L.check(L.lib().tt_kv_cache_bind_stream(self.handle, _stream(command_buffer)))
 
+    def write_rows(self, layer: int, slots, positions, k_rows, v_rows, src_stride_bytes: int, command_buffer=None):
+        """kSlot / vSlot for a decode batch: row i of k_rows / v_rows goes to (slots[i], positions[i]); one launch.
+        slots / positions: numpy uint32 arrays (kept by the caller between steps when they do not change)."""
+        L.check(L.lib().tt_kv_cache_write_rows(
+            self.handle, 0 if self._allocator is not None else _stream(command_buffer), layer, slots.ctypes.data,
+            positions.ctypes.data, len(slots), k_rows.data_ptr() if hasattr(k_rows, "data_ptr") else int(k_rows),
+            v_rows.data_ptr() if hasattr(v_rows, "data_ptr") else int(v_rows), src_stride_bytes))
+
     def reserve(self, tokens: int, slot: int = 0):
         L.check(L.lib().tt_kv_cache_reserve(self.handle, tokens, slot))
 

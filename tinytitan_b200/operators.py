@@ -81,6 +81,7 @@ class Context:
 
     PROFILE_DECODE_PARTIAL = 1
     PROFILE_GDN_STEP = 2
+    PROFILE_EXCHANGE = 4
 
     def profile_enable(self, enabled=True):
         """`enabled`: False/0 off, True/1 the split-KV pass-1 kernel, or a mask of PROFILE_*."""
