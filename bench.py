@@ -17,6 +17,11 @@ d 128, fp32 state) per session per step. Ranks share nothing (weak scaling, no c
           state (as in the reference), not per-step inputs.
   roofline   the split-KV pass-1 kernel against the measured HBM copy bandwidth
   cpu_baseline / --impl reference   the reference's CPU path on the host cores (bounded sample)
+
+Timing: the `--steps`-long loop is one batch (barrier + synchronize on both sides, CUDA events, max
+over ranks); batches are repeated until at least half a second has been timed, `ms_per_step` is the
+MEDIAN batch divided by the steps, the spread of the batches is reported next to it, and the clocks
+are sampled while the batches run.
 """
 from __future__ import annotations
 
@@ -80,7 +85,7 @@ def algorithmic_bytes(lens):
 CPU_SAMPLE_SESSIONS = 8
 
 
-def cpu_step_setup(lens):
+def cpu_step_setup(lens, threads=None):
     import oracle
     rng = np.random.default_rng(7)
     sample = lens[:CPU_SAMPLE_SESSIONS]
@@ -99,7 +104,7 @@ def cpu_step_setup(lens):
     state = (0.02 * rng.standard_normal((n, GV, GD, GD), dtype=np.float32))
     zeros = np.zeros(GV, np.float32)
     use_ref = oracle.ref() is not None
-    threads = oracle.max_threads()
+    threads = threads or oracle.max_threads()
 
     def step():
         oracle.cpu_engine_attention_sessions(query, keys, values, sample, bases, HKV, SCALE, threads)
@@ -113,16 +118,18 @@ def cpu_step_setup(lens):
     return step, n, threads, desc, ("reference+port" if use_ref else "port")
 
 
-def time_cpu(lens, steps, warmup):
-    step, n, threads, desc, kind = cpu_step_setup(lens)
-    for _ in range(max(1, warmup)):
+def time_cpu(lens, steps, warmup, threads=None):
+    step, n, threads, desc, kind = cpu_step_setup(lens, threads)
+    for _ in range(warmup):
         step()
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
     dt = (time.perf_counter() - t0) / steps
-    return {"value": n / dt, "unit": UNIT, "cores": threads, "kind": "port" if kind == "port" else "port",
-            "sample": desc, "ms_per_step": dt * 1e3, "gdn_kernel": kind}
+    # attention is the C port of the Swift engine (the Swift original cannot be built here), so the arm is a
+    # "port" even when the GDN half runs the reference's own compiled kernel
+    return {"value": n / dt, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc, "ms_per_step": dt * 1e3,
+            "gdn_kernel": kind}
 
 
 def cpu_side_baselines():
@@ -166,11 +173,12 @@ def run_reference_arm(args):
     if rank != 0:
         return 0
     lens = session_lengths(0)
-    steps = max(1, min(args.steps, 5))
-    res = time_cpu(lens, steps, min(args.warmup, 1))
+    # a CPU step of the 8-session sample is ~60 ms on 16 cores: K steps and W warm-ups as asked
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    res = time_cpu(lens, steps, warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
-        "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+        "steps": steps, "warmup": warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": config_dict(args.gpus, lens),
         "cpu_baseline": {"value": res["value"], "unit": UNIT, "cores": res["cores"], "kind": "port",
@@ -186,7 +194,7 @@ def run_reference_arm(args):
 # GPU arm
 # ------------------------------------------------------------------------------------------
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks / throttle reasons sampled every 100 ms while the timed batches run."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -197,7 +205,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu_index)],
+                                          "-lms", "100", "-i", str(self.gpu_index)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -305,8 +313,9 @@ class Workload:
                             conv_out_offset=s * la.qkv_dim * esz, a_proj_offset=s * GV * esz,
                             b_proj_offset=s * GV * esz, y_offset=s * GV * GD * esz) for s in range(N_SESSIONS)]
         self.gdn_batch = self.gdn.prepare_batch(gs)
-        # rows of the KV store that receive each session's newest token (position S_i - 1)
-        self.new_rows = torch.tensor([s * cap + n - 1 for s, n in enumerate(self.lens)], device="cuda")
+        # where each session's newest token goes: (slot, position S_i - 1), written by tt_kv_cache_write_rows
+        self.new_slots = np.arange(N_SESSIONS, dtype=np.uint32)
+        self.new_positions = np.array([n - 1 for n in self.lens], np.uint32)
         # pinned host side of the end-to-end step
         self.d_newkv.copy_(torch.randn(2, N_SESSIONS, self.row_elems, device="cuda", generator=gen).half())
         self.h_in = torch.empty(self.d_in.shape, dtype=torch.float16).pin_memory().copy_(self.d_in.cpu())
@@ -322,15 +331,15 @@ class Workload:
     def step_e2e(self):
         t = self.torch
         self.d_in.copy_(self.h_in, non_blocking=True)                # q, conv/a/b rows, new K/V rows: one copy
-        self.k_all.index_copy_(0, self.new_rows, self.d_newkv[0])   # the projection's write into kSlot/vSlot
-        self.v_all.index_copy_(0, self.new_rows, self.d_newkv[1])
+        # the projections' write into kSlot / vSlot of every session: one launch of the library's own
+        self.kv.write_rows(0, self.new_slots, self.new_positions, self.d_newkv[0], self.d_newkv[1], self.row_elems * 2)
         self.step()
         self.h_out.copy_(self.d_out, non_blocking=True)              # attention rows and GDN y: one copy
         t.cuda.current_stream().synchronize()   # the caller reads the step's result
 
 
 def timed_loop(torch, dist, world, fn, steps):
-    """Barrier + synchronize on both sides, CUDA events on the launching stream, max over ranks."""
+    """One batch: barrier + synchronize on both sides, CUDA events on the launching stream, max over ranks."""
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if world > 1:
         dist.barrier()
@@ -346,6 +355,14 @@ def timed_loop(torch, dist, world, fn, steps):
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     return float(ms.item())
+
+
+def timed_batches(torch, dist, world, fn, steps, min_seconds=0.5, max_batches=400):
+    """`steps`-long batches repeated until `min_seconds` have been timed (at least 3 batches). Returns the
+    per-batch milliseconds; the count is fixed from the first batch so that every rank runs the same number."""
+    first = timed_loop(torch, dist, world, fn, steps)
+    n = int(min(max_batches, max(3, -(-min_seconds * 1e3 // max(first, 1e-3)))))
+    return [first] + [timed_loop(torch, dist, world, fn, steps) for _ in range(n - 1)]
 
 
 class _Skip(Exception):
@@ -459,16 +476,11 @@ def aux_measurements(w, pk, only=None, c5_sessions=64):
         pass
     except Exception as exc:
         aux["decode_c4_1gpu"] = {"error": str(exc)}
-    # config 5 on one GPU: 64 sessions x 4 draft rows, S = 16384 (+3), 32/2/256; GDN 4-row step with 64 value heads
-    try:
-        want("verify_c5")
-        n5, w5, s5, hq5 = c5_sessions, 4, 16384 + 3, 32
-        g = torch.Generator(device="cuda"); g.manual_seed(8)
-        k5 = torch.randn(n5, s5, HKV * HD, device="cuda", generator=g).half()
-        v5 = torch.randn(n5, s5, HKV * HD, device="cuda", generator=g).half()
-        q5 = torch.randn(n5, w5, hq5 * HD, device="cuda", generator=g).half(); o5 = torch.empty_like(q5)
-        ses = [tt.DecodeSession(q5[i], o5[i], k5[i], v5[i], s5, w5) for i in range(n5)]
-        batch = w.attn.prepare_batch(ses, HD, hq5, HKV, scale=SCALE, io_dtype=tt.TT_F16)
+    # config 5: 64 sessions x 4 draft rows, S = 16384 (+3), 32/2/256; GDN 4-row step with 64 value heads. Once with
+    # all 64 sessions on this GPU and once with 8 (the share of one GPU when the batch is sharded over 8).
+    def verify_case(n5, suffix):
+        w5, s5, hq5 = 4, 16384 + 3, 32
+        batch, keep = make_decode_batch(torch, tt, w.attn, [s5] * n5, hq5, w5, 8)
         ms = ev_time(lambda: w.attn.encode_prepared(batch), 10)
         w.ctx.profile_enable(w.ctx.PROFILE_DECODE_PARTIAL)
         for _ in range(10):
@@ -477,28 +489,35 @@ def aux_measurements(w, pk, only=None, c5_sessions=64):
         w.ctx.profile_enable(False)
         kms = sum(t) / max(1, len(t))
         b5 = n5 * s5 * HKV * HD * 2 * 2 + 2 * n5 * w5 * hq5 * HD * 2
-        aux["verify_c5_1gpu"] = {"ms": ms, "pass1_kernel_ms": kms, "GBps": b5 / ms / 1e6,
-                                 "frac_hbm": b5 / ms / 1e6 / pk["hbm_gbs"], "pass1_frac_hbm": b5 / kms / 1e6 / pk["hbm_gbs"],
-                                 "tok_per_s": n5 * w5 / ms * 1e3,
-                                 "note": "ms = whole call (table uploads, pass 1, combine), one Python call per step"}
-        del k5, v5
-        cfg5 = tt.LinearAttentionConfig(GK, 64, GD, GD)
-        st5 = 0.02 * torch.randn(n5, 64 * GD * GD, device="cuda", generator=g)
-        qk = torch.randn(n5 * w5, 2 * GK, GD, device="cuda", generator=g)
-        qk = qk / qk.norm(dim=-1, keepdim=True); qk[:, :GK] *= GD ** -0.5
-        conv5 = torch.cat([qk.reshape(n5 * w5, -1), torch.randn(n5 * w5, 64 * GD, device="cuda", generator=g)], 1).half().contiguous()
-        a5 = (-torch.randn(n5 * w5, 64, device="cuda", generator=g)).half(); b5g = torch.randn(n5 * w5, 64, device="cuda", generator=g).half()
-        y5 = torch.empty(n5 * w5, 64 * GD, device="cuda", dtype=torch.float16)
-        z5 = torch.zeros(64, device="cuda", dtype=torch.bfloat16)
-        gdn5 = tt.GDN(w.ctx, cfg5)
-        gs = [tt.GDNSession(conv5[i * w5:(i + 1) * w5], a5[i * w5:(i + 1) * w5], b5g[i * w5:(i + 1) * w5], st5[i],
-                            y5[i * w5:(i + 1) * w5]) for i in range(n5)]
-        gb = gdn5.prepare_batch(gs)
+        # host cost of one call: the split planner simulates the dispatch when the batch's tile counts change
+        # (a fresh context = a cold plan) and reuses the plan otherwise
+        cold_ctx = tt.Context(w.ctx.device)
+        cold_attn = tt.Attention(cold_ctx)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter(); cold_attn.encode_prepared(batch); cold_us = (time.perf_counter() - t0) * 1e6
+        t0 = time.perf_counter(); cold_attn.encode_prepared(batch); warm_us = (time.perf_counter() - t0) * 1e6
+        torch.cuda.synchronize()
+        cold_ctx.close()
+        aux["verify_c5" + suffix] = {"sessions": n5, "ms": ms, "pass1_kernel_ms": kms, "GBps": b5 / ms / 1e6,
+                                     "frac_hbm": b5 / ms / 1e6 / pk["hbm_gbs"], "pass1_frac_hbm": b5 / kms / 1e6 / pk["hbm_gbs"],
+                                     "tok_per_s": n5 * w5 / ms * 1e3, "host_us_first_call_cold_plan": cold_us,
+                                     "host_us_next_call_cached_plan": warm_us,
+                                     "note": "ms = whole call (table uploads, pass 1, combine), one Python call per step"}
+        del batch, keep
+        gdn5, gb, z5, keep2, cfg5 = make_gdn_batch(torch, tt, w.ctx, n5, 64, w5, 9)
         ms = ev_time(lambda: gdn5.encode_prepared(gb, z5, z5, rows=w5), 10)
         kms = kernel_ms(lambda: gdn5.encode_prepared(gb, z5, z5, rows=w5), 10)
         bg = n5 * 64 * GD * GD * 4 * 2 + n5 * w5 * (cfg5.qkv_dim + 64 * GD) * 2
-        aux["gdn_verify_c5_1gpu"] = {"ms": ms, "kernel_ms": kms, "GBps": bg / kms / 1e6,
-                                     "frac_hbm": bg / kms / 1e6 / pk["hbm_gbs"]}
+        aux["gdn_verify_c5" + suffix] = {"sessions": n5, "ms": ms, "kernel_ms": kms, "GBps": bg / kms / 1e6,
+                                         "frac_hbm": bg / kms / 1e6 / pk["hbm_gbs"]}
+
+    try:
+        want("verify_c5")
+        if only is None:
+            verify_case(64, "_1gpu")
+            verify_case(8, "_8sessions_share_of_one_gpu")
+        else:
+            verify_case(c5_sessions, "_1gpu")
     except _Skip:
         pass
     except Exception as exc:
@@ -579,6 +598,21 @@ def split_kv_c4(w, torch, dist, rank, world, pk):
 
     ms_nccl = timed(lambda: plain.step(q, k, v, hi - lo, out_a))
     ms_fused = timed(lambda: fused.step(q, k, v, hi - lo, out_b))
+    # Where the fused step's time goes: every rank's own kernel durations (event pairs the library records
+    # around pass 1 and around the merge + exchange kernel, whose duration INCLUDES its wait for the slowest
+    # peer) next to the wall figure above. wall - (pass 1 + exchange) on the fastest rank is launch gaps and
+    # host time; exchange(max over ranks) - exchange(min over ranks) is the skew the flag wait absorbs.
+    w.ctx.profile_enable(w.ctx.PROFILE_DECODE_PARTIAL | w.ctx.PROFILE_EXCHANGE)
+    dist.barrier(); torch.cuda.synchronize()
+    for _ in range(100):
+        fused.step(q, k, v, hi - lo, out_b)
+    torch.cuda.synchronize()
+    rec = w.ctx.profile_collect()
+    w.ctx.profile_enable(False)
+    mine = torch.tensor([statistics.mean(rec[0::2]) if rec else 0.0, statistics.mean(rec[1::2]) if rec else 0.0], device="cuda")
+    allr = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(allr, mine)
+    p1 = [float(t[0]) for t in allr]; ex = [float(t[1]) for t in allr]
     agree = float((out_a.float() - out_b.float()).abs().max().item())
     status = w.ctx.poll_status()
     fused.close()
@@ -586,14 +620,108 @@ def split_kv_c4(w, torch, dist, rank, world, pk):
     return {"S": s4, "keys_per_gpu": hi - lo, "ms_nccl_allgather": ms_nccl, "ms_fused_exchange": ms_fused,
             "GBps_aggregate_fused": bytes_total / ms_fused / 1e6,
             "frac_hbm_aggregate_fused": bytes_total / ms_fused / 1e6 / (pk["hbm_gbs"] * world),
+            "fused_kernels_ms": {"pass1_min": min(p1), "pass1_max": max(p1), "merge_exchange_min": min(ex),
+                                 "merge_exchange_max": max(ex),
+                                 "launch_and_host_ms": ms_fused - (min(p1) + min(ex)),
+                                 "skew_absorbed_by_the_flag_wait_ms": max(ex) - min(ex)},
             "max_abs_diff_between_paths": agree, "device_status": status,
             "note": "one Python call per step on every rank; device time, max over ranks"}
 
 
+def make_decode_batch(torch, tt, attn, lens, hq, q_rows, seed):
+    """A batched decode call over freshly drawn sessions of the given lengths (one KV store, slot layout)."""
+    g = torch.Generator(device="cuda"); g.manual_seed(seed)
+    n = len(lens)
+    cap = max(lens) + 8
+    k = torch.randn(n * cap, HKV * HD, device="cuda", generator=g).half()
+    v = torch.randn(n * cap, HKV * HD, device="cuda", generator=g).half()
+    q = torch.randn(n, q_rows, hq * HD, device="cuda", generator=g).half()
+    o = torch.empty_like(q)
+    row = HKV * HD * 2
+    ses = [tt.DecodeSession(q, o, k, v, lens[i], q_rows, 0, q_offset=i * q_rows * hq * HD * 2, out_offset=i * q_rows * hq * HD * 2,
+                            k_offset=i * cap * row, v_offset=i * cap * row) for i in range(n)]
+    batch = attn.prepare_batch(ses, HD, hq, HKV, scale=SCALE, io_dtype=tt.TT_F16)
+    return batch, (k, v, q, o)
+
+
+def make_gdn_batch(torch, tt, ctx, n, hv, rows, seed):
+    g = torch.Generator(device="cuda"); g.manual_seed(seed)
+    cfg = tt.LinearAttentionConfig(GK, hv, GD, GD)
+    st = 0.02 * torch.randn(n, hv * GD * GD, device="cuda", generator=g)
+    qk = torch.randn(n * rows, 2 * GK, GD, device="cuda", generator=g)
+    qk = qk / qk.norm(dim=-1, keepdim=True); qk[:, :GK] *= GD ** -0.5
+    conv = torch.cat([qk.reshape(n * rows, -1), torch.randn(n * rows, hv * GD, device="cuda", generator=g)], 1).half().contiguous()
+    a = (-torch.randn(n * rows, hv, device="cuda", generator=g)).half(); b = torch.randn(n * rows, hv, device="cuda", generator=g).half()
+    y = torch.empty(n * rows, hv * GD, device="cuda", dtype=torch.float16)
+    z = torch.zeros(hv, device="cuda", dtype=torch.bfloat16)
+    gdn = tt.GDN(ctx, cfg)
+    gs = [tt.GDNSession(conv[i * rows:(i + 1) * rows], a[i * rows:(i + 1) * rows], b[i * rows:(i + 1) * rows], st[i],
+                        y[i * rows:(i + 1) * rows]) for i in range(n)]
+    return gdn, gdn.prepare_batch(gs), z, (st, conv, a, b, y), cfg
+
+
+def sharded_configs(w, torch, dist, rank, world, pk):
+    """Configs 2 and 5 as stated: a FIXED batch (32 drawn sessions; 64 verify sessions of 4 draft rows at
+    context 16384) split over the `world` GPUs with no collective. The whole batch is first timed on rank 0
+    alone, then every rank runs its shard; value = sessions of the whole batch / max-over-ranks step time,
+    efficiency = t(1 GPU) / (world * t(world GPUs))."""
+    from tinytitan_b200 import sharding
+    tt = w.tt
+    out = {}
+
+    def device_ms(fn, reps, everyone=True):
+        for _ in range(3):
+            fn()
+        if everyone:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda")
+        if everyone:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def one_config(name, lens, hq, q_rows, hv, reps):
+        # whole batch on rank 0 alone
+        t1 = torch.zeros(1, device="cuda")
+        if rank == 0:
+            batch, keep = make_decode_batch(torch, tt, w.attn, lens, hq, q_rows, 900)
+            gdn, gb, z, keep2, _ = make_gdn_batch(torch, tt, w.ctx, len(lens), hv, q_rows, 901)
+            t1[0] = device_ms(lambda: (w.attn.encode_prepared(batch), gdn.encode_prepared(gb, z, z, rows=q_rows)), reps, everyone=False)
+            del batch, keep, gb, keep2
+            torch.cuda.empty_cache()
+        dist.broadcast(t1, 0)
+        shard = sharding.shard_sessions(lens, world, "greedy")[rank]
+        mine = [lens[i] for i in shard]
+        batch, keep = make_decode_batch(torch, tt, w.attn, mine, hq, q_rows, 910 + rank)
+        gdn, gb, z, keep2, cfg = make_gdn_batch(torch, tt, w.ctx, len(mine), hv, q_rows, 920 + rank)
+        tn = device_ms(lambda: (w.attn.encode_prepared(batch), gdn.encode_prepared(gb, z, z, rows=q_rows)), reps)
+        my_bytes = sum(mine) * HKV * HD * 2 * 2 + 2 * len(mine) * q_rows * hq * HD * 2 + \
+            len(mine) * hv * GD * GD * 4 * 2 + len(mine) * q_rows * (cfg.qkv_dim + hv * GD) * 2
+        b = torch.tensor([float(my_bytes)], device="cuda")
+        dist.all_reduce(b, op=dist.ReduceOp.MAX)
+        assert w.ctx.poll_status() == 0
+        out[name] = {"sessions_total": len(lens), "sessions_per_gpu": len(mine), "rows_per_session": q_rows,
+                     "ms_step_1gpu_whole_batch": float(t1.item()), "ms_step": tn,
+                     "tok_per_s": len(lens) * q_rows / tn * 1e3,
+                     "speedup_over_1gpu": float(t1.item()) / tn, "efficiency": float(t1.item()) / tn / world,
+                     "frac_hbm_per_gpu_heaviest_shard": float(b.item()) / tn / 1e6 / pk["hbm_gbs"],
+                     "note": "attention + GDN step of the shard per step, device time, max over ranks; greedy byte balancing"}
+        del batch, keep, gb, keep2
+
+    one_config("c2_strong", session_lengths(0) if N_SESSIONS == 32 else session_lengths(0), HQ, 1, GV, 200)
+    one_config("c5_sharded", [16384 + 3] * 64, 32, 4, 64, 50)
+    return out
+
+
 # ncu (dram__bytes_read.sum + dram__bytes_write.sum) of attn_decode_partial_kernel per algorithmic
-# byte, from the 8-session capture summarised in profiles/decode_partial_8sessions_ncu_full.md
-# (227.1 MB of DRAM traffic for 216.9 MB of algorithmic bytes). Traffic grows in proportion to
-# the keys processed, so a full launch is this ratio times its algorithmic bytes.
+# byte, from an 8-session capture of this workload (227.1 MB of DRAM traffic for 216.9 MB of
+# algorithmic bytes). Traffic grows in proportion to the keys processed, so a full launch is this
+# ratio times its algorithmic bytes.
 TRAFFIC_PER_ALGORITHMIC_BYTE = 1.047
 
 
@@ -621,10 +749,11 @@ def run_gpu_arm(args):
     torch.cuda.synchronize()
     sampler.start()
     launches0 = w.ctx.launch_count
-    # per-launch device time of the dominant kernel is recorded for the first <= 256 steps
+    batch_ms = timed_batches(torch, dist, world, w.step, args.steps)
+    launches = (w.ctx.launch_count - launches0) // len(batch_ms)       # per batch of `steps` steps
+    # per-launch device time of the dominant kernels (the library's own event pairs), one more batch
     w.ctx.profile_enable(w.ctx.PROFILE_DECODE_PARTIAL | w.ctx.PROFILE_GDN_STEP)
-    ms_total = timed_loop(torch, dist, world, w.step, args.steps)
-    launches = w.ctx.launch_count - launches0
+    timed_loop(torch, dist, world, w.step, min(args.steps, 128))
     both_ms = w.ctx.profile_collect()
     w.ctx.profile_enable(False)
     # a step launches the decode pass 1 and then the GDN step: the record alternates
@@ -633,24 +762,24 @@ def run_gpu_arm(args):
 
     for _ in range(3):
         w.step_e2e()
-    e2e_steps = max(1, min(args.steps, 200))
-    ms_e2e = timed_loop(torch, dist, world, w.step_e2e, e2e_steps)
-    # keep the same load running long enough for nvidia-smi (200 ms period) to see it
-    t_end = time.perf_counter() + 0.7
-    while time.perf_counter() < t_end:
-        for _ in range(50):
-            w.step()
-        torch.cuda.synchronize()
+    e2e_steps = args.steps
+    e2e_ms = timed_batches(torch, dist, world, w.step_e2e, e2e_steps)
     clocks = sampler.stop()
-    clocks["note"] = "sampled over the timed regions plus 0.7 s of the same step replayed afterwards"
+    clocks["note"] = "sampled every 100 ms over the timed batches of the device-resident and the end-to-end step"
 
-    c4 = None
+    c4 = strong = None
     if world > 1 and not args.no_aux:
         try:
             c4 = split_kv_c4(w, torch, dist, rank, world, pk)
         except Exception as exc:   # the same code runs on every rank, so a failure is common to all
             c4 = {"error": str(exc)}
+        try:
+            strong = sharded_configs(w, torch, dist, rank, world, pk)
+        except Exception as exc:
+            strong = {"error": str(exc)}
 
+    ms_total = statistics.median(batch_ms)
+    ms_e2e = statistics.median(e2e_ms)
     ms_per_step = ms_total / args.steps
     value = world * N_SESSIONS / (ms_per_step * 1e-3)
     e2e_value = world * N_SESSIONS / (ms_e2e / e2e_steps * 1e-3)
@@ -661,10 +790,14 @@ def run_gpu_arm(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "timing": {"batches": len(batch_ms), "steps_per_batch": args.steps, "statistic": "median batch",
+                       "ms_per_step_min": min(batch_ms) / args.steps, "ms_per_step_max": max(batch_ms) / args.steps,
+                       "timed_seconds": sum(batch_ms) / 1e3},
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": config_dict(world, w.lens),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h,
-                    "steps": e2e_steps, "ms_per_step": ms_e2e / e2e_steps},
+                    "steps": e2e_steps, "ms_per_step": ms_e2e / e2e_steps, "batches": len(e2e_ms),
+                    "ms_per_step_min": min(e2e_ms) / e2e_steps, "ms_per_step_max": max(e2e_ms) / e2e_steps},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "attn_decode_partial_kernel<256,2,half>", "achieved": achieved,
@@ -682,11 +815,16 @@ def run_gpu_arm(args):
             line["aux"] = aux_measurements(w, pk)
             cpu = time_cpu(w.lens, 3, 1)
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            # the reference runs decode attention on ONE thread (CPUQwen35.swift:313-348): the same sample, one thread
+            one = time_cpu(w.lens, 2, 1, threads=1)
+            line["cpu_baseline"]["single_thread"] = {"value": one["value"], "unit": UNIT, "cores": 1, "ms_per_step": one["ms_per_step"]}
             line["aux"]["cpu"] = cpu_side_baselines()
         else:
             line["cpu_baseline"] = None
             if c4 is not None:
                 line["aux"] = {"decode_c4_split_kv": c4}
+                if isinstance(strong, dict):
+                    line["aux"].update(strong)
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

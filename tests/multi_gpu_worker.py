@@ -32,6 +32,17 @@ def main():
         lc.step(q, k_local, v_local, hi - lo, out)
     torch.cuda.synchronize()
 
+    # the CPU oracle over ALL rows, computed once on rank 0 and broadcast: the bar every path below is held to
+    want = torch.empty(hq, hd, device="cuda")
+    if rank == 0:
+        import oracle
+        f = lambda t: t.float().cpu().numpy()
+        want.copy_(torch.from_numpy(oracle.attn_decode_split(f(q), f(k).reshape(s, hkv, hd), f(v).reshape(s, hkv, hd), hkv,
+                                                             0.0625, s, n_chunks=64)))
+    dist.broadcast(want, 0)
+    TOL = 2e-3
+    err = (out.float() - want).abs().max().item()
+    assert err <= TOL, f"rank {rank}: split-KV merge over NCCL differs from the oracle by {err}"
     full = torch.empty_like(out)
     attn.encode_full(q, k, v, full, hd, hq, hkv, s, scale=0.0625)      # single-GPU answer over all rows
     torch.cuda.synchronize()
@@ -51,6 +62,8 @@ def main():
         fused.step(q, k_local, v_local, hi - lo, out_f)
     torch.cuda.synchronize()
     assert ctx.poll_status() == 0
+    err = (out_f.float() - want).abs().max().item()
+    assert err <= TOL, f"rank {rank}: fused exchange differs from the oracle by {err}"
     err = (out_f.float() - full.float()).abs().max().item()
     assert err <= 1e-3, f"rank {rank}: fused exchange differs from single-GPU attention by {err}"
     assert (out_f.float() - out.float()).abs().max().item() <= 1e-3
@@ -63,6 +76,10 @@ def main():
     torch.cuda.synchronize()
     assert ctx.poll_status() == 0
     assert (out_t.float() - full.float()).abs().max().item() <= 1e-3
+    assert (out_t.float() - want).abs().max().item() <= TOL
+    if rank == 0:
+        print(f"ORACLE_MAX_ABS_ERR world={world} S={s} nccl={(out.float() - want).abs().max().item():.2e} "
+              f"fused={(out_f.float() - want).abs().max().item():.2e}")
     # device time of one step, both ways (max over ranks is taken by the reader of the log)
     def timed(fn, reps=50):
         for _ in range(5):

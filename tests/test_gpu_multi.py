@@ -12,7 +12,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
-def test_kv_split_merge_and_session_sharding_over_nccl():
+@pytest.mark.parametrize("seq", ["50001", "262144"])       # a ragged split, and the long-context configuration's size
+def test_kv_split_merge_and_session_sharding_over_nccl(seq, monkeypatch):
+    monkeypatch.setenv("TT_TEST_SEQ", seq)
     world = min(torch.cuda.device_count(), 8)
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

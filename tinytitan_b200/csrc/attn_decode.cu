@@ -68,10 +68,14 @@ struct DecodeSmem {
     static constexpr int kPitch = HD + 8;                          // elements per staged row
     static constexpr int kRowBytes = kPitch * 2;
     static constexpr int kTileBytes = kKeysPerBlock * kRowBytes;   // one K (or V) block
-    static constexpr int kStageBytes = 2 * kTileBytes;             // K block + V block
-    static constexpr int kRingBytes = kStages * kStageBytes;
-    static constexpr int kXchgBytes = 2 * 2 * 32 * 9 * 4;          // [buffer][warp][lane][8 scores + flag]
-    static constexpr int kTotal = kRingBytes + kXchgBytes + 64;
+    static constexpr int kStageBytes = 2 * kTileBytes;             // K block + V block (quantised variant's ring)
+    static constexpr int kRingBytes = kStages * kStageBytes;       // K ring followed by V ring
+    static constexpr int kVRing = kStages * kTileBytes;
+    static constexpr int kScorePitch = 24;                         // floats per query row of a handed-over score tile
+    static constexpr int kScoreBytes = 2 * 16 * kScorePitch * 4;   // [buffer][query row][key]
+    static constexpr int kXchgBytes = 2 * 2 * 32 * 9 * 4;          // quantised variant: [buffer][warp][lane][8 scores + flag]
+    static constexpr int kBars = 2 * kStages + 4;                  // k_full[], v_full[], s_full[2], s_empty[2]
+    static constexpr int kTotal = kRingBytes + kScoreBytes + kBars * 8;
 };
 
 __device__ __forceinline__ void pair_barrier() { asm volatile("bar.sync 1, 64;" ::: "memory"); }
@@ -79,14 +83,22 @@ __device__ __forceinline__ void pair_barrier() { asm volatile("bar.sync 1, 64;" 
 // ---------------------------------------------------------------------------------------
 // Pass 1. grid = items, block = one warp pair (64 threads), 4 CTAs per SM.
 //
-// Both warps of the pair stream the SAME 16-key blocks through one 3-stage ring; warp h owns
-// head-dim half h: it holds that half of the 16-row Q tile in registers, computes the partial
-// scores over its half, the two halves are added through a double-buffered exchange in shared
-// memory (one named barrier per block), both warps run the identical softmax update, and each
-// accumulates P.V for its own half of the output columns. The pair therefore ends with one
-// consistent (m, l) and the two halves of O -- no merge.
+// The two warps of a CTA have different jobs and run one block apart. Both products are
+// TRANSPOSED so that the 8-wide N dimension of mma.m16n8k16 is the query rows of one KV head
+// (8 with a GQA group of 8, two n-tiles for up to 16 packed rows) and the 16-wide M dimension is
+// filled by keys (Q.K^T) or head dimensions (P.V) -- nothing is padding:
+//   warp 0  streams K blocks through its own 3-stage ring (bulk copies, one per key row) and
+//           forms S^T = K . Q^T (A = the K block read with ldmatrix, B = the query rows held
+//           in registers), then hands the 16 x 8 score tile over through shared memory;
+//   warp 1  streams V blocks through its own ring, takes the score tile in the B-operand layout
+//           (one query row per lane quad-row, so a row's maximum is two shuffles), runs the
+//           online softmax and accumulates O^T += V^T . P^T (A = the V block read with
+//           ldmatrix.trans); it ends with (m, l) and the whole output tile.
+// Each warp refills the stage it has just read itself, so the rings need no cross-warp
+// synchronisation; the only hand-shake is a double-buffered score tile (two mbarrier pairs).
+// Every wait is bounded.
 // ---------------------------------------------------------------------------------------
-template <int HD, typename T>
+template <int HD, int NT, typename T>
 __global__ void __launch_bounds__(64, 4)
 attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
                            const TTDecodeSession *__restrict__ sessions, float *__restrict__ part_o,
@@ -95,11 +107,10 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
                            uint32_t q_row_stride, float scale_log2, uint32_t *__restrict__ status,
                            const __grid_constant__ TTSessionTable table, uint32_t table_keys_per_item) {
     using S = DecodeSmem<HD>;
-    constexpr int HH = HD / 2;          // head-dim half per warp
-    constexpr int KS = HH / 16;         // k-steps of the partial Q.K^T
-    constexpr int NT = HH / 8;          // n-tiles of this warp's half of O
+    constexpr int KS = HD / 16;         // k-steps of K.Q^T and m-tiles of V^T.P^T
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
 
     const uint32_t group = n_q_heads / n_kv_heads;
     // Calls with up to kParamSessions sessions carry them in the kernel parameters and derive the
@@ -131,222 +142,242 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
         ses = sessions[item.session];
     }
 
-    unsigned char *ring = smem;
-    float *xchg = reinterpret_cast<float *>(smem + S::kRingBytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::kRingBytes + S::kXchgBytes);
+    unsigned char *k_ring = smem;
+    unsigned char *v_ring = smem + S::kVRing;
+    float *score = reinterpret_cast<float *>(smem + S::kRingBytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::kRingBytes + S::kScoreBytes);
+    uint64_t *k_full = bars, *v_full = bars + kStages, *s_full = bars + 2 * kStages, *s_empty = bars + 2 * kStages + 2;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+        for (int b = 0; b < S::kBars; ++b) mbar_init(&bars[b], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-
+    __syncthreads();
     // everything above overlapped the tail of the kernel before this one in the stream; its
     // results (the query rows, the newest K/V rows, partials being merged) are read from here on
     pdl_wait();
-    // ---- this warp's half of the Q tile, straight into mma A fragments ----
-    uint32_t qf[KS][4];
-    {
-        const uint32_t r0 = lane >> 2, r1 = r0 + 8;
-        const T *q0 = nullptr, *q1 = nullptr;
-        if (r0 < item.row_count) {
-            const uint32_t packed = item.row_begin + r0;
-            q0 = reinterpret_cast<const T *>(ses.q) + (size_t)(packed / group) * q_row_stride +
-                 (size_t)(item.kv_head * group + packed % group) * HD + warp * HH + (lane & 3) * 2;
-        }
-        if (r1 < item.row_count) {
-            const uint32_t packed = item.row_begin + r1;
-            q1 = reinterpret_cast<const T *>(ses.q) + (size_t)(packed / group) * q_row_stride +
-                 (size_t)(item.kv_head * group + packed % group) * HD + warp * HH + (lane & 3) * 2;
-        }
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            qf[ks][0] = q0 ? *reinterpret_cast<const uint32_t *>(q0 + ks * 16) : 0u;
-            qf[ks][1] = q1 ? *reinterpret_cast<const uint32_t *>(q1 + ks * 16) : 0u;
-            qf[ks][2] = q0 ? *reinterpret_cast<const uint32_t *>(q0 + ks * 16 + 8) : 0u;
-            qf[ks][3] = q1 ? *reinterpret_cast<const uint32_t *>(q1 + ks * 16 + 8) : 0u;
-        }
-    }
 
     const uint32_t n_keys = item.key_end - item.key_begin;
     const uint32_t n_blocks = (n_keys + kKeysPerBlock - 1) / kKeysPerBlock;
-    const unsigned char *kbase = reinterpret_cast<const unsigned char *>(ses.k) + (size_t)item.kv_head * HD * 2;
-    const unsigned char *vbase = reinterpret_cast<const unsigned char *>(ses.v) + (size_t)item.kv_head * HD * 2;
-
-    auto block_valid = [&](uint32_t i) {
-        return min((uint32_t)kKeysPerBlock, n_keys - i * kKeysPerBlock);
-    };
-    // thread 0 announces the bytes of block i; ordered before the copies by a barrier
-    auto announce = [&](uint32_t i) {
-        mbar_expect_tx(&bars[i % kStages], block_valid(i) * 2u * (uint32_t)(HD * 2));
-    };
-    // warp 0 fetches the K rows of block i, warp 1 the V rows (lanes 0..15, one row each)
-    auto issue = [&](uint32_t i) {
+    auto block_valid = [&](uint32_t i) { return min((uint32_t)kKeysPerBlock, n_keys - i * kKeysPerBlock); };
+    // lanes 0..15 of a warp fetch one row each of block i into the warp's own ring
+    auto issue = [&](uint32_t i, unsigned char *ring, const unsigned char *base, uint64_t *full, bool zero_fill) {
+        const uint32_t valid = block_valid(i), stage = i % kStages;
+        if (lane == 0) mbar_expect_tx(&full[stage], valid * (uint32_t)(HD * 2));
+        __syncwarp();
         if (lane < kKeysPerBlock) {
-            const uint32_t valid = block_valid(i);
-            unsigned char *dst = ring + (i % kStages) * S::kStageBytes + warp * S::kTileBytes + lane * S::kRowBytes;
+            unsigned char *dst = ring + stage * S::kTileBytes + lane * S::kRowBytes;
             if ((uint32_t)lane < valid) {
                 uint32_t p = item.key_begin + i * kKeysPerBlock + lane;
                 if (ses.row_index != nullptr) p = ses.row_index[p];
                 if (ses.ring_capacity) p %= ses.ring_capacity;
-                bulk_copy_g2s(dst, (warp ? vbase : kbase) + (size_t)p * kv_stride_bytes, HD * 2, &bars[i % kStages]);
-            } else if (warp == 1) {
+                bulk_copy_g2s(dst, base + (size_t)p * kv_stride_bytes, HD * 2, &full[stage]);
+            } else if (zero_fill) {
                 // a V row that is never fetched must still be finite: it meets p == 0 in P.V
                 const uint4 z = make_uint4(0u, 0u, 0u, 0u);
                 for (int c = 0; c < HD / 8; ++c) reinterpret_cast<uint4 *>(dst)[c] = z;
             }
         }
     };
+    bool timed_out = false;
+    uint32_t consumed = 0, issued = 0;      // blocks of this warp's own ring
 
-    float m_run[2] = {-INFINITY, -INFINITY};
-    float l_run[2] = {0.f, 0.f};
-    float acc[NT][4];
+    if (warp == 0) {
+        // ================= K . Q^T =================
+        const unsigned char *kbase = reinterpret_cast<const unsigned char *>(ses.k) + (size_t)item.kv_head * HD * 2;
+        // the query rows as B fragments: lane (g, t) holds dims 2t, 2t+1 (+8) of row g of every n-tile
+        uint32_t qf[NT][KS][2];
 #pragma unroll
-    for (int n = 0; n < NT; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
-
-    // visible-key limit of the two rows this thread owns; rows past row_count are never
-    // written, so they take the tile's smallest limit and need no masking of their own
-    const uint32_t w_first = item.row_begin / group;
-    const uint32_t limit_min = ses.seq_len - (ses.q_rows - 1 - w_first);
-    uint32_t limit[2];
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t r = nt * 8 + g;
+            const T *qp = nullptr;
+            if (r < item.row_count) {
+                const uint32_t packed = item.row_begin + r;
+                qp = reinterpret_cast<const T *>(ses.q) + (size_t)(packed / group) * q_row_stride +
+                     (size_t)(item.kv_head * group + packed % group) * HD + t * 2;
+            }
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const uint32_t r = (lane >> 2) + 8 * h;
-        limit[h] = r < item.row_count ? ses.seq_len - (ses.q_rows - 1 - (item.row_begin + r) / group) : limit_min;
+            for (int ks = 0; ks < KS; ++ks) {
+                qf[nt][ks][0] = qp ? *reinterpret_cast<const uint32_t *>(qp + ks * 16) : 0u;
+                qf[nt][ks][1] = qp ? *reinterpret_cast<const uint32_t *>(qp + ks * 16 + 8) : 0u;
+            }
+        }
+        for (; issued < n_blocks && issued < (uint32_t)kStages; ++issued) issue(issued, k_ring, kbase, k_full, false);
+        // A fragment of a K block: matrix j = lane / 8 covers keys 8 (j & 1) .. +7, dims 8 (j >> 1) .. +7
+        const uint32_t k_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * S::kRowBytes + (lane >> 4) * 16;
+        for (uint32_t i = 0; i < n_blocks; ++i) {
+            if (!warp_all(mbar_wait(&k_full[i % kStages], (i / kStages) & 1))) { timed_out = true; break; }
+            const uint32_t stage = smem_u32(k_ring + (i % kStages) * S::kTileBytes);
+            // two accumulator chains per n-tile (even / odd k-steps) halve the dependent MMA depth
+            float s0[NT][4], s1[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) { s0[nt][0] = s0[nt][1] = s0[nt][2] = s0[nt][3] = 0.f; s1[nt][0] = s1[nt][1] = s1[nt][2] = s1[nt][3] = 0.f; }
+#pragma unroll
+            for (int ks = 0; ks < KS; ks += 2) {
+                uint32_t a[4], b[4];
+                ldmatrix_x4(a, stage + k_off + ks * 32);
+                ldmatrix_x4(b, stage + k_off + (ks + 1) * 32);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    mma_16816<T>(s0[nt], a, qf[nt][ks][0], qf[nt][ks][1]);
+                    mma_16816<T>(s1[nt], b, qf[nt][ks + 1][0], qf[nt][ks + 1][1]);
+                }
+            }
+            consumed = i + 1;
+            __syncwarp();                                   // every lane has its fragments: the stage may be refilled
+            if (issued < n_blocks) { issue(issued, k_ring, kbase, k_full, false); ++issued; }
+            // hand the tile over: element (query row r, key k) at score[buffer][r][k]
+            if (i >= 2 && !warp_all(mbar_wait(&s_empty[i & 1], ((i >> 1) - 1) & 1))) { timed_out = true; break; }
+            float *sb = score + (i & 1) * 16 * S::kScorePitch;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                float *r0 = sb + (nt * 8 + 2 * t) * S::kScorePitch, *r1 = r0 + S::kScorePitch;
+                r0[g] = s0[nt][0] + s1[nt][0]; r1[g] = s0[nt][1] + s1[nt][1];
+                r0[g + 8] = s0[nt][2] + s1[nt][2]; r1[g + 8] = s0[nt][3] + s1[nt][3];
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_full[i & 1]);
+        }
+        if (timed_out) {
+            // blocks issued into this warp's ring and not yet waited for may still be landing
+            for (uint32_t b = consumed; b < issued; ++b) mbar_wait(&k_full[b % kStages], (b / kStages) & 1, 1u << 16);
+            if (lane == 0) atomicOr(status, TT_DEV_WAIT_TIMEOUT);
+        }
+        return;
     }
 
-    const uint32_t prologue = min(n_blocks, (uint32_t)(kStages - 1));
-    if (threadIdx.x == 0)
-        for (uint32_t i = 0; i < prologue; ++i) announce(i);
-    __syncthreads();
-    for (uint32_t i = 0; i < prologue; ++i) issue(i);
+    // ================= softmax and V^T . P^T =================
+    const unsigned char *vbase = reinterpret_cast<const unsigned char *>(ses.v) + (size_t)item.kv_head * HD * 2;
+    for (; issued < n_blocks && issued < (uint32_t)kStages; ++issued) issue(issued, v_ring, vbase, v_full, true);
 
-    bool timed_out = false;
-    uint32_t timed_block = 0;
-    const uint32_t k_off = ((lane & 7) + ((lane >> 4) << 3)) * S::kRowBytes + ((lane >> 3) & 1) * 16 + warp * HH * 2;
-    const uint32_t v_off = S::kTileBytes + ((lane & 7) + ((lane >> 3) & 1) * 8) * S::kRowBytes + (lane >> 4) * 16 +
-                           warp * HH * 2;
+    float acc[NT][KS][4];               // O^T: dims 16 mt + g (+8) x query rows 2t, 2t+1 of n-tile nt
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int mt = 0; mt < KS; ++mt) acc[nt][mt][0] = acc[nt][mt][1] = acc[nt][mt][2] = acc[nt][mt][3] = 0.f;
+    float m_run[NT], l_run[NT];         // of query row 8 nt + g; l is this lane's share (keys 2t, 2t+1, 2t+8, 2t+9)
+    uint32_t limit[NT];                 // visible-key limit of that row
+    const uint32_t w_first = item.row_begin / group;
+    const uint32_t limit_min = ses.seq_len - (ses.q_rows - 1 - w_first);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        m_run[nt] = -INFINITY; l_run[nt] = 0.f;
+        const uint32_t r = nt * 8 + g;
+        // rows past row_count are never written: they take the tile's smallest limit and need no masking of their own
+        limit[nt] = r < item.row_count ? ses.seq_len - (ses.q_rows - 1 - (item.row_begin + r) / group) : limit_min;
+    }
+    // A fragment of V^T: matrix j = lane / 8 covers keys 8 (j >> 1) .. +7, dims 8 (j & 1) .. +7 (read transposed)
+    const uint32_t v_off = ((lane & 7) + (lane >> 4) * 8) * S::kRowBytes + ((lane >> 3) & 1) * 16;
 
     for (uint32_t i = 0; i < n_blocks; ++i) {
-        const uint32_t nxt = i + kStages - 1;
-        if (threadIdx.x == 0 && nxt < n_blocks) announce(nxt);
-        const bool got = __all_sync(0xffffffffu, mbar_wait(&bars[i % kStages], (i / kStages) & 1)) != 0;
-
-        const uint32_t stage = smem_u32(ring + (i % kStages) * S::kStageBytes);
-        // ---- partial S over this warp's head-dim half: two independent chains per n-tile ----
-        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-        float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};
+        if (!warp_all(mbar_wait(&s_full[i & 1], (i >> 1) & 1))) { timed_out = true; break; }
+        const float *sb = score + (i & 1) * 16 * S::kScorePitch;
+        float sv[NT][4];
 #pragma unroll
-        for (int ks = 0; ks < KS; ks += 2) {
-            uint32_t b[4], c[4];
-            ldmatrix_x4(b, stage + k_off + ks * 32);
-            ldmatrix_x4(c, stage + k_off + (ks + 1) * 32);
-            mma_16816<T>(s0, qf[ks], b[0], b[1]);
-            mma_16816<T>(s1, qf[ks], b[2], b[3]);
-            mma_16816<T>(t0, qf[ks + 1], c[0], c[1]);
-            mma_16816<T>(t1, qf[ks + 1], c[2], c[3]);
+        for (int nt = 0; nt < NT; ++nt) {
+            const float2 lo = *reinterpret_cast<const float2 *>(sb + (nt * 8 + g) * S::kScorePitch + 2 * t);
+            const float2 hi = *reinterpret_cast<const float2 *>(sb + (nt * 8 + g) * S::kScorePitch + 2 * t + 8);
+            sv[nt][0] = lo.x; sv[nt][1] = lo.y; sv[nt][2] = hi.x; sv[nt][3] = hi.y;
         }
-        float *mine = xchg + (((i & 1) * 2 + warp) * 32 + lane) * 9;
-        const float *theirs = xchg + (((i & 1) * 2 + (warp ^ 1)) * 32 + lane) * 9;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) { mine[j] = s0[j] + t0[j]; mine[4 + j] = s1[j] + t1[j]; }
-        mine[8] = got ? 1.f : 0.f;
-        pair_barrier();
-        if (!(got && theirs[8] != 0.f)) { timed_out = true; timed_block = i; break; }   // same decision in both warps
-        float sv[2][4];  // [row half][key: n0c0 n0c1 n1c0 n1c1]
-        sv[0][0] = mine[0] + theirs[0]; sv[0][1] = mine[1] + theirs[1];
-        sv[1][0] = mine[2] + theirs[2]; sv[1][1] = mine[3] + theirs[3];
-        sv[0][2] = mine[4] + theirs[4]; sv[0][3] = mine[5] + theirs[5];
-        sv[1][2] = mine[6] + theirs[6]; sv[1][3] = mine[7] + theirs[7];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[i & 1]);
 
-        // every lane of the pair is past block i-1 now: its stage may be refilled
-        if (nxt < n_blocks) issue(nxt);
-
-        // ---- mask + online softmax (identical in both warps) ----
+        // ---- mask + online softmax of row 8 nt + g over this lane's four keys ----
         const uint32_t blk_key0 = item.key_begin + i * kKeysPerBlock;
         const bool plain = (blk_key0 + kKeysPerBlock <= limit_min) && (blk_key0 + kKeysPerBlock <= item.key_end) &&
                            (ses.keep == nullptr);
-        float alpha[2];
+        uint32_t pb[NT][2];
+        float alpha[NT];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int nt = 0; nt < NT; ++nt) {
             float mx = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                float s = sv[h][j] * scale_log2;
+                float s = sv[nt][j] * scale_log2;
                 if (!plain) {
-                    const uint32_t key = blk_key0 + (lane & 3) * 2 + (j >> 1) * 8 + (j & 1);
-                    bool ok = key < limit[h] && key < item.key_end;
+                    const uint32_t key = blk_key0 + 2 * t + (j >> 1) * 8 + (j & 1);
+                    bool ok = key < limit[nt] && key < item.key_end;
                     if (ok && ses.keep != nullptr) ok = ses.keep[key] != 0;
                     s = ok ? s : -INFINITY;
                 }
-                sv[h][j] = s;
+                sv[nt][j] = s;
                 mx = fmaxf(mx, s);
             }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(m_run[h], mx);
+            const float m_new = fmaxf(m_run[nt], mx);
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            alpha[h] = fast_exp2(m_run[h] - m_use);
-            m_run[h] = m_new;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) sv[h][j] = fast_exp2(sv[h][j] - m_use);
+            alpha[nt] = fast_exp2(m_run[nt] - m_use);
+            m_run[nt] = m_new;
+            pb[nt][0] = pack2<T>(fast_exp2(sv[nt][0] - m_use), fast_exp2(sv[nt][1] - m_use));
+            pb[nt][1] = pack2<T>(fast_exp2(sv[nt][2] - m_use), fast_exp2(sv[nt][3] - m_use));
+            // row sums from the ROUNDED weights the MMA consumes: O / l stays a convex combination
+            l_run[nt] = l_run[nt] * alpha[nt] + sum2<T>(pb[nt][0]) + sum2<T>(pb[nt][1]);
         }
-        uint32_t pa[4];
-        pa[0] = pack2<T>(sv[0][0], sv[0][1]);
-        pa[1] = pack2<T>(sv[1][0], sv[1][1]);
-        pa[2] = pack2<T>(sv[0][2], sv[0][3]);
-        pa[3] = pack2<T>(sv[1][2], sv[1][3]);
-        // row sums from the ROUNDED weights the MMA consumes: O / l stays a convex combination
-        l_run[0] = l_run[0] * alpha[0] + sum2<T>(pa[0]) + sum2<T>(pa[2]);
-        l_run[1] = l_run[1] * alpha[1] + sum2<T>(pa[1]) + sum2<T>(pa[3]);
-
-        if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+        // the accumulators hold query rows 2t, 2t+1: their factors live in the lanes of quad rows 2t and 2t+1
+        bool rescale = false;
 #pragma unroll
-            for (int n = 0; n < NT; ++n) {
-                acc[n][0] *= alpha[0]; acc[n][1] *= alpha[0];
-                acc[n][2] *= alpha[1]; acc[n][3] *= alpha[1];
+        for (int nt = 0; nt < NT; ++nt) rescale |= alpha[nt] != 1.f;
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const float a0 = __shfl_sync(0xffffffffu, alpha[nt], 8 * t), a1 = __shfl_sync(0xffffffffu, alpha[nt], 8 * t + 4);
+#pragma unroll
+                for (int mt = 0; mt < KS; ++mt) {
+                    acc[nt][mt][0] *= a0; acc[nt][mt][1] *= a1;
+                    acc[nt][mt][2] *= a0; acc[nt][mt][3] *= a1;
+                }
             }
         }
 
-        // ---- O(own half) += P V ----
+        // ---- O^T += V^T P^T ----
+        if (!warp_all(mbar_wait(&v_full[i % kStages], (i / kStages) & 1))) { timed_out = true; break; }
+        const uint32_t stage = smem_u32(v_ring + (i % kStages) * S::kTileBytes);
 #pragma unroll
-        for (int np = 0; np < NT / 2; ++np) {
-            uint32_t b[4];
-            ldmatrix_x4_trans(b, stage + v_off + np * 32);
-            mma_16816<T>(acc[2 * np], pa, b[0], b[1]);
-            mma_16816<T>(acc[2 * np + 1], pa, b[2], b[3]);
+        for (int mt = 0; mt < KS; ++mt) {
+            uint32_t a[4];
+            ldmatrix_x4_trans(a, stage + v_off + mt * 32);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) mma_16816<T>(acc[nt][mt], a, pb[nt][0], pb[nt][1]);
         }
+        consumed = i + 1;
+        __syncwarp();
+        if (issued < n_blocks) { issue(issued, v_ring, vbase, v_full, true); ++issued; }
     }
 
     if (timed_out) {
-        // the block that gave up and the one issued behind it may still be landing in this CTA's
-        // shared memory: give them a short, bounded chance to finish before the CTA exits
-        for (uint32_t b = timed_block; b < n_blocks && b < timed_block + 2; ++b)
-            mbar_wait(&bars[b % kStages], (b / kStages) & 1, 1u << 16);
+        for (uint32_t b = consumed; b < issued; ++b) mbar_wait(&v_full[b % kStages], (b / kStages) & 1, 1u << 16);
         if (lane == 0) atomicOr(status, TT_DEV_WAIT_TIMEOUT);
     }
 
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
-        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
-    }
-
-    // ---- write the partial: this warp's half of O, and (warp 0) m and l ----
+    // ---- write the partial: (m, l) of row 8 nt + g by the quad's first lane, O^T by everyone ----
     const uint32_t rows_total = ses.q_rows * n_q_heads;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const uint32_t r = (lane >> 2) + 8 * h;
-        if (r >= item.row_count) continue;
+    auto partial_row = [&](uint32_t r) {
         const uint32_t packed = item.row_begin + r;
         const uint32_t rho = (packed / group) * n_q_heads + item.kv_head * group + packed % group;
-        const size_t prow = (size_t)ses.partial_base + (size_t)item.part_index * rows_total + rho;
-        float *dst = part_o + prow * HD + warp * HH + (lane & 3) * 2;
+        return (size_t)ses.partial_base + (size_t)item.part_index * rows_total + rho;
+    };
 #pragma unroll
-        for (int n = 0; n < NT; ++n)
-            *reinterpret_cast<float2 *>(dst + n * 8) = make_float2(acc[n][2 * h], acc[n][2 * h + 1]);
-        if (warp == 0 && (lane & 3) == 0) {
-            part_m[prow] = m_run[h] * kLn2;   // natural-log domain, the reference's partial format
-            part_l[prow] = l_run[h];
+    for (int nt = 0; nt < NT; ++nt) {
+        float l = l_run[nt];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const uint32_t r = nt * 8 + g;
+        if (t == 0 && r < item.row_count) {
+            const size_t prow = partial_row(r);
+            part_m[prow] = m_run[nt] * kLn2;   // natural-log domain, the reference's partial format
+            part_l[prow] = l;
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t ro = nt * 8 + 2 * t + h;
+            if (ro >= item.row_count) continue;
+            float *dst = part_o + partial_row(ro) * HD + g;
+#pragma unroll
+            for (int mt = 0; mt < KS; ++mt) {
+                dst[mt * 16] = acc[nt][mt][h];
+                dst[mt * 16 + 8] = acc[nt][mt][2 + h];
+            }
         }
     }
 }
@@ -828,18 +859,29 @@ __global__ void attn_combine_parts_kernel(const float *__restrict__ m, const flo
     }
 }
 
-template <int HD, typename T>
-cudaError_t launch_partial(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
-                           const TTDecodeSession *sessions, float *part_o, float *part_m,
-                           float *part_l, const tt_attn_batch_params *p, uint32_t *status,
-                           const TTSessionTable &table, uint32_t table_keys) {
-    auto kernel = attn_decode_partial_kernel<HD, T>;
+template <int HD, int NT, typename T>
+cudaError_t launch_partial_nt(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
+                              const TTDecodeSession *sessions, float *part_o, float *part_m,
+                              float *part_l, const tt_attn_batch_params *p, uint32_t *status,
+                              const TTSessionTable &table, uint32_t table_keys) {
+    auto kernel = attn_decode_partial_kernel<HD, NT, T>;
     const int smem = DecodeSmem<HD>::kTotal;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     return tt_launch_pdl(kernel, dim3(n_items), dim3(64), (size_t)smem, stream, items, sessions, part_o, part_m, part_l,
                          p->n_q_heads, p->n_kv_heads, p->kv_token_stride_elements * 2u, p->q_row_stride_elements,
                          p->scale * kLog2e, status, table, table_keys);
+}
+
+// `wide_rows`: some session has more than 8 packed query rows per KV head (two n-tiles per item)
+template <int HD, typename T>
+cudaError_t launch_partial(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
+                           const TTDecodeSession *sessions, float *part_o, float *part_m,
+                           float *part_l, const tt_attn_batch_params *p, uint32_t *status,
+                           const TTSessionTable &table, uint32_t table_keys, bool wide_rows) {
+    if (wide_rows)
+        return launch_partial_nt<HD, 2, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys);
+    return launch_partial_nt<HD, 1, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys);
 }
 
 template <int HD, int BITS>
@@ -871,11 +913,11 @@ template <typename T>
 cudaError_t launch_partial_hd(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
                               const TTDecodeSession *sessions, float *part_o, float *part_m,
                               float *part_l, const tt_attn_batch_params *p, uint32_t *status,
-                              const TTSessionTable &table, uint32_t table_keys) {
+                              const TTSessionTable &table, uint32_t table_keys, bool wide_rows) {
     switch (p->head_dim) {
-        case 64: return launch_partial<64, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys);
-        case 128: return launch_partial<128, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys);
-        case 256: return launch_partial<256, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys);
+        case 64: return launch_partial<64, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys, wide_rows);
+        case 128: return launch_partial<128, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys, wide_rows);
+        case 256: return launch_partial<256, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys, wide_rows);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -1256,6 +1298,8 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     float *part_l = part_m + partial_cursor;
 
     const uint32_t table_keys = in_params ? keys_per_item : 0u;
+    bool wide_rows = false;             // more than 8 packed query rows per KV head somewhere: two n-tiles per item
+    for (uint32_t i = 0; i < n_sessions; ++i) wide_rows |= in_sessions[i].q_rows * group > 8;
     cudaError_t e = cudaSuccess;
     if (!in_params) {
         if (wide) {
@@ -1280,10 +1324,10 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
                                  table, table_keys, quant, meta_bytes);
     else if (p->io_dtype == TT_F16)
         e = launch_partial_hd<__half>(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status,
-                                      table, table_keys);
+                                      table, table_keys, wide_rows);
     else
         e = launch_partial_hd<__nv_bfloat16>(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p,
-                                             ctx->status, table, table_keys);
+                                             ctx->status, table, table_keys, wide_rows);
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_decode_partial launch");
     timer.stop();
     ctx->launches++;
@@ -1546,8 +1590,8 @@ TT_API int tt_attn_decode_noalloc(tt_stream stream, const void *q, const void *k
     p.head_dim = head_dim; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
     p.kv_token_stride_elements = n_kv_heads * head_dim; p.q_row_stride_elements = n_q_heads * head_dim;
     p.out_row_stride_elements = n_q_heads * head_dim; p.scale = scale; p.io_dtype = TT_F16;
-    if (launch_partial_hd<__half>(s, grid, nullptr, nullptr, part_o, part_m, part_l, &p, status, table, keys_per_item) !=
-        cudaSuccess)
+    if (launch_partial_hd<__half>(s, grid, nullptr, nullptr, part_o, part_m, part_l, &p, status, table, keys_per_item,
+                                  group > 8) != cudaSuccess)
         return TT_ERR_CUDA;
     attn_decode_combine_kernel<__half><<<dim3(1, n_q_heads, (head_dim / 4 + 15) / 16), 256, 0, s>>>(
         nullptr, part_o, part_m, part_l, n_q_heads, head_dim, n_q_heads * head_dim, 0, nullptr, nullptr, nullptr, table,
