@@ -58,18 +58,28 @@ def test_split_planner():
     rng = np.random.default_rng(0)
     keys = [int(x) for x in rng.integers(1024, 32769, size=32)]
     rc, per, items = _plan(keys, [1] * 32)
-    assert rc == 0 and per % 64 == 0 and 64 <= per <= 16384
-    assert items == sum(-(-k // per) for k in keys) * 2
-    assert 8 * 148 <= items <= 20 * 148            # enough items to balance, not so many that merges dominate
+    assert rc == 0 and per % 16 == 0 and 64 <= per <= 16384
+    # an item serves a PAIR of adjacent KV heads when the head count is even (whole cache rows are streamed)
+    assert items == sum(-(-k // per) for k in keys)
+    # 32 streams on 148 SMs x 2 resident CTAs: the items fill ONE wave as tightly as the ragged lengths allow,
+    # and a shorter item length would spill into a second, mostly empty wave
+    assert 0.9 * 296 <= items <= 296
+    assert sum(-(-k // (per - 16)) for k in keys) > 296
     # a single short session is not split below the minimum item length
     rc, per, items = _plan([4096], [1], hq=8)
-    assert rc == 0 and per == 64 and items == 64 * 2
-    # an empty range still yields one (empty) item per kv head
+    assert rc == 0 and per == 64 and items == 64
+    # an odd head count keeps one head per item
+    rc, per, items = _plan([4096], [1], hq=9, hkv=3)
+    assert rc == 0 and items == 3 * (-(-4096 // per))
+    # an empty range still yields one (empty) item per KV head pair
     rc, per, items = _plan([0], [1])
-    assert rc == 0 and items == 2
-    # 64 packed rows (4 draft rows x group 16) -> 4 row tiles per kv head
+    assert rc == 0 and items == 1
+    # 64 packed rows (4 draft rows x group 16) -> 4 row tiles per KV head pair; 256 streams take three waves
     rc, per, items = _plan([16384] * 64, [4] * 64, hq=32)
-    assert rc == 0 and items == 64 * 2 * 4 * (-(-16384 // per))
+    assert rc == 0 and items == 64 * 4 * (-(-16384 // per)) and 2 * 296 < items <= 3 * 296
+    # one long session: exactly one wave
+    rc, per, items = _plan([262144], [1])
+    assert rc == 0 and 0.95 * 296 <= items <= 296
     # workspace too small for even one part per session -> OOM status, never a silent truncation
     rc, _, _ = _plan([100000] * 8, [1] * 8, ws=1024)
     assert rc == L.TT_ERR_OOM

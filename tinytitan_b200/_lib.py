@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libtinytitan_cuda.so")
+# TINYTITAN_CUDA_LIB selects another build of the same library (e.g. one compiled with experiment flags)
+LIB_PATH = os.environ.get("TINYTITAN_CUDA_LIB") or os.path.join(_HERE, "libtinytitan_cuda.so")
 
 TT_OK, TT_ERR_INVALID_ARG, TT_ERR_UNSUPPORTED_SHAPE, TT_ERR_OOM, TT_ERR_CUDA, TT_ERR_TIMEOUT, TT_ERR_BUSY = range(7)
 TT_F16, TT_BF16 = 0, 1

@@ -63,56 +63,63 @@ __device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&c)[4], const ui
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int HD>
+// Shared memory of the fp16/bf16 pass-1 kernel for HPC KV heads per CTA.
+template <int HD, int HPC>
 struct DecodeSmem {
-    static constexpr int kPitch = HD + 8;                          // elements per staged row
+    static constexpr int kPitch = HPC * HD + 8;                    // elements per staged row (all HPC heads of a key)
     static constexpr int kRowBytes = kPitch * 2;
     static constexpr int kTileBytes = kKeysPerBlock * kRowBytes;   // one K (or V) block
-    static constexpr int kStageBytes = 2 * kTileBytes;             // K block + V block (quantised variant's ring)
-    static constexpr int kRingBytes = kStages * kStageBytes;       // K ring followed by V ring
-    static constexpr int kVRing = kStages * kTileBytes;
+    static constexpr int kVRing = kStages * kTileBytes;            // K ring first, V ring behind it
+    static constexpr int kRingBytes = 2 * kStages * kTileBytes;
     static constexpr int kScorePitch = 24;                         // floats per query row of a handed-over score tile
-    static constexpr int kScoreBytes = 2 * 16 * kScorePitch * 4;   // [buffer][query row][key]
-    static constexpr int kXchgBytes = 2 * 2 * 32 * 9 * 4;          // quantised variant: [buffer][warp][lane][8 scores + flag]
-    static constexpr int kBars = 2 * kStages + 4;                  // k_full[], v_full[], s_full[2], s_empty[2]
+    static constexpr int kScoreTile = 16 * kScorePitch;            // [query row][key]
+    static constexpr int kScoreBytes = HPC * 2 * kScoreTile * 4;   // [head][buffer]
+    static constexpr int kBars = 4 * kStages + 4 * HPC;            // k_full, v_full, k_empty, v_empty [kStages]; s_full, s_empty [HPC][2]
     static constexpr int kTotal = kRingBytes + kScoreBytes + kBars * 8;
 };
 
 __device__ __forceinline__ void pair_barrier() { asm volatile("bar.sync 1, 64;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------
-// Pass 1. grid = items, block = one warp pair (64 threads), 4 CTAs per SM.
+// Pass 1. grid = items, block = 2 * HPC warps; 4 / HPC CTAs per SM.
 //
-// The two warps of a CTA have different jobs and run one block apart. Both products are
-// TRANSPOSED so that the 8-wide N dimension of mma.m16n8k16 is the query rows of one KV head
-// (8 with a GQA group of 8, two n-tiles for up to 16 packed rows) and the 16-wide M dimension is
-// filled by keys (Q.K^T) or head dimensions (P.V) -- nothing is padding:
-//   warp 0  streams K blocks through its own 3-stage ring (bulk copies, one per key row) and
-//           forms S^T = K . Q^T (A = the K block read with ldmatrix, B = the query rows held
-//           in registers), then hands the 16 x 8 score tile over through shared memory;
-//   warp 1  streams V blocks through its own ring, takes the score tile in the B-operand layout
-//           (one query row per lane quad-row, so a row's maximum is two shuffles), runs the
-//           online softmax and accumulates O^T += V^T . P^T (A = the V block read with
-//           ldmatrix.trans); it ends with (m, l) and the whole output tile.
-// Each warp refills the stage it has just read itself, so the rings need no cross-warp
-// synchronisation; the only hand-shake is a double-buffered score tile (two mbarrier pairs).
-// Every wait is bounded.
+// A work item is (session, HPC adjacent KV heads, up to 16 packed query rows per head, key range).
+// With HPC = 2 a CTA streams whole cache rows (both KV heads of a key, 1 KB at head_dim 256) so
+// that DRAM is read in long contiguous pieces; a pure streaming read of 512-byte pieces at a 1 KB
+// pitch measured 6.6 TB/s on this part against 7.1 TB/s for whole rows.
+//
+// The warps of a CTA have different jobs and run one block apart. Both products are TRANSPOSED so
+// that the 8-wide N dimension of mma.m16n8k16 is the query rows of one KV head (8 with a GQA group
+// of 8, two n-tiles for up to 16 packed rows) and the 16-wide M dimension is filled by keys
+// (Q.K^T) or head dimensions (P.V) -- nothing is padding:
+//   warps 0 .. HPC-1      (one per KV head) form S^T = K . Q^T from the K ring (A = the K block read
+//                         with ldmatrix, B = the query rows held in registers) and hand the
+//                         16 x 8 score tile over through shared memory;
+//   warps HPC .. 2 HPC-1  take the score tile in the B-operand layout (one query row per lane
+//                         quad-row, so a row's maximum is two shuffles), run the online softmax
+//                         and accumulate O^T += V^T . P^T from the V ring (A = the V block read
+//                         with ldmatrix.trans); they end with (m, l) and the whole output tile.
+// K and V have their own 3-stage rings of bulk copies (one per key row, completion on the stage's
+// mbarrier). Warp 0 refills a K stage once every K.Q^T warp has released it, warp HPC a V stage
+// once every P.V warp has; the score tiles are double buffered per head. Every wait is bounded.
 // ---------------------------------------------------------------------------------------
-template <int HD, int NT, typename T>
-__global__ void __launch_bounds__(64, 4)
+template <int HD, int NT, int HPC, typename T>
+__global__ void __launch_bounds__(64 * HPC, 4 / HPC)
 attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
                            const TTDecodeSession *__restrict__ sessions, float *__restrict__ part_o,
                            float *__restrict__ part_m, float *__restrict__ part_l,
                            uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t kv_stride_bytes,
                            uint32_t q_row_stride, float scale_log2, uint32_t *__restrict__ status,
                            const __grid_constant__ TTSessionTable table, uint32_t table_keys_per_item) {
-    using S = DecodeSmem<HD>;
+    using S = DecodeSmem<HD, HPC>;
     constexpr int KS = HD / 16;         // k-steps of K.Q^T and m-tiles of V^T.P^T
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    const int role = warp / HPC, head = warp % HPC;   // role 0: K.Q^T, role 1: softmax + V^T.P^T
 
     const uint32_t group = n_q_heads / n_kv_heads;
+    const uint32_t n_kv_groups = n_kv_heads / HPC;
     // Calls with up to kParamSessions sessions carry them in the kernel parameters and derive the
     // work item from the block index (the items of a session are equal slices, item_prefix says
     // where each session's items start), so no table is copied to the device and a CTA starts
@@ -130,9 +137,9 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
         const uint32_t local = blockIdx.x - table.item_prefix[lo];
         const uint32_t packed_rows = ses.q_rows * group;
         const uint32_t row_tiles = (packed_rows + 15) / 16;
-        const uint32_t rt = local % row_tiles, kvh = (local / row_tiles) % n_kv_heads;
-        const uint32_t part = local / (row_tiles * n_kv_heads);
-        item.session = lo; item.kv_head = kvh; item.part_index = part; item.partial_base = ses.partial_base;
+        const uint32_t rt = local % row_tiles, kvg = (local / row_tiles) % n_kv_groups;
+        const uint32_t part = local / (row_tiles * n_kv_groups);
+        item.session = lo; item.kv_head = kvg * HPC; item.part_index = part; item.partial_base = ses.partial_base;
         item.key_begin = min(ses.seq_len, ses.kv_start + part * table_keys_per_item);
         item.key_end = min(ses.seq_len, item.key_begin + table_keys_per_item);
         item.row_begin = rt * 16;
@@ -141,15 +148,19 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
         item = items[blockIdx.x];
         ses = sessions[item.session];
     }
+    const uint32_t kv_head = item.kv_head + head;      // the head this warp serves
 
     unsigned char *k_ring = smem;
     unsigned char *v_ring = smem + S::kVRing;
-    float *score = reinterpret_cast<float *>(smem + S::kRingBytes);
+    float *score = reinterpret_cast<float *>(smem + S::kRingBytes) + head * 2 * S::kScoreTile;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::kRingBytes + S::kScoreBytes);
-    uint64_t *k_full = bars, *v_full = bars + kStages, *s_full = bars + 2 * kStages, *s_empty = bars + 2 * kStages + 2;
+    uint64_t *k_full = bars, *v_full = bars + kStages, *k_empty = bars + 2 * kStages, *v_empty = bars + 3 * kStages;
+    uint64_t *s_full = bars + 4 * kStages + head * 4, *s_empty = s_full + 2;
 
     if (threadIdx.x == 0) {
-        for (int b = 0; b < S::kBars; ++b) mbar_init(&bars[b], 1);
+        for (int b = 0; b < 2 * kStages; ++b) mbar_init(&bars[b], 1);                   // filled by one expect_tx arrival
+        for (int b = 2 * kStages; b < 4 * kStages; ++b) mbar_init(&bars[b], HPC);       // released by every reader warp
+        for (int b = 4 * kStages; b < S::kBars; ++b) mbar_init(&bars[b], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -160,10 +171,10 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
     const uint32_t n_keys = item.key_end - item.key_begin;
     const uint32_t n_blocks = (n_keys + kKeysPerBlock - 1) / kKeysPerBlock;
     auto block_valid = [&](uint32_t i) { return min((uint32_t)kKeysPerBlock, n_keys - i * kKeysPerBlock); };
-    // lanes 0..15 of a warp fetch one row each of block i into the warp's own ring
+    // lanes 0..15 of the issuing warp fetch one row each (all HPC heads of the key) of block i
     auto issue = [&](uint32_t i, unsigned char *ring, const unsigned char *base, uint64_t *full, bool zero_fill) {
         const uint32_t valid = block_valid(i), stage = i % kStages;
-        if (lane == 0) mbar_expect_tx(&full[stage], valid * (uint32_t)(HD * 2));
+        if (lane == 0) mbar_expect_tx(&full[stage], valid * (uint32_t)(HPC * HD * 2));
         __syncwarp();
         if (lane < kKeysPerBlock) {
             unsigned char *dst = ring + stage * S::kTileBytes + lane * S::kRowBytes;
@@ -171,18 +182,18 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
                 uint32_t p = item.key_begin + i * kKeysPerBlock + lane;
                 if (ses.row_index != nullptr) p = ses.row_index[p];
                 if (ses.ring_capacity) p %= ses.ring_capacity;
-                bulk_copy_g2s(dst, base + (size_t)p * kv_stride_bytes, HD * 2, &full[stage]);
+                bulk_copy_g2s(dst, base + (size_t)p * kv_stride_bytes, HPC * HD * 2, &full[stage]);
             } else if (zero_fill) {
                 // a V row that is never fetched must still be finite: it meets p == 0 in P.V
                 const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-                for (int c = 0; c < HD / 8; ++c) reinterpret_cast<uint4 *>(dst)[c] = z;
+                for (int c = 0; c < HPC * HD / 8; ++c) reinterpret_cast<uint4 *>(dst)[c] = z;
             }
         }
     };
     bool timed_out = false;
-    uint32_t consumed = 0, issued = 0;      // blocks of this warp's own ring
+    uint32_t consumed = 0, issued = 0;      // blocks of the ring this warp fills (warps 0 and HPC only)
 
-    if (warp == 0) {
+    if (role == 0) {
         // ================= K . Q^T =================
         const unsigned char *kbase = reinterpret_cast<const unsigned char *>(ses.k) + (size_t)item.kv_head * HD * 2;
         // the query rows as B fragments: lane (g, t) holds dims 2t, 2t+1 (+8) of row g of every n-tile
@@ -194,7 +205,7 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
             if (r < item.row_count) {
                 const uint32_t packed = item.row_begin + r;
                 qp = reinterpret_cast<const T *>(ses.q) + (size_t)(packed / group) * q_row_stride +
-                     (size_t)(item.kv_head * group + packed % group) * HD + t * 2;
+                     (size_t)(kv_head * group + packed % group) * HD + t * 2;
             }
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
@@ -202,9 +213,10 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
                 qf[nt][ks][1] = qp ? *reinterpret_cast<const uint32_t *>(qp + ks * 16 + 8) : 0u;
             }
         }
-        for (; issued < n_blocks && issued < (uint32_t)kStages; ++issued) issue(issued, k_ring, kbase, k_full, false);
+        if (head == 0)
+            for (; issued < n_blocks && issued < (uint32_t)kStages; ++issued) issue(issued, k_ring, kbase, k_full, false);
         // A fragment of a K block: matrix j = lane / 8 covers keys 8 (j & 1) .. +7, dims 8 (j >> 1) .. +7
-        const uint32_t k_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * S::kRowBytes + (lane >> 4) * 16;
+        const uint32_t k_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * S::kRowBytes + (lane >> 4) * 16 + head * HD * 2;
         for (uint32_t i = 0; i < n_blocks; ++i) {
             if (!warp_all(mbar_wait(&k_full[i % kStages], (i / kStages) & 1))) { timed_out = true; break; }
             const uint32_t stage = smem_u32(k_ring + (i % kStages) * S::kTileBytes);
@@ -223,12 +235,12 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
                     mma_16816<T>(s1[nt], b, qf[nt][ks + 1][0], qf[nt][ks + 1][1]);
                 }
             }
-            consumed = i + 1;
-            __syncwarp();                                   // every lane has its fragments: the stage may be refilled
-            if (issued < n_blocks) { issue(issued, k_ring, kbase, k_full, false); ++issued; }
+            __syncwarp();                                   // every lane has its fragments: this warp releases the stage
+            if (lane == 0) mbar_arrive(&k_empty[i % kStages]);
+            if (head == 0) consumed = i + 1;
             // hand the tile over: element (query row r, key k) at score[buffer][r][k]
             if (i >= 2 && !warp_all(mbar_wait(&s_empty[i & 1], ((i >> 1) - 1) & 1))) { timed_out = true; break; }
-            float *sb = score + (i & 1) * 16 * S::kScorePitch;
+            float *sb = score + (i & 1) * S::kScoreTile;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 float *r0 = sb + (nt * 8 + 2 * t) * S::kScorePitch, *r1 = r0 + S::kScorePitch;
@@ -237,9 +249,14 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_full[i & 1]);
+            if (head == 0 && issued < n_blocks) {           // block i + kStages goes into the stage block i just left
+                if (!warp_all(mbar_wait(&k_empty[i % kStages], (i / kStages) & 1))) { timed_out = true; break; }
+                issue(issued, k_ring, kbase, k_full, false);
+                ++issued;
+            }
         }
         if (timed_out) {
-            // blocks issued into this warp's ring and not yet waited for may still be landing
+            // blocks issued into the ring and not yet waited for may still be landing
             for (uint32_t b = consumed; b < issued; ++b) mbar_wait(&k_full[b % kStages], (b / kStages) & 1, 1u << 16);
             if (lane == 0) atomicOr(status, TT_DEV_WAIT_TIMEOUT);
         }
@@ -248,7 +265,8 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
 
     // ================= softmax and V^T . P^T =================
     const unsigned char *vbase = reinterpret_cast<const unsigned char *>(ses.v) + (size_t)item.kv_head * HD * 2;
-    for (; issued < n_blocks && issued < (uint32_t)kStages; ++issued) issue(issued, v_ring, vbase, v_full, true);
+    if (head == 0)
+        for (; issued < n_blocks && issued < (uint32_t)kStages; ++issued) issue(issued, v_ring, vbase, v_full, true);
 
     float acc[NT][KS][4];               // O^T: dims 16 mt + g (+8) x query rows 2t, 2t+1 of n-tile nt
 #pragma unroll
@@ -267,11 +285,11 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
         limit[nt] = r < item.row_count ? ses.seq_len - (ses.q_rows - 1 - (item.row_begin + r) / group) : limit_min;
     }
     // A fragment of V^T: matrix j = lane / 8 covers keys 8 (j >> 1) .. +7, dims 8 (j & 1) .. +7 (read transposed)
-    const uint32_t v_off = ((lane & 7) + (lane >> 4) * 8) * S::kRowBytes + ((lane >> 3) & 1) * 16;
+    const uint32_t v_off = ((lane & 7) + (lane >> 4) * 8) * S::kRowBytes + ((lane >> 3) & 1) * 16 + head * HD * 2;
 
     for (uint32_t i = 0; i < n_blocks; ++i) {
         if (!warp_all(mbar_wait(&s_full[i & 1], (i >> 1) & 1))) { timed_out = true; break; }
-        const float *sb = score + (i & 1) * 16 * S::kScorePitch;
+        const float *sb = score + (i & 1) * S::kScoreTile;
         float sv[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -340,9 +358,16 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) mma_16816<T>(acc[nt][mt], a, pb[nt][0], pb[nt][1]);
         }
-        consumed = i + 1;
         __syncwarp();
-        if (issued < n_blocks) { issue(issued, v_ring, vbase, v_full, true); ++issued; }
+        if (lane == 0) mbar_arrive(&v_empty[i % kStages]);
+        if (head == 0) {
+            consumed = i + 1;
+            if (issued < n_blocks) {
+                if (!warp_all(mbar_wait(&v_empty[i % kStages], (i / kStages) & 1))) { timed_out = true; break; }
+                issue(issued, v_ring, vbase, v_full, true);
+                ++issued;
+            }
+        }
     }
 
     if (timed_out) {
@@ -354,7 +379,7 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
     const uint32_t rows_total = ses.q_rows * n_q_heads;
     auto partial_row = [&](uint32_t r) {
         const uint32_t packed = item.row_begin + r;
-        const uint32_t rho = (packed / group) * n_q_heads + item.kv_head * group + packed % group;
+        const uint32_t rho = (packed / group) * n_q_heads + kv_head * group + packed % group;
         return (size_t)ses.partial_base + (size_t)item.part_index * rows_total + rho;
     };
 #pragma unroll
@@ -859,29 +884,31 @@ __global__ void attn_combine_parts_kernel(const float *__restrict__ m, const flo
     }
 }
 
-template <int HD, int NT, typename T>
+template <int HD, int NT, int HPC, typename T>
 cudaError_t launch_partial_nt(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
                               const TTDecodeSession *sessions, float *part_o, float *part_m,
                               float *part_l, const tt_attn_batch_params *p, uint32_t *status,
                               const TTSessionTable &table, uint32_t table_keys) {
-    auto kernel = attn_decode_partial_kernel<HD, NT, T>;
-    const int smem = DecodeSmem<HD>::kTotal;
+    auto kernel = attn_decode_partial_kernel<HD, NT, HPC, T>;
+    const int smem = DecodeSmem<HD, HPC>::kTotal;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    return tt_launch_pdl(kernel, dim3(n_items), dim3(64), (size_t)smem, stream, items, sessions, part_o, part_m, part_l,
+    return tt_launch_pdl(kernel, dim3(n_items), dim3(64 * HPC), (size_t)smem, stream, items, sessions, part_o, part_m, part_l,
                          p->n_q_heads, p->n_kv_heads, p->kv_token_stride_elements * 2u, p->q_row_stride_elements,
                          p->scale * kLog2e, status, table, table_keys);
 }
 
-// `wide_rows`: some session has more than 8 packed query rows per KV head (two n-tiles per item)
+// `wide_rows`: some session has more than 8 packed query rows per KV head (two n-tiles per item);
+// `hpc`: KV heads served by one CTA (tt_decode_heads_per_cta)
 template <int HD, typename T>
 cudaError_t launch_partial(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
                            const TTDecodeSession *sessions, float *part_o, float *part_m,
                            float *part_l, const tt_attn_batch_params *p, uint32_t *status,
-                           const TTSessionTable &table, uint32_t table_keys, bool wide_rows) {
-    if (wide_rows)
-        return launch_partial_nt<HD, 2, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys);
-    return launch_partial_nt<HD, 1, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys);
+                           const TTSessionTable &table, uint32_t table_keys, bool wide_rows, uint32_t hpc) {
+#define TT_P(NT, HPC) launch_partial_nt<HD, NT, HPC, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys)
+    if (hpc == 2) return wide_rows ? TT_P(2, 2) : TT_P(1, 2);
+    return wide_rows ? TT_P(2, 1) : TT_P(1, 1);
+#undef TT_P
 }
 
 template <int HD, int BITS>
@@ -913,11 +940,11 @@ template <typename T>
 cudaError_t launch_partial_hd(cudaStream_t stream, uint32_t n_items, const TTDecodeItem *items,
                               const TTDecodeSession *sessions, float *part_o, float *part_m,
                               float *part_l, const tt_attn_batch_params *p, uint32_t *status,
-                              const TTSessionTable &table, uint32_t table_keys, bool wide_rows) {
+                              const TTSessionTable &table, uint32_t table_keys, bool wide_rows, uint32_t hpc) {
     switch (p->head_dim) {
-        case 64: return launch_partial<64, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys, wide_rows);
-        case 128: return launch_partial<128, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys, wide_rows);
-        case 256: return launch_partial<256, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys, wide_rows);
+        case 64: return launch_partial<64, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys, wide_rows, hpc);
+        case 128: return launch_partial<128, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys, wide_rows, hpc);
+        case 256: return launch_partial<256, T>(stream, n_items, items, sessions, part_o, part_m, part_l, p, status, table, table_keys, wide_rows, hpc);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -929,40 +956,83 @@ cudaError_t launch_partial_hd(cudaStream_t stream, uint32_t n_items, const TTDec
 // ---------------------------------------------------------------------------------------
 static uint32_t ceil_div_u32(uint64_t a, uint64_t b) { return (uint32_t)((a + b - 1) / b); }
 
+// KV heads one pass-1 CTA of the fp16/bf16 kernel serves: adjacent pairs when the head count is
+// even, so that whole cache rows are streamed (quantised rows keep one head per CTA).
+static uint32_t tt_decode_heads_per_cta(uint32_t n_kv_heads, bool quantised) {
+    return (!quantised && n_kv_heads % 2 == 0) ? 2u : 1u;
+}
+
+static int plan_splits(const uint32_t *keys_per_session, const uint32_t *q_rows_per_session,
+                       uint32_t n_sessions, uint32_t head_dim, uint32_t n_q_heads,
+                       uint32_t n_kv_heads, uint32_t sm_count, size_t workspace_bytes, uint32_t heads_per_cta,
+                       uint32_t *out_keys_per_item, uint32_t *out_n_items);
+
 TT_API int tt_attn_plan_splits(const uint32_t *keys_per_session, const uint32_t *q_rows_per_session,
                                uint32_t n_sessions, uint32_t head_dim, uint32_t n_q_heads,
                                uint32_t n_kv_heads, uint32_t sm_count, size_t workspace_bytes,
                                uint32_t *out_keys_per_item, uint32_t *out_n_items) {
+    return plan_splits(keys_per_session, q_rows_per_session, n_sessions, head_dim, n_q_heads, n_kv_heads, sm_count,
+                       workspace_bytes, n_kv_heads ? tt_decode_heads_per_cta(n_kv_heads, false) : 1u, out_keys_per_item,
+                       out_n_items);
+}
+
+static int plan_splits(const uint32_t *keys_per_session, const uint32_t *q_rows_per_session,
+                       uint32_t n_sessions, uint32_t head_dim, uint32_t n_q_heads,
+                       uint32_t n_kv_heads, uint32_t sm_count, size_t workspace_bytes, uint32_t heads_per_cta,
+                       uint32_t *out_keys_per_item, uint32_t *out_n_items) {
     if (keys_per_session == nullptr || n_sessions == 0 || n_kv_heads == 0 || n_q_heads % n_kv_heads != 0 ||
         head_dim == 0 || sm_count == 0)
         return TT_ERR_INVALID_ARG;
     const uint32_t group = n_q_heads / n_kv_heads;
-    const uint32_t rows_per_item = 16u, items_per_sm = 12u;
-    // Streams of keys to be read: one per (session, kv head, row tile).
-    uint64_t key_rows = 0, max_rows = 0;
-    for (uint32_t i = 0; i < n_sessions; ++i) {
-        const uint32_t qr = q_rows_per_session ? q_rows_per_session[i] : 1u;
-        const uint32_t tiles = ceil_div_u32((uint64_t)qr * group, rows_per_item);
-        key_rows += (uint64_t)keys_per_session[i] * n_kv_heads * tiles;
-        max_rows += (uint64_t)qr * n_q_heads;
-    }
-    // Four 64-thread CTAs are resident per SM; ~12 items per SM give the hardware scheduler three
-    // waves to even out ragged sessions, while an item stays long enough (>= 64 keys, i.e. four
-    // pipeline blocks) to amortise its pipeline fill, which the co-resident CTAs overlap anyway.
-    uint64_t target = key_rows / ((uint64_t)sm_count * items_per_sm);
-    uint32_t keys = (uint32_t)((target + 63) / 64 * 64);
-    if (keys < 64) keys = 64;
-    if (keys > 16384) keys = 16384;
-    for (;;) {
-        uint64_t items = 0, prows = 0;
+    const uint32_t rows_per_item = 16u;
+    const uint32_t units_per_part = n_kv_heads / heads_per_cta;      // CTAs per (session, part, row tile)
+    // Items and partial rows of a candidate item length.
+    auto count = [&](uint32_t keys, uint64_t *items, uint64_t *prows) {
+        *items = 0; *prows = 0;
         for (uint32_t i = 0; i < n_sessions; ++i) {
             const uint32_t qr = q_rows_per_session ? q_rows_per_session[i] : 1u;
             const uint32_t tiles = ceil_div_u32((uint64_t)qr * group, rows_per_item);
             uint32_t parts = ceil_div_u32(keys_per_session[i], keys);
             if (parts == 0) parts = 1;  // an empty range still produces its (-inf, 0, 0) partial
-            items += (uint64_t)parts * n_kv_heads * tiles;
-            prows += (uint64_t)parts * qr * n_q_heads;
+            *items += (uint64_t)parts * units_per_part * tiles;
+            *prows += (uint64_t)parts * qr * n_q_heads;
         }
+    };
+    // The kernel is HBM-bound and its items are equal slices, so what matters is how the items fill the
+    // CTA slots of the machine (4 / heads_per_cta per SM): a launch of exactly `waves` full waves ends
+    // with every SM busy, one of 1.5 waves leaves half the machine idle for a third of the time
+    // (measured on one 262,144-key session: 90 us at one wave, 120 us at 1.5, 104 us at three). The item
+    // length is therefore the SHORTEST multiple of the 16-key block for which the items fit `waves`
+    // waves: one wave when a handful of long streams divide evenly (fewest partials to merge), three
+    // when many ragged sessions need the scheduler to even them out. TT_DECODE_WAVES overrides the
+    // choice (an experiment knob).
+    const uint64_t slots = (uint64_t)sm_count * (4u / heads_per_cta);
+    static const uint32_t waves_env = getenv("TT_DECODE_WAVES") ? (uint32_t)atoi(getenv("TT_DECODE_WAVES")) : 0u;
+    uint64_t streams = 0, max_keys = 0;
+    for (uint32_t i = 0; i < n_sessions; ++i) {
+        const uint32_t qr = q_rows_per_session ? q_rows_per_session[i] : 1u;
+        streams += (uint64_t)units_per_part * ceil_div_u32((uint64_t)qr * group, rows_per_item);
+        if (keys_per_session[i] > max_keys) max_keys = keys_per_session[i];
+    }
+    uint32_t waves = waves_env ? waves_env : (streams * 8 <= slots ? 1u : 3u);
+    uint32_t keys = 64;
+    if (streams >= waves * slots) {
+        keys = 1u << 30;                    // more streams than slots: one item per stream, nothing to split
+    } else {
+        // smallest multiple of 16 (at least 64) whose item count fits: the count falls as the length grows
+        uint32_t lo = 4, hi = (uint32_t)((max_keys + 15) / 16);      // in 16-key blocks
+        if (hi < lo) hi = lo;
+        while (lo < hi) {
+            const uint32_t mid = lo + (hi - lo) / 2;
+            uint64_t items, prows;
+            count(mid * 16, &items, &prows);
+            if (items <= waves * slots) hi = mid; else lo = mid + 1;
+        }
+        keys = lo * 16;
+    }
+    for (;;) {
+        uint64_t items, prows;
+        count(keys, &items, &prows);
         const uint64_t need = prows * ((uint64_t)head_dim + 2) * sizeof(float);
         if (workspace_bytes == 0 || need <= workspace_bytes || keys >= (1u << 30)) {
             if (workspace_bytes != 0 && need > workspace_bytes) return TT_ERR_OOM;
@@ -1242,11 +1312,12 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     // Up to kParamSessions sessions travel in the kernel parameters: nothing is uploaded and the
     // item table is never built (a CTA derives its item from the block index).
     const bool in_params = !wide && n_sessions <= kParamSessions;
+    const uint32_t hpc = tt_decode_heads_per_cta(p->n_kv_heads, quantised);
     TTSessionTable &table = ctx->session_table;
     table.n = 0;
     if (!wide) {
-        int rc = tt_attn_plan_splits(keys, rows, n_sessions, p->head_dim, p->n_q_heads, p->n_kv_heads,
-                                     (uint32_t)ctx->sm_count, ctx->workspace_bytes, &keys_per_item, &n_items);
+        int rc = plan_splits(keys, rows, n_sessions, p->head_dim, p->n_q_heads, p->n_kv_heads, (uint32_t)ctx->sm_count,
+                             ctx->workspace_bytes, hpc, &keys_per_item, &n_items);
         if (rc != TT_OK) return tt_set_error(ctx, rc, "split-KV partials do not fit the context workspace");
         if (!in_params && n_items > ctx->max_items)
             return tt_set_error(ctx, TT_ERR_OOM, "%u work items exceed the context's item table (%u)", n_items,
@@ -1267,14 +1338,14 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
             if (in_params) {
                 table.s[i] = s;
                 table.item_prefix[i] = item_cursor;
-                item_cursor += parts * p->n_kv_heads * ceil_div_u32(packed_rows, rows_per_item);
+                item_cursor += parts * (p->n_kv_heads / hpc) * ceil_div_u32(packed_rows, rows_per_item);
             } else {
                 for (uint32_t part = 0; part < parts; ++part) {
                     const uint32_t kb = s.kv_start + part * keys_per_item;
                     uint32_t ke = kb + keys_per_item;
                     if (ke > s.seq_len) ke = s.seq_len;
                     if (ke < kb) ke = kb;
-                    for (uint32_t kvh = 0; kvh < p->n_kv_heads; ++kvh)
+                    for (uint32_t kvh = 0; kvh < p->n_kv_heads; kvh += hpc)
                         for (uint32_t rb = 0; rb < packed_rows; rb += rows_per_item) {
                             TTDecodeItem &it = ctx->h_items[item_cursor++];
                             it.session = i; it.kv_head = kvh; it.key_begin = kb; it.key_end = ke;
@@ -1324,10 +1395,10 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
                                  table, table_keys, quant, meta_bytes);
     else if (p->io_dtype == TT_F16)
         e = launch_partial_hd<__half>(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status,
-                                      table, table_keys, wide_rows);
+                                      table, table_keys, wide_rows, hpc);
     else
         e = launch_partial_hd<__nv_bfloat16>(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p,
-                                             ctx->status, table, table_keys, wide_rows);
+                                             ctx->status, table, table_keys, wide_rows, hpc);
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_decode_partial launch");
     timer.stop();
     ctx->launches++;
@@ -1577,7 +1648,8 @@ TT_API int tt_attn_decode_noalloc(tt_stream stream, const void *q, const void *k
     ses.seq_len = seq_len; ses.q_rows = 1; ses.kv_start = kv_start;
     ses.n_parts = parts; ses.partial_base = 0; ses.ring_capacity = 0; ses.keep = nullptr; ses.row_index = nullptr;
     const uint32_t group = n_q_heads / n_kv_heads;
-    const uint32_t grid = parts * n_kv_heads * ceil_div_u32(group, 16);
+    const uint32_t hpc = tt_decode_heads_per_cta(n_kv_heads, false);
+    const uint32_t grid = parts * (n_kv_heads / hpc) * ceil_div_u32(group, 16);
     table.item_prefix[0] = 0; table.item_prefix[1] = grid; table.n = 1;
 
     cudaStream_t s = (cudaStream_t)stream;
@@ -1591,7 +1663,7 @@ TT_API int tt_attn_decode_noalloc(tt_stream stream, const void *q, const void *k
     p.kv_token_stride_elements = n_kv_heads * head_dim; p.q_row_stride_elements = n_q_heads * head_dim;
     p.out_row_stride_elements = n_q_heads * head_dim; p.scale = scale; p.io_dtype = TT_F16;
     if (launch_partial_hd<__half>(s, grid, nullptr, nullptr, part_o, part_m, part_l, &p, status, table, keys_per_item,
-                                  group > 8) != cudaSuccess)
+                                  group > 8, hpc) != cudaSuccess)
         return TT_ERR_CUDA;
     attn_decode_combine_kernel<__half><<<dim3(1, n_q_heads, (head_dim / 4 + 15) / 16), 256, 0, s>>>(
         nullptr, part_o, part_m, part_l, n_q_heads, head_dim, n_q_heads * head_dim, 0, nullptr, nullptr, nullptr, table,
