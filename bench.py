@@ -749,7 +749,7 @@ def run_gpu_arm(args):
     torch.cuda.synchronize()
     sampler.start()
     launches0 = w.ctx.launch_count
-    batch_ms = timed_batches(torch, dist, world, w.step, args.steps)
+    batch_ms = timed_batches(torch, dist, world, w.step, args.steps, args.min_seconds)
     launches = (w.ctx.launch_count - launches0) // len(batch_ms)       # per batch of `steps` steps
     # per-launch device time of the dominant kernels (the library's own event pairs), one more batch
     w.ctx.profile_enable(w.ctx.PROFILE_DECODE_PARTIAL | w.ctx.PROFILE_GDN_STEP)
@@ -763,7 +763,7 @@ def run_gpu_arm(args):
     for _ in range(3):
         w.step_e2e()
     e2e_steps = args.steps
-    e2e_ms = timed_batches(torch, dist, world, w.step_e2e, e2e_steps)
+    e2e_ms = timed_batches(torch, dist, world, w.step_e2e, e2e_steps, args.min_seconds)
     clocks = sampler.stop()
     clocks["note"] = "sampled every 100 ms over the timed batches of the device-resident and the end-to-end step"
 
@@ -845,6 +845,9 @@ def main():
                     choices=["gdn_step_c2", "prefill_c3", "gdn_scan_c3", "decode_c4", "verify_c5", "decode_c1"],
                     help="run one side measurement alone and exit (for profiler captures)")
     ap.add_argument("--c5-sessions", type=int, default=64, help="sessions of the config-5 side measurement")
+    ap.add_argument("--min-seconds", type=float, default=0.5,
+                    help="batches of --steps steps are repeated until this much time has been measured (0: three batches; "
+                         "for profiler captures)")
     args = ap.parse_args()
     global N_SESSIONS
     N_SESSIONS = args.sessions

@@ -100,7 +100,8 @@ int tt_ctx_profile_collect(tt_context *ctx, float *out_ms, uint32_t capacity, ui
  * affine-quantised rows [packed codes | fp16 scale per 64-element group | fp16 bias per
  * group] (KVCacheManager+Validation.swift:30-41), decoded as code*scale+bias
  * (attn_load_kv, attention.metal:89-117). Quantised rows need head_dim 128 or 256,
- * group_size 64, fp16 queries, 16-byte aligned strides, no keep mask and no ring. */
+ * group_size 64, fp16 queries and 16-byte aligned strides; a keep mask, a sliding window and
+ * a ring work as with fp16 rows. */
 typedef struct tt_kv_format {
     uint32_t bits;
     uint32_t stride_bytes; /* bytes per token row; 0 means n_kv_heads*head_dim*2 */
@@ -475,6 +476,20 @@ int tt_gdn_conv_mix(tt_context *ctx, tt_stream stream, void *tail, const void *q
                     uint32_t rows, int update_tail);
 /* GDN.encodeConvTailUpdate -> gdn_conv_tail_update (GDN.swift:238-262, gdn.metal:396-447):
  * tail := last taps-1 raw rows of [old tail | rows of qkv]. */
+/* The decode prologue of a GDN layer for a batch of sessions in one launch: what
+ * GDN.encodeConvDecode followed by GDN.encodeQKNorm (GDN.swift:185-229, :399-427) does with two
+ * launches per session. For every session: conv_out := SiLU(conv([tail | qkv])), the tail shifted
+ * in place, then the q and k heads of conv_out RMS-normed with the folded scales. Bit-identical to
+ * tt_gdn_conv_mix(update_tail = 1) + tt_gdn_qk_norm. key_dim <= 256; the value width must be a
+ * multiple of key_dim. */
+typedef struct tt_gdn_pre_session {
+    void *tail;       /* fp16 [(taps-1)][channels], updated in place */
+    const void *qkv;  /* fp16 [channels], the new raw row */
+    void *conv_out;   /* fp16 [channels] */
+} tt_gdn_pre_session;
+int tt_gdn_decode_pre(tt_context *ctx, tt_stream stream, const tt_gdn_pre_session *sessions,
+                      uint32_t n_sessions, const void *conv_weight, uint32_t n_k_heads,
+                      uint32_t key_dim, uint32_t channels, uint32_t taps);
 int tt_gdn_conv_tail_update(tt_context *ctx, tt_stream stream, void *tail, const void *qkv,
                             uint32_t channels, uint32_t taps, uint32_t rows);
 /* GDN.encodeConvTailCheckpoint -> gdn_conv_tail_checkpoint (GDN.swift:264-286,

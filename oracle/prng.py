@@ -27,7 +27,18 @@ class SplitMix64:
         return np.float32(lo) + (np.float32(hi) - np.float32(lo)) * u
 
     def uniform_array(self, n: int, lo: float, hi: float) -> np.ndarray:
-        return np.array([self.uniform(lo, hi) for _ in range(n)], dtype=np.float32)
+        """n successive uniform() draws, vectorised: the state advances by a constant, so draw i is a
+        function of state + (i + 1) * gamma (uint64 arithmetic wraps exactly like the scalar form)."""
+        if n == 0:
+            return np.zeros(0, np.float32)
+        with np.errstate(over="ignore"):
+            z = np.uint64(self.state) + (np.arange(1, n + 1, dtype=np.uint64) * np.uint64(0x9E3779B97F4A7C15))
+            self.state = int(z[-1])
+            z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+            z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+            z = z ^ (z >> np.uint64(31))
+        u = (z >> np.uint64(40)).astype(np.float32) / np.float32(1 << 24)
+        return (np.float32(lo) + (np.float32(hi) - np.float32(lo)) * u).astype(np.float32)
 
 
 def seed_tree_key(root: int, label: str) -> SplitMix64:

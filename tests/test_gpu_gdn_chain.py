@@ -134,3 +134,25 @@ def test_gated_norm_sigmoid_gate_and_production_width():
         assert np.abs(got[t, :cfg.qkv_dim] - want).max() <= 1e-3
     assert np.array_equal(got[:, cfg.qkv_dim:], conv[:, cfg.qkv_dim:])      # padding untouched
     assert np.array_equal(got[:, 2 * 16 * 128:cfg.qkv_dim], conv[:, 2 * 16 * 128:cfg.qkv_dim])   # v slice untouched
+
+
+def test_batched_decode_prologue_is_bit_identical_to_the_separate_kernels():
+    # conv + tail shift + q/k norm of a whole batch in one launch (tt_gdn_decode_pre) against
+    # tt_gdn_conv_mix(update_tail) + tt_gdn_qk_norm per session, at the production widths, over several steps
+    r = np.random.default_rng(19)
+    cfg = tt.LinearAttentionConfig(16, 32, 128, 128, 4)
+    gdn = tt.GDN(context(), cfg)
+    n, c = 5, cfg.qkv_dim
+    conv_w = dev(rounded(r.uniform(-0.4, 0.4, size=(c, 4)), torch.bfloat16), torch.bfloat16)
+    tails_a = dev(rounded(r.normal(size=(n, 3, c)))); tails_b = tails_a.clone()
+    out_a = torch.empty(n, c, device="cuda", dtype=torch.float16); out_b = torch.empty_like(out_a)
+    for step in range(3):
+        qkv = dev(rounded(r.normal(size=(n, c))))
+        for i in range(n):
+            gdn.encode_conv_decode(tails_a[i], qkv[i], conv_w, out_a[i])
+            gdn.encode_qk_norm(out_a[i])
+        launches = context().launch_count
+        gdn.encode_decode_prologue([(tails_b[i], qkv[i], out_b[i]) for i in range(n)], conv_w)
+        assert context().launch_count - launches == 1
+        torch.cuda.synchronize()
+        assert torch.equal(out_a, out_b) and torch.equal(tails_a, tails_b)

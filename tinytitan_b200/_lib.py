@@ -70,6 +70,10 @@ class GdnShape(C.Structure):
                 ("value_dim", C.c_uint32), ("flags", C.c_uint32), ("readout_scale", C.c_float)]
 
 
+class GdnPreSession(C.Structure):
+    _fields_ = [("tail", C.c_void_p), ("qkv", C.c_void_p), ("conv_out", C.c_void_p)]
+
+
 class GdnSession(C.Structure):
     _fields_ = [("conv_out", C.c_void_p), ("a", C.c_void_p), ("b", C.c_void_p), ("state", C.c_void_p),
                 ("y", C.c_void_p), ("checkpoint_state", C.c_void_p)]
@@ -155,6 +159,7 @@ SIGNATURES = {
     "tt_kv_window_reset_slot": (C.c_int, [_vp, _u32]),
     "tt_kv_window_host_row": (C.c_int, [_vp, _u32, _u32, _u32, C.c_int, _vp]),
     "tt_kv_window_counters": (None, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "tt_gdn_decode_pre": (C.c_int, [_vp, _vp, C.POINTER(GdnPreSession), _u32, _vp, _u32, _u32, _u32, _u32]),
     "tt_ctx_set_exchange_poll_limit": (C.c_int, [_vp, _u32]),
     "tt_attn_decode_noalloc_status": (C.c_int, [_vp, C.POINTER(_u32)]),
     "tt_attn_reference_split_geometry": (None, [_u32, _u32, _u32, _u32, C.c_int, C.POINTER(SplitGeometry)]),

@@ -1462,8 +1462,6 @@ static int decode_one(tt_context *ctx, tt_stream stream, const void *q, const vo
         if (kv_format->bits != 16 && kv_format->bits != 8 && kv_format->bits != 4)
             return tt_set_error(ctx, TT_ERR_INVALID_ARG, "KV bits must be 4, 8, or 16");
         if (kv_format->bits != 16) {
-            if (keep_mask != nullptr || ring_capacity != 0)
-                return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "quantised KV rows with a keep mask or ring are not implemented");
             if (kv_format->group_size != 64)
                 return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE, "quantisation group size must be 64");
             quant.bits = kv_format->bits; quant.stride_bytes = kv_format->stride_bytes; quant.value_bytes = kv_format->value_bytes;

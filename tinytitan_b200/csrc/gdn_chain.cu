@@ -113,6 +113,59 @@ __global__ void gdn_gated_norm_kernel(const __half *y, const __half *z, const __
     }
 }
 
+// The decode-step prologue of a Gated-DeltaNet layer in ONE launch for a whole batch of sessions:
+// causal conv + SiLU of the new qkv row with the in-place tail shift (gdn_conv_mix_decode), and the
+// q/k head norm with the folded scales (gdn_qk_norm). One warp per (session, Dk-wide channel group):
+// the q and k groups are heads and get the norm, the v groups only the conv. The conv output is
+// rounded to fp16 before the norm reads it, exactly as the separate kernels store and re-load it,
+// so the result is bit-identical to tt_gdn_conv_mix(update_tail = 1) followed by tt_gdn_qk_norm.
+constexpr uint32_t kPreSessions = 64;
+struct GdnPreTable {
+    struct Entry { __half *tail; const __half *qkv; __half *conv_out; } s[kPreSessions];
+};
+__global__ void __launch_bounds__(128)
+gdn_decode_pre_kernel(const __grid_constant__ GdnPreTable table, const __nv_bfloat16 *__restrict__ conv_w, uint32_t channels,
+                      uint32_t taps, uint32_t hk, uint32_t dk, uint32_t n_sessions) {
+    const uint32_t groups = (channels + dk - 1) / dk;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const uint32_t z = warp / groups, grp = warp % groups;
+    if (z >= n_sessions) return;
+    __half *tail = table.s[z].tail;
+    const __half *qkv = table.s[z].qkv;
+    __half *out = table.s[z].conv_out;
+    const int history = (int)taps - 1;
+    const bool is_head = grp < 2 * hk;                   // q heads, then k heads, then the value channels
+    float sumsq = 0.f;
+    constexpr int kMaxPerLane = 8;                       // dk <= 256
+    float vals[kMaxPerLane];
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+        const uint32_t ch = grp * dk + lane + 32 * i;
+        vals[i] = 0.f;
+        if (lane + 32 * i >= dk || ch >= channels) continue;
+        // decode arithmetic order of gdn_conv_mix_decode: current row first, then the tail rows
+        float acc = __half2float(qkv[ch]) * __bfloat162float(conv_w[(size_t)ch * taps + (taps - 1)]);
+        for (int j = 0; j < history; ++j)
+            acc = fmaf(__half2float(tail[(size_t)j * channels + ch]), __bfloat162float(conv_w[(size_t)ch * taps + j]), acc);
+        const __half rounded = __float2half_rn(silu(acc));
+        for (int j = 0; j + 1 < history; ++j) tail[(size_t)j * channels + ch] = tail[(size_t)(j + 1) * channels + ch];
+        if (history > 0) tail[(size_t)(history - 1) * channels + ch] = qkv[ch];
+        if (!is_head) { out[ch] = rounded; continue; }
+        vals[i] = __half2float(rounded);
+        sumsq = fmaf(vals[i], vals[i], sumsq);
+    }
+    if (!is_head) return;
+    // summation order of gdn_qk_norm_kernel: lane-strided partial sums, then the xor tree
+    sumsq = warp_sum(sumsq);
+    const float inv_rms = rsqrtf(sumsq / (float)dk + kRmsEps);
+    const float scale = grp < hk ? 1.f / (float)dk : rsqrtf((float)dk);
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+        const uint32_t ch = grp * dk + lane + 32 * i;
+        if (lane + 32 * i < dk && ch < channels) out[ch] = __float2half_rn(vals[i] * inv_rms * scale);
+    }
+}
+
 int finish(tt_context *ctx, const char *what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, what);
@@ -134,6 +187,33 @@ TT_API int tt_gdn_conv_mix(tt_context *ctx, tt_stream stream, void *tail, const 
                                                                (const __nv_bfloat16 *)conv_weight, (__half *)out,
                                                                channels, taps, rows, update_tail);
     return finish(ctx, "gdn_conv_mix launch");
+}
+
+TT_API int tt_gdn_decode_pre(tt_context *ctx, tt_stream stream, const tt_gdn_pre_session *sessions, uint32_t n_sessions,
+                             const void *conv_weight, uint32_t n_k_heads, uint32_t key_dim, uint32_t channels, uint32_t taps) {
+    TT_ENTER(ctx);
+    if (sessions == nullptr || conv_weight == nullptr || n_k_heads == 0 || key_dim == 0 || channels == 0 || taps == 0)
+        return tt_set_error(ctx, TT_ERR_INVALID_ARG, "decode prologue needs non-null buffers and positive sizes");
+    if (key_dim > 256 || channels < 2 * n_k_heads * key_dim || (channels - 2 * n_k_heads * key_dim) % key_dim != 0)
+        return tt_set_error(ctx, TT_ERR_UNSUPPORTED_SHAPE,
+                            "decode prologue: key_dim <= 256 and a value width that is a multiple of key_dim");
+    const uint32_t groups = channels / key_dim;
+    for (uint32_t base = 0; base < n_sessions; base += kPreSessions) {
+        const uint32_t n = n_sessions - base < kPreSessions ? n_sessions - base : kPreSessions;
+        static thread_local GdnPreTable table;
+        for (uint32_t i = 0; i < n; ++i) {
+            const tt_gdn_pre_session &s = sessions[base + i];
+            if (s.tail == nullptr || s.qkv == nullptr || s.conv_out == nullptr)
+                return tt_set_error(ctx, TT_ERR_INVALID_ARG, "session %u has a null buffer", base + i);
+            table.s[i].tail = (__half *)s.tail; table.s[i].qkv = (const __half *)s.qkv; table.s[i].conv_out = (__half *)s.conv_out;
+        }
+        const uint32_t warps = n * groups;
+        cudaError_t e = tt_launch_pdl(gdn_decode_pre_kernel, dim3((warps + 3) / 4), dim3(128), 0, (cudaStream_t)stream, table,
+                                      (const __nv_bfloat16 *)conv_weight, channels, taps, n_k_heads, key_dim, n);
+        if (e != cudaSuccess) return tt_check_cuda(ctx, e, "gdn_decode_pre launch");
+        ctx->launches++;
+    }
+    return TT_OK;
 }
 
 TT_API int tt_gdn_conv_tail_update(tt_context *ctx, tt_stream stream, void *tail, const void *qkv, uint32_t channels,

@@ -516,6 +516,17 @@ class GDN:
             _addr(conv_weight, conv_weight_offset), _addr(out, out_offset), self.config.qkv_dim,
             self.config.conv_kernel_size, 1, 1))
 
+    def encode_decode_prologue(self, sessions, conv_weight, command_buffer=None):
+        """encodeConvDecode + encodeQKNorm for a batch of sessions in one launch; `sessions` is a sequence of
+        (tail, qkv, conv_out) buffers (tensors or device addresses)."""
+        n = len(sessions)
+        arr = (L.GdnPreSession * max(n, 1))()
+        for i, (tail, qkv, conv_out) in enumerate(sessions):
+            arr[i] = L.GdnPreSession(_addr(tail), _addr(qkv), _addr(conv_out))
+        self.context.check(L.lib().tt_gdn_decode_pre(
+            self.context.handle, _stream(command_buffer), arr, n, _addr(conv_weight), self.config.num_k_heads,
+            self.config.key_head_dim, self.config.qkv_dim, self.config.conv_kernel_size))
+
     def encode_conv_prefill(self, tail, qkv_rows, conv_weight, out, rows, command_buffer=None, tail_offset=0,
                             qkv_rows_offset=0, conv_weight_offset=0, out_offset=0):
         """GDN.encodeConvPrefill: conv over [tail | chunk rows]; the tail is read-only here."""
