@@ -182,7 +182,10 @@ attn_decode_partial_kernel(const TTDecodeItem *__restrict__ items,
                 uint32_t p = item.key_begin + i * kKeysPerBlock + lane;
                 if (ses.row_index != nullptr) p = ses.row_index[p];
                 if (ses.ring_capacity) p %= ses.ring_capacity;
-                bulk_copy_g2s(dst, base + (size_t)p * kv_stride_bytes, HPC * HD * 2, &full[stage]);
+                // read once: evict-first in L2, so that the stream does not push out the partials, the query
+                // rows and what the neighbouring kernels of the step keep there (measured on the config-2
+                // step: 0.1854 -> 0.1778 ms)
+                bulk_copy_g2s_stream(dst, base + (size_t)p * kv_stride_bytes, HPC * HD * 2, &full[stage]);
             } else if (zero_fill) {
                 // a V row that is never fetched must still be finite: it meets p == 0 in P.V
                 const uint4 z = make_uint4(0u, 0u, 0u, 0u);
@@ -540,8 +543,8 @@ attn_decode_partial_quant_kernel(const TTDecodeItem *__restrict__ items,
                 if (ses.row_index != nullptr) p = ses.row_index[p];
                 if (ses.ring_capacity) p %= ses.ring_capacity;
                 const unsigned char *src = (warp ? vbase : kbase) + (size_t)p * kv_stride_bytes;
-                bulk_copy_g2s(dst, src + head_value_offset, S::kValBytes, &bars[i % kStages]);
-                bulk_copy_g2s(dst + S::kValBytes, src + value_bytes, meta_bytes, &bars[i % kStages]);
+                bulk_copy_g2s_stream(dst, src + head_value_offset, S::kValBytes, &bars[i % kStages]);
+                bulk_copy_g2s_stream(dst + S::kValBytes, src + value_bytes, meta_bytes, &bars[i % kStages]);
             }
         }
     };

@@ -85,7 +85,9 @@ __device__ __forceinline__ void exchange_and_merge(const ExchangeParams &p, uint
     if (tid == 0) *all_arrived = 1;
     __syncthreads();
     if (tid < p.world) {
-        __threadfence_system();
+        // the release store is cumulative over the barrier above: the cell written by the other threads of
+        // the CTA is visible to whoever acquires the flag, without a separate system-scope fence (which
+        // measured 3 us per step)
         uint32_t *flags = reinterpret_cast<uint32_t *>(p.peer[tid] + parity_off + l.flags_offset);
         st_release_sys(flags + my_cell, p.epoch);
     }
