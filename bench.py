@@ -273,9 +273,8 @@ class Workload:
         self.state_all = device_view(self.gdn_state.state_slot(1, 0), N_SESSIONS * n_state, torch.float32)
         self.state_all.normal_(0.0, 0.02, generator=gen)
         la = arch.linear_attention
-        # The step's inputs live in ONE device buffer, the attention layer's first (query rows, new K/V rows),
-        # then the GDN layer's (conv / a / b rows), and its outputs in another: the end-to-end step moves each
-        # layer's inputs with one host->device copy and each layer's outputs with one device->host copy.
+        # The step's inputs live in ONE device buffer and its outputs in another, so the end-to-end
+        # step moves them with a single host->device and a single device->host copy.
         n_q, n_conv, n_g, n_kv = N_SESSIONS * HQ * HD, N_SESSIONS * la.qkv_dim, N_SESSIONS * GV, 2 * N_SESSIONS * self.row_elems
         self.d_in = torch.empty(n_q + n_conv + 2 * n_g + n_kv, device="cuda", dtype=torch.float16)
         o = 0
@@ -285,7 +284,6 @@ class Workload:
             return v
         self.q = take(n_q, (N_SESSIONS, HQ * HD))
         self.d_newkv = take(n_kv, (2, N_SESSIONS, self.row_elems))
-        self.n_attn_in = o
         self.conv = take(n_conv, (N_SESSIONS, la.qkv_dim))
         self.a = take(n_g, (N_SESSIONS, GV))
         self.b = take(n_g, (N_SESSIONS, GV))
@@ -324,9 +322,6 @@ class Workload:
         self.h_out = torch.empty(self.d_out.shape, dtype=torch.float16).pin_memory()
         self.h2d = self.h_in.numel() * 2
         self.d2h = self.h_out.numel() * 2
-        self.n_attn_out = N_SESSIONS * HQ * HD
-        self.copy_stream = torch.cuda.Stream()
-        self.ev_gdn_in, self.ev_attn_done = torch.cuda.Event(), torch.cuda.Event()
         torch.cuda.synchronize()
 
     def step(self):
@@ -334,27 +329,17 @@ class Workload:
         self.gdn.encode_prepared(self.gdn_batch, self.a_log, self.dt_bias)
 
     def step_e2e(self):
-        """One step driven from pinned host buffers. Every byte of the step's inputs crosses host->device and
-        every byte of its outputs device->host inside the step; the GDN layer's inputs travel on a second
-        stream while the attention layer computes, the attention rows go back while the GDN layer computes."""
+        """One step driven from pinned host buffers: every byte of the step's inputs crosses host->device and
+        every byte of its outputs device->host inside the step. One stream: sending the GDN layer's inputs and
+        the attention rows over a second stream while the other layer computes measured the same 0.23 ms (the
+        two copies are ~25 us of the step and the event hops cost what the overlap saves)."""
         t = self.torch
-        main, copy, na, no = t.cuda.current_stream(), self.copy_stream, self.n_attn_in, self.n_attn_out
-        self.d_in[:na].copy_(self.h_in[:na], non_blocking=True)      # attention layer: query rows, new K/V rows
-        with t.cuda.stream(copy):
-            self.d_in[na:].copy_(self.h_in[na:], non_blocking=True)  # GDN layer: conv / a / b rows
-            self.ev_gdn_in.record(copy)
+        self.d_in.copy_(self.h_in, non_blocking=True)                # q, new K/V rows, conv/a/b rows: one copy
         # the projections' write into kSlot / vSlot of every session: one launch of the library's own
         self.kv.write_rows(0, self.new_slots, self.new_positions, self.d_newkv[0], self.d_newkv[1], self.row_elems * 2)
-        self.attn.encode_prepared(self.attn_batch)
-        self.ev_attn_done.record(main)
-        with t.cuda.stream(copy):
-            copy.wait_event(self.ev_attn_done)
-            self.h_out[:no].copy_(self.d_out[:no], non_blocking=True)    # attention rows
-        main.wait_event(self.ev_gdn_in)
-        self.gdn.encode_prepared(self.gdn_batch, self.a_log, self.dt_bias)
-        self.h_out[no:].copy_(self.d_out[no:], non_blocking=True)        # GDN y
-        copy.synchronize()
-        main.synchronize()   # the caller reads the step's result
+        self.step()
+        self.h_out.copy_(self.d_out, non_blocking=True)              # attention rows and GDN y: one copy
+        t.cuda.current_stream().synchronize()   # the caller reads the step's result
 
 
 def timed_loop(torch, dist, world, fn, steps):

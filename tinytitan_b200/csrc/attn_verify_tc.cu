@@ -2,23 +2,29 @@
 //
 // With W draft rows and G query heads per KV head, W*G packed query rows (17..64) share every K/V
 // row of a KV head. The mma.sync decode kernel serves 16 packed rows per pass and re-reads the key
-// range for the rest; here one CTA computes all of them against each K/V row it streams, in the
-// transposed form so that the 128-wide MMA dimension is filled by KEYS, not by padded query rows:
+// range for the rest; here one CTA computes all of them against each K/V row it streams. A packed
+// row is a TMEM lane, so a softmax thread owns a whole row of the score tile and nothing of the
+// softmax crosses threads:
 //
-//   S^T[j%2] = K_j . Q^T          SS MMA  M128 (keys) N64 (rows) K16 x16    TMEM cols   0..127
-//   P^T_j    = exp2(S^T - m)      tcgen05.ld -> registers -> shared memory (B operand, N-major)
-//   O^T     += V_j^T . P^T_j      SS MMA  M128 (head-dim half) N64 K16 x8, twice   cols 128..255
-//   l^T     += 1 . P^T_j          SS MMA  against ones: the row sums of the ROUNDED weights,
-//                                 replicated over the lanes                         cols 256..319
+//   S[j%2]  = Q . K_j^T        SS MMA  M128 N128 (keys) K16 x16    TMEM columns   0..255 (two tiles)
+//   P_j     = exp2(S - m)      tcgen05.ld -> registers -> tcgen05.st over the first 64 columns of the
+//                              same score tile (two 16-bit weights per column)
+//   O      += P_j . V_j        TS MMA  M128 N128 (head-dim half) K16 x8, twice      columns 256..511
 //
-// K streams as [128 keys][64 head-dim] chunks (one TMA box, 16 KB) through a 4-slot ring and is
-// released chunk by chunk as its four MMAs retire; V streams as [128 keys][128 head-dim] blocks
-// (two boxes, 32 KB) through a 3-slot ring, so the loads of the next tile's V are in flight while
-// this tile's is consumed. Lanes 0 and 1 of warp 0 are the K and V producers, warp 1 issues the
-// MMAs and owns TMEM, warps 2-5 (one thread per key of the tile) run the softmax. The per-row
-// reference maximum lives in shared memory and is only raised when a score exceeds it by more than
-// 2^8; the raise (rare after the first tile) rescales O^T and l^T in TMEM. Each CTA writes one
-// unnormalised (m, l, o) partial per packed row, in the layout the split-KV combine kernel merges.
+// Only the 64 packed rows exist: the M128 instructions read rows 64..127 of the Q operand from
+// whatever follows Q in shared memory and leave the result in TMEM lanes 64..127, which nothing
+// reads. Keeping Q as the only resident operand in shared memory (32 KB) and P in TMEM leaves
+// 192 KB for ONE ring of twelve 16 KB slots that K ([128 keys][64 head-dim] chunks) and V (the same
+// boxes, consumed in adjacent pairs) travel through in the order the MMAs consume them:
+// K(0) K(1) V(0) K(2) V(1) ... The kernel is bound by the bytes it keeps in flight per SM, and this
+// ring holds a tile and a half more than separate K and V rings next to a P buffer did.
+//
+// Warps 0 and 1 are the softmax (row = thread), lane 0 of warp 2 is the TMA producer, lane 0 of
+// warp 3 issues the MMAs; warp 2 owns the TMEM allocation. The reference maximum of a row is only
+// raised when a score exceeds it by more than 2^8; the raise rescales the row of O in TMEM (after
+// P.V of the previous tile has retired). The row sum is taken on the ROUNDED weights. Each CTA
+// writes one unnormalised (m, l, o) partial per packed row, in the layout the split-KV combine
+// kernel merges, or the finished rows when its item is the whole key range of the session.
 //
 // Semantics: attention.metal:162-269 (partial pass over a key range, row r of a W-row group
 // masked at seq_len - (W-1-r)); every mbarrier wait is bounded.
@@ -30,46 +36,35 @@ namespace {
 
 constexpr int kHD = 256;
 constexpr int kBK = 128;                   // keys per tile
-constexpr int kRows = 64;                  // packed query rows (MMA N)
-constexpr int kThreads = 192;
-constexpr int kKSlots = 4, kVSlots = 3;
+constexpr int kRows = 64;                  // packed query rows
+constexpr int kThreads = 128;
+constexpr int kSlots = 12;                 // ring slots (even: a V pair never wraps)
+constexpr int kUnitsPerTile = 8;           // 4 K chunks + 4 V chunks
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRaiseThreshold = 8.0f;
 
-constexpr int kChunkBytes = kBK * 64 * 2;      // [128 keys][64 head-dim], 128-byte rows: 16384
-constexpr int kVBlockBytes = 2 * kChunkBytes;  // [128 keys][128 head-dim]
-constexpr int kQBytes = kRows * kHD * 2;       // 4 sub-tiles [64][64]
+constexpr int kSlotBytes = kBK * 64 * 2;       // [128 keys][64 head-dim], 128-byte rows: 16384
+constexpr int kQBytes = kRows * kHD * 2;       // 4 sub-tiles [64 rows][64 head-dim]
 constexpr int kQSub = kRows * 64 * 2;          // 8192
-constexpr int kPBytes = kBK * kRows * 2;       // [128 keys][64 rows], 128-byte rows
-constexpr int kOnesBytes = 1024;               // one 8-row group of 1.0; every group of the operand aliases it
-constexpr int kOffV = kKSlots * kChunkBytes;
-constexpr int kOffQ = kOffV + kVSlots * kVBlockBytes;
-constexpr int kOffP = kOffQ + kQBytes;
-constexpr int kOffOnes = kOffP + kPBytes;
-constexpr int kOffMisc = kOffOnes + kOnesBytes;
+constexpr int kOffRing = kQBytes;
+constexpr int kOffMisc = kOffRing + kSlots * kSlotBytes;
 
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS = 0, kColO = 128, kColL = 256;
+constexpr uint32_t kColS = 0, kColO = 256;     // S: two tiles of 128 columns
 
 struct Misc {
-    uint64_t k_full[kKSlots], k_empty[kKSlots];
-    uint64_t v_full[kVSlots], v_empty[kVSlots];
+    uint64_t full[kSlots], empty[kSlots];
     uint64_t s_full[2];
-    uint64_t p_ready, p_free;
-    uint64_t o_ready;
-    uint64_t sync;              // softmax warps' own barrier (count 4: one arrive per warp)
+    uint64_t p_ready[2];        // count 2: one arrive per softmax warp
+    uint64_t o_ready[2];        // [tile parity]: P.V of the tile has retired. Two barriers, because the softmax threads
+                                // may be two P.V products ahead of the tensor pipe when they reach the epilogue and
+                                // a single barrier's parity cannot tell tile n-1 from tile n-3
     uint32_t tmem_base;
     uint32_t pad;
-    uint32_t raise_tile[2];     // [tile parity]: 1 + the last tile for which some key asked for higher maxima
-    float mref[kRows];          // log2-domain reference maximum per packed row
-    float factor[kRows];
-    float tile_max[4][kRows];
-    float lsum[kRows];
-    uint32_t limit[kRows];      // first masked key per packed row
-    uint32_t prow[kRows];       // partial row index per packed row
 };
 constexpr int kSmemBytes = kOffMisc + (int)sizeof(Misc) + 1024 /*align*/;
+static_assert(kSmemBytes <= 232448, "the verify kernel's shared memory exceeds the per-CTA limit");
 
 struct VerifyParams {
     const TTDecodeItem *items;
@@ -80,57 +75,30 @@ struct VerifyParams {
     uint32_t out_row_stride;     // elements
     uint32_t direct;             // every session is one part: write the normalised rows, no partials
     float scale_log2;
-    uint32_t idesc_qk, idesc_pv, idesc_l;
+    uint32_t idesc_qk, idesc_pv;
 };
 
-// Barrier among the four softmax warps with a bounded wait (a named barrier could not give up if a
-// warp left after a time-out): one arrive per warp, every lane waits. `phase` flips per use.
-__device__ __forceinline__ bool softmax_sync(uint64_t *bar, uint32_t &phase, int lane) {
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar);
-    const bool ok = warp_all(mbar_wait(bar, phase & 1));
-    phase ^= 1;
-    return ok;
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-// Column maxima over the warp: every lane holds one value for each of 64 columns; afterwards lane L
-// holds the warp-wide maxima of columns 2L and 2L+1. Each butterfly step hands the partner the half
-// of the columns it keeps, so the whole reduction is 62 shuffles instead of 320.
-__device__ __forceinline__ void warp_colmax64(const uint32_t (&v)[2][32], int lane, float &m0, float &m1) {
-    float a[32], b[16], c[8], d[4];
-    bool up = (lane & 16) != 0;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        const float lo = __uint_as_float(v[0][i]), hi = __uint_as_float(v[1][i]);
-        a[i] = fmaxf(up ? hi : lo, __shfl_xor_sync(0xffffffffu, up ? lo : hi, 16));
-    }
-    up = (lane & 8) != 0;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) b[i] = fmaxf(up ? a[i + 16] : a[i], __shfl_xor_sync(0xffffffffu, up ? a[i] : a[i + 16], 8));
-    up = (lane & 4) != 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) c[i] = fmaxf(up ? b[i + 8] : b[i], __shfl_xor_sync(0xffffffffu, up ? b[i] : b[i + 8], 4));
-    up = (lane & 2) != 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) d[i] = fmaxf(up ? c[i + 4] : c[i], __shfl_xor_sync(0xffffffffu, up ? c[i] : c[i + 4], 2));
-    up = (lane & 1) != 0;
-    m0 = fmaxf(up ? d[2] : d[0], __shfl_xor_sync(0xffffffffu, up ? d[0] : d[2], 1));
-    m1 = fmaxf(up ? d[3] : d[1], __shfl_xor_sync(0xffffffffu, up ? d[1] : d[3], 1));
-}
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParams p, uint32_t *__restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char *k_ring = smem;
-    unsigned char *v_ring = smem + kOffV;
-    unsigned char *q_s = smem + kOffQ;
-    unsigned char *p_s = smem + kOffP;
-    unsigned char *ones_s = smem + kOffOnes;
+    unsigned char *q_s = smem;
+    unsigned char *ring = smem + kOffRing;
     Misc *ms = reinterpret_cast<Misc *>(smem + kOffMisc);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();       // the kernel before this one may have produced the query rows or the newest K/V rows
     const TTDecodeItem item = p.items[blockIdx.x];
     const TTDecodeSession ses = p.sessions[item.session];
     const uint32_t group = p.n_q_heads / p.n_kv_heads;
@@ -138,49 +106,47 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
     const uint32_t n_tiles = (item.key_end - item.key_begin + kBK - 1) / kBK;
     const uint32_t rows_total = ses.q_rows * p.n_q_heads;
 
-    // K chunk kc = 4*tile + (64-wide head-dim slice); V block vb = 2*tile + head-dim half
+    // Ring unit u (16 KB) in consumption order: K(0) | K(1) V(0) | K(2) V(1) | ... | V(n-1), four units each.
     const CUtensorMap *k_map = p.maps + 2 * item.session, *v_map = k_map + 1;
-    const uint32_t n_kchunks = 4 * n_tiles, n_vblocks = 2 * n_tiles;
-    auto load_k = [&](uint32_t kc) {
-        const uint32_t slot = kc % kKSlots;
-        mbar_expect_tx(&ms->k_full[slot], kChunkBytes);
-        tma_load_2d(k_ring + slot * kChunkBytes, k_map, (int)(item.kv_head * kHD + (kc & 3) * 64),
-                    (int)(item.key_begin + (kc >> 2) * kBK), &ms->k_full[slot]);
+    const uint32_t n_units = kUnitsPerTile * n_tiles;
+    auto load_unit = [&](uint32_t u) {
+        // block of four: 0 -> K(0); odd 2t+1 -> K(t+1) (while it exists); even 2t+2 -> V(t); the last block is V(n-1)
+        const uint32_t blk = u >> 2, c = u & 3;
+        bool is_k; uint32_t tile;
+        if (blk == 0) { is_k = true; tile = 0; }
+        else if (blk == 2 * n_tiles - 1) { is_k = false; tile = n_tiles - 1; }
+        else if (blk & 1) { is_k = true; tile = (blk + 1) >> 1; }
+        else { is_k = false; tile = (blk >> 1) - 1; }
+        const uint32_t slot = u % kSlots;
+        mbar_expect_tx(&ms->full[slot], kSlotBytes);
+        tma_load_2d(ring + slot * kSlotBytes, is_k ? k_map : v_map, (int)(item.kv_head * kHD + c * 64),
+                    (int)(item.key_begin + tile * kBK), &ms->full[slot]);
     };
-    auto load_v = [&](uint32_t vb) {
-        const uint32_t slot = vb % kVSlots;
-        mbar_expect_tx(&ms->v_full[slot], kVBlockBytes);
-        const int x = (int)(item.kv_head * kHD + (vb & 1) * 128), y = (int)(item.key_begin + (vb >> 1) * kBK);
-        tma_load_2d(v_ring + slot * kVBlockBytes, v_map, x, y, &ms->v_full[slot]);
-        tma_load_2d(v_ring + slot * kVBlockBytes + kChunkBytes, v_map, x + 64, y, &ms->v_full[slot]);
-    };
-    // The first ring fills leave before the CTA-wide sync so that they overlap the staging of Q (the
+    // The first ring fill leaves before the CTA-wide sync so that it overlaps the staging of Q (the
     // thread that initialises the barriers is the one that uses them first).
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kKSlots; ++s) { mbar_init(&ms->k_full[s], 1); mbar_init(&ms->k_empty[s], 1); }
-        for (int s = 0; s < kVSlots; ++s) { mbar_init(&ms->v_full[s], 1); mbar_init(&ms->v_empty[s], 1); }
+    if (threadIdx.x == 64) {
+        for (int s = 0; s < kSlots; ++s) { mbar_init(&ms->full[s], 1); mbar_init(&ms->empty[s], 1); }
         mbar_init(&ms->s_full[0], 1); mbar_init(&ms->s_full[1], 1);
-        mbar_init(&ms->p_ready, 128);
-        mbar_init(&ms->p_free, 1);
-        mbar_init(&ms->o_ready, 1);
-        mbar_init(&ms->sync, 4);
-        ms->raise_tile[0] = 0; ms->raise_tile[1] = 0;
+        mbar_init(&ms->p_ready[0], 2); mbar_init(&ms->p_ready[1], 2);
+        mbar_init(&ms->o_ready[0], 1); mbar_init(&ms->o_ready[1], 1);
         mbar_fence_init();
         if (n_tiles > 0) {
             // the maps were rewritten by a host copy since the last launch that used these addresses
             asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(k_map) : "memory");
             asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(v_map) : "memory");
-            for (uint32_t kc = 0; kc < (uint32_t)kKSlots && kc < n_kchunks; ++kc) load_k(kc);
-            for (uint32_t vb = 0; vb < (uint32_t)kVSlots && vb < n_vblocks; ++vb) load_v(vb);
+            for (uint32_t u = 0; u < (uint32_t)kSlots && u < n_units; ++u) load_unit(u);
         }
     }
-    if (warp == 1) tmem_alloc(&ms->tmem_base, kTmemCols);
+    if (warp == 2) {
+        __syncwarp();
+        tmem_alloc(&ms->tmem_base, kTmemCols);
+    }
 
-    // ---- stage Q^T's operand: packed row r = w*G + g -> q[w][kv_head*G + g][:], K-major, 128-byte
-    // swizzle; asynchronous 16-byte copies so that all of a thread's chunks are in flight together
-    if (warp != 0) {
+    // ---- stage Q: packed row r = w*G + g -> q[w][kv_head*G + g][:], K-major, 128-byte swizzle;
+    // asynchronous 16-byte copies so that all of a thread's chunks are in flight together
+    {
         const T *q = reinterpret_cast<const T *>(ses.q);
-        for (uint32_t c = threadIdx.x - 32; c < kRows * (kHD / 8); c += kThreads - 32) {
+        for (uint32_t c = threadIdx.x; c < kRows * (kHD / 8); c += kThreads) {
             const uint32_t r = c / (kHD / 8), chunk = c % (kHD / 8);       // 16-byte chunk of the row
             const uint32_t sub = chunk >> 3, cc = chunk & 7;
             unsigned char *dst = q_s + sub * kQSub + r * 128 + ((cc ^ (r & 7)) << 4);
@@ -193,17 +159,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        const uint32_t one2 = std::is_same<T, __half>::value ? 0x3C003C00u : 0x3F803F80u;   // 1.0 twice
-        for (uint32_t c = threadIdx.x - 32; c < kOnesBytes / 16; c += kThreads - 32)
-            *reinterpret_cast<uint4 *>(ones_s + c * 16) = make_uint4(one2, one2, one2, one2);
-        for (uint32_t r = threadIdx.x - 32; r < kRows; r += kThreads - 32) {
-            const uint32_t w = r / group, g = r - w * group;
-            ms->mref[r] = -INFINITY;
-            ms->factor[r] = 1.f;
-            ms->limit[r] = r < n_rows ? ses.seq_len - (ses.q_rows - 1 - w) : 0u;
-            const uint32_t rho = w * p.n_q_heads + item.kv_head * group + g;
-            ms->prow[r] = item.partial_base + item.part_index * rows_total + rho;
-        }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         fence_async_smem();
     }
@@ -213,42 +168,42 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
     const uint32_t tmem = ms->tmem_base;
     bool failed = false;
 
-    if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producers
+    if (warp == 2) {
+        // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             bool ok = true;
-            for (uint32_t kc = kKSlots; ok && kc < n_kchunks; ++kc) {
-                ok = mbar_wait(&ms->k_empty[kc % kKSlots], ((kc / kKSlots) - 1) & 1);
-                if (ok) load_k(kc);
+            uint32_t u = kSlots;
+            for (; ok && u < n_units; ++u) {
+                ok = mbar_wait(&ms->empty[u % kSlots], ((u / kSlots) - 1) & 1);
+                if (ok) load_unit(u);
             }
-            failed = !ok;
-        } else if (lane == 1) {
-            bool ok = true;
-            for (uint32_t vb = kVSlots; ok && vb < n_vblocks; ++vb) {
-                ok = mbar_wait(&ms->v_empty[vb % kVSlots], ((vb / kVSlots) - 1) & 1);
-                if (ok) load_v(vb);
+            if (!ok) {
+                // give the copies still in flight a bounded chance to land before the shared memory is released
+                --u;
+                for (uint32_t v = u > (uint32_t)kSlots ? u - kSlots : 0; v < u; ++v)
+                    mbar_wait(&ms->full[v % kSlots], (v / kSlots) & 1, 1u << 16);
             }
             failed = !ok;
         }
-    } else if (warp == 1) {
+    } else if (warp == 3) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0 && n_tiles > 0) {
-            const uint32_t k_a = smem_u32(k_ring), v_a = smem_u32(v_ring), q_a = smem_u32(q_s), p_a = smem_u32(p_s),
-                           ones_a = smem_u32(ones_s);
-            // S^T(j) = K_j . Q^T, one 64-wide head-dim slice at a time as the chunks land
+            const uint32_t ring_a = smem_u32(ring), q_a = smem_u32(q_s);
+            uint32_t u = 0;
+            // S(j) = Q . K_j^T, one 64-wide head-dim chunk at a time as the chunks land
             auto issue_qk = [&](uint32_t j) {
-                const uint32_t d = tmem + kColS + (j & 1) * kRows;
-                for (uint32_t c = 0; c < 4; ++c) {
-                    const uint32_t kc = 4 * j + c, slot = kc % kKSlots;
-                    if (!mbar_wait(&ms->k_full[slot], (kc / kKSlots) & 1)) return false;
+                const uint32_t d = tmem + kColS + (j & 1) * kBK;
+                for (uint32_t c = 0; c < 4; ++c, ++u) {
+                    const uint32_t slot = u % kSlots;
+                    if (!mbar_wait(&ms->full[slot], (u / kSlots) & 1)) return false;
                     tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t ad = make_desc(k_a + slot * kChunkBytes + ks * 32, 16, 1024);
-                        const uint64_t bd = make_desc(q_a + c * kQSub + ks * 32, 16, 1024);
+                        const uint64_t ad = make_desc(q_a + c * kQSub + ks * 32, 16, 1024);
+                        const uint64_t bd = make_desc(ring_a + slot * kSlotBytes + ks * 32, 16, 1024);
                         mma_ss(d, ad, bd, p.idesc_qk, (c > 0 || ks > 0) ? 1u : 0u);
                     }
-                    mma_commit(&ms->k_empty[slot]);
+                    mma_commit(&ms->empty[slot]);
                 }
                 mma_commit(&ms->s_full[j & 1]);
                 return true;
@@ -256,212 +211,172 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
             bool ok = issue_qk(0);
             for (uint32_t j = 0; ok && j < n_tiles; ++j) {
                 if (j + 1 < n_tiles) ok = issue_qk(j + 1);
-                if (ok) ok = mbar_wait(&ms->p_ready, j & 1);
+                if (ok) ok = mbar_wait(&ms->p_ready[j & 1], (j >> 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t acc0 = j > 0 ? 1u : 0u;
-                // l^T += 1 . P^T_j: every 8-row group of the A operand is the same 1 KB of ones (SBO 0)
-#pragma unroll
-                for (int kk = 0; kk < kBK / 16; ++kk) {
-                    const uint64_t ad = make_desc(ones_a + (kk & 3) * 32, 16, 0);
-                    const uint64_t bd = make_desc(p_a + kk * 2048, kPBytes, 1024);
-                    mma_ss(tmem + kColL, ad, bd, p.idesc_l, (acc0 || kk > 0) ? 1u : 0u);
-                }
-                // O^T(half) += V_j(half)^T . P^T_j
-                for (uint32_t half = 0; ok && half < 2; ++half) {
-                    const uint32_t vb = 2 * j + half, slot = vb % kVSlots;
-                    ok = mbar_wait(&ms->v_full[slot], (vb / kVSlots) & 1);
+                const uint32_t p_t = tmem + kColS + (j & 1) * kBK;    // P_j: 64 columns of 16-bit pairs over S_j
+                // O(half) += P_j . V_j(half): V as the MN-major B operand, two 64-wide head-dim atoms one
+                // slot apart (LBO), 8-key groups 1024 B apart (SBO), 16 keys (2048 B) per step
+                for (uint32_t half = 0; ok && half < 2; ++half, u += 2) {
+                    const uint32_t slot = u % kSlots;
+                    ok = mbar_wait(&ms->full[slot], (u / kSlots) & 1) && mbar_wait(&ms->full[slot + 1], (u / kSlots) & 1);
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < kBK / 16; ++kk) {
-                        // V block as the M-major A operand: 64-wide head-dim atoms kChunkBytes apart (LBO),
-                        // 8-key groups 1024 B apart (SBO); P^T as the N-major B operand, one atom wide
-                        const uint64_t ad = make_desc(v_a + slot * kVBlockBytes + kk * 2048, kChunkBytes, 1024);
-                        const uint64_t bd = make_desc(p_a + kk * 2048, kPBytes, 1024);
-                        mma_ss(tmem + kColO + half * kRows, ad, bd, p.idesc_pv, (acc0 || kk > 0) ? 1u : 0u);
+                        const uint64_t bd = make_desc(ring_a + slot * kSlotBytes + kk * 2048, kSlotBytes, 1024);
+                        mma_ts(tmem + kColO + half * 128, p_t + kk * 8, bd, p.idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                     }
-                    mma_commit(&ms->v_empty[slot]);
+                    mma_commit(&ms->empty[slot]);
+                    mma_commit(&ms->empty[slot + 1]);
                 }
                 if (!ok) break;
-                mma_commit(&ms->p_free);
-                mma_commit(&ms->o_ready);
+                mma_commit(&ms->o_ready[j & 1]);
             }
             failed = !ok;
         }
     } else {
-        // ------------------------------------------------------------------ softmax: one key per thread
-        const uint32_t quarter = warp & 3;                       // TMEM lane quarter this warp may touch
-        const uint32_t i = quarter * 32 + lane;                  // key inside the tile == TMEM lane
-        const uint32_t lane_addr = (quarter * 32) << 16;
-        uint32_t min_limit = 0xffffffffu;
-        for (uint32_t r = 0; r < n_rows; r += group) min_limit = min(min_limit, ms->limit[r]);
+        // ------------------------------------------------------------------ softmax: one packed row per thread
+        const uint32_t row = warp * 32 + lane;                   // packed row == TMEM lane
+        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        const bool row_valid = row < n_rows;
+        const uint32_t w_idx = row / group, g_idx = row - w_idx * group;
+        // first key this row may not see: its causal limit inside the draft rows, cut at the item's end
+        const uint32_t lim = row_valid ? min(ses.seq_len - (ses.q_rows - 1 - w_idx), item.key_end) : 0u;
+        float m_ref = -INFINITY, l_run = 0.f;                    // log2-domain reference maximum, running row sum
         bool ok = true;
-        uint32_t sync_phase = 0;
 
         for (uint32_t j = 0; j < n_tiles; ++j) {
             const uint32_t st = j & 1;
             ok = warp_all(mbar_wait(&ms->s_full[st], (j >> 1) & 1));
             if (!ok) break;
             tc_fence_after();
-            uint32_t raw[2][32];
-            tmem_ld32(tmem + lane_addr + kColS + st * kRows, raw[0]);
-            tmem_ld32(tmem + lane_addr + kColS + st * kRows + 32, raw[1]);
+            const uint32_t s_addr = tmem + lane_addr + kColS + st * kBK;
+            uint32_t raw[4][32];
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) tmem_ld32(s_addr + c4 * 32, raw[c4]);
             tmem_wait_ld();
 
-            const uint32_t key0 = item.key_begin + j * kBK, key = key0 + i;
-            const bool need_mask = key0 + kBK > min_limit || key0 + kBK > item.key_end;
-            bool exceed = false;
+            const uint32_t key0 = item.key_begin + j * kBK;
+            if (key0 + kBK > lim) {          // masked keys become -inf before the (positive) scale
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+                for (int c4 = 0; c4 < 4; ++c4)
 #pragma unroll
-                for (int c = 0; c < 32; c += 4) {
-                    const float4 m4 = *reinterpret_cast<const float4 *>(&ms->mref[h * 32 + c]);
-                    const float mm[4] = {m4.x, m4.y, m4.z, m4.w};
+                    for (int c = 0; c < 32; ++c)
+                        if (key0 + c4 * 32 + c >= lim) raw[c4][c] = 0xff800000u;
+            }
+            float mx4[4];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        float s = __uint_as_float(raw[h][c + u]) * p.scale_log2;
-                        if (need_mask && (key >= ms->limit[h * 32 + c + u] || key >= item.key_end)) s = -INFINITY;
-                        raw[h][c + u] = __float_as_uint(s);
-                        exceed |= (s - mm[u]) > kRaiseThreshold;     // -inf - -inf is NaN: compares false
-                    }
-                }
-
-            if (__any_sync(0xffffffffu, exceed) && lane == 0) atomicMax(&ms->raise_tile[st], j + 1);
-            ok = softmax_sync(&ms->sync, sync_phase, lane);
-            if (!ok) break;
-            if (ms->raise_tile[st] == j + 1) {
-                // raise the reference maxima to the true maxima so far, rescale what is accumulated
-                float m0, m1;
-                warp_colmax64(raw, lane, m0, m1);
-                *reinterpret_cast<float2 *>(&ms->tile_max[quarter][2 * lane]) = make_float2(m0, m1);
-                ok = softmax_sync(&ms->sync, sync_phase, lane);
+            for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(__uint_as_float(raw[0][u]), __uint_as_float(raw[1][u]));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], fmaxf(__uint_as_float(raw[2][u]), __uint_as_float(raw[3][u])));
+#pragma unroll
+            for (int c = 4; c < 32; ++c)
+                mx4[c & 3] = fmaxf(mx4[c & 3], fmaxf(fmaxf(__uint_as_float(raw[0][c]), __uint_as_float(raw[1][c])),
+                                                     fmaxf(__uint_as_float(raw[2][c]), __uint_as_float(raw[3][c]))));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+            const float m_new = fmaxf(m_ref, mx);
+            // lazy rescale: keep the stale reference while it is within 2^8 of the true maximum
+            const bool raise = (m_new - m_ref > kRaiseThreshold) || (m_ref == -INFINITY && m_new != -INFINITY);
+            if (j == 0) {
+                m_ref = m_new;
+            } else if (__any_sync(0xffffffffu, raise)) {
+                // O holds the sum over tiles < j; it may only be touched once P.V of tile j-1 has retired
+                ok = warp_all(mbar_wait(&ms->o_ready[(j - 1) & 1], ((j - 1) >> 1) & 1));
                 if (!ok) break;
-                if (i < kRows) {
-                    const float m_old = ms->mref[i];
-                    const float tm = fmaxf(fmaxf(ms->tile_max[0][i], ms->tile_max[1][i]),
-                                           fmaxf(ms->tile_max[2][i], ms->tile_max[3][i]));
-                    const float m_new = fmaxf(m_old, tm);
-                    ms->factor[i] = (m_new == -INFINITY) ? 1.f : fast_exp2(m_old - m_new);   // exp2(-inf) == 0
-                    ms->mref[i] = m_new;
-                }
-                ok = softmax_sync(&ms->sync, sync_phase, lane);
-                if (!ok) break;
-                if (j > 0) {
-                    // everything accumulated so far must have retired before it is touched
-                    ok = warp_all(mbar_wait(&ms->o_ready, (j - 1) & 1));
-                    if (!ok) break;
-                    tc_fence_after();
+                tc_fence_after();
+                const float factor = raise ? fast_exp2(m_ref - m_new) : 1.f;   // exp2(-inf) == 0: the row of O was zero
+                if (raise) { l_run *= factor; m_ref = m_new; }
 #pragma unroll 1
-                    for (uint32_t c0 = kColO; c0 < kColL + kRows; c0 += 32) {
-                        uint32_t o[32];
-                        tmem_ld32(tmem + lane_addr + c0, o);
-                        tmem_wait_ld();
-                        const float *f = &ms->factor[c0 & 63];      // columns repeat every 64: O lo, O hi, l
+                for (int c0 = 0; c0 < kHD; c0 += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem + lane_addr + kColO + c0, o);
+                    tmem_wait_ld();
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f[c]);
-                        tmem_st32(tmem + lane_addr + c0, o);
-                    }
-                    tmem_wait_st();
+                    for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
+                    tmem_st32(tmem + lane_addr + kColO + c0, o);
                 }
             }
-
-            // P^T row of this key: 64 weights -> 128 bytes, chunk c at (c ^ (key & 7)); the exponentials are
-            // formed first, the single P buffer is only waited for when they are ready to be stored
-            uint4 w[8];
+            const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int c4 = 0; c4 < 4; ++c4) {
+                uint32_t pk[16];
 #pragma unroll
-                for (int c = 0; c < 32; c += 8) {
-                    const float4 ma = *reinterpret_cast<const float4 *>(&ms->mref[h * 32 + c]);
-                    const float4 mb = *reinterpret_cast<const float4 *>(&ms->mref[h * 32 + c + 4]);
-                    const float mm[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
-                    float e[8];
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const float m_use = (mm[u] == -INFINITY) ? 0.f : mm[u];
-                        e[u] = fast_exp2(__uint_as_float(raw[h][c + u]) - m_use);
-                    }
-                    uint4 &o = w[h * 4 + (c >> 3)];
-                    o.x = pack2<T>(e[0], e[1]); o.y = pack2<T>(e[2], e[3]);
-                    o.z = pack2<T>(e[4], e[5]); o.w = pack2<T>(e[6], e[7]);
+                for (int c = 0; c < 16; ++c) {
+                    // one FMA per exponent argument: raw * scale - m
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(raw[c4][2 * c]), p.scale_log2, neg_m));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(raw[c4][2 * c + 1]), p.scale_log2, neg_m));
+                    pk[c] = pack2<T>(p0, p1);       // P takes V's type: A and B of one tcgen05.mma share a format
+                    rs4[c & 3] += sum2<T>(pk[c]);   // the row sum uses the ROUNDED weights the MMA will see
                 }
-            if (j >= 1) {
-                ok = warp_all(mbar_wait(&ms->p_free, (j - 1) & 1));
-                if (!ok) break;
+                // keys 32*c4 .. 32*c4+31 of the row -> columns 16*c4 .. of the score tile they came from (every
+                // column written here has been read above)
+                tmem_st16(s_addr + c4 * 16, pk);
             }
-            unsigned char *prow = p_s + i * 128;
-#pragma unroll
-            for (uint32_t chunk = 0; chunk < 8; ++chunk)
-                *reinterpret_cast<uint4 *>(prow + ((chunk ^ (i & 7)) << 4)) = w[chunk];
-            fence_async_smem();
-            tc_fence_before();
-            mbar_arrive(&ms->p_ready);
+            l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            tmem_wait_st();
+            tc_fence_before();                 // orders P and a rescale of O before the P.V they precede
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ms->p_ready[st]);
         }
 
-        // ---- partial of this item: O^T (transposed back on the way out), m, l
-        if (ok && n_tiles > 0) ok = warp_all(mbar_wait(&ms->o_ready, (n_tiles - 1) & 1));
+        // ---- this item's rows: O, m, l
+        if (ok && n_tiles > 0) ok = warp_all(mbar_wait(&ms->o_ready[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1));
         if (ok) {
             tc_fence_after();
-            if (n_tiles > 0 && quarter == 0) {   // every lane of l^T holds the 64 sums; the load is warp-wide
-                uint32_t l0[32], l1[32];
-                tmem_ld32(tmem + lane_addr + kColL, l0);
-                tmem_ld32(tmem + lane_addr + kColL + 32, l1);
-                tmem_wait_ld();
-                if (lane == 0) {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) { ms->lsum[c] = __uint_as_float(l0[c]); ms->lsum[32 + c] = __uint_as_float(l1[c]); }
-                }
-            }
-            ok = softmax_sync(&ms->sync, sync_phase, lane);
-        }
-        if (ok && p.direct) {
-            // the item covers the session's whole key range: normalise and store the output rows
-            T *out = reinterpret_cast<T *>(ses.out);
+            const uint32_t rho = w_idx * p.n_q_heads + item.kv_head * group + g_idx;
+            if (p.direct) {
+                // the item covers the session's whole key range: normalise and store the output row
+                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;          // no visible key: zeros
+                T *orow = reinterpret_cast<T *>(ses.out) + (size_t)w_idx * p.out_row_stride +
+                          (size_t)(item.kv_head * group + g_idx) * kHD;
 #pragma unroll 1
-            for (uint32_t half = 0; half < 2; ++half) {
-                uint32_t o0[32], o1[32];
-                if (n_tiles > 0) {
-                    tmem_ld32(tmem + lane_addr + kColO + half * kRows, o0);
-                    tmem_ld32(tmem + lane_addr + kColO + half * kRows + 32, o1);
-                    tmem_wait_ld();
-                } else {
+                for (int c0 = 0; c0 < kHD; c0 += 32) {
+                    uint32_t o[32];
+                    if (n_tiles > 0) {
+                        tmem_ld32(tmem + lane_addr + kColO + c0, o);
+                        tmem_wait_ld();
+                    } else {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) { o0[c] = 0u; o1[c] = 0u; }
-                }
+                        for (int c = 0; c < 32; ++c) o[c] = 0u;
+                    }
+                    if (row_valid) {
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    if ((uint32_t)c < n_rows) {
-                        const float l = n_tiles > 0 ? ms->lsum[c] : 0.f;
-                        const float inv = l > 0.f ? 1.f / l : 0.f;          // no visible key: zeros
-                        const uint32_t w = (uint32_t)c / group, g = (uint32_t)c - w * group;
-                        const float v = __uint_as_float(c < 32 ? o0[c & 31] : o1[c & 31]) * inv;
-                        out[(size_t)w * p.out_row_stride + (size_t)(item.kv_head * group + g) * kHD + half * 128 + i] = (T)v;
+                        for (int c = 0; c < 32; c += 8) {
+                            uint4 v;
+                            v.x = pack2<T>(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+                            v.y = pack2<T>(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+                            v.z = pack2<T>(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+                            v.w = pack2<T>(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+                            *reinterpret_cast<uint4 *>(orow + c0 + c) = v;
+                        }
                     }
                 }
-            }
-        } else if (ok) {
-            if (i < n_rows) {
-                const float m = ms->mref[i];
-                p.part_m[ms->prow[i]] = n_tiles > 0 ? m * kLn2 : -INFINITY;   // natural-log domain
-                p.part_l[ms->prow[i]] = (n_tiles > 0 && m != -INFINITY) ? ms->lsum[i] : 0.f;
-            }
-#pragma unroll 1
-            for (uint32_t half = 0; half < 2; ++half) {
-                uint32_t o0[32], o1[32];
-                if (n_tiles > 0) {
-                    tmem_ld32(tmem + lane_addr + kColO + half * kRows, o0);
-                    tmem_ld32(tmem + lane_addr + kColO + half * kRows + 32, o1);
-                    tmem_wait_ld();
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) { o0[c] = 0u; o1[c] = 0u; }
+            } else {
+                const size_t prow = (size_t)item.partial_base + (size_t)item.part_index * rows_total + rho;
+                if (row_valid) {
+                    p.part_m[prow] = (n_tiles > 0 && m_ref != -INFINITY) ? m_ref * kLn2 : -INFINITY;   // natural-log domain
+                    p.part_l[prow] = (n_tiles > 0 && m_ref != -INFINITY) ? l_run : 0.f;
                 }
-                float *dst = p.part_o + half * 128 + i;
+                float *dst = p.part_o + prow * kHD;
+#pragma unroll 1
+                for (int c0 = 0; c0 < kHD; c0 += 32) {
+                    uint32_t o[32];
+                    if (n_tiles > 0) {
+                        tmem_ld32(tmem + lane_addr + kColO + c0, o);
+                        tmem_wait_ld();
+                    } else {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    if ((uint32_t)c < n_rows) dst[(size_t)ms->prow[c] * kHD] = __uint_as_float(o0[c]);
-                    if ((uint32_t)(32 + c) < n_rows) dst[(size_t)ms->prow[32 + c] * kHD] = __uint_as_float(o1[c]);
+                        for (int c = 0; c < 32; ++c) o[c] = 0u;
+                    }
+                    if (row_valid) {
+#pragma unroll
+                        for (int c = 0; c < 32; c += 4)
+                            *reinterpret_cast<float4 *>(dst + c0 + c) =
+                                make_float4(__uint_as_float(o[c]), __uint_as_float(o[c + 1]), __uint_as_float(o[c + 2]),
+                                            __uint_as_float(o[c + 3]));
+                    }
                 }
             }
         }
@@ -471,7 +386,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
     if (failed) atomicOr(status, TT_DEV_WAIT_TIMEOUT);
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 2) {
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
@@ -510,21 +425,20 @@ int tt_launch_verify_tc(tt_context *ctx, cudaStream_t stream, uint32_t n_session
     kp.n_q_heads = p->n_q_heads; kp.n_kv_heads = p->n_kv_heads; kp.q_row_stride = p->q_row_stride_elements;
     kp.out_row_stride = p->out_row_stride_elements; kp.direct = direct ? 1u : 0u;
     kp.scale_log2 = p->scale * kLog2e;
-    kp.idesc_qk = tt_make_idesc_f16(p->io_dtype, kRows, false, false);
-    kp.idesc_pv = tt_make_idesc_f16(p->io_dtype, kRows, true, true);
-    kp.idesc_l = tt_make_idesc_f16(p->io_dtype, kRows, true, false);
+    kp.idesc_qk = tt_make_idesc_f16(p->io_dtype, kBK, false);        // Q (K-major) x K rows (K-major), N = 128 keys
+    kp.idesc_pv = tt_make_idesc_f16(p->io_dtype, kHD / 2, true);     // P (TMEM) x V (MN-major), N = 128 head dims
     if (p->io_dtype == TT_F16) {
         auto kernel = attn_verify_tc_kernel<__half>;
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "verify smem attribute");
-        kernel<<<n_items, kThreads, kSmemBytes, stream>>>(kp, ctx->status);
+        e = tt_launch_pdl(kernel, dim3(n_items), dim3(kThreads), (size_t)kSmemBytes, stream, kp, ctx->status);
     } else {
         auto kernel = attn_verify_tc_kernel<__nv_bfloat16>;
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "verify smem attribute");
-        kernel<<<n_items, kThreads, kSmemBytes, stream>>>(kp, ctx->status);
+        e = tt_launch_pdl(kernel, dim3(n_items), dim3(kThreads), (size_t)kSmemBytes, stream, kp, ctx->status);
     }
-    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_verify_tc launch");
     return TT_OK;
 }

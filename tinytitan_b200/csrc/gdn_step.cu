@@ -270,23 +270,42 @@ gdn_step_kernel(GdnParams p, uint32_t n_sessions, uint32_t n_items, uint32_t *__
 
         const size_t lane_off = ((size_t)w.h * p.dv + w.dv0 + row_a) * DK + 4 * l;
 
+        // Gates of a short multi-row item (2..4 tokens, the verify step): lane t evaluates token t's pair once
+        // and the warp reads it back with two shuffles per token, instead of every lane evaluating the two
+        // exponentials and the logarithm of every token. The item's tokens were all requested at least
+        // kTokDepth - 4 tokens ago.
+        const bool lane_gates = !f32_gates && p.rows > 1 && p.rows <= 4;
+        float g_lane = 1.f, beta_lane = 0.f;
+        auto gate_pair = [&](const __half *entry, uint32_t t, float &g, float &beta) {
+            const uint2 gw = *reinterpret_cast<const uint2 *>(entry + 2 * DK + kRowsPerWarp);
+            const size_t gi = ((size_t)t * p.hv + w.h) * 2;
+            const uint32_t sh_a = ((reinterpret_cast<uintptr_t>(ses.a) + gi) & 2) * 8;
+            const uint32_t sh_b = ((reinterpret_cast<uintptr_t>(ses.b) + gi) & 2) * 8;
+            const float raw_a = __half2float(__ushort_as_half((unsigned short)(gw.x >> sh_a)));
+            const float raw_b = __half2float(__ushort_as_half((unsigned short)(gw.y >> sh_b)));
+            g = exp_2ulp(hp.x * softplus_fast(raw_a + hp.y));
+            beta = __frcp_rn(1.f + exp_2ulp(-raw_b));
+        };
+        if (lane_gates) {
+            cp_async_wait<kTokDepth - 4>();
+            __syncwarp();
+            const uint32_t t = (uint32_t)lane < p.rows ? lane : 0;
+            gate_pair(tok_ring + ((pair + t) % kTokDepth) * kTokHalves, t, g_lane, beta_lane);
+        }
+
         for (uint32_t t = 0; t < p.rows; ++t, ++pair) {
             cp_async_wait<kTokDepth - 1>();   // this lane's pieces of `pair` have landed ...
             __syncwarp();                     // ... and so have everyone else's
             const __half *entry = tok_ring + (pair % kTokDepth) * kTokHalves;
-            const uint2 gw = *reinterpret_cast<const uint2 *>(entry + 2 * DK + kRowsPerWarp);
             float g, beta;
             if (f32_gates) {
+                const uint2 gw = *reinterpret_cast<const uint2 *>(entry + 2 * DK + kRowsPerWarp);
                 g = __uint_as_float(gw.x); beta = __uint_as_float(gw.y);
+            } else if (lane_gates) {
+                g = __shfl_sync(0xffffffffu, g_lane, t);
+                beta = __shfl_sync(0xffffffffu, beta_lane, t);
             } else {
-                const size_t gi = ((size_t)t * p.hv + w.h) * 2;
-                const uint32_t sh_a = ((reinterpret_cast<uintptr_t>(ses.a) + gi) & 2) * 8;
-                const uint32_t sh_b = ((reinterpret_cast<uintptr_t>(ses.b) + gi) & 2) * 8;
-                const float raw_a = __half2float(__ushort_as_half((unsigned short)(gw.x >> sh_a)));
-                const float raw_b = __half2float(__ushort_as_half((unsigned short)(gw.y >> sh_b)));
-                const float x = raw_a + hp.y;
-                g = exp_2ulp(hp.x * softplus_fast(x));
-                beta = __frcp_rn(1.f + exp_2ulp(-raw_b));
+                gate_pair(entry, t, g, beta);
             }
             const float2 vv = __half22float2(*reinterpret_cast<const __half2 *>(entry + 2 * DK + row_a));
             const __half *qs = entry + 4 * l, *ks = entry + DK + 4 * l;
