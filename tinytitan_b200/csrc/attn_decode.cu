@@ -1073,9 +1073,9 @@ TT_API void tt_attn_reference_split_geometry(uint32_t n_q_heads, uint32_t n_kv_h
     out->use_swa_grouped_partial = swa_grouped ? 1u : 0u;
 }
 
-int tt_verify_tc_encode_maps(tt_context *ctx, uint32_t n_sessions, const tt_attn_batch_params *p);
+int tt_verify_tc_encode_maps(tt_context *ctx, uint32_t n_sessions, const tt_attn_batch_params *p, void *dst_maps);
 int tt_launch_verify_tc(tt_context *ctx, cudaStream_t stream, uint32_t n_sessions, uint32_t n_items, float *part_o,
-                        float *part_m, float *part_l, const tt_attn_batch_params *p, bool direct);
+                        float *part_m, float *part_l, const tt_attn_batch_params *p, bool direct, bool in_params);
 
 // Split plan of the tensor-core verify pass: one item per (session, kv head, key range) serving all
 // packed rows, the parts of one session of equal length (a multiple of the 128-key tile). One CTA is
@@ -1222,6 +1222,10 @@ static bool plan_wide(tt_context *ctx, const TTDecodeSession *in_sessions, uint3
         s.n_parts = parts;
         s.partial_base = partial_cursor;
         ctx->h_sessions[i] = s;
+        if (n_sessions <= kVerifyParamSessions) {      // the parameter form: the kernel derives the same items
+            ctx->session_table.s[i] = s;
+            ctx->session_table.item_prefix[i] = item_cursor;
+        }
         if (rows_total > max_rows) max_rows = rows_total;
         for (uint32_t part = 0; part < parts; ++part) {
             const uint32_t kb = s.kv_start + part * len;
@@ -1236,6 +1240,10 @@ static bool plan_wide(tt_context *ctx, const TTDecodeSession *in_sessions, uint3
             }
         }
         partial_cursor += parts * rows_total;
+    }
+    if (n_sessions <= kVerifyParamSessions) {
+        ctx->session_table.item_prefix[n_sessions] = item_cursor;
+        ctx->session_table.n = n_sessions;
     }
     *out_items = item_cursor; *out_partial_rows = partial_cursor; *out_max_rows = max_rows;
     return true;
@@ -1311,13 +1319,15 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     tt_bind_decode_tables(ctx, n_sessions, wide);
     uint32_t keys_per_item = 0, n_items = 0;
     uint32_t partial_cursor = 0, item_cursor = 0, max_rows = 0;
-    if (wide) wide = plan_wide(ctx, in_sessions, n_sessions, p, keys, &n_items, &partial_cursor, &max_rows);
-    // Up to kParamSessions sessions travel in the kernel parameters: nothing is uploaded and the
-    // item table is never built (a CTA derives its item from the block index).
-    const bool in_params = !wide && n_sessions <= kParamSessions;
-    const uint32_t hpc = tt_decode_heads_per_cta(p->n_kv_heads, quantised);
     TTSessionTable &table = ctx->session_table;
     table.n = 0;
+    if (wide) wide = plan_wide(ctx, in_sessions, n_sessions, p, keys, &n_items, &partial_cursor, &max_rows);
+    if (!wide) table.n = 0;
+    // Up to kParamSessions sessions (kVerifyParamSessions of a verify batch, whose tensor maps travel
+    // too) go in the kernel parameters: nothing is uploaded and the item table is not read (a CTA
+    // derives its item from the block index).
+    const bool in_params = wide ? n_sessions <= kVerifyParamSessions : n_sessions <= kParamSessions;
+    const uint32_t hpc = tt_decode_heads_per_cta(p->n_kv_heads, quantised);
     if (!wide) {
         int rc = plan_splits(keys, rows, n_sessions, p->head_dim, p->n_q_heads, p->n_kv_heads, (uint32_t)ctx->sm_count,
                              ctx->workspace_bytes, hpc, &keys_per_item, &n_items);
@@ -1375,11 +1385,11 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     bool wide_rows = false;             // more than 8 packed query rows per KV head somewhere: two n-tiles per item
     for (uint32_t i = 0; i < n_sessions; ++i) wide_rows |= in_sessions[i].q_rows * group > 8;
     cudaError_t e = cudaSuccess;
+    if (wide) {
+        const int rc = tt_verify_tc_encode_maps(ctx, n_sessions, p, in_params ? (void *)ctx->verify_maps.m : ctx->h_tensor_maps);
+        if (rc != TT_OK) return rc;
+    }
     if (!in_params) {
-        if (wide) {
-            const int rc = tt_verify_tc_encode_maps(ctx, n_sessions, p);
-            if (rc != TT_OK) return rc;
-        }
         // sessions, maps and items sit back to back: one upload
         const size_t bytes = (size_t)(reinterpret_cast<unsigned char *>(ctx->h_items + n_items) - ctx->h_tables);
         e = cudaMemcpyAsync(ctx->tables, ctx->h_tables, bytes, cudaMemcpyHostToDevice, stream);
@@ -1391,7 +1401,7 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     bool direct = wide && mode == 0;
     for (uint32_t i = 0; direct && i < n_sessions; ++i) direct = ctx->h_sessions[i].n_parts == 1;
     if (wide) {
-        const int rc = tt_launch_verify_tc(ctx, stream, n_sessions, n_items, part_o, part_m, part_l, p, direct);
+        const int rc = tt_launch_verify_tc(ctx, stream, n_sessions, n_items, part_o, part_m, part_l, p, direct, in_params);
         if (rc != TT_OK) return rc;
     } else if (quantised)
         e = launch_partial_quant(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status,

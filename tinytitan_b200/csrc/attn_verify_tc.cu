@@ -88,8 +88,13 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Up to kVerifyParamSessions sessions travel in the kernel parameters together with their tensor maps
+// (table.n != 0): nothing is uploaded before the launch, a CTA derives its item from the block index,
+// and the maps need no proxy fence. Larger batches read the tables the host copied to device memory.
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParams p, uint32_t *__restrict__ status) {
+__global__ void __launch_bounds__(kThreads, 1)
+attn_verify_tc_kernel(VerifyParams p, uint32_t *__restrict__ status, const __grid_constant__ TTSessionTable table,
+                      const __grid_constant__ TTVerifyMaps pmaps) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char *q_s = smem;
@@ -99,15 +104,37 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
     pdl_wait();       // the kernel before this one may have produced the query rows or the newest K/V rows
-    const TTDecodeItem item = p.items[blockIdx.x];
-    const TTDecodeSession ses = p.sessions[item.session];
+    TTDecodeItem item;
+    TTDecodeSession ses;
+    const bool in_params = table.n != 0;
+    if (in_params) {
+        uint32_t i = 0;
+        while (i + 1 < table.n && table.item_prefix[i + 1] <= blockIdx.x) ++i;
+        ses = table.s[i];
+        const uint32_t local = blockIdx.x - table.item_prefix[i];
+        const uint32_t part = local / p.n_kv_heads;
+        const uint32_t keys = ses.seq_len > ses.kv_start ? ses.seq_len - ses.kv_start : 0u;
+        const uint32_t len = ((keys + ses.n_parts - 1) / ses.n_parts + 127) / 128 * 128;   // the host planner's part length
+        item.session = i;
+        item.kv_head = local - part * p.n_kv_heads;
+        item.key_begin = ses.kv_start + part * len;
+        item.key_end = min(ses.seq_len, item.key_begin + len);
+        if (item.key_end < item.key_begin) item.key_end = item.key_begin;
+        item.part_index = part;
+        item.partial_base = ses.partial_base;
+    } else {
+        item = p.items[blockIdx.x];
+        ses = p.sessions[item.session];
+    }
     const uint32_t group = p.n_q_heads / p.n_kv_heads;
     const uint32_t n_rows = ses.q_rows * group;                    // packed rows in use (<= 64)
     const uint32_t n_tiles = (item.key_end - item.key_begin + kBK - 1) / kBK;
     const uint32_t rows_total = ses.q_rows * p.n_q_heads;
 
     // Ring unit u (16 KB) in consumption order: K(0) | K(1) V(0) | K(2) V(1) | ... | V(n-1), four units each.
-    const CUtensorMap *k_map = p.maps + 2 * item.session, *v_map = k_map + 1;
+    const CUtensorMap *k_map = in_params ? reinterpret_cast<const CUtensorMap *>(pmaps.m[2 * item.session])
+                                         : p.maps + 2 * item.session;
+    const CUtensorMap *v_map = k_map + 1;
     const uint32_t n_units = kUnitsPerTile * n_tiles;
     auto load_unit = [&](uint32_t u) {
         // block of four: 0 -> K(0); odd 2t+1 -> K(t+1) (while it exists); even 2t+2 -> V(t); the last block is V(n-1)
@@ -122,28 +149,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
         tma_load_2d(ring + slot * kSlotBytes, is_k ? k_map : v_map, (int)(item.kv_head * kHD + c * 64),
                     (int)(item.key_begin + tile * kBK), &ms->full[slot]);
     };
-    // The first ring fill leaves before the CTA-wide sync so that it overlaps the staging of Q (the
-    // thread that initialises the barriers is the one that uses them first).
-    if (threadIdx.x == 64) {
-        for (int s = 0; s < kSlots; ++s) { mbar_init(&ms->full[s], 1); mbar_init(&ms->empty[s], 1); }
-        mbar_init(&ms->s_full[0], 1); mbar_init(&ms->s_full[1], 1);
-        mbar_init(&ms->p_ready[0], 2); mbar_init(&ms->p_ready[1], 2);
-        mbar_init(&ms->o_ready[0], 1); mbar_init(&ms->o_ready[1], 1);
-        mbar_fence_init();
-        if (n_tiles > 0) {
-            // the maps were rewritten by a host copy since the last launch that used these addresses
-            asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(k_map) : "memory");
-            asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(v_map) : "memory");
-            for (uint32_t u = 0; u < (uint32_t)kSlots && u < n_units; ++u) load_unit(u);
-        }
-    }
-    if (warp == 2) {
-        __syncwarp();
-        tmem_alloc(&ms->tmem_base, kTmemCols);
-    }
-
     // ---- stage Q: packed row r = w*G + g -> q[w][kv_head*G + g][:], K-major, 128-byte swizzle;
-    // asynchronous 16-byte copies so that all of a thread's chunks are in flight together
+    // asynchronous 16-byte copies so that all of a thread's chunks are in flight together, issued
+    // ahead of the ring fill because the first product waits for Q as well as for K(0)
     {
         const T *q = reinterpret_cast<const T *>(ses.q);
         for (uint32_t c = threadIdx.x; c < kRows * (kHD / 8); c += kThreads) {
@@ -159,9 +167,31 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        fence_async_smem();
     }
+    // The first ring fill leaves before the CTA-wide sync so that it overlaps the arrival of Q (the
+    // thread that initialises the barriers is the one that uses them first).
+    if (threadIdx.x == 64) {
+        for (int s = 0; s < kSlots; ++s) { mbar_init(&ms->full[s], 1); mbar_init(&ms->empty[s], 1); }
+        mbar_init(&ms->s_full[0], 1); mbar_init(&ms->s_full[1], 1);
+        mbar_init(&ms->p_ready[0], 2); mbar_init(&ms->p_ready[1], 2);
+        mbar_init(&ms->o_ready[0], 1); mbar_init(&ms->o_ready[1], 1);
+        mbar_fence_init();
+        if (n_tiles > 0) {
+            if (!in_params) {
+                // the maps were rewritten by a host copy since the last launch that used these addresses
+                asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(k_map) : "memory");
+                asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(v_map) : "memory");
+            }
+            for (uint32_t u = 0; u < (uint32_t)kSlots && u < n_units; ++u) load_unit(u);
+        }
+    }
+    if (warp == 2) {
+        __syncwarp();
+        tmem_alloc(&ms->tmem_base, kTmemCols);
+    }
+
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -396,10 +426,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_verify_tc_kernel(VerifyParam
 }  // namespace
 
 // One K and one V tensor map per session of a verify batch ([seq_len rows][n_kv_heads * 256], box
-// 128 x 64, keys past seq_len read as zero), written into the staging table that the caller uploads
-// together with the session and item tables.
-int tt_verify_tc_encode_maps(tt_context *ctx, uint32_t n_sessions, const tt_attn_batch_params *p) {
-    CUtensorMap *maps = reinterpret_cast<CUtensorMap *>(ctx->h_tensor_maps);
+// 128 x 64, keys past seq_len read as zero), written to `dst_maps`: the context's parameter block for a
+// small batch, else the staging table that the caller uploads together with the session and item tables.
+int tt_verify_tc_encode_maps(tt_context *ctx, uint32_t n_sessions, const tt_attn_batch_params *p, void *dst_maps) {
+    CUtensorMap *maps = reinterpret_cast<CUtensorMap *>(dst_maps);
     for (uint32_t i = 0; i < n_sessions; ++i) {
         const TTDecodeSession &s = ctx->h_sessions[i];
         const uint64_t rows = s.seq_len > 0 ? s.seq_len : 1;
@@ -415,8 +445,11 @@ int tt_verify_tc_encode_maps(tt_context *ctx, uint32_t n_sessions, const tt_attn
 // Pass 1 of a verify batch on the tensor cores: the items (one per (session, kv head, key range), all
 // packed rows at once), the sessions and the tensor maps are already on the device.
 int tt_launch_verify_tc(tt_context *ctx, cudaStream_t stream, uint32_t n_sessions, uint32_t n_items, float *part_o,
-                        float *part_m, float *part_l, const tt_attn_batch_params *p, bool direct) {
+                        float *part_m, float *part_l, const tt_attn_batch_params *p, bool direct, bool in_params) {
     (void)n_sessions;
+    static thread_local TTSessionTable no_table;       // n == 0: the kernel reads the device tables
+    no_table.n = 0;
+    const TTSessionTable &table = in_params ? ctx->session_table : no_table;
     cudaError_t e;
     VerifyParams kp;
     kp.items = ctx->items; kp.sessions = ctx->sessions;
@@ -431,12 +464,12 @@ int tt_launch_verify_tc(tt_context *ctx, cudaStream_t stream, uint32_t n_session
         auto kernel = attn_verify_tc_kernel<__half>;
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "verify smem attribute");
-        e = tt_launch_pdl(kernel, dim3(n_items), dim3(kThreads), (size_t)kSmemBytes, stream, kp, ctx->status);
+        e = tt_launch_pdl(kernel, dim3(n_items), dim3(kThreads), (size_t)kSmemBytes, stream, kp, ctx->status, table, ctx->verify_maps);
     } else {
         auto kernel = attn_verify_tc_kernel<__nv_bfloat16>;
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return tt_check_cuda(ctx, e, "verify smem attribute");
-        e = tt_launch_pdl(kernel, dim3(n_items), dim3(kThreads), (size_t)kSmemBytes, stream, kp, ctx->status);
+        e = tt_launch_pdl(kernel, dim3(n_items), dim3(kThreads), (size_t)kSmemBytes, stream, kp, ctx->status, table, ctx->verify_maps);
     }
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_verify_tc launch");

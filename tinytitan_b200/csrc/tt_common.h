@@ -59,6 +59,13 @@ struct TTSessionTable {
     uint32_t n;
 };
 
+// Tensor maps of a verify batch that travel in the kernel parameters next to its TTSessionTable: the K and
+// the V map of session i at [2 * i], [2 * i + 1]. 128 bytes each, 64-byte aligned as the copy engine wants.
+constexpr uint32_t kVerifyParamSessions = 16;
+struct alignas(64) TTVerifyMaps {
+    unsigned char m[2 * kVerifyParamSessions][128];
+};
+
 struct tt_context {
     int device = 0;
     int sm_count = 0;
@@ -87,6 +94,7 @@ struct tt_context {
     uint32_t *h_rows = nullptr;
     void *h_tensor_maps = nullptr;
     TTSessionTable session_table;       // the parameter form of the current decode call's sessions
+    TTVerifyMaps verify_maps;           // ... and of a verify batch's tensor maps
     uint64_t launches = 0;
     uint32_t exchange_poll_limit = 0;   // 0: the exchange kernels' default (about a second)
     // last verify split plan: the part length only depends on the sessions' 128-key tile counts and
