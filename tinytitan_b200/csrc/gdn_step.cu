@@ -15,6 +15,7 @@
 #include "tt_sm100.h"
 
 #include <algorithm>
+#include <type_traits>
 
 namespace {
 
@@ -293,20 +294,8 @@ gdn_step_kernel(GdnParams p, uint32_t n_sessions, uint32_t n_items, uint32_t *__
             gate_pair(tok_ring + ((pair + t) % kTokDepth) * kTokHalves, t, g_lane, beta_lane);
         }
 
-        for (uint32_t t = 0; t < p.rows; ++t, ++pair) {
-            cp_async_wait<kTokDepth - 1>();   // this lane's pieces of `pair` have landed ...
-            __syncwarp();                     // ... and so have everyone else's
-            const __half *entry = tok_ring + (pair % kTokDepth) * kTokHalves;
-            float g, beta;
-            if (f32_gates) {
-                const uint2 gw = *reinterpret_cast<const uint2 *>(entry + 2 * DK + kRowsPerWarp);
-                g = __uint_as_float(gw.x); beta = __uint_as_float(gw.y);
-            } else if (lane_gates) {
-                g = __shfl_sync(0xffffffffu, g_lane, t);
-                beta = __shfl_sync(0xffffffffu, beta_lane, t);
-            } else {
-                gate_pair(entry, t, g, beta);
-            }
+        // one token applied to the 8 rows in registers
+        auto apply_token = [&](const __half *entry, uint32_t t, float g, float beta) {
             const float2 vv = __half22float2(*reinterpret_cast<const __half2 *>(entry + 2 * DK + row_a));
             const __half *qs = entry + 4 * l, *ks = entry + DK + 4 * l;
 
@@ -338,20 +327,52 @@ gdn_step_kernel(GdnParams p, uint32_t n_sessions, uint32_t n_items, uint32_t *__
                 ya2 = dot4(sa[j], q4, ya2);
                 yb2 = dot4(sb[j], q4, yb2);
             }
-            const float ya = ya2.x + ya2.y, yb = yb2.x + yb2.y;
-            __syncwarp();                       // every lane has read the entry: it may be refilled
-            prefetch(pair + kTokDepth);
-
-            const float y_mine = group_sum2(ya, yb, upper);
+            const float y_mine = group_sum2(ya2.x + ya2.y, yb2.x + yb2.y, upper);
             if ((lane & 3) == 0) {     // lane 0 of the group holds row A's readout, lane 4 row B's
                 __half *y = reinterpret_cast<__half *>(ses.y) + (size_t)t * p.hv * p.dv + (size_t)w.h * p.dv;
                 y[w.dv0 + row_a + (upper ? 1 : 0)] = __float2half_rn(y_mine * p.readout_scale);
             }
-
             if (t == 0 && ses.checkpoint_state != nullptr) {
                 float *ck = ses.checkpoint_state + lane_off;
 #pragma unroll
                 for (int j = 0; j < C; ++j) { st_f4(ck + 32 * j, sa[j]); st_f4(ck + DK + 32 * j, sb[j]); }
+            }
+        };
+
+        if (lane_gates) {
+            // all tokens of the item in one unrolled block: the loads and conversions of a token's q and k
+            // are independent of the state, so the compiler moves them under the shuffle reductions of the
+            // token before (with one token per loop trip every warp sat through each reduction idle)
+            auto block = [&](auto n_const) {
+                constexpr uint32_t N = decltype(n_const)::value;
+#pragma unroll
+                for (uint32_t t = 0; t < N; ++t) {
+                    const float g = __shfl_sync(0xffffffffu, g_lane, t), beta = __shfl_sync(0xffffffffu, beta_lane, t);
+                    apply_token(tok_ring + ((pair + t) % kTokDepth) * kTokHalves, t, g, beta);
+                }
+                __syncwarp();                   // every lane has read the entries: they may be refilled
+#pragma unroll
+                for (uint32_t t = 0; t < N; ++t) prefetch(pair + kTokDepth + t);
+                pair += N;
+            };
+            if (p.rows == 4) block(std::integral_constant<uint32_t, 4>{});
+            else if (p.rows == 3) block(std::integral_constant<uint32_t, 3>{});
+            else block(std::integral_constant<uint32_t, 2>{});
+        } else {
+            for (uint32_t t = 0; t < p.rows; ++t, ++pair) {
+                cp_async_wait<kTokDepth - 1>();   // this lane's pieces of `pair` have landed ...
+                __syncwarp();                     // ... and so have everyone else's
+                const __half *entry = tok_ring + (pair % kTokDepth) * kTokHalves;
+                float g, beta;
+                if (f32_gates) {
+                    const uint2 gw = *reinterpret_cast<const uint2 *>(entry + 2 * DK + kRowsPerWarp);
+                    g = __uint_as_float(gw.x); beta = __uint_as_float(gw.y);
+                } else {
+                    gate_pair(entry, t, g, beta);
+                }
+                apply_token(entry, t, g, beta);
+                __syncwarp();                       // every lane has read the entry: it may be refilled
+                prefetch(pair + kTokDepth);
             }
         }
 
