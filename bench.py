@@ -506,7 +506,7 @@ def aux_measurements(w, pk, only=None, c5_sessions=64):
                                      "frac_hbm": b5 / ms / 1e6 / pk["hbm_gbs"], "pass1_frac_hbm": b5 / kms / 1e6 / pk["hbm_gbs"],
                                      "tok_per_s": n5 * w5 / ms * 1e3, "host_us_first_call_cold_plan": cold_us,
                                      "host_us_next_call_cached_plan": warm_us,
-                                     "note": "ms = whole call (table uploads, pass 1, combine), one Python call per step"}
+                                     "note": "ms = whole call (pass 1 + merge; tables travel in the kernel parameters up to 16 sessions, else one upload), one Python call per step"}
         del batch, keep
         gdn5, gb, z5, keep2, cfg5 = make_gdn_batch(torch, tt, w.ctx, n5, 64, w5, 9)
         ms = ev_time(lambda: gdn5.encode_prepared(gb, z5, z5, rows=w5), 10)
