@@ -492,6 +492,17 @@ int tt_gdn_decode_pre(tt_context *ctx, tt_stream stream, const tt_gdn_pre_sessio
                       uint32_t key_dim, uint32_t channels, uint32_t taps);
 int tt_gdn_conv_tail_update(tt_context *ctx, tt_stream stream, void *tail, const void *qkv,
                             uint32_t channels, uint32_t taps, uint32_t rows);
+/* The prefill prologue of a GDN layer over a chunk of rows in one launch: what
+ * GDN.encodeConvPrefill, GDN.encodeConvTailCheckpoint, GDN.encodeConvTailUpdate and GDN.encodeQKNorm
+ * (GDN.swift:206-313) do with four. conv_out := SiLU(conv([tail | rows of qkv])) with the q and k
+ * heads RMS-normed with the folded scales; checkpoint_tail (nullable) := the tail as it stands after
+ * row 0 alone; with update_tail != 0 the tail becomes the last taps-1 raw rows of [old tail | rows].
+ * Bit-identical to the four separate calls. key_dim 32, 64, 128 or 256; channels a multiple of
+ * key_dim; taps <= 8; buffers aligned to key_dim / 16 bytes. */
+int tt_gdn_prefill_pre(tt_context *ctx, tt_stream stream, void *tail, const void *qkv,
+                       const void *conv_weight, void *conv_out, void *checkpoint_tail,
+                       uint32_t n_k_heads, uint32_t key_dim, uint32_t channels, uint32_t taps,
+                       uint32_t rows, int update_tail);
 /* GDN.encodeConvTailCheckpoint -> gdn_conv_tail_checkpoint (GDN.swift:264-286,
  * gdn.metal:449-464): the tail as it stands after qkv row 0 alone. */
 int tt_gdn_conv_tail_checkpoint(tt_context *ctx, tt_stream stream, const void *tail, const void *qkv,

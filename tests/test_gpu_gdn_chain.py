@@ -156,3 +156,70 @@ def test_batched_decode_prologue_is_bit_identical_to_the_separate_kernels():
         assert context().launch_count - launches == 1
         torch.cuda.synchronize()
         assert torch.equal(out_a, out_b) and torch.equal(tails_a, tails_b)
+
+
+@pytest.mark.parametrize("cfg,rows", [(CFG, 7), (CFG, 2), (tt.LinearAttentionConfig(16, 32, 128, 128, 4), 70),
+                                      (tt.LinearAttentionConfig(16, 32, 128, 128, 4), 1),
+                                      (tt.LinearAttentionConfig(4, 8, 64, 64, 3), 33)])
+def test_prefill_prologue_is_bit_identical_to_the_separate_kernels(cfg, rows):
+    # conv + SiLU over the chunk, the tail checkpoint after row 0, the tail update and the q/k norm in ONE launch
+    # against the four separate launches, at the fixture width (one channel per lane) and at production width
+    # (vector loads, several row blocks per channel group, a chunk longer and shorter than the conv history)
+    g = torch.Generator(device="cuda"); g.manual_seed(911 + rows)
+    c, taps = cfg.qkv_dim, cfg.conv_kernel_size
+    gdn = tt.GDN(context(), cfg)
+    conv_w = (torch.rand(c, taps, device="cuda", generator=g) * 0.8 - 0.4).bfloat16()
+    qkv = (torch.rand(rows, c, device="cuda", generator=g) * 2 - 1).half()
+    tail0 = (torch.rand(taps - 1, c, device="cuda", generator=g) * 2 - 1).half()
+
+    tail_a, out_a, ck_a = tail0.clone(), torch.empty_like(qkv), torch.empty_like(tail0)
+    gdn.encode_conv_prefill(tail_a, qkv, conv_w, out_a, rows)
+    gdn.encode_conv_tail_checkpoint(tail_a, qkv, ck_a)
+    gdn.encode_conv_tail_update(tail_a, qkv, rows)
+    gdn.encode_qk_norm(out_a, rows=rows)
+
+    tail_b, out_b, ck_b = tail0.clone(), torch.empty_like(qkv), torch.empty_like(tail0)
+    launches = context().launch_count
+    gdn.encode_prefill_prologue(tail_b, qkv, conv_w, out_b, rows, checkpoint_tail=ck_b)
+    assert context().launch_count - launches == 1
+    torch.cuda.synchronize()
+    assert torch.equal(out_a, out_b) and torch.equal(tail_a, tail_b) and torch.equal(ck_a, ck_b)
+
+    # the conv + SiLU itself against a float64 statement of the same sum (rounded once to fp16), q/k slices aside
+    full = torch.cat([tail0, qkv]).double()
+    want = sum(full[j:j + rows] * conv_w.double()[:, j] for j in range(taps))
+    want = want / (1 + torch.exp(-want))
+    lo = 2 * cfg.num_k_heads * cfg.key_head_dim
+    assert (out_b[:, lo:].double() - want[:, lo:]).abs().max().item() <= 2e-3
+    # the read-only form leaves the tail alone
+    tail_c = tail0.clone()
+    gdn.encode_prefill_prologue(tail_c, qkv, conv_w, out_b, rows, update_tail=False)
+    torch.cuda.synchronize()
+    assert torch.equal(tail_c, tail0)
+
+
+@pytest.mark.parametrize("cfg", [tt.LinearAttentionConfig(16, 32, 128, 128, 4), tt.LinearAttentionConfig(1, 1, 32, 36, 4),
+                                 tt.LinearAttentionConfig(1, 1, 8, 18, 4), tt.LinearAttentionConfig(1, 1, 8, 17, 4)])
+def test_conv_mix_lane_chunks_and_decode_order(cfg):
+    # every lane-chunk width of the conv kernel (8192, 100, 34 and 33 channels: 8, 4, 2 and 1 channels per lane,
+    # the last with a partial group), prefill and decode forms, against float64
+    channels = cfg.qkv_dim
+    g = torch.Generator(device="cuda"); g.manual_seed(channels)
+    taps, rows = 4, 19
+    gdn = tt.GDN(context(), cfg)
+    conv_w = (torch.rand(channels, taps, device="cuda", generator=g) * 0.8 - 0.4).bfloat16()
+    qkv = (torch.rand(rows, channels, device="cuda", generator=g) * 2 - 1).half()
+    tail = (torch.rand(taps - 1, channels, device="cuda", generator=g) * 2 - 1).half()
+    out = torch.empty_like(qkv)
+    gdn.encode_conv_prefill(tail, qkv, conv_w, out, rows)
+    full = torch.cat([tail, qkv]).double()
+    want = sum(full[j:j + rows] * conv_w.double()[:, j] for j in range(taps))
+    want = want / (1 + torch.exp(-want))
+    torch.cuda.synchronize()
+    assert (out.double() - want).abs().max().item() <= 2e-3
+    one = torch.empty(channels, device="cuda", dtype=torch.float16)
+    t2 = tail.clone()
+    gdn.encode_conv_decode(t2, qkv[0], conv_w, one)
+    torch.cuda.synchronize()
+    assert (one.double() - want[0]).abs().max().item() <= 2e-3
+    assert torch.equal(t2, torch.cat([tail[1:], qkv[:1]]))

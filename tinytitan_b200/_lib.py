@@ -160,6 +160,7 @@ SIGNATURES = {
     "tt_kv_window_host_row": (C.c_int, [_vp, _u32, _u32, _u32, C.c_int, _vp]),
     "tt_kv_window_counters": (None, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "tt_gdn_decode_pre": (C.c_int, [_vp, _vp, C.POINTER(GdnPreSession), _u32, _vp, _u32, _u32, _u32, _u32]),
+    "tt_gdn_prefill_pre": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.c_int]),
     "tt_ctx_set_exchange_poll_limit": (C.c_int, [_vp, _u32]),
     "tt_attn_decode_noalloc_status": (C.c_int, [_vp, C.POINTER(_u32)]),
     "tt_attn_reference_split_geometry": (None, [_u32, _u32, _u32, _u32, C.c_int, C.POINTER(SplitGeometry)]),

@@ -527,6 +527,15 @@ class GDN:
             self.context.handle, _stream(command_buffer), arr, n, _addr(conv_weight), self.config.num_k_heads,
             self.config.key_head_dim, self.config.qkv_dim, self.config.conv_kernel_size))
 
+    def encode_prefill_prologue(self, tail, qkv_rows, conv_weight, conv_out, rows, checkpoint_tail=None, update_tail=True,
+                                command_buffer=None):
+        """encodeConvPrefill + encodeConvTailCheckpoint + encodeConvTailUpdate + encodeQKNorm over a chunk of rows in
+        one launch (bit-identical to the four separate calls)."""
+        self.context.check(L.lib().tt_gdn_prefill_pre(
+            self.context.handle, _stream(command_buffer), _addr(tail), _addr(qkv_rows), _addr(conv_weight),
+            _addr(conv_out), _addr(checkpoint_tail) if checkpoint_tail is not None else None, self.config.num_k_heads,
+            self.config.key_head_dim, self.config.qkv_dim, self.config.conv_kernel_size, rows, int(update_tail)))
+
     def encode_conv_prefill(self, tail, qkv_rows, conv_weight, out, rows, command_buffer=None, tail_offset=0,
                             qkv_rows_offset=0, conv_weight_offset=0, out_offset=0):
         """GDN.encodeConvPrefill: conv over [tail | chunk rows]; the tail is read-only here."""
