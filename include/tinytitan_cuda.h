@@ -187,16 +187,17 @@ int tt_attn_combine(tt_context *ctx, tt_stream stream, const float *m, const flo
  * Every rank owns an exchange buffer (tt_peer_buffer_create) that the other ranks map
  * (tt_peer_buffer_open) with the 64-byte handle the owner hands out through any host channel.
  * tt_attn_exchange_combine stores this rank's triple into slot `rank` of every rank's buffer
- * (plain stores over NVLink), publishes it with a release store of `epoch` to a per-head flag,
- * waits -- with a poll limit, TT_DEV_WAIT_TIMEOUT in the status word when it runs out -- until
- * all ranks' flags of this epoch have arrived in its own buffer, and merges. `epoch` must be
+ * (plain 16-byte stores over NVLink in which every 8 bytes are one value and `epoch`, so a word
+ * validates itself and no flag or fence follows the data), polls -- with a limit,
+ * TT_DEV_WAIT_TIMEOUT in the status word when it runs out -- until every word of every rank's
+ * slot in its own buffer carries this epoch, and merges. `epoch` must be
  * the same on all ranks for one step and grow by exactly 1 per step, starting at 1 (slots are
  * double-buffered on its parity: a rank can be at most one step ahead of another).
  * peer_buffers[r] is rank r's buffer as mapped by THIS process (its own for r == rank).
  * world <= 16; head_dim a multiple of 4. */
 size_t tt_attn_exchange_bytes(uint32_t world, uint32_t n_q_heads, uint32_t head_dim);
 /* No counterpart in the reference. How many polls (about 0.25 us each) the exchange kernels of
- * this context wait for the other ranks' flags before they give up, set TT_DEV_WAIT_TIMEOUT in
+ * this context wait for the other ranks' words before they give up, set TT_DEV_WAIT_TIMEOUT in
  * the status word and leave the output untouched; 0 restores the default (about one second).
  * A short limit lets a host that already knows a peer is gone (a heartbeat, a store) get its
  * stream back quickly; the status is read with tt_ctx_poll_status (TT_ERR_TIMEOUT). */

@@ -119,10 +119,10 @@ def test_verify_split_planner():
 
 
 def test_exchange_buffer_size_is_pure_arithmetic():
-    # two parities of [world][heads][64-column blocks] cells of 68 floats plus one flag per cell,
-    # each parity padded to 256 bytes
+    # two parities of [world][heads][64-column blocks] cells; a cell is 66 values (64 columns, max, sum), each
+    # travelling as 8 bytes {value, epoch}: 33 words of 16 bytes; each parity padded to 256 bytes
     cells = 8 * 16 * 4
-    assert L.lib().tt_attn_exchange_bytes(8, 16, 256) == 2 * ((cells * 68 * 4 + cells * 4 + 255) // 256 * 256)
+    assert L.lib().tt_attn_exchange_bytes(8, 16, 256) == 2 * ((cells * 33 * 16 + 255) // 256 * 256)
     assert L.lib().tt_attn_exchange_bytes(2, 16, 256) < L.lib().tt_attn_exchange_bytes(4, 16, 256)
     assert L.lib().tt_attn_exchange_bytes(2, 8, 64) % 512 == 0
 
