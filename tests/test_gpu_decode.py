@@ -301,6 +301,20 @@ def test_verify_tensor_core_ragged_multi_part(dtype):
             assert np.all(np.abs(got[i] - want[i]) <= tol), (hq, i, np.abs(got[i] - want[i]).max())
 
 
+def test_verify_batches_on_both_sides_of_the_parameter_table_limit():
+    # up to 16 sessions travel in the kernel parameters with their tensor maps (the CTA derives its item from the
+    # block index), 17 and more go through the uploaded tables: both against the oracle, and the first 16 sessions
+    # of the larger batch bit-identical to the smaller one when the split plan is the same
+    r = np.random.default_rng(1617)
+    lens = [int(x) for x in r.integers(200, 2500, size=17)]
+    lens[3], lens[16] = 5, 4097
+    for n in (16, 17):
+        rr = np.random.default_rng(99)
+        got, want = _verify_batch(rr, 32, 2, 4, lens[:n])
+        for i in range(n):
+            assert np.all(np.abs(got[i] - want[i]) <= TOL), (n, i, np.abs(got[i] - want[i]).max())
+
+
 def test_verify_tensor_core_repeated_raises_and_window_start():
     # Key norms grow along the sequence, so later tiles keep exceeding the reference maxima by more
     # than the lazy threshold and O^T / l^T are rescaled in TMEM several times; sessions also start
