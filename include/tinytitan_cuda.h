@@ -276,7 +276,7 @@ int tt_attn_plan_splits(const uint32_t *keys_per_session, const uint32_t *q_rows
                         uint32_t n_kv_heads, uint32_t sm_count, size_t workspace_bytes,
                         uint32_t *out_keys_per_item, uint32_t *out_n_items);
 
-/* The split plan of the tensor-core verify pass (17..64 packed rows per KV head, head_dim 256), as
+/* The split plan of the tensor-core verify pass (17..128 packed rows per KV head, head_dim 256), as
  * pure arithmetic: one work item per (session, kv head, part); the parts of a session have one
  * common length, a multiple of the 128-key tile, chosen for the whole batch by simulating the
  * in-order dispatch of the items over sm_count SMs. out_parts / out_part_len: [n_sessions].

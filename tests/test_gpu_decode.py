@@ -315,6 +315,17 @@ def test_verify_batches_on_both_sides_of_the_parameter_table_limit():
             assert np.all(np.abs(got[i] - want[i]) <= TOL), (n, i, np.abs(got[i] - want[i]).max())
 
 
+@pytest.mark.parametrize("hq,q_rows", [(32, 8), (32, 5), (16, 16)])
+def test_verify_tensor_core_up_to_128_packed_rows(hq, q_rows):
+    # 128, 80 and 128 packed rows per KV head: the 128-row form of the tensor-core kernel (four softmax warps, Q in
+    # 64 KB, ten ring slots), several parts per session and a single-part session, against the oracle
+    r = np.random.default_rng(128 + q_rows)
+    lens = [3000, 700 + q_rows, q_rows, 1290]
+    got, want = _verify_batch(r, hq, 2, q_rows, lens)
+    for i in range(len(lens)):
+        assert np.all(np.abs(got[i] - want[i]) <= TOL), (i, np.abs(got[i] - want[i]).max())
+
+
 def test_verify_tensor_core_repeated_raises_and_window_start():
     # Key norms grow along the sequence, so later tiles keep exceeding the reference maxima by more
     # than the lazy threshold and O^T / l^T are rescaled in TMEM several times; sessions also start

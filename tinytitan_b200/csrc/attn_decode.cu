@@ -1075,7 +1075,8 @@ TT_API void tt_attn_reference_split_geometry(uint32_t n_q_heads, uint32_t n_kv_h
 
 int tt_verify_tc_encode_maps(tt_context *ctx, uint32_t n_sessions, const tt_attn_batch_params *p, void *dst_maps);
 int tt_launch_verify_tc(tt_context *ctx, cudaStream_t stream, uint32_t n_sessions, uint32_t n_items, float *part_o,
-                        float *part_m, float *part_l, const tt_attn_batch_params *p, bool direct, bool in_params);
+                        float *part_m, float *part_l, const tt_attn_batch_params *p, bool direct, bool in_params,
+                        bool rows128);
 
 // Split plan of the tensor-core verify pass: one item per (session, kv head, key range) serving all
 // packed rows, the parts of one session of equal length (a multiple of the 128-key tile). One CTA is
@@ -1307,13 +1308,15 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
         keys[i] = s.seq_len > s.kv_start ? s.seq_len - s.kv_start : 0u;
         rows[i] = s.q_rows;
     }
-    // Verify batches (17..64 packed rows per KV head, head_dim 256, plain 16-bit rows) take the
+    // Verify batches (17..128 packed rows per KV head, head_dim 256, plain 16-bit rows) take the
     // tensor-core pass 1: one item serves all packed rows of a (session, kv head, key range).
     bool wide = !quantised && p->head_dim == 256 && getenv("TT_VERIFY_FORCE_MMA_SYNC") == nullptr;
+    bool wide128 = false;       // some session has more than 64 packed rows: the 128-row form of the kernel
     for (uint32_t i = 0; wide && i < n_sessions; ++i) {
         const TTDecodeSession &s = in_sessions[i];
         const uint32_t packed = s.q_rows * group;
-        wide = packed > 16 && packed <= 64 && s.ring_capacity == 0 && s.keep == nullptr && s.row_index == nullptr;
+        wide = packed > 16 && packed <= 128 && s.ring_capacity == 0 && s.keep == nullptr && s.row_index == nullptr;
+        wide128 |= packed > 64;
     }
 
     tt_bind_decode_tables(ctx, n_sessions, wide);
@@ -1401,7 +1404,7 @@ int tt_launch_decode(tt_context *ctx, cudaStream_t stream, const TTDecodeSession
     bool direct = wide && mode == 0;
     for (uint32_t i = 0; direct && i < n_sessions; ++i) direct = ctx->h_sessions[i].n_parts == 1;
     if (wide) {
-        const int rc = tt_launch_verify_tc(ctx, stream, n_sessions, n_items, part_o, part_m, part_l, p, direct, in_params);
+        const int rc = tt_launch_verify_tc(ctx, stream, n_sessions, n_items, part_o, part_m, part_l, p, direct, in_params, wide128);
         if (rc != TT_OK) return rc;
     } else if (quantised)
         e = launch_partial_quant(stream, n_items, ctx->items, ctx->sessions, part_o, part_m, part_l, p, ctx->status,

@@ -1,6 +1,6 @@
 // Few-token ("verify") decode attention on the sm_100a tensor cores, head_dim 256.
 //
-// With W draft rows and G query heads per KV head, W*G packed query rows (17..64) share every K/V
+// With W draft rows and G query heads per KV head, W*G packed query rows (17..128) share every K/V
 // row of a KV head. The mma.sync decode kernel serves 16 packed rows per pass and re-reads the key
 // range for the rest; here one CTA computes all of them against each K/V row it streams. A packed
 // row is a TMEM lane, so a softmax thread owns a whole row of the score tile and nothing of the
@@ -36,25 +36,32 @@ namespace {
 
 constexpr int kHD = 256;
 constexpr int kBK = 128;                   // keys per tile
-constexpr int kRows = 64;                  // packed query rows
-constexpr int kThreads = 128;
-constexpr int kSlots = 12;                 // ring slots (even: a V pair never wraps)
+constexpr int kMaxSlots = 12;
 constexpr int kUnitsPerTile = 8;           // 4 K chunks + 4 V chunks
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRaiseThreshold = 8.0f;
 
 constexpr int kSlotBytes = kBK * 64 * 2;       // [128 keys][64 head-dim], 128-byte rows: 16384
-constexpr int kQBytes = kRows * kHD * 2;       // 4 sub-tiles [64 rows][64 head-dim]
-constexpr int kQSub = kRows * 64 * 2;          // 8192
-constexpr int kOffRing = kQBytes;
-constexpr int kOffMisc = kOffRing + kSlots * kSlotBytes;
+// Geometry for ROWS packed query rows (64 or 128): one softmax warp per 32 rows, then the producer warp
+// and the MMA warp; Q and the ring share the shared memory, so 128 rows leave ten slots instead of twelve.
+template <int ROWS>
+struct VerifyGeom {
+    static constexpr int kSoftmaxWarps = ROWS / 32;
+    static constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;
+    static constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
+    static constexpr int kSlots = ROWS == 64 ? 12 : 10;        // even: a V pair never wraps
+    static constexpr int kQBytes = ROWS * kHD * 2;             // 4 sub-tiles [ROWS][64 head-dim]
+    static constexpr int kQSub = ROWS * 64 * 2;
+    static constexpr int kOffRing = kQBytes;
+    static constexpr int kOffMisc = kOffRing + kSlots * kSlotBytes;
+};
 
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 256;     // S: two tiles of 128 columns
 
 struct Misc {
-    uint64_t full[kSlots], empty[kSlots];
+    uint64_t full[kMaxSlots], empty[kMaxSlots];
     uint64_t s_full[2];
     uint64_t p_ready[2];        // count 2: one arrive per softmax warp
     uint64_t o_ready[2];        // [tile parity]: P.V of the tile has retired. Two barriers, because the softmax threads
@@ -63,8 +70,10 @@ struct Misc {
     uint32_t tmem_base;
     uint32_t pad;
 };
-constexpr int kSmemBytes = kOffMisc + (int)sizeof(Misc) + 1024 /*align*/;
-static_assert(kSmemBytes <= 232448, "the verify kernel's shared memory exceeds the per-CTA limit");
+template <int ROWS>
+constexpr int verify_smem_bytes() { return VerifyGeom<ROWS>::kOffMisc + (int)sizeof(Misc) + 1024 /*align*/; }
+static_assert(verify_smem_bytes<64>() <= 232448 && verify_smem_bytes<128>() <= 232448,
+              "the verify kernel's shared memory exceeds the per-CTA limit");
 
 struct VerifyParams {
     const TTDecodeItem *items;
@@ -91,15 +100,17 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 // Up to kVerifyParamSessions sessions travel in the kernel parameters together with their tensor maps
 // (table.n != 0): nothing is uploaded before the launch, a CTA derives its item from the block index,
 // and the maps need no proxy fence. Larger batches read the tables the host copied to device memory.
-template <typename T>
-__global__ void __launch_bounds__(kThreads, 1)
+template <typename T, int ROWS>
+__global__ void __launch_bounds__(VerifyGeom<ROWS>::kThreads, 1)
 attn_verify_tc_kernel(VerifyParams p, uint32_t *__restrict__ status, const __grid_constant__ TTSessionTable table,
                       const __grid_constant__ TTVerifyMaps pmaps) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char *q_s = smem;
-    unsigned char *ring = smem + kOffRing;
-    Misc *ms = reinterpret_cast<Misc *>(smem + kOffMisc);
+    using G = VerifyGeom<ROWS>;
+    constexpr int kSlots = G::kSlots, kThreads = G::kThreads, kQSub = G::kQSub;
+    unsigned char *ring = smem + G::kOffRing;
+    Misc *ms = reinterpret_cast<Misc *>(smem + G::kOffMisc);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
@@ -127,7 +138,7 @@ attn_verify_tc_kernel(VerifyParams p, uint32_t *__restrict__ status, const __gri
         ses = p.sessions[item.session];
     }
     const uint32_t group = p.n_q_heads / p.n_kv_heads;
-    const uint32_t n_rows = ses.q_rows * group;                    // packed rows in use (<= 64)
+    const uint32_t n_rows = ses.q_rows * group;                    // packed rows in use (<= ROWS)
     const uint32_t n_tiles = (item.key_end - item.key_begin + kBK - 1) / kBK;
     const uint32_t rows_total = ses.q_rows * p.n_q_heads;
 
@@ -154,7 +165,7 @@ attn_verify_tc_kernel(VerifyParams p, uint32_t *__restrict__ status, const __gri
     // ahead of the ring fill because the first product waits for Q as well as for K(0)
     {
         const T *q = reinterpret_cast<const T *>(ses.q);
-        for (uint32_t c = threadIdx.x; c < kRows * (kHD / 8); c += kThreads) {
+        for (uint32_t c = threadIdx.x; c < ROWS * (kHD / 8); c += kThreads) {
             const uint32_t r = c / (kHD / 8), chunk = c % (kHD / 8);       // 16-byte chunk of the row
             const uint32_t sub = chunk >> 3, cc = chunk & 7;
             unsigned char *dst = q_s + sub * kQSub + r * 128 + ((cc ^ (r & 7)) << 4);
@@ -170,10 +181,10 @@ attn_verify_tc_kernel(VerifyParams p, uint32_t *__restrict__ status, const __gri
     }
     // The first ring fill leaves before the CTA-wide sync so that it overlaps the arrival of Q (the
     // thread that initialises the barriers is the one that uses them first).
-    if (threadIdx.x == 64) {
+    if (threadIdx.x == G::kProducerWarp * 32) {
         for (int s = 0; s < kSlots; ++s) { mbar_init(&ms->full[s], 1); mbar_init(&ms->empty[s], 1); }
         mbar_init(&ms->s_full[0], 1); mbar_init(&ms->s_full[1], 1);
-        mbar_init(&ms->p_ready[0], 2); mbar_init(&ms->p_ready[1], 2);
+        mbar_init(&ms->p_ready[0], G::kSoftmaxWarps); mbar_init(&ms->p_ready[1], G::kSoftmaxWarps);
         mbar_init(&ms->o_ready[0], 1); mbar_init(&ms->o_ready[1], 1);
         mbar_fence_init();
         if (n_tiles > 0) {
@@ -185,7 +196,7 @@ attn_verify_tc_kernel(VerifyParams p, uint32_t *__restrict__ status, const __gri
             for (uint32_t u = 0; u < (uint32_t)kSlots && u < n_units; ++u) load_unit(u);
         }
     }
-    if (warp == 2) {
+    if (warp == G::kProducerWarp) {
         __syncwarp();
         tmem_alloc(&ms->tmem_base, kTmemCols);
     }
@@ -198,7 +209,7 @@ attn_verify_tc_kernel(VerifyParams p, uint32_t *__restrict__ status, const __gri
     const uint32_t tmem = ms->tmem_base;
     bool failed = false;
 
-    if (warp == 2) {
+    if (warp == G::kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             bool ok = true;
@@ -215,7 +226,7 @@ attn_verify_tc_kernel(VerifyParams p, uint32_t *__restrict__ status, const __gri
             }
             failed = !ok;
         }
-    } else if (warp == 3) {
+    } else if (warp == G::kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0 && n_tiles > 0) {
             const uint32_t ring_a = smem_u32(ring), q_a = smem_u32(q_s);
@@ -416,7 +427,7 @@ attn_verify_tc_kernel(VerifyParams p, uint32_t *__restrict__ status, const __gri
     if (failed) atomicOr(status, TT_DEV_WAIT_TIMEOUT);
     tc_fence_before();
     __syncthreads();
-    if (warp == 2) {
+    if (warp == G::kProducerWarp) {
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
@@ -445,7 +456,8 @@ int tt_verify_tc_encode_maps(tt_context *ctx, uint32_t n_sessions, const tt_attn
 // Pass 1 of a verify batch on the tensor cores: the items (one per (session, kv head, key range), all
 // packed rows at once), the sessions and the tensor maps are already on the device.
 int tt_launch_verify_tc(tt_context *ctx, cudaStream_t stream, uint32_t n_sessions, uint32_t n_items, float *part_o,
-                        float *part_m, float *part_l, const tt_attn_batch_params *p, bool direct, bool in_params) {
+                        float *part_m, float *part_l, const tt_attn_batch_params *p, bool direct, bool in_params,
+                        bool rows128) {
     (void)n_sessions;
     static thread_local TTSessionTable no_table;       // n == 0: the kernel reads the device tables
     no_table.n = 0;
@@ -460,16 +472,19 @@ int tt_launch_verify_tc(tt_context *ctx, cudaStream_t stream, uint32_t n_session
     kp.scale_log2 = p->scale * kLog2e;
     kp.idesc_qk = tt_make_idesc_f16(p->io_dtype, kBK, false);        // Q (K-major) x K rows (K-major), N = 128 keys
     kp.idesc_pv = tt_make_idesc_f16(p->io_dtype, kHD / 2, true);     // P (TMEM) x V (MN-major), N = 128 head dims
-    if (p->io_dtype == TT_F16) {
-        auto kernel = attn_verify_tc_kernel<__half>;
-        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return tt_check_cuda(ctx, e, "verify smem attribute");
-        e = tt_launch_pdl(kernel, dim3(n_items), dim3(kThreads), (size_t)kSmemBytes, stream, kp, ctx->status, table, ctx->verify_maps);
+    auto launch = [&](auto kernel, int threads, int smem) {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (err != cudaSuccess) return err;
+        return tt_launch_pdl(kernel, dim3(n_items), dim3(threads), (size_t)smem, stream, kp, ctx->status, table, ctx->verify_maps);
+    };
+    if (rows128) {
+        constexpr int kT = VerifyGeom<128>::kThreads, kS = verify_smem_bytes<128>();
+        e = p->io_dtype == TT_F16 ? launch(attn_verify_tc_kernel<__half, 128>, kT, kS)
+                                  : launch(attn_verify_tc_kernel<__nv_bfloat16, 128>, kT, kS);
     } else {
-        auto kernel = attn_verify_tc_kernel<__nv_bfloat16>;
-        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return tt_check_cuda(ctx, e, "verify smem attribute");
-        e = tt_launch_pdl(kernel, dim3(n_items), dim3(kThreads), (size_t)kSmemBytes, stream, kp, ctx->status, table, ctx->verify_maps);
+        constexpr int kT = VerifyGeom<64>::kThreads, kS = verify_smem_bytes<64>();
+        e = p->io_dtype == TT_F16 ? launch(attn_verify_tc_kernel<__half, 64>, kT, kS)
+                                  : launch(attn_verify_tc_kernel<__nv_bfloat16, 64>, kT, kS);
     }
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return tt_check_cuda(ctx, e, "attn_verify_tc launch");
