@@ -894,7 +894,7 @@ cudaError_t launch_partial_nt(cudaStream_t stream, uint32_t n_items, const TTDec
                               const TTSessionTable &table, uint32_t table_keys) {
     auto kernel = attn_decode_partial_kernel<HD, NT, HPC, T>;
     const int smem = DecodeSmem<HD, HPC>::kTotal;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = tt_set_smem_once(kernel, smem);
     if (e != cudaSuccess) return e;
     return tt_launch_pdl(kernel, dim3(n_items), dim3(64 * HPC), (size_t)smem, stream, items, sessions, part_o, part_m, part_l,
                          p->n_q_heads, p->n_kv_heads, p->kv_token_stride_elements * 2u, p->q_row_stride_elements,
@@ -921,7 +921,7 @@ cudaError_t launch_partial_quant_one(cudaStream_t stream, uint32_t n_items, cons
                                      uint32_t table_keys, const TTKvQuant *quant, uint32_t meta_bytes) {
     auto kernel = attn_decode_partial_quant_kernel<HD, BITS>;
     const int smem = QuantSmem<HD, BITS>::kTotal;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = tt_set_smem_once(kernel, smem);
     if (e != cudaSuccess) return e;
     return tt_launch_pdl(kernel, dim3(n_items), dim3(64), (size_t)smem, stream, items, sessions, part_o, part_m, part_l,
                          p->n_q_heads, p->n_kv_heads, quant->stride_bytes, p->q_row_stride_elements, p->scale * kLog2e,

@@ -473,7 +473,7 @@ int tt_launch_verify_tc(tt_context *ctx, cudaStream_t stream, uint32_t n_session
     kp.idesc_qk = tt_make_idesc_f16(p->io_dtype, kBK, false);        // Q (K-major) x K rows (K-major), N = 128 keys
     kp.idesc_pv = tt_make_idesc_f16(p->io_dtype, kHD / 2, true);     // P (TMEM) x V (MN-major), N = 128 head dims
     auto launch = [&](auto kernel, int threads, int smem) {
-        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t err = tt_set_smem_once(kernel, smem);
         if (err != cudaSuccess) return err;
         return tt_launch_pdl(kernel, dim3(n_items), dim3(threads), (size_t)smem, stream, kp, ctx->status, table, ctx->verify_maps);
     };

@@ -1,4 +1,5 @@
 // Context: device binding, one-time scratch allocation, error reporting.
+#include <mutex>
 #include "tt_common.h"
 
 #include <cstdlib>
@@ -43,6 +44,27 @@ TT_API const char *tt_last_error_string(const tt_context *ctx) { return ctx ? ct
 // Lays the three tables of a decode call out back to back (128-byte aligned) in the host staging
 // buffer and, identically, in the device buffer: sessions, then (verify batches) two tensor maps per
 // session, then the items.
+cudaError_t tt_set_smem_once_impl(const void *kernel, int smem) {
+    struct Entry { const void *fn; int dev; int smem; };
+    static Entry table[256];
+    static int n = 0;
+    static std::mutex lock;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> guard(lock);
+    for (int i = 0; i < n; ++i)
+        if (table[i].fn == kernel && table[i].dev == dev) {
+            if (table[i].smem >= smem) return cudaSuccess;
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e == cudaSuccess) table[i].smem = smem;
+            return e;
+        }
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess && n < 256) table[n++] = Entry{kernel, dev, smem};
+    return e;
+}
+
 void tt_bind_decode_tables(tt_context *ctx, uint32_t n_sessions, bool with_maps) {
     const size_t off_maps = (sizeof(TTDecodeSession) * n_sessions + 127) / 128 * 128;
     const size_t off_items = off_maps + (with_maps ? (size_t)256 * n_sessions : 0);

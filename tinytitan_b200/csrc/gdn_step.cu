@@ -462,7 +462,7 @@ int launch_step(tt_context *ctx, cudaStream_t stream, const tt_gdn_session *h_se
                                           kTokDepth * (2 * shape->key_dim + kRowsPerWarp + 4) * sizeof(__half));
     TTLaunchTimer timer(ctx, stream, TT_PROFILE_GDN_STEP);
     auto launch = [&](auto kernel) {
-        cudaError_t le = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t le = tt_set_smem_once(kernel, (int)smem);
         if (le != cudaSuccess) return le;
         return tt_launch_pdl(kernel, dim3(grid), dim3(kWarps * 32), smem, stream, p, n, n_items, ctx->status, ptab);
     };

@@ -146,6 +146,12 @@ cudaError_t tt_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Opt-in dynamic shared memory of a kernel, set once per (kernel, device) instead of on every launch: the
+// attribute call is a host round trip of its own at the start of every decode step. Implemented in context.cu.
+cudaError_t tt_set_smem_once_impl(const void *kernel, int smem);
+template <typename K>
+cudaError_t tt_set_smem_once(K kernel, int smem) { return tt_set_smem_once_impl(reinterpret_cast<const void *>(kernel), smem); }
+
 struct TTBusyGuard {
     tt_context *ctx;
     bool ok;
