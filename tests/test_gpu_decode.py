@@ -70,6 +70,29 @@ def test_shapes_normal_inputs(hd, hq, hkv, s):
     assert np.abs(got - want).max() <= TOL
 
 
+def test_gqa_head_mapping_by_permutation():
+    # CPUEngineTests.swift:730-825: query head h reads KV head h / (Hq / Hkv). Swapping the KV heads of the cache
+    # must give exactly the outputs of the original cache with the two query-head groups swapped (same kernel,
+    # same arithmetic per head, so bit for bit), on the decode kernel and on the tensor-core verify kernel.
+    r = np.random.default_rng(730)
+    hq, hkv, hd, s = 16, 2, 256, 777
+    g = hq // hkv
+    q = rounded(r.normal(size=(hq, hd)))
+    k = rounded(r.normal(size=(s, hkv, hd))); v = rounded(r.normal(size=(s, hkv, hd)))
+    base = _decode(q, k.reshape(s, -1), v.reshape(s, -1), hkv, scale=0.0625)
+    q_swapped = np.concatenate([q[g:], q[:g]])
+    swapped = _decode(q_swapped, k[:, ::-1].reshape(s, -1).copy(), v[:, ::-1].reshape(s, -1).copy(), hkv, scale=0.0625)
+    assert np.array_equal(np.concatenate([swapped[g:], swapped[:g]]), base)
+    # a changed KV head 1 leaves the outputs of the heads that read KV head 0 alone
+    v2 = v.copy(); v2[:, 1] += 1.0
+    moved = _decode(q, k.reshape(s, -1), rounded(v2).reshape(s, -1), hkv, scale=0.0625)
+    assert np.array_equal(moved[:g], base[:g]) and not np.array_equal(moved[g:], base[g:])
+    # the same through the verify kernel (4 draft rows x 32 heads: 64 packed rows per KV head)
+    rr = np.random.default_rng(731)
+    got, want = _verify_batch(rr, 32, 2, 4, [900])
+    assert np.all(np.abs(got[0] - want[0]) <= TOL)
+
+
 def test_sliding_window_ring_and_keep_mask():
     r = np.random.default_rng(7)
     hd, hq, hkv, s = 256, 16, 2, 900
