@@ -93,7 +93,9 @@ def tc_case(r, start, chunk, hq, hkv, window=0, dtype=torch.float16, pad=0, extr
     (77, 200, 2, 1, 0, 0, 0), (0, 513, 2, 1, 0, 0, 0), (130, 129, 4, 1, 100, 0, 5), (0, 1024, 16, 2, 0, 0, 0),
     # around the 128-key tile and the 64-key halves the two softmax groups and the V loads work in
     (0, 127, 2, 1, 0, 0, 0), (0, 255, 2, 1, 0, 0, 0), (0, 257, 2, 2, 0, 0, 0), (128, 128, 2, 1, 0, 0, 0),
-    (65, 190, 2, 1, 0, 0, 0), (0, 600, 2, 1, 200, 0, 0), (300, 77, 2, 1, 65, 8, 3)])
+    (65, 190, 2, 1, 0, 0, 0), (0, 600, 2, 1, 200, 0, 0), (300, 77, 2, 1, 65, 8, 3),
+    # the last boundary of PrefillAttentionTests.swift:144-180 (1 ... 1025 keys)
+    (0, 1025, 2, 1, 0, 0, 0)])
 def test_tcgen05_kernel_matches_oracle(start, chunk, hq, hkv, window, pad, extra):
     r = np.random.default_rng(start * 7 + chunk)
     q, k, v, p = tc_case(r, start, chunk, hq, hkv, window, pad=pad, extra_valid=extra)
