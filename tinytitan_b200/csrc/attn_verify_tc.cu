@@ -11,20 +11,21 @@
 //                              same score tile (two 16-bit weights per column)
 //   O      += P_j . V_j        TS MMA  M128 N128 (head-dim half) K16 x8, twice      columns 256..511
 //
-// Only the 64 packed rows exist: the M128 instructions read rows 64..127 of the Q operand from
-// whatever follows Q in shared memory and leave the result in TMEM lanes 64..127, which nothing
-// reads. Keeping Q as the only resident operand in shared memory (32 KB) and P in TMEM leaves
-// 192 KB for ONE ring of twelve 16 KB slots that K ([128 keys][64 head-dim] chunks) and V (the same
-// boxes, consumed in adjacent pairs) travel through in the order the MMAs consume them:
-// K(0) K(1) V(0) K(2) V(1) ... The kernel is bound by the bytes it keeps in flight per SM, and this
-// ring holds a tile and a half more than separate K and V rings next to a P buffer did.
+// Two geometries. Up to 64 packed rows: only those rows exist; the M128 instructions read rows 64..127
+// of the Q operand from whatever follows Q in shared memory and leave the result in TMEM lanes
+// 64..127, which nothing reads. Keeping Q as the only resident operand in shared memory (32 KB) and
+// P in TMEM leaves 192 KB for ONE ring of twelve 16 KB slots that K ([128 keys][64 head-dim] chunks)
+// and V (the same boxes, consumed in adjacent pairs) travel through in the order the MMAs consume
+// them: K(0) K(1) V(0) K(2) V(1) ... The kernel is bound by the bytes it keeps in flight per SM, and
+// this ring holds a tile and a half more than separate K and V rings next to a P buffer did.
+// 65..128 packed rows: Q takes 64 KB, the ring ten slots, and four softmax warps own the 128 lanes.
 //
-// Warps 0 and 1 are the softmax (row = thread), lane 0 of warp 2 is the TMA producer, lane 0 of
-// warp 3 issues the MMAs; warp 2 owns the TMEM allocation. The reference maximum of a row is only
-// raised when a score exceeds it by more than 2^8; the raise rescales the row of O in TMEM (after
-// P.V of the previous tile has retired). The row sum is taken on the ROUNDED weights. Each CTA
-// writes one unnormalised (m, l, o) partial per packed row, in the layout the split-KV combine
-// kernel merges, or the finished rows when its item is the whole key range of the session.
+// One softmax warp per 32 packed rows (row = thread), then the producer warp (lane 0 issues the TMA
+// loads; the warp owns the TMEM allocation) and the MMA warp (lane 0 issues). The reference maximum
+// of a row is only raised when a score exceeds it by more than 2^8; the raise rescales the row of O
+// in TMEM (after P.V of the previous tile has retired). The row sum is taken on the ROUNDED weights.
+// Each CTA writes one unnormalised (m, l, o) partial per packed row, in the layout the split-KV
+// combine kernel merges, or the finished rows when its item is the whole key range of the session.
 //
 // Semantics: attention.metal:162-269 (partial pass over a key range, row r of a W-row group
 // masked at seq_len - (W-1-r)); every mbarrier wait is bounded.
